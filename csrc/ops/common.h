@@ -1,0 +1,96 @@
+// Shared helpers of the operator layer.
+//
+// Every operator wrapper follows the same steps the reference's generated
+// CnnlOps layer does (torch_mlu/tools/template/cnnl_ops.cpp:38-113,
+// gen.py:73-81): switch to the tensor's device, log the arguments at DEBUG
+// level, optionally dump inputs, run the device kernel, on failure re-run the
+// op on the CPU, optionally synchronise.  Here that is one RAII object and one
+// macro instead of five generated class layers.
+#pragma once
+#include <ATen/ATen.h>
+#include <ATen/native/CPUFallback.h>
+#include <torch/library.h>
+
+#include "../runtime/caching_allocator.h"
+#include "../runtime/device.h"
+#include "../runtime/log.h"
+#include "../runtime/queue.h"
+#include "../runtime/tensor_impl.h"
+
+namespace catch_b200 {
+namespace ops {
+
+// Boxed CPU fallback used for unregistered ops and as the per-op safety net.
+void cpu_fallback(const c10::OperatorHandle& op, torch::jit::Stack* stack);
+
+// True when operators must not launch device kernels: host simulation or the
+// force-CPU test mode.
+inline bool use_cpu_path() { return hostsim() || flags().test_cpu_dispatch; }
+
+// Sets the device of `t` current for the lifetime of the scope, logs the op
+// name, and synchronises on exit when CATCH_B200_ASYNC_DISABLE is set.
+class OpScope {
+ public:
+  OpScope(const char* name, const at::Tensor& t);
+  OpScope(const char* name, int device);
+  ~OpScope() noexcept(false);
+  int device() const { return device_; }
+  Queue queue() const { return getCurrentQueue(device_); }
+  void* stream() const { return getCurrentQueue(device_).handle(); }
+
+ private:
+  const char* name_;
+  int device_;
+  DeviceSwitch sw_;
+};
+
+// Hook for the dump tool: called with the op name and its tensor arguments /
+// results when dumping is active (see runtime/dumper.h).
+bool dump_active();
+void dump_op_begin(const char* name);
+void dump_tensor(const char* label, const at::Tensor& t);
+void dump_op_end();
+
+std::string describe(const at::Tensor& t);  // "Float[2, 3]{strides}@b200:0"
+
+// Workspace from the caching allocator, freed (stream-ordered) on scope exit.
+class Workspace {
+ public:
+  Workspace(size_t bytes, const OpScope& s) : ptr_(bytes ? raw_alloc(bytes, s.device(), s.queue()) : nullptr) {}
+  ~Workspace() {
+    if (ptr_) raw_free(ptr_);
+  }
+  void* get() const { return ptr_; }
+  template <typename T>
+  T* as() const { return static_cast<T*>(ptr_); }
+
+ private:
+  void* ptr_;
+};
+
+// Runs `device_expr`; when it throws and per-op try/catch is enabled, logs the
+// failure and evaluates `cpu_expr` instead (reference: ENABLE_CNNL_TRYCATCH).
+#define B200_DISPATCH(opname, device_expr, cpu_expr)                                        \
+  [&]() {                                                                                   \
+    if (::catch_b200::ops::use_cpu_path()) return cpu_expr;                                 \
+    if (!::catch_b200::flags().op_trycatch) return device_expr;                             \
+    try {                                                                                   \
+      return device_expr;                                                                   \
+    } catch (const c10::OutOfMemoryError&) {                                                \
+      throw;                                                                                \
+    } catch (const std::exception& e) {                                                     \
+      B200LOG(WARNING) << opname << " failed on the device (" << e.what()                   \
+                       << "); running it on the CPU instead.";                              \
+      return cpu_expr;                                                                      \
+    }                                                                                       \
+  }()
+
+// Calls the boxed CPU fallback for one ATen overload with unboxed arguments,
+// e.g. B200_CPU(add_Tensor, self, other, alpha).
+#define B200_CPU(OP, ...) \
+  at::native::call_fallback_fn<&::catch_b200::ops::cpu_fallback, at::_ops::OP>::call(__VA_ARGS__)
+#define B200_CPU_SYMINT(OP, ...) \
+  at::native::call_fallback_fn_symint<&::catch_b200::ops::cpu_fallback, at::_ops::OP>::call(__VA_ARGS__)
+
+}  // namespace ops
+}  // namespace catch_b200

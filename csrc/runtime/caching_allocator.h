@@ -1,0 +1,67 @@
+// Per-device, queue-aware caching allocator for device memory.
+//
+// Capability parity with torch_mlu/csrc/aten/core/caching_allocator.cpp
+// (constants :58-69, stats :97-124, malloc/free :330-425, recordQueue :578-599,
+// debug allocator :612-762, public API :805-886):
+//   * 512-byte rounding, requests <= 1 MiB are carved from 2 MiB segments,
+//     bigger ones from segments of at least 20 MiB (or exact 2 MiB multiples)
+//   * best-fit lookup per (queue, size), split on allocation, merge on free
+//   * a block used on other queues (recordQueue) is returned to the pool only
+//     after notifiers placed on those queues have been reached
+//   * out-of-memory: release all cached segments and retry once, then raise
+//     an error that lists the totals
+//   * statistics: allocated / max_allocated / reserved(cached) / max_reserved
+//   * optional debug mode: guard regions before and after each block that are
+//     verified when the block is freed and on demand
+// The data structures are this project's own (intrusive doubly linked segment
+// lists plus two ordered sets per device).
+#pragma once
+#include <c10/core/Allocator.h>
+#include <cstddef>
+#include <cstdint>
+#include <string>
+#include <vector>
+#include "queue.h"
+
+namespace catch_b200 {
+
+struct MemoryStats {
+  int64_t allocated = 0;
+  int64_t max_allocated = 0;
+  int64_t reserved = 0;
+  int64_t max_reserved = 0;
+  int64_t num_alloc = 0;
+  int64_t num_free = 0;
+  int64_t num_segments = 0;
+  int64_t num_ooms = 0;
+  int64_t num_retries = 0;
+};
+
+struct DebugReport {
+  int64_t blocks_checked = 0;
+  int64_t corrupted = 0;
+  std::string detail;  // one line per corrupted block
+};
+
+c10::Allocator* getB200CachingAllocator();
+
+// Raw interface used by operators for workspaces.
+void* raw_alloc(size_t bytes, int device, const Queue& q);
+void raw_free(void* ptr);
+
+void recordQueue(const c10::DataPtr& ptr, const Queue& q);
+void recordQueueRaw(void* ptr, const Queue& q);
+void emptyCache();
+MemoryStats memoryStats(int device);
+void resetPeakStats(int device);
+// true = allocate exactly what is asked from the driver (no over-sized
+// segments); false (default) = cache-friendly segment sizes.
+void setNativeMemoryStrategy(bool native);
+bool nativeMemoryStrategy();
+// Debug allocator: enable before the first allocation (or via the environment).
+void setMemoryDebug(bool on);
+bool memoryDebugEnabled();
+DebugReport memoryDebugCheck(const void* ptr = nullptr);  // nullptr = every live block
+std::string memorySummary(int device);
+
+}  // namespace catch_b200
