@@ -1,0 +1,568 @@
+// Implicit-GEMM convolution (forward / data gradient) and weight gradient on
+// tcgen05 tensor cores with tensor-memory accumulators.
+//
+// Replaces cnnlConvolutionForward / BackwardData / BackwardFilter of the reference
+// (torch_mlu/csrc/aten/operators/cnnl/internal/convolution_float_forward_internal.cpp:136,
+// convolution_float_backward_internal.cpp:89,162).
+//
+// Forward (and dgrad):  M = 128 output pixels (a BW x BH x BNI box of the pixel
+// grid), N = tile_n output channels, K loop = taps x 64-channel blocks.  Warp roles
+// are those of the GEMM kernel (TMA producer / MMA issuer / 4 epilogue warps, two
+// accumulator buffers).  The A tile of a tap is ONE 4-D tiled tensor-map load whose
+// origin is the tile's pixel origin plus the tap offset; halo elements outside the
+// view are zero-filled by the copy engine, so no im2col buffer exists anywhere.
+//
+// Wgrad: M = 128 output channels, N = up to four 64-wide blocks of the flattened
+// (tap, input-channel) axis, K = pixels (64 per stage).  Both operands are MN-major
+// (channels contiguous) straight out of the NHWC tensors.  CTAs split the pixel
+// range and add their partial tiles to an fp32 buffer.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include "kernels_api.h"
+#include "tcgen05.cuh"
+#include "tma_util.cuh"
+
+namespace b200 {
+
+constexpr int CONV_THREADS = 192;
+constexpr int CONV_MAX_STAGES = 8;
+constexpr int CONV_A_BYTES = 128 * 128;
+
+struct ConvArgs {
+  int N, P, Q, Cin, Cout;
+  int bw, bh, bni;              // pixel box (bw*bh*bni == 128)
+  int tiles_q, tiles_p, tiles_n, tiles_co, tile_n;
+  int c_blocks;                 // Cin / 64 (rounded up)
+  int ntaps, stages, b_mn;
+  uint32_t idesc;
+  B200ConvTap taps[B200_CONV_MAX_TAPS];
+  void* out;
+  int out_dtype;
+  long long o_sn, o_sh, o_sw;
+  int o_mul_h, o_off_h, o_mul_w, o_off_w;
+  const float* scale;
+  const void* bias;
+  int bias_dtype;
+  const void* residual;
+  int res_dtype;
+  int act;
+  int* err;
+};
+
+struct ConvMaps {
+  CUtensorMap a[B200_CONV_MAX_MAPS];
+  CUtensorMap w;
+};
+
+__device__ __forceinline__ float ld_scalar(const void* p, long long i, int dt) {
+  if (dt == B200_F32) return static_cast<const float*>(p)[i];
+  if (dt == B200_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  return __half2float(static_cast<const __half*>(p)[i]);
+}
+
+__global__ void __launch_bounds__(CONV_THREADS, 1)
+conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int stage_bytes = CONV_A_BYTES + g.tile_n * 128;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)g.stages * stage_bytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + CONV_MAX_STAGES;
+  uint64_t* acc_full = bars + 2 * CONV_MAX_STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < g.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
+    mbar_fence_init();
+    tma_prefetch_desc(&maps.w);
+    tma_prefetch_desc(&maps.a[0]);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int pix_tiles = g.tiles_q * g.tiles_p * g.tiles_n;
+  const int total_tiles = pix_tiles * g.tiles_co;
+  const int k_iters = g.ntaps * g.c_blocks;
+  bool failed = false;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+        // pixel tiles vary fastest so concurrently running CTAs share the weight tile
+        const int pt = tile % pix_tiles, ct = tile / pix_tiles;
+        const int q0 = (pt % g.tiles_q) * g.bw;
+        const int p0 = ((pt / g.tiles_q) % g.tiles_p) * g.bh;
+        const int n0 = (pt / (g.tiles_q * g.tiles_p)) * g.bni;
+        const int co0 = ct * g.tile_n;
+        for (int it = 0; it < k_iters; ++it) {
+          const int tap = it / g.c_blocks, cb = it - tap * g.c_blocks;
+          const B200ConvTap tp = g.taps[tap];
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, g.err, ERR_TIMEOUT_EMPTY)) { failed = true; break; }
+          mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)stage_bytes);
+          uint8_t* sa = smem + (size_t)stage * stage_bytes;
+          tma_load_4d(sa, &maps.a[tp.map], &full_bar[stage], cb * 64, q0 + tp.dw, p0 + tp.dh, n0);
+          if (!g.b_mn) {
+            tma_load_3d(sa + CONV_A_BYTES, &maps.w, &full_bar[stage], cb * 64, co0, tp.wtap);
+          } else {
+            for (int j = 0; j < g.tile_n / 64; ++j)
+              tma_load_3d(sa + CONV_A_BYTES + j * 8192, &maps.w, &full_bar[stage], co0 + j * 64, cb * 64, tp.wtap);
+          }
+          if (++stage == g.stages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, g.err, ERR_TIMEOUT_TMEM_EMPTY)) { failed = true; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * 256;
+        for (int it = 0; it < k_iters; ++it) {
+          if (!mbar_wait(&full_bar[stage], phase, g.err, ERR_TIMEOUT_FULL)) { failed = true; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + (size_t)stage * stage_bytes);
+          const uint32_t sb = sa + CONV_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t bdesc = g.b_mn ? make_smem_desc_sw128(sb + k * 2048, 8192, 1024)
+                                          : make_smem_desc_sw128(sb + k * 32, 16, 1024);
+            umma_f16(d_tmem, make_smem_desc_sw128(sa + k * 32, 16, 1024), bdesc, g.idesc,
+                     (it > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == g.stages) { stage = 0; phase ^= 1; }
+        }
+        if (failed) break;
+        umma_commit(&acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    int acc = 0; uint32_t acc_phase = 0;
+    const int esz = g.out_dtype == B200_F32 ? 4 : 2;
+    const int rsz = g.res_dtype == B200_F32 ? 4 : 2;
+    for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+      const int pt = tile % pix_tiles, ct = tile / pix_tiles;
+      const int q0 = (pt % g.tiles_q) * g.bw;
+      const int p0 = ((pt / g.tiles_q) % g.tiles_p) * g.bh;
+      const int n0 = (pt / (g.tiles_q * g.tiles_p)) * g.bni;
+      const int co0 = ct * g.tile_n;
+      const int r = quarter * 32 + lane;
+      const int q = q0 + r % g.bw, p = p0 + (r / g.bw) % g.bh, n = n0 + r / (g.bw * g.bh);
+      const bool row_ok = q < g.Q && p < g.P && n < g.N;
+      const long long off = (long long)n * g.o_sn + (long long)(p * g.o_mul_h + g.o_off_h) * g.o_sh +
+                            (long long)(q * g.o_mul_w + g.o_off_w) * g.o_sw;
+      if (!mbar_wait(&acc_full[acc], acc_phase, g.err, ERR_TIMEOUT_TMEM_FULL)) { failed = true; break; }
+      tc_fence_after();
+      for (int c = 0; c < g.tile_n; c += 32) {
+        uint32_t rr[32];
+        tmem_ld32(tmem_base + acc * 256 + ((uint32_t)(quarter * 32) << 16) + c, rr);
+        tmem_ld_wait();
+        const int cbase = co0 + c;
+        if (!row_ok || cbase >= g.Cout) continue;
+        const int valid = min(32, g.Cout - cbase);
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rr[j]);
+        if (g.scale) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) if (j < valid) v[j] *= g.scale[cbase + j];
+        }
+        if (g.bias) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) if (j < valid) v[j] += ld_scalar(g.bias, cbase + j, g.bias_dtype);
+        }
+        if (g.residual) {
+          const uint8_t* rp = static_cast<const uint8_t*>(g.residual) + (off + cbase) * rsz;
+          if (valid == 32 && rsz == 2 && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
+            alignas(16) uint16_t hh[32];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(hh)[j] = reinterpret_cast<const uint4*>(rp)[j];
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              v[j] += g.res_dtype == B200_BF16 ? __bfloat162float(__ushort_as_bfloat16(hh[j]))
+                                               : __half2float(__ushort_as_half(hh[j]));
+          } else {
+            for (int j = 0; j < valid; ++j) v[j] += ld_scalar(g.residual, off + cbase + j, g.res_dtype);
+          }
+        }
+        if (g.act == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+        }
+        uint8_t* op = static_cast<uint8_t*>(g.out) + (off + cbase) * esz;
+        if (g.out_dtype == B200_F32) {
+          float* o = reinterpret_cast<float*>(op);
+          if (valid == 32 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+            for (int j = 0; j < valid; ++j) o[j] = v[j];
+          }
+        } else {
+          alignas(16) uint16_t h[32];
+          if (g.out_dtype == B200_BF16) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) h[j] = __bfloat16_as_ushort(__float2bfloat16(v[j]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) h[j] = __half_as_ushort(__float2half(v[j]));
+          }
+          uint16_t* o = reinterpret_cast<uint16_t*>(op);
+          if (valid == 32 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(o)[j] = reinterpret_cast<const uint4*>(h)[j];
+          } else {
+            for (int j = 0; j < valid; ++j) o[j] = h[j];
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  if (*((volatile int*)g.err) != 0) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// ------------------------------------------------------------------------- wgrad
+struct WgradArgs {
+  int N, P, Q, Cin, Cout;
+  int bw, bh, bni;               // pixel box, bw*bh*bni == 64
+  int tiles_q, tiles_p, tiles_n; // pixel chunks
+  int m_tiles;                   // ceil(Cout / 128)
+  int n_blocks_total;            // ntaps * (Cin / 64)
+  int n_blocks_per_tile;         // <= 4
+  int n_tiles;
+  int c_blocks;                  // Cin / 64
+  int splits, chunks_per_split;
+  int stages, ntaps;
+  uint32_t idesc;
+  B200ConvTap taps[B200_CONV_MAX_TAPS];
+  float* dw_acc;
+  long long dw_ld;               // wtaps * Cin
+  int* err;
+};
+struct WgradMaps {
+  CUtensorMap x[B200_CONV_MAX_MAPS];
+  CUtensorMap dy;
+};
+
+__global__ void __launch_bounds__(CONV_THREADS, 1)
+conv_wgrad_kernel(const __grid_constant__ WgradMaps maps, const __grid_constant__ WgradArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // stage: A = 2 blocks (128 out-channels) x (64 pixels x 128 B); B = n_blocks x 8 KB
+  const int blk_bytes = 64 * 128;
+  const int stage_bytes = 2 * blk_bytes + g.n_blocks_per_tile * blk_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)g.stages * stage_bytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + CONV_MAX_STAGES;
+  uint64_t* acc_full = bars + 2 * CONV_MAX_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < g.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&acc_full[0], 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&maps.dy);
+    tma_prefetch_desc(&maps.x[0]);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 256);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // One work item per CTA: (m tile, n tile, split).
+  const int item = blockIdx.x;
+  const int split = item % g.splits;
+  const int nt = (item / g.splits) % g.n_tiles;
+  const int mt = item / (g.splits * g.n_tiles);
+  const int total_chunks = g.tiles_q * g.tiles_p * g.tiles_n;
+  const int chunk_begin = split * g.chunks_per_split;
+  const int chunk_end = min(total_chunks, chunk_begin + g.chunks_per_split);
+  const int nb0 = nt * g.n_blocks_per_tile;
+  const int nblk = min(g.n_blocks_per_tile, g.n_blocks_total - nb0);
+  const int co0 = mt * 128;
+  bool failed = false;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      for (int ch = chunk_begin; ch < chunk_end; ++ch) {
+        const int q0 = (ch % g.tiles_q) * g.bw;
+        const int p0 = ((ch / g.tiles_q) % g.tiles_p) * g.bh;
+        const int n0 = (ch / (g.tiles_q * g.tiles_p)) * g.bni;
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1, g.err, ERR_TIMEOUT_EMPTY)) { failed = true; break; }
+        mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)((2 + nblk) * blk_bytes));
+        uint8_t* sa = smem + (size_t)stage * stage_bytes;
+        tma_load_4d(sa, &maps.dy, &full_bar[stage], co0, q0, p0, n0);
+        tma_load_4d(sa + blk_bytes, &maps.dy, &full_bar[stage], co0 + 64, q0, p0, n0);
+        for (int j = 0; j < nblk; ++j) {
+          const int nb = nb0 + j;
+          const int tap = nb / g.c_blocks, cb = nb - tap * g.c_blocks;
+          const B200ConvTap tp = g.taps[tap];
+          tma_load_4d(sa + (2 + j) * blk_bytes, &maps.x[tp.map], &full_bar[stage], cb * 64, q0 + tp.dw, p0 + tp.dh, n0);
+        }
+        if (++stage == g.stages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      for (int ch = chunk_begin; ch < chunk_end; ++ch) {
+        if (!mbar_wait(&full_bar[stage], phase, g.err, ERR_TIMEOUT_FULL)) { failed = true; break; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + (size_t)stage * stage_bytes);
+        const uint32_t sb = sa + 2 * blk_bytes;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          // MN-major operands: 16 pixels (K) per MMA = 2048 B; blocks of 64 channels 8 KB apart.
+          umma_f16(tmem_base, make_smem_desc_sw128(sa + k * 2048, blk_bytes, 1024),
+                   make_smem_desc_sw128(sb + k * 2048, blk_bytes, 1024), g.idesc, (ch > chunk_begin || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[stage]);
+        if (++stage == g.stages) { stage = 0; phase ^= 1; }
+      }
+      if (!failed) umma_commit(&acc_full[0]);
+    }
+  } else if (chunk_end > chunk_begin) {
+    const int quarter = warp & 3;
+    if (mbar_wait(&acc_full[0], 0, g.err, ERR_TIMEOUT_TMEM_FULL)) {
+      tc_fence_after();
+      const int co = co0 + quarter * 32 + lane;
+      const int ncols = nblk * 64;
+      for (int c = 0; c < g.n_blocks_per_tile * 64; c += 32) {
+        if (c >= ncols) break;
+        uint32_t rr[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c, rr);
+        tmem_ld_wait();
+        if (co >= g.Cout) continue;
+        // flattened column -> (tap slot, channel): blocks never straddle a tap
+        const int nb = nb0 + c / 64;
+        const int tap = nb / g.c_blocks, cb = nb - tap * g.c_blocks;
+        const int ci = cb * 64 + (c % 64);
+        if (ci >= g.Cin) continue;
+        float* dst = g.dw_acc + (long long)co * g.dw_ld + (long long)g.taps[tap].wtap * g.Cin + ci;
+        const int valid = min(32, g.Cin - ci);
+        if (g.splits == 1) {
+          for (int j = 0; j < valid; ++j) dst[j] = __uint_as_float(rr[j]);
+        } else if (valid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "r"(rr[j]), "r"(rr[j + 1]),
+                         "r"(rr[j + 2]), "r"(rr[j + 3])
+                         : "memory");
+          }
+        } else {
+          for (int j = 0; j < valid; ++j) atomicAdd(dst + j, __uint_as_float(rr[j]));
+        }
+      }
+    }
+  }
+  if (*((volatile int*)g.err) != 0) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
+}
+
+// Choose a power-of-two pixel box bw*bh*bni == total that wastes the fewest rows.
+static void pick_box(int total, int N, int P, int Q, int* bw, int* bh, int* bni) {
+  double best = 1e30;
+  for (int w = 1; w <= total; w *= 2) {
+    for (int h = 1; w * h <= total; h *= 2) {
+      const int n = total / (w * h);
+      if (w > 256 || h > 256 || n > 256) continue;
+      const double tiles = (double)((Q + w - 1) / w) * ((P + h - 1) / h) * ((N + n - 1) / n);
+      const double cost = tiles - 1e-3 * w - 1e-5 * h;  // ties: wider, then taller boxes
+      if (cost < best) { best = cost; *bw = w; *bh = h; *bni = n; }
+    }
+  }
+}
+
+static int encode_view(CUtensorMap* m, const B200ConvView& v, CUtensorMapDataType dt, int boxc, int bw, int bh, int bni) {
+  uint64_t dims[4] = {(uint64_t)v.dims[0], (uint64_t)v.dims[1], (uint64_t)v.dims[2], (uint64_t)v.dims[3]};
+  uint64_t str[3] = {(uint64_t)v.strides[0] * 2, (uint64_t)v.strides[1] * 2, (uint64_t)v.strides[2] * 2};
+  uint32_t box[4] = {(uint32_t)boxc, (uint32_t)bw, (uint32_t)bh, (uint32_t)bni};
+  return encode_tiled(m, dt, 4, v.base, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+static int set_smem_attr_once(const void* fn, int dev, bool* done) {
+  if (done[dev & 63]) return 0;
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+  if (e != cudaSuccess) return (int)e;
+  done[dev & 63] = true;
+  return 0;
+}
+
+}  // namespace b200
+
+extern "C" int b200_conv_fprop(const B200ConvParams* p, void* stream) {
+  using namespace b200;
+  if (p->N <= 0 || p->P <= 0 || p->Q <= 0 || p->Cout <= 0) return 0;
+  if (p->ntaps <= 0 || p->ntaps > B200_CONV_MAX_TAPS || p->num_views <= 0 || p->num_views > B200_CONV_MAX_MAPS)
+    return (int)cudaErrorInvalidValue;
+  if (p->Cin % 8 || p->ab_dtype == B200_F32) return (int)cudaErrorInvalidValue;
+  const CUtensorMapDataType dt = p->ab_dtype == B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+
+  ConvArgs g{};
+  g.N = p->N; g.P = p->P; g.Q = p->Q; g.Cin = p->Cin; g.Cout = p->Cout;
+  pick_box(128, p->N, p->P, p->Q, &g.bw, &g.bh, &g.bni);
+  g.tiles_q = (p->Q + g.bw - 1) / g.bw;
+  g.tiles_p = (p->P + g.bh - 1) / g.bh;
+  g.tiles_n = (p->N + g.bni - 1) / g.bni;
+  const long pix_tiles = (long)g.tiles_q * g.tiles_p * g.tiles_n;
+  if (p->tile_n > 0) {
+    g.tile_n = p->tile_n;
+  } else {
+    // widest tile that still leaves every SM with work; never wider than Cout needs
+    int tn = 256;
+    while (tn > 32 && (tn / 2 >= p->Cout || (pix_tiles * ((p->Cout + tn - 1) / tn) < sms && tn > 64))) tn /= 2;
+    if (p->Cout <= 32) tn = 32;
+    g.tile_n = tn;
+  }
+  g.b_mn = p->w_stride_n == 1 && p->w_stride_k != 1;
+  if (g.b_mn && g.tile_n < 64) g.tile_n = 64;
+  if (g.tile_n % 32 || g.tile_n > 256 || (g.b_mn && g.tile_n % 64)) return (int)cudaErrorInvalidValue;
+  g.tiles_co = (p->Cout + g.tile_n - 1) / g.tile_n;
+  g.c_blocks = (p->Cin + 63) / 64;
+  g.ntaps = p->ntaps;
+  for (int i = 0; i < p->ntaps; ++i) g.taps[i] = p->taps[i];
+  const int fmt = p->ab_dtype == B200_BF16 ? 1 : 0;
+  g.idesc = make_idesc(1, fmt, fmt, 0, g.b_mn, 128, g.tile_n);
+  g.out = p->out; g.out_dtype = p->out_dtype;
+  g.o_sn = p->o_sn; g.o_sh = p->o_sh; g.o_sw = p->o_sw;
+  g.o_mul_h = p->o_mul_h; g.o_off_h = p->o_off_h; g.o_mul_w = p->o_mul_w; g.o_off_w = p->o_off_w;
+  g.scale = static_cast<const float*>(p->scale);
+  g.bias = p->bias; g.bias_dtype = p->bias_dtype;
+  g.residual = p->residual; g.res_dtype = p->res_dtype; g.act = p->act;
+  g.err = error_flag_ptr();
+  if (!g.err) return (int)cudaErrorInvalidDevice;
+  const int stage_bytes = CONV_A_BYTES + g.tile_n * 128;
+  g.stages = (200 * 1024) / stage_bytes;
+  if (g.stages > CONV_MAX_STAGES) g.stages = CONV_MAX_STAGES;
+  if (g.stages < 2) g.stages = 2;
+
+  ConvMaps maps;
+  for (int i = 0; i < p->num_views; ++i) {
+    int rc = encode_view(&maps.a[i], p->views[i], dt, 64, g.bw, g.bh, g.bni);
+    if (rc) return rc;
+  }
+  for (int i = p->num_views; i < B200_CONV_MAX_MAPS; ++i) maps.a[i] = maps.a[0];
+  {
+    int rc;
+    if (!g.b_mn) {
+      uint64_t dims[3] = {(uint64_t)p->Cin, (uint64_t)p->Cout, (uint64_t)p->wtaps};
+      uint64_t str[2] = {(uint64_t)p->w_stride_n * 2, (uint64_t)p->w_stride_tap * 2};
+      uint32_t box[3] = {64, (uint32_t)g.tile_n, 1};
+      rc = encode_tiled(&maps.w, dt, 3, p->weight, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
+    } else {
+      uint64_t dims[3] = {(uint64_t)p->Cout, (uint64_t)p->Cin, (uint64_t)p->wtaps};
+      uint64_t str[2] = {(uint64_t)p->w_stride_k * 2, (uint64_t)p->w_stride_tap * 2};
+      uint32_t box[3] = {64, 64, 1};
+      rc = encode_tiled(&maps.w, dt, 3, p->weight, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
+    }
+    if (rc) return rc;
+  }
+  static bool attr_done[64] = {false};
+  int rc = set_smem_attr_once((const void*)conv_fprop_kernel, dev, attr_done);
+  if (rc) return rc;
+  const size_t smem = (size_t)g.stages * stage_bytes + 1024 + 256;
+  const long total_tiles = pix_tiles * g.tiles_co;
+  const int ctas = (int)(total_tiles < sms ? total_tiles : sms);
+  conv_fprop_kernel<<<ctas, CONV_THREADS, smem, (cudaStream_t)stream>>>(maps, g);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_conv_wgrad(const B200ConvWgradParams* p, void* stream) {
+  using namespace b200;
+  if (p->N <= 0 || p->P <= 0 || p->Q <= 0 || p->Cout <= 0 || p->Cin <= 0) return 0;
+  if (p->ntaps <= 0 || p->ntaps > B200_CONV_MAX_TAPS || p->num_views <= 0 || p->num_views > B200_CONV_MAX_MAPS)
+    return (int)cudaErrorInvalidValue;
+  if (p->Cin % 8 || p->Cout % 8 || p->ab_dtype == B200_F32) return (int)cudaErrorInvalidValue;
+  const CUtensorMapDataType dt = p->ab_dtype == B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+
+  WgradArgs g{};
+  g.N = p->N; g.P = p->P; g.Q = p->Q; g.Cin = p->Cin; g.Cout = p->Cout;
+  pick_box(64, p->N, p->P, p->Q, &g.bw, &g.bh, &g.bni);
+  g.tiles_q = (p->Q + g.bw - 1) / g.bw;
+  g.tiles_p = (p->P + g.bh - 1) / g.bh;
+  g.tiles_n = (p->N + g.bni - 1) / g.bni;
+  g.m_tiles = (p->Cout + 127) / 128;
+  g.c_blocks = (p->Cin + 63) / 64;
+  g.n_blocks_total = p->ntaps * g.c_blocks;
+  g.n_blocks_per_tile = g.n_blocks_total < 4 ? g.n_blocks_total : 4;
+  g.n_tiles = (g.n_blocks_total + g.n_blocks_per_tile - 1) / g.n_blocks_per_tile;
+  const long chunks = (long)g.tiles_q * g.tiles_p * g.tiles_n;
+  const long base_items = (long)g.m_tiles * g.n_tiles;
+  int splits = p->splits;
+  if (splits <= 0) {
+    splits = (int)((2L * sms + base_items - 1) / base_items);  // about two waves of CTAs
+    const long max_splits = (chunks + 15) / 16;                // at least 16 chunks per split
+    if (splits > max_splits) splits = (int)max_splits;
+    if (splits < 1) splits = 1;
+  }
+  if (splits > chunks) splits = (int)chunks;
+  g.chunks_per_split = (int)((chunks + splits - 1) / splits);
+  g.splits = (int)((chunks + g.chunks_per_split - 1) / g.chunks_per_split);
+  g.ntaps = p->ntaps;
+  for (int i = 0; i < p->ntaps; ++i) g.taps[i] = p->taps[i];
+  const int fmt = p->ab_dtype == B200_BF16 ? 1 : 0;
+  g.idesc = make_idesc(1, fmt, fmt, 1, 1, 128, g.n_blocks_per_tile * 64);
+  g.dw_acc = p->dw_acc;
+  g.dw_ld = (long long)p->wtaps * p->Cin;
+  g.err = error_flag_ptr();
+  if (!g.err) return (int)cudaErrorInvalidDevice;
+  const int stage_bytes = (2 + g.n_blocks_per_tile) * 64 * 128;
+  g.stages = (200 * 1024) / stage_bytes;
+  if (g.stages > CONV_MAX_STAGES) g.stages = CONV_MAX_STAGES;
+
+  WgradMaps maps;
+  for (int i = 0; i < p->num_views; ++i) {
+    int rc = encode_view(&maps.x[i], p->views[i], dt, 64, g.bw, g.bh, g.bni);
+    if (rc) return rc;
+  }
+  for (int i = p->num_views; i < B200_CONV_MAX_MAPS; ++i) maps.x[i] = maps.x[0];
+  {
+    B200ConvView v;
+    v.base = p->dy;
+    v.dims[0] = p->Cout; v.dims[1] = p->Q; v.dims[2] = p->P; v.dims[3] = p->N;
+    v.strides[0] = p->dy_sw; v.strides[1] = p->dy_sh; v.strides[2] = p->dy_sn;
+    int rc = encode_view(&maps.dy, v, dt, 64, g.bw, g.bh, g.bni);
+    if (rc) return rc;
+  }
+  static bool attr_done[64] = {false};
+  int rc = set_smem_attr_once((const void*)conv_wgrad_kernel, dev, attr_done);
+  if (rc) return rc;
+  const size_t smem = (size_t)g.stages * stage_bytes + 1024 + 256;
+  const long items = base_items * g.splits;
+  conv_wgrad_kernel<<<(int)items, CONV_THREADS, smem, (cudaStream_t)stream>>>(maps, g);
+  return (int)cudaGetLastError();
+}

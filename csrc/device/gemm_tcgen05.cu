@@ -1,0 +1,401 @@
+// Persistent, warp-specialised GEMM on the 5th-generation tensor cores.
+//
+//   D[M,N] = act(alpha * A[M,K] * B[N,K]^T + bias + beta * R)
+//
+// Replaces cnnlMatMul / cnnlBatchMatMulBCast of the reference
+// (torch_mlu/csrc/aten/operators/cnnl/internal/matmul_internal.cpp:106,
+// bmm_internal.cpp:89) and is the main loop the convolution kernels reuse.
+//
+// Structure (one CTA per SM, 192 threads):
+//   warp 0    : TMA producer -- per k-block one expect_tx + tiled tensor-map loads
+//               of the A (128 x 128 B) and B (tile_n x 128 B) tiles, 128-byte swizzle
+//   warp 1    : allocates 512 tensor-memory columns, issues tcgen05.mma (one elected
+//               thread), commits to the stage's "empty" barrier and, after the last
+//               k-block of a tile, to the accumulator's "full" barrier
+//   warps 2-5 : epilogue -- tcgen05.ld 32 columns at a time, alpha/bias/residual/
+//               activation in registers, cast, 16-byte global stores
+// The accumulator is double buffered (2 x 256 columns) so the epilogue of tile i
+// overlaps the main loop of tile i+1.  All waits are bounded (see tcgen05.cuh).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include "kernels_api.h"
+#include "tcgen05.cuh"
+#include "tma_util.cuh"
+
+namespace b200 {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_MAX_STAGES = 8;
+constexpr int GEMM_A_STAGE_BYTES = GEMM_BM * 128;  // 16 KB
+constexpr int GEMM_TMEM_COLS = 512;
+constexpr int GEMM_ACC_STRIDE = 256;  // columns per accumulator buffer
+
+struct GemmKernelArgs {
+  int M, N, K, batch;
+  int tile_n, stages, k_blocks, tiles_m, tiles_n;
+  int elem_bytes;       // 2 or 4
+  int a_mn, b_mn;
+  uint32_t idesc;
+  int mn_lbo, mn_sbo, mn_kstep;  // descriptor fields of MN-major operands (bytes)
+  void* D;
+  int64_t ldd, stride_d;
+  int d_dtype;
+  const void* bias;
+  int bias_dtype, bias_per_row;
+  const void* residual;
+  int64_t ldr, stride_r;
+  int res_dtype;
+  float alpha, beta;
+  int act;
+  int* err;
+};
+
+__device__ __forceinline__ float load_scalar(const void* p, int64_t i, int dt) {
+  if (dt == B200_F32) return static_cast<const float*>(p)[i];
+  if (dt == B200_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  return __half2float(static_cast<const __half*>(p)[i]);
+}
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  if (act == 1) return v > 0.f ? v : 0.f;
+  if (act == 2) return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
+  return v;
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const GemmKernelArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment is required by the 128-byte swizzle atoms.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int b_stage_bytes = g.tile_n * 128;
+  const int stage_bytes = GEMM_A_STAGE_BYTES + b_stage_bytes;
+  uint8_t* tiles = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + (size_t)g.stages * stage_bytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + GEMM_MAX_STAGES;
+  uint64_t* acc_full = bars + 2 * GEMM_MAX_STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < g.stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 128);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, GEMM_TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_per_batch = g.tiles_m * g.tiles_n;
+  const int total_tiles = tiles_per_batch * g.batch;
+  const int bk_elems = 128 / g.elem_bytes;          // K elements per k-block
+  const int mn_block = 128 / g.elem_bytes;          // MN elements per 128-byte row (MN-major)
+  bool failed = false;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t tx_bytes = (uint32_t)stage_bytes;
+      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+        const int bz = tile / tiles_per_batch;
+        const int t = tile - bz * tiles_per_batch;
+        const int m0 = (t % g.tiles_m) * GEMM_BM;
+        const int n0 = (t / g.tiles_m) * g.tile_n;
+        for (int kb = 0; kb < g.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, g.err, ERR_TIMEOUT_EMPTY)) { failed = true; break; }
+          mbar_arrive_expect_tx(&full_bar[stage], tx_bytes);
+          uint8_t* sa = tiles + (size_t)stage * stage_bytes;
+          uint8_t* sb = sa + GEMM_A_STAGE_BYTES;
+          const int k0 = kb * bk_elems;
+          if (!g.a_mn) {
+            tma_load_3d(sa, &tmA, &full_bar[stage], k0, m0, bz);
+          } else {
+            const int blk_bytes = bk_elems * 128;
+            for (int i = 0; i < GEMM_BM / mn_block; ++i)
+              tma_load_3d(sa + i * blk_bytes, &tmA, &full_bar[stage], m0 + i * mn_block, k0, bz);
+          }
+          if (!g.b_mn) {
+            tma_load_3d(sb, &tmB, &full_bar[stage], k0, n0, bz);
+          } else {
+            const int blk_bytes = bk_elems * 128;
+            for (int i = 0; i < g.tile_n / mn_block; ++i)
+              tma_load_3d(sb + i * blk_bytes, &tmB, &full_bar[stage], n0 + i * mn_block, k0, bz);
+          }
+          if (++stage == g.stages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      const bool tf32 = g.elem_bytes == 4;
+      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, g.err, ERR_TIMEOUT_TMEM_EMPTY)) { failed = true; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * GEMM_ACC_STRIDE;
+        for (int kb = 0; kb < g.k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, g.err, ERR_TIMEOUT_FULL)) { failed = true; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + (size_t)stage * stage_bytes);
+          const uint32_t sb = sa + GEMM_A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t adesc = g.a_mn ? make_smem_desc_sw128(sa + k * g.mn_kstep, g.mn_lbo, g.mn_sbo)
+                                          : make_smem_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t bdesc = g.b_mn ? make_smem_desc_sw128(sb + k * g.mn_kstep, g.mn_lbo, g.mn_sbo)
+                                          : make_smem_desc_sw128(sb + k * 32, 16, 1024);
+            const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+            if (tf32) umma_tf32(d_tmem, adesc, bdesc, g.idesc, accum);
+            else umma_f16(d_tmem, adesc, bdesc, g.idesc, accum);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the smem stage once the MMAs have read it
+          if (++stage == g.stages) { stage = 0; phase ^= 1; }
+        }
+        if (failed) break;
+        umma_commit(&acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;  // tcgen05.ld: warp w may touch lanes [32*(w%4), +32)
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+      const int bz = tile / tiles_per_batch;
+      const int t = tile - bz * tiles_per_batch;
+      const int m0 = (t % g.tiles_m) * GEMM_BM;
+      const int n0 = (t / g.tiles_m) * g.tile_n;
+      if (!mbar_wait(&acc_full[acc], acc_phase, g.err, ERR_TIMEOUT_TMEM_FULL)) { failed = true; break; }
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const bool row_ok = row < g.M;
+      const float row_bias = (g.bias && g.bias_per_row && row_ok) ? load_scalar(g.bias, row, g.bias_dtype) : 0.f;
+      uint8_t* drow = static_cast<uint8_t*>(g.D) +
+                      ((size_t)bz * g.stride_d + (size_t)row * g.ldd) * (g.d_dtype == B200_F32 ? 4 : 2);
+      const uint8_t* rrow = g.residual ? static_cast<const uint8_t*>(g.residual) +
+                                             ((size_t)bz * g.stride_r + (size_t)row * g.ldr) *
+                                                 (g.res_dtype == B200_F32 ? 4 : 2)
+                                       : nullptr;
+      for (int c = 0; c < g.tile_n; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + acc * GEMM_ACC_STRIDE + ((uint32_t)(quarter * 32) << 16) + c, r);
+        tmem_ld_wait();
+        const int n_base = n0 + c;
+        if (!row_ok || n_base >= g.N) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * g.alpha;
+        const int valid = min(32, g.N - n_base);
+        if (g.bias) {
+          if (g.bias_per_row) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += row_bias;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < valid) v[j] += load_scalar(g.bias, n_base + j, g.bias_dtype);
+          }
+        }
+        if (rrow) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < valid) v[j] += g.beta * load_scalar(rrow, n_base + j, g.res_dtype);
+        }
+        if (g.act) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], g.act);
+        }
+        if (g.d_dtype == B200_F32) {
+          float* o = reinterpret_cast<float*>(drow) + n_base;
+          if (valid == 32 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+            for (int j = 0; j < valid; ++j) o[j] = v[j];
+          }
+        } else {
+          alignas(16) uint16_t h[32];
+          if (g.d_dtype == B200_BF16) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) h[j] = __bfloat16_as_ushort(__float2bfloat16(v[j]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) h[j] = __half_as_ushort(__float2half(v[j]));
+          }
+          uint16_t* o = reinterpret_cast<uint16_t*>(drow) + n_base;
+          if (valid == 32 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(o)[j] = reinterpret_cast<const uint4*>(h)[j];
+          } else {
+            for (int j = 0; j < valid; ++j) o[j] = h[j];
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  if (*((volatile int*)g.err) != 0) {
+    // Error path: give copies that are still in flight time to land before the
+    // shared memory goes away.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, GEMM_TMEM_COLS);
+  }
+}
+
+static int g_dbg_lbo = -1, g_dbg_sbo = -1, g_dbg_kstep = -1;
+
+static int pick_tile_n(int M, int N, int sms) {
+  // Candidates are multiples of 32 up to 256; prefer the one with the fewest
+  // waves of CTAs, then the least padding, then the widest tile.
+  const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
+  int best = 256;
+  double best_cost = 1e30;
+  for (int tn = 256; tn >= 32; tn -= 32) {
+    const int tiles_n = (N + tn - 1) / tn;
+    const long tiles = (long)tiles_m * tiles_n;
+    const long waves = (tiles + sms - 1) / sms;
+    // cost ~ time: waves * (tile_n work) with a fixed per-tile overhead
+    const double cost = (double)waves * (tn + 24);
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = tn;
+    }
+  }
+  return best;
+}
+
+}  // namespace b200
+
+extern "C" void b200_gemm_debug_override(int lbo, int sbo, int kstep) {
+  b200::g_dbg_lbo = lbo;
+  b200::g_dbg_sbo = sbo;
+  b200::g_dbg_kstep = kstep;
+}
+
+extern "C" int b200_gemm(const B200GemmParams* p, void* stream) {
+  using namespace b200;
+  if (p->M <= 0 || p->N <= 0 || p->batch <= 0) return 0;
+  if (p->K <= 0) return (int)cudaErrorInvalidValue;
+  const int es = p->ab_dtype == B200_F32 ? 4 : 2;
+  // fp32 operands run as tf32 and must be K-major (the host layer transposes).
+  if (es == 4 && (p->a_mn_major || p->b_mn_major)) return (int)cudaErrorInvalidValue;
+  const CUtensorMapDataType dt = p->ab_dtype == B200_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : p->ab_dtype == B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                           : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  auto ok16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (!ok16(p->A) || !ok16(p->B) || (p->lda * es) % 16 || (p->ldb * es) % 16 || (p->stride_a * es) % 16 ||
+      (p->stride_b * es) % 16)
+    return (int)cudaErrorInvalidValue;
+
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int bk = 128 / es;
+  const int mn_block = 128 / es;
+
+  GemmKernelArgs g{};
+  g.M = p->M; g.N = p->N; g.K = p->K; g.batch = p->batch;
+  g.tile_n = p->tile_n > 0 ? p->tile_n : pick_tile_n(p->M, p->N, sms);
+  if (p->b_mn_major && g.tile_n % mn_block) g.tile_n = (g.tile_n + mn_block - 1) / mn_block * mn_block;
+  if (g.tile_n > 256 || g.tile_n % 32) return (int)cudaErrorInvalidValue;
+  g.k_blocks = (p->K + bk - 1) / bk;
+  g.tiles_m = (p->M + GEMM_BM - 1) / GEMM_BM;
+  g.tiles_n = (p->N + g.tile_n - 1) / g.tile_n;
+  g.elem_bytes = es;
+  g.a_mn = p->a_mn_major; g.b_mn = p->b_mn_major;
+  const int fmt = p->ab_dtype == B200_F32 ? 2 : (p->ab_dtype == B200_BF16 ? 1 : 0);
+  g.idesc = make_idesc(1, fmt, fmt, g.a_mn, g.b_mn, GEMM_BM, g.tile_n);
+  // MN-major: 8-row K groups are 1024 B apart, 128-byte MN blocks are one
+  // k-block (bk rows x 128 B) apart, one MMA consumes 32 B of K = (32/es) rows.
+  g.mn_sbo = g_dbg_sbo >= 0 ? g_dbg_sbo : 1024;
+  g.mn_lbo = g_dbg_lbo >= 0 ? g_dbg_lbo : bk * 128;
+  g.mn_kstep = g_dbg_kstep >= 0 ? g_dbg_kstep : (32 / es) * 128;
+  g.D = p->D; g.ldd = p->ldd; g.stride_d = p->stride_d; g.d_dtype = p->d_dtype;
+  g.bias = p->bias; g.bias_dtype = p->bias_dtype; g.bias_per_row = p->bias_per_row;
+  g.residual = p->residual; g.ldr = p->ldr; g.stride_r = p->stride_r; g.res_dtype = p->res_dtype;
+  g.alpha = p->alpha; g.beta = p->beta; g.act = p->act;
+  g.err = error_flag_ptr();
+  if (!g.err) return (int)cudaErrorInvalidDevice;
+
+  const int stage_bytes = GEMM_A_STAGE_BYTES + g.tile_n * 128;
+  const int smem_budget = 200 * 1024;
+  g.stages = smem_budget / stage_bytes;
+  if (g.stages > GEMM_MAX_STAGES) g.stages = GEMM_MAX_STAGES;
+  if (g.stages > g.k_blocks + 1) g.stages = g.k_blocks + 1 < 2 ? 2 : g.k_blocks + 1;
+  if (g.stages < 2) g.stages = 2;
+  const size_t smem = (size_t)g.stages * stage_bytes + 1024 /*align*/ + 256 /*barriers*/;
+
+  CUtensorMap tmA, tmB;
+  const uint64_t batch_a = (uint64_t)(p->batch > 1 ? p->stride_a : (int64_t)p->lda * (p->a_mn_major ? p->K : p->M));
+  const uint64_t batch_b = (uint64_t)(p->batch > 1 ? p->stride_b : (int64_t)p->ldb * (p->b_mn_major ? p->K : p->N));
+  int rc;
+  if (!p->a_mn_major) {
+    uint64_t dims[3] = {(uint64_t)p->K, (uint64_t)p->M, (uint64_t)p->batch};
+    uint64_t str[2] = {(uint64_t)p->lda * es, batch_a * es};
+    uint32_t box[3] = {(uint32_t)bk, GEMM_BM, 1};
+    rc = encode_tiled(&tmA, dt, 3, p->A, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    uint64_t dims[3] = {(uint64_t)p->M, (uint64_t)p->K, (uint64_t)p->batch};
+    uint64_t str[2] = {(uint64_t)p->lda * es, batch_a * es};
+    uint32_t box[3] = {(uint32_t)mn_block, (uint32_t)bk, 1};
+    rc = encode_tiled(&tmA, dt, 3, p->A, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  if (rc) return rc;
+  if (!p->b_mn_major) {
+    uint64_t dims[3] = {(uint64_t)p->K, (uint64_t)p->N, (uint64_t)p->batch};
+    uint64_t str[2] = {(uint64_t)p->ldb * es, batch_b * es};
+    uint32_t box[3] = {(uint32_t)bk, (uint32_t)g.tile_n, 1};
+    rc = encode_tiled(&tmB, dt, 3, p->B, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    uint64_t dims[3] = {(uint64_t)p->N, (uint64_t)p->K, (uint64_t)p->batch};
+    uint64_t str[2] = {(uint64_t)p->ldb * es, batch_b * es};
+    uint32_t box[3] = {(uint32_t)mn_block, (uint32_t)bk, 1};
+    rc = encode_tiled(&tmB, dt, 3, p->B, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  if (rc) return rc;
+
+  static bool attr_set[64] = {false};
+  if (!attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev & 63] = true;
+  }
+  const long total_tiles = (long)g.tiles_m * g.tiles_n * g.batch;
+  int ctas = p->max_ctas > 0 ? p->max_ctas : sms;
+  if (ctas > total_tiles) ctas = (int)total_tiles;
+  gemm_tcgen05_kernel<<<ctas, GEMM_THREADS, smem, (cudaStream_t)stream>>>(tmA, tmB, g);
+  return (int)cudaGetLastError();
+}

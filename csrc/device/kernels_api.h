@@ -67,6 +67,121 @@ typedef struct B200EwDesc {
 } B200EwDesc;
 B200_API int b200_elementwise(const B200EwDesc* desc, void* stream);
 
+
+// ---- device-side error flag -------------------------------------------------------
+// Kernels with bounded waits record a non-zero code here instead of hanging.
+// Returns the flag's value on the current device and clears it.
+B200_API int b200_read_and_clear_error_flag(int* value);
+
+// ---- tcgen05 GEMM ---------------------------------------------------------------------
+// D[M,N] = act(alpha * A[M,K] * B[N,K]^T + bias + beta * R[M,N])   (row-major D / R)
+// A and B are 16-bit (bf16/f16) or fp32 (computed as tf32); accumulation is fp32 in
+// tensor memory.  "K-major" operand X: element (row,k) at X[row*ld + k];
+// "MN-major": element (row,k) at X[k*ld + row].  Leading dimensions must be
+// multiples of 16 bytes and base pointers 16-byte aligned.
+typedef struct B200GemmParams {
+  int M, N, K, batch;
+  const void* A;
+  const void* B;
+  void* D;
+  int64_t lda, ldb, ldd;                 // elements
+  int64_t stride_a, stride_b, stride_d;  // batch strides, elements
+  int a_mn_major, b_mn_major;
+  int ab_dtype;                          // B200_BF16 / B200_F16 / B200_F32
+  int d_dtype;                           // B200_BF16 / B200_F16 / B200_F32
+  const void* bias;                      // optional
+  int bias_dtype;                        // dtype of bias (f32 / bf16 / f16)
+  int bias_per_row;                      // 0: bias[n], 1: bias[m]
+  const void* residual;                  // optional, same logical shape as D
+  int64_t ldr, stride_r;
+  int res_dtype;
+  float alpha, beta;
+  int act;                               // 0 none, 1 relu, 2 gelu (erf)
+  int tile_n;                            // 0 = choose automatically (32..256, multiple of 32)
+  int max_ctas;                          // 0 = one per SM
+} B200GemmParams;
+B200_API int b200_gemm(const B200GemmParams* p, void* stream);
+// Test hook: override the MN-major descriptor fields (bytes); negative = default.
+B200_API void b200_gemm_debug_override(int lbo, int sbo, int kstep);
+
+// ---- tcgen05 implicit-GEMM convolution --------------------------------------------------
+// Activations are NHWC 16-bit tensors.  The kernel walks a list of filter taps; for
+// each tap the A tile (128 output pixels x 64 input channels) is one tiled tensor-map
+// load from a (possibly strided) view of the input, shifted by the tap's offset with
+// out-of-bounds elements read as zero.  Strided convolutions use one view per input
+// parity.  The same kernel serves the data gradient (input = dy, flipped weights,
+// optional strided output addressing).
+#define B200_CONV_MAX_TAPS 49
+#define B200_CONV_MAX_MAPS 4
+typedef struct B200ConvTap {
+  short dh, dw;   // offset added to the tile's (h, w) origin in the tap's view
+  short map;      // which input view
+  short wtap;     // index of the [Cout][Cin] weight slice
+} B200ConvTap;
+
+typedef struct B200ConvView {
+  const void* base;
+  long long dims[4];     // {C, W, H, N} extents of the view
+  long long strides[3];  // element strides of W, H, N (C is contiguous)
+} B200ConvView;
+
+typedef struct B200ConvParams {
+  int N, P, Q;           // pixel grid covered by this launch (tiles are boxes of it)
+  int Cin, Cout;         // Cin: channels per tap seen by the kernel (multiple of 8)
+  int ab_dtype;          // B200_BF16 / B200_F16
+  int num_views;
+  B200ConvView views[B200_CONV_MAX_MAPS];
+  int ntaps;
+  B200ConvTap taps[B200_CONV_MAX_TAPS];
+  // weight element (tap, n = output channel, k = input channel) lives at
+  //   weight + tap*w_stride_tap + n*w_stride_n + k*w_stride_k   (elements);
+  // exactly one of w_stride_n / w_stride_k is 1 (k contiguous: forward with
+  // channels-last filters; n contiguous: data gradient reading the same filters).
+  const void* weight;
+  long long w_stride_tap, w_stride_n, w_stride_k;
+  int wtaps;
+  // element (n,p,q,c) of the result goes to
+  //   out + n*o_sn + (p*o_mul_h + o_off_h)*o_sh + (q*o_mul_w + o_off_w)*o_sw + c
+  void* out;
+  int out_dtype;
+  long long o_sn, o_sh, o_sw;
+  int o_mul_h, o_off_h, o_mul_w, o_off_w;
+  const void* scale;     // optional per-Cout fp32 multiplier (folded batch norm)
+  const void* bias;      // optional per-Cout bias
+  int bias_dtype;
+  const void* residual;  // optional, addressed like `out`
+  int res_dtype;
+  int act;               // 0 none, 1 relu
+  int tile_n;            // 0 = automatic
+} B200ConvParams;
+B200_API int b200_conv_fprop(const B200ConvParams* p, void* stream);
+
+// Weight gradient: dw_acc[co][tap*Cin + ci] += sum over pixels dy[n,p,q,co] * x_tap[n,p,q,ci]
+// (fp32, zero-initialised by the caller; CTAs that share a tile add atomically).
+typedef struct B200ConvWgradParams {
+  int N, P, Q;           // pixel grid of dy
+  int Cin, Cout;
+  int ab_dtype;
+  const void* dy;        // NHWC [N,P,Q,Cout]
+  long long dy_sn, dy_sh, dy_sw;
+  int num_views;
+  B200ConvView views[B200_CONV_MAX_MAPS];
+  int ntaps;
+  B200ConvTap taps[B200_CONV_MAX_TAPS];  // wtap = destination tap slot
+  float* dw_acc;         // [Cout][wtaps*Cin]
+  int wtaps;
+  int splits;            // 0 = automatic
+} B200ConvWgradParams;
+B200_API int b200_conv_wgrad(const B200ConvWgradParams* p, void* stream);
+
+// ---- layout helpers -----------------------------------------------------------------------
+// Pack an [N,C<=8,H,W] tensor with arbitrary element strides into a zero-bordered
+// NHWC buffer with 8 channels: out[n][h+pad_top][w+pad_left][c] (16-bit `out_dtype`),
+// out dims [N][Hp][Wp][8].  Used by the first-layer convolution (C = 3).
+B200_API int b200_pack_nhwc8(const void* in, int in_dtype, long long sn, long long sc, long long sh, long long sw,
+                             int N, int C, int H, int W, void* out, int out_dtype, int Hp, int Wp, int pad_top,
+                             int pad_left, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -145,3 +145,32 @@ int b200_host_alloc_mapped(void** host_ptr, void** dev_ptr, size_t bytes) {
 }
 
 }  // extern "C"
+
+// ---- device-side error flag (one int per device, file-scope) ----------------------
+#include "tma_util.cuh"
+#include "kernels_api.h"
+__device__ int g_b200_error_flag;
+namespace b200 {
+int* error_flag_ptr() {
+  static int* ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_b200_error_flag) != cudaSuccess) return nullptr;
+    ptrs[dev] = static_cast<int*>(p);
+  }
+  return ptrs[dev];
+}
+}  // namespace b200
+extern "C" int b200_read_and_clear_error_flag(int* value) {
+  int* p = b200::error_flag_ptr();
+  if (!p) return (int)cudaErrorInvalidDevice;
+  cudaError_t e = cudaMemcpy(value, p, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return (int)e;
+  if (*value != 0) {
+    int zero = 0;
+    e = cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice);
+  }
+  return (int)e;
+}

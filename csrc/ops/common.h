@@ -27,6 +27,12 @@ void cpu_fallback(const c10::OperatorHandle& op, torch::jit::Stack* stack);
 // force-CPU test mode.
 inline bool use_cpu_path() { return hostsim() || flags().test_cpu_dispatch; }
 
+// Compute kernels are registered with the dispatcher only when they can run:
+// under host simulation or CATCH_B200_TEST_CPU_DISPATCH=1 (both decided when the
+// library is loaded) the registrations are skipped, so every compute op reaches
+// the boxed CPU fallback while factories, views and copies stay native.
+inline bool device_kernels_enabled() { return !use_cpu_path(); }
+
 // Sets the device of `t` current for the lifetime of the scope, logs the op
 // name, and synchronises on exit when CATCH_B200_ASYNC_DISABLE is set.
 class OpScope {

@@ -1,0 +1,338 @@
+// Host drivers of the tcgen05 convolution kernels: layout normalisation (NHWC),
+// per-parity input views for strided convolutions, tap tables, the first-layer
+// "row window" formulation for tiny channel counts, data and weight gradients.
+//
+// Behavioural parity: cnnl_convolution_overrideable / _backward_overrideable
+// (torch_mlu/csrc/aten/operators/cnnl/convolution_overrideable.cpp:241-297) make
+// inputs channels-last, pick a dense or depthwise kernel and return channels-last
+// results; configurations the device kernels do not cover raise, and the caller
+// (conv.cpp) reruns them on the CPU.
+#include "conv_impl.h"
+
+#include "common.h"
+#include "kernels.h"
+
+namespace catch_b200 {
+namespace ops {
+namespace {
+
+using at::Tensor;
+
+struct ConvGeom {
+  int64_t N, C, H, W, K, R, S, P, Q;
+  int64_t sh, sw, ph, pw;
+};
+
+inline int64_t floordiv(int64_t a, int64_t b) { return (a >= 0) ? a / b : -((-a + b - 1) / b); }
+inline int64_t ceildiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+at::ScalarType compute_dtype(at::ScalarType t) { return t == at::kBFloat16 ? at::kBFloat16 : at::kHalf; }
+
+// channels-last (dense NHWC) tensor of dtype `dt`
+Tensor to_nhwc(const Tensor& x, at::ScalarType dt) {
+  Tensor t = x.scalar_type() == dt ? x : x.to(dt);
+  if (t.size(1) == 1 || (t.size(2) == 1 && t.size(3) == 1)) {
+    // stride ambiguity: force a fresh channels-last copy
+    Tensor o = empty_b200(t.sizes(), dt, t.device().index(), at::MemoryFormat::ChannelsLast);
+    o.copy_(t);
+    return o;
+  }
+  return t.contiguous(at::MemoryFormat::ChannelsLast);
+}
+
+void check_supported(const Tensor& input, const Tensor& weight, at::IntArrayRef stride, at::IntArrayRef padding,
+                     at::IntArrayRef dilation, bool transposed, int64_t groups) {
+  TORCH_CHECK(input.dim() == 4 && weight.dim() == 4, "b200 conv: only 2-D convolutions run on the device");
+  TORCH_CHECK(!transposed, "b200 conv: transposed convolution has no device kernel");
+  TORCH_CHECK(groups == 1, "b200 conv: grouped convolution has no device kernel");
+  TORCH_CHECK(dilation[0] == 1 && dilation[1] == 1, "b200 conv: dilation has no device kernel");
+  TORCH_CHECK(stride[0] >= 1 && stride[0] <= 2 && stride[1] >= 1 && stride[1] <= 2, "b200 conv: stride must be 1 or 2");
+  const auto t = input.scalar_type();
+  TORCH_CHECK(t == at::kBFloat16 || t == at::kHalf || t == at::kFloat, "b200 conv: unsupported dtype ", t);
+  TORCH_CHECK(weight.size(0) % 8 == 0, "b200 conv: output channels must be a multiple of 8");
+  const int64_t C = input.size(1);
+  TORCH_CHECK(C % 8 == 0 || (C <= 8 && weight.size(3) <= 8), "b200 conv: input channels must be a multiple of 8 (or <= 8)");
+}
+
+ConvGeom geom(const Tensor& input, const Tensor& weight, at::IntArrayRef stride, at::IntArrayRef padding) {
+  ConvGeom g;
+  g.N = input.size(0); g.C = input.size(1); g.H = input.size(2); g.W = input.size(3);
+  g.K = weight.size(0); g.R = weight.size(2); g.S = weight.size(3);
+  g.sh = stride[0]; g.sw = stride[1]; g.ph = padding[0]; g.pw = padding[1];
+  g.P = (g.H + 2 * g.ph - g.R) / g.sh + 1;
+  g.Q = (g.W + 2 * g.pw - g.S) / g.sw + 1;
+  return g;
+}
+
+// Per-parity views of an NHWC tensor x for a convolution with stride (sh, sw):
+// view (a, b) holds the pixels (a + i*sh, b + j*sw).  Fills views / taps for the
+// forward problem (also used by wgrad).  Returns number of taps.
+template <typename Params>
+void build_forward_taps(Params& p, const Tensor& x, const ConvGeom& g) {
+  const int64_t x_sn = x.stride(0), x_sh = x.stride(2), x_sw = x.stride(3);
+  const char* base = static_cast<const char*>(x.data_ptr());
+  p.num_views = (int)(g.sh * g.sw);
+  bool view_ok[B200_CONV_MAX_MAPS] = {false, false, false, false};
+  for (int64_t a = 0; a < g.sh; ++a) {
+    for (int64_t b = 0; b < g.sw; ++b) {
+      const int idx = (int)(a * g.sw + b);
+      B200ConvView& v = p.views[idx];
+      const int64_t hv = ceildiv(g.H - a, g.sh), wv = ceildiv(g.W - b, g.sw);
+      view_ok[idx] = hv > 0 && wv > 0;
+      v.base = base + (a * x_sh + b * x_sw) * x.element_size();
+      v.dims[0] = g.C; v.dims[1] = std::max<int64_t>(wv, 1); v.dims[2] = std::max<int64_t>(hv, 1); v.dims[3] = g.N;
+      v.strides[0] = g.sw * x_sw; v.strides[1] = g.sh * x_sh; v.strides[2] = x_sn;
+    }
+  }
+  p.ntaps = 0;
+  for (int64_t r = 0; r < g.R; ++r) {
+    for (int64_t s = 0; s < g.S; ++s) {
+      const int64_t oh = r - g.ph, ow = s - g.pw;
+      const int64_t a = ((oh % g.sh) + g.sh) % g.sh, b = ((ow % g.sw) + g.sw) % g.sw;
+      const int idx = (int)(a * g.sw + b);
+      if (!view_ok[idx]) continue;
+      B200ConvTap& t = p.taps[p.ntaps++];
+      t.dh = (short)((oh - a) / g.sh);
+      t.dw = (short)((ow - b) / g.sw);
+      t.map = (short)idx;
+      t.wtap = (short)(r * g.S + s);
+    }
+  }
+}
+
+// ---- first layer (C <= 8): rows of the padded NHWC8 image are the K dimension ----
+struct StemPack {
+  Tensor xp;       // [N][Hp][Wp][8]
+  int64_t Hp, Wp;
+};
+StemPack pack_stem_input(const Tensor& input, const ConvGeom& g, at::ScalarType dt, const OpScope& scope) {
+  StemPack sp;
+  sp.Hp = g.H + 2 * g.ph;
+  // every window of 8 pixels must stay inside its row
+  sp.Wp = std::max<int64_t>(g.W + 2 * g.pw, (g.Q - 1) * g.sw + 8);
+  sp.xp = empty_b200({g.N, sp.Hp, sp.Wp, 8}, dt, input.device().index());
+  B200_KERNEL_CHECK(b200_pack_nhwc8(input.data_ptr(), to_b200_dtype(input.scalar_type()), input.stride(0),
+                                    input.stride(1), input.stride(2), input.stride(3), (int)g.N, (int)g.C, (int)g.H,
+                                    (int)g.W, sp.xp.data_ptr(), to_b200_dtype(dt), (int)sp.Hp, (int)sp.Wp, (int)g.ph,
+                                    (int)g.pw, scope.stream()));
+  return sp;
+}
+template <typename Params>
+void build_stem_taps(Params& p, const StemPack& sp, const ConvGeom& g) {
+  // view a (row parity): rows a, a+sh, ...; each "pixel" of the view is a window of
+  // 8 packed pixels (64 elements) starting at packed column q*sw.
+  const char* base = static_cast<const char*>(sp.xp.data_ptr());
+  p.num_views = (int)g.sh;
+  for (int64_t a = 0; a < g.sh; ++a) {
+    B200ConvView& v = p.views[a];
+    v.base = base + a * sp.Wp * 8 * 2;
+    v.dims[0] = 64; v.dims[1] = g.Q; v.dims[2] = ceildiv(sp.Hp - a, g.sh); v.dims[3] = g.N;
+    v.strides[0] = g.sw * 8; v.strides[1] = g.sh * sp.Wp * 8; v.strides[2] = sp.Hp * sp.Wp * 8;
+  }
+  p.ntaps = 0;
+  for (int64_t r = 0; r < g.R; ++r) {
+    B200ConvTap& t = p.taps[p.ntaps++];
+    t.dh = (short)(r / g.sh);
+    t.dw = 0;
+    t.map = (short)(r % g.sh);
+    t.wtap = (short)r;
+  }
+}
+// weight [K, C, R, S] -> [R][K][8(s)][8(c)] zero padded
+Tensor pack_stem_weight(const Tensor& weight, const ConvGeom& g, at::ScalarType dt) {
+  Tensor wp = at::zeros({g.R, g.K, 8, 8}, weight.options().dtype(dt));
+  wp.narrow(2, 0, g.S).narrow(3, 0, g.C).copy_(weight.permute({2, 0, 3, 1}));
+  return wp;
+}
+
+Tensor forward_impl(const Tensor& input, const Tensor& weight, const std::optional<Tensor>& bias, const ConvGeom& g,
+                    const float* scale, const Tensor* residual, int act, at::ScalarType out_dtype) {
+  const at::ScalarType dt = compute_dtype(input.scalar_type());
+  OpScope scope("conv_fprop", input);
+  Tensor out = empty_b200({g.N, g.K, g.P, g.Q}, out_dtype, input.device().index(), at::MemoryFormat::ChannelsLast);
+  if (out.numel() == 0) return out;
+  B200ConvParams p;
+  std::memset(&p, 0, sizeof(p));
+  Tensor x, w;
+  StemPack sp;
+  if (g.C % 8 != 0 || g.C < 8) {
+    sp = pack_stem_input(input, g, dt, scope);
+    w = pack_stem_weight(weight, g, dt);
+    build_stem_taps(p, sp, g);
+    p.Cin = 64;
+    p.weight = w.data_ptr();
+    p.w_stride_k = 1; p.w_stride_n = 64; p.w_stride_tap = g.K * 64;
+    p.wtaps = (int)g.R;
+  } else {
+    x = to_nhwc(input, dt);
+    w = to_nhwc(weight, dt);  // memory [K][R][S][C]
+    build_forward_taps(p, x, g);
+    p.Cin = (int)g.C;
+    p.weight = w.data_ptr();
+    p.w_stride_k = 1; p.w_stride_n = g.R * g.S * g.C; p.w_stride_tap = g.C;
+    p.wtaps = (int)(g.R * g.S);
+  }
+  p.N = (int)g.N; p.P = (int)g.P; p.Q = (int)g.Q; p.Cout = (int)g.K;
+  p.ab_dtype = to_b200_dtype(dt);
+  p.out = out.data_ptr(); p.out_dtype = to_b200_dtype(out_dtype);
+  p.o_sn = out.stride(0); p.o_sh = out.stride(2); p.o_sw = out.stride(3);
+  p.o_mul_h = 1; p.o_mul_w = 1;
+  p.scale = scale;
+  Tensor b;
+  if (bias.has_value() && bias->defined()) {
+    b = bias->contiguous();
+    p.bias = b.data_ptr();
+    p.bias_dtype = to_b200_dtype(b.scalar_type());
+  }
+  Tensor res;
+  if (residual) {
+    res = to_nhwc(*residual, residual->scalar_type());
+    TORCH_CHECK(res.sizes() == out.sizes(), "conv residual shape mismatch");
+    p.residual = res.data_ptr();
+    p.res_dtype = to_b200_dtype(res.scalar_type());
+  }
+  p.act = act;
+  TORCH_CHECK(p.ntaps > 0, "b200 conv: empty tap list");
+  B200_KERNEL_CHECK(b200_conv_fprop(&p, scope.stream()));
+  return out;
+}
+
+Tensor dgrad_impl(const Tensor& grad, const Tensor& weight, const ConvGeom& g, at::ScalarType out_dtype) {
+  const at::ScalarType dt = compute_dtype(grad.scalar_type());
+  OpScope scope("conv_dgrad", grad);
+  Tensor dx = empty_b200({g.N, g.C, g.H, g.W}, out_dtype, grad.device().index(), at::MemoryFormat::ChannelsLast);
+  if (dx.numel() == 0) return dx;
+  Tensor dy = to_nhwc(grad, dt);
+  Tensor w = to_nhwc(weight, dt);
+  bool need_zero = false;
+  struct Launch { B200ConvParams p; };
+  std::vector<B200ConvParams> launches;
+  for (int64_t a = 0; a < g.sh; ++a) {
+    for (int64_t b = 0; b < g.sw; ++b) {
+      const int64_t Pa = ceildiv(g.H - a, g.sh), Qb = ceildiv(g.W - b, g.sw);
+      if (Pa <= 0 || Qb <= 0) continue;
+      B200ConvParams p;
+      std::memset(&p, 0, sizeof(p));
+      p.ntaps = 0;
+      for (int64_t r = 0; r < g.R; ++r) {
+        if ((a + g.ph - r) % g.sh != 0) continue;
+        for (int64_t s = 0; s < g.S; ++s) {
+          if ((b + g.pw - s) % g.sw != 0) continue;
+          B200ConvTap& t = p.taps[p.ntaps++];
+          t.dh = (short)floordiv(a + g.ph - r, g.sh);
+          t.dw = (short)floordiv(b + g.pw - s, g.sw);
+          t.map = 0;
+          t.wtap = (short)(r * g.S + s);
+        }
+      }
+      if (p.ntaps == 0) { need_zero = true; continue; }
+      p.N = (int)g.N; p.P = (int)Pa; p.Q = (int)Qb;
+      p.Cin = (int)g.K; p.Cout = (int)g.C;
+      p.ab_dtype = to_b200_dtype(dt);
+      p.num_views = 1;
+      p.views[0].base = dy.data_ptr();
+      p.views[0].dims[0] = g.K; p.views[0].dims[1] = g.Q; p.views[0].dims[2] = g.P; p.views[0].dims[3] = g.N;
+      p.views[0].strides[0] = dy.stride(3); p.views[0].strides[1] = dy.stride(2); p.views[0].strides[2] = dy.stride(0);
+      p.weight = w.data_ptr();
+      // element (tap, n = ci, k = co) of the channels-last filter [K][R][S][C]
+      p.w_stride_n = 1; p.w_stride_k = g.R * g.S * g.C; p.w_stride_tap = g.C;
+      p.wtaps = (int)(g.R * g.S);
+      p.out = dx.data_ptr(); p.out_dtype = to_b200_dtype(out_dtype);
+      p.o_sn = dx.stride(0); p.o_sh = dx.stride(2); p.o_sw = dx.stride(3);
+      p.o_mul_h = (int)g.sh; p.o_off_h = (int)a; p.o_mul_w = (int)g.sw; p.o_off_w = (int)b;
+      launches.push_back(p);
+    }
+  }
+  if (need_zero) dx.zero_();
+  for (auto& p : launches) B200_KERNEL_CHECK(b200_conv_fprop(&p, scope.stream()));
+  return dx;
+}
+
+Tensor wgrad_impl(const Tensor& grad, const Tensor& input, const Tensor& weight, const ConvGeom& g) {
+  const at::ScalarType dt = compute_dtype(grad.scalar_type());
+  OpScope scope("conv_wgrad", grad);
+  Tensor dy = to_nhwc(grad, dt);
+  B200ConvWgradParams p;
+  std::memset(&p, 0, sizeof(p));
+  Tensor x;
+  StemPack sp;
+  const bool stem = g.C % 8 != 0 || g.C < 8;
+  int64_t cin_k, wtaps;
+  if (stem) {
+    sp = pack_stem_input(input, g, dt, scope);
+    build_stem_taps(p, sp, g);
+    cin_k = 64; wtaps = g.R;
+  } else {
+    x = to_nhwc(input, dt);
+    build_forward_taps(p, x, g);
+    cin_k = g.C; wtaps = g.R * g.S;
+  }
+  Tensor acc = at::zeros({g.K, wtaps * cin_k}, grad.options().dtype(at::kFloat));
+  p.N = (int)g.N; p.P = (int)g.P; p.Q = (int)g.Q; p.Cin = (int)cin_k; p.Cout = (int)g.K;
+  p.ab_dtype = to_b200_dtype(dt);
+  p.dy = dy.data_ptr();
+  p.dy_sn = dy.stride(0); p.dy_sh = dy.stride(2); p.dy_sw = dy.stride(3);
+  p.dw_acc = acc.data_ptr<float>();
+  p.wtaps = (int)wtaps;
+  if (p.ntaps > 0) B200_KERNEL_CHECK(b200_conv_wgrad(&p, scope.stream()));
+  Tensor dw;
+  if (stem) {
+    // acc [K][R][8(s)][8(c)] -> [K, C, R, S]
+    dw = acc.view({g.K, g.R, 8, 8}).narrow(2, 0, g.S).narrow(3, 0, g.C).permute({0, 3, 1, 2});
+  } else {
+    // acc [K][R][S][C] is the channels-last memory of a [K, C, R, S] tensor
+    dw = acc.view({g.K, g.R, g.S, g.C}).permute({0, 3, 1, 2});
+  }
+  Tensor out = at::empty_like(weight, weight.options(), weight.suggest_memory_format());
+  out.copy_(dw);
+  return out;
+}
+
+}  // namespace
+
+at::Tensor conv_forward_device(const at::Tensor& input, const at::Tensor& weight, const std::optional<at::Tensor>& bias,
+                               at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation,
+                               bool transposed, at::IntArrayRef, int64_t groups) {
+  check_supported(input, weight, stride, padding, dilation, transposed, groups);
+  TORCH_CHECK(input.size(1) == weight.size(1), "conv: channel mismatch");
+  ConvGeom g = geom(input, weight, stride, padding);
+  TORCH_CHECK(g.P > 0 && g.Q > 0, "conv: output size is too small");
+  return forward_impl(input, weight, bias, g, nullptr, nullptr, 0, input.scalar_type());
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> conv_backward_device(
+    const at::Tensor& grad, const at::Tensor& input, const at::Tensor& weight, at::IntArrayRef stride,
+    at::IntArrayRef padding, at::IntArrayRef dilation, bool transposed, at::IntArrayRef, int64_t groups,
+    std::array<bool, 3> mask) {
+  check_supported(input, weight, stride, padding, dilation, transposed, groups);
+  ConvGeom g = geom(input, weight, stride, padding);
+  at::Tensor dx, dw, db;
+  if (mask[0]) {
+    TORCH_CHECK(g.C % 8 == 0, "b200 conv dgrad: input channels must be a multiple of 8");
+    dx = dgrad_impl(grad, weight, g, input.scalar_type());
+  }
+  if (mask[1]) dw = wgrad_impl(grad, input, weight, g);
+  if (mask[2]) db = grad.sum({0, 2, 3});
+  return {dx, dw, db};
+}
+
+// Fused inference convolution used by the fusion pass and the quantization-free
+// fast path: act(conv(x, w) * scale + bias + residual).
+at::Tensor conv_bn_act_device(const at::Tensor& input, const at::Tensor& weight, const std::optional<at::Tensor>& scale,
+                              const std::optional<at::Tensor>& bias, const std::optional<at::Tensor>& residual,
+                              at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation, int64_t groups,
+                              int64_t act) {
+  check_supported(input, weight, stride, padding, dilation, false, groups);
+  ConvGeom g = geom(input, weight, stride, padding);
+  at::Tensor sc;
+  const float* scp = nullptr;
+  if (scale.has_value() && scale->defined()) {
+    sc = scale->to(at::kFloat).contiguous();
+    scp = sc.data_ptr<float>();
+  }
+  const at::Tensor* res = (residual.has_value() && residual->defined()) ? &*residual : nullptr;
+  return forward_impl(input, weight, bias, g, scp, res, (int)act, input.scalar_type());
+}
+
+}  // namespace ops
+}  // namespace catch_b200

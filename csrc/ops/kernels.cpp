@@ -9,7 +9,8 @@ static int compute_class(at::ScalarType t) {
   return 2;
 }
 
-void launch_ew(at::TensorIteratorBase& iter, int op, double s0, double s1, void* stream) {
+void launch_ew(at::TensorIteratorBase& iter, int op, double s0, double s1, void* stream,
+               std::optional<at::ScalarType> compute) {
   if (iter.numel() == 0) return;
   TORCH_CHECK(iter.ndim() <= B200_EW_MAX_DIMS, "b200 elementwise: more than ", B200_EW_MAX_DIMS,
               " non-coalescable dimensions");
@@ -23,10 +24,9 @@ void launch_ew(at::TensorIteratorBase& iter, int op, double s0, double s1, void*
   d.scalar[0] = s0;
   d.scalar[1] = s1;
   for (int k = 0; k < d.ndim; ++k) d.shape[k] = iter.shape()[k];
-  // Compute type: the promoted input dtype (comparisons promote inputs but write bool).
-  at::ScalarType ct = iter.common_dtype();
-  if (ct == at::ScalarType::Undefined) ct = iter.ntensors() > 1 ? iter.dtype(iter.ntensors() - 1) : iter.dtype(0);
-  if (op == EW_WHERE) ct = iter.dtype(0);
+  // Compute type: the promoted input dtype (comparisons promote inputs but
+  // write bool); iterators built without promotion pass it explicitly.
+  at::ScalarType ct = compute.has_value() ? *compute : iter.common_dtype();
   d.compute = compute_class(ct);
   bool dense = iter.ndim() <= 1;
   for (int i = 0; i < d.noperands; ++i) {
@@ -69,13 +69,18 @@ void launch_copy(const at::Tensor& src, const at::Tensor& dst, void* stream) {
     launch_copy(dense, dst, stream);
     return;
   }
-  launch_ew(iter, EW_COPY, 0, 0, stream);
+  // Value-preserving compute class: the wider of the two dtypes' classes.
+  const at::ScalarType ct = (src.scalar_type() == at::kDouble || dst.scalar_type() == at::kDouble) ? at::kDouble
+                            : (c10::isFloatingType(src.scalar_type()) ? at::kFloat
+                               : (c10::isFloatingType(dst.scalar_type()) && src.scalar_type() != at::kLong ? at::kFloat
+                                                                                                       : at::kLong));
+  launch_ew(iter, EW_COPY, 0, 0, stream, ct);
 }
 
 void launch_fill(const at::Tensor& dst, double value, void* stream) {
   if (dst.numel() == 0) return;
   auto iter = at::TensorIteratorConfig().add_output(dst).resize_outputs(false).check_all_same_dtype(false).build();
-  launch_ew(iter, EW_FILL, value, 0, stream);
+  launch_ew(iter, EW_FILL, value, 0, stream, dst.scalar_type());
 }
 
 }  // namespace ops

@@ -33,7 +33,8 @@ inline int to_b200_dtype(at::ScalarType t) {
 
 // Launches the element-wise family over a built TensorIterator (operand 0 is
 // the output).  `s0`/`s1` are the op's scalar parameters.
-void launch_ew(at::TensorIteratorBase& iter, int op, double s0, double s1, void* stream);
+void launch_ew(at::TensorIteratorBase& iter, int op, double s0, double s1, void* stream,
+               std::optional<at::ScalarType> compute = std::nullopt);
 // dst <- src with arbitrary strides / dtypes (same device).
 void launch_copy(const at::Tensor& src, const at::Tensor& dst, void* stream);
 void launch_fill(const at::Tensor& dst, double value, void* stream);

@@ -1,0 +1,78 @@
+"""Implicit-GEMM convolution kernels (forward, data gradient, weight gradient)
+against an fp32 CPU reference (needs a B200)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from common import assert_tensors_equal
+
+pytestmark = pytest.mark.gpu
+DEV = "blackwell"
+
+CASES = [
+    # N, C, H, W, K, R, stride, pad
+    (4, 64, 56, 56, 256, 1, 1, 0),
+    (4, 64, 56, 56, 64, 3, 1, 1),
+    (2, 128, 56, 56, 128, 3, 2, 1),
+    (2, 256, 56, 56, 512, 1, 2, 0),
+    (3, 72, 13, 9, 40, 3, 1, 1),
+    (2, 512, 7, 7, 512, 3, 1, 1),
+    (2, 3, 224, 224, 64, 7, 2, 3),
+    (2, 64, 15, 15, 64, 3, 2, 1),
+]
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _backend():
+    import catch_b200  # noqa: F401
+
+    assert torch.b200.backend_name() == "cuda"
+    torch.b200.set_flag("op_trycatch", False)  # a failing device kernel must not be masked by the CPU fallback
+    yield
+    torch.b200.set_flag("op_trycatch", True)
+
+
+@pytest.mark.parametrize("case", CASES)
+@pytest.mark.parametrize("dtype,channels_last", [(torch.bfloat16, True), (torch.float32, False)])
+def test_conv_forward_backward(case, dtype, channels_last):
+    N, C, H, W, K, R, stride, pad = case
+    torch.manual_seed(0)
+    x = torch.randn(N, C, H, W)
+    w = torch.randn(K, C, R, R) / (C * R * R) ** 0.5
+    xq, wq = x.to(dtype).float(), w.to(dtype).float()
+    xr, wr = xq.clone().requires_grad_(C >= 8), wq.clone().requires_grad_()
+    ref = F.conv2d(xr, wr, None, stride, pad)
+    gy = torch.randn_like(ref)
+    gyq = gy.to(dtype).float()
+    ref.backward(gyq)
+
+    xd = xq.to(dtype).to(DEV)
+    wd = wq.to(dtype).to(DEV)
+    if channels_last:
+        xd = xd.contiguous(memory_format=torch.channels_last)
+        wd = wd.contiguous(memory_format=torch.channels_last)
+    xd.requires_grad_(C >= 8)
+    wd.requires_grad_()
+    out = F.conv2d(xd, wd, None, stride, pad)
+    assert out.device.type == DEV and out.dtype == dtype
+    prec = 2e-2 if dtype == torch.bfloat16 else 3e-3
+    assert_tensors_equal(out, ref, prec=prec, use_MSE=True, msg="fprop")
+    out.backward(gyq.to(dtype).to(DEV))
+    assert_tensors_equal(wd.grad, wr.grad, prec=prec, use_MSE=True, msg="wgrad")
+    if C >= 8:
+        assert_tensors_equal(xd.grad, xr.grad, prec=prec, use_MSE=True, msg="dgrad")
+    from catch_b200.ops import capi
+
+    torch.b200.synchronize()
+    assert capi.read_error_flag() == 0
+
+
+def test_conv_bias():
+    torch.manual_seed(1)
+    x = torch.randn(2, 64, 10, 10).bfloat16()
+    conv = torch.nn.Conv2d(64, 96, 3, padding=1).bfloat16()
+    ref = conv(x).float()
+    dconv = torch.nn.Conv2d(64, 96, 3, padding=1).bfloat16()
+    dconv.load_state_dict(conv.state_dict())
+    out = dconv.to(DEV)(x.to(DEV))
+    assert_tensors_equal(out, ref, prec=2e-2, use_MSE=True)
