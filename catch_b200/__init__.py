@@ -27,5 +27,6 @@ _torch.utils.generate_methods_for_privateuse1_backend(for_tensor=True, for_modul
                                                       for_packed_sequence=True)
 
 from .device_module import *  # noqa: F401,F403,E402
+from . import distributed  # noqa: F401,E402  (registers the "bwccl" backend)
 
 __version__ = "0.1.0"

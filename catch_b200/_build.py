@@ -83,22 +83,8 @@ def write_ninja(verbose: bool = False) -> Path:
     cxx_flags = (
         "-O2 -std=c++17 -fPIC -fvisibility=hidden -Wall -Wno-unused-variable -Wno-unused-function "
         "-Wno-sign-compare -Wno-unknown-pragmas -D_GLIBCXX_USE_CXX11_ABI=1 -DTORCH_EXTENSION_NAME=_C "
-        "-DTORCH_API_INCLUDE_EXTENSION_H -DPYBIND11_COMPILER_TYPE=\\\"_gcc\\\" -DPYBIND11_STDLIB=\\\"_libstdcpp\\\" "
-        "-DPYBIND11_BUILD_ABI=\\\"_cxxabi1018\\\""
+        "-DTORCH_API_INCLUDE_EXTENSION_H"
     )
-    try:
-        import torch
-
-        # pybind11 ABI tags must match the ones torch was built with.
-        tags = []
-        for name in ("COMPILER_TYPE", "STDLIB", "BUILD_ABI"):
-            v = getattr(torch._C, f"_PYBIND11_{name}", None)
-            if v is not None:
-                tags.append(f'-DPYBIND11_{name}=\\"{v}\\"')
-        if tags:
-            cxx_flags = cxx_flags.split("-DPYBIND11_COMPILER_TYPE")[0] + " ".join(tags)
-    except Exception:
-        pass
     lines = [
         "ninja_required_version = 1.3",
         f"nvcc = {NVCC}",

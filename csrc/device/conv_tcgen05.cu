@@ -46,6 +46,7 @@ struct ConvArgs {
   const void* residual;
   int res_dtype;
   int act;
+  float alpha;
   int* err;
 };
 
@@ -172,7 +173,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
         const int valid = min(32, g.Cout - cbase);
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rr[j]);
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rr[j]) * g.alpha;
         if (g.scale) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) if (j < valid) v[j] *= g.scale[cbase + j];
@@ -460,6 +461,7 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p, void* stream) {
   g.scale = static_cast<const float*>(p->scale);
   g.bias = p->bias; g.bias_dtype = p->bias_dtype;
   g.residual = p->residual; g.res_dtype = p->res_dtype; g.act = p->act;
+  g.alpha = p->alpha == 0.f ? 1.f : p->alpha;
   g.err = error_flag_ptr();
   if (!g.err) return (int)cudaErrorInvalidDevice;
   const int stage_bytes = CONV_A_BYTES + g.tile_n * 128;

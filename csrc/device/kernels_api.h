@@ -153,6 +153,7 @@ typedef struct B200ConvParams {
   int res_dtype;
   int act;               // 0 none, 1 relu
   int tile_n;            // 0 = automatic
+  float alpha;           // accumulator multiplier applied first (0 is treated as 1)
 } B200ConvParams;
 B200_API int b200_conv_fprop(const B200ConvParams* p, void* stream);
 
@@ -181,6 +182,194 @@ B200_API int b200_conv_wgrad(const B200ConvWgradParams* p, void* stream);
 B200_API int b200_pack_nhwc8(const void* in, int in_dtype, long long sn, long long sc, long long sh, long long sw,
                              int N, int C, int H, int W, void* out, int out_dtype, int Hp, int Wp, int pad_top,
                              int pad_left, void* stream);
+
+// ---- batch norm (channels innermost: x is [rows, C] with row pitch C) -----------------
+// Statistics accumulate in fp64 (zero `sums` before the call): sums[c] = sum x,
+// sums[C + c] = sum x^2.
+B200_API int b200_bn_stats(const void* x, int x_dtype, long long rows, int C, double* sums, void* stream);
+// mean / invstd from the sums; optionally updates running statistics
+// (running = (1-momentum)*running + momentum*batch, unbiased variance).
+B200_API int b200_bn_finalize(const double* sums, long long rows, int C, float eps, float momentum, float* mean,
+                              float* invstd, void* running_mean, void* running_var, int running_dtype, void* stream);
+// invstd from running_var (inference).
+B200_API int b200_bn_invstd_from_var(const void* var, int var_dtype, int C, float eps, float* invstd, void* stream);
+// y = act((x - mean) * invstd * gamma + beta + residual); mean given as fp32 or, for
+// inference, in `mean_dtype`.  act: 0 none, 1 relu.
+B200_API int b200_bn_apply(const void* x, int x_dtype, void* y, int y_dtype, long long rows, int C, const void* mean,
+                           int mean_dtype, const float* invstd, const void* gamma, const void* beta, int param_dtype,
+                           const void* residual, int res_dtype, int act, void* stream);
+// Backward reductions (fp64, zero `sums` first): sums[c] = sum dy, sums[C+c] = sum dy * xhat.
+// If `relu_out` is given dy is first masked by relu_out > 0 (fused ReLU backward).
+B200_API int b200_bn_backward_reduce(const void* dy, int dy_dtype, const void* x, int x_dtype, const void* mean,
+                                     int mean_dtype, const float* invstd, const void* relu_out, int relu_dtype,
+                                     long long rows, int C, double* sums, void* stream);
+// dx = gamma*invstd*(dy - sum_dy/rows - xhat*sum_dy_xhat/rows) (training) or gamma*invstd*dy (eval);
+// writes dgamma / dbeta (fp32) when non-null.
+B200_API int b200_bn_backward_apply(const void* dy, int dy_dtype, const void* x, int x_dtype, const void* mean,
+                                    int mean_dtype, const float* invstd, const void* gamma, int param_dtype,
+                                    const void* relu_out, int relu_dtype, const double* sums, long long rows, int C,
+                                    int training, void* dx, int dx_dtype, float* dgamma, float* dbeta, void* stream);
+
+// ---- layer norm over the last dimension ---------------------------------------------------
+B200_API int b200_layernorm_fwd(const void* x, int dtype, long long rows, int cols, const void* gamma, const void* beta,
+                                int param_dtype, float eps, void* y, float* mean, float* rstd, void* stream);
+// dx per row; dgamma/dbeta partial sums are accumulated with atomics into fp32 buffers (zeroed by caller).
+B200_API int b200_layernorm_bwd(const void* dy, const void* x, int dtype, long long rows, int cols, const void* gamma,
+                                int param_dtype, const float* mean, const float* rstd, void* dx, float* dgamma,
+                                float* dbeta, void* stream);
+
+// ---- pooling (generic strides, flattened h*W+w indices) -------------------------------------
+typedef struct B200PoolParams {
+  int N, C, H, W, P, Q;
+  int kh, kw, sh, sw, ph, pw, dh, dw;
+  long long in_s[4];    // element strides of N, C, H, W
+  long long out_s[4];   // element strides of N, C, P, Q
+  int channels_last;    // iterate with C fastest
+  int dtype;
+  int count_include_pad;
+  int divisor_override; // 0 = none
+} B200PoolParams;
+B200_API int b200_maxpool2d_fwd(const B200PoolParams* p, const void* x, void* y, long long* indices, void* stream);
+B200_API int b200_maxpool2d_bwd(const B200PoolParams* p, const void* dy, const long long* indices, void* dx, void* stream);
+B200_API int b200_avgpool2d_fwd(const B200PoolParams* p, const void* x, void* y, void* stream);
+B200_API int b200_avgpool2d_bwd(const B200PoolParams* p, const void* dy, void* dx, void* stream);
+// adaptive average pooling: windows [floor(i*H/P), ceil((i+1)*H/P))
+B200_API int b200_adaptive_avgpool2d_fwd(const B200PoolParams* p, const void* x, void* y, void* stream);
+B200_API int b200_adaptive_avgpool2d_bwd(const B200PoolParams* p, const void* dy, void* dx, void* stream);
+
+// ---- softmax / losses over contiguous rows ---------------------------------------------------
+B200_API int b200_softmax_fwd(const void* x, int in_dtype, void* y, int out_dtype, long long rows, int cols, int log_mode,
+                              void* stream);
+// grad_in = softmax: y*(dy - sum(dy*y)) ; log_softmax: dy - exp(y)*sum(dy)
+B200_API int b200_softmax_bwd(const void* dy, const void* y, int dtype, void* dx, int dx_dtype, long long rows, int cols,
+                              int log_mode, void* stream);
+// NLL loss on log-probabilities [rows, cols]; reduction 0 none, 1 mean, 2 sum.  `out` is fp32-computed,
+// stored in `dtype`; total_weight (same dtype) receives the sum of weights of non-ignored rows.
+B200_API int b200_nll_loss_fwd(const void* logp, int dtype, const long long* target, const void* weight, long long rows,
+                               int cols, int reduction, long long ignore_index, void* out, void* total_weight,
+                               void* stream);
+B200_API int b200_nll_loss_bwd(const void* grad_out, int dtype, const long long* target, const void* weight,
+                               const void* total_weight, long long rows, int cols, int reduction, long long ignore_index,
+                               void* grad_in, void* stream);
+// Fused softmax + cross entropy (mean reduction over non-ignored rows): writes the
+// per-row loss (fp32), and d(logits) scaled by grad_scale / n_valid in `dlogits` when non-null.
+B200_API int b200_softmax_xent(const void* logits, int dtype, const long long* target, long long rows, int cols,
+                               long long ignore_index, float label_smoothing, float* row_loss, float* n_valid,
+                               void* dlogits, int dl_dtype, float grad_scale, void* stream);
+
+// ---- reductions ----------------------------------------------------------------------------------
+enum B200ReduceOp { RED_SUM = 0, RED_MEAN, RED_PROD, RED_MAX, RED_MIN, RED_ANY, RED_ALL, RED_NORM1, RED_NORM2,
+                    RED_NORM_INF, RED_ARGMAX, RED_ARGMIN, RED_SUMSQ };
+#define B200_RED_MAX_DIMS 6
+typedef struct B200ReduceParams {
+  int op;
+  int in_dtype, out_dtype;          // out for ARG* is int64
+  long long n_out, n_red;
+  int n_kept, n_reduced;
+  long long kept_size[B200_RED_MAX_DIMS], kept_in_stride[B200_RED_MAX_DIMS];
+  long long red_size[B200_RED_MAX_DIMS], red_in_stride[B200_RED_MAX_DIMS];
+  const void* in;
+  void* out;                        // contiguous over the kept dims (in order)
+  long long* out_index;             // optional (max/min with indices); flat index along the single reduced dim
+  float* workspace;                 // n_out * splits * 2 floats when splits > 1
+  int splits;                       // filled by b200_reduce_plan
+} B200ReduceParams;
+B200_API int b200_reduce_plan(B200ReduceParams* p);   // chooses splits; returns workspace floats needed
+B200_API int b200_reduce(const B200ReduceParams* p, void* stream);
+
+// ---- fused multi-tensor optimizers ------------------------------------------------------------------
+#define B200_OPT_MAX_TENSORS 48
+typedef struct B200OptTensors {
+  int count;
+  void* param[B200_OPT_MAX_TENSORS];      // fp32 master parameters
+  const void* grad[B200_OPT_MAX_TENSORS];
+  void* state1[B200_OPT_MAX_TENSORS];     // momentum buffer / exp_avg
+  void* state2[B200_OPT_MAX_TENSORS];     // exp_avg_sq (AdamW)
+  void* lowp[B200_OPT_MAX_TENSORS];       // optional 16-bit copy of the parameter to refresh
+  long long numel[B200_OPT_MAX_TENSORS];
+  int grad_dtype, lowp_dtype;
+} B200OptTensors;
+// SGD: g = grad*grad_scale + wd*p; buf = first ? g : mu*buf + (1-dampening)*g; g = nesterov ? g + mu*buf : buf; p -= lr*g
+B200_API int b200_sgd_step(const B200OptTensors* t, float lr, float momentum, float dampening, float weight_decay,
+                           int nesterov, int first_step, float grad_scale, void* stream);
+// AdamW (decoupled weight decay), bias corrections computed from `step`.
+B200_API int b200_adamw_step(const B200OptTensors* t, float lr, float beta1, float beta2, float eps, float weight_decay,
+                             long long step, float grad_scale, int adam_l2_mode, void* stream);
+
+// ---- embedding / index ---------------------------------------------------------------------------------
+B200_API int b200_embedding_fwd(const void* weight, int dtype, const long long* idx, long long n_idx, int dim,
+                                long long padding_idx, void* out, void* stream);
+// dweight (fp32 or same dtype, zeroed by caller) += scatter of dy rows
+B200_API int b200_embedding_bwd(const void* dy, int dtype, const long long* idx, long long n_idx, int dim,
+                                long long padding_idx, void* dweight, int dw_dtype, void* stream);
+// out[i, :] = src[index[i], :] for a [n, row_elems] view (index_select along dim 0 of a 2-D view)
+B200_API int b200_index_select_rows(const void* src, int elem_bytes, const long long* idx, long long n_idx,
+                                    long long row_elems, long long n_src_rows, void* out, void* stream);
+
+// ---- random numbers (Philox 4x32-10) ----------------------------------------------------------------------
+B200_API int b200_rng_uniform(void* out, int dtype, long long n, unsigned long long seed, unsigned long long offset,
+                              double lo, double hi, void* stream);
+B200_API int b200_rng_normal(void* out, int dtype, long long n, unsigned long long seed, unsigned long long offset,
+                             double mean, double std, void* stream);
+B200_API int b200_rng_bernoulli(void* out, int dtype, long long n, unsigned long long seed, unsigned long long offset,
+                                double p, void* stream);
+// y = x * mask / (1-p); mask is uint8 (bool)
+B200_API int b200_dropout_fwd(const void* x, int dtype, long long n, unsigned long long seed, unsigned long long offset,
+                              float p, void* y, unsigned char* mask, void* stream);
+
+// ---- debug dump kernel ---------------------------------------------------------------------------------------
+// Prints up to `count` elements of a device tensor with device-side printf.
+B200_API int b200_dump_device(const void* x, int dtype, long long count, void* stream);
+
+// ---- collectives over peer-mapped memory (NVLink / NVSwitch) ------------------------------------
+// Every rank owns an "arena" (staging bytes followed by a flag block) that all peers map
+// through CUDA IPC.  Kernels signal and wait on monotonically increasing sequence numbers
+// in the flag blocks with system-scope release / acquire accesses; every wait is bounded
+// and reports through `status` (host-mapped): 0 ok, else B200_COMM_TIMEOUT | (peer << 8).
+#define B200_COMM_MAX_RANKS 16
+#define B200_COMM_TIMEOUT 1
+#define B200_COMM_FLAG_BYTES 4096
+typedef struct B200CommCtx {
+  int rank, world;
+  void* arena[B200_COMM_MAX_RANKS];                 // peer staging bases (arena[rank] is local)
+  unsigned long long* flags[B200_COMM_MAX_RANKS];   // peer flag blocks: ready[16], done[16], p2p ready[16], p2p done[16], counter
+  int* status;                                      // host-mapped status word
+  unsigned long long timeout_ns;                    // wait limit (0 = 10 s)
+} B200CommCtx;
+enum B200CommOp { COMM_SUM = 0, COMM_PROD = 1, COMM_MIN = 2, COMM_MAX = 3, COMM_AVG = 4 };
+
+// In-place all-reduce of `n` elements of `dtype` stored at arena + offset on every rank
+// (two-shot: each rank reduces one shard reading all peers, then writes the result to all
+// peers).  result = op(...) * scale.  `no_signal` (tests only) skips this rank's "ready"
+// signal so peers run into their bounded wait.
+B200_API int b200_comm_allreduce(const B200CommCtx* ctx, size_t offset, long long n, int dtype, int op, float scale,
+                                 unsigned long long seq, int no_signal, void* stream);
+// Fused DDP step for one gradient bucket: reduce-scatter of the gradients in the arena
+// (dtype grad_dtype) * scale, SGD-momentum / AdamW update of this rank's shard of the
+// fp32 master parameters (which live in every rank's arena at param_offset), then the
+// updated shard is written to every peer's parameter region (all-gather of parameters
+// instead of gradients).  state1/state2 are this rank's local optimizer-state shards.
+typedef struct B200FusedOptArgs {
+  int kind;                  // 0 = SGD momentum, 1 = AdamW
+  float lr, momentum, dampening, weight_decay, beta1, beta2, eps, bc1, bc2_sqrt;
+  int nesterov, first_step;
+  float* state1;             // momentum / exp_avg shard (shard_elems floats)
+  float* state2;             // exp_avg_sq shard
+  size_t lowp_offset;        // optional 16-bit parameter copy region in the arena (0 = none)
+  int lowp_dtype;
+} B200FusedOptArgs;
+B200_API long long b200_comm_shard_elems(long long n, int world, int dtype);
+B200_API int b200_comm_allreduce_opt(const B200CommCtx* ctx, size_t grad_offset, size_t param_offset, long long n,
+                                     int grad_dtype, float scale, const B200FusedOptArgs* opt, unsigned long long seq,
+                                     void* stream);
+// Building blocks for broadcast / all-gather / reduce / send / recv.
+B200_API int b200_comm_signal(const B200CommCtx* ctx, int which /*0 ready, 1 done, 2 p2p ready, 3 p2p done*/, int peer /*-1 = all*/,
+                              unsigned long long seq, void* stream);
+B200_API int b200_comm_wait(const B200CommCtx* ctx, int which, int peer /*-1 = all*/, unsigned long long seq,
+                            void* stream);
+B200_API int b200_comm_copy(void* dst, const void* src, size_t bytes, void* stream);
+// dst[i] = op(dst[i], src[i]) for n elements (used by reduce / reduce_scatter pulls)
+B200_API int b200_comm_accumulate(void* dst, const void* src, long long n, int dtype, int op, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,461 @@
+// Batch normalisation (statistics, apply, backward) and layer normalisation
+// kernels for channels-innermost data.
+//
+// Replaces cnnlBatchNormForwardTraining / ForwardInference / Backward /
+// FrozenBatchNormBackward (torch_mlu/csrc/aten/operators/cnnl/internal/
+// native_batch_norm_internal.cpp:119,137, native_batch_norm_backward_internal.cpp:122,147).
+// LayerNorm has no device kernel in the reference.
+//
+// Column reductions: a CTA owns a slab of rows; thread (tx, ty) accumulates the
+// 8-channel vector tx over rows ty, ty+RY, ...; the RY partial vectors are folded
+// in shared memory and added to the fp64 totals with one atomic per channel.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include "kernels_api.h"
+
+namespace {
+
+template <typename T> struct Cv;
+template <> struct Cv<float> {
+  static __device__ __forceinline__ float to(float v) { return v; }
+  static __device__ __forceinline__ float from(float v) { return v; }
+};
+template <> struct Cv<__nv_bfloat16> {
+  static __device__ __forceinline__ float to(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from(float v) { return __float2bfloat16(v); }
+};
+template <> struct Cv<__half> {
+  static __device__ __forceinline__ float to(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from(float v) { return __float2half(v); }
+};
+
+__device__ __forceinline__ float ldf(const void* p, long long i, int dt) {
+  if (dt == B200_F32) return static_cast<const float*>(p)[i];
+  if (dt == B200_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  if (dt == B200_F16) return __half2float(static_cast<const __half*>(p)[i]);
+  return (float)static_cast<const double*>(p)[i];
+}
+__device__ __forceinline__ void stf(void* p, long long i, int dt, float v) {
+  if (dt == B200_F32) static_cast<float*>(p)[i] = v;
+  else if (dt == B200_BF16) static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16(v);
+  else if (dt == B200_F16) static_cast<__half*>(p)[i] = __float2half(v);
+  else static_cast<double*>(p)[i] = v;
+}
+
+// VEC elements of type T per 16 bytes (fp32: 4, 16-bit: 8)
+template <typename T> struct VecOf { static constexpr int N = 16 / sizeof(T); };
+
+template <typename T>
+__device__ __forceinline__ void load_vec(const T* p, float* f) {
+  constexpr int V = VecOf<T>::N;
+  alignas(16) T t[V];
+  *reinterpret_cast<uint4*>(t) = *reinterpret_cast<const uint4*>(p);
+#pragma unroll
+  for (int i = 0; i < V; ++i) f[i] = Cv<T>::to(t[i]);
+}
+template <typename T>
+__device__ __forceinline__ void store_vec(T* p, const float* f) {
+  constexpr int V = VecOf<T>::N;
+  alignas(16) T t[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) t[i] = Cv<T>::from(f[i]);
+  *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(t);
+}
+
+constexpr int RED_THREADS = 256;
+
+// Generic two-quantity column reduction.  F(row, c_vec_start, out_a[V], out_b[V]).
+template <typename T, int NQ, typename F>
+__device__ void column_reduce(long long rows, int C, double* sums, F f) {
+  constexpr int V = VecOf<T>::N;
+  const int cvecs = C / V;                   // C % V == 0 guaranteed by the launcher
+  const int tx_n = cvecs < RED_THREADS ? cvecs : RED_THREADS;
+  const int ty_n = RED_THREADS / tx_n;
+  const int tx = threadIdx.x % tx_n, ty = threadIdx.x / tx_n;
+  extern __shared__ float sh[];              // [ty_n][tx_n*V*NQ]
+  const long long rows_per_cta = (rows + gridDim.x - 1) / gridDim.x;
+  const long long r0 = (long long)blockIdx.x * rows_per_cta;
+  const long long r1 = r0 + rows_per_cta < rows ? r0 + rows_per_cta : rows;
+  for (int cv = tx; cv < cvecs; cv += tx_n) {
+    float acc[NQ][V];
+#pragma unroll
+    for (int q = 0; q < NQ; ++q)
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[q][i] = 0.f;
+    if (ty < ty_n) {
+      for (long long r = r0 + ty; r < r1; r += ty_n) f(r, cv * V, acc);
+    }
+    // fold the ty_n partials
+    float* mine = sh + ((size_t)ty * tx_n + tx) * V * NQ;
+    if (ty < ty_n) {
+#pragma unroll
+      for (int q = 0; q < NQ; ++q)
+#pragma unroll
+        for (int i = 0; i < V; ++i) mine[q * V + i] = acc[q][i];
+    }
+    __syncthreads();
+    if (ty == 0) {
+#pragma unroll
+      for (int q = 0; q < NQ; ++q)
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          double s = 0.0;
+          for (int y = 0; y < ty_n; ++y) s += sh[((size_t)y * tx_n + tx) * V * NQ + q * V + i];
+          atomicAdd(&sums[(size_t)q * C + cv * V + i], s);
+        }
+    }
+    __syncthreads();
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(RED_THREADS) bn_stats_kernel(const T* x, long long rows, int C, double* sums) {
+  constexpr int V = VecOf<T>::N;
+  column_reduce<T, 2>(rows, C, sums, [&](long long r, int c0, float (*acc)[V]) {
+    float v[V];
+    load_vec<T>(x + r * C + c0, v);
+#pragma unroll
+    for (int i = 0; i < V; ++i) { acc[0][i] += v[i]; acc[1][i] += v[i] * v[i]; }
+  });
+}
+
+__global__ void bn_finalize_kernel(const double* sums, long long rows, int C, float eps, float momentum, float* mean,
+                                   float* invstd, void* rmean, void* rvar, int rdt) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const double m = sums[c] / (double)rows;
+  double var = sums[C + c] / (double)rows - m * m;
+  if (var < 0) var = 0;
+  mean[c] = (float)m;
+  invstd[c] = (float)(1.0 / sqrt(var + (double)eps));
+  if (rmean) {
+    const double unbiased = rows > 1 ? var * (double)rows / (double)(rows - 1) : var;
+    stf(rmean, c, rdt, (float)((1.0 - momentum) * ldf(rmean, c, rdt) + momentum * m));
+    stf(rvar, c, rdt, (float)((1.0 - momentum) * ldf(rvar, c, rdt) + momentum * unbiased));
+  }
+}
+
+__global__ void bn_invstd_kernel(const void* var, int dt, int C, float eps, float* invstd) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c < C) invstd[c] = rsqrtf(ldf(var, c, dt) + eps);
+}
+
+template <typename TX, typename TY>
+__global__ void __launch_bounds__(256) bn_apply_kernel(const TX* x, TY* y, long long nvec, int C, const void* mean,
+                                                       int mdt, const float* invstd, const void* gamma,
+                                                       const void* beta, int pdt, const void* res, int rdt, int act) {
+  constexpr int V = VecOf<TX>::N > VecOf<TY>::N ? VecOf<TY>::N : VecOf<TX>::N;  // elements per thread-iteration
+  const int cvecs = C / V;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    const int c0 = (int)(i % cvecs) * V;
+    float v[V], rv[V], o[V];
+    constexpr bool kSame = sizeof(TX) == sizeof(TY);
+    if constexpr (kSame) {
+      load_vec<TX>(x + i * V, v);
+    } else {
+#pragma unroll
+      for (int k = 0; k < V; ++k) v[k] = Cv<TX>::to(x[i * V + k]);
+    }
+    if (res) {
+      if (kSame && rdt == (sizeof(TX) == 4 ? B200_F32 : (int)B200_BF16) && sizeof(TX) == 2) {
+        load_vec<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(res) + i * V, rv);
+      } else {
+#pragma unroll
+        for (int k = 0; k < V; ++k) rv[k] = ldf(res, i * V + k, rdt);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const int c = c0 + k;
+      const float g = gamma ? ldf(gamma, c, pdt) : 1.f;
+      const float b = beta ? ldf(beta, c, pdt) : 0.f;
+      float t = (v[k] - ldf(mean, c, mdt)) * invstd[c] * g + b;
+      if (res) t += rv[k];
+      if (act == 1) t = t > 0.f ? t : 0.f;
+      o[k] = t;
+    }
+    if constexpr (kSame) {
+      store_vec<TY>(y + i * V, o);
+    } else {
+#pragma unroll
+      for (int k = 0; k < V; ++k) y[i * V + k] = Cv<TY>::from(o[k]);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(RED_THREADS)
+bn_bwd_reduce_kernel(const T* dy, const T* x, const void* mean, int mdt, const float* invstd, const T* relu_out,
+                     long long rows, int C, double* sums) {
+  constexpr int V = VecOf<T>::N;
+  column_reduce<T, 2>(rows, C, sums, [&](long long r, int c0, float (*acc)[V]) {
+    float g[V], v[V], o[V];
+    load_vec<T>(dy + r * C + c0, g);
+    load_vec<T>(x + r * C + c0, v);
+    if (relu_out) load_vec<T>(relu_out + r * C + c0, o);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      float gi = g[i];
+      if (relu_out && !(o[i] > 0.f)) gi = 0.f;
+      const float xh = (v[i] - ldf(mean, c0 + i, mdt)) * invstd[c0 + i];
+      acc[0][i] += gi;
+      acc[1][i] += gi * xh;
+    }
+  });
+}
+
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256)
+bn_bwd_apply_kernel(const T* dy, const T* x, const void* mean, int mdt, const float* invstd, const void* gamma, int pdt,
+                    const T* relu_out, const double* sums, long long rows, int C, int training, TO* dx, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C);
+    float g = Cv<T>::to(dy[i]);
+    if (relu_out && !(Cv<T>::to(relu_out[i]) > 0.f)) g = 0.f;
+    const float is = invstd[c];
+    const float ga = gamma ? ldf(gamma, c, pdt) : 1.f;
+    float o;
+    if (training) {
+      const float xh = (Cv<T>::to(x[i]) - ldf(mean, c, mdt)) * is;
+      const float sdy = (float)(sums[c] / (double)rows), sdx = (float)(sums[C + c] / (double)rows);
+      o = ga * is * (g - sdy - xh * sdx);
+    } else {
+      o = ga * is * g;
+    }
+    dx[i] = Cv<TO>::from(o);
+  }
+}
+
+__global__ void bn_param_grads_kernel(const double* sums, int C, float* dgamma, float* dbeta) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  if (dbeta) dbeta[c] = (float)sums[c];
+  if (dgamma) dgamma[c] = (float)sums[C + c];
+}
+
+inline int red_grid(long long rows) {
+  long long g = (rows + 63) / 64;
+  if (g > 148 * 4) g = 148 * 4;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+inline size_t red_smem(int C, int V, int NQ) {
+  const int cvecs = C / V;
+  const int tx_n = cvecs < RED_THREADS ? cvecs : RED_THREADS;
+  const int ty_n = RED_THREADS / tx_n;
+  return (size_t)ty_n * tx_n * V * NQ * sizeof(float);
+}
+inline int ew_grid(long long n) {
+  long long g = (n + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+// ------------------------------------------------------------------- layer norm
+template <typename T>
+__global__ void __launch_bounds__(256) layernorm_fwd_kernel(const T* x, long long rows, int cols, const void* gamma,
+                                                            const void* beta, int pdt, float eps, T* y, float* mean,
+                                                            float* rstd) {
+  // one warp per row
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= rows) return;
+  const T* xr = x + row * cols;
+  float s = 0.f, ss = 0.f;
+  for (int c = lane; c < cols; c += 32) { const float v = Cv<T>::to(xr[c]); s += v; ss += v * v; }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { s += __shfl_xor_sync(0xffffffff, s, o); ss += __shfl_xor_sync(0xffffffff, ss, o); }
+  const float m = s / cols;
+  float var = ss / cols - m * m;
+  var = var < 0.f ? 0.f : var;
+  const float r = rsqrtf(var + eps);
+  if (lane == 0) { mean[row] = m; rstd[row] = r; }
+  T* yr = y + row * cols;
+  for (int c = lane; c < cols; c += 32) {
+    float o = (Cv<T>::to(xr[c]) - m) * r;
+    if (gamma) o *= ldf(gamma, c, pdt);
+    if (beta) o += ldf(beta, c, pdt);
+    yr[c] = Cv<T>::from(o);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) layernorm_bwd_kernel(const T* dy, const T* x, long long rows, int cols,
+                                                            const void* gamma, int pdt, const float* mean,
+                                                            const float* rstd, T* dx, float* dgamma, float* dbeta) {
+  // one warp per row for dx; dgamma/dbeta: each warp keeps partial sums for the
+  // columns its lanes own over the rows it processes, added atomically at the end.
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warps = blockDim.x >> 5;
+  constexpr int MAXC = 48;  // columns per lane kept in registers (cols <= 1536); larger rows use atomics directly
+  float pg[MAXC], pb[MAXC];
+  const bool keep = cols <= MAXC * 32 && (dgamma || dbeta);
+  if (keep) {
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) { pg[i] = 0.f; pb[i] = 0.f; }
+  }
+  for (long long row = (long long)blockIdx.x * warps + warp; row < rows; row += (long long)gridDim.x * warps) {
+    const T* xr = x + row * cols;
+    const T* gr = dy + row * cols;
+    const float m = mean[row], r = rstd[row];
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = lane; c < cols; c += 32) {
+      const float g = Cv<T>::to(gr[c]) * (gamma ? ldf(gamma, c, pdt) : 1.f);
+      const float xh = (Cv<T>::to(xr[c]) - m) * r;
+      s1 += g;
+      s2 += g * xh;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { s1 += __shfl_xor_sync(0xffffffff, s1, o); s2 += __shfl_xor_sync(0xffffffff, s2, o); }
+    s1 /= cols; s2 /= cols;
+    T* dr = dx ? dx + row * cols : nullptr;
+    int k = 0;
+    for (int c = lane; c < cols; c += 32, ++k) {
+      const float go = Cv<T>::to(gr[c]);
+      const float g = go * (gamma ? ldf(gamma, c, pdt) : 1.f);
+      const float xh = (Cv<T>::to(xr[c]) - m) * r;
+      if (dr) dr[c] = Cv<T>::from(r * (g - s1 - xh * s2));
+      if (keep) {
+        if (k < MAXC) { pg[k] += go * xh; pb[k] += go; }
+      } else {
+        if (dgamma) atomicAdd(&dgamma[c], go * xh);
+        if (dbeta) atomicAdd(&dbeta[c], go);
+      }
+    }
+  }
+  if (keep) {
+    int k = 0;
+    for (int c = lane; c < cols; c += 32, ++k) {
+      if (k < MAXC) {
+        if (dgamma) atomicAdd(&dgamma[c], pg[k]);
+        if (dbeta) atomicAdd(&dbeta[c], pb[k]);
+      }
+    }
+  }
+}
+
+}  // namespace
+
+#define DISPATCH_FLOAT(dt, T, ...)                                   \
+  switch (dt) {                                                      \
+    case B200_F32: { using T = float; __VA_ARGS__; break; }          \
+    case B200_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; } \
+    case B200_F16: { using T = __half; __VA_ARGS__; break; }         \
+    default: return (int)cudaErrorInvalidValue;                      \
+  }
+
+extern "C" int b200_bn_stats(const void* x, int dt, long long rows, int C, double* sums, void* stream) {
+  if (rows <= 0 || C <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  DISPATCH_FLOAT(dt, T, {
+    constexpr int V = VecOf<T>::N;
+    if (C % V) return (int)cudaErrorInvalidValue;
+    bn_stats_kernel<T><<<red_grid(rows), RED_THREADS, red_smem(C, V, 2), s>>>(static_cast<const T*>(x), rows, C, sums);
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_bn_finalize(const double* sums, long long rows, int C, float eps, float momentum, float* mean,
+                                float* invstd, void* rmean, void* rvar, int rdt, void* stream) {
+  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, (cudaStream_t)stream>>>(sums, rows, C, eps, momentum, mean, invstd,
+                                                                         rmean, rvar, rdt);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_bn_invstd_from_var(const void* var, int dt, int C, float eps, float* invstd, void* stream) {
+  bn_invstd_kernel<<<(C + 127) / 128, 128, 0, (cudaStream_t)stream>>>(var, dt, C, eps, invstd);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_bn_apply(const void* x, int xdt, void* y, int ydt, long long rows, int C, const void* mean, int mdt,
+                             const float* invstd, const void* gamma, const void* beta, int pdt, const void* res,
+                             int rdt, int act, void* stream) {
+  if (rows <= 0 || C <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long n = rows * C;
+#define BN_APPLY(TX, TY)                                                                                            \
+  {                                                                                                                 \
+    constexpr int V = VecOf<TX>::N > VecOf<TY>::N ? VecOf<TY>::N : VecOf<TX>::N;                                    \
+    if (C % V) return (int)cudaErrorInvalidValue;                                                                   \
+    bn_apply_kernel<TX, TY><<<ew_grid(n / V), 256, 0, s>>>(static_cast<const TX*>(x), static_cast<TY*>(y), n / V, C, \
+                                                            mean, mdt, invstd, gamma, beta, pdt, res, rdt, act);    \
+  }
+  if (xdt == B200_BF16 && ydt == B200_BF16) BN_APPLY(__nv_bfloat16, __nv_bfloat16)
+  else if (xdt == B200_F16 && ydt == B200_F16) BN_APPLY(__half, __half)
+  else if (xdt == B200_F32 && ydt == B200_F32) BN_APPLY(float, float)
+  else if (xdt == B200_BF16 && ydt == B200_F32) BN_APPLY(__nv_bfloat16, float)
+  else if (xdt == B200_F32 && ydt == B200_BF16) BN_APPLY(float, __nv_bfloat16)
+  else if (xdt == B200_F16 && ydt == B200_F32) BN_APPLY(__half, float)
+  else if (xdt == B200_F32 && ydt == B200_F16) BN_APPLY(float, __half)
+  else return (int)cudaErrorInvalidValue;
+#undef BN_APPLY
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_bn_backward_reduce(const void* dy, int dt, const void* x, int xdt, const void* mean, int mdt,
+                                       const float* invstd, const void* relu_out, int rdt, long long rows, int C,
+                                       double* sums, void* stream) {
+  if (rows <= 0 || C <= 0) return 0;
+  if (dt != xdt || (relu_out && rdt != dt)) return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  DISPATCH_FLOAT(dt, T, {
+    constexpr int V = VecOf<T>::N;
+    if (C % V) return (int)cudaErrorInvalidValue;
+    bn_bwd_reduce_kernel<T><<<red_grid(rows), RED_THREADS, red_smem(C, V, 2), s>>>(
+        static_cast<const T*>(dy), static_cast<const T*>(x), mean, mdt, invstd, static_cast<const T*>(relu_out), rows, C,
+        sums);
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_bn_backward_apply(const void* dy, int dt, const void* x, int xdt, const void* mean, int mdt,
+                                      const float* invstd, const void* gamma, int pdt, const void* relu_out, int rdt,
+                                      const double* sums, long long rows, int C, int training, void* dx, int dxdt,
+                                      float* dgamma, float* dbeta, void* stream) {
+  if (rows <= 0 || C <= 0) return 0;
+  if (dt != xdt || (relu_out && rdt != dt)) return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long n = rows * C;
+  if (dx) {
+#define BN_BWD(T, TO)                                                                                                  \
+  bn_bwd_apply_kernel<T, TO><<<ew_grid(n), 256, 0, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x), mean, mdt, \
+                                                         invstd, gamma, pdt, static_cast<const T*>(relu_out), sums,     \
+                                                         rows, C, training, static_cast<TO*>(dx), n)
+    if (dt == B200_BF16 && dxdt == B200_BF16) BN_BWD(__nv_bfloat16, __nv_bfloat16);
+    else if (dt == B200_F16 && dxdt == B200_F16) BN_BWD(__half, __half);
+    else if (dt == B200_F32 && dxdt == B200_F32) BN_BWD(float, float);
+    else return (int)cudaErrorInvalidValue;
+#undef BN_BWD
+  }
+  if (dgamma || dbeta) bn_param_grads_kernel<<<(C + 127) / 128, 128, 0, s>>>(sums, C, dgamma, dbeta);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_layernorm_fwd(const void* x, int dt, long long rows, int cols, const void* gamma, const void* beta,
+                                  int pdt, float eps, void* y, float* mean, float* rstd, void* stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int warps = 8;
+  DISPATCH_FLOAT(dt, T, {
+    layernorm_fwd_kernel<T><<<(unsigned)((rows + warps - 1) / warps), warps * 32, 0, s>>>(
+        static_cast<const T*>(x), rows, cols, gamma, beta, pdt, eps, static_cast<T*>(y), mean, rstd);
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_layernorm_bwd(const void* dy, const void* x, int dt, long long rows, int cols, const void* gamma,
+                                  int pdt, const float* mean, const float* rstd, void* dx, float* dgamma, float* dbeta,
+                                  void* stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int warps = 8;
+  long long grid = (rows + warps - 1) / warps;
+  if (grid > 148 * 2) grid = 148 * 2;
+  DISPATCH_FLOAT(dt, T, {
+    layernorm_bwd_kernel<T><<<(unsigned)grid, warps * 32, 0, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x),
+                                                                  rows, cols, gamma, pdt, mean, rstd,
+                                                                  static_cast<T*>(dx), dgamma, dbeta);
+  });
+  return (int)cudaGetLastError();
+}

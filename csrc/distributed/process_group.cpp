@@ -1,0 +1,723 @@
+#include "process_group.h"
+
+#include <ATen/ATen.h>
+#include <c10/util/Exception.h>
+#include <cstring>
+#include <thread>
+
+#include "../runtime/caching_allocator.h"
+#include "../runtime/device.h"
+#include "../runtime/log.h"
+#include "../runtime/tensor_impl.h"
+
+namespace catch_b200 {
+
+namespace ops {
+void note_kernel_launch();
+}
+
+namespace {
+
+int dtype_code(at::ScalarType t) {
+  switch (t) {
+    case at::kFloat: return B200_F32;
+    case at::kBFloat16: return B200_BF16;
+    case at::kHalf: return B200_F16;
+    case at::kDouble: return B200_F64;
+    case at::kInt: return B200_I32;
+    case at::kLong: return B200_I64;
+    default: return -1;
+  }
+}
+int op_code(const c10d::ReduceOp& op) {
+  switch (static_cast<c10d::ReduceOp::RedOpType>(op)) {
+    case c10d::ReduceOp::SUM: return COMM_SUM;
+    case c10d::ReduceOp::PRODUCT: return COMM_PROD;
+    case c10d::ReduceOp::MIN: return COMM_MIN;
+    case c10d::ReduceOp::MAX: return COMM_MAX;
+    case c10d::ReduceOp::AVG: return COMM_AVG;
+    default: TORCH_CHECK(false, "bwccl: unsupported reduce op");
+  }
+}
+size_t env_mb(const char* name, size_t dflt) {
+  const char* s = std::getenv(name);
+  return (s && *s) ? static_cast<size_t>(std::atoll(s)) : dflt;
+}
+#define COMM_CHECK(expr)                                                                         \
+  do {                                                                                           \
+    ::catch_b200::ops::note_kernel_launch();                                                     \
+    int _e = (expr);                                                                             \
+    TORCH_CHECK(_e == 0, "bwccl: device call failed: ", device_error_string(_e), " (", #expr, ")"); \
+  } while (0)
+
+std::atomic<int> g_pg_counter{0};
+}  // namespace
+
+int next_process_group_id() { return g_pg_counter.fetch_add(1); }
+
+// ------------------------------------------------------------------ SymmetricArena
+// Layout of one rank's arena: [staging | p2p mailbox | user region | flag block].
+class SymmetricArena {
+ public:
+  SymmetricArena(int device, int rank, int world, const c10::intrusive_ptr<c10d::Store>& store, const std::string& uid,
+                 std::chrono::milliseconds timeout)
+      : device_(device), rank_(rank), world_(world) {
+    TORCH_CHECK(world <= B200_COMM_MAX_RANKS, "bwccl: at most ", B200_COMM_MAX_RANKS, " ranks per group");
+    staging_ = env_mb("CATCH_B200_SYMM_STAGING_MB", 128) << 20;
+    mailbox_ = size_t(16) << 20;
+    user_ = env_mb("CATCH_B200_SYMM_USER_MB", 1536) << 20;
+    total_ = staging_ + mailbox_ + user_ + B200_COMM_FLAG_BYTES;
+    DeviceSwitch sw(device);
+    COMM_CHECK(b200_malloc(&base_, total_));
+    COMM_CHECK(b200_memset_async(static_cast<char*>(base_) + total_ - B200_COMM_FLAG_BYTES, 0, B200_COMM_FLAG_BYTES, nullptr));
+    COMM_CHECK(b200_device_synchronize());
+    void* host = nullptr;
+    void* dev = nullptr;
+    COMM_CHECK(b200_host_alloc_mapped(&host, &dev, 64));
+    status_host_ = static_cast<int*>(host);
+    status_dev_ = static_cast<int*>(dev);
+    // exchange IPC handles through the store
+    char handle[64];
+    COMM_CHECK(b200_ipc_get_handle(base_, handle));
+    store->set(uid + "/ipc/" + std::to_string(rank), std::vector<uint8_t>(handle, handle + 64));
+    std::memset(&ctx_, 0, sizeof(ctx_));
+    ctx_.rank = rank;
+    ctx_.world = world;
+    ctx_.status = status_dev_;
+    for (int p = 0; p < world; ++p) {
+      void* ptr = base_;
+      if (p != rank) {
+        const std::string key = uid + "/ipc/" + std::to_string(p);
+        store->wait({key}, timeout);
+        auto h = store->get(key);
+        TORCH_CHECK(h.size() == 64, "bwccl: malformed IPC handle from rank ", p);
+        COMM_CHECK(b200_ipc_open_handle(reinterpret_cast<const char*>(h.data()), &ptr));
+        opened_.push_back(ptr);
+      }
+      ctx_.arena[p] = ptr;
+      ctx_.flags[p] = reinterpret_cast<unsigned long long*>(static_cast<char*>(ptr) + total_ - B200_COMM_FLAG_BYTES);
+    }
+    // nobody may signal before every rank has zeroed its flags and mapped its peers
+    store->add(uid + "/mapped", 1);
+    const auto t0 = std::chrono::steady_clock::now();
+    while (store->add(uid + "/mapped", 0) < world) {
+      TORCH_CHECK(std::chrono::steady_clock::now() - t0 < timeout, "bwccl: timed out waiting for peers to map the arena");
+      std::this_thread::sleep_for(std::chrono::milliseconds(2));
+    }
+  }
+  ~SymmetricArena() {
+    try {
+      DeviceSwitch sw(device_);
+      b200_device_synchronize();
+      for (void* p : opened_) b200_ipc_close_handle(p);
+      b200_free(base_);
+      b200_host_free(status_host_);
+    } catch (...) {
+    }
+  }
+  B200CommCtx ctx() const { return ctx_; }
+  char* local() const { return static_cast<char*>(base_); }
+  size_t staging_bytes() const { return staging_; }
+  size_t mailbox_offset() const { return staging_; }
+  size_t mailbox_bytes() const { return mailbox_; }
+  size_t user_alloc(size_t bytes) {
+    bytes = (bytes + 255) / 256 * 256;
+    TORCH_CHECK(user_used_ + bytes <= user_, "bwccl: symmetric user region exhausted (", user_ >> 20,
+                " MiB); raise CATCH_B200_SYMM_USER_MB");
+    const size_t off = staging_ + mailbox_ + user_used_;
+    user_used_ += bytes;
+    return off;
+  }
+  size_t offset_of(const void* p) const {
+    const char* c = static_cast<const char*>(p);
+    TORCH_CHECK(c >= local() && c < local() + total_, "bwccl: tensor does not live in the symmetric arena");
+    return static_cast<size_t>(c - local());
+  }
+  int* status_host() const { return status_host_; }
+  void set_timeout_ns(unsigned long long ns) { ctx_.timeout_ns = ns; }
+
+ private:
+  int device_, rank_, world_;
+  void* base_ = nullptr;
+  size_t staging_, mailbox_, user_, total_, user_used_ = 0;
+  int* status_host_ = nullptr;
+  int* status_dev_ = nullptr;
+  std::vector<void*> opened_;
+  B200CommCtx ctx_;
+};
+
+// ------------------------------------------------------------------------- WorkB200
+WorkB200::WorkB200(int rank, c10d::OpType op, std::vector<at::Tensor> outputs, int device, int* status,
+                   std::chrono::milliseconds timeout)
+    : c10d::Work(rank, op), outputs_(std::move(outputs)), device_(device), status_(status), timeout_(timeout) {}
+
+void WorkB200::finish_host(std::exception_ptr err) {
+  host_done_ = true;
+  error_ = err;
+}
+void WorkB200::check_status() const {
+  if (error_) std::rethrow_exception(error_);
+  if (status_ && *((volatile int*)status_) != 0) {
+    const int s = *((volatile int*)status_);
+    TORCH_CHECK_WITH(DistBackendError, false, "bwccl: a device-side wait timed out (status ", s & 0xff, ", waiting for rank ",
+                     (s >> 8) & 0xff, "). A peer did not reach the collective in time.");
+  }
+}
+bool WorkB200::isCompleted() { return host_done_ || notifier_.query(); }
+bool WorkB200::isSuccess() const { return !error_ && !(status_ && *((volatile int*)status_) != 0); }
+std::exception_ptr WorkB200::exception() const {
+  try {
+    check_status();
+  } catch (...) {
+    return std::current_exception();
+  }
+  return nullptr;
+}
+void WorkB200::synchronize() {
+  if (host_done_) {
+    check_status();
+    return;
+  }
+  // device-side ordering: later work on the current queue waits for the collective
+  notifier_.wait(getCurrentQueue(device_));
+  if (flags().blocking_wait) {
+    notifier_.synchronize();
+    check_status();
+  }
+}
+bool WorkB200::wait(std::chrono::milliseconds timeout) {
+  if (host_done_) {
+    check_status();
+    return true;
+  }
+  if (timeout == kNoTimeout && !flags().blocking_wait) {
+    synchronize();
+    return true;
+  }
+  const auto limit = timeout == kNoTimeout ? timeout_ : timeout;
+  const auto t0 = std::chrono::steady_clock::now();
+  while (!notifier_.query()) {
+    if (std::chrono::steady_clock::now() - t0 > limit) {
+      TORCH_CHECK_WITH(DistBackendError, false, "bwccl: collective did not complete within ", limit.count(), " ms");
+    }
+    std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+  check_status();
+  notifier_.wait(getCurrentQueue(device_));
+  return true;
+}
+c10::intrusive_ptr<c10::ivalue::Future> WorkB200::getFuture() {
+  if (!future_) {
+    future_ = c10::make_intrusive<c10::ivalue::Future>(c10::ListType::create(c10::TensorType::get()));
+    // Completion of the future means "ordered on the current queue": consumers of the
+    // value run on that queue, which waits on the notifier.
+    if (!host_done_) notifier_.wait(getCurrentQueue(device_));
+    if (error_) future_->setError(error_);
+    else future_->markCompleted(c10::IValue(outputs_));
+  }
+  return future_;
+}
+
+// ------------------------------------------------------------------ ProcessGroupB200
+ProcessGroupB200::ProcessGroupB200(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size,
+                                   std::chrono::milliseconds timeout)
+    : c10d::Backend(rank, size), store_(store), timeout_(timeout), send_seq_(size, 0), recv_seq_(size, 0) {
+  uid_ = "bwccl/" + std::to_string(next_process_group_id());
+  B200LOG(INFO) << "ProcessGroupB200 rank " << rank << "/" << size << " uid " << uid_;
+}
+
+ProcessGroupB200::~ProcessGroupB200() {
+  try {
+    if (arena_) {
+      comm_q_.synchronize();
+      send_q_.synchronize();
+      recv_q_.synchronize();
+    }
+  } catch (...) {
+  }
+}
+
+void ProcessGroupB200::ensure_arena(int device) {
+  if (hostsim()) {
+    device_ = device;
+    return;
+  }
+  if (arena_) {
+    TORCH_CHECK(device == device_, "bwccl: one device per process; this group is bound to device ", device_);
+    return;
+  }
+  device_ = device;
+  DeviceSwitch sw(device);
+  arena_ = std::make_unique<SymmetricArena>(device, rank_, size_, store_, uid_, timeout_);
+  comm_q_ = getQueueFromPool(device);
+  send_q_ = getQueueFromPool(device);
+  recv_q_ = getQueueFromPool(device);
+}
+
+void ProcessGroupB200::check_single(const std::vector<at::Tensor>& tensors) const {
+  TORCH_CHECK(tensors.size() == 1, "bwccl: expecting one tensor only but got multiple (one device per process)");
+  TORCH_CHECK(is_b200(tensors[0]), "bwccl: tensors must live on the blackwell device, got ", tensors[0].device());
+  TORCH_CHECK(!tensors[0].is_sparse(), "bwccl: sparse tensors are not supported");
+}
+
+void ProcessGroupB200::throw_if_failed() const {
+  if (arena_ && *((volatile int*)arena_->status_host()) != 0) {
+    const int s = *((volatile int*)arena_->status_host());
+    TORCH_CHECK_WITH(DistBackendError, false, "bwccl: a previous collective failed (device wait timed out waiting for rank ",
+                     (s >> 8) & 0xff, "); the communicator is unusable until clear_status().");
+  }
+}
+
+c10::intrusive_ptr<WorkB200> ProcessGroupB200::make_work(c10d::OpType op, std::vector<at::Tensor> outputs) {
+  return c10::make_intrusive<WorkB200>(rank_, op, std::move(outputs), device_, arena_ ? arena_->status_host() : nullptr,
+                                       timeout_);
+}
+
+template <typename F>
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::run_on_comm(c10d::OpType op, std::vector<at::Tensor> tensors, F&& fn,
+                                                             Queue* q) {
+  throw_if_failed();
+  DeviceSwitch sw(device_);
+  Queue& cq = q ? *q : comm_q_;
+  // order the comm queue after everything submitted to the compute queue so far
+  Notifier ready(false);
+  ready.place(getCurrentQueue(device_));
+  ready.wait(cq);
+  for (auto& t : tensors) recordQueue(t.storage().data_ptr(), cq);
+  auto work = make_work(op, tensors);
+  work->keep_alive_ = tensors;
+  fn(cq.handle());
+  work->notifier_.place(cq);
+  if (flags().async_disable) work->notifier_.synchronize();
+  return work;
+}
+
+// ---- host-simulated transport ----------------------------------------------------------
+std::vector<std::vector<uint8_t>> ProcessGroupB200::store_exchange(const std::vector<uint8_t>& mine, bool everyone_sends,
+                                                                   int root) {
+  const uint64_t s = ++host_seq_;
+  auto key = [&](uint64_t seq, int r) { return uid_ + "/x/" + std::to_string(seq) + "/" + std::to_string(r); };
+  if (everyone_sends || rank_ == root) store_->set(key(s, rank_), mine);
+  std::vector<std::vector<uint8_t>> all(size_);
+  for (int r = 0; r < size_; ++r) {
+    if (!everyone_sends && r != root) continue;
+    if (r == rank_) {
+      all[r] = mine;
+      continue;
+    }
+    store_->wait({key(s, r)}, timeout_);  // throws on timeout: a missing peer is detected here
+    all[r] = store_->get(key(s, r));
+  }
+  // everybody has posted round s, hence finished reading round s-2
+  if (s > 2) store_->deleteKey(key(s - 2, rank_));
+  return all;
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::hostsim_collective(c10d::OpType op, std::vector<at::Tensor> outs,
+                                                                    std::function<void()> fn) {
+  auto work = c10::make_intrusive<WorkB200>(rank_, op, std::move(outs), device_, nullptr, timeout_);
+  try {
+    fn();
+    work->finish_host();
+  } catch (...) {
+    work->finish_host(std::current_exception());
+    throw;
+  }
+  return work;
+}
+
+static std::vector<uint8_t> to_bytes(const at::Tensor& t) {
+  at::Tensor c = t.cpu().contiguous();
+  const uint8_t* p = static_cast<const uint8_t*>(c.data_ptr());
+  return std::vector<uint8_t>(p, p + c.nbytes());
+}
+static at::Tensor from_bytes(const std::vector<uint8_t>& b, const at::Tensor& like) {
+  at::Tensor c = at::empty(like.sizes(), like.options().device(at::kCPU));
+  TORCH_CHECK(b.size() == c.nbytes(), "bwccl(hostsim): message size mismatch (", b.size(), " vs ", c.nbytes(), ")");
+  std::memcpy(c.data_ptr(), b.data(), b.size());
+  return c;
+}
+static at::Tensor cpu_reduce(std::vector<at::Tensor>& parts, int op, int world) {
+  at::Tensor acc = parts[0].clone();
+  for (size_t i = 1; i < parts.size(); ++i) {
+    switch (op) {
+      case COMM_PROD: acc.mul_(parts[i]); break;
+      case COMM_MIN: acc = at::minimum(acc, parts[i]); break;
+      case COMM_MAX: acc = at::maximum(acc, parts[i]); break;
+      default: acc.add_(parts[i]);
+    }
+  }
+  if (op == COMM_AVG) acc = at::div(acc, world);
+  return acc;
+}
+
+// ---- collectives -------------------------------------------------------------------------
+static at::Tensor arithmetic_view(const at::Tensor& t) {
+  // dtypes the kernels cannot add are widened to int32 for the reduction
+  if (dtype_code(t.scalar_type()) >= 0) return t.contiguous();
+  TORCH_CHECK(c10::isIntegralType(t.scalar_type(), /*includeBool=*/true), "bwccl: unsupported dtype ", t.scalar_type());
+  return t.to(at::kInt).contiguous();
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::allreduce(std::vector<at::Tensor>& tensors,
+                                                           const c10d::AllreduceOptions& opts) {
+  check_single(tensors);
+  at::Tensor& t = tensors[0];
+  ensure_arena(t.device().index());
+  const int op = op_code(opts.reduceOp);
+  if (hostsim()) {
+    return hostsim_collective(c10d::OpType::ALLREDUCE, {t}, [&] {
+      auto all = store_exchange(to_bytes(t), true, 0);
+      std::vector<at::Tensor> parts;
+      for (auto& b : all) parts.push_back(from_bytes(b, t));
+      t.copy_(cpu_reduce(parts, op, size_));
+    });
+  }
+  at::Tensor work_t = arithmetic_view(t);
+  const bool copy_back = !work_t.is_same(t);
+  return run_on_comm(c10d::OpType::ALLREDUCE, {t, work_t}, [&, work_t, copy_back](void* stream) mutable {
+    const B200CommCtx ctx = arena_->ctx();
+    const size_t es = work_t.element_size();
+    const int64_t max_elems = static_cast<int64_t>(arena_->staging_bytes() / es);
+    char* p = static_cast<char*>(work_t.data_ptr());
+    for (int64_t done = 0; done < work_t.numel(); done += max_elems) {
+      const int64_t n = std::min<int64_t>(max_elems, work_t.numel() - done);
+      COMM_CHECK(b200_comm_copy(arena_->local(), p + done * es, n * es, stream));
+      COMM_CHECK(b200_comm_allreduce(&ctx, 0, n, dtype_code(work_t.scalar_type()), op, 1.0f, ++seq_, 0, stream));
+      COMM_CHECK(b200_comm_copy(p + done * es, arena_->local(), n * es, stream));
+    }
+    if (copy_back) {
+      QueueGuard g(comm_q_);
+      t.copy_(work_t);
+    }
+  });
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::allreduce_coalesced(std::vector<at::Tensor>& tensors,
+                                                                     const c10d::AllreduceCoalescedOptions& opts) {
+  c10::intrusive_ptr<c10d::Work> last;
+  for (auto& t : tensors) {
+    std::vector<at::Tensor> one{t};
+    last = allreduce(one, opts);
+  }
+  return last;
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::allreduce_symm(const at::Tensor& t, int64_t op, double scale,
+                                                                bool test_no_signal) {
+  TORCH_CHECK(!hostsim() && arena_, "allreduce_symm needs the CUDA backend and an initialised arena");
+  const size_t off = arena_->offset_of(t.data_ptr());
+  return run_on_comm(c10d::OpType::ALLREDUCE, {t}, [&, off](void* stream) {
+    const B200CommCtx ctx = arena_->ctx();
+    COMM_CHECK(b200_comm_allreduce(&ctx, off, t.numel(), dtype_code(t.scalar_type()), (int)op, (float)scale, ++seq_,
+                                   test_no_signal ? 1 : 0, stream));
+  });
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::broadcast(std::vector<at::Tensor>& tensors,
+                                                           const c10d::BroadcastOptions& opts) {
+  check_single(tensors);
+  at::Tensor& t = tensors[0];
+  ensure_arena(t.device().index());
+  const int root = static_cast<int>(opts.rootRank);
+  if (hostsim()) {
+    return hostsim_collective(c10d::OpType::BROADCAST, {t}, [&] {
+      auto all = store_exchange(rank_ == root ? to_bytes(t) : std::vector<uint8_t>(), false, root);
+      if (rank_ != root) t.copy_(from_bytes(all[root], t));
+    });
+  }
+  at::Tensor c = t.contiguous();
+  const bool copy_back = !c.is_same(t);
+  return run_on_comm(c10d::OpType::BROADCAST, {t, c}, [&, c, copy_back](void* stream) mutable {
+    const B200CommCtx ctx = arena_->ctx();
+    const size_t cap = arena_->staging_bytes();
+    char* p = static_cast<char*>(c.data_ptr());
+    for (size_t done = 0; done < c.nbytes() || done == 0; done += cap) {
+      const size_t n = std::min(cap, c.nbytes() - done);
+      const uint64_t s = ++seq_;
+      if (rank_ == root) {
+        COMM_CHECK(b200_comm_copy(arena_->local(), p + done, n, stream));
+        COMM_CHECK(b200_comm_signal(&ctx, 0, -1, s, stream));   // data is ready
+        COMM_CHECK(b200_comm_signal(&ctx, 1, root, s, stream));  // the root itself has nothing to pull
+        COMM_CHECK(b200_comm_wait(&ctx, 1, -1, s, stream));      // every peer has pulled
+      } else {
+        COMM_CHECK(b200_comm_wait(&ctx, 0, root, s, stream));
+        COMM_CHECK(b200_comm_copy(p + done, ctx.arena[root], n, stream));
+        COMM_CHECK(b200_comm_signal(&ctx, 1, root, s, stream));
+      }
+      if (c.nbytes() == 0) break;
+    }
+    if (copy_back && rank_ != root) {
+      QueueGuard g(comm_q_);
+      t.copy_(c);
+    }
+  });
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::reduce(std::vector<at::Tensor>& tensors, const c10d::ReduceOptions& opts) {
+  check_single(tensors);
+  at::Tensor& t = tensors[0];
+  ensure_arena(t.device().index());
+  const int op = op_code(opts.reduceOp);
+  const int root = static_cast<int>(opts.rootRank);
+  if (hostsim()) {
+    return hostsim_collective(c10d::OpType::REDUCE, {t}, [&] {
+      auto all = store_exchange(to_bytes(t), true, 0);
+      if (rank_ == root) {
+        std::vector<at::Tensor> parts;
+        for (auto& b : all) parts.push_back(from_bytes(b, t));
+        t.copy_(cpu_reduce(parts, op, size_));
+      }
+    });
+  }
+  at::Tensor work_t = arithmetic_view(t);
+  return run_on_comm(c10d::OpType::REDUCE, {t, work_t}, [&, work_t](void* stream) mutable {
+    const B200CommCtx ctx = arena_->ctx();
+    const size_t es = work_t.element_size();
+    const int64_t max_elems = static_cast<int64_t>(arena_->staging_bytes() / es);
+    char* p = static_cast<char*>(work_t.data_ptr());
+    for (int64_t done = 0; done < work_t.numel(); done += max_elems) {
+      const int64_t n = std::min<int64_t>(max_elems, work_t.numel() - done);
+      COMM_CHECK(b200_comm_copy(arena_->local(), p + done * es, n * es, stream));
+      COMM_CHECK(b200_comm_allreduce(&ctx, 0, n, dtype_code(work_t.scalar_type()), op, 1.0f, ++seq_, 0, stream));
+      if (rank_ == root) COMM_CHECK(b200_comm_copy(p + done * es, arena_->local(), n * es, stream));
+    }
+    if (rank_ == root && !work_t.is_same(t)) {
+      QueueGuard g(comm_q_);
+      t.copy_(work_t);
+    }
+  });
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::_allgather_base(at::Tensor& output, at::Tensor& input,
+                                                                 const c10d::AllgatherOptions&) {
+  TORCH_CHECK(is_b200(input) && is_b200(output), "bwccl: tensors must live on the blackwell device");
+  TORCH_CHECK(output.numel() == input.numel() * size_ && output.scalar_type() == input.scalar_type(),
+              "bwccl: all_gather output must hold world_size inputs");
+  ensure_arena(input.device().index());
+  if (hostsim()) {
+    return hostsim_collective(c10d::OpType::_ALLGATHER_BASE, {output}, [&] {
+      auto all = store_exchange(to_bytes(input), true, 0);
+      at::Tensor flat = output.view({size_, -1});
+      for (int r = 0; r < size_; ++r) flat[r].copy_(from_bytes(all[r], input).view({-1}));
+    });
+  }
+  TORCH_CHECK(output.is_contiguous(), "bwccl: all_gather output must be contiguous");
+  at::Tensor in = input.contiguous();
+  return run_on_comm(c10d::OpType::_ALLGATHER_BASE, {output, in}, [&, in](void* stream) mutable {
+    const B200CommCtx ctx = arena_->ctx();
+    const size_t cap = arena_->staging_bytes();
+    const size_t total = in.nbytes();
+    char* src = static_cast<char*>(in.data_ptr());
+    char* dst = static_cast<char*>(output.data_ptr());
+    for (size_t done = 0; done < total; done += cap) {
+      const size_t n = std::min(cap, total - done);
+      const uint64_t s = ++seq_;
+      COMM_CHECK(b200_comm_copy(arena_->local(), src + done, n, stream));
+      COMM_CHECK(b200_comm_signal(&ctx, 0, -1, s, stream));
+      COMM_CHECK(b200_comm_wait(&ctx, 0, -1, s, stream));
+      for (int i = 0; i < size_; ++i) {
+        const int p = (rank_ + i) % size_;
+        COMM_CHECK(b200_comm_copy(dst + p * total + done, ctx.arena[p], n, stream));
+      }
+      COMM_CHECK(b200_comm_signal(&ctx, 1, -1, s, stream));
+      COMM_CHECK(b200_comm_wait(&ctx, 1, -1, s, stream));
+    }
+  });
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::allgather(std::vector<std::vector<at::Tensor>>& outputs,
+                                                           std::vector<at::Tensor>& inputs,
+                                                           const c10d::AllgatherOptions& opts) {
+  check_single(inputs);
+  TORCH_CHECK(outputs.size() == 1 && static_cast<int>(outputs[0].size()) == size_,
+              "bwccl: all_gather expects one output list with world_size tensors");
+  at::Tensor& in = inputs[0];
+  for (auto& o : outputs[0])
+    TORCH_CHECK(o.sizes() == in.sizes() && o.scalar_type() == in.scalar_type(), "bwccl: all_gather output shape / dtype mismatch");
+  ensure_arena(in.device().index());
+  // gather straight into one flat tensor, then hand out the pieces
+  at::Tensor flat = at::empty({size_, in.numel()}, in.options());
+  auto work = _allgather_base(flat, in, opts);
+  if (hostsim()) {
+    for (int r = 0; r < size_; ++r) outputs[0][r].copy_(flat[r].view(in.sizes()));
+    return work;
+  }
+  {
+    QueueGuard g(comm_q_);
+    for (int r = 0; r < size_; ++r) outputs[0][r].copy_(flat[r].view(in.sizes()));
+  }
+  auto w = c10::static_intrusive_pointer_cast<WorkB200>(work);
+  w->keep_alive_.push_back(flat);
+  w->notifier_.place(comm_q_);
+  return work;
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::_reduce_scatter_base(at::Tensor& output, at::Tensor& input,
+                                                                      const c10d::ReduceScatterOptions& opts) {
+  TORCH_CHECK(input.numel() == output.numel() * size_, "bwccl: reduce_scatter input must hold world_size outputs");
+  at::Tensor tmp = input.clone();
+  std::vector<at::Tensor> v{tmp};
+  c10d::AllreduceOptions ao;
+  ao.reduceOp = opts.reduceOp;
+  auto work = allreduce(v, ao);
+  if (hostsim()) {
+    output.copy_(tmp.view({size_, -1})[rank_].view(output.sizes()));
+    return work;
+  }
+  {
+    QueueGuard g(comm_q_);
+    output.copy_(tmp.view({size_, -1})[rank_].view(output.sizes()));
+  }
+  auto w = c10::static_intrusive_pointer_cast<WorkB200>(work);
+  w->keep_alive_.push_back(tmp);
+  w->notifier_.place(comm_q_);
+  return work;
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::reduce_scatter(std::vector<at::Tensor>& outputs,
+                                                                std::vector<std::vector<at::Tensor>>& inputs,
+                                                                const c10d::ReduceScatterOptions& opts) {
+  check_single(outputs);
+  TORCH_CHECK(inputs.size() == 1 && static_cast<int>(inputs[0].size()) == size_, "bwccl: reduce_scatter expects world_size inputs");
+  std::vector<at::Tensor> flat_parts;
+  for (auto& t : inputs[0]) flat_parts.push_back(t.reshape({-1}));
+  at::Tensor flat = at::cat(flat_parts);
+  return _reduce_scatter_base(outputs[0], flat, opts);
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::send(std::vector<at::Tensor>& tensors, int dst, int) {
+  check_single(tensors);
+  TORCH_CHECK(dst != rank_ && dst >= 0 && dst < size_, "bwccl: invalid destination rank ", dst, " (sending to self is not supported)");
+  at::Tensor t = tensors[0].contiguous();
+  ensure_arena(t.device().index());
+  if (hostsim()) {
+    return hostsim_collective(c10d::OpType::SEND, {}, [&] {
+      const uint64_t s = ++send_seq_[dst];
+      store_->set(uid_ + "/p2p/" + std::to_string(rank_) + ">" + std::to_string(dst) + "/" + std::to_string(s), to_bytes(t));
+    });
+  }
+  return run_on_comm(c10d::OpType::SEND, {t}, [&, t](void* stream) mutable {
+    const B200CommCtx ctx = arena_->ctx();
+    const size_t cap = arena_->mailbox_bytes();
+    char* p = static_cast<char*>(t.data_ptr());
+    for (size_t done = 0; done < t.nbytes() || done == 0; done += cap) {
+      const size_t n = std::min(cap, t.nbytes() - done);
+      const uint64_t s = ++send_seq_[dst];
+      COMM_CHECK(b200_comm_copy(arena_->local() + arena_->mailbox_offset(), p + done, n, stream));
+      COMM_CHECK(b200_comm_signal(&ctx, 2, dst, s, stream));
+      COMM_CHECK(b200_comm_wait(&ctx, 3, dst, s, stream));
+      if (t.nbytes() == 0) break;
+    }
+  }, &send_q_);
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::recv(std::vector<at::Tensor>& tensors, int src, int) {
+  check_single(tensors);
+  TORCH_CHECK(src != rank_ && src >= 0 && src < size_, "bwccl: invalid source rank ", src);
+  at::Tensor& t = tensors[0];
+  ensure_arena(t.device().index());
+  if (hostsim()) {
+    return hostsim_collective(c10d::OpType::RECV, {t}, [&] {
+      const uint64_t s = ++recv_seq_[src];
+      const std::string key = uid_ + "/p2p/" + std::to_string(src) + ">" + std::to_string(rank_) + "/" + std::to_string(s);
+      store_->wait({key}, timeout_);
+      t.copy_(from_bytes(store_->get(key), t));
+      store_->deleteKey(key);
+    });
+  }
+  at::Tensor c = t.is_contiguous() ? t : at::empty_like(t, at::MemoryFormat::Contiguous);
+  return run_on_comm(c10d::OpType::RECV, {t, c}, [&, c](void* stream) mutable {
+    const B200CommCtx ctx = arena_->ctx();
+    const size_t cap = arena_->mailbox_bytes();
+    char* p = static_cast<char*>(c.data_ptr());
+    for (size_t done = 0; done < c.nbytes() || done == 0; done += cap) {
+      const size_t n = std::min(cap, c.nbytes() - done);
+      const uint64_t s = ++recv_seq_[src];
+      COMM_CHECK(b200_comm_wait(&ctx, 2, src, s, stream));
+      COMM_CHECK(b200_comm_copy(p + done, static_cast<char*>(ctx.arena[src]) + arena_->mailbox_offset(), n, stream));
+      COMM_CHECK(b200_comm_signal(&ctx, 3, src, s, stream));
+      if (c.nbytes() == 0) break;
+    }
+    if (!c.is_same(t)) {
+      QueueGuard g(recv_q_);
+      t.copy_(c);
+    }
+  }, &recv_q_);
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::barrier(const c10d::BarrierOptions&) {
+  ensure_arena(device_ >= 0 ? device_ : current_device());
+  if (hostsim()) {
+    return hostsim_collective(c10d::OpType::BARRIER, {}, [&] { store_exchange({1}, true, 0); });
+  }
+  auto work = run_on_comm(c10d::OpType::BARRIER, {}, [&](void* stream) {
+    const B200CommCtx ctx = arena_->ctx();
+    const uint64_t s = ++seq_;
+    COMM_CHECK(b200_comm_signal(&ctx, 0, -1, s, stream));
+    COMM_CHECK(b200_comm_wait(&ctx, 0, -1, s, stream));
+    COMM_CHECK(b200_comm_signal(&ctx, 1, -1, s, stream));
+    COMM_CHECK(b200_comm_wait(&ctx, 1, -1, s, stream));
+  });
+  // a barrier is a host-visible synchronisation point
+  auto w = c10::static_intrusive_pointer_cast<WorkB200>(work);
+  w->notifier_.synchronize();
+  if (w->exception()) std::rethrow_exception(w->exception());
+  return work;
+}
+
+// ---- fused DDP path -------------------------------------------------------------------------
+at::Tensor ProcessGroupB200::symm_empty(int64_t numel, at::ScalarType dtype) {
+  ensure_arena(device_ >= 0 ? device_ : current_device());
+  TORCH_CHECK(!hostsim() && arena_, "symm_empty needs the CUDA backend");
+  const size_t bytes = static_cast<size_t>(numel) * c10::elementSize(dtype);
+  const size_t off = arena_->user_alloc(bytes + 16 * size_);  // room for shard padding
+  void* ptr = arena_->local() + off;
+  c10::DataPtr dp(ptr, nullptr, [](void*) {}, make_device(device_));
+  auto storage = c10::make_intrusive<c10::StorageImpl>(c10::StorageImpl::use_byte_size_t(), bytes, std::move(dp), nullptr, false);
+  at::Tensor t = at::detail::make_tensor<B200TensorImpl>(c10::Storage(std::move(storage)),
+                                                         c10::DispatchKeySet(c10::DispatchKey::PrivateUse1),
+                                                         c10::scalarTypeToTypeMeta(dtype));
+  t.unsafeGetTensorImpl()->set_sizes_contiguous({numel});
+  return t;
+}
+
+int64_t ProcessGroupB200::shard_elems(int64_t numel, at::ScalarType dtype) const {
+  return b200_comm_shard_elems(numel, size_, dtype_code(dtype));
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::fused_allreduce_step(
+    const at::Tensor& grads, const at::Tensor& params, const at::Tensor& state1, const at::Tensor& state2, int64_t kind,
+    double lr, double momentum, double dampening, double weight_decay, double beta1, double beta2, double eps,
+    int64_t step, bool nesterov, bool first_step, double scale) {
+  TORCH_CHECK(!hostsim() && arena_, "fused_allreduce_step needs the CUDA backend");
+  TORCH_CHECK(params.scalar_type() == at::kFloat && grads.numel() == params.numel(), "fused_allreduce_step: params must be fp32 and match grads");
+  const int64_t shard = shard_elems(grads.numel(), grads.scalar_type());
+  TORCH_CHECK(state1.scalar_type() == at::kFloat && state1.numel() >= shard, "fused_allreduce_step: state shard too small");
+  const size_t goff = arena_->offset_of(grads.data_ptr()), poff = arena_->offset_of(params.data_ptr());
+  B200FusedOptArgs o;
+  std::memset(&o, 0, sizeof(o));
+  o.kind = (int)kind;
+  o.lr = (float)lr; o.momentum = (float)momentum; o.dampening = (float)dampening; o.weight_decay = (float)weight_decay;
+  o.beta1 = (float)beta1; o.beta2 = (float)beta2; o.eps = (float)eps;
+  o.bc1 = kind == 1 ? (float)(1.0 - std::pow(beta1, (double)step)) : 1.f;
+  o.bc2_sqrt = kind == 1 ? (float)std::sqrt(1.0 - std::pow(beta2, (double)step)) : 1.f;
+  o.nesterov = nesterov; o.first_step = first_step;
+  o.state1 = state1.data_ptr<float>();
+  o.state2 = state2.defined() && state2.numel() ? state2.data_ptr<float>() : nullptr;
+  return run_on_comm(c10d::OpType::ALLREDUCE, {grads, params, state1}, [&, goff, poff, o](void* stream) {
+    const B200CommCtx ctx = arena_->ctx();
+    COMM_CHECK(b200_comm_allreduce_opt(&ctx, goff, poff, grads.numel(), dtype_code(grads.scalar_type()), (float)scale, &o,
+                                       ++seq_, stream));
+  });
+}
+
+void ProcessGroupB200::set_wait_limit_ms(int64_t ms) {
+  if (arena_) arena_->set_timeout_ns(static_cast<unsigned long long>(ms) * 1000000ull);
+}
+int64_t ProcessGroupB200::status_word() const { return arena_ ? *((volatile int*)arena_->status_host()) : 0; }
+void ProcessGroupB200::clear_status() {
+  if (arena_) *((volatile int*)arena_->status_host()) = 0;
+}
+
+}  // namespace catch_b200

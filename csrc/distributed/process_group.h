@@ -1,0 +1,130 @@
+// torch.distributed backend of the b200 device ("bwccl").
+//
+// Capability parity with ProcessGroupCNCL (torch_mlu/csrc/distributed/
+// process_group_cncl.{hpp,cpp}): one process per device; collectives run on a
+// dedicated communication queue that is ordered against the compute queue with
+// notifiers (no host blocking); tensors handed to a collective are recorded on the
+// comm queue so the caching allocator does not recycle them early; bootstrap goes
+// through the c10d Store.  Differences on purpose: the transport is this project's
+// own kernels over peer-mapped memory (comm.cu) instead of a vendor library;
+// timeouts are honoured and device-side wait failures surface as exceptions (the
+// reference ignores the timeout and never reports asynchronous errors,
+// process_group_cncl.cpp:107-115,583-589); reduce_scatter / _allgather_base /
+// allreduce_coalesced are implemented.
+// Under host simulation the same class moves bytes through the Store, so rank
+// logic, ordering, time-outs and failure handling are testable without GPUs.
+#pragma once
+#include <torch/csrc/distributed/c10d/Backend.hpp>
+#include <torch/csrc/distributed/c10d/Store.hpp>
+#include <torch/csrc/distributed/c10d/Work.hpp>
+
+#include <atomic>
+#include <memory>
+
+#include "../device/kernels_api.h"
+#include "../runtime/notifier.h"
+#include "../runtime/queue.h"
+
+namespace catch_b200 {
+
+class SymmetricArena;
+
+class WorkB200 : public c10d::Work {
+ public:
+  WorkB200(int rank, c10d::OpType op, std::vector<at::Tensor> outputs, int device, int* status,
+           std::chrono::milliseconds timeout);
+  bool isCompleted() override;
+  bool isSuccess() const override;
+  std::exception_ptr exception() const override;
+  bool wait(std::chrono::milliseconds timeout = kNoTimeout) override;
+  void synchronize() override;
+  std::vector<at::Tensor> result() override { return outputs_; }
+  c10::intrusive_ptr<c10::ivalue::Future> getFuture() override;
+  void finish_host(std::exception_ptr err = nullptr);  // host-only work (hostsim / errors)
+
+  Notifier notifier_{/*enable_timing=*/false};
+  std::vector<at::Tensor> keep_alive_;
+
+ private:
+  void check_status() const;
+  std::vector<at::Tensor> outputs_;
+  int device_;
+  int* status_;
+  std::chrono::milliseconds timeout_;
+  bool host_done_ = false;
+  std::exception_ptr error_;
+  c10::intrusive_ptr<c10::ivalue::Future> future_;
+};
+
+class ProcessGroupB200 : public c10d::Backend {
+ public:
+  ProcessGroupB200(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size, std::chrono::milliseconds timeout);
+  ~ProcessGroupB200() override;
+
+  const std::string getBackendName() const override { return "bwccl"; }
+  void setTimeout(std::chrono::milliseconds timeout) override { timeout_ = timeout; }
+
+  c10::intrusive_ptr<c10d::Work> broadcast(std::vector<at::Tensor>& tensors, const c10d::BroadcastOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> allreduce(std::vector<at::Tensor>& tensors, const c10d::AllreduceOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> allreduce_coalesced(std::vector<at::Tensor>& tensors,
+                                                     const c10d::AllreduceCoalescedOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> reduce(std::vector<at::Tensor>& tensors, const c10d::ReduceOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> allgather(std::vector<std::vector<at::Tensor>>& outputs, std::vector<at::Tensor>& inputs,
+                                           const c10d::AllgatherOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> _allgather_base(at::Tensor& output, at::Tensor& input,
+                                                 const c10d::AllgatherOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> reduce_scatter(std::vector<at::Tensor>& outputs,
+                                                std::vector<std::vector<at::Tensor>>& inputs,
+                                                const c10d::ReduceScatterOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> _reduce_scatter_base(at::Tensor& output, at::Tensor& input,
+                                                      const c10d::ReduceScatterOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> send(std::vector<at::Tensor>& tensors, int dst, int tag) override;
+  c10::intrusive_ptr<c10d::Work> recv(std::vector<at::Tensor>& tensors, int src, int tag) override;
+  c10::intrusive_ptr<c10d::Work> barrier(const c10d::BarrierOptions& opts) override;
+
+  // ---- fused DDP path -------------------------------------------------------------
+  // A tensor that lives in this rank's arena at the same offset on every rank.
+  at::Tensor symm_empty(int64_t numel, at::ScalarType dtype);
+  // reduce-scatter of `grads` (a symm_empty tensor) * scale, optimizer step on this
+  // rank's shard of `params` (a symm_empty fp32 tensor), all-gather of the parameters.
+  c10::intrusive_ptr<c10d::Work> fused_allreduce_step(const at::Tensor& grads, const at::Tensor& params,
+                                                      const at::Tensor& state1, const at::Tensor& state2, int64_t kind,
+                                                      double lr, double momentum, double dampening, double weight_decay,
+                                                      double beta1, double beta2, double eps, int64_t step,
+                                                      bool nesterov, bool first_step, double scale);
+  int64_t shard_elems(int64_t numel, at::ScalarType dtype) const;
+  // all-reduce in place on a symm_empty tensor (no staging copies)
+  c10::intrusive_ptr<c10d::Work> allreduce_symm(const at::Tensor& t, int64_t op, double scale, bool test_no_signal);
+  void set_wait_limit_ms(int64_t ms);
+  int64_t status_word() const;
+  void clear_status();
+  int device_index() const { return device_; }
+
+ private:
+  void ensure_arena(int device);
+  void check_single(const std::vector<at::Tensor>& tensors) const;
+  c10::intrusive_ptr<WorkB200> make_work(c10d::OpType op, std::vector<at::Tensor> outputs);
+  // runs fn(stream) on the comm queue ordered after the current compute queue
+  template <typename F>
+  c10::intrusive_ptr<c10d::Work> run_on_comm(c10d::OpType op, std::vector<at::Tensor> tensors, F&& fn, Queue* q = nullptr);
+  void throw_if_failed() const;
+  // host-simulated transport
+  std::vector<std::vector<uint8_t>> store_exchange(const std::vector<uint8_t>& mine, bool everyone_sends, int root);
+  c10::intrusive_ptr<c10d::Work> hostsim_collective(c10d::OpType op, std::vector<at::Tensor> outs,
+                                                    std::function<void()> fn);
+
+  c10::intrusive_ptr<c10d::Store> store_;
+  std::chrono::milliseconds timeout_;
+  int device_ = -1;
+  std::unique_ptr<SymmetricArena> arena_;
+  Queue comm_q_, send_q_, recv_q_;
+  uint64_t seq_ = 0;
+  std::vector<uint64_t> send_seq_, recv_seq_;
+  uint64_t host_seq_ = 0;
+  std::string uid_;
+};
+
+// Number of ProcessGroupB200 objects created so far in this process (names Store keys).
+int next_process_group_id();
+
+}  // namespace catch_b200

@@ -197,8 +197,20 @@ Tensor forward_impl(const Tensor& input, const Tensor& weight, const std::option
   return out;
 }
 
-Tensor dgrad_impl(const Tensor& grad, const Tensor& weight, const ConvGeom& g, at::ScalarType out_dtype) {
-  const at::ScalarType dt = compute_dtype(grad.scalar_type());
+// fp32 gradients are computed on fp16 tensor cores; a power-of-two scale moves
+// them into fp16's normal range first (gradients of a mean-reduced loss are tiny)
+// and is divided out again in the epilogue.
+double fp16_safe_scale(const Tensor& grad) {
+  if (grad.scalar_type() != at::kFloat || grad.numel() == 0) return 1.0;
+  const double amax = grad.abs().max().item<double>();
+  if (!(amax > 0.0) || !std::isfinite(amax)) return 1.0;
+  return std::exp2(std::floor(std::log2(1024.0 / amax)));
+}
+
+Tensor dgrad_impl(const Tensor& grad_in, const Tensor& weight, const ConvGeom& g, at::ScalarType out_dtype) {
+  const at::ScalarType dt = compute_dtype(grad_in.scalar_type());
+  const double gscale = fp16_safe_scale(grad_in);
+  const Tensor grad = gscale == 1.0 ? grad_in : grad_in * gscale;
   OpScope scope("conv_dgrad", grad);
   Tensor dx = empty_b200({g.N, g.C, g.H, g.W}, out_dtype, grad.device().index(), at::MemoryFormat::ChannelsLast);
   if (dx.numel() == 0) return dx;
@@ -240,6 +252,7 @@ Tensor dgrad_impl(const Tensor& grad, const Tensor& weight, const ConvGeom& g, a
       p.out = dx.data_ptr(); p.out_dtype = to_b200_dtype(out_dtype);
       p.o_sn = dx.stride(0); p.o_sh = dx.stride(2); p.o_sw = dx.stride(3);
       p.o_mul_h = (int)g.sh; p.o_off_h = (int)a; p.o_mul_w = (int)g.sw; p.o_off_w = (int)b;
+      p.alpha = (float)(1.0 / gscale);
       launches.push_back(p);
     }
   }
@@ -248,8 +261,10 @@ Tensor dgrad_impl(const Tensor& grad, const Tensor& weight, const ConvGeom& g, a
   return dx;
 }
 
-Tensor wgrad_impl(const Tensor& grad, const Tensor& input, const Tensor& weight, const ConvGeom& g) {
-  const at::ScalarType dt = compute_dtype(grad.scalar_type());
+Tensor wgrad_impl(const Tensor& grad_in, const Tensor& input, const Tensor& weight, const ConvGeom& g) {
+  const at::ScalarType dt = compute_dtype(grad_in.scalar_type());
+  const double gscale = fp16_safe_scale(grad_in);
+  const Tensor grad = gscale == 1.0 ? grad_in : grad_in * gscale;
   OpScope scope("conv_wgrad", grad);
   Tensor dy = to_nhwc(grad, dt);
   B200ConvWgradParams p;
@@ -284,7 +299,7 @@ Tensor wgrad_impl(const Tensor& grad, const Tensor& input, const Tensor& weight,
     dw = acc.view({g.K, g.R, g.S, g.C}).permute({0, 3, 1, 2});
   }
   Tensor out = at::empty_like(weight, weight.options(), weight.suggest_memory_format());
-  out.copy_(dw);
+  out.copy_(gscale == 1.0 ? dw : dw * (1.0 / gscale));
   return out;
 }
 

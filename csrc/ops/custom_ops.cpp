@@ -1,0 +1,78 @@
+// Custom operator schemas of the backend (namespace catch_b200):
+//   conv_bn_act / linear_act        -- fused inference ops produced by the fusion pass
+//   conv2d / linear (quantized)     -- int8 ops with the reference's argument order
+//                                      (torch_mlu/core/quantized/modules/conv.py:182-190, linear.py:44-48)
+//   softmax_cross_entropy           -- fused loss (value and logits gradient)
+//   fused_sgd_step / fused_adamw_step
+//   dump                            -- device printf of a tensor (reference: torch_mlu::dump)
+#include <torch/library.h>
+#include "common.h"
+
+namespace catch_b200 {
+namespace ops {
+
+at::Tensor linear_act(const at::Tensor& x, const at::Tensor& w, const std::optional<at::Tensor>& bias, int64_t act);
+at::Tensor conv_bn_act_device(const at::Tensor& input, const at::Tensor& weight, const std::optional<at::Tensor>& scale,
+                              const std::optional<at::Tensor>& bias, const std::optional<at::Tensor>& residual,
+                              at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation, int64_t groups,
+                              int64_t act);
+std::tuple<at::Tensor, at::Tensor> softmax_cross_entropy(const at::Tensor& logits, const at::Tensor& target,
+                                                         int64_t ignore_index, double label_smoothing);
+void fused_sgd_step(at::TensorList params, at::TensorList grads, at::TensorList momentum_bufs, at::TensorList lowp,
+                    double lr, double momentum, double dampening, double weight_decay, bool nesterov, bool first_step,
+                    double grad_scale);
+void fused_adamw_step(at::TensorList params, at::TensorList grads, at::TensorList exp_avg, at::TensorList exp_avg_sq,
+                      at::TensorList lowp, double lr, double beta1, double beta2, double eps, double weight_decay,
+                      int64_t step, double grad_scale, bool adam_l2_mode);
+bool dump_tensor_device(const at::Tensor& t);
+
+// act(conv(x, w) * scale + bias + residual); runs the fused tcgen05 kernel when it
+// can, otherwise composes stock ops (which themselves dispatch to this backend).
+static at::Tensor conv_bn_act(const at::Tensor& input, const at::Tensor& weight, const std::optional<at::Tensor>& scale,
+                              const std::optional<at::Tensor>& bias, const std::optional<at::Tensor>& residual,
+                              at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation, int64_t groups,
+                              int64_t act) {
+  auto compose = [&]() {
+    at::Tensor y = at::conv2d(input, weight, {}, stride, padding, dilation, groups);
+    if (scale.has_value() && scale->defined()) y = y * scale->to(y.scalar_type()).view({1, -1, 1, 1});
+    if (bias.has_value() && bias->defined()) y = y + bias->to(y.scalar_type()).view({1, -1, 1, 1});
+    if (residual.has_value() && residual->defined()) y = y + *residual;
+    if (act == 1) y = at::relu(y);
+    return y;
+  };
+  if (use_cpu_path() || !is_b200(input)) return compose();
+  if (!flags().op_trycatch)
+    return conv_bn_act_device(input, weight, scale, bias, residual, stride, padding, dilation, groups, act);
+  try {
+    return conv_bn_act_device(input, weight, scale, bias, residual, stride, padding, dilation, groups, act);
+  } catch (const c10::OutOfMemoryError&) {
+    throw;
+  } catch (const std::exception& e) {
+    B200LOG(DBG) << "conv_bn_act: fused kernel rejected the configuration (" << e.what() << "); composing stock ops.";
+    return compose();
+  }
+}
+
+TORCH_LIBRARY(catch_b200, m) {
+  m.def("conv_bn_act(Tensor input, Tensor weight, Tensor? scale, Tensor? bias, Tensor? residual, int[] stride, "
+        "int[] padding, int[] dilation, int groups, int act) -> Tensor");
+  m.def("linear_act(Tensor input, Tensor weight, Tensor? bias, int act) -> Tensor");
+  m.def("softmax_cross_entropy(Tensor logits, Tensor target, int ignore_index, float label_smoothing) -> (Tensor, Tensor)");
+  m.def("fused_sgd_step(Tensor[] params, Tensor[] grads, Tensor[] momentum_bufs, Tensor[] lowp, float lr, float momentum, "
+        "float dampening, float weight_decay, bool nesterov, bool first_step, float grad_scale) -> ()");
+  m.def("fused_adamw_step(Tensor[] params, Tensor[] grads, Tensor[] exp_avg, Tensor[] exp_avg_sq, Tensor[] lowp, float lr, "
+        "float beta1, float beta2, float eps, float weight_decay, int step, float grad_scale, bool adam_l2_mode) -> ()");
+  m.def("dump(Tensor t) -> bool");
+}
+
+TORCH_LIBRARY_IMPL(catch_b200, CompositeExplicitAutograd, m) {
+  m.impl("conv_bn_act", TORCH_FN(conv_bn_act));
+  m.impl("linear_act", TORCH_FN(linear_act));
+  m.impl("softmax_cross_entropy", TORCH_FN(softmax_cross_entropy));
+  m.impl("fused_sgd_step", TORCH_FN(fused_sgd_step));
+  m.impl("fused_adamw_step", TORCH_FN(fused_adamw_step));
+  m.impl("dump", TORCH_FN(dump_tensor_device));
+}
+
+}  // namespace ops
+}  // namespace catch_b200

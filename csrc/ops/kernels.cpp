@@ -1,7 +1,14 @@
 #include "kernels.h"
 
+#include <atomic>
+
 namespace catch_b200 {
 namespace ops {
+
+static std::atomic<long long> g_launches{0};
+void note_kernel_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+long long kernel_launch_count() { return g_launches.load(); }
+void reset_kernel_launch_count() { g_launches.store(0); }
 
 static int compute_class(at::ScalarType t) {
   if (t == at::kDouble) return 1;

@@ -8,8 +8,14 @@
 namespace catch_b200 {
 namespace ops {
 
+// Every launcher call that reaches the device is counted (benchmarks report it).
+void note_kernel_launch();
+long long kernel_launch_count();
+void reset_kernel_launch_count();
+
 #define B200_KERNEL_CHECK(expr)                                                                     \
   do {                                                                                              \
+    ::catch_b200::ops::note_kernel_launch();                                                        \
     int _e = (expr);                                                                                \
     TORCH_CHECK(_e == 0, "b200 kernel launch failed: ", ::catch_b200::device_error_string(_e), " (", \
                 #expr, ")");                                                                        \
@@ -30,6 +36,8 @@ inline int to_b200_dtype(at::ScalarType t) {
     default: TORCH_CHECK(false, "b200: unsupported dtype ", t);
   }
 }
+
+inline long long* i64ptr(const at::Tensor& t) { return reinterpret_cast<long long*>(t.data_ptr<int64_t>()); }
 
 // Launches the element-wise family over a built TensorIterator (operand 0 is
 // the output).  `s0`/`s1` are the op's scalar parameters.

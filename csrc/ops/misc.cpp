@@ -1,0 +1,224 @@
+// Embedding, index_select, random number operators, dropout, the device dump
+// op and the fused optimizer steps.
+//
+// Parity: index_select.cpp / the generator of the reference; embedding, dropout
+// and the fused optimizers are new (the reference runs them through the CPU
+// fallback or as many small element-wise launches).
+#include <ATen/core/op_registration/op_registration.h>
+#include "../runtime/generator.h"
+#include "common.h"
+#include "kernels.h"
+
+namespace catch_b200 {
+namespace ops {
+namespace {
+
+using at::Tensor;
+
+bool f_ok(at::ScalarType t) { return t == at::kFloat || t == at::kBFloat16 || t == at::kHalf; }
+
+Tensor embedding_device(const Tensor& weight, const Tensor& indices, int64_t padding_idx) {
+  TORCH_CHECK(weight.dim() == 2 && indices.scalar_type() == at::kLong, "b200 embedding: weight must be 2-D and indices int64");
+  OpScope scope("embedding", weight);
+  Tensor w = weight.contiguous(), idx = indices.contiguous();
+  std::vector<int64_t> shape(indices.sizes().begin(), indices.sizes().end());
+  shape.push_back(w.size(1));
+  Tensor out = empty_b200(shape, w.scalar_type(), w.device().index());
+  B200_KERNEL_CHECK(b200_index_select_rows(w.data_ptr(), (int)w.element_size(), i64ptr(idx), idx.numel(), w.size(1),
+                                           w.size(0), out.data_ptr(), scope.stream()));
+  (void)padding_idx;
+  return out;
+}
+Tensor k_embedding(const Tensor& weight, const Tensor& indices, c10::SymInt padding_idx, bool scale, bool sparse) {
+  return B200_DISPATCH("embedding", embedding_device(weight, indices, padding_idx.expect_int()),
+                       B200_CPU_SYMINT(embedding, weight, indices, padding_idx, scale, sparse));
+}
+Tensor embedding_bwd_device(const Tensor& grad, const Tensor& indices, int64_t num_weights, int64_t padding_idx, bool scale) {
+  TORCH_CHECK(!scale && f_ok(grad.scalar_type()) && indices.scalar_type() == at::kLong, "b200 embedding_backward: unsupported arguments");
+  OpScope scope("embedding_dense_backward", grad);
+  Tensor g = grad.contiguous().view({-1, grad.size(-1)}), idx = indices.contiguous();
+  // accumulate in fp32 for accuracy, then cast
+  Tensor acc = at::zeros({num_weights, g.size(1)}, grad.options().dtype(at::kFloat));
+  B200_KERNEL_CHECK(b200_embedding_bwd(g.data_ptr(), to_b200_dtype(g.scalar_type()), i64ptr(idx), idx.numel(), (int)g.size(1),
+                                       padding_idx, acc.data_ptr(), B200_F32, scope.stream()));
+  return grad.scalar_type() == at::kFloat ? acc : acc.to(grad.scalar_type());
+}
+Tensor k_embedding_dense_backward(const Tensor& grad, const Tensor& indices, c10::SymInt num_weights, c10::SymInt padding_idx,
+                                  bool scale) {
+  return B200_DISPATCH("embedding_dense_backward",
+                       embedding_bwd_device(grad, indices, num_weights.expect_int(), padding_idx.expect_int(), scale),
+                       B200_CPU_SYMINT(embedding_dense_backward, grad, indices, num_weights, padding_idx, scale));
+}
+
+Tensor index_select_device(const Tensor& self, int64_t dim, const Tensor& index) {
+  TORCH_CHECK(index.dim() <= 1 && index.scalar_type() == at::kLong, "b200 index_select: index must be a 1-D int64 tensor");
+  dim = at::maybe_wrap_dim(dim, self.dim());
+  OpScope scope("index_select", self);
+  if (self.dim() == 0) return self.clone();
+  Tensor x = self.movedim(dim, 0).contiguous();
+  Tensor idx = index.contiguous().view({-1});
+  std::vector<int64_t> shape(x.sizes().begin(), x.sizes().end());
+  const int64_t n_src = shape[0];
+  shape[0] = idx.numel();
+  Tensor out = empty_b200(shape, self.scalar_type(), self.device().index());
+  const int64_t row = n_src ? x.numel() / n_src : 0;
+  B200_KERNEL_CHECK(b200_index_select_rows(x.data_ptr(), (int)x.element_size(), i64ptr(idx), idx.numel(), row, n_src,
+                                           out.data_ptr(), scope.stream()));
+  return out.movedim(0, dim);
+}
+Tensor k_index_select(const Tensor& self, int64_t dim, const Tensor& index) {
+  return B200_DISPATCH("index_select", index_select_device(self, dim, index), B200_CPU(index_select, self, dim, index));
+}
+
+// ---- random ---------------------------------------------------------------------------
+std::pair<uint64_t, uint64_t> philox(std::optional<at::Generator> gen, const Tensor& t, uint64_t n) {
+  auto g = at::get_generator_or_default<B200GeneratorImpl>(gen, getDefaultB200Generator(t.device().index()));
+  std::lock_guard<std::mutex> lock(g->mutex_);
+  return g->philox_engine_inputs(n);
+}
+Tensor& rng_fill(Tensor& self, std::optional<at::Generator> gen, int mode, double a, double b) {
+  if (self.numel() == 0) return self;
+  TORCH_CHECK(f_ok(self.scalar_type()) || self.scalar_type() == at::kDouble || (mode == 2),
+              "b200 random fill: unsupported dtype ", self.scalar_type());
+  OpScope scope("random_fill", self);
+  Tensor dst = self.is_contiguous() ? self : at::empty_like(self, at::MemoryFormat::Contiguous);
+  auto so = philox(gen, self, (uint64_t)dst.numel());
+  const int dt = to_b200_dtype(dst.scalar_type());
+  if (mode == 0) B200_KERNEL_CHECK(b200_rng_uniform(dst.data_ptr(), dt, dst.numel(), so.first, so.second, a, b, scope.stream()));
+  else if (mode == 1) B200_KERNEL_CHECK(b200_rng_normal(dst.data_ptr(), dt, dst.numel(), so.first, so.second, a, b, scope.stream()));
+  else B200_KERNEL_CHECK(b200_rng_bernoulli(dst.data_ptr(), dt, dst.numel(), so.first, so.second, a, scope.stream()));
+  if (!dst.is_same(self)) self.copy_(dst);
+  return self;
+}
+Tensor& k_uniform_(Tensor& self, double from, double to, std::optional<at::Generator> gen) {
+  return rng_fill(self, gen, 0, from, to);
+}
+Tensor& k_normal_(Tensor& self, double mean, double std, std::optional<at::Generator> gen) {
+  return rng_fill(self, gen, 1, mean, std);
+}
+Tensor& k_bernoulli_float_(Tensor& self, double p, std::optional<at::Generator> gen) {
+  return rng_fill(self, gen, 2, p, 0);
+}
+std::tuple<Tensor, Tensor> k_native_dropout(const Tensor& input, double p, std::optional<bool> train) {
+  if (!train.value_or(true) || p == 0.0 || input.numel() == 0) {
+    return {input.clone(), at::ones_like(input, input.options().dtype(at::kBool))};
+  }
+  TORCH_CHECK(f_ok(input.scalar_type()), "b200 dropout: unsupported dtype ", input.scalar_type());
+  OpScope scope("native_dropout", input);
+  Tensor x = input.contiguous();
+  Tensor y = at::empty_like(x), mask = at::empty_like(x, x.options().dtype(at::kBool));
+  auto so = philox(std::nullopt, input, (uint64_t)x.numel());
+  B200_KERNEL_CHECK(b200_dropout_fwd(x.data_ptr(), to_b200_dtype(x.scalar_type()), x.numel(), so.first, so.second, (float)p,
+                                     y.data_ptr(), static_cast<unsigned char*>(mask.data_ptr()), scope.stream()));
+  return {y, mask};
+}
+Tensor k_native_dropout_backward(const Tensor& grad, const Tensor& mask, double scale) {
+  return grad * mask.to(grad.scalar_type()) * scale;
+}
+
+}  // namespace
+
+// ---- custom ops (namespace catch_b200) ------------------------------------------------------
+bool dump_tensor_device(const at::Tensor& t) {
+  if (!is_b200(t) || use_cpu_path()) {
+    std::cout << t << std::endl;
+    return true;
+  }
+  OpScope scope("dump", t);
+  at::Tensor x = t.contiguous();
+  if (x.scalar_type() != at::kFloat && x.scalar_type() != at::kHalf && x.scalar_type() != at::kBFloat16) x = x.to(at::kFloat);
+  B200_KERNEL_CHECK(b200_dump_device(x.data_ptr(), to_b200_dtype(x.scalar_type()), x.numel(), scope.stream()));
+  scope.queue().synchronize();
+  return true;
+}
+
+static void fill_opt_tensors(B200OptTensors& T, at::TensorList params, at::TensorList grads, at::TensorList s1,
+                             at::TensorList s2, at::TensorList lowp, size_t begin, size_t end) {
+  std::memset(&T, 0, sizeof(T));
+  T.count = (int)(end - begin);
+  for (size_t i = begin; i < end; ++i) {
+    const size_t k = i - begin;
+    TORCH_CHECK(params[i].scalar_type() == at::kFloat && params[i].is_contiguous(), "fused optimizer: parameters must be contiguous fp32");
+    TORCH_CHECK(grads[i].is_contiguous() && grads[i].numel() == params[i].numel(), "fused optimizer: gradient layout mismatch");
+    T.param[k] = params[i].data_ptr();
+    T.grad[k] = grads[i].data_ptr();
+    T.state1[k] = s1.empty() ? nullptr : s1[i].data_ptr();
+    T.state2[k] = s2.empty() ? nullptr : s2[i].data_ptr();
+    T.lowp[k] = lowp.empty() ? nullptr : lowp[i].data_ptr();
+    T.numel[k] = params[i].numel();
+  }
+  T.grad_dtype = to_b200_dtype(grads[begin].scalar_type());
+  T.lowp_dtype = lowp.empty() ? B200_BF16 : to_b200_dtype(lowp[begin].scalar_type());
+}
+
+void fused_sgd_step(at::TensorList params, at::TensorList grads, at::TensorList momentum_bufs, at::TensorList lowp,
+                    double lr, double momentum, double dampening, double weight_decay, bool nesterov, bool first_step,
+                    double grad_scale) {
+  if (params.empty()) return;
+  TORCH_CHECK(params.size() == grads.size(), "fused_sgd_step: list length mismatch");
+  if (use_cpu_path()) {
+    for (size_t i = 0; i < params.size(); ++i) {
+      at::Tensor p = params[i];
+      at::Tensor d = grads[i].to(at::kFloat) * grad_scale + p * weight_decay;
+      if (momentum != 0.0) {
+        at::Tensor buf = momentum_bufs[i];
+        if (first_step) buf.copy_(d); else buf.mul_(momentum).add_(d, 1.0 - dampening);
+        d = nesterov ? d + buf * momentum : buf;
+      }
+      p.sub_(d * lr);
+      if (!lowp.empty()) lowp[i].copy_(p);
+    }
+    return;
+  }
+  OpScope scope("fused_sgd_step", params[0]);
+  for (size_t b = 0; b < params.size(); b += B200_OPT_MAX_TENSORS) {
+    const size_t e = std::min(params.size(), b + (size_t)B200_OPT_MAX_TENSORS);
+    B200OptTensors T;
+    fill_opt_tensors(T, params, grads, momentum != 0.0 ? momentum_bufs : at::TensorList(), {}, lowp, b, e);
+    B200_KERNEL_CHECK(b200_sgd_step(&T, (float)lr, (float)momentum, (float)dampening, (float)weight_decay, nesterov,
+                                    first_step, (float)grad_scale, scope.stream()));
+  }
+}
+
+void fused_adamw_step(at::TensorList params, at::TensorList grads, at::TensorList exp_avg, at::TensorList exp_avg_sq,
+                      at::TensorList lowp, double lr, double beta1, double beta2, double eps, double weight_decay,
+                      int64_t step, double grad_scale, bool adam_l2_mode) {
+  if (params.empty()) return;
+  if (use_cpu_path()) {
+    const double bc1 = 1.0 - std::pow(beta1, (double)step), bc2 = std::sqrt(1.0 - std::pow(beta2, (double)step));
+    for (size_t i = 0; i < params.size(); ++i) {
+      at::Tensor p = params[i];
+      at::Tensor g = grads[i].to(at::kFloat) * grad_scale;
+      if (adam_l2_mode) g = g + p * weight_decay; else p.mul_(1.0 - lr * weight_decay);
+      exp_avg[i].mul_(beta1).add_(g, 1.0 - beta1);
+      exp_avg_sq[i].mul_(beta2).addcmul_(g, g, 1.0 - beta2);
+      at::Tensor denom = exp_avg_sq[i].sqrt() / bc2 + eps;
+      p.addcdiv_(exp_avg[i], denom, -lr / bc1);
+      if (!lowp.empty()) lowp[i].copy_(p);
+    }
+    return;
+  }
+  OpScope scope("fused_adamw_step", params[0]);
+  for (size_t b = 0; b < params.size(); b += B200_OPT_MAX_TENSORS) {
+    const size_t e = std::min(params.size(), b + (size_t)B200_OPT_MAX_TENSORS);
+    B200OptTensors T;
+    fill_opt_tensors(T, params, grads, exp_avg, exp_avg_sq, lowp, b, e);
+    B200_KERNEL_CHECK(b200_adamw_step(&T, (float)lr, (float)beta1, (float)beta2, (float)eps, (float)weight_decay, step,
+                                      (float)grad_scale, adam_l2_mode, scope.stream()));
+  }
+}
+
+TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+  if (!device_kernels_enabled()) return;
+  m.impl("embedding", TORCH_FN(k_embedding));
+  m.impl("embedding_dense_backward", TORCH_FN(k_embedding_dense_backward));
+  m.impl("index_select", TORCH_FN(k_index_select));
+  m.impl("uniform_", TORCH_FN(k_uniform_));
+  m.impl("normal_", TORCH_FN(k_normal_));
+  m.impl("bernoulli_.float", TORCH_FN(k_bernoulli_float_));
+  m.impl("native_dropout", TORCH_FN(k_native_dropout));
+  m.impl("native_dropout_backward", TORCH_FN(k_native_dropout_backward));
+}
+
+}  // namespace ops
+}  // namespace catch_b200

@@ -1,0 +1,304 @@
+// Batch normalisation and layer normalisation operators.
+//
+// Parity: torch_mlu/csrc/aten/operators/cnnl/native_batch_norm.cpp:77,
+// native_batch_norm_backward.cpp:85 (train / eval, 2-5-D inputs viewed as
+// channels-last 4-D).  LayerNorm is new (the reference has no device kernel).
+#include "common.h"
+#include "kernels.h"
+
+namespace catch_b200 {
+namespace ops {
+namespace {
+
+using at::Tensor;
+
+struct RowsView {
+  Tensor t;       // dense tensor whose memory is [rows, C]
+  int64_t rows, C;
+  bool channels_last_4d;
+};
+
+// Memory view [rows, C] of an [N, C, *] tensor (copying to channels-last if needed).
+RowsView rows_view(const Tensor& x) {
+  RowsView v;
+  v.C = x.size(1);
+  v.rows = v.C ? x.numel() / v.C : 0;
+  v.channels_last_4d = false;
+  if (x.dim() == 2) {
+    v.t = x.contiguous();
+  } else if (x.dim() == 4) {
+    v.t = x.contiguous(at::MemoryFormat::ChannelsLast);
+    v.channels_last_4d = true;
+  } else if (x.dim() == 5) {
+    v.t = x.contiguous(at::MemoryFormat::ChannelsLast3d);
+  } else {
+    // [N, C, L] -> treat as [N, C, L, 1]
+    v.t = x.unsqueeze(-1).contiguous(at::MemoryFormat::ChannelsLast).squeeze(-1);
+  }
+  return v;
+}
+
+Tensor like_rows(const RowsView& v, const Tensor& x, at::ScalarType dt) {
+  // allocate an output with the same memory layout as v.t
+  return at::empty_strided(v.t.sizes(), v.t.strides(), x.options().dtype(dt));
+}
+
+bool bn_dtype_ok(at::ScalarType t) { return t == at::kFloat || t == at::kBFloat16 || t == at::kHalf; }
+
+const void* opt_ptr(const std::optional<Tensor>& t, Tensor& keep) {
+  if (t.has_value() && t->defined()) {
+    keep = t->contiguous();
+    return keep.data_ptr();
+  }
+  return nullptr;
+}
+
+std::tuple<Tensor, Tensor, Tensor> batch_norm_device(const Tensor& input, const std::optional<Tensor>& weight,
+                                                     const std::optional<Tensor>& bias,
+                                                     const std::optional<Tensor>& running_mean,
+                                                     const std::optional<Tensor>& running_var, bool training,
+                                                     double momentum, double eps) {
+  TORCH_CHECK(input.dim() >= 2 && bn_dtype_ok(input.scalar_type()), "b200 batch_norm: unsupported input ", describe(input));
+  OpScope scope("native_batch_norm", input);
+  RowsView v = rows_view(input);
+  const int C = (int)v.C;
+  const int vec = input.scalar_type() == at::kFloat ? 4 : 8;
+  TORCH_CHECK(C % vec == 0, "b200 batch_norm: channels must be a multiple of ", vec);
+  Tensor out = like_rows(v, input, input.scalar_type());
+  auto fopt = input.options().dtype(at::kFloat);
+  Tensor wk, bk, rmk, rvk;
+  const void* gamma = opt_ptr(weight, wk);
+  const void* beta = opt_ptr(bias, bk);
+  int pdt = B200_F32;
+  if (gamma) pdt = to_b200_dtype(wk.scalar_type());
+  else if (beta) pdt = to_b200_dtype(bk.scalar_type());
+  if (gamma && beta) TORCH_CHECK(wk.scalar_type() == bk.scalar_type(), "batch_norm: weight and bias dtypes differ");
+  const int xdt = to_b200_dtype(input.scalar_type());
+  Tensor save_mean, save_invstd;
+  if (training) {
+    save_mean = at::empty({C}, fopt);
+    save_invstd = at::empty({C}, fopt);
+    if (input.numel() == 0) return {out, save_mean, save_invstd};
+    Tensor sums = at::zeros({2 * C}, input.options().dtype(at::kDouble));
+    B200_KERNEL_CHECK(b200_bn_stats(v.t.data_ptr(), xdt, v.rows, C, sums.data_ptr<double>(), scope.stream()));
+    void* rm = nullptr;
+    void* rv = nullptr;
+    int rdt = B200_F32;
+    if (running_mean.has_value() && running_mean->defined()) {
+      TORCH_CHECK(running_mean->is_contiguous() && running_var->is_contiguous(), "batch_norm: running stats must be contiguous");
+      rm = running_mean->data_ptr();
+      rv = running_var->data_ptr();
+      rdt = to_b200_dtype(running_mean->scalar_type());
+    }
+    B200_KERNEL_CHECK(b200_bn_finalize(sums.data_ptr<double>(), v.rows, C, (float)eps, (float)momentum,
+                                       save_mean.data_ptr<float>(), save_invstd.data_ptr<float>(), rm, rv, rdt,
+                                       scope.stream()));
+    B200_KERNEL_CHECK(b200_bn_apply(v.t.data_ptr(), xdt, out.data_ptr(), xdt, v.rows, C, save_mean.data_ptr(), B200_F32,
+                                    save_invstd.data_ptr<float>(), gamma, beta, pdt, nullptr, 0, 0, scope.stream()));
+  } else {
+    TORCH_CHECK(running_mean.has_value() && running_mean->defined() && running_var.has_value() && running_var->defined(),
+                "batch_norm: running statistics are required in evaluation mode");
+    save_mean = at::empty({0}, fopt);
+    save_invstd = at::empty({0}, fopt);
+    if (input.numel() == 0) return {out, save_mean, save_invstd};
+    Tensor invstd = at::empty({C}, fopt);
+    Tensor rm = running_mean->contiguous(), rv = running_var->contiguous();
+    B200_KERNEL_CHECK(b200_bn_invstd_from_var(rv.data_ptr(), to_b200_dtype(rv.scalar_type()), C, (float)eps,
+                                              invstd.data_ptr<float>(), scope.stream()));
+    B200_KERNEL_CHECK(b200_bn_apply(v.t.data_ptr(), xdt, out.data_ptr(), xdt, v.rows, C, rm.data_ptr(),
+                                    to_b200_dtype(rm.scalar_type()), invstd.data_ptr<float>(), gamma, beta, pdt, nullptr,
+                                    0, 0, scope.stream()));
+  }
+  return {out, save_mean, save_invstd};
+}
+
+std::tuple<Tensor, Tensor, Tensor> k_native_batch_norm(const Tensor& input, const std::optional<Tensor>& weight,
+                                                     const std::optional<Tensor>& bias,
+                                                     const std::optional<Tensor>& running_mean,
+                                                     const std::optional<Tensor>& running_var, bool training,
+                                                     double momentum, double eps) {
+  return B200_DISPATCH("native_batch_norm",
+                       batch_norm_device(input, weight, bias, running_mean, running_var, training, momentum, eps),
+                       B200_CPU(native_batch_norm, input, weight, bias, running_mean, running_var, training, momentum, eps));
+}
+
+std::tuple<Tensor, Tensor, Tensor> bn_legit(const Tensor& input, const std::optional<Tensor>& weight,
+                                            const std::optional<Tensor>& bias, Tensor& running_mean, Tensor& running_var,
+                                            bool training, double momentum, double eps) {
+  return k_native_batch_norm(input, weight, bias, running_mean, running_var, training, momentum, eps);
+}
+std::tuple<Tensor, Tensor, Tensor> bn_legit_no_stats(const Tensor& input, const std::optional<Tensor>& weight,
+                                                     const std::optional<Tensor>& bias, bool training, double momentum,
+                                                     double eps) {
+  return k_native_batch_norm(input, weight, bias, std::nullopt, std::nullopt, training, momentum, eps);
+}
+std::tuple<Tensor, Tensor, Tensor> bn_legit_no_training(const Tensor& input, const std::optional<Tensor>& weight,
+                                                        const std::optional<Tensor>& bias, const Tensor& running_mean,
+                                                        const Tensor& running_var, double momentum, double eps) {
+  return k_native_batch_norm(input, weight, bias, running_mean, running_var, false, momentum, eps);
+}
+
+std::tuple<Tensor, Tensor, Tensor> batch_norm_backward_device(
+    const Tensor& grad_out, const Tensor& input, const std::optional<Tensor>& weight,
+    const std::optional<Tensor>& running_mean, const std::optional<Tensor>& running_var,
+    const std::optional<Tensor>& save_mean, const std::optional<Tensor>& save_invstd, bool train, double eps,
+    std::array<bool, 3> mask) {
+  TORCH_CHECK(bn_dtype_ok(input.scalar_type()) && grad_out.scalar_type() == input.scalar_type(),
+              "b200 batch_norm_backward: unsupported dtypes");
+  OpScope scope("native_batch_norm_backward", input);
+  RowsView xv = rows_view(input);
+  const int C = (int)xv.C;
+  const int vec = input.scalar_type() == at::kFloat ? 4 : 8;
+  TORCH_CHECK(C % vec == 0, "b200 batch_norm_backward: channels must be a multiple of ", vec);
+  // grad in the same memory layout as x
+  Tensor dy = at::empty_strided(xv.t.sizes(), xv.t.strides(), grad_out.options());
+  if (grad_out.sizes() == xv.t.sizes() && grad_out.strides() == xv.t.strides()) dy = grad_out;
+  else dy.copy_(grad_out);
+  auto fopt = input.options().dtype(at::kFloat);
+  Tensor wk;
+  const void* gamma = opt_ptr(weight, wk);
+  const int pdt = gamma ? to_b200_dtype(wk.scalar_type()) : B200_F32;
+  const int xdt = to_b200_dtype(input.scalar_type());
+  Tensor mean_t, invstd_t;
+  int mdt = B200_F32;
+  if (train) {
+    TORCH_CHECK(save_mean.has_value() && save_mean->defined() && save_invstd.has_value() && save_invstd->defined(),
+                "batch_norm_backward: saved statistics missing");
+    mean_t = save_mean->contiguous();
+    invstd_t = save_invstd->to(at::kFloat).contiguous();
+    mdt = to_b200_dtype(mean_t.scalar_type());
+  } else {
+    mean_t = running_mean->contiguous();
+    mdt = to_b200_dtype(mean_t.scalar_type());
+    invstd_t = at::empty({C}, fopt);
+    Tensor rv = running_var->contiguous();
+    B200_KERNEL_CHECK(b200_bn_invstd_from_var(rv.data_ptr(), to_b200_dtype(rv.scalar_type()), C, (float)eps,
+                                              invstd_t.data_ptr<float>(), scope.stream()));
+  }
+  Tensor dx, dgamma, dbeta;
+  if (mask[0]) dx = at::empty_strided(xv.t.sizes(), xv.t.strides(), input.options());
+  if (mask[1]) dgamma = at::empty({C}, fopt);
+  if (mask[2]) dbeta = at::empty({C}, fopt);
+  if (input.numel() == 0) {
+    if (dgamma.defined()) dgamma.zero_();
+    if (dbeta.defined()) dbeta.zero_();
+    return {dx, dgamma, dbeta};
+  }
+  Tensor sums = at::zeros({2 * C}, input.options().dtype(at::kDouble));
+  B200_KERNEL_CHECK(b200_bn_backward_reduce(dy.data_ptr(), xdt, xv.t.data_ptr(), xdt, mean_t.data_ptr(), mdt,
+                                            invstd_t.data_ptr<float>(), nullptr, 0, xv.rows, C,
+                                            sums.data_ptr<double>(), scope.stream()));
+  B200_KERNEL_CHECK(b200_bn_backward_apply(dy.data_ptr(), xdt, xv.t.data_ptr(), xdt, mean_t.data_ptr(), mdt,
+                                           invstd_t.data_ptr<float>(), gamma, pdt, nullptr, 0, sums.data_ptr<double>(),
+                                           xv.rows, C, train ? 1 : 0, dx.defined() ? dx.data_ptr() : nullptr, xdt,
+                                           dgamma.defined() ? dgamma.data_ptr<float>() : nullptr,
+                                           dbeta.defined() ? dbeta.data_ptr<float>() : nullptr, scope.stream()));
+  if (weight.has_value() && weight->defined() && weight->scalar_type() != at::kFloat) {
+    if (dgamma.defined()) dgamma = dgamma.to(weight->scalar_type());
+    if (dbeta.defined()) dbeta = dbeta.to(weight->scalar_type());
+  }
+  return {dx, dgamma, dbeta};
+}
+
+std::tuple<Tensor, Tensor, Tensor> k_native_batch_norm_backward(
+    const Tensor& grad_out, const Tensor& input, const std::optional<Tensor>& weight,
+    const std::optional<Tensor>& running_mean, const std::optional<Tensor>& running_var,
+    const std::optional<Tensor>& save_mean, const std::optional<Tensor>& save_invstd, bool train, double eps,
+    std::array<bool, 3> mask) {
+  return B200_DISPATCH("native_batch_norm_backward",
+                       batch_norm_backward_device(grad_out, input, weight, running_mean, running_var, save_mean,
+                                                  save_invstd, train, eps, mask),
+                       B200_CPU(native_batch_norm_backward, grad_out, input, weight, running_mean, running_var,
+                                save_mean, save_invstd, train, eps, mask));
+}
+
+// ------------------------------------------------------------------- layer norm
+std::tuple<Tensor, Tensor, Tensor> layer_norm_device(const Tensor& input, at::IntArrayRef normalized_shape,
+                                                     const std::optional<Tensor>& weight,
+                                                     const std::optional<Tensor>& bias, double eps) {
+  TORCH_CHECK(bn_dtype_ok(input.scalar_type()), "b200 layer_norm: unsupported dtype ", input.scalar_type());
+  OpScope scope("native_layer_norm", input);
+  int64_t cols = 1;
+  for (auto s : normalized_shape) cols *= s;
+  const int64_t rows = cols ? input.numel() / cols : 0;
+  Tensor x = input.contiguous();
+  Tensor y = at::empty_like(x);
+  std::vector<int64_t> stat_shape(input.sizes().begin(), input.sizes().end() - normalized_shape.size());
+  for (size_t i = 0; i < normalized_shape.size(); ++i) stat_shape.push_back(1);
+  auto fopt = input.options().dtype(at::kFloat);
+  Tensor mean = at::empty(stat_shape, fopt), rstd = at::empty(stat_shape, fopt);
+  Tensor wk, bk;
+  const void* gamma = opt_ptr(weight, wk);
+  const void* beta = opt_ptr(bias, bk);
+  const int pdt = gamma ? to_b200_dtype(wk.scalar_type()) : (beta ? to_b200_dtype(bk.scalar_type()) : B200_F32);
+  B200_KERNEL_CHECK(b200_layernorm_fwd(x.data_ptr(), to_b200_dtype(x.scalar_type()), rows, (int)cols, gamma, beta, pdt,
+                                       (float)eps, y.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                                       scope.stream()));
+  if (input.scalar_type() != at::kFloat) {
+    // stock kernels return statistics in the input dtype
+    return {y, mean.to(input.scalar_type()), rstd.to(input.scalar_type())};
+  }
+  return {y, mean, rstd};
+}
+std::tuple<Tensor, Tensor, Tensor> k_native_layer_norm(const Tensor& input, at::IntArrayRef normalized_shape,
+                                                     const std::optional<Tensor>& weight,
+                                                     const std::optional<Tensor>& bias, double eps) {
+  return B200_DISPATCH("native_layer_norm", layer_norm_device(input, normalized_shape, weight, bias, eps),
+                       B200_CPU(native_layer_norm, input, normalized_shape, weight, bias, eps));
+}
+
+std::tuple<Tensor, Tensor, Tensor> layer_norm_backward_device(const Tensor& grad_out, const Tensor& input,
+                                                              at::IntArrayRef normalized_shape, const Tensor& mean,
+                                                              const Tensor& rstd, const std::optional<Tensor>& weight,
+                                                              const std::optional<Tensor>& bias,
+                                                              std::array<bool, 3> mask) {
+  TORCH_CHECK(bn_dtype_ok(input.scalar_type()) && grad_out.scalar_type() == input.scalar_type(),
+              "b200 layer_norm_backward: unsupported dtypes");
+  OpScope scope("native_layer_norm_backward", input);
+  int64_t cols = 1;
+  for (auto s : normalized_shape) cols *= s;
+  const int64_t rows = cols ? input.numel() / cols : 0;
+  Tensor x = input.contiguous(), dy = grad_out.contiguous();
+  Tensor m = mean.to(at::kFloat).contiguous(), r = rstd.to(at::kFloat).contiguous();
+  Tensor wk;
+  const void* gamma = opt_ptr(weight, wk);
+  const int pdt = gamma ? to_b200_dtype(wk.scalar_type()) : B200_F32;
+  Tensor dx, dg, db;
+  auto fopt = input.options().dtype(at::kFloat);
+  if (mask[0]) dx = at::empty_like(x);
+  if (mask[1]) dg = at::zeros({cols}, fopt);
+  if (mask[2]) db = at::zeros({cols}, fopt);
+  B200_KERNEL_CHECK(b200_layernorm_bwd(dy.data_ptr(), x.data_ptr(), to_b200_dtype(x.scalar_type()), rows, (int)cols,
+                                       gamma, pdt, m.data_ptr<float>(), r.data_ptr<float>(),
+                                       dx.defined() ? dx.data_ptr() : nullptr, dg.defined() ? dg.data_ptr<float>() : nullptr,
+                                       db.defined() ? db.data_ptr<float>() : nullptr, scope.stream()));
+  if (dg.defined() && weight.has_value() && weight->defined()) dg = dg.to(weight->scalar_type()).view(weight->sizes());
+  if (db.defined() && bias.has_value() && bias->defined()) db = db.to(bias->scalar_type()).view(bias->sizes());
+  else if (db.defined() && weight.has_value() && weight->defined()) db = db.to(weight->scalar_type()).view(weight->sizes());
+  return {dx, dg, db};
+}
+std::tuple<Tensor, Tensor, Tensor> k_native_layer_norm_backward(const Tensor& grad_out, const Tensor& input,
+                                                              at::IntArrayRef normalized_shape, const Tensor& mean,
+                                                              const Tensor& rstd, const std::optional<Tensor>& weight,
+                                                              const std::optional<Tensor>& bias,
+                                                              std::array<bool, 3> mask) {
+  return B200_DISPATCH("native_layer_norm_backward",
+                       layer_norm_backward_device(grad_out, input, normalized_shape, mean, rstd, weight, bias, mask),
+                       B200_CPU(native_layer_norm_backward, grad_out, input, normalized_shape, mean, rstd, weight, bias, mask));
+}
+
+}  // namespace
+
+TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+  if (!device_kernels_enabled()) return;
+  m.impl("native_batch_norm", TORCH_FN(k_native_batch_norm));
+  m.impl("_native_batch_norm_legit", TORCH_FN(bn_legit));
+  m.impl("_native_batch_norm_legit.no_stats", TORCH_FN(bn_legit_no_stats));
+  m.impl("_native_batch_norm_legit_no_training", TORCH_FN(bn_legit_no_training));
+  m.impl("native_batch_norm_backward", TORCH_FN(k_native_batch_norm_backward));
+  m.impl("native_layer_norm", TORCH_FN(k_native_layer_norm));
+  m.impl("native_layer_norm_backward", TORCH_FN(k_native_layer_norm_backward));
+}
+
+}  // namespace ops
+}  // namespace catch_b200

@@ -1,0 +1,205 @@
+"""Operator kernels on a real B200 against CPU references: batch norm, layer
+norm, pooling, softmax / losses, reductions, embedding, RNG, optimizers."""
+import copy
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from common import assert_tensors_equal
+
+pytestmark = pytest.mark.gpu
+DEV = "blackwell"
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _backend():
+    import catch_b200  # noqa: F401
+
+    assert torch.b200.backend_name() == "cuda"
+    torch.b200.set_flag("op_trycatch", False)
+    yield
+    torch.b200.set_flag("op_trycatch", True)
+
+
+def _fb(fn, x, *extra, prec=3e-3, dtype=torch.float32):
+    """forward + backward of fn on CPU (fp32) and on the device."""
+    xr = x.clone().requires_grad_()
+    xd = x.to(dtype).to(DEV).requires_grad_()
+    yr = fn(xr, *extra)
+    yd = fn(xd, *[e.to(DEV) if isinstance(e, torch.Tensor) else e for e in extra])
+    assert_tensors_equal(yd, yr, prec=prec, use_MSE=True, msg="fwd")
+    g = torch.randn_like(yr)
+    yr.backward(g)
+    yd.backward(g.to(dtype).to(DEV))
+    assert_tensors_equal(xd.grad, xr.grad, prec=prec, use_MSE=True, msg="bwd")
+
+
+@pytest.mark.parametrize("dtype,cl", [(torch.float32, False), (torch.float32, True), (torch.bfloat16, True)])
+@pytest.mark.parametrize("train", [True, False])
+def test_batch_norm(dtype, cl, train):
+    torch.manual_seed(0)
+    x = torch.randn(6, 32, 9, 7) * 2 + 1
+    bn = torch.nn.BatchNorm2d(32)
+    bn.weight.data.uniform_(0.5, 1.5); bn.bias.data.normal_()
+    bn.running_mean.normal_(); bn.running_var.uniform_(0.5, 2)
+    bd = copy.deepcopy(bn).to(DEV)
+    bn.train(train); bd.train(train)
+    xq = x.to(dtype).float()
+    xr = xq.clone().requires_grad_()
+    xd = xq.to(dtype).to(DEV)
+    if cl:
+        xd = xd.contiguous(memory_format=torch.channels_last)
+    xd.requires_grad_()
+    yr, yd = bn(xr), bd(xd)
+    prec = 2e-2 if dtype == torch.bfloat16 else 3e-3
+    assert_tensors_equal(yd, yr, prec=prec, use_MSE=True)
+    g = torch.randn_like(yr)
+    yr.backward(g); yd.backward(g.to(dtype).to(DEV))
+    assert_tensors_equal(xd.grad, xr.grad, prec=prec, use_MSE=True, msg="dx")
+    assert_tensors_equal(bd.weight.grad, bn.weight.grad, prec=prec, use_MSE=True, msg="dgamma")
+    assert_tensors_equal(bd.bias.grad, bn.bias.grad, prec=prec, use_MSE=True, msg="dbeta")
+    if train:
+        assert_tensors_equal(bd.running_mean, bn.running_mean, prec=prec, use_MSE=True)
+        assert_tensors_equal(bd.running_var, bn.running_var, prec=prec, use_MSE=True)
+
+
+def test_layer_norm():
+    torch.manual_seed(1)
+    x = torch.randn(4, 17, 768)
+    ln = torch.nn.LayerNorm(768)
+    ln.weight.data.uniform_(0.5, 1.5); ln.bias.data.normal_()
+    ld = copy.deepcopy(ln).to(DEV)
+    xr, xd = x.clone().requires_grad_(), x.to(DEV).requires_grad_()
+    yr, yd = ln(xr), ld(xd)
+    assert_tensors_equal(yd, yr, prec=3e-3, use_MSE=True)
+    g = torch.randn_like(yr)
+    yr.backward(g); yd.backward(g.to(DEV))
+    assert_tensors_equal(xd.grad, xr.grad, prec=3e-3, use_MSE=True)
+    assert_tensors_equal(ld.weight.grad, ln.weight.grad, prec=3e-3, use_MSE=True)
+    assert_tensors_equal(ld.bias.grad, ln.bias.grad, prec=3e-3, use_MSE=True)
+
+
+@pytest.mark.parametrize("cl", [False, True])
+def test_pooling(cl):
+    torch.manual_seed(2)
+    x = torch.randn(3, 16, 23, 19)
+    def prep(t):
+        return t.contiguous(memory_format=torch.channels_last) if cl else t
+    for fn in (lambda t: F.max_pool2d(prep(t), 3, 2, 1), lambda t: F.max_pool2d(prep(t), 2, 2, 0, ceil_mode=True),
+               lambda t: F.avg_pool2d(prep(t), 3, 2, 1), lambda t: F.avg_pool2d(prep(t), 2, 2, 0, ceil_mode=True, count_include_pad=False),
+               lambda t: F.adaptive_avg_pool2d(prep(t), (1, 1)), lambda t: F.adaptive_avg_pool2d(prep(t), (5, 4))):
+        _fb(fn, x)
+    y, idx = F.max_pool2d(x.to(DEV), 3, 2, 1, return_indices=True)
+    yr, idxr = F.max_pool2d(x, 3, 2, 1, return_indices=True)
+    assert torch.equal(idx.cpu(), idxr)
+
+
+def test_softmax_losses():
+    torch.manual_seed(3)
+    x = torch.randn(33, 1000)
+    t = torch.randint(0, 1000, (33,))
+    t[5] = -100
+    _fb(lambda a: F.softmax(a, -1), x)
+    _fb(lambda a: F.log_softmax(a, -1), x)
+    _fb(lambda a: F.softmax(a, 0), x[:, :7])
+    _fb(lambda a, tt: F.cross_entropy(a, tt), x, t)
+    _fb(lambda a, tt: F.cross_entropy(a, tt, reduction="sum"), x, t)
+    _fb(lambda a, tt: F.nll_loss(F.log_softmax(a, 1), tt, reduction="none"), x, t)
+    loss, dl = torch.ops.catch_b200.softmax_cross_entropy(x.to(DEV), t.to(DEV), -100, 0.1)
+    xr = x.clone().requires_grad_()
+    lr = F.cross_entropy(xr, t, label_smoothing=0.1)
+    lr.backward()
+    assert_tensors_equal(loss, lr, prec=1e-4)
+    assert_tensors_equal(dl, xr.grad, prec=3e-3, use_MSE=True)
+
+
+def test_reductions():
+    torch.manual_seed(4)
+    x = torch.randn(5, 6, 7, 8)
+    d = x.to(DEV)
+    for fn in (lambda t: t.sum(), lambda t: t.sum(1), lambda t: t.sum((0, 2)), lambda t: t.mean((2, 3), keepdim=True),
+               lambda t: t.amax(1), lambda t: t.amin((0, 3)), lambda t: t.max(), lambda t: t.min(), lambda t: t.norm(),
+               lambda t: t.norm(1, dim=(1,)), lambda t: t.transpose(1, 3).sum(2), lambda t: t.prod(3)):
+        assert_tensors_equal(fn(d), fn(x), prec=3e-3, use_MSE=True)
+    v, i = d.max(2)
+    vr, ir = x.max(2)
+    assert torch.equal(i.cpu(), ir) and torch.equal(v.cpu(), vr)
+    assert torch.equal(d.argmax(1).cpu(), x.argmax(1)) and d.argmax().item() == x.argmax().item()
+    big = torch.randn(3, 1 << 18)
+    assert_tensors_equal(big.to(DEV).sum(), big.sum(), prec=1e-3, use_MSE=True)
+    assert_tensors_equal(big.to(DEV).sum(1), big.sum(1), prec=1e-3, use_MSE=True)
+    assert (d > 100).any().item() is False and (d < 100).all().item() is True
+    assert_tensors_equal(d.bfloat16().sum((0, 1)), x.bfloat16().float().sum((0, 1)), prec=2e-2, use_MSE=True)
+
+
+def test_embedding_and_index_select():
+    torch.manual_seed(5)
+    emb = torch.nn.Embedding(100, 64)
+    ed = copy.deepcopy(emb).to(DEV)
+    idx = torch.randint(0, 100, (4, 9))
+    yr, yd = emb(idx), ed(idx.to(DEV))
+    assert torch.equal(yd.cpu(), yr)
+    g = torch.randn_like(yr)
+    yr.backward(g); yd.backward(g.to(DEV))
+    assert_tensors_equal(ed.weight.grad, emb.weight.grad, prec=1e-5)
+    x = torch.randn(7, 5, 3)
+    sel = torch.tensor([4, 0, 2])
+    assert torch.equal(x.to(DEV).index_select(1, sel.to(DEV)).cpu(), x.index_select(1, sel))
+
+
+def test_rng_and_dropout():
+    torch.b200.manual_seed(123)
+    a = torch.randn(100000, device=DEV)
+    torch.b200.manual_seed(123)
+    b = torch.randn(100000, device=DEV)
+    assert torch.equal(a.cpu(), b.cpu())
+    assert abs(a.mean().item()) < 0.02 and abs(a.std().item() - 1) < 0.02
+    u = torch.rand(100000, device=DEV)
+    assert 0.49 < u.mean().item() < 0.51 and u.min().item() >= 0 and u.max().item() < 1
+    x = torch.ones(200000, device=DEV)
+    y = F.dropout(x, 0.3, training=True)
+    keep = (y != 0).float().mean().item()
+    assert abs(keep - 0.7) < 0.01 and abs(y.max().item() - 1 / 0.7) < 1e-3
+
+
+def test_fused_optimizers_on_device():
+    from catch_b200.optim import FusedAdamW, FusedSGD
+
+    for make_f, make_r in ((lambda p: FusedSGD(p, lr=0.1, momentum=0.9, weight_decay=1e-4), lambda p: torch.optim.SGD(p, lr=0.1, momentum=0.9, weight_decay=1e-4)),
+                           (lambda p: FusedAdamW(p, lr=1e-2), lambda p: torch.optim.AdamW(p, lr=1e-2))):
+        torch.manual_seed(6)
+        shapes = [(64, 128), (128,), (5000, 3), (1,), (70000,)]
+        ref = [torch.nn.Parameter(torch.randn(*s)) for s in shapes]
+        dev = [torch.nn.Parameter(p.detach().clone().to(DEV)) for p in ref]
+        o_r, o_d = make_r(ref), make_f(dev)
+        for _ in range(3):
+            for a, b in zip(ref, dev):
+                g = torch.randn_like(a)
+                a.grad = g
+                b.grad = g.to(DEV)
+            o_r.step(); o_d.step()
+        for a, b in zip(ref, dev):
+            assert_tensors_equal(b, a, prec=1e-5, use_MSE=True)
+
+
+def test_resnet18_train_step_matches_cpu():
+    import torchvision
+
+    torch.manual_seed(7)
+    ref = torchvision.models.resnet18(num_classes=16)
+    dev = copy.deepcopy(ref).to(DEV)
+    x = torch.randn(8, 3, 64, 64)
+    t = torch.randint(0, 16, (8,))
+    lr_, ld_ = F.cross_entropy(ref(x), t), F.cross_entropy(dev(x.to(DEV)), t.to(DEV))
+    assert_tensors_equal(ld_, lr_, prec=5e-3)
+    lr_.backward(); ld_.backward()
+    # fp32 convolutions run on fp16 tensor cores: activations near zero can fall on the
+    # other side of a ReLU than on the CPU, so gradients are compared by direction.
+    bad = {}
+    for (n, a), (_, b) in zip(ref.named_parameters(), dev.named_parameters()):
+        ga, gb = a.grad.double().flatten(), b.grad.cpu().double().flatten()
+        cos = (ga @ gb / (ga.norm() * gb.norm() + 1e-30)).item()
+        if cos < 0.98:
+            bad[n] = round(cos, 4)
+    assert not bad, f"gradient direction mismatches: {bad}"
