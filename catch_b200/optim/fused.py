@@ -15,6 +15,14 @@ import torch
 from torch.optim import Optimizer
 
 
+def _grad_like(p: torch.Tensor) -> torch.Tensor:
+    """The gradient of ``p`` laid out in memory exactly like ``p`` (the kernels are element-wise)."""
+    g = p.grad
+    if g.stride() == p.stride():
+        return g
+    return torch.empty_like(p, dtype=g.dtype).copy_(g)
+
+
 def _group_by_device_dtype(params, grads, *states):
     buckets = {}
     for i, (p, g) in enumerate(zip(params, grads)):
@@ -47,10 +55,10 @@ class FusedSGD(Optimizer):
             for p in group["params"]:
                 if p.grad is None:
                     continue
-                g = p.grad if p.grad.is_contiguous() else p.grad.contiguous()
+                g = _grad_like(p)
                 st = self.state[p]
                 if group["momentum"] != 0 and "momentum_buffer" not in st:
-                    st["momentum_buffer"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+                    st["momentum_buffer"] = torch.zeros_like(p)
                     fresh.append(p); fresh_g.append(g); fresh_b.append(st["momentum_buffer"])
                 else:
                     seen.append(p); seen_g.append(g)
@@ -93,13 +101,13 @@ class FusedAdamW(Optimizer):
                 st = self.state[p]
                 if "step" not in st:
                     st["step"] = torch.tensor(0.0)
-                    st["exp_avg"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
-                    st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+                    st["exp_avg"] = torch.zeros_like(p)
+                    st["exp_avg_sq"] = torch.zeros_like(p)
                 st["step"] += 1
                 by_step.setdefault(int(st["step"].item()), []).append(p)
             b1, b2 = group["betas"]
             for step, ps in by_step.items():
-                gs = [p.grad if p.grad.is_contiguous() else p.grad.contiguous() for p in ps]
+                gs = [_grad_like(p) for p in ps]
                 m1 = [self.state[p]["exp_avg"] for p in ps]
                 m2 = [self.state[p]["exp_avg_sq"] for p in ps]
                 for p_, g_, a_, v_ in _group_by_device_dtype(ps, gs, m1, m2):

@@ -28,6 +28,14 @@ import torch.distributed as dist
 from ..distributed import get_backend
 
 
+def _view_like(flat: torch.Tensor, p: torch.Tensor) -> torch.Tensor:
+    """A view of the flat slice with p's shape that keeps a channels-last layout."""
+    if p.dim() == 4 and p.is_contiguous(memory_format=torch.channels_last) and not p.is_contiguous():
+        n, c, h, w = p.shape
+        return flat.view(n, h, w, c).permute(0, 3, 1, 2)
+    return flat.view(p.shape)
+
+
 class _Bucket:
     def __init__(self, params: List[torch.nn.Parameter]):
         self.params = params
@@ -68,6 +76,7 @@ class FusedDataParallel(torch.nn.Module):
         self.kind = {"sgd": 0, "adamw": 1}[optimizer.lower()]
         self.lr, self.momentum, self.dampening, self.weight_decay = lr, momentum, dampening, weight_decay
         self.nesterov, self.betas, self.eps = nesterov, betas, eps
+        assert grad_dtype == torch.float32, "gradient buckets are fp32 (autograd accumulates into them in place)"
         self.grad_dtype = grad_dtype
         self.step_count = 0
         self.group = process_group or (dist.group.WORLD if dist.is_initialized() else None)
@@ -115,10 +124,10 @@ class FusedDataParallel(torch.nn.Module):
         b.grad_views = []
         for p in b.params:
             n = p.numel()
-            view = b.flat[off:off + n].view(p.shape)
+            view = _view_like(b.flat[off:off + n], p.data)
             view.copy_(p.data)
+            b.grad_views.append(_view_like(b.grads[off:off + n], p.data))
             p.data = view
-            b.grad_views.append(b.grads[off:off + n].view(p.shape))
             self._param_bucket[p] = b
             off += n
         if self.pg is not None:

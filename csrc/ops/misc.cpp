@@ -138,8 +138,14 @@ static void fill_opt_tensors(B200OptTensors& T, at::TensorList params, at::Tenso
   T.count = (int)(end - begin);
   for (size_t i = begin; i < end; ++i) {
     const size_t k = i - begin;
-    TORCH_CHECK(params[i].scalar_type() == at::kFloat && params[i].is_contiguous(), "fused optimizer: parameters must be contiguous fp32");
-    TORCH_CHECK(grads[i].is_contiguous() && grads[i].numel() == params[i].numel(), "fused optimizer: gradient layout mismatch");
+    // the update is element-wise, so any dense layout works as long as parameter,
+    // gradient and state share it
+    TORCH_CHECK(params[i].scalar_type() == at::kFloat && params[i].is_non_overlapping_and_dense(),
+                "fused optimizer: parameters must be dense fp32 tensors");
+    TORCH_CHECK(grads[i].strides() == params[i].strides() && grads[i].sizes() == params[i].sizes(),
+                "fused optimizer: gradient layout differs from the parameter's");
+    TORCH_CHECK(s1.empty() || s1[i].strides() == params[i].strides(), "fused optimizer: state layout differs from the parameter's");
+    TORCH_CHECK(s2.empty() || s2[i].strides() == params[i].strides(), "fused optimizer: state layout differs from the parameter's");
     T.param[k] = params[i].data_ptr();
     T.grad[k] = grads[i].data_ptr();
     T.state1[k] = s1.empty() ? nullptr : s1[i].data_ptr();

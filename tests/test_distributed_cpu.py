@@ -1,0 +1,114 @@
+"""The bwccl process group on the host-simulated device: collectives, point to
+point, DDP end to end against a single-process CPU run, and failure detection
+(a rank that never joins -> time-out error on the others).  No GPU needed."""
+import datetime
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from dist_utils import run_ranks
+
+DEV = "blackwell"
+
+
+def _init(rank, world, timeout_s=60):
+    import catch_b200  # noqa: F401
+
+    torch.b200.set_device(rank % torch.b200.device_count())
+    dist.init_process_group("bwccl", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=timeout_s))
+
+
+def _collectives(rank, world):
+    _init(rank, world)
+    for dtype in (torch.float32, torch.float64, torch.int64, torch.int32, torch.uint8, torch.bool, torch.bfloat16):
+        t = (torch.arange(6) % 2 == 0).to(dtype).to(DEV) if dtype == torch.bool else (torch.arange(6) + rank).to(dtype).to(DEV)
+        dist.broadcast(t, 0)
+        exp = (torch.arange(6) % 2 == 0).to(dtype) if dtype == torch.bool else torch.arange(6).to(dtype)
+        assert torch.equal(t.cpu(), exp), dtype
+        outs = [torch.empty_like(t) for _ in range(world)]
+        mine = torch.full((6,), rank + 1).to(dtype).to(DEV)
+        dist.all_gather(outs, mine)
+        for r in range(world):
+            assert torch.equal(outs[r].cpu(), torch.full((6,), r + 1).to(dtype)), dtype
+    x = torch.full((5, 3), float(rank + 1), device=DEV)
+    w = dist.all_reduce(x, async_op=True)
+    w.wait()
+    assert w.is_completed()
+    assert torch.equal(x.cpu(), torch.full((5, 3), float(sum(range(1, world + 1)))))
+    for op, exp in ((dist.ReduceOp.PRODUCT, 2.0), (dist.ReduceOp.MIN, 1.0), (dist.ReduceOp.MAX, 2.0)):
+        y = torch.full((4,), float(rank + 1), device=DEV)
+        dist.all_reduce(y, op=op)
+        assert torch.equal(y.cpu(), torch.full((4,), exp)), op
+    z = torch.full((4,), float(rank + 1), device=DEV)
+    dist.reduce(z, 1)
+    if rank == 1:
+        assert torch.equal(z.cpu(), torch.full((4,), 3.0))
+    big = torch.empty(world * 4, device=DEV)
+    dist.all_gather_into_tensor(big, torch.full((4,), float(rank), device=DEV))
+    assert torch.equal(big.cpu(), torch.arange(world).repeat_interleave(4).float())
+    rs = torch.empty(3, device=DEV)
+    dist.reduce_scatter_tensor(rs, torch.arange(world * 3, dtype=torch.float32, device=DEV))
+    assert torch.equal(rs.cpu(), world * torch.arange(rank * 3, rank * 3 + 3).float())
+    if rank == 0:
+        dist.send(torch.tensor([7.0, 8.0], device=DEV), 1)
+    else:
+        r = torch.zeros(2, device=DEV)
+        dist.recv(r, 0)
+        assert torch.equal(r.cpu(), torch.tensor([7.0, 8.0]))
+    dist.barrier()
+    with pytest.raises(Exception, match="destination rank|self"):
+        dist.send(torch.zeros(1, device=DEV), rank)
+    dist.destroy_process_group()
+
+
+def test_collectives_two_ranks():
+    run_ranks(_collectives, world=2)
+
+
+def _ddp(rank, world):
+    _init(rank, world)
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(10, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4))
+    ref = torch.nn.Sequential(torch.nn.Linear(10, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4))
+    ref.load_state_dict(net.state_dict())
+    ddp = torch.nn.parallel.DistributedDataParallel(net.to(DEV))
+    opt = torch.optim.SGD(ddp.parameters(), lr=0.05, momentum=0.9)
+    opt_ref = torch.optim.SGD(ref.parameters(), lr=0.05, momentum=0.9)
+    g = torch.Generator().manual_seed(1)
+    for _ in range(5):
+        x = torch.randn(8 * world, 10, generator=g)
+        y = torch.randn(8 * world, 4, generator=g)
+        opt_ref.zero_grad()
+        torch.nn.functional.mse_loss(ref(x), y).backward()
+        opt_ref.step()
+        xs, ys = x[rank * 8:(rank + 1) * 8].to(DEV), y[rank * 8:(rank + 1) * 8].to(DEV)
+        opt.zero_grad()
+        torch.nn.functional.mse_loss(ddp(xs), ys).backward()
+        opt.step()
+    for a, b in zip(ref.parameters(), ddp.module.parameters()):
+        assert (a - b.cpu()).abs().max().item() < 3e-3
+    dist.destroy_process_group()
+
+
+def test_ddp_matches_single_process_cpu():
+    run_ranks(_ddp, world=2)
+
+
+def _missing_peer(rank, world):
+    _init(rank, world, timeout_s=3)
+    t = torch.ones(4, device=DEV)
+    dist.all_reduce(t)  # both ranks take part once
+    if rank == 1:
+        os._exit(0)  # leaves between steps, nothing in flight
+    try:
+        dist.all_reduce(t)
+    except Exception as e:  # the surviving rank must get an error, not hang
+        assert "imeout" in str(e) or "timed out" in str(e) or "wait" in str(e).lower(), str(e)
+        os._exit(0)
+    os._exit(3)
+
+
+def test_rank_that_leaves_is_detected():
+    run_ranks(_missing_peer, world=2, timeout=60)

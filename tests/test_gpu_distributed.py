@@ -1,0 +1,177 @@
+"""bwccl on real GPUs (needs >= 2 B200s): collectives over peer-mapped memory,
+stock DDP, the fused all-reduce + optimizer path, and the bounded device-side
+wait (a rank withholds its signal; peers report a time-out and stay usable)."""
+import datetime
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from dist_utils import run_ranks
+
+pytestmark = pytest.mark.gpu
+DEV = "blackwell"
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+needs2 = pytest.mark.skipif(_ngpu() < 2, reason="needs two GPUs")
+ENV = {"NCCL_NVLS_ENABLE": "0"}
+
+
+def _init(rank, world):
+    import catch_b200  # noqa: F401
+
+    assert torch.b200.backend_name() == "cuda"
+    torch.b200.set_device(rank)
+    dist.init_process_group("bwccl", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+
+
+def _collectives(rank, world):
+    _init(rank, world)
+    for dtype in (torch.float32, torch.bfloat16, torch.int64, torch.uint8):
+        t = (torch.arange(1000) % 100 + rank).to(dtype).to(DEV)
+        dist.broadcast(t, 0)
+        assert torch.equal(t.cpu(), (torch.arange(1000) % 100).to(dtype)), dtype
+        outs = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(outs, torch.full((1000,), rank + 1).to(dtype).to(DEV))
+        for r in range(world):
+            assert torch.equal(outs[r].cpu(), torch.full((1000,), r + 1).to(dtype))
+    for n in (1, 7, 4096, 1 << 20, (1 << 24) + 3):
+        x = torch.full((n,), float(rank + 1), device=DEV)
+        dist.all_reduce(x)
+        assert torch.equal(x.cpu(), torch.full((n,), float(sum(range(1, world + 1))))), n
+    torch.manual_seed(5)
+    xb = torch.randn(100000).bfloat16()
+    dxb = (xb * (rank + 1)).to(DEV)
+    dist.all_reduce(dxb)
+    ref = sum((xb * (r + 1)).float() for r in range(world))
+    assert (dxb.float().cpu() - ref).abs().max() <= 0.02 * ref.abs().max()
+    y = torch.full((33,), float(rank + 1), device=DEV)
+    dist.all_reduce(y, op=dist.ReduceOp.MAX)
+    assert torch.equal(y.cpu(), torch.full((33,), float(world)))
+    z = torch.full((4,), float(rank + 1), device=DEV)
+    dist.reduce(z, 0)
+    if rank == 0:
+        assert torch.equal(z.cpu(), torch.full((4,), float(sum(range(1, world + 1)))))
+    rs = torch.empty(3, device=DEV)
+    dist.reduce_scatter_tensor(rs, torch.arange(world * 3, dtype=torch.float32, device=DEV))
+    assert torch.equal(rs.cpu(), world * torch.arange(rank * 3, rank * 3 + 3).float())
+    if rank == 0:
+        dist.send(torch.arange(5000, dtype=torch.float32, device=DEV), 1)
+    elif rank == 1:
+        r = torch.zeros(5000, device=DEV)
+        dist.recv(r, 0)
+        assert torch.equal(r.cpu(), torch.arange(5000, dtype=torch.float32))
+    dist.barrier()
+    torch.b200.synchronize()
+    dist.destroy_process_group()
+
+
+@needs2
+def test_collectives():
+    run_ranks(_collectives, world=2, env=ENV, timeout=240)
+
+
+def _ddp(rank, world):
+    _init(rank, world)
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.ReLU(), torch.nn.Linear(128, 8))
+    ref = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.ReLU(), torch.nn.Linear(128, 8))
+    ref.load_state_dict(net.state_dict())
+    ddp = torch.nn.parallel.DistributedDataParallel(net.to(DEV))
+    opt = torch.optim.SGD(ddp.parameters(), lr=0.05, momentum=0.9)
+    opt_ref = torch.optim.SGD(ref.parameters(), lr=0.05, momentum=0.9)
+    g = torch.Generator().manual_seed(1)
+    for _ in range(5):
+        x = torch.randn(16 * world, 64, generator=g)
+        y = torch.randn(16 * world, 8, generator=g)
+        opt_ref.zero_grad()
+        torch.nn.functional.mse_loss(ref(x), y).backward()
+        opt_ref.step()
+        opt.zero_grad()
+        torch.nn.functional.mse_loss(ddp(x[rank * 16:(rank + 1) * 16].to(DEV)), y[rank * 16:(rank + 1) * 16].to(DEV)).backward()
+        opt.step()
+    for a, b in zip(ref.parameters(), ddp.module.parameters()):
+        assert (a - b.cpu()).abs().max().item() < 3e-3
+    dist.destroy_process_group()
+
+
+@needs2
+def test_stock_ddp_matches_cpu():
+    run_ranks(_ddp, world=2, env=ENV, timeout=240)
+
+
+def _fused(rank, world, kind):
+    from catch_b200.parallel import FusedDataParallel
+
+    _init(rank, world)
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(64, 256), torch.nn.Tanh(), torch.nn.Linear(256, 8))
+    ref = torch.nn.Sequential(torch.nn.Linear(64, 256), torch.nn.Tanh(), torch.nn.Linear(256, 8))
+    ref.load_state_dict(net.state_dict())
+    if kind == "sgd":
+        fdp = FusedDataParallel(net.to(DEV), "sgd", lr=0.05, momentum=0.9, weight_decay=1e-4, bucket_mb=0.005)
+        opt_ref = torch.optim.SGD(ref.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-4)
+    else:
+        fdp = FusedDataParallel(net.to(DEV), "adamw", lr=1e-3, weight_decay=0.01, bucket_mb=0.005)
+        opt_ref = torch.optim.AdamW(ref.parameters(), lr=1e-3, weight_decay=0.01)
+    assert len(fdp.buckets) > 1
+    g = torch.Generator().manual_seed(1)
+    for _ in range(5):
+        x = torch.randn(16 * world, 64, generator=g)
+        y = torch.randn(16 * world, 8, generator=g)
+        opt_ref.zero_grad()
+        torch.nn.functional.mse_loss(ref(x), y).backward()
+        opt_ref.step()
+        torch.nn.functional.mse_loss(fdp(x[rank * 16:(rank + 1) * 16].to(DEV)), y[rank * 16:(rank + 1) * 16].to(DEV)).backward()
+        fdp.step()
+    torch.b200.synchronize()
+    for a, b in zip(ref.parameters(), fdp.module.parameters()):
+        assert (a - b.cpu()).abs().max().item() < 3e-3, (a - b.cpu()).abs().max().item()
+    # every rank holds bit-identical parameters
+    flat = torch.cat([p.detach().reshape(-1) for p in fdp.module.parameters()])
+    outs = [torch.empty_like(flat) for _ in range(world)]
+    dist.all_gather(outs, flat)
+    assert all(torch.equal(outs[0].cpu(), o.cpu()) for o in outs)
+    dist.destroy_process_group()
+
+
+@needs2
+@pytest.mark.parametrize("kind", ["sgd", "adamw"])
+def test_fused_allreduce_optimizer(kind):
+    run_ranks(_fused, world=2, args=(kind,), env=ENV, timeout=240)
+
+
+def _bounded_wait(rank, world):
+    from catch_b200.distributed import get_backend
+
+    _init(rank, world)
+    pg = get_backend()
+    t = pg.symm_empty(1024, torch.float32)
+    t.fill_(1.0)
+    dist.barrier()
+    pg.allreduce_symm(t).wait()
+    torch.b200.synchronize()
+    assert torch.equal(t.cpu(), torch.full((1024,), float(world)))
+    pg.set_wait_limit_ms(500)
+    # rank 0 withholds its "ready" signal: every device-side wait on it must run out
+    pg.allreduce_symm(t, 0, 1.0, rank == 0)
+    torch.b200.synchronize()
+    assert pg.status_word() & 0xFF == 1, pg.status_word()
+    pg.clear_status()
+    dist.barrier()  # the context and the communicator are still usable
+    t.fill_(2.0)
+    dist.barrier()
+    pg.allreduce_symm(t).wait()
+    torch.b200.synchronize()
+    assert torch.equal(t.cpu(), torch.full((1024,), 2.0 * world))
+    dist.destroy_process_group()
+
+
+@needs2
+def test_device_wait_is_bounded():
+    run_ranks(_bounded_wait, world=2, env=ENV, timeout=240)
