@@ -459,3 +459,48 @@ extern "C" int b200_layernorm_bwd(const void* dy, const void* x, int dt, long lo
   });
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------
+// Allocation-free batch statistics (declared in noalloc_api.h; no counterpart in the
+// reference).  Same kernels as b200_bn_stats + b200_bn_finalize, but the fp64 scratch
+// lives in a file-scope device array, so callers that may not allocate device memory
+// can still use them.  In host code the array's name is only a handle for the runtime:
+// the device address is fetched with cudaGetSymbolAddress, once per device.
+#include "noalloc_api.h"
+
+static __device__ __align__(256) double g_bn_noalloc_scratch[2 * B200_NOALLOC_BN_MAX_CHANNELS];
+
+static int bn_noalloc_scratch_ptr(double** out) {
+  static double* ptrs[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_bn_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    ptrs[dev] = static_cast<double*>(p);
+  }
+  *out = ptrs[dev];
+  return 0;
+}
+
+extern "C" int b200_bn_batch_stats_noalloc(const void* x, int x_dtype, long long rows, int C, float eps, float* mean,
+                                           float* invstd, void* stream) {
+  if (C <= 0 || rows <= 0) return (int)cudaErrorInvalidValue;
+  if (C > B200_NOALLOC_BN_MAX_CHANNELS) return (int)cudaErrorInvalidValue;  // beyond the built-in scratch
+  const int vec = x_dtype == B200_F32 ? 4 : 8;
+  if (x_dtype != B200_F32 && x_dtype != B200_BF16 && x_dtype != B200_F16) return (int)cudaErrorInvalidValue;
+  if (C % vec) return (int)cudaErrorInvalidValue;
+  double* scratch = nullptr;
+  int rc = bn_noalloc_scratch_ptr(&scratch);
+  if (rc) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  // the sums must start at zero; the array still holds the previous call's values
+  cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(double) * 2 * (size_t)C, s);
+  if (e != cudaSuccess) return (int)e;
+  rc = b200_bn_stats(x, x_dtype, rows, C, scratch, stream);
+  if (rc) return rc;
+  return b200_bn_finalize(scratch, rows, C, eps, 0.f, mean, invstd, nullptr, nullptr, B200_F32, stream);
+}
