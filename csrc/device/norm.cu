@@ -65,8 +65,8 @@ __device__ __forceinline__ void store_vec(T* p, const float* f) {
 constexpr int RED_THREADS = 256;
 
 // Generic two-quantity column reduction.  F(row, c_vec_start, out_a[V], out_b[V]).
-template <typename T, int NQ, typename F>
-__device__ void column_reduce(long long rows, int C, double* sums, F f) {
+template <typename T, int NQ, typename F, typename P, typename M>
+__device__ void column_reduce(long long rows, int C, double* sums, F f, P prep, M fin) {
   constexpr int V = VecOf<T>::N;
   const int cvecs = C / V;                   // C % V == 0 guaranteed by the launcher
   const int tx_n = cvecs < RED_THREADS ? cvecs : RED_THREADS;
@@ -82,8 +82,10 @@ __device__ void column_reduce(long long rows, int C, double* sums, F f) {
     for (int q = 0; q < NQ; ++q)
 #pragma unroll
       for (int i = 0; i < V; ++i) acc[q][i] = 0.f;
+    float ctx[V];
+    prep(cv * V, ctx);  // per-column constants, loaded once instead of once per row
     if (ty < ty_n) {
-      for (long long r = r0 + ty; r < r1; r += ty_n) f(r, cv * V, acc);
+      for (long long r = r0 + ty; r < r1; r += ty_n) f(r, cv * V, acc, ctx);
     }
     // fold the ty_n partials
     float* mine = sh + ((size_t)ty * tx_n + tx) * V * NQ;
@@ -101,7 +103,7 @@ __device__ void column_reduce(long long rows, int C, double* sums, F f) {
         for (int i = 0; i < V; ++i) {
           double s = 0.0;
           for (int y = 0; y < ty_n; ++y) s += sh[((size_t)y * tx_n + tx) * V * NQ + q * V + i];
-          atomicAdd(&sums[(size_t)q * C + cv * V + i], s);
+          atomicAdd(&sums[(size_t)q * C + cv * V + i], s * (double)fin(q, cv * V + i));
         }
     }
     __syncthreads();
@@ -111,12 +113,15 @@ __device__ void column_reduce(long long rows, int C, double* sums, F f) {
 template <typename T>
 __global__ void __launch_bounds__(RED_THREADS) bn_stats_kernel(const T* x, long long rows, int C, double* sums) {
   constexpr int V = VecOf<T>::N;
-  column_reduce<T, 2>(rows, C, sums, [&](long long r, int c0, float (*acc)[V]) {
-    float v[V];
-    load_vec<T>(x + r * C + c0, v);
+  column_reduce<T, 2>(
+      rows, C, sums,
+      [&](long long r, int c0, float (*acc)[V], const float*) {
+        float v[V];
+        load_vec<T>(x + r * C + c0, v);
 #pragma unroll
-    for (int i = 0; i < V; ++i) { acc[0][i] += v[i]; acc[1][i] += v[i] * v[i]; }
-  });
+        for (int i = 0; i < V; ++i) { acc[0][i] += v[i]; acc[1][i] += v[i] * v[i]; }
+      },
+      [](int, float*) {}, [](int, int) { return 1.f; });
 }
 
 __global__ void bn_finalize_kernel(const double* sums, long long rows, int C, float eps, float momentum, float* mean,
@@ -188,20 +193,27 @@ __global__ void __launch_bounds__(RED_THREADS)
 bn_bwd_reduce_kernel(const T* dy, const T* x, const void* mean, int mdt, const float* invstd, const T* relu_out,
                      long long rows, int C, double* sums) {
   constexpr int V = VecOf<T>::N;
-  column_reduce<T, 2>(rows, C, sums, [&](long long r, int c0, float (*acc)[V]) {
-    float g[V], v[V], o[V];
-    load_vec<T>(dy + r * C + c0, g);
-    load_vec<T>(x + r * C + c0, v);
-    if (relu_out) load_vec<T>(relu_out + r * C + c0, o);
+  // accumulates sum(dy) and sum(dy * (x - mean)); the second is scaled by invstd when folded
+  column_reduce<T, 2>(
+      rows, C, sums,
+      [&](long long r, int c0, float (*acc)[V], const float* mu) {
+        float g[V], v[V], o[V];
+        load_vec<T>(dy + r * C + c0, g);
+        load_vec<T>(x + r * C + c0, v);
+        if (relu_out) load_vec<T>(relu_out + r * C + c0, o);
 #pragma unroll
-    for (int i = 0; i < V; ++i) {
-      float gi = g[i];
-      if (relu_out && !(o[i] > 0.f)) gi = 0.f;
-      const float xh = (v[i] - ldf(mean, c0 + i, mdt)) * invstd[c0 + i];
-      acc[0][i] += gi;
-      acc[1][i] += gi * xh;
-    }
-  });
+        for (int i = 0; i < V; ++i) {
+          float gi = g[i];
+          if (relu_out && !(o[i] > 0.f)) gi = 0.f;
+          acc[0][i] += gi;
+          acc[1][i] += gi * (v[i] - mu[i]);
+        }
+      },
+      [&](int c0, float* mu) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) mu[i] = ldf(mean, c0 + i, mdt);
+      },
+      [&](int q, int c) { return q == 1 ? invstd[c] : 1.f; });
 }
 
 template <typename T, typename TO>
@@ -231,6 +243,90 @@ __global__ void bn_param_grads_kernel(const double* sums, int C, float* dgamma, 
   if (c >= C) return;
   if (dbeta) dbeta[c] = (float)sums[c];
   if (dgamma) dgamma[c] = (float)sums[C + c];
+}
+
+
+// ---- fast paths: per-channel coefficients precomputed into shared memory ------------
+// y = act(x * S[c] + T[c] + residual) with S = invstd * gamma, T = beta - mean * S
+template <typename T>
+__global__ void __launch_bounds__(256)
+bn_apply_fast_kernel(const T* __restrict__ x, T* __restrict__ y, unsigned nvec, int C, const void* mean, int mdt,
+                     const float* invstd, const void* gamma, const void* beta, int pdt, const T* __restrict__ res,
+                     int act) {
+  constexpr int V = VecOf<T>::N;
+  extern __shared__ float coef[];
+  float* S = coef;
+  float* Tc = coef + C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float sc = invstd[c] * (gamma ? ldf(gamma, c, pdt) : 1.f);
+    S[c] = sc;
+    Tc[c] = (beta ? ldf(beta, c, pdt) : 0.f) - ldf(mean, c, mdt) * sc;
+  }
+  __syncthreads();
+  const unsigned cvecs = C / V;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += gridDim.x * blockDim.x) {
+    const int c0 = (int)(i % cvecs) * V;
+    float v[V], r[V];
+    load_vec<T>(x + (size_t)i * V, v);
+    if (res) load_vec<T>(res + (size_t)i * V, r);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      float t = fmaf(v[k], S[c0 + k], Tc[c0 + k]);
+      if (res) t += r[k];
+      if (act == 1) t = t > 0.f ? t : 0.f;
+      v[k] = t;
+    }
+    store_vec<T>(y + (size_t)i * V, v);
+  }
+}
+
+// dx = A[c] * dy + B[c] * x + D[c]   (training), dx = A[c] * dy (eval)
+template <typename T>
+__global__ void __launch_bounds__(256)
+bn_bwd_apply_fast_kernel(const T* __restrict__ dy, const T* __restrict__ x, const void* mean, int mdt,
+                         const float* invstd, const void* gamma, int pdt, const T* __restrict__ relu_out,
+                         const double* sums, long long rows, int C, int training, T* __restrict__ dx, unsigned nvec) {
+  constexpr int V = VecOf<T>::N;
+  extern __shared__ float coef[];
+  float* A = coef;
+  float* B = coef + C;
+  float* D = coef + 2 * C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float is = invstd[c];
+    const float a = (gamma ? ldf(gamma, c, pdt) : 1.f) * is;
+    A[c] = a;
+    if (training) {
+      const float sdy = (float)(sums[c] / (double)rows), sdx = (float)(sums[C + c] / (double)rows);
+      const float b = -a * is * sdx;
+      B[c] = b;
+      D[c] = -a * sdy - b * ldf(mean, c, mdt);
+    } else {
+      B[c] = 0.f;
+      D[c] = 0.f;
+    }
+  }
+  __syncthreads();
+  const unsigned cvecs = C / V;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += gridDim.x * blockDim.x) {
+    const int c0 = (int)(i % cvecs) * V;
+    float g[V], v[V], o[V];
+    load_vec<T>(dy + (size_t)i * V, g);
+    load_vec<T>(x + (size_t)i * V, v);
+    if (relu_out) load_vec<T>(relu_out + (size_t)i * V, o);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      float gi = g[k];
+      if (relu_out && !(o[k] > 0.f)) gi = 0.f;
+      g[k] = fmaf(A[c0 + k], gi, fmaf(B[c0 + k], v[k], D[c0 + k]));
+    }
+    store_vec<T>(dx + (size_t)i * V, g);
+  }
+}
+
+inline int ew_grid_u(unsigned n) {
+  unsigned g = (n + 255) / 256;
+  if (g > 148 * 8) g = 148 * 8;
+  return g < 1 ? 1 : (int)g;
 }
 
 inline int red_grid(long long rows) {
@@ -374,6 +470,18 @@ extern "C" int b200_bn_apply(const void* x, int xdt, void* y, int ydt, long long
   if (rows <= 0 || C <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   const long long n = rows * C;
+  // fast path: same 16-bit / fp32 type in and out, coefficients fit in shared memory
+  if (xdt == ydt && C <= 8192 && (!res || rdt == xdt) && n / (xdt == B200_F32 ? 4 : 8) < 0xffffffffLL) {
+    const int V = xdt == B200_F32 ? 4 : 8;
+    if (C % V == 0) {
+      const unsigned nvec = (unsigned)(n / V);
+      const size_t sm = sizeof(float) * 2 * C;
+      DISPATCH_FLOAT(xdt, T, (bn_apply_fast_kernel<T><<<ew_grid_u(nvec), 256, sm, s>>>(
+                                 static_cast<const T*>(x), static_cast<T*>(y), nvec, C, mean, mdt, invstd, gamma, beta,
+                                 pdt, static_cast<const T*>(res), act)));
+      return (int)cudaGetLastError();
+    }
+  }
 #define BN_APPLY(TX, TY)                                                                                            \
   {                                                                                                                 \
     constexpr int V = VecOf<TX>::N > VecOf<TY>::N ? VecOf<TY>::N : VecOf<TX>::N;                                    \
@@ -417,6 +525,15 @@ extern "C" int b200_bn_backward_apply(const void* dy, int dt, const void* x, int
   if (dt != xdt || (relu_out && rdt != dt)) return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   const long long n = rows * C;
+  if (dx && dxdt == dt && C <= 8192 && C % (dt == B200_F32 ? 4 : 8) == 0 && n / (dt == B200_F32 ? 4 : 8) < 0xffffffffLL) {
+    const int V = dt == B200_F32 ? 4 : 8;
+    const unsigned nvec = (unsigned)(n / V);
+    const size_t sm = sizeof(float) * 3 * C;
+    DISPATCH_FLOAT(dt, T, (bn_bwd_apply_fast_kernel<T><<<ew_grid_u(nvec), 256, sm, s>>>(
+                               static_cast<const T*>(dy), static_cast<const T*>(x), mean, mdt, invstd, gamma, pdt,
+                               static_cast<const T*>(relu_out), sums, rows, C, training, static_cast<T*>(dx), nvec)));
+    dx = nullptr;  // done
+  }
   if (dx) {
 #define BN_BWD(T, TO)                                                                                                  \
   bn_bwd_apply_kernel<T, TO><<<ew_grid(n), 256, 0, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x), mean, mdt, \

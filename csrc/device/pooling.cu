@@ -31,6 +31,20 @@ template <> struct Cv<__half> {
 
 // linear thread index -> (n, c, a, b) with c fastest (channels_last) or b fastest
 __device__ __forceinline__ void decode(long long i, int C, int A, int B, int cl, int& n, int& c, int& a, int& b) {
+  if (i <= 0xffffffffLL) {
+    // 32-bit divisions are several times cheaper than 64-bit ones
+    unsigned u = (unsigned)i;
+    if (cl) {
+      c = (int)(u % (unsigned)C); u /= (unsigned)C;
+      b = (int)(u % (unsigned)B); u /= (unsigned)B;
+      a = (int)(u % (unsigned)A); n = (int)(u / (unsigned)A);
+    } else {
+      b = (int)(u % (unsigned)B); u /= (unsigned)B;
+      a = (int)(u % (unsigned)A); u /= (unsigned)A;
+      c = (int)(u % (unsigned)C); n = (int)(u / (unsigned)C);
+    }
+    return;
+  }
   if (cl) {
     c = (int)(i % C); i /= C;
     b = (int)(i % B); i /= B;

@@ -5,6 +5,7 @@
 // and the fused optimizers are new (the reference runs them through the CPU
 // fallback or as many small element-wise launches).
 #include <ATen/core/op_registration/op_registration.h>
+#include <ATen/CPUGeneratorImpl.h>
 #include "../runtime/generator.h"
 #include "common.h"
 #include "kernels.h"
@@ -99,6 +100,32 @@ Tensor& k_normal_(Tensor& self, double mean, double std, std::optional<at::Gener
 Tensor& k_bernoulli_float_(Tensor& self, double p, std::optional<at::Generator> gen) {
   return rng_fill(self, gen, 2, p, 0);
 }
+// CPU path (host simulation / forced CPU dispatch): the values come from a CPU
+// generator seeded from this device's (seed, offset) pair, so torch.blackwell
+// seeding and RNG-state save / restore behave the same with and without a GPU.
+Tensor& rng_fill_cpu(Tensor& self, std::optional<at::Generator> gen, int mode, double a, double b) {
+  if (self.numel() == 0) return self;
+  auto so = philox(gen, self, (uint64_t)self.numel());
+  at::Generator cpu_gen = at::detail::createCPUGenerator(so.first * 0x9E3779B97F4A7C15ull + so.second);
+  Tensor host = at::empty(self.sizes(), self.options().device(at::kCPU));
+  if (mode == 0) host.uniform_(a, b, cpu_gen);
+  else if (mode == 1) host.normal_(a, b, cpu_gen);
+  else host.bernoulli_(a, cpu_gen);
+  self.copy_(host);
+  return self;
+}
+Tensor& c_uniform_(Tensor& self, double from, double to, std::optional<at::Generator> gen) { return rng_fill_cpu(self, gen, 0, from, to); }
+Tensor& c_normal_(Tensor& self, double mean, double std, std::optional<at::Generator> gen) { return rng_fill_cpu(self, gen, 1, mean, std); }
+Tensor& c_bernoulli_float_(Tensor& self, double p, std::optional<at::Generator> gen) { return rng_fill_cpu(self, gen, 2, p, 0); }
+std::tuple<Tensor, Tensor> c_native_dropout(const Tensor& input, double p, std::optional<bool> train) {
+  if (!train.value_or(true) || p == 0.0 || input.numel() == 0)
+    return {input.clone(), at::ones_like(input, input.options().dtype(at::kBool))};
+  Tensor keep = at::empty(input.sizes(), input.options().dtype(at::kFloat));
+  rng_fill_cpu(keep, std::nullopt, 2, 1.0 - p, 0);
+  Tensor mask = keep.to(at::kBool);
+  return {input * mask.to(input.scalar_type()) * (p < 1.0 ? 1.0 / (1.0 - p) : 0.0), mask};
+}
+
 std::tuple<Tensor, Tensor> k_native_dropout(const Tensor& input, double p, std::optional<bool> train) {
   if (!train.value_or(true) || p == 0.0 || input.numel() == 0) {
     return {input.clone(), at::ones_like(input, input.options().dtype(at::kBool))};
@@ -215,7 +242,13 @@ void fused_adamw_step(at::TensorList params, at::TensorList grads, at::TensorLis
 }
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
-  if (!device_kernels_enabled()) return;
+  if (!device_kernels_enabled()) {
+    m.impl("uniform_", TORCH_FN(c_uniform_));
+    m.impl("normal_", TORCH_FN(c_normal_));
+    m.impl("bernoulli_.float", TORCH_FN(c_bernoulli_float_));
+    m.impl("native_dropout", TORCH_FN(c_native_dropout));
+    return;
+  }
   m.impl("embedding", TORCH_FN(k_embedding));
   m.impl("embedding_dense_backward", TORCH_FN(k_embedding_dense_backward));
   m.impl("index_select", TORCH_FN(k_index_select));

@@ -117,6 +117,7 @@ class PinnedAllocator final : public c10::Allocator {
   }
   size_t cached_bytes() {
     std::lock_guard<std::mutex> g(mu_);
+    drain();  // blocks whose copies have finished count as cached
     size_t s = 0;
     for (auto* b : free_) s += b->size;
     return s;

@@ -1,0 +1,256 @@
+"""Runtime API on the host-simulated device: devices, queues, notifiers, caching
+allocator statistics, debug allocator, pinned memory, tensor movement, legacy
+constructors, torch.load with a device map_location, RNG reproducibility.
+Mirrors the reference's runtime tests (test/test_device.py, test_queue.py,
+test_notifier.py, test_caching_allocator.py, test_mlu.py)."""
+import io
+import threading
+
+import pytest
+import torch
+
+import catch_b200  # noqa: F401
+
+DEV = "blackwell"
+bw = torch.b200
+
+
+def test_device_management():
+    assert bw.is_available() and bw.device_count() >= 2
+    assert torch.blackwell is torch.b200
+    prev = bw.current_device()
+    bw.set_device(1)
+    assert bw.current_device() == 1
+    with bw.device(0):
+        assert bw.current_device() == 0
+        assert torch.empty(1, device=DEV).device.index == 0
+    assert bw.current_device() == 1
+    x = torch.zeros(1, device="blackwell:0")
+    with bw.device_of(x):
+        assert bw.current_device() == 0
+    bw.set_device(prev)
+    p = bw.get_device_properties(0)
+    assert p.major == 10 and p.total_memory > 0 and isinstance(p.name, str)
+    assert bw.get_device_capability() == (10, 0)
+    assert bw.get_device_name(0) == p.name
+    with pytest.raises(Exception):
+        bw.set_device(99)
+    bw.synchronize()
+    assert "catch_b200" in bw.get_version()
+
+
+def test_tensor_to_and_device_strings():
+    x = torch.arange(12.0).reshape(3, 4)
+    for spec in (DEV, "blackwell:1", torch.device(DEV, 0)):
+        y = x.to(spec)
+        assert y.device.type == DEV and torch.equal(y.cpu(), x)
+    assert x.blackwell().is_blackwell
+    m = torch.nn.Linear(4, 2).blackwell()
+    assert next(m.parameters()).device.type == DEV
+    y = x.to(DEV)
+    assert torch.equal(y.t().contiguous().cpu(), x.t())
+    assert torch.equal(y[1:, ::2].cpu(), x[1:, ::2])
+    assert y.double().dtype == torch.float64 and torch.equal(y.long().cpu(), x.long())
+    z = torch.empty_strided((2, 3), (1, 2), device=DEV)
+    assert z.stride() == (1, 2)
+    assert y.sum().item() == x.sum().item()
+    y2 = y.clone()
+    y2.resize_(5, 4)
+    assert y2.shape == (5, 4)
+    assert bw.FloatTensor(2, 3).shape == (2, 3) and bw.LongTensor([1, 2]).dtype == torch.int64
+    with pytest.raises(Exception):
+        _ = y + torch.ones(3, 4, device="blackwell:1")  # tensors on different devices
+
+
+def test_queues():
+    d = bw.current_device()
+    dq = bw.default_queue()
+    assert bw.current_queue() == dq and dq.device_index == d
+    with bw.Queue() as q:
+        assert bw.current_queue() == q and q != dq
+        assert q.query()
+        q.synchronize()
+    assert bw.current_queue() == dq
+    seen = {bw.queue_from_pool().queue_id for _ in range(40)}
+    assert len(seen) == 32  # the pool wraps around after 32 queues
+    other = {}
+
+    def worker():
+        other["q"] = bw.current_queue()
+
+    with bw.Queue():
+        t = threading.Thread(target=worker)
+        t.start(); t.join()
+    assert other["q"] == dq  # the current queue is thread-local
+    with bw.Queue(1) as q1:
+        assert bw.current_device() == 1 and q1.device_index == 1
+    assert bw.current_device() == d
+    s = torch.Stream(device=DEV)  # generic torch.Stream goes through the device guard
+    with s:
+        assert torch.empty(1, device=DEV).device.type == DEV
+
+
+def test_notifiers():
+    a, b = bw.Notifier(), bw.Notifier()
+    assert a.query()
+    a.place()
+    x = torch.ones(1000, device=DEV)
+    for _ in range(10):
+        x = x * 2
+    b.place(bw.current_queue())
+    b.synchronize()
+    assert b.query()
+    assert a.elapsed_time(b) >= 0.0
+    assert a.hardware_time(b) == pytest.approx(a.elapsed_time(b) * 1000, rel=0.5, abs=1e3)
+    b.wait(bw.current_queue())
+    with pytest.raises(Exception):
+        bw.Notifier().elapsed_time(b)
+    e1, e2 = torch.Event(device=DEV, enable_timing=True), torch.Event(device=DEV, enable_timing=True)
+    e1.record(); e2.record(); e2.synchronize()
+    assert e1.elapsed_time(e2) >= 0.0
+
+
+def test_caching_allocator_stats():
+    bw.empty_cache()
+    d = bw.current_device()
+    base_a, base_r = bw.memory_allocated(d), bw.memory_reserved(d)
+    x = torch.empty(1000, device=DEV)  # 4000 B -> rounded to 4096, from a 2 MiB segment
+    assert bw.memory_allocated(d) == base_a + 4096
+    assert bw.memory_reserved(d) >= base_r + (2 << 20)
+    y = torch.empty(3 << 20, dtype=torch.uint8, device=DEV)  # large pool: a 20 MiB segment
+    assert bw.memory_reserved(d) >= base_r + (22 << 20)
+    peak = bw.max_memory_allocated(d)
+    assert peak >= bw.memory_allocated(d)
+    del x, y
+    assert bw.memory_allocated(d) == base_a
+    assert bw.memory_reserved(d) >= base_r + (22 << 20)  # cached, not returned
+    z = torch.empty(1000, device=DEV)
+    assert bw.memory_reserved(d) >= base_r + (22 << 20)  # reuse, no growth
+    del z
+    bw.empty_cache()
+    assert bw.memory_reserved(d) == base_r
+    assert bw.max_memory_allocated(d) == peak
+    bw.reset_peak_memory_stats(d)
+    assert bw.max_memory_allocated(d) == bw.memory_allocated(d)
+    assert bw.memory_cached(d) == bw.memory_reserved(d)
+    st = bw.memory_stats(d)
+    assert st["num_alloc"] >= 3 and "allocated_bytes.current" in st
+    assert "allocated" in bw.memory_summary(d)
+
+
+def test_record_queue_defers_reuse():
+    with bw.Queue() as side:
+        pass
+    x = torch.empty(1 << 16, device=DEV)
+    ptr = x.data_ptr()
+    bw.record_queue(x, side)
+    del x
+    y = torch.empty(1 << 16, device=DEV)  # after the side queue's notifier has fired the block may come back
+    assert y.data_ptr() is not None and ptr is not None
+
+
+def test_native_memory_strategy_and_oom():
+    bw.empty_cache()
+    d = bw.current_device()
+    bw.set_memory_strategy(True)
+    try:
+        r0 = bw.memory_reserved(d)
+        t = torch.empty(3 << 20, dtype=torch.uint8, device=DEV)
+        assert bw.memory_reserved(d) - r0 == 3 << 20  # exactly what was asked for
+        del t
+    finally:
+        bw.set_memory_strategy(False)
+        bw.empty_cache()
+    catch_b200._C._hostsim_set_memory_limit(64 << 20)
+    try:
+        keep = torch.empty(40 << 20, dtype=torch.uint8, device=DEV)
+        del keep  # cached: the next big request must free the cache and retry
+        big = torch.empty(50 << 20, dtype=torch.uint8, device=DEV)
+        assert bw.memory_stats(d)["num_alloc_retries"] >= 1
+        with pytest.raises(torch.OutOfMemoryError, match="out of memory"):
+            torch.empty(100 << 20, dtype=torch.uint8, device=DEV)
+        del big
+    finally:
+        catch_b200._C._hostsim_set_memory_limit(8 << 30)
+        bw.empty_cache()
+
+
+def test_debug_allocator_detects_overrun():
+    import ctypes
+
+    bw.empty_cache()
+    bw.set_memory_debug(True)
+    try:
+        x = torch.zeros(100, device=DEV)
+        checked, corrupted, _ = bw.memory_debug(x)
+        assert checked == 1 and corrupted == 0
+        # host simulation: device memory is host memory, so an overrun can be staged from here
+        ctypes.memset(x.data_ptr() + 512, 0, 8)  # first bytes after the rounded block
+        with pytest.raises(RuntimeError, match="out-of-bounds"):
+            bw.memory_debug(x)
+        ctypes.memset(x.data_ptr() + 512, 0xA5, 8)
+        bw.memory_debug()
+        del x
+    finally:
+        bw.empty_cache()
+        bw.set_memory_debug(False)
+
+
+def test_pinned_memory():
+    x = torch.randn(1000)
+    assert not bw.is_pinned(x)
+    p = bw.pin_memory(x)
+    assert bw.is_pinned(p) and torch.equal(p, x)
+    y = p.to(DEV, non_blocking=True)
+    bw.synchronize()
+    assert torch.equal(y.cpu(), x)
+    del p
+    assert catch_b200._C._pinned_cached_bytes() >= 4000
+    catch_b200._C._pinned_empty_cache()
+    assert catch_b200._C._pinned_cached_bytes() == 0
+
+
+def test_save_load_and_map_location():
+    m = torch.nn.Linear(3, 2).to(DEV)
+    buf = io.BytesIO()
+    torch.save(m.state_dict(), buf)
+    buf.seek(0)
+    sd = torch.load(buf, map_location="cpu")
+    assert all(v.device.type == "cpu" for v in sd.values())
+    buf.seek(0)
+    sd = torch.load(buf, map_location="blackwell:1")
+    assert all(v.device == torch.device(DEV, 1) for v in sd.values())
+    m2 = torch.nn.Linear(3, 2)
+    m2.load_state_dict({k: v.cpu() for k, v in sd.items()})
+    assert torch.equal(m2.weight, m.weight.cpu())
+    opt = torch.optim.SGD(m2.parameters(), lr=0.1, momentum=0.9)
+    m2(torch.randn(2, 3)).sum().backward(); opt.step()
+    bw.to(opt, DEV)
+    assert all(v.device.type == DEV for s in opt.state.values() for v in s.values() if isinstance(v, torch.Tensor))
+
+
+def test_rng_reproducible():
+    bw.manual_seed(7)
+    a = torch.randn(100, device=DEV)
+    bw.manual_seed(7)
+    b = torch.randn(100, device=DEV)
+    assert torch.equal(a.cpu(), b.cpu())
+    st = bw.get_rng_state()
+    c = torch.rand(10, device=DEV)
+    bw.set_rng_state(st)
+    assert torch.equal(torch.rand(10, device=DEV).cpu(), c.cpu())
+    torch.manual_seed(3)  # seeds every device generator too
+    d1 = torch.randn(5, device=DEV)
+    torch.manual_seed(3)
+    assert torch.equal(torch.randn(5, device=DEV).cpu(), d1.cpu())
+
+
+def test_flags_and_logging(capfd):
+    assert bw.get_flag("fallback_to_cpu") is True
+    bw.set_log_level(-1)
+    try:
+        _ = torch.ones(2, device=DEV) + 1
+        err = capfd.readouterr().err
+        assert "[DEBUG]" in err and "runs on the CPU path" in err
+    finally:
+        bw.set_log_level(1)
