@@ -47,12 +47,14 @@ struct ConvArgs {
   int res_dtype;
   int act;
   float alpha;
+  int tma_store;                // epilogue stages 64-channel blocks in shared memory and stores them by TMA
   int* err;
 };
 
 struct ConvMaps {
   CUtensorMap a[B200_CONV_MAX_MAPS];
   CUtensorMap w;
+  CUtensorMap out;
 };
 
 __device__ __forceinline__ float ld_scalar(const void* p, long long i, int dt) {
@@ -72,6 +74,8 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
   uint64_t* acc_full = bars + 2 * CONV_MAX_STAGES;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  // two 16 KB staging buffers (128 pixels x 64 channels, 128-byte swizzle) for the TMA-store epilogue
+  uint8_t* stage_out = smem + (size_t)g.stages * stage_bytes + 1024;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -79,6 +83,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
     for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
     mbar_fence_init();
     tma_prefetch_desc(&maps.w);
+    if (g.tma_store) tma_prefetch_desc(&maps.out);
     tma_prefetch_desc(&maps.a[0]);
   }
   if (warp == 1) tmem_alloc(tmem_slot, 512);
@@ -149,6 +154,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
   } else {
     const int quarter = warp & 3;
     int acc = 0; uint32_t acc_phase = 0;
+    uint32_t out_blocks = 0;
     const int esz = g.out_dtype == B200_F32 ? 4 : 2;
     const int rsz = g.res_dtype == B200_F32 ? 4 : 2;
     for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
@@ -164,6 +170,69 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
                             (long long)(q * g.o_mul_w + g.o_off_w) * g.o_sw;
       if (!mbar_wait(&acc_full[acc], acc_phase, g.err, ERR_TIMEOUT_TMEM_FULL)) { failed = true; break; }
       tc_fence_after();
+      if (g.tma_store) {
+        // Stage 64 channels x 128 pixels at a time in shared memory (the 128-byte swizzled
+        // layout the output tensor map expects) and let the copy engine write full lines;
+        // rows / channels outside the tensor are clipped by the store.
+        const bool issuer = threadIdx.x == 64;
+        for (int cb = 0; cb < g.tile_n; cb += 64) {
+          uint8_t* sbuf = stage_out + (out_blocks & 1) * 16384;
+          if (issuer) tma_store_wait_read<1>();  // the store that last used this buffer has read it
+          named_barrier(1, 128);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int c = cb + half * 32;
+            uint32_t rr[32];
+            tmem_ld32(tmem_base + acc * 256 + ((uint32_t)(quarter * 32) << 16) + c, rr);
+            tmem_ld_wait();
+            const int cbase = co0 + c;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rr[j]) * g.alpha;
+            if (g.scale) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (cbase + j < g.Cout) v[j] *= g.scale[cbase + j];
+            }
+            if (g.bias) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (cbase + j < g.Cout) v[j] += ld_scalar(g.bias, cbase + j, g.bias_dtype);
+            }
+            if (g.residual && row_ok) {
+              for (int j = 0; j < 32; ++j)
+                if (cbase + j < g.Cout) v[j] += ld_scalar(g.residual, off + cbase + j, g.res_dtype);
+            }
+            if (g.act == 1) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+            }
+            alignas(16) uint16_t h[32];
+            if (g.out_dtype == B200_BF16) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) h[j] = __bfloat16_as_ushort(__float2bfloat16(v[j]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) h[j] = __half_as_ushort(__float2half(v[j]));
+            }
+            uint8_t* srow = sbuf + r * 128;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int chunk = (half * 4 + k) ^ (r & 7);
+              *reinterpret_cast<uint4*>(srow + chunk * 16) = reinterpret_cast<const uint4*>(h)[k];
+            }
+          }
+          fence_proxy_async_smem();
+          named_barrier(1, 128);
+          if (issuer) {
+            tma_store_4d(&maps.out, sbuf, co0 + cb, q0, p0, n0);
+            tma_store_commit();
+          }
+          ++out_blocks;
+        }
+        tc_fence_before();
+        mbar_arrive(&acc_empty[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        continue;
+      }
       for (int c = 0; c < g.tile_n; c += 32) {
         uint32_t rr[32];
         tmem_ld32(tmem_base + acc * 256 + ((uint32_t)(quarter * 32) << 16) + c, rr);
@@ -233,6 +302,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
     }
   }
 
+  if (g.tma_store && threadIdx.x == 64) tma_store_wait_all<0>();  // staged tiles must be read before smem goes away
   if (*((volatile int*)g.err) != 0) {
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -411,7 +481,7 @@ static int encode_view(CUtensorMap* m, const B200ConvView& v, CUtensorMapDataTyp
 
 static int set_smem_attr_once(const void* fn, int dev, bool* done) {
   if (done[dev & 63]) return 0;
-  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   if (e != cudaSuccess) return (int)e;
   done[dev & 63] = true;
   return 0;
@@ -465,11 +535,22 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p, void* stream) {
   g.err = error_flag_ptr();
   if (!g.err) return (int)cudaErrorInvalidDevice;
   const int stage_bytes = CONV_A_BYTES + g.tile_n * 128;
-  g.stages = (200 * 1024) / stage_bytes;
+  g.tma_store = (p->out_dtype != B200_F32 && g.tile_n % 64 == 0 && p->Cout % 8 == 0) ? 1 : 0;
+  const int smem_cap = 227 * 1024 - 2048 - 1024 - (g.tma_store ? 32768 : 0);
+  g.stages = smem_cap / stage_bytes;
   if (g.stages > CONV_MAX_STAGES) g.stages = CONV_MAX_STAGES;
   if (g.stages < 2) g.stages = 2;
 
   ConvMaps maps;
+  maps.out = CUtensorMap{};
+  if (g.tma_store) {
+    B200ConvView ov;
+    ov.base = static_cast<const char*>(p->out) + ((long long)p->o_off_h * p->o_sh + (long long)p->o_off_w * p->o_sw) * 2;
+    ov.dims[0] = p->Cout; ov.dims[1] = p->Q; ov.dims[2] = p->P; ov.dims[3] = p->N;
+    ov.strides[0] = p->o_sw * p->o_mul_w; ov.strides[1] = p->o_sh * p->o_mul_h; ov.strides[2] = p->o_sn;
+    int rc = encode_view(&maps.out, ov, dt, 64, g.bw, g.bh, g.bni);
+    if (rc) return rc;
+  }
   for (int i = 0; i < p->num_views; ++i) {
     int rc = encode_view(&maps.a[i], p->views[i], dt, 64, g.bw, g.bh, g.bni);
     if (rc) return rc;
@@ -493,7 +574,7 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p, void* stream) {
   static bool attr_done[64] = {false};
   int rc = set_smem_attr_once((const void*)conv_fprop_kernel, dev, attr_done);
   if (rc) return rc;
-  const size_t smem = (size_t)g.stages * stage_bytes + 1024 + 256;
+  const size_t smem = (size_t)g.stages * stage_bytes + 1024 /*align*/ + 1024 /*barriers*/ + (g.tma_store ? 32768 : 0);
   const long total_tiles = pix_tiles * g.tiles_co;
   const int ctas = (int)(total_tiles < sms ? total_tiles : sms);
   conv_fprop_kernel<<<ctas, CONV_THREADS, smem, (cudaStream_t)stream>>>(maps, g);
