@@ -1,0 +1,64 @@
+"""TorchScript fusion mode.
+
+* ``set_fusion_enabled(bool)`` / ``fusion_enabled()`` -- the global toggle (the
+  reference's ``_jit_override_can_fuse_on_mlu`` / ``_jit_can_fuse_on_mlu``,
+  torch_mlu/csrc/jit/interface.cpp:36-45).
+* ``optimize(module, example_inputs=None)`` -- freeze an eval-mode scripted / traced
+  module (folds batch norm into the preceding convolution), lower the graph, rewrite
+  conv(+BN)+ReLU(+residual) and linear+bias(+activation) chains into the backend's fused
+  tcgen05 ops and group supported nodes into ``catch_b200::FusionGroup`` nodes.
+* The same passes are registered as graph-executor pre-passes, so a scripted module
+  that was not explicitly optimised still gets fusion groups on its first run.
+
+Environment: ``CATCH_B200_FORCED_FALLBACK_OPS=a,b`` keeps the listed ops out of fusion
+groups; ``CATCH_B200_FUSED_KERNEL_DEBUG=cpu`` also runs every group on the CPU and
+writes both results to ``fused_kernel_<n>_{device,cpu}.pt``.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _C
+
+_C._jit_register_passes()
+
+
+def fusion_enabled() -> bool:
+    return _C._jit_can_fuse_on_b200()
+
+
+def set_fusion_enabled(enable: bool) -> None:
+    _C._jit_override_can_fuse_on_b200(bool(enable))
+
+
+def lower_graph(graph) -> None:
+    _C._jit_pass_lower_graph(graph)
+
+
+def fuse_kernels(graph) -> None:
+    _C._jit_pass_fuse_kernels(graph)
+
+
+def segment_graph(graph) -> None:
+    _C._jit_pass_segment_graph(graph)
+
+
+def fusion_stats() -> dict:
+    return {"runners": _C._jit_fusion_cache_size(), "compiles": _C._jit_fusion_compile_count(),
+            "fallbacks": _C._jit_fusion_fallback_count()}
+
+
+def optimize(module: torch.jit.ScriptModule, preserved_attrs=None) -> torch.jit.ScriptModule:
+    """Freeze ``module`` (must be in eval mode) and run the fusion passes on its forward graph."""
+    if module.training:
+        raise ValueError("catch_b200.jit.optimize expects a module in eval() mode")
+    frozen = torch.jit.freeze(module, preserved_attrs=preserved_attrs or [])
+    graph = frozen.graph
+    torch._C._jit_pass_fold_frozen_conv_bn(graph)
+    torch._C._jit_pass_fold_frozen_conv_add_or_sub(graph)
+    torch._C._jit_pass_fold_frozen_conv_mul_or_div(graph)
+    if fusion_enabled():
+        lower_graph(graph)
+        fuse_kernels(graph)
+        segment_graph(graph)
+    return frozen

@@ -1,0 +1,193 @@
+// The catch_b200::FusionGroup operator: runner cache keyed by the canonical graph
+// text, per-runner plans keyed by argument dtypes / shapes / device, interpreter
+// fallback, and the debug mode that also runs the group on the CPU.
+// Reference: torch_mlu/csrc/jit/partition/customer_partition_manager.cpp:51-72,
+// runtime/runner_cache.cpp:44-85, runtime/graph_runner.cpp:55-238.
+#include <torch/csrc/jit/passes/canonicalize.h>
+#include <torch/csrc/jit/runtime/custom_operator.h>
+#include <torch/csrc/jit/runtime/interpreter.h>
+#include <torch/csrc/jit/serialization/pickle.h>
+
+#include <atomic>
+#include <fstream>
+#include <mutex>
+#include <sstream>
+#include <unordered_map>
+
+#include "../runtime/log.h"
+#include "../runtime/tensor_impl.h"
+#include "fusion.h"
+
+namespace catch_b200 {
+namespace jit {
+
+using namespace torch::jit;
+
+namespace {
+
+std::atomic<int64_t> g_compiles{0}, g_fallbacks{0};
+
+std::string arg_spec(const Stack& stack, size_t n_inputs) {
+  std::ostringstream os;
+  for (size_t i = stack.size() - n_inputs; i < stack.size(); ++i) {
+    const IValue& v = stack[i];
+    if (v.isTensor()) {
+      const at::Tensor& t = v.toTensor();
+      if (!t.defined()) { os << "U;"; continue; }
+      os << static_cast<int>(t.scalar_type()) << t.sizes() << "@" << t.device() << (t.is_contiguous() ? "c" : "s") << ";";
+    } else {
+      os << "_;";
+    }
+  }
+  return os.str();
+}
+
+class FusedRunner {
+ public:
+  explicit FusedRunner(std::shared_ptr<Graph> g) : graph_(std::move(g)), fallback_(graph_, "b200_fusion_fallback") {}
+
+  void run(Stack& stack) {
+    const size_t n_in = graph_->inputs().size();
+    const std::string spec = arg_spec(stack, n_in);
+    std::shared_ptr<Code> plan;
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      auto it = plans_.find(spec);
+      if (it != plans_.end()) plan = it->second;
+    }
+    Stack saved;
+    const char* dbg = std::getenv("CATCH_B200_FUSED_KERNEL_DEBUG");
+    if (dbg) saved.assign(stack.end() - n_in, stack.end());
+    try {
+      if (!plan) plan = compile(spec, stack, n_in);
+      InterpreterState(*plan).run(stack);
+    } catch (const c10::OutOfMemoryError&) {
+      throw;
+    } catch (const std::exception& e) {
+      TORCH_WARN("b200 fusion group failed (", e.what(), "); running it op by op instead.");
+      g_fallbacks++;
+      run_fallback(stack, n_in, saved);
+      return;
+    }
+    if (dbg) debug_compare(dbg, saved, stack);
+  }
+
+  size_t plan_count() {
+    std::lock_guard<std::mutex> g(mu_);
+    return plans_.size();
+  }
+
+ private:
+  std::shared_ptr<Code> compile(const std::string& spec, const Stack& stack, size_t n_in) {
+    // specialise a copy of the subgraph: concrete input types, fused kernels
+    std::shared_ptr<Graph> g = graph_->copy();
+    for (size_t i = 0; i < n_in; ++i) {
+      const IValue& v = stack[stack.size() - n_in + i];
+      if (v.isTensor() && v.toTensor().defined()) g->inputs()[i]->setType(TensorType::create(v.toTensor()));
+    }
+    FuseKernels(g);
+    auto code = std::make_shared<Code>(g, "b200_fusion_group");
+    g_compiles++;
+    std::lock_guard<std::mutex> lk(mu_);
+    plans_[spec] = code;
+    return code;
+  }
+
+  void run_fallback(Stack& stack, size_t n_in, const Stack& saved) {
+    (void)saved;
+    (void)n_in;
+    InterpreterState(fallback_).run(stack);
+  }
+
+  void debug_compare(const std::string& mode, const Stack& inputs, const Stack& stack) {
+    // mode "cpu": run the same subgraph on CPU copies and write both results next to each other
+    if (mode != "cpu") return;
+    Stack cpu_stack;
+    for (const IValue& v : inputs) cpu_stack.push_back(v.isTensor() && v.toTensor().defined() ? IValue(v.toTensor().cpu()) : v);
+    try {
+      InterpreterState(fallback_).run(cpu_stack);
+    } catch (const std::exception& e) {
+      TORCH_WARN("b200 fusion debug: CPU run failed: ", e.what());
+      return;
+    }
+    static std::atomic<int> counter{0};
+    const int id = counter++;
+    const size_t n_out = graph_->outputs().size();
+    c10::List<at::Tensor> dev_out, cpu_out;
+    for (size_t i = 0; i < n_out; ++i) {
+      const IValue& d = stack[stack.size() - n_out + i];
+      const IValue& c = cpu_stack[cpu_stack.size() - n_out + i];
+      if (d.isTensor()) dev_out.push_back(d.toTensor().cpu());
+      if (c.isTensor()) cpu_out.push_back(c.toTensor());
+    }
+    auto write = [&](const std::string& name, const c10::List<at::Tensor>& l) {
+      auto bytes = torch::jit::pickle_save(IValue(l));
+      std::ofstream f(name, std::ios::binary);
+      f.write(bytes.data(), static_cast<std::streamsize>(bytes.size()));
+    };
+    write("fused_kernel_" + std::to_string(id) + "_device.pt", dev_out);
+    write("fused_kernel_" + std::to_string(id) + "_cpu.pt", cpu_out);
+  }
+
+  std::shared_ptr<Graph> graph_;
+  Code fallback_;
+  std::mutex mu_;
+  std::unordered_map<std::string, std::shared_ptr<Code>> plans_;
+};
+
+class RunnerCache {
+ public:
+  static RunnerCache& get() {
+    static RunnerCache c;
+    return c;
+  }
+  int64_t registerFusion(const Node* node) {
+    std::shared_ptr<Graph> g = node->g(attr::Subgraph)->copy();
+    std::shared_ptr<Graph> canon = Canonicalize(g, /*keep_unique_names=*/false);
+    const std::string text = canon->toString(/*print_source_locations=*/false);
+    std::lock_guard<std::mutex> lk(mu_);
+    auto it = by_text_.find(text);
+    if (it != by_text_.end()) return it->second;
+    const int64_t key = static_cast<int64_t>(runners_.size());
+    runners_.push_back(std::make_shared<FusedRunner>(g));
+    by_text_[text] = key;
+    return key;
+  }
+  std::shared_ptr<FusedRunner> retrieve(int64_t key) {
+    std::lock_guard<std::mutex> lk(mu_);
+    TORCH_CHECK(key >= 0 && key < static_cast<int64_t>(runners_.size()), "b200 fusion: unknown runner key ", key);
+    return runners_[key];
+  }
+  int64_t size() {
+    std::lock_guard<std::mutex> lk(mu_);
+    return static_cast<int64_t>(runners_.size());
+  }
+  void clear() {
+    std::lock_guard<std::mutex> lk(mu_);
+    by_text_.clear();  // existing closures keep their runners alive through the vector
+  }
+
+ private:
+  std::mutex mu_;
+  std::unordered_map<std::string, int64_t> by_text_;
+  std::vector<std::shared_ptr<FusedRunner>> runners_;
+};
+
+Operation create_fusion_operation(const Node* node) {
+  const int64_t key = RunnerCache::get().registerFusion(node);
+  auto runner = RunnerCache::get().retrieve(key);
+  return [runner](Stack& stack) { runner->run(stack); };
+}
+
+RegisterOperators reg_fusion({Operator(Symbol::fromQualString("catch_b200::FusionGroup"), create_fusion_operation,
+                                       AliasAnalysisKind::CONSERVATIVE)});
+
+}  // namespace
+
+int64_t fusion_cache_size() { return RunnerCache::get().size(); }
+void fusion_cache_clear() { RunnerCache::get().clear(); }
+int64_t fusion_compile_count() { return g_compiles.load(); }
+int64_t fusion_fallback_count() { return g_fallbacks.load(); }
+
+}  // namespace jit
+}  // namespace catch_b200

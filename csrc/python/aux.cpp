@@ -1,9 +1,28 @@
-// Bindings of dump tool / profiler / JIT toggles (filled in as those subsystems land).
+// Bindings of the dump tool, JIT fusion toggles and profiler helpers.
 #include <torch/csrc/utils/pybind.h>
 #include <torch/extension.h>
+
+#include <torch/csrc/jit/python/pybind_utils.h>
+
+#include "../jit/fusion.h"
+#include "../runtime/dumper.h"
 
 namespace py = pybind11;
 
 namespace catch_b200 {
-void bind_aux(py::module& m) { (void)m; }
+void bind_aux(py::module& m) {
+  m.def("_dump_start", &dump_start, py::arg("dir"), py::arg("enable") = true, py::arg("use_cpu") = false, py::arg("level") = 0);
+  m.def("_dump_finish", &dump_finish);
+  m.def("_dump_running", &dump_running);
+  m.def("_jit_can_fuse_on_b200", &jit::fusion_enabled);
+  m.def("_jit_override_can_fuse_on_b200", &jit::set_fusion_enabled);
+  m.def("_jit_register_passes", &jit::register_passes);
+  m.def("_jit_fusion_cache_size", &jit::fusion_cache_size);
+  m.def("_jit_fusion_cache_clear", &jit::fusion_cache_clear);
+  m.def("_jit_fusion_compile_count", &jit::fusion_compile_count);
+  m.def("_jit_fusion_fallback_count", &jit::fusion_fallback_count);
+  m.def("_jit_pass_lower_graph", [](std::shared_ptr<torch::jit::Graph>& g) { jit::LowerGraph(g); });
+  m.def("_jit_pass_fuse_kernels", [](std::shared_ptr<torch::jit::Graph>& g) { jit::FuseKernels(g); });
+  m.def("_jit_pass_segment_graph", [](std::shared_ptr<torch::jit::Graph>& g) { jit::SegmentGraph(g); });
+}
 }  // namespace catch_b200

@@ -1,0 +1,126 @@
+"""Dump tool, profiler, prefetch loader and fusion passes on the host-simulated device."""
+import os
+
+import torch
+
+import catch_b200  # noqa: F401
+from catch_b200 import dumptool, jit, profiler
+from catch_b200.utils import PrefetchLoader
+
+DEV = "blackwell"
+
+
+def test_dump_tool_files(tmp_path):
+    x = torch.arange(12.0).reshape(3, 4).to(DEV)
+    d = str(tmp_path / "dump")
+    with dumptool.Dumper(d, enable=True, use_cpu=True, level=2):
+        y = torch.relu(x - 5.0)
+    ops = sorted(os.listdir(d))
+    assert any(o.endswith("aten__sub") or "sub" in o for o in ops) and any("relu" in o for o in ops)
+    relu_dir = os.path.join(d, [o for o in ops if "relu" in o][0])
+    files = sorted(os.listdir(relu_dir))
+    assert "dev_0" in files and "dev_result_0" in files and "cpu_result_0" in files
+    head, *vals = open(os.path.join(relu_dir, "dev_result_0")).read().splitlines()
+    assert head == "Tensor : Type = Float : Shape = [3, 4] : Stride = [4, 1] : Dumped = 12"
+    assert [float(v) for v in vals] == torch.relu(torch.arange(12.0) - 5).tolist()
+    errs, ok = dumptool.compare_dump(relu_dir)
+    assert ok and errs
+    # level 0: first ten values; a second dump goes to "<dir>1"
+    with dumptool.Dumper(d, level=0):
+        torch.relu(x)
+    assert os.path.isdir(d + "1")
+    sub = os.path.join(d + "1", os.listdir(d + "1")[0])
+    assert open(os.path.join(sub, "dev_0")).read().splitlines()[0].endswith("Dumped = 10")
+    assert y.device.type == DEV
+
+
+def test_profiler_reports_device_time():
+    x = torch.randn(64, 64, device=DEV)
+    with profiler.profile(record_shapes=True, profile_memory=True) as prof:
+        y = (x @ x).relu().sum()
+    assert y.device.type == DEV
+    names = {e.name for e in prof.function_events}
+    assert "aten::mm" in names and "aten::relu" in names
+    table = prof.key_averages().table(sort_by="self_cpu_time_total")
+    assert "aten::mm" in table
+    with profiler.timed_region() as t:
+        _ = x + 1
+    assert t.ms >= 0.0
+
+
+def test_prefetch_loader_matches_plain():
+    data = [(torch.full((4, 3), float(i)), torch.tensor([i] * 4)) for i in range(5)]
+    for use_q in (True, False):
+        got = list(PrefetchLoader(data, DEV, use_io_queue=use_q))
+        assert len(got) == 5
+        for i, (a, b) in enumerate(got):
+            assert a.device.type == DEV and torch.equal(a.cpu(), data[i][0]) and torch.equal(b.cpu(), data[i][1])
+
+
+class Block(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.conv1 = torch.nn.Conv2d(8, 16, 3, padding=1, bias=False)
+        self.bn1 = torch.nn.BatchNorm2d(16)
+        self.conv2 = torch.nn.Conv2d(16, 16, 3, padding=1, bias=False)
+        self.bn2 = torch.nn.BatchNorm2d(16)
+        self.skip = torch.nn.Conv2d(8, 16, 1, bias=False)
+        self.drop = torch.nn.Dropout(0.5)
+        self.fc = torch.nn.Linear(16, 10)
+
+    def forward(self, x):
+        y = torch.relu(self.bn1(self.conv1(x)))
+        y = self.bn2(self.conv2(y))
+        y = torch.relu(y + self.skip(x))
+        y = self.drop(y.mean((2, 3)))
+        return torch.relu(self.fc(y))
+
+
+def test_fusion_passes_rewrite_and_segment():
+    torch.manual_seed(0)
+    m = Block().eval()
+    for bn in (m.bn1, m.bn2):
+        bn.running_mean.normal_(); bn.running_var.uniform_(0.5, 2.0)
+    x = torch.randn(2, 8, 12, 12)
+    ref = m(x)
+    sm = torch.jit.script(m)
+    opt = jit.optimize(sm)
+    g = str(opt.graph)
+    assert "catch_b200::FusionGroup" in g
+    assert "aten::batch_norm" not in g and "aten::dropout" not in g
+    inner = "".join(str(n.g("Subgraph")) for n in opt.graph.nodes() if n.kind() == "catch_b200::FusionGroup")
+    assert inner.count("catch_b200::conv_bn_act") == 3 and "catch_b200::linear_act" in inner
+    assert "aten::conv2d" not in inner and "aten::relu" not in inner.replace("relu_", "")
+    out = opt(x)
+    assert torch.allclose(out, ref, atol=1e-4), (out - ref).abs().max()
+    dev_out = opt.to(DEV)(x.to(DEV)) if False else None  # module.to on a frozen module is checked on the GPU
+    before = jit.fusion_stats()
+    opt(x); opt(torch.randn(3, 8, 12, 12))
+    after = jit.fusion_stats()
+    assert after["compiles"] >= before["compiles"] + 1  # a new shape compiles a new plan
+
+
+def test_fusion_toggle_and_forced_fallback():
+    m = torch.jit.script(Block().eval())
+    jit.set_fusion_enabled(False)
+    try:
+        assert not jit.fusion_enabled() and not torch.b200._jit_can_fuse_on_b200()
+        g = str(jit.optimize(m).graph)
+        assert "FusionGroup" not in g
+    finally:
+        torch.b200._jit_override_can_fuse_on_b200(True)
+    assert jit.fusion_enabled()
+
+
+def test_lowering_removes_exception_ifs_and_dropout():
+    @torch.jit.script
+    def f(x):
+        if x.dim() != 2:
+            raise RuntimeError("bad rank")
+        y = torch.nn.functional.dropout(x, 0.5, False)
+        return y.contiguous() + 1
+
+    g = f.graph
+    jit.lower_graph(g)
+    s = str(g)
+    assert "prim::RaiseException" not in s and "aten::dropout" not in s and "aten::contiguous" not in s
