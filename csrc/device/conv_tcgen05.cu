@@ -32,7 +32,9 @@ struct ConvArgs {
   int N, P, Q, Cin, Cout;
   int bw, bh, bni;              // pixel box (bw*bh*bni == 128)
   int tiles_q, tiles_p, tiles_n, tiles_co, tile_n;
-  int c_blocks;                 // Cin / 64 (rounded up)
+  int c_blocks;                 // Cin / cblk (rounded up)
+  int cblk;                     // input channels per 128-byte row: 64 (16-bit) or 128 (int8)
+  int kind;                     // 0 f16/bf16, 2 int8
   int ntaps, stages, b_mn;
   uint32_t idesc;
   B200ConvTap taps[B200_CONV_MAX_TAPS];
@@ -113,9 +115,9 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, g.err, ERR_TIMEOUT_EMPTY)) { failed = true; break; }
           mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)stage_bytes);
           uint8_t* sa = smem + (size_t)stage * stage_bytes;
-          tma_load_4d(sa, &maps.a[tp.map], &full_bar[stage], cb * 64, q0 + tp.dw, p0 + tp.dh, n0);
+          tma_load_4d(sa, &maps.a[tp.map], &full_bar[stage], cb * g.cblk, q0 + tp.dw, p0 + tp.dh, n0);
           if (!g.b_mn) {
-            tma_load_3d(sa + CONV_A_BYTES, &maps.w, &full_bar[stage], cb * 64, co0, tp.wtap);
+            tma_load_3d(sa + CONV_A_BYTES, &maps.w, &full_bar[stage], cb * g.cblk, co0, tp.wtap);
           } else {
             for (int j = 0; j < g.tile_n / 64; ++j)
               tma_load_3d(sa + CONV_A_BYTES + j * 8192, &maps.w, &full_bar[stage], co0 + j * 64, cb * 64, tp.wtap);
@@ -140,8 +142,11 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
           for (int k = 0; k < 4; ++k) {
             const uint64_t bdesc = g.b_mn ? make_smem_desc_sw128(sb + k * 2048, 8192, 1024)
                                           : make_smem_desc_sw128(sb + k * 32, 16, 1024);
-            umma_f16(d_tmem, make_smem_desc_sw128(sa + k * 32, 16, 1024), bdesc, g.idesc,
-                     (it > 0 || k > 0) ? 1u : 0u);
+            if (g.kind == 2)
+              umma_i8(d_tmem, make_smem_desc_sw128(sa + k * 32, 16, 1024), bdesc, g.idesc, (it > 0 || k > 0) ? 1u : 0u);
+            else
+              umma_f16(d_tmem, make_smem_desc_sw128(sa + k * 32, 16, 1024), bdesc, g.idesc,
+                       (it > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == g.stages) { stage = 0; phase ^= 1; }
@@ -188,7 +193,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
             const int cbase = co0 + c;
             float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rr[j]) * g.alpha;
+            for (int j = 0; j < 32; ++j) v[j] = (g.kind == 2 ? (float)(int)rr[j] : __uint_as_float(rr[j])) * g.alpha;
             if (g.scale) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) if (cbase + j < g.Cout) v[j] *= g.scale[cbase + j];
@@ -242,7 +247,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
         const int valid = min(32, g.Cout - cbase);
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rr[j]) * g.alpha;
+        for (int j = 0; j < 32; ++j) v[j] = (g.kind == 2 ? (float)(int)rr[j] : __uint_as_float(rr[j])) * g.alpha;
         if (g.scale) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) if (j < valid) v[j] *= g.scale[cbase + j];
@@ -472,9 +477,10 @@ static void pick_box(int total, int N, int P, int Q, int* bw, int* bh, int* bni)
   }
 }
 
-static int encode_view(CUtensorMap* m, const B200ConvView& v, CUtensorMapDataType dt, int boxc, int bw, int bh, int bni) {
+static int encode_view(CUtensorMap* m, const B200ConvView& v, CUtensorMapDataType dt, int boxc, int bw, int bh, int bni,
+                       int es = 2) {
   uint64_t dims[4] = {(uint64_t)v.dims[0], (uint64_t)v.dims[1], (uint64_t)v.dims[2], (uint64_t)v.dims[3]};
-  uint64_t str[3] = {(uint64_t)v.strides[0] * 2, (uint64_t)v.strides[1] * 2, (uint64_t)v.strides[2] * 2};
+  uint64_t str[3] = {(uint64_t)v.strides[0] * es, (uint64_t)v.strides[1] * es, (uint64_t)v.strides[2] * es};
   uint32_t box[4] = {(uint32_t)boxc, (uint32_t)bw, (uint32_t)bh, (uint32_t)bni};
   return encode_tiled(m, dt, 4, v.base, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
 }
@@ -494,8 +500,12 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p, void* stream) {
   if (p->N <= 0 || p->P <= 0 || p->Q <= 0 || p->Cout <= 0) return 0;
   if (p->ntaps <= 0 || p->ntaps > B200_CONV_MAX_TAPS || p->num_views <= 0 || p->num_views > B200_CONV_MAX_MAPS)
     return (int)cudaErrorInvalidValue;
-  if (p->Cin % 8 || p->ab_dtype == B200_F32) return (int)cudaErrorInvalidValue;
-  const CUtensorMapDataType dt = p->ab_dtype == B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const int es = p->ab_dtype == B200_I8 ? 1 : 2;
+  if ((p->Cin * es) % 16 || p->ab_dtype == B200_F32) return (int)cudaErrorInvalidValue;
+  const CUtensorMapDataType dt = p->ab_dtype == B200_I8    ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : p->ab_dtype == B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                           : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const CUtensorMapDataType out_dt = p->out_dtype == B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -520,11 +530,14 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p, void* stream) {
   if (g.b_mn && g.tile_n < 64) g.tile_n = 64;
   if (g.tile_n % 32 || g.tile_n > 256 || (g.b_mn && g.tile_n % 64)) return (int)cudaErrorInvalidValue;
   g.tiles_co = (p->Cout + g.tile_n - 1) / g.tile_n;
-  g.c_blocks = (p->Cin + 63) / 64;
+  g.cblk = 128 / es;
+  g.kind = es == 1 ? 2 : 0;
+  if (g.kind == 2 && g.b_mn) return (int)cudaErrorInvalidValue;
+  g.c_blocks = (p->Cin + g.cblk - 1) / g.cblk;
   g.ntaps = p->ntaps;
   for (int i = 0; i < p->ntaps; ++i) g.taps[i] = p->taps[i];
-  const int fmt = p->ab_dtype == B200_BF16 ? 1 : 0;
-  g.idesc = make_idesc(1, fmt, fmt, 0, g.b_mn, 128, g.tile_n);
+  const int fmt = (p->ab_dtype == B200_BF16 || p->ab_dtype == B200_I8) ? 1 : 0;
+  g.idesc = make_idesc(g.kind == 2 ? 2 : 1, fmt, fmt, 0, g.b_mn, 128, g.tile_n);
   g.out = p->out; g.out_dtype = p->out_dtype;
   g.o_sn = p->o_sn; g.o_sh = p->o_sh; g.o_sw = p->o_sw;
   g.o_mul_h = p->o_mul_h; g.o_off_h = p->o_off_h; g.o_mul_w = p->o_mul_w; g.o_off_w = p->o_off_w;
@@ -548,11 +561,11 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p, void* stream) {
     ov.base = static_cast<const char*>(p->out) + ((long long)p->o_off_h * p->o_sh + (long long)p->o_off_w * p->o_sw) * 2;
     ov.dims[0] = p->Cout; ov.dims[1] = p->Q; ov.dims[2] = p->P; ov.dims[3] = p->N;
     ov.strides[0] = p->o_sw * p->o_mul_w; ov.strides[1] = p->o_sh * p->o_mul_h; ov.strides[2] = p->o_sn;
-    int rc = encode_view(&maps.out, ov, dt, 64, g.bw, g.bh, g.bni);
+    int rc = encode_view(&maps.out, ov, out_dt, 64, g.bw, g.bh, g.bni);
     if (rc) return rc;
   }
   for (int i = 0; i < p->num_views; ++i) {
-    int rc = encode_view(&maps.a[i], p->views[i], dt, 64, g.bw, g.bh, g.bni);
+    int rc = encode_view(&maps.a[i], p->views[i], dt, g.cblk, g.bw, g.bh, g.bni, es);
     if (rc) return rc;
   }
   for (int i = p->num_views; i < B200_CONV_MAX_MAPS; ++i) maps.a[i] = maps.a[0];
@@ -560,8 +573,8 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p, void* stream) {
     int rc;
     if (!g.b_mn) {
       uint64_t dims[3] = {(uint64_t)p->Cin, (uint64_t)p->Cout, (uint64_t)p->wtaps};
-      uint64_t str[2] = {(uint64_t)p->w_stride_n * 2, (uint64_t)p->w_stride_tap * 2};
-      uint32_t box[3] = {64, (uint32_t)g.tile_n, 1};
+      uint64_t str[2] = {(uint64_t)p->w_stride_n * es, (uint64_t)p->w_stride_tap * es};
+      uint32_t box[3] = {(uint32_t)g.cblk, (uint32_t)g.tile_n, 1};
       rc = encode_tiled(&maps.w, dt, 3, p->weight, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
     } else {
       uint64_t dims[3] = {(uint64_t)p->Cout, (uint64_t)p->Cin, (uint64_t)p->wtaps};

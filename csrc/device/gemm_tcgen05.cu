@@ -34,7 +34,9 @@ constexpr int GEMM_ACC_STRIDE = 256;  // columns per accumulator buffer
 struct GemmKernelArgs {
   int M, N, K, batch;
   int tile_n, stages, k_blocks, tiles_m, tiles_n;
-  int elem_bytes;       // 2 or 4
+  int elem_bytes;       // 1 (int8), 2 or 4
+  int kind;             // 0 f16/bf16, 1 tf32, 2 int8
+  const float* col_scale;
   int a_mn, b_mn;
   uint32_t idesc;
   int mn_lbo, mn_sbo, mn_kstep;  // descriptor fields of MN-major operands (bytes)
@@ -149,7 +151,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
-      const bool tf32 = g.elem_bytes == 4;
       for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, g.err, ERR_TIMEOUT_TMEM_EMPTY)) { failed = true; break; }
         tc_fence_after();
@@ -166,7 +167,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint64_t bdesc = g.b_mn ? make_smem_desc_sw128(sb + k * g.mn_kstep, g.mn_lbo, g.mn_sbo)
                                           : make_smem_desc_sw128(sb + k * 32, 16, 1024);
             const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
-            if (tf32) umma_tf32(d_tmem, adesc, bdesc, g.idesc, accum);
+            if (g.kind == 1) umma_tf32(d_tmem, adesc, bdesc, g.idesc, accum);
+            else if (g.kind == 2) umma_i8(d_tmem, adesc, bdesc, g.idesc, accum);
             else umma_f16(d_tmem, adesc, bdesc, g.idesc, accum);
           }
           umma_commit(&empty_bar[stage]);  // frees the smem stage once the MMAs have read it
@@ -206,8 +208,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (!row_ok || n_base >= g.N) continue;
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * g.alpha;
+        for (int j = 0; j < 32; ++j) v[j] = (g.kind == 2 ? (float)(int)r[j] : __uint_as_float(r[j])) * g.alpha;
         const int valid = min(32, g.N - n_base);
+        if (g.col_scale) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < valid) v[j] *= g.col_scale[n_base + j];
+        }
         if (g.bias) {
           if (g.bias_per_row) {
 #pragma unroll
@@ -309,11 +316,13 @@ extern "C" int b200_gemm(const B200GemmParams* p, void* stream) {
   using namespace b200;
   if (p->M <= 0 || p->N <= 0 || p->batch <= 0) return 0;
   if (p->K <= 0) return (int)cudaErrorInvalidValue;
-  const int es = p->ab_dtype == B200_F32 ? 4 : 2;
+  const int es = p->ab_dtype == B200_F32 ? 4 : (p->ab_dtype == B200_I8 ? 1 : 2);
+  if (es == 1 && (p->a_mn_major || p->b_mn_major)) return (int)cudaErrorInvalidValue;  // int8 operands are K-major
   // fp32 operands run as tf32 and must be K-major (the host layer transposes).
   if (es == 4 && (p->a_mn_major || p->b_mn_major)) return (int)cudaErrorInvalidValue;
   const CUtensorMapDataType dt = p->ab_dtype == B200_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                  : p->ab_dtype == B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                 : p->ab_dtype == B200_I8  ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                                            : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   auto ok16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   if (!ok16(p->A) || !ok16(p->B) || (p->lda * es) % 16 || (p->ldb * es) % 16 || (p->stride_a * es) % 16 ||
@@ -336,8 +345,10 @@ extern "C" int b200_gemm(const B200GemmParams* p, void* stream) {
   g.tiles_n = (p->N + g.tile_n - 1) / g.tile_n;
   g.elem_bytes = es;
   g.a_mn = p->a_mn_major; g.b_mn = p->b_mn_major;
-  const int fmt = p->ab_dtype == B200_F32 ? 2 : (p->ab_dtype == B200_BF16 ? 1 : 0);
-  g.idesc = make_idesc(1, fmt, fmt, g.a_mn, g.b_mn, GEMM_BM, g.tile_n);
+  const int fmt = p->ab_dtype == B200_F32 ? 2 : ((p->ab_dtype == B200_BF16 || p->ab_dtype == B200_I8) ? 1 : 0);
+  g.kind = es == 4 ? 1 : (es == 1 ? 2 : 0);
+  g.col_scale = p->col_scale;
+  g.idesc = make_idesc(g.kind == 2 ? 2 : 1, fmt, fmt, g.a_mn, g.b_mn, GEMM_BM, g.tile_n);
   // MN-major: 8-row K groups are 1024 B apart, 128-byte MN blocks are one
   // k-block (bk rows x 128 B) apart, one MMA consumes 32 B of K = (32/es) rows.
   g.mn_sbo = g_dbg_sbo >= 0 ? g_dbg_sbo : 1024;

@@ -87,7 +87,7 @@ typedef struct B200GemmParams {
   int64_t lda, ldb, ldd;                 // elements
   int64_t stride_a, stride_b, stride_d;  // batch strides, elements
   int a_mn_major, b_mn_major;
-  int ab_dtype;                          // B200_BF16 / B200_F16 / B200_F32
+  int ab_dtype;                          // B200_BF16 / B200_F16 / B200_F32 (tf32) / B200_I8 (int32 accumulate)
   int d_dtype;                           // B200_BF16 / B200_F16 / B200_F32
   const void* bias;                      // optional
   int bias_dtype;                        // dtype of bias (f32 / bf16 / f16)
@@ -99,6 +99,7 @@ typedef struct B200GemmParams {
   int act;                               // 0 none, 1 relu, 2 gelu (erf)
   int tile_n;                            // 0 = choose automatically (32..256, multiple of 32)
   int max_ctas;                          // 0 = one per SM
+  const float* col_scale;                // optional fp32 multiplier per output column (applied after alpha)
 } B200GemmParams;
 B200_API int b200_gemm(const B200GemmParams* p, void* stream);
 // Test hook: override the MN-major descriptor fields (bytes); negative = default.
@@ -128,7 +129,7 @@ typedef struct B200ConvView {
 typedef struct B200ConvParams {
   int N, P, Q;           // pixel grid covered by this launch (tiles are boxes of it)
   int Cin, Cout;         // Cin: channels per tap seen by the kernel (multiple of 8)
-  int ab_dtype;          // B200_BF16 / B200_F16
+  int ab_dtype;          // B200_BF16 / B200_F16 / B200_I8 (signed, int32 accumulate; Cin multiple of 16)
   int num_views;
   B200ConvView views[B200_CONV_MAX_MAPS];
   int ntaps;
@@ -370,6 +371,16 @@ B200_API int b200_comm_wait(const B200CommCtx* ctx, int which, int peer /*-1 = a
 B200_API int b200_comm_copy(void* dst, const void* src, size_t bytes, void* stream);
 // dst[i] = op(dst[i], src[i]) for n elements (used by reduce / reduce_scatter pulls)
 B200_API int b200_comm_accumulate(void* dst, const void* src, long long n, int dtype, int op, void* stream);
+
+// ---- int8 quantisation -------------------------------------------------------------------------
+// q[i] = clamp(round_half_even(x[i] * scale), -127, 127) as int8 (per-tensor scale)
+B200_API int b200_quantize_int8(const void* x, int x_dtype, long long n, float scale, void* q, void* stream);
+// per-row (output-channel) symmetric weight quantisation of a dense [rows, cols] matrix:
+// scale[r] = 127 / max|w[r, :]| (1 if the row is all zero), q = round(w * scale[r])
+B200_API int b200_quantize_int8_rows(const void* w, int w_dtype, long long rows, long long cols, void* q, float* scale,
+                                     void* stream);
+// abs-max of a tensor into *out (fp32, must be zero-initialised; uses an atomic max on the bit pattern)
+B200_API int b200_absmax(const void* x, int x_dtype, long long n, float* out, void* stream);
 
 #ifdef __cplusplus
 }
