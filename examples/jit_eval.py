@@ -1,0 +1,20 @@
+"""Fusion-mode (TorchScript) ResNet-50 inference (counterpart of examples/inference/jit_eval.py)."""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import torch
+import torchvision
+
+import catch_b200  # noqa: F401
+from catch_b200 import jit
+
+dev = torch.device("blackwell", 0)
+model = torchvision.models.resnet50().eval()
+x = torch.randn(16, 3, 224, 224)
+traced = torch.jit.trace(model, x)
+fused = jit.optimize(traced).half().to(dev)
+with torch.no_grad():
+    out = fused(x.half().to(dev).contiguous(memory_format=torch.channels_last))
+print("fusion groups:", str(fused.graph).count("catch_b200::FusionGroup"), "top-1:", out.argmax(1).cpu().tolist())
+print(jit.fusion_stats())
