@@ -185,33 +185,36 @@ __device__ __forceinline__ C apply(C a, C b, C c, C s0, C s1) {
 }
 
 // ------------------------------------------------------------- generic kernel
-template <typename C, int OP>
+// IDX = unsigned (fast 32-bit index arithmetic, used whenever every offset fits) or
+// long long.
+template <typename C, int OP, typename IDX>
 __global__ void __launch_bounds__(256) ew_generic(const B200EwDesc d) {
-  const int64_t stride_t = (int64_t)gridDim.x * blockDim.x;
+  const IDX stride_t = (IDX)gridDim.x * blockDim.x;
   const C s0 = (C)d.scalar[0], s1 = (C)d.scalar[1];
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < d.numel; i += stride_t) {
-    int64_t off[B200_EW_MAX_OPERANDS] = {0, 0, 0, 0};
+  const IDX numel = (IDX)d.numel;
+  for (IDX i = (IDX)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += stride_t) {
+    IDX off[B200_EW_MAX_OPERANDS] = {0, 0, 0, 0};
     if (d.contiguous) {
 #pragma unroll
       for (int k = 0; k < B200_EW_MAX_OPERANDS; ++k) off[k] = i;
     } else {
-      int64_t rem = i;
+      IDX rem = i;
       for (int dim = 0; dim < d.ndim; ++dim) {
-        const int64_t sz = d.shape[dim];
-        const int64_t idx = rem % sz;
+        const IDX sz = (IDX)d.shape[dim];
+        const IDX idx = rem % sz;
         rem /= sz;
 #pragma unroll
-        for (int k = 0; k < B200_EW_MAX_OPERANDS; ++k) off[k] += idx * d.strides[k][dim];
+        for (int k = 0; k < B200_EW_MAX_OPERANDS; ++k) off[k] += idx * (IDX)d.strides[k][dim];
       }
     }
     C v[3] = {C(0), C(0), C(0)};
 #pragma unroll
     for (int k = 1; k < B200_EW_MAX_OPERANDS; ++k) {
       if (k < d.noperands) {
-        v[k - 1] = (d.scalar_mask >> k) & 1 ? (C)d.scalar_operand[k] : load_as<C>(d.ptr[k], off[k], d.dtype[k]);
+        v[k - 1] = (d.scalar_mask >> k) & 1 ? (C)d.scalar_operand[k] : load_as<C>(d.ptr[k], (int64_t)off[k], d.dtype[k]);
       }
     }
-    store_as<C>(d.ptr[0], off[0], d.dtype[0], apply<C, OP>(v[0], v[1], v[2], s0, s1));
+    store_as<C>(d.ptr[0], (int64_t)off[0], d.dtype[0], apply<C, OP>(v[0], v[1], v[2], s0, s1));
   }
 }
 
@@ -301,9 +304,24 @@ inline int grid_for(int64_t work, int block) {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// true when every element offset of every operand fits in 32 bits (strides are >= 0)
+inline bool fits_32bit(const B200EwDesc& d) {
+  if (d.numel >= 0xffffffffLL) return false;
+  for (int k = 0; k < d.noperands; ++k) {
+    long long span = 0;
+    for (int dim = 0; dim < d.ndim; ++dim) {
+      if (d.strides[k][dim] < 0) return false;
+      span += (d.shape[dim] - 1) * d.strides[k][dim];
+    }
+    if (span >= 0xffffffffLL) return false;
+  }
+  return true;
+}
+
 template <typename C, int OP>
 int launch_generic(const B200EwDesc& d, cudaStream_t s) {
-  ew_generic<C, OP><<<grid_for(d.numel, 256), 256, 0, s>>>(d);
+  if (fits_32bit(d)) ew_generic<C, OP, unsigned><<<grid_for(d.numel, 256), 256, 0, s>>>(d);
+  else ew_generic<C, OP, long long><<<grid_for(d.numel, 256), 256, 0, s>>>(d);
   return (int)cudaGetLastError();
 }
 

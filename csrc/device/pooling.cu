@@ -184,6 +184,95 @@ __global__ void adaptive_bwd_kernel(const B200PoolParams p, const T* dy, T* dx, 
   }
 }
 
+
+// ---- channels-last fast paths: one thread handles 8 consecutive channels ------------------
+template <typename T>
+__global__ void __launch_bounds__(256) maxpool_fwd_cl8_kernel(const B200PoolParams p, const T* __restrict__ x,
+                                                              T* __restrict__ y, long long* __restrict__ idx,
+                                                              unsigned total) {
+  const unsigned cv = p.C / 8;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    unsigned u = i;
+    const int c0 = (int)(u % cv) * 8; u /= cv;
+    const int ow = (int)(u % (unsigned)p.Q); u /= (unsigned)p.Q;
+    const int oh = (int)(u % (unsigned)p.P);
+    const int n = (int)(u / (unsigned)p.P);
+    const int h0 = max(oh * p.sh - p.ph, 0), w0 = max(ow * p.sw - p.pw, 0);
+    const int h1 = min(oh * p.sh - p.ph + p.kh, p.H), w1 = min(ow * p.sw - p.pw + p.kw, p.W);
+    float best[8];
+    int bi[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { best[k] = -INFINITY; bi[k] = h0 * p.W + w0; }
+    const T* xp = x + (size_t)n * p.in_s[0] + c0;
+    for (int h = h0; h < h1; ++h)
+      for (int w = w0; w < w1; ++w) {
+        alignas(16) T v[8];
+        *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(xp + (size_t)h * p.in_s[2] + (size_t)w * p.in_s[3]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float f = Cv<T>::to(v[k]);
+          if (f > best[k] || f != f) { best[k] = f; bi[k] = h * p.W + w; }
+        }
+      }
+    const size_t o = (size_t)n * p.out_s[0] + (size_t)oh * p.out_s[2] + (size_t)ow * p.out_s[3] + c0;
+    alignas(16) T r[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) r[k] = Cv<T>::from(best[k]);
+    *reinterpret_cast<uint4*>(y + o) = *reinterpret_cast<const uint4*>(r);
+    if (idx) {
+      alignas(16) long long li[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) li[k] = bi[k];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) reinterpret_cast<uint4*>(idx + o)[k] = reinterpret_cast<const uint4*>(li)[k];
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) maxpool_bwd_cl8_kernel(const B200PoolParams p, const T* __restrict__ dy,
+                                                              const long long* __restrict__ idx, T* __restrict__ dx,
+                                                              unsigned total) {
+  const unsigned cv = p.C / 8;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    unsigned u = i;
+    const int c0 = (int)(u % cv) * 8; u /= cv;
+    const int w = (int)(u % (unsigned)p.W); u /= (unsigned)p.W;
+    const int h = (int)(u % (unsigned)p.H);
+    const int n = (int)(u / (unsigned)p.H);
+    const int oh0 = (h + p.ph < p.kh) ? 0 : (h + p.ph - p.kh) / p.sh + 1;
+    const int ow0 = (w + p.pw < p.kw) ? 0 : (w + p.pw - p.kw) / p.sw + 1;
+    const int oh1 = min((h + p.ph) / p.sh + 1, p.P), ow1 = min((w + p.pw) / p.sw + 1, p.Q);
+    const long long me = (long long)h * p.W + w;
+    float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int oh = oh0; oh < oh1; ++oh)
+      for (int ow = ow0; ow < ow1; ++ow) {
+        const size_t o = (size_t)n * p.out_s[0] + (size_t)oh * p.out_s[2] + (size_t)ow * p.out_s[3] + c0;
+        alignas(16) long long li[8];
+        alignas(16) T v[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) reinterpret_cast<uint4*>(li)[k] = reinterpret_cast<const uint4*>(idx + o)[k];
+        *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(dy + o);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (li[k] == me) g[k] += Cv<T>::to(v[k]);
+      }
+    alignas(16) T r[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) r[k] = Cv<T>::from(g[k]);
+    *reinterpret_cast<uint4*>(dx + (size_t)n * p.in_s[0] + (size_t)h * p.in_s[2] + (size_t)w * p.in_s[3] + c0) =
+        *reinterpret_cast<const uint4*>(r);
+  }
+}
+
+// channels-last, 16-bit, C % 8 == 0, unit dilation, 16-byte aligned rows
+inline bool cl8_ok(const B200PoolParams* p, const void* a, const void* b, long long total) {
+  return p->channels_last && p->dtype != B200_F32 && p->C % 8 == 0 && p->dh == 1 && p->dw == 1 && p->in_s[1] == 1 &&
+         p->out_s[1] == 1 && p->in_s[3] % 8 == 0 && p->in_s[2] % 8 == 0 && p->in_s[0] % 8 == 0 && p->out_s[3] % 8 == 0 &&
+         p->out_s[2] % 8 == 0 && p->out_s[0] % 8 == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0 &&
+         total / 8 < 0xffffffffLL;
+}
+
 inline int grid_for(long long n) {
   long long g = (n + 255) / 256;
   if (g > 148 * 32) g = 148 * 32;
@@ -203,6 +292,16 @@ inline int grid_for(long long n) {
 extern "C" int b200_maxpool2d_fwd(const B200PoolParams* p, const void* x, void* y, long long* idx, void* stream) {
   const long long total = (long long)p->N * p->C * p->P * p->Q;
   if (total <= 0) return 0;
+  if (cl8_ok(p, x, y, total) && (!idx || (reinterpret_cast<uintptr_t>(idx) & 15) == 0)) {
+    const unsigned tv = (unsigned)(total / 8);
+    if (p->dtype == B200_BF16)
+      maxpool_fwd_cl8_kernel<__nv_bfloat16><<<grid_for(tv), 256, 0, (cudaStream_t)stream>>>(
+          *p, static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), idx, tv);
+    else
+      maxpool_fwd_cl8_kernel<__half><<<grid_for(tv), 256, 0, (cudaStream_t)stream>>>(
+          *p, static_cast<const __half*>(x), static_cast<__half*>(y), idx, tv);
+    return (int)cudaGetLastError();
+  }
   POOL_DISPATCH(p->dtype, T, (maxpool_fwd_kernel<T><<<grid_for(total), 256, 0, (cudaStream_t)stream>>>(
                                  *p, static_cast<const T*>(x), static_cast<T*>(y), idx, total)));
   return (int)cudaGetLastError();
@@ -210,6 +309,16 @@ extern "C" int b200_maxpool2d_fwd(const B200PoolParams* p, const void* x, void* 
 extern "C" int b200_maxpool2d_bwd(const B200PoolParams* p, const void* dy, const long long* idx, void* dx, void* stream) {
   const long long total = (long long)p->N * p->C * p->H * p->W;
   if (total <= 0) return 0;
+  if (cl8_ok(p, dx, dy, total) && (reinterpret_cast<uintptr_t>(idx) & 15) == 0) {
+    const unsigned tv = (unsigned)(total / 8);
+    if (p->dtype == B200_BF16)
+      maxpool_bwd_cl8_kernel<__nv_bfloat16><<<grid_for(tv), 256, 0, (cudaStream_t)stream>>>(
+          *p, static_cast<const __nv_bfloat16*>(dy), idx, static_cast<__nv_bfloat16*>(dx), tv);
+    else
+      maxpool_bwd_cl8_kernel<__half><<<grid_for(tv), 256, 0, (cudaStream_t)stream>>>(
+          *p, static_cast<const __half*>(dy), idx, static_cast<__half*>(dx), tv);
+    return (int)cudaGetLastError();
+  }
   POOL_DISPATCH(p->dtype, T, (maxpool_bwd_kernel<T><<<grid_for(total), 256, 0, (cudaStream_t)stream>>>(
                                  *p, static_cast<const T*>(dy), idx, static_cast<T*>(dx), total)));
   return (int)cudaGetLastError();
