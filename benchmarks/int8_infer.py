@@ -1,0 +1,70 @@
+"""ResNet-50 post-training int8 inference, batch 128, one GPU.
+
+    python benchmarks/int8_infer.py [--batch 128] [--iters 20]
+
+Per-channel symmetric int8 weights, per-tensor activation scales calibrated on 8
+batches of 32 N(0,1) inputs (seed 1); evaluation on fresh N(0,1) inputs.  Reports
+images/sec of the int8 model and of the fp16 eager model on this backend, and the
+top-1 agreement between them.
+"""
+import argparse
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import torch
+import torchvision
+
+import catch_b200  # noqa: F401
+from catch_b200.quantize import quantize_dynamic
+
+
+def bench(fn, iters):
+    for _ in range(3):
+        out = fn()
+    torch.b200.synchronize()
+    a, b = torch.b200.Notifier(), torch.b200.Notifier()
+    a.place()
+    for _ in range(iters):
+        out = fn()
+    b.place()
+    torch.b200.synchronize()
+    return a.elapsed_time(b) / iters, out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=128)
+    ap.add_argument("--iters", type=int, default=20)
+    args = ap.parse_args()
+    dev = torch.device("blackwell", 0)
+    torch.manual_seed(0)
+    model = torchvision.models.resnet50().eval()
+    mixed = {"conv1": "float"}  # the 3-channel first layer stays in floating point
+    calib = quantize_dynamic(model, {"per_channel": True, "iteration": 8}, dtype="int8", gen_quant=True, mixed_layer=mixed)
+    calib = calib.half().to(dev).to(memory_format=torch.channels_last)
+    g = torch.Generator().manual_seed(1)
+    with torch.no_grad():
+        for _ in range(8):
+            calib(torch.randn(32, 3, 224, 224, generator=g).half().to(dev))
+    sd = {k: v.cpu() for k, v in calib.state_dict().items()}
+    qmodel = quantize_dynamic(model, mixed_layer=mixed)
+    qmodel.load_state_dict(sd, strict=False)
+    qmodel = qmodel.half().to(dev).to(memory_format=torch.channels_last)
+    fmodel = torchvision.models.resnet50().eval()
+    fmodel.load_state_dict({k: v for k, v in model.state_dict().items()})
+    fmodel = fmodel.half().to(dev).to(memory_format=torch.channels_last)
+    x = torch.randn(args.batch, 3, 224, 224, generator=torch.Generator().manual_seed(2)).half().to(dev)
+    x = x.contiguous(memory_format=torch.channels_last)
+    with torch.no_grad():
+        ms_q, out_q = bench(lambda: qmodel(x), args.iters)
+        ms_f, out_f = bench(lambda: fmodel(x), args.iters)
+    agree = (out_q.argmax(1) == out_f.argmax(1)).float().mean().item()
+    rel = ((out_q.float() - out_f.float()).norm() / out_f.float().norm()).item()
+    nq = sum(1 for m in qmodel.modules() if getattr(m, "is_quantized", lambda: False)())
+    print(f"int8: {ms_q:.3f} ms, {args.batch / ms_q * 1e3:.1f} images/sec ({nq} quantized layers); "
+          f"fp16: {ms_f:.3f} ms, {args.batch / ms_f * 1e3:.1f} images/sec; top-1 agreement {agree:.3f}, rel-RMS {rel:.3e}")
+
+
+if __name__ == "__main__":
+    main()

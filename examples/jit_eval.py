@@ -10,11 +10,12 @@ import catch_b200  # noqa: F401
 from catch_b200 import jit
 
 dev = torch.device("blackwell", 0)
-model = torchvision.models.resnet50().eval()
-x = torch.randn(16, 3, 224, 224)
-traced = torch.jit.trace(model, x)
-fused = jit.optimize(traced).half().to(dev)
+# move first, then trace and freeze: freezing turns the weights into graph constants
+model = torchvision.models.resnet50().eval().half().to(dev).to(memory_format=torch.channels_last)
+x = torch.randn(16, 3, 224, 224).half().to(dev).contiguous(memory_format=torch.channels_last)
 with torch.no_grad():
-    out = fused(x.half().to(dev).contiguous(memory_format=torch.channels_last))
+    traced = torch.jit.trace(model, x)
+    fused = jit.optimize(traced)
+    out = fused(x)
 print("fusion groups:", str(fused.graph).count("catch_b200::FusionGroup"), "top-1:", out.argmax(1).cpu().tolist())
 print(jit.fusion_stats())
