@@ -105,6 +105,7 @@ def main():
     import torchvision
 
     import catch_b200  # noqa: F401
+    from catch_b200.fusion import fuse_bn_act
     from catch_b200.parallel import FusedDataParallel
 
     rank = int(os.environ.get("RANK", "0"))
@@ -120,6 +121,7 @@ def main():
 
     torch.manual_seed(0)
     model = getattr(torchvision.models, args.model)(weights=None)
+    model = fuse_bn_act(model)  # same parameters / state dict; BN(+add)+ReLU chains run as fused kernels
     model = model.to(dev).to(memory_format=torch.channels_last)
     grad_dtype = torch.bfloat16 if args.grad_dtype == "bf16" else torch.float32
     fdp = FusedDataParallel(model, "sgd", lr=0.1, momentum=0.9, weight_decay=1e-4, bucket_mb=25.0, grad_dtype=grad_dtype)
@@ -195,7 +197,7 @@ def main():
             "dtype": "bf16", "data": "synthetic N(0,1) images, uniform labels, random-init weights",
             "config": {"model": args.model, "global_batch": world * B, "per_gpu_batch": B, "image": "3x224x224",
                        "optimizer": "SGD(momentum 0.9, lr 0.1, wd 1e-4)", "bucket_mb": 25,
-                       "parallelism": f"dp{world}", "memory_format": "channels_last", "grad_allreduce_dtype": args.grad_dtype,
+                       "parallelism": f"dp{world}", "memory_format": "channels_last", "module_fusion": "catch_b200.fusion.fuse_bn_act", "grad_allreduce_dtype": args.grad_dtype,
                        "l2_note": "per-step inputs (154 MB) and activations exceed the 126 MB L2"},
             "clocks": clocks, "gpu_launches": int(launches),
             "e2e": {"value": round(ips_e2e, 1), "unit": "images/sec", "ms_per_step": round(ms_e2e / args.steps, 3),

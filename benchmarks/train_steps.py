@@ -24,6 +24,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--image", type=int, default=224)
     ap.add_argument("--stock", action="store_true")
+    ap.add_argument("--no-fuse", action="store_true", help="do not fuse BN+ReLU chains with catch_b200.fusion.fuse_bn_act")
     args = ap.parse_args()
     torch.manual_seed(0)
     model = getattr(torchvision.models, args.model)(weights=None)
@@ -51,7 +52,11 @@ def main():
         import catch_b200  # noqa: F401
         from catch_b200.parallel import FusedDataParallel
 
+        from catch_b200.fusion import fuse_bn_act
+
         dev = torch.device("blackwell", 0)
+        if not args.no_fuse:
+            model = fuse_bn_act(model)
         model = model.to(dev).to(memory_format=torch.channels_last)
         fdp = FusedDataParallel(model, "sgd", lr=0.1, momentum=0.9, weight_decay=1e-4)
         x, y = x.to(dev).contiguous(memory_format=torch.channels_last), y.to(dev)

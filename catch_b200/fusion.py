@@ -1,0 +1,129 @@
+"""Training-time module fusion: batch norm + (residual add) + ReLU in one kernel pair.
+
+    model = catch_b200.fusion.fuse_bn_act(model)      # torch.fx rewrite, same state_dict
+
+Every ``BatchNorm2d -> ReLU`` and ``BatchNorm2d -> add(residual) -> ReLU`` chain of an
+fx-traceable model (torchvision ResNets are) is replaced by ``BatchNormAct2d``, a
+``BatchNorm2d`` subclass (same parameters and buffers, same state-dict keys) whose
+forward calls ``torch.ops.catch_b200.batch_norm_act``: the normalisation, the residual
+add and the ReLU are applied in one pass over the activation, and the backward masks
+the gradient inside the batch-norm reduction and apply kernels instead of running a
+separate ReLU backward.  The reference has no counterpart (its fusion exists only in
+inference mode); on B200 the batch-norm and activation passes are memory-bound and
+dominate a ResNet step, which is why they are fused here.
+"""
+from __future__ import annotations
+
+import operator
+from typing import Optional
+
+import torch
+import torch.fx as fx
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+class _BNActFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, running_mean, running_var, residual, training, momentum, eps, act):
+        out, mean, invstd = torch.ops.catch_b200.batch_norm_act(x, weight, bias, running_mean, running_var, residual,
+                                                                training, momentum, eps, act)
+        ctx.save_for_backward(out, x, weight, running_mean, mean, invstd)
+        ctx.cfg = (training, act, residual is not None)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        out, x, weight, running_mean, mean, invstd = ctx.saved_tensors
+        training, act, has_res = ctx.cfg
+        dx, dgamma, dbeta, dres = torch.ops.catch_b200.batch_norm_act_backward(
+            grad_out, out, x, weight, running_mean, mean, invstd, training, act, has_res)
+        return (dx, dgamma if weight is not None else None, dbeta if weight is not None else None, None, None,
+                dres if has_res else None, None, None, None, None)
+
+
+def _device_kernels_available(x: torch.Tensor) -> bool:
+    return x.device.type == "blackwell" and not torch.b200.is_hostsim()
+
+
+class BatchNormAct2d(nn.BatchNorm2d):
+    """``BatchNorm2d`` followed by an optional residual add and ReLU, fused on the device."""
+
+    act: int = 1
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        training = self.training or (self.running_mean is None and self.running_var is None)
+        momentum = 0.0 if self.momentum is None else self.momentum
+        if self.training and self.track_running_stats and self.num_batches_tracked is not None:
+            self.num_batches_tracked.add_(1)
+            if self.momentum is None:
+                momentum = 1.0 / float(self.num_batches_tracked)
+        rm = self.running_mean if (not self.training or self.track_running_stats) else None
+        rv = self.running_var if (not self.training or self.track_running_stats) else None
+        c_vec = 4 if x.dtype == torch.float32 else 8
+        if (_device_kernels_available(x) and x.dim() == 4 and x.shape[1] % c_vec == 0
+                and x.dtype in (torch.float32, torch.bfloat16, torch.float16) and x.numel() > 0
+                and (residual is None or (residual.shape == x.shape and residual.dtype == x.dtype))):
+            return _BNActFn.apply(x, self.weight, self.bias, rm, rv, residual, training, momentum, self.eps, self.act)
+        y = F.batch_norm(x, rm, rv, self.weight, self.bias, training, momentum, self.eps)
+        if residual is not None:
+            y = y + residual
+        return F.relu(y) if self.act == 1 else y
+
+
+def _is_relu(node: fx.Node, modules) -> bool:
+    if node.op == "call_module":
+        return isinstance(modules[node.target], nn.ReLU)
+    if node.op == "call_function":
+        return node.target in (F.relu, torch.relu, torch.relu_)
+    if node.op == "call_method":
+        return node.target in ("relu", "relu_")
+    return False
+
+
+def _is_add(node: fx.Node) -> bool:
+    if node.op == "call_function" and node.target in (operator.add, operator.iadd, torch.add):
+        return len(node.args) == 2 and all(isinstance(a, fx.Node) for a in node.args) and not node.kwargs
+    if node.op == "call_method" and node.target in ("add", "add_"):
+        return len(node.args) == 2 and all(isinstance(a, fx.Node) for a in node.args) and not node.kwargs
+    return False
+
+
+def fuse_bn_act(model: nn.Module) -> fx.GraphModule:
+    """Return an fx GraphModule of ``model`` with BN(+add)+ReLU chains fused (see module docstring)."""
+    gm = fx.symbolic_trace(model)
+    modules = dict(gm.named_modules())
+    fused = 0
+    for node in list(gm.graph.nodes):
+        if node.op != "call_module" or type(modules[node.target]) is not nn.BatchNorm2d:
+            continue
+        if len(node.users) != 1:
+            continue
+        user = next(iter(node.users))
+        residual, relu_node, add_node = None, None, None
+        if _is_relu(user, modules):
+            relu_node = user
+        elif _is_add(user) and len(user.users) == 1 and _is_relu(next(iter(user.users)), modules):
+            add_node, relu_node = user, next(iter(user.users))
+            residual = user.args[1] if user.args[0] is node else user.args[0]
+            if residual is node:
+                continue
+        else:
+            continue
+        bn = modules[node.target]
+        bn.__class__ = BatchNormAct2d
+        bn.act = 1
+        # the residual must be computed before the fused node: place the fused call where the ReLU was
+        with gm.graph.inserting_before(relu_node):
+            args = (node.args[0],) if residual is None else (node.args[0], residual)
+            new = gm.graph.call_module(node.target, args)
+        relu_node.replace_all_uses_with(new)
+        gm.graph.erase_node(relu_node)
+        if add_node is not None:
+            gm.graph.erase_node(add_node)
+        gm.graph.erase_node(node)
+        fused += 1
+    gm.graph.lint()
+    gm.recompile()
+    gm.fused_bn_act_count = fused
+    return gm

@@ -205,11 +205,13 @@ B200_API int b200_bn_backward_reduce(const void* dy, int dy_dtype, const void* x
                                      int mean_dtype, const float* invstd, const void* relu_out, int relu_dtype,
                                      long long rows, int C, double* sums, void* stream);
 // dx = gamma*invstd*(dy - sum_dy/rows - xhat*sum_dy_xhat/rows) (training) or gamma*invstd*dy (eval);
-// writes dgamma / dbeta (fp32) when non-null.
+// writes dgamma / dbeta (fp32) when non-null; `dres` (optional, same dtype as dy) receives the relu-masked dy,
+// i.e. the gradient of a residual input that was added before the fused ReLU.
 B200_API int b200_bn_backward_apply(const void* dy, int dy_dtype, const void* x, int x_dtype, const void* mean,
                                     int mean_dtype, const float* invstd, const void* gamma, int param_dtype,
                                     const void* relu_out, int relu_dtype, const double* sums, long long rows, int C,
-                                    int training, void* dx, int dx_dtype, float* dgamma, float* dbeta, void* stream);
+                                    int training, void* dx, int dx_dtype, float* dgamma, float* dbeta, void* dres,
+                                    void* stream);
 
 // ---- layer norm over the last dimension ---------------------------------------------------
 B200_API int b200_layernorm_fwd(const void* x, int dtype, long long rows, int cols, const void* gamma, const void* beta,

@@ -285,7 +285,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 bn_bwd_apply_fast_kernel(const T* __restrict__ dy, const T* __restrict__ x, const void* mean, int mdt,
                          const float* invstd, const void* gamma, int pdt, const T* __restrict__ relu_out,
-                         const double* sums, long long rows, int C, int training, T* __restrict__ dx, unsigned nvec) {
+                         const double* sums, long long rows, int C, int training, T* __restrict__ dx, unsigned nvec,
+                         T* __restrict__ dres) {
   constexpr int V = VecOf<T>::N;
   extern __shared__ float coef[];
   float* A = coef;
@@ -312,13 +313,15 @@ bn_bwd_apply_fast_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
     float g[V], v[V], o[V];
     load_vec<T>(dy + (size_t)i * V, g);
     load_vec<T>(x + (size_t)i * V, v);
-    if (relu_out) load_vec<T>(relu_out + (size_t)i * V, o);
+    if (relu_out) {
+      load_vec<T>(relu_out + (size_t)i * V, o);
 #pragma unroll
-    for (int k = 0; k < V; ++k) {
-      float gi = g[k];
-      if (relu_out && !(o[k] > 0.f)) gi = 0.f;
-      g[k] = fmaf(A[c0 + k], gi, fmaf(B[c0 + k], v[k], D[c0 + k]));
+      for (int k = 0; k < V; ++k)
+        if (!(o[k] > 0.f)) g[k] = 0.f;
     }
+    if (dres) store_vec<T>(dres + (size_t)i * V, g);  // gradient of the fused residual input: the masked dy
+#pragma unroll
+    for (int k = 0; k < V; ++k) g[k] = fmaf(A[c0 + k], g[k], fmaf(B[c0 + k], v[k], D[c0 + k]));
     store_vec<T>(dx + (size_t)i * V, g);
   }
 }
@@ -520,18 +523,20 @@ extern "C" int b200_bn_backward_reduce(const void* dy, int dt, const void* x, in
 extern "C" int b200_bn_backward_apply(const void* dy, int dt, const void* x, int xdt, const void* mean, int mdt,
                                       const float* invstd, const void* gamma, int pdt, const void* relu_out, int rdt,
                                       const double* sums, long long rows, int C, int training, void* dx, int dxdt,
-                                      float* dgamma, float* dbeta, void* stream) {
+                                      float* dgamma, float* dbeta, void* dres, void* stream) {
   if (rows <= 0 || C <= 0) return 0;
   if (dt != xdt || (relu_out && rdt != dt)) return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   const long long n = rows * C;
+  if (dres && !(dx && dxdt == dt && C <= 8192 && C % (dt == B200_F32 ? 4 : 8) == 0)) return (int)cudaErrorInvalidValue;
   if (dx && dxdt == dt && C <= 8192 && C % (dt == B200_F32 ? 4 : 8) == 0 && n / (dt == B200_F32 ? 4 : 8) < 0xffffffffLL) {
     const int V = dt == B200_F32 ? 4 : 8;
     const unsigned nvec = (unsigned)(n / V);
     const size_t sm = sizeof(float) * 3 * C;
     DISPATCH_FLOAT(dt, T, (bn_bwd_apply_fast_kernel<T><<<ew_grid_u(nvec), 256, sm, s>>>(
                                static_cast<const T*>(dy), static_cast<const T*>(x), mean, mdt, invstd, gamma, pdt,
-                               static_cast<const T*>(relu_out), sums, rows, C, training, static_cast<T*>(dx), nvec)));
+                               static_cast<const T*>(relu_out), sums, rows, C, training, static_cast<T*>(dx), nvec,
+                               static_cast<T*>(dres))));
     dx = nullptr;  // done
   }
   if (dx) {

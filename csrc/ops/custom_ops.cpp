@@ -25,6 +25,16 @@ void fused_adamw_step(at::TensorList params, at::TensorList grads, at::TensorLis
                       at::TensorList lowp, double lr, double beta1, double beta2, double eps, double weight_decay,
                       int64_t step, double grad_scale, bool adam_l2_mode);
 bool dump_tensor_device(const at::Tensor& t);
+std::tuple<at::Tensor, at::Tensor, at::Tensor> batch_norm_act(const at::Tensor& input, const std::optional<at::Tensor>& weight,
+                                                              const std::optional<at::Tensor>& bias,
+                                                              const std::optional<at::Tensor>& running_mean,
+                                                              const std::optional<at::Tensor>& running_var,
+                                                              const std::optional<at::Tensor>& residual, bool training,
+                                                              double momentum, double eps, int64_t act);
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_backward(
+    const at::Tensor& grad_out, const at::Tensor& out, const at::Tensor& input, const std::optional<at::Tensor>& weight,
+    const std::optional<at::Tensor>& running_mean, const at::Tensor& save_mean, const at::Tensor& save_invstd, bool training,
+    int64_t act, bool has_residual);
 
 // act(conv(x, w) * scale + bias + residual); runs the fused tcgen05 kernel when it
 // can, otherwise composes stock ops (which themselves dispatch to this backend).
@@ -63,6 +73,10 @@ TORCH_LIBRARY(catch_b200, m) {
   m.def("fused_adamw_step(Tensor[] params, Tensor[] grads, Tensor[] exp_avg, Tensor[] exp_avg_sq, Tensor[] lowp, float lr, "
         "float beta1, float beta2, float eps, float weight_decay, int step, float grad_scale, bool adam_l2_mode) -> ()");
   m.def("dump(Tensor t) -> bool");
+  m.def("batch_norm_act(Tensor input, Tensor? weight, Tensor? bias, Tensor(a!)? running_mean, Tensor(b!)? running_var, "
+        "Tensor? residual, bool training, float momentum, float eps, int act) -> (Tensor, Tensor, Tensor)");
+  m.def("batch_norm_act_backward(Tensor grad_out, Tensor out, Tensor input, Tensor? weight, Tensor? running_mean, "
+        "Tensor save_mean, Tensor save_invstd, bool training, int act, bool has_residual) -> (Tensor, Tensor, Tensor, Tensor)");
 }
 
 TORCH_LIBRARY_IMPL(catch_b200, CompositeExplicitAutograd, m) {
@@ -72,6 +86,8 @@ TORCH_LIBRARY_IMPL(catch_b200, CompositeExplicitAutograd, m) {
   m.impl("fused_sgd_step", TORCH_FN(fused_sgd_step));
   m.impl("fused_adamw_step", TORCH_FN(fused_adamw_step));
   m.impl("dump", TORCH_FN(dump_tensor_device));
+  m.impl("batch_norm_act", TORCH_FN(batch_norm_act));
+  m.impl("batch_norm_act_backward", TORCH_FN(batch_norm_act_backward));
 }
 
 }  // namespace ops

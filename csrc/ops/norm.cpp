@@ -192,7 +192,7 @@ std::tuple<Tensor, Tensor, Tensor> batch_norm_backward_device(
                                            invstd_t.data_ptr<float>(), gamma, pdt, nullptr, 0, sums.data_ptr<double>(),
                                            xv.rows, C, train ? 1 : 0, dx.defined() ? dx.data_ptr() : nullptr, xdt,
                                            dgamma.defined() ? dgamma.data_ptr<float>() : nullptr,
-                                           dbeta.defined() ? dbeta.data_ptr<float>() : nullptr, scope.stream()));
+                                           dbeta.defined() ? dbeta.data_ptr<float>() : nullptr, nullptr, scope.stream()));
   if (weight.has_value() && weight->defined() && weight->scalar_type() != at::kFloat) {
     if (dgamma.defined()) dgamma = dgamma.to(weight->scalar_type());
     if (dbeta.defined()) dbeta = dbeta.to(weight->scalar_type());
@@ -212,6 +212,126 @@ std::tuple<Tensor, Tensor, Tensor> k_native_batch_norm_backward(
                                 save_mean, save_invstd, train, eps, mask));
 }
 
+
+// ---------------------------------------------------------------- fused BN + act
+// out = act(batch_norm(x) + residual); act 1 = ReLU.  Training statistics and running
+// statistics behave exactly like native_batch_norm.  The backward masks the incoming
+// gradient with out > 0 inside the reduction and apply kernels, so neither the ReLU nor
+// the residual add costs a pass over the activation.
+}  // namespace
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> batch_norm_act(const at::Tensor& input, const std::optional<at::Tensor>& weight,
+                                                              const std::optional<at::Tensor>& bias,
+                                                              const std::optional<at::Tensor>& running_mean,
+                                                              const std::optional<at::Tensor>& running_var,
+                                                              const std::optional<at::Tensor>& residual, bool training,
+                                                              double momentum, double eps, int64_t act) {
+  const bool has_res = residual.has_value() && residual->defined();
+  auto compose = [&]() {
+    auto r = at::native_batch_norm(input, weight, bias, running_mean, running_var, training, momentum, eps);
+    at::Tensor y = std::get<0>(r);
+    if (has_res) y = y + *residual;
+    if (act == 1) y = at::relu(y);
+    return std::make_tuple(y, std::get<1>(r), std::get<2>(r));
+  };
+  const int vec = input.scalar_type() == at::kFloat ? 4 : 8;
+  if (use_cpu_path() || !is_b200(input) || !bn_dtype_ok(input.scalar_type()) || input.dim() < 2 || input.size(1) % vec != 0 ||
+      input.numel() == 0 || (has_res && (residual->scalar_type() != input.scalar_type() || residual->sizes() != input.sizes())))
+    return compose();
+  OpScope scope("batch_norm_act", input);
+  RowsView v = rows_view(input);
+  const int C = (int)v.C;
+  at::Tensor out = like_rows(v, input, input.scalar_type());
+  at::Tensor res;
+  if (has_res) {
+    res = at::empty_strided(v.t.sizes(), v.t.strides(), residual->options());
+    if (residual->sizes() == v.t.sizes() && residual->strides() == v.t.strides()) res = *residual;
+    else res.copy_(*residual);
+  }
+  auto fopt = input.options().dtype(at::kFloat);
+  at::Tensor wk, bk;
+  const void* gamma = opt_ptr(weight, wk);
+  const void* beta = opt_ptr(bias, bk);
+  const int pdt = gamma ? to_b200_dtype(wk.scalar_type()) : (beta ? to_b200_dtype(bk.scalar_type()) : B200_F32);
+  const int xdt = to_b200_dtype(input.scalar_type());
+  at::Tensor save_mean, save_invstd;
+  const void* mean_ptr;
+  int mdt = B200_F32;
+  at::Tensor rmk;
+  if (training) {
+    save_mean = at::empty({C}, fopt);
+    save_invstd = at::empty({C}, fopt);
+    at::Tensor sums = at::zeros({2 * C}, input.options().dtype(at::kDouble));
+    B200_KERNEL_CHECK(b200_bn_stats(v.t.data_ptr(), xdt, v.rows, C, sums.data_ptr<double>(), scope.stream()));
+    void* rm = nullptr;
+    void* rv = nullptr;
+    int rdt = B200_F32;
+    if (running_mean.has_value() && running_mean->defined()) {
+      rm = running_mean->data_ptr();
+      rv = running_var->data_ptr();
+      rdt = to_b200_dtype(running_mean->scalar_type());
+    }
+    B200_KERNEL_CHECK(b200_bn_finalize(sums.data_ptr<double>(), v.rows, C, (float)eps, (float)momentum,
+                                       save_mean.data_ptr<float>(), save_invstd.data_ptr<float>(), rm, rv, rdt, scope.stream()));
+    mean_ptr = save_mean.data_ptr();
+  } else {
+    TORCH_CHECK(running_mean.has_value() && running_mean->defined(), "batch_norm_act: running statistics required in eval mode");
+    save_mean = at::empty({0}, fopt);
+    save_invstd = at::empty({C}, fopt);  // kept for the backward of frozen batch norm
+    rmk = running_mean->contiguous();
+    at::Tensor rv = running_var->contiguous();
+    B200_KERNEL_CHECK(b200_bn_invstd_from_var(rv.data_ptr(), to_b200_dtype(rv.scalar_type()), C, (float)eps,
+                                              save_invstd.data_ptr<float>(), scope.stream()));
+    mean_ptr = rmk.data_ptr();
+    mdt = to_b200_dtype(rmk.scalar_type());
+  }
+  B200_KERNEL_CHECK(b200_bn_apply(v.t.data_ptr(), xdt, out.data_ptr(), xdt, v.rows, C, mean_ptr, mdt,
+                                  save_invstd.data_ptr<float>(), gamma, beta, pdt, has_res ? res.data_ptr() : nullptr, xdt,
+                                  (int)act, scope.stream()));
+  return {out, save_mean, save_invstd};
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_backward(
+    const at::Tensor& grad_out, const at::Tensor& out, const at::Tensor& input, const std::optional<at::Tensor>& weight,
+    const std::optional<at::Tensor>& running_mean, const at::Tensor& save_mean, const at::Tensor& save_invstd, bool training,
+    int64_t act, bool has_residual) {
+  TORCH_CHECK(!use_cpu_path() && is_b200(input), "batch_norm_act_backward runs on the device only");
+  OpScope scope("batch_norm_act_backward", input);
+  RowsView xv = rows_view(input);
+  const int C = (int)xv.C;
+  auto same_layout = [&](const at::Tensor& t) {
+    if (t.sizes() == xv.t.sizes() && t.strides() == xv.t.strides()) return t;
+    return at::empty_strided(xv.t.sizes(), xv.t.strides(), t.options()).copy_(t);
+  };
+  at::Tensor dy = same_layout(grad_out), y = same_layout(out);
+  auto fopt = input.options().dtype(at::kFloat);
+  at::Tensor wk;
+  const void* gamma = opt_ptr(weight, wk);
+  const int pdt = gamma ? to_b200_dtype(wk.scalar_type()) : B200_F32;
+  const int xdt = to_b200_dtype(input.scalar_type());
+  at::Tensor mean_t = training ? save_mean.contiguous() : running_mean->contiguous();
+  const int mdt = to_b200_dtype(mean_t.scalar_type());
+  at::Tensor invstd = save_invstd.contiguous();
+  at::Tensor dx = at::empty_strided(xv.t.sizes(), xv.t.strides(), input.options());
+  at::Tensor dres = has_residual ? at::empty_strided(xv.t.sizes(), xv.t.strides(), input.options()) : at::Tensor();
+  at::Tensor dgamma = at::empty({C}, fopt), dbeta = at::empty({C}, fopt);
+  at::Tensor sums = at::zeros({2 * C}, input.options().dtype(at::kDouble));
+  const void* mask = act == 1 ? y.data_ptr() : nullptr;
+  B200_KERNEL_CHECK(b200_bn_backward_reduce(dy.data_ptr(), xdt, xv.t.data_ptr(), xdt, mean_t.data_ptr(), mdt,
+                                            invstd.data_ptr<float>(), mask, xdt, xv.rows, C, sums.data_ptr<double>(),
+                                            scope.stream()));
+  B200_KERNEL_CHECK(b200_bn_backward_apply(dy.data_ptr(), xdt, xv.t.data_ptr(), xdt, mean_t.data_ptr(), mdt,
+                                           invstd.data_ptr<float>(), gamma, pdt, mask, xdt, sums.data_ptr<double>(), xv.rows, C,
+                                           training ? 1 : 0, dx.data_ptr(), xdt, dgamma.data_ptr<float>(),
+                                           dbeta.data_ptr<float>(), has_residual ? dres.data_ptr() : nullptr, scope.stream()));
+  if (weight.has_value() && weight->defined() && weight->scalar_type() != at::kFloat) {
+    dgamma = dgamma.to(weight->scalar_type());
+    dbeta = dbeta.to(weight->scalar_type());
+  }
+  return {dx, dgamma, dbeta, dres};
+}
+
+namespace {
 // ------------------------------------------------------------------- layer norm
 std::tuple<Tensor, Tensor, Tensor> layer_norm_device(const Tensor& input, at::IntArrayRef normalized_shape,
                                                      const std::optional<Tensor>& weight,

@@ -18,6 +18,7 @@ def _ngpu():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
+WORLD = min(int(os.environ.get("CATCH_B200_TEST_WORLD", "2")), max(_ngpu(), 1))
 needs2 = pytest.mark.skipif(_ngpu() < 2, reason="needs two GPUs")
 ENV = {"NCCL_NVLS_ENABLE": "0"}
 
@@ -73,7 +74,7 @@ def _collectives(rank, world):
 
 @needs2
 def test_collectives():
-    run_ranks(_collectives, world=2, env=ENV, timeout=240)
+    run_ranks(_collectives, world=WORLD, env=ENV, timeout=240)
 
 
 def _ddp(rank, world):
@@ -102,7 +103,7 @@ def _ddp(rank, world):
 
 @needs2
 def test_stock_ddp_matches_cpu():
-    run_ranks(_ddp, world=2, env=ENV, timeout=240)
+    run_ranks(_ddp, world=WORLD, env=ENV, timeout=240)
 
 
 def _fused(rank, world, kind):
@@ -143,7 +144,7 @@ def _fused(rank, world, kind):
 @needs2
 @pytest.mark.parametrize("kind", ["sgd", "adamw"])
 def test_fused_allreduce_optimizer(kind):
-    run_ranks(_fused, world=2, args=(kind,), env=ENV, timeout=240)
+    run_ranks(_fused, world=WORLD, args=(kind,), env=ENV, timeout=240)
 
 
 def _bounded_wait(rank, world):
@@ -174,4 +175,4 @@ def _bounded_wait(rank, world):
 
 @needs2
 def test_device_wait_is_bounded():
-    run_ranks(_bounded_wait, world=2, env=ENV, timeout=240)
+    run_ranks(_bounded_wait, world=WORLD, env=ENV, timeout=240)

@@ -203,3 +203,52 @@ def test_resnet18_train_step_matches_cpu():
         if cos < 0.98:
             bad[n] = round(cos, 4)
     assert not bad, f"gradient direction mismatches: {bad}"
+
+
+def test_fused_bn_act_matches_unfused():
+    """fx-fused BN(+add)+ReLU kernels against the unfused model on the device and the CPU."""
+    import torchvision
+    from catch_b200.fusion import fuse_bn_act
+
+    torch.manual_seed(8)
+    ref = torchvision.models.resnet18(num_classes=16)
+    base = copy.deepcopy(ref).to(DEV).to(memory_format=torch.channels_last)
+    fused = fuse_bn_act(copy.deepcopy(ref)).to(DEV).to(memory_format=torch.channels_last)
+    assert fused.fused_bn_act_count == 17
+    x = torch.randn(8, 3, 64, 64)
+    t = torch.randint(0, 16, (8,))
+    outs = []
+    for m in (base, fused):  # fp32: both models then see identical convolution numerics
+        loss = F.cross_entropy(m(x.to(DEV)), t.to(DEV))
+        loss.backward()
+        outs.append(loss.item())
+    assert abs(outs[0] - outs[1]) < 1e-3, outs
+    bad = {}
+    for (n, a), (_, b) in zip(base.named_parameters(), fused.named_parameters()):
+        ga, gb = a.grad.double().flatten().cpu(), b.grad.double().flatten().cpu()
+        cos = (ga @ gb / (ga.norm() * gb.norm() + 1e-30)).item()
+        if cos < 0.995:
+            bad[n] = round(cos, 4)
+    assert not bad, bad
+    for (n, a), (_, b) in zip(base.named_buffers(), fused.named_buffers()):
+        assert_tensors_equal(b.float(), a.float(), prec=2e-2, use_MSE=True, msg=n)
+    # a single fused layer in fp32 against the CPU, forward and backward, with a residual
+    bn = torch.nn.BatchNorm2d(32)
+    bn.weight.data.uniform_(0.5, 1.5); bn.bias.data.normal_()
+    fb = copy.deepcopy(bn)
+    fb.__class__ = __import__("catch_b200.fusion", fromlist=["BatchNormAct2d"]).BatchNormAct2d
+    fb = fb.to(DEV)
+    xr = torch.randn(4, 32, 9, 7, requires_grad=True)
+    rr = torch.randn(4, 32, 9, 7, requires_grad=True)
+    xd = xr.detach().to(DEV).contiguous(memory_format=torch.channels_last).requires_grad_()
+    rd = rr.detach().to(DEV).contiguous(memory_format=torch.channels_last).requires_grad_()
+    yr = torch.relu(bn(xr) + rr)
+    yd = fb(xd, rd)
+    assert_tensors_equal(yd, yr, prec=3e-3, use_MSE=True)
+    g = torch.randn_like(yr)
+    yr.backward(g); yd.backward(g.to(DEV))
+    assert_tensors_equal(xd.grad, xr.grad, prec=3e-3, use_MSE=True, msg="dx")
+    assert_tensors_equal(rd.grad, rr.grad, prec=3e-3, use_MSE=True, msg="dres")
+    assert_tensors_equal(fb.weight.grad, bn.weight.grad, prec=3e-3, use_MSE=True)
+    assert_tensors_equal(fb.bias.grad, bn.bias.grad, prec=3e-3, use_MSE=True)
+    assert_tensors_equal(fb.running_var, bn.running_var, prec=3e-3, use_MSE=True)
