@@ -12,10 +12,19 @@ import os
 import sys
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import importlib.util
+
 import torch
 import torch.distributed as dist
 
-from catch_b200.models import BertConfig, BertForSequenceClassification
+# The model definition is loaded by path so that the --stock arm never imports the package
+# (registering a PrivateUse1 backend changes which accelerator autograd's stream logic tracks).
+_spec = importlib.util.spec_from_file_location(
+    "_bert_def", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "catch_b200", "models", "bert.py"))
+_bert = importlib.util.module_from_spec(_spec)
+sys.modules["_bert_def"] = _bert
+_spec.loader.exec_module(_bert)
+BertConfig, BertForSequenceClassification = _bert.BertConfig, _bert.BertForSequenceClassification
 
 
 def main():

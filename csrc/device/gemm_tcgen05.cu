@@ -50,6 +50,7 @@ struct GemmKernelArgs {
   int res_dtype;
   float alpha, beta;
   int act;
+  int tma_store;        // epilogue stages 64-column blocks in shared memory and stores them by TMA
   int* err;
 };
 
@@ -67,7 +68,7 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const GemmKernelArgs g) {
+                    const __grid_constant__ CUtensorMap tmD, const GemmKernelArgs g) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment is required by the 128-byte swizzle atoms.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -80,6 +81,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint64_t* acc_full = bars + 2 * GEMM_MAX_STAGES;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint8_t* stage_out = tiles + (size_t)g.stages * stage_bytes + 1024;  // 2 x 16 KB, 128-byte swizzled
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -184,6 +186,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int quarter = warp & 3;  // tcgen05.ld: warp w may touch lanes [32*(w%4), +32)
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint32_t out_blocks = 0;
     for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
       const int bz = tile / tiles_per_batch;
       const int t = tile - bz * tiles_per_batch;
@@ -200,6 +203,70 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                              ((size_t)bz * g.stride_r + (size_t)row * g.ldr) *
                                                  (g.res_dtype == B200_F32 ? 4 : 2)
                                        : nullptr;
+      if (g.tma_store) {
+        const bool issuer = threadIdx.x == 64;
+        const int rr_ = quarter * 32 + lane;
+        for (int cb = 0; cb < g.tile_n; cb += 64) {
+          uint8_t* sbuf = stage_out + (out_blocks & 1) * 16384;
+          if (issuer) tma_store_wait_read<1>();
+          named_barrier(1, 128);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int c = cb + half * 32;
+            uint32_t r[32];
+            tmem_ld32(tmem_base + acc * GEMM_ACC_STRIDE + ((uint32_t)(quarter * 32) << 16) + c, r);
+            tmem_ld_wait();
+            const int n_base = n0 + c;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = (g.kind == 2 ? (float)(int)r[j] : __uint_as_float(r[j])) * g.alpha;
+            if (g.col_scale) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (n_base + j < g.N) v[j] *= g.col_scale[n_base + j];
+            }
+            if (g.bias) {
+              if (g.bias_per_row) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += row_bias;
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) if (n_base + j < g.N) v[j] += load_scalar(g.bias, n_base + j, g.bias_dtype);
+              }
+            }
+            if (rrow && row_ok) {
+              for (int j = 0; j < 32; ++j)
+                if (n_base + j < g.N) v[j] += g.beta * load_scalar(rrow, n_base + j, g.res_dtype);
+            }
+            if (g.act) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], g.act);
+            }
+            alignas(16) uint16_t h[32];
+            if (g.d_dtype == B200_BF16) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) h[j] = __bfloat16_as_ushort(__float2bfloat16(v[j]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) h[j] = __half_as_ushort(__float2half(v[j]));
+            }
+            uint8_t* srow = sbuf + rr_ * 128;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              *reinterpret_cast<uint4*>(srow + (((half * 4 + k) ^ (rr_ & 7)) * 16)) = reinterpret_cast<const uint4*>(h)[k];
+          }
+          fence_proxy_async_smem();
+          named_barrier(1, 128);
+          if (issuer) {
+            tma_store_3d(&tmD, sbuf, n0 + cb, m0, bz);
+            tma_store_commit();
+          }
+          ++out_blocks;
+        }
+        tc_fence_before();
+        mbar_arrive(&acc_empty[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        continue;
+      }
       for (int c = 0; c < g.tile_n; c += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_base + acc * GEMM_ACC_STRIDE + ((uint32_t)(quarter * 32) << 16) + c, r);
@@ -268,6 +335,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 
   // ---------------------------------------------------------------- teardown
+  if (g.tma_store && threadIdx.x == 64) tma_store_wait_all<0>();
   if (*((volatile int*)g.err) != 0) {
     // Error path: give copies that are still in flight time to land before the
     // shared memory goes away.
@@ -362,12 +430,15 @@ extern "C" int b200_gemm(const B200GemmParams* p, void* stream) {
   if (!g.err) return (int)cudaErrorInvalidDevice;
 
   const int stage_bytes = GEMM_A_STAGE_BYTES + g.tile_n * 128;
-  const int smem_budget = 200 * 1024;
+  g.tma_store = (p->d_dtype != B200_F32 && g.tile_n % 64 == 0 && (p->ldd * 2) % 16 == 0 && (p->stride_d * 2) % 16 == 0 &&
+                 (reinterpret_cast<uintptr_t>(p->D) & 15) == 0)
+                    ? 1 : 0;
+  const int smem_budget = 227 * 1024 - 2048 - 1024 - (g.tma_store ? 32768 : 0);
   g.stages = smem_budget / stage_bytes;
   if (g.stages > GEMM_MAX_STAGES) g.stages = GEMM_MAX_STAGES;
   if (g.stages > g.k_blocks + 1) g.stages = g.k_blocks + 1 < 2 ? 2 : g.k_blocks + 1;
   if (g.stages < 2) g.stages = 2;
-  const size_t smem = (size_t)g.stages * stage_bytes + 1024 /*align*/ + 256 /*barriers*/;
+  const size_t smem = (size_t)g.stages * stage_bytes + 1024 /*align*/ + 1024 /*barriers*/ + (g.tma_store ? 32768 : 0);
 
   CUtensorMap tmA, tmB;
   const uint64_t batch_a = (uint64_t)(p->batch > 1 ? p->stride_a : (int64_t)p->lda * (p->a_mn_major ? p->K : p->M));
@@ -398,15 +469,24 @@ extern "C" int b200_gemm(const B200GemmParams* p, void* stream) {
   }
   if (rc) return rc;
 
+  CUtensorMap tmD = tmA;
+  if (g.tma_store) {
+    const CUtensorMapDataType ddt = p->d_dtype == B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    uint64_t dims[3] = {(uint64_t)p->N, (uint64_t)p->M, (uint64_t)p->batch};
+    uint64_t str[2] = {(uint64_t)p->ldd * 2, (uint64_t)(p->batch > 1 ? p->stride_d : (int64_t)p->ldd * p->M) * 2};
+    uint32_t box[3] = {64, GEMM_BM, 1};
+    rc = encode_tiled(&tmD, ddt, 3, p->D, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  }
   static bool attr_set[64] = {false};
   if (!attr_set[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return (int)e;
     attr_set[dev & 63] = true;
   }
   const long total_tiles = (long)g.tiles_m * g.tiles_n * g.batch;
   int ctas = p->max_ctas > 0 ? p->max_ctas : sms;
   if (ctas > total_tiles) ctas = (int)total_tiles;
-  gemm_tcgen05_kernel<<<ctas, GEMM_THREADS, smem, (cudaStream_t)stream>>>(tmA, tmB, g);
+  gemm_tcgen05_kernel<<<ctas, GEMM_THREADS, smem, (cudaStream_t)stream>>>(tmA, tmB, tmD, g);
   return (int)cudaGetLastError();
 }
