@@ -1,7 +1,7 @@
 """Per-layer convolution timings for the ResNet-50 shapes (batch 256, bf16, NHWC):
 this backend's tcgen05 kernels against stock PyTorch (cuDNN) on the same GPU.
 
-    python benchmarks/conv_layers.py [--batch 256] [--iters 10]
+    python benchmarks/conv_layers.py [--batch 256] [--iters 10] [--no-stock] [--layer IDX]
 
 Prints, for forward / data-gradient / weight-gradient of each distinct layer shape,
 microseconds, TFLOP/s and the bound implied by the measured peaks (time at the bf16
@@ -58,6 +58,7 @@ def main():
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--iters", type=int, default=7)
     ap.add_argument("--no-stock", action="store_true")
+    ap.add_argument("--layer", type=int, default=-1, help="index into the layer table; -1 = all")
     args = ap.parse_args()
     bw, fl, src = peaks()
     N = args.batch
@@ -67,7 +68,7 @@ def main():
     tot = {"ours": 0.0, "stock": 0.0, "bound": 0.0}
     print(f"peaks ({src}): {bw / 1e12:.2f} TB/s, {fl / 1e12:.0f} TFLOP/s")
     print(f"{'layer':34s} {'pass':6s} {'ours us':>9s} {'TF/s':>7s} {'stock us':>9s} {'bound us':>9s} {'ours/bound':>10s}")
-    for (C, H, K, R, s, p, cnt) in LAYERS:
+    for (C, H, K, R, s, p, cnt) in (LAYERS if args.layer < 0 else [LAYERS[args.layer]]):
         P = (H + 2 * p - R) // s + 1
         x = torch.randn(N, C, H, H).bfloat16()
         w = (torch.randn(K, C, R, R) / (C * R * R) ** 0.5).bfloat16()

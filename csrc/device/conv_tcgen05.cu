@@ -7,8 +7,10 @@
 //
 // Forward (and dgrad):  M = 128 output pixels (a BW x BH x BNI box of the pixel
 // grid), N = tile_n output channels, K loop = taps x 64-channel blocks.  Warp roles
-// are those of the GEMM kernel (TMA producer / MMA issuer / 4 epilogue warps, two
-// accumulator buffers).  The A tile of a tap is ONE 4-D tiled tensor-map load whose
+// are those of the GEMM kernel (TMA producer / MMA issuer / 8 epilogue warps, two
+// accumulator buffers); each epilogue warp stages and stores its own 32 pixels, so the
+// store path has no CTA-wide barrier.  When the weights of one output-channel tile are
+// small they stay resident in shared memory and the pipeline stages hold activations only.  The A tile of a tap is ONE 4-D tiled tensor-map load whose
 // origin is the tile's pixel origin plus the tap offset; halo elements outside the
 // view are zero-filled by the copy engine, so no im2col buffer exists anywhere.
 //
@@ -24,8 +26,11 @@
 
 namespace b200 {
 
-constexpr int CONV_THREADS = 192;
-constexpr int CONV_MAX_STAGES = 8;
+constexpr int CONV_THREADS = 192;        // weight-gradient kernel: TMA warp, MMA warp, 4 epilogue warps
+constexpr int CONV_EPI_WARPS = 8;          // forward kernel: two epilogue warps per tensor-memory lane quarter
+constexpr int CONV_EPI_THREADS = CONV_EPI_WARPS * 32;
+constexpr int CONV_FPROP_THREADS = 64 + CONV_EPI_THREADS;
+constexpr int CONV_MAX_STAGES = 12;
 constexpr int CONV_A_BYTES = 128 * 128;
 
 struct ConvArgs {
@@ -49,6 +54,8 @@ struct ConvArgs {
   int res_dtype;
   int act;
   float alpha;
+  int b_res_bytes;              // > 0: weights of one output-channel tile stay resident in shared memory
+  int coef_bytes;               // shared memory reserved for per-channel scale / bias (0 or 2048)
   int tma_store;                // epilogue stages 64-channel blocks in shared memory and stores them by TMA
   int* err;
 };
@@ -65,24 +72,83 @@ __device__ __forceinline__ float ld_scalar(const void* p, long long i, int dt) {
   return __half2float(static_cast<const __half*>(p)[i]);
 }
 
-__global__ void __launch_bounds__(CONV_THREADS, 1)
+// 32 floats -> 16 words of packed bf16 / fp16 pairs (element 2i in the low half).
+__device__ __forceinline__ void pack16(const float (&v)[32], uint32_t (&pk)[16], int dt) {
+  if (dt == B200_BF16) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+      pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const __half2 h2 = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+      pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
+    }
+  }
+}
+
+// v[j] = v[j] * scale[j] + bias[j] for 32 consecutive channels; the coefficients sit in shared memory.
+__device__ __forceinline__ void apply_coef(float (&v)[32], const float* sc, const float* bi) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float4 s4 = *reinterpret_cast<const float4*>(sc + j);
+    const float4 b4 = *reinterpret_cast<const float4*>(bi + j);
+    v[j] = fmaf(v[j], s4.x, b4.x); v[j + 1] = fmaf(v[j + 1], s4.y, b4.y);
+    v[j + 2] = fmaf(v[j + 2], s4.z, b4.z); v[j + 3] = fmaf(v[j + 3], s4.w, b4.w);
+  }
+}
+
+// v[j] += residual[j] for `valid` (<= 32) consecutive elements starting at rp.
+__device__ __forceinline__ void add_residual(float (&v)[32], const uint8_t* rp, int valid, int dt) {
+  if (valid == 32 && dt != B200_F32 && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
+    alignas(16) uint16_t hh[32];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(hh)[j] = __ldg(reinterpret_cast<const uint4*>(rp) + j);
+    if (dt == B200_BF16) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] += __bfloat162float(__ushort_as_bfloat16(hh[j]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] += __half2float(__ushort_as_half(hh[j]));
+    }
+  } else {
+    // constant indices keep v[] in registers
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) v[j] += ld_scalar(rp, j, dt);
+  }
+}
+
+__global__ void __launch_bounds__(CONV_FPROP_THREADS, 1)
 conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvArgs g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const int stage_bytes = CONV_A_BYTES + g.tile_n * 128;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)g.stages * stage_bytes);
+  // Layout: [resident weights (b_res_bytes, may be 0)] [stages] [barriers 1 KB] [coefficients] [output staging 32 KB]
+  // Streaming mode: a stage holds an A tile (16 KB) and the tap's weight tile.
+  // Resident mode : a stage holds only the A tile; the weights of the current output-channel
+  //                 tile (all taps, all channel blocks) stay in shared memory across pixel tiles.
+  const int b_blk_bytes = g.tile_n * 128;
+  const int stage_bytes = CONV_A_BYTES + (g.b_res_bytes ? 0 : b_blk_bytes);
+  uint8_t* bres = smem;
+  uint8_t* stage0 = smem + g.b_res_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage0 + (size_t)g.stages * stage_bytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + CONV_MAX_STAGES;
   uint64_t* acc_full = bars + 2 * CONV_MAX_STAGES;
   uint64_t* acc_empty = acc_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-  // two 16 KB staging buffers (128 pixels x 64 channels, 128-byte swizzle) for the TMA-store epilogue
-  uint8_t* stage_out = smem + (size_t)g.stages * stage_bytes + 1024;
+  uint64_t* b_full = acc_empty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_full + 1);
+  float* coef = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 1024);
+  // eight 4 KB staging buffers (32 pixels x 64 channels, 128-byte swizzle), one per epilogue warp
+  uint8_t* stage_out = reinterpret_cast<uint8_t*>(bars) + 1024 + g.coef_bytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < g.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], CONV_EPI_THREADS); }
+    mbar_init(b_full, 1);
     mbar_fence_init();
     tma_prefetch_desc(&maps.w);
     if (g.tma_store) tma_prefetch_desc(&maps.out);
@@ -102,6 +168,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
   if (warp == 0) {
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
+      int cur_ct = -1;
       for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
         // pixel tiles vary fastest so concurrently running CTAs share the weight tile
         const int pt = tile % pix_tiles, ct = tile / pix_tiles;
@@ -109,18 +176,41 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
         const int p0 = ((pt / g.tiles_q) % g.tiles_p) * g.bh;
         const int n0 = (pt / (g.tiles_q * g.tiles_p)) * g.bni;
         const int co0 = ct * g.tile_n;
+        if (g.b_res_bytes && ct != cur_ct) {
+          // Every MMA that read the previous weights has finished once all stages are empty.
+          for (int i = 0; i < g.stages && !failed; ++i) {
+            const int s = stage + i < g.stages ? stage + i : stage + i - g.stages;
+            const uint32_t par = s >= stage ? (phase ^ 1) : phase;
+            if (!mbar_wait(&empty_bar[s], par, g.err, ERR_TIMEOUT_EMPTY)) failed = true;
+          }
+          if (failed) break;
+          mbar_arrive_expect_tx(b_full, (uint32_t)g.b_res_bytes);
+          for (int it = 0; it < k_iters; ++it) {
+            const int tap = it / g.c_blocks, cb = it - tap * g.c_blocks;
+            uint8_t* sb = bres + (size_t)it * b_blk_bytes;
+            if (!g.b_mn) {
+              tma_load_3d(sb, &maps.w, b_full, cb * g.cblk, co0, g.taps[tap].wtap);
+            } else {
+              for (int j = 0; j < g.tile_n / 64; ++j)
+                tma_load_3d(sb + j * 8192, &maps.w, b_full, co0 + j * 64, cb * 64, g.taps[tap].wtap);
+            }
+          }
+          cur_ct = ct;
+        }
         for (int it = 0; it < k_iters; ++it) {
           const int tap = it / g.c_blocks, cb = it - tap * g.c_blocks;
           const B200ConvTap tp = g.taps[tap];
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, g.err, ERR_TIMEOUT_EMPTY)) { failed = true; break; }
           mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)stage_bytes);
-          uint8_t* sa = smem + (size_t)stage * stage_bytes;
+          uint8_t* sa = stage0 + (size_t)stage * stage_bytes;
           tma_load_4d(sa, &maps.a[tp.map], &full_bar[stage], cb * g.cblk, q0 + tp.dw, p0 + tp.dh, n0);
-          if (!g.b_mn) {
-            tma_load_3d(sa + CONV_A_BYTES, &maps.w, &full_bar[stage], cb * g.cblk, co0, tp.wtap);
-          } else {
-            for (int j = 0; j < g.tile_n / 64; ++j)
-              tma_load_3d(sa + CONV_A_BYTES + j * 8192, &maps.w, &full_bar[stage], co0 + j * 64, cb * 64, tp.wtap);
+          if (!g.b_res_bytes) {
+            if (!g.b_mn) {
+              tma_load_3d(sa + CONV_A_BYTES, &maps.w, &full_bar[stage], cb * g.cblk, co0, tp.wtap);
+            } else {
+              for (int j = 0; j < g.tile_n / 64; ++j)
+                tma_load_3d(sa + CONV_A_BYTES + j * 8192, &maps.w, &full_bar[stage], co0 + j * 64, cb * 64, tp.wtap);
+            }
           }
           if (++stage == g.stages) { stage = 0; phase ^= 1; }
         }
@@ -129,15 +219,22 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
   } else if (warp == 1) {
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
+      int cur_ct = -1; uint32_t b_phase = 0;
       for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+        const int ct = tile / pix_tiles;
+        if (g.b_res_bytes && ct != cur_ct) {
+          if (!mbar_wait(b_full, b_phase, g.err, ERR_TIMEOUT_FULL)) { failed = true; break; }
+          b_phase ^= 1;
+          cur_ct = ct;
+        }
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, g.err, ERR_TIMEOUT_TMEM_EMPTY)) { failed = true; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * 256;
         for (int it = 0; it < k_iters; ++it) {
           if (!mbar_wait(&full_bar[stage], phase, g.err, ERR_TIMEOUT_FULL)) { failed = true; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + (size_t)stage * stage_bytes);
-          const uint32_t sb = sa + CONV_A_BYTES;
+          const uint32_t sa = smem_u32(stage0 + (size_t)stage * stage_bytes);
+          const uint32_t sb = g.b_res_bytes ? smem_u32(bres + (size_t)it * b_blk_bytes) : sa + CONV_A_BYTES;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint64_t bdesc = g.b_mn ? make_smem_desc_sw128(sb + k * 2048, 8192, 1024)
@@ -157,158 +254,136 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
       }
     }
   } else {
+    // Eight epilogue warps.  tcgen05.ld lets warp w touch tensor-memory lanes [32*(w%4), +32),
+    // so two warps share each quarter of the tile's 128 pixels and take alternate column blocks.
+    // Nothing in the store path synchronises across warps: each warp stages its own 32 pixels
+    // x 64 channels (4 KB, 128-byte swizzle) and issues its own tensor-map store.
     const int quarter = warp & 3;
+    const int colhalf = (warp - 2) >> 2;
+    uint8_t* sbuf = stage_out + (warp - 2) * 4096;
     int acc = 0; uint32_t acc_phase = 0;
-    uint32_t out_blocks = 0;
     const int esz = g.out_dtype == B200_F32 ? 4 : 2;
     const int rsz = g.res_dtype == B200_F32 ? 4 : 2;
+    const bool has_coef = g.scale != nullptr || g.bias != nullptr;
+    const int r = quarter * 32 + lane;
+    // origin of this warp's 32 pixels inside the tile's pixel box (all extents are powers of two)
+    const int w_off = (quarter * 32) % g.bw, h_off = ((quarter * 32) / g.bw) % g.bh, n_off = (quarter * 32) / (g.bw * g.bh);
     for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
       const int pt = tile % pix_tiles, ct = tile / pix_tiles;
       const int q0 = (pt % g.tiles_q) * g.bw;
       const int p0 = ((pt / g.tiles_q) % g.tiles_p) * g.bh;
       const int n0 = (pt / (g.tiles_q * g.tiles_p)) * g.bni;
       const int co0 = ct * g.tile_n;
-      const int r = quarter * 32 + lane;
       const int q = q0 + r % g.bw, p = p0 + (r / g.bw) % g.bh, n = n0 + r / (g.bw * g.bh);
       const bool row_ok = q < g.Q && p < g.P && n < g.N;
       const long long off = (long long)n * g.o_sn + (long long)(p * g.o_mul_h + g.o_off_h) * g.o_sh +
                             (long long)(q * g.o_mul_w + g.o_off_w) * g.o_sw;
+      const float* cs = coef;
+      const float* cbias = cs + 256;
+      if (has_coef) {
+        // Every epilogue thread passes the barrier at the end of a tile after its last read of
+        // the coefficients, so they can be overwritten here.
+        for (int t = threadIdx.x - 64; t < g.tile_n; t += CONV_EPI_THREADS) {
+          const int co = co0 + t;
+          coef[t] = (g.scale && co < g.Cout) ? g.scale[co] : 1.f;
+          coef[256 + t] = (g.bias && co < g.Cout) ? ld_scalar(g.bias, co, g.bias_dtype) : 0.f;
+        }
+        named_barrier(2, CONV_EPI_THREADS);
+      }
       if (!mbar_wait(&acc_full[acc], acc_phase, g.err, ERR_TIMEOUT_TMEM_FULL)) { failed = true; break; }
       tc_fence_after();
-      if (g.tma_store) {
-        // Stage 64 channels x 128 pixels at a time in shared memory (the 128-byte swizzled
-        // layout the output tensor map expects) and let the copy engine write full lines;
-        // rows / channels outside the tensor are clipped by the store.
-        const bool issuer = threadIdx.x == 64;
-        for (int cb = 0; cb < g.tile_n; cb += 64) {
-          uint8_t* sbuf = stage_out + (out_blocks & 1) * 16384;
-          if (issuer) tma_store_wait_read<1>();  // the store that last used this buffer has read it
-          named_barrier(1, 128);
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const int c = cb + half * 32;
-            uint32_t rr[32];
-            tmem_ld32(tmem_base + acc * 256 + ((uint32_t)(quarter * 32) << 16) + c, rr);
-            tmem_ld_wait();
-            const int cbase = co0 + c;
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = (g.kind == 2 ? (float)(int)rr[j] : __uint_as_float(rr[j])) * g.alpha;
-            if (g.scale) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (cbase + j < g.Cout) v[j] *= g.scale[cbase + j];
-            }
-            if (g.bias) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (cbase + j < g.Cout) v[j] += ld_scalar(g.bias, cbase + j, g.bias_dtype);
-            }
-            if (g.residual && row_ok) {
-              for (int j = 0; j < 32; ++j)
-                if (cbase + j < g.Cout) v[j] += ld_scalar(g.residual, off + cbase + j, g.res_dtype);
-            }
-            if (g.act == 1) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
-            }
-            alignas(16) uint16_t h[32];
-            if (g.out_dtype == B200_BF16) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) h[j] = __bfloat16_as_ushort(__float2bfloat16(v[j]));
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) h[j] = __half_as_ushort(__float2half(v[j]));
-            }
-            uint8_t* srow = sbuf + r * 128;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const int chunk = (half * 4 + k) ^ (r & 7);
-              *reinterpret_cast<uint4*>(srow + chunk * 16) = reinterpret_cast<const uint4*>(h)[k];
-            }
-          }
-          fence_proxy_async_smem();
-          named_barrier(1, 128);
-          if (issuer) {
-            tma_store_4d(&maps.out, sbuf, co0 + cb, q0, p0, n0);
-            tma_store_commit();
-          }
-          ++out_blocks;
-        }
-        tc_fence_before();
-        mbar_arrive(&acc_empty[acc]);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
-        continue;
-      }
-      for (int c = 0; c < g.tile_n; c += 32) {
-        uint32_t rr[32];
-        tmem_ld32(tmem_base + acc * 256 + ((uint32_t)(quarter * 32) << 16) + c, rr);
-        tmem_ld_wait();
-        const int cbase = co0 + c;
-        if (!row_ok || cbase >= g.Cout) continue;
-        const int valid = min(32, g.Cout - cbase);
-        float v[32];
+      const uint32_t t_addr = tmem_base + acc * 256 + ((uint32_t)(quarter * 32) << 16);
+
+      // accumulator chunk (32 channels starting at tile column c) -> alpha, scale/bias, residual, activation
+      auto finish = [&](const uint32_t (&rr)[32], int c, float (&v)[32]) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = (g.kind == 2 ? (float)(int)rr[j] : __uint_as_float(rr[j])) * g.alpha;
-        if (g.scale) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) if (j < valid) v[j] *= g.scale[cbase + j];
-        }
-        if (g.bias) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) if (j < valid) v[j] += ld_scalar(g.bias, cbase + j, g.bias_dtype);
-        }
-        if (g.residual) {
-          const uint8_t* rp = static_cast<const uint8_t*>(g.residual) + (off + cbase) * rsz;
-          if (valid == 32 && rsz == 2 && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
-            alignas(16) uint16_t hh[32];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(hh)[j] = reinterpret_cast<const uint4*>(rp)[j];
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              v[j] += g.res_dtype == B200_BF16 ? __bfloat162float(__ushort_as_bfloat16(hh[j]))
-                                               : __half2float(__ushort_as_half(hh[j]));
-          } else {
-            for (int j = 0; j < valid; ++j) v[j] += ld_scalar(g.residual, off + cbase + j, g.res_dtype);
-          }
-        }
+        if (has_coef) apply_coef(v, cs + c, cbias + c);
+        const int cbase = co0 + c;
+        if (g.residual && row_ok && cbase < g.Cout)
+          add_residual(v, static_cast<const uint8_t*>(g.residual) + (off + cbase) * rsz, min(32, g.Cout - cbase), g.res_dtype);
         if (g.act == 1) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
         }
-        uint8_t* op = static_cast<uint8_t*>(g.out) + (off + cbase) * esz;
-        if (g.out_dtype == B200_F32) {
-          float* o = reinterpret_cast<float*>(op);
-          if (valid == 32 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+      };
+
+      if (g.tma_store) {
+        for (int cb = colhalf * 64; cb < g.tile_n; cb += 128) {
+          uint32_t ra[32], rb[32];
+          tmem_ld32(t_addr + cb, ra);
+          tmem_ld32(t_addr + cb + 32, rb);
+          tmem_ld_wait();
+          if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has read the buffer
+          __syncwarp();
+          uint8_t* srow = sbuf + lane * 128;
+          float v[32];
+          uint32_t pk[16];
+          finish(ra, cb, v);
+          pack16(v, pk, g.out_dtype);
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-          } else {
-            for (int j = 0; j < valid; ++j) o[j] = v[j];
+          for (int k = 0; k < 4; ++k)
+            *reinterpret_cast<uint4*>(srow + ((k ^ (lane & 7)) * 16)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
+          finish(rb, cb + 32, v);
+          pack16(v, pk, g.out_dtype);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            *reinterpret_cast<uint4*>(srow + (((4 + k) ^ (lane & 7)) * 16)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            // rows / channels outside the tensor are clipped by the store
+            tma_store_4d(&maps.out, sbuf, co0 + cb, q0 + w_off, p0 + h_off, n0 + n_off);
+            tma_store_commit();
           }
-        } else {
-          alignas(16) uint16_t h[32];
-          if (g.out_dtype == B200_BF16) {
+        }
+      } else {
+        for (int c = colhalf * 32; c < g.tile_n; c += 64) {
+          uint32_t rr[32];
+          tmem_ld32(t_addr + c, rr);
+          tmem_ld_wait();
+          const int cbase = co0 + c;
+          if (!row_ok || cbase >= g.Cout) continue;
+          const int valid = min(32, g.Cout - cbase);
+          float v[32];
+          finish(rr, c, v);
+          uint8_t* op = static_cast<uint8_t*>(g.out) + (off + cbase) * esz;
+          if (g.out_dtype == B200_F32) {
+            float* o = reinterpret_cast<float*>(op);
+            if (valid == 32 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) h[j] = __bfloat16_as_ushort(__float2bfloat16(v[j]));
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < valid) o[j] = v[j];
+            }
           } else {
+            uint32_t pk[16];
+            pack16(v, pk, g.out_dtype);
+            uint16_t* o = reinterpret_cast<uint16_t*>(op);
+            if (valid == 32 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) h[j] = __half_as_ushort(__float2half(v[j]));
-          }
-          uint16_t* o = reinterpret_cast<uint16_t*>(op);
-          if (valid == 32 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+              for (int j = 0; j < 4; ++j)
+                reinterpret_cast<uint4*>(o)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+            } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(o)[j] = reinterpret_cast<const uint4*>(h)[j];
-          } else {
-            for (int j = 0; j < valid; ++j) o[j] = h[j];
+              for (int j = 0; j < 32; ++j)
+                if (j < valid) o[j] = (uint16_t)(pk[j >> 1] >> ((j & 1) * 16));
+            }
           }
         }
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      if (has_coef) named_barrier(2, CONV_EPI_THREADS);
     }
+    if (g.tma_store && lane == 0) tma_store_wait_all<0>();  // stores must be complete before shared memory goes away
   }
 
-  if (g.tma_store && threadIdx.x == 64) tma_store_wait_all<0>();  // staged tiles must be read before smem goes away
   if (*((volatile int*)g.err) != 0) {
+    // give loads that may still be in flight time to land before shared memory is released
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
   }
@@ -440,7 +515,9 @@ conv_wgrad_kernel(const __grid_constant__ WgradMaps maps, const __grid_constant_
         float* dst = g.dw_acc + (long long)co * g.dw_ld + (long long)g.taps[tap].wtap * g.Cin + ci;
         const int valid = min(32, g.Cin - ci);
         if (g.splits == 1) {
-          for (int j = 0; j < valid; ++j) dst[j] = __uint_as_float(rr[j]);
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < valid) dst[j] = __uint_as_float(rr[j]);
         } else if (valid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
@@ -449,7 +526,9 @@ conv_wgrad_kernel(const __grid_constant__ WgradMaps maps, const __grid_constant_
                          : "memory");
           }
         } else {
-          for (int j = 0; j < valid; ++j) atomicAdd(dst + j, __uint_as_float(rr[j]));
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < valid) atomicAdd(dst + j, __uint_as_float(rr[j]));
         }
       }
     }
@@ -495,9 +574,31 @@ static int set_smem_attr_once(const void* fn, int dev, bool* done) {
 
 }  // namespace b200
 
-extern "C" int b200_conv_fprop(const B200ConvParams* p, void* stream) {
+// A pointwise (single centred tap) convolution over densely packed pixels is a plain GEMM:
+// fold batch, rows and columns into one pixel axis so that every A tile is one contiguous
+// 128-pixel run for the copy engine instead of a small 3-D box.
+static bool flatten_pointwise(B200ConvParams* q) {
+  if (q->ntaps != 1 || q->num_views != 1 || q->taps[0].dh != 0 || q->taps[0].dw != 0 || q->taps[0].map != 0) return false;
+  const B200ConvView& v = q->views[0];
+  if (v.dims[1] != q->Q || v.dims[2] != q->P || v.dims[3] != q->N) return false;
+  if (v.strides[1] != v.strides[0] * v.dims[1] || v.strides[2] != v.strides[1] * v.dims[2]) return false;
+  if (q->o_mul_h != 1 || q->o_mul_w != 1 || q->o_off_h != 0 || q->o_off_w != 0) return false;
+  if (q->o_sh != q->o_sw * q->Q || q->o_sn != q->o_sh * q->P) return false;
+  const long long pixels = (long long)q->N * q->P * q->Q;
+  if (pixels > 0x7fffffffLL) return false;
+  q->views[0].dims[1] = pixels; q->views[0].dims[2] = 1; q->views[0].dims[3] = 1;
+  q->views[0].strides[1] = v.strides[0] * pixels; q->views[0].strides[2] = v.strides[0] * pixels;
+  q->Q = (int)pixels; q->P = 1; q->N = 1;
+  q->o_sh = q->o_sw * pixels; q->o_sn = q->o_sh;
+  return true;
+}
+
+extern "C" int b200_conv_fprop(const B200ConvParams* p_in, void* stream) {
   using namespace b200;
-  if (p->N <= 0 || p->P <= 0 || p->Q <= 0 || p->Cout <= 0) return 0;
+  if (p_in->N <= 0 || p_in->P <= 0 || p_in->Q <= 0 || p_in->Cout <= 0) return 0;
+  B200ConvParams flat = *p_in;
+  flatten_pointwise(&flat);
+  const B200ConvParams* p = &flat;
   if (p->ntaps <= 0 || p->ntaps > B200_CONV_MAX_TAPS || p->num_views <= 0 || p->num_views > B200_CONV_MAX_MAPS)
     return (int)cudaErrorInvalidValue;
   const int es = p->ab_dtype == B200_I8 ? 1 : 2;
@@ -547,10 +648,16 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p, void* stream) {
   g.alpha = p->alpha == 0.f ? 1.f : p->alpha;
   g.err = error_flag_ptr();
   if (!g.err) return (int)cudaErrorInvalidDevice;
-  const int stage_bytes = CONV_A_BYTES + g.tile_n * 128;
   g.tma_store = (p->out_dtype != B200_F32 && g.tile_n % 64 == 0 && p->Cout % 8 == 0) ? 1 : 0;
-  const int smem_cap = 227 * 1024 - 2048 - 1024 - (g.tma_store ? 32768 : 0);
-  g.stages = smem_cap / stage_bytes;
+  g.coef_bytes = (p->scale || p->bias) ? 2048 : 0;
+  const int smem_cap = 227 * 1024 - 2048 - g.coef_bytes - (g.tma_store ? 32768 : 0);
+  // Weights of one output-channel tile (every tap and channel block) stay in shared memory when
+  // they are small and each CTA reuses them over several pixel tiles; the stages then hold only
+  // activations, which puts more of them in flight.
+  const long b_tile_bytes = (long)g.ntaps * g.c_blocks * g.tile_n * 128;
+  g.b_res_bytes = (b_tile_bytes <= 96 * 1024 && pix_tiles >= 2L * sms) ? (int)b_tile_bytes : 0;
+  const int stage_bytes = CONV_A_BYTES + (g.b_res_bytes ? 0 : g.tile_n * 128);
+  g.stages = (smem_cap - g.b_res_bytes) / stage_bytes;
   if (g.stages > CONV_MAX_STAGES) g.stages = CONV_MAX_STAGES;
   if (g.stages < 2) g.stages = 2;
 
@@ -561,7 +668,11 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p, void* stream) {
     ov.base = static_cast<const char*>(p->out) + ((long long)p->o_off_h * p->o_sh + (long long)p->o_off_w * p->o_sw) * 2;
     ov.dims[0] = p->Cout; ov.dims[1] = p->Q; ov.dims[2] = p->P; ov.dims[3] = p->N;
     ov.strides[0] = p->o_sw * p->o_mul_w; ov.strides[1] = p->o_sh * p->o_mul_h; ov.strides[2] = p->o_sn;
-    int rc = encode_view(&maps.out, ov, out_dt, 64, g.bw, g.bh, g.bni);
+    // each epilogue warp stores its own 32 pixels: the first 32 rows of the (bw, bh, bni) box order
+    const int sw = g.bw < 32 ? g.bw : 32;
+    const int sh = g.bh < 32 / sw ? g.bh : 32 / sw;
+    const int sn = 32 / (sw * sh);
+    int rc = encode_view(&maps.out, ov, out_dt, 64, sw, sh, sn);
     if (rc) return rc;
   }
   for (int i = 0; i < p->num_views; ++i) {
@@ -587,10 +698,11 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p, void* stream) {
   static bool attr_done[64] = {false};
   int rc = set_smem_attr_once((const void*)conv_fprop_kernel, dev, attr_done);
   if (rc) return rc;
-  const size_t smem = (size_t)g.stages * stage_bytes + 1024 /*align*/ + 1024 /*barriers*/ + (g.tma_store ? 32768 : 0);
+  const size_t smem = 1024 /*align*/ + (size_t)g.b_res_bytes + (size_t)g.stages * stage_bytes + 1024 /*barriers*/ +
+                      g.coef_bytes + (g.tma_store ? 32768 : 0);
   const long total_tiles = pix_tiles * g.tiles_co;
   const int ctas = (int)(total_tiles < sms ? total_tiles : sms);
-  conv_fprop_kernel<<<ctas, CONV_THREADS, smem, (cudaStream_t)stream>>>(maps, g);
+  conv_fprop_kernel<<<ctas, CONV_FPROP_THREADS, smem, (cudaStream_t)stream>>>(maps, g);
   return (int)cudaGetLastError();
 }
 

@@ -6,13 +6,13 @@
 // (torch_mlu/csrc/aten/operators/cnnl/internal/matmul_internal.cpp:106,
 // bmm_internal.cpp:89) and is the main loop the convolution kernels reuse.
 //
-// Structure (one CTA per SM, 192 threads):
+// Structure (one CTA per SM, 320 threads):
 //   warp 0    : TMA producer -- per k-block one expect_tx + tiled tensor-map loads
 //               of the A (128 x 128 B) and B (tile_n x 128 B) tiles, 128-byte swizzle
 //   warp 1    : allocates 512 tensor-memory columns, issues tcgen05.mma (one elected
 //               thread), commits to the stage's "empty" barrier and, after the last
 //               k-block of a tile, to the accumulator's "full" barrier
-//   warps 2-5 : epilogue -- tcgen05.ld 32 columns at a time, alpha/bias/residual/
+//   warps 2-9 : epilogue (two warps per lane quarter, alternate chunks) -- tcgen05.ld 32 columns at a time, alpha/bias/residual/
 //               activation in registers, cast, 16-byte global stores
 // The accumulator is double buffered (2 x 256 columns) so the epilogue of tile i
 // overlaps the main loop of tile i+1.  All waits are bounded (see tcgen05.cuh).
@@ -25,7 +25,9 @@
 namespace b200 {
 
 constexpr int GEMM_BM = 128;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_EPI_WARPS = 8;  // two epilogue warps per tensor-memory lane quarter
+constexpr int GEMM_EPI_THREADS = GEMM_EPI_WARPS * 32;
+constexpr int GEMM_THREADS = 64 + GEMM_EPI_THREADS;
 constexpr int GEMM_MAX_STAGES = 8;
 constexpr int GEMM_A_STAGE_BYTES = GEMM_BM * 128;  // 16 KB
 constexpr int GEMM_TMEM_COLS = 512;
@@ -50,6 +52,7 @@ struct GemmKernelArgs {
   int res_dtype;
   float alpha, beta;
   int act;
+  int coef_bytes;       // shared memory reserved for column scale / bias (0 or 2048)
   int tma_store;        // epilogue stages 64-column blocks in shared memory and stores them by TMA
   int* err;
 };
@@ -64,6 +67,61 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   if (act == 1) return v > 0.f ? v : 0.f;
   if (act == 2) return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
   return v;
+}
+
+// 32 floats -> 16 words of packed bf16 / fp16 pairs (element 2i in the low half).
+__device__ __forceinline__ void pack16(const float (&v)[32], uint32_t (&pk)[16], int dt) {
+  if (dt == B200_BF16) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+      pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const __half2 h2 = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+      pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
+    }
+  }
+}
+
+// v[j] = v[j] * scale[j] + bias[j] for 32 consecutive columns; the coefficients sit in shared memory.
+__device__ __forceinline__ void apply_coef(float (&v)[32], const float* sc, const float* bi) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float4 s4 = *reinterpret_cast<const float4*>(sc + j);
+    const float4 b4 = *reinterpret_cast<const float4*>(bi + j);
+    v[j] = fmaf(v[j], s4.x, b4.x); v[j + 1] = fmaf(v[j + 1], s4.y, b4.y);
+    v[j + 2] = fmaf(v[j + 2], s4.z, b4.z); v[j + 3] = fmaf(v[j + 3], s4.w, b4.w);
+  }
+}
+
+// v[j] += beta * residual[j] for `valid` (<= 32) consecutive elements starting at rp.
+__device__ __forceinline__ void add_residual(float (&v)[32], const uint8_t* rp, int valid, int dt, float beta) {
+  if (valid == 32 && dt != B200_F32 && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
+    alignas(16) uint16_t hh[32];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(hh)[j] = __ldg(reinterpret_cast<const uint4*>(rp) + j);
+    if (dt == B200_BF16) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] += beta * __bfloat162float(__ushort_as_bfloat16(hh[j]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] += beta * __half2float(__ushort_as_half(hh[j]));
+    }
+  } else if (valid == 32 && dt == B200_F32 && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      const float4 r4 = __ldg(reinterpret_cast<const float4*>(rp) + j / 4);
+      v[j] += beta * r4.x; v[j + 1] += beta * r4.y; v[j + 2] += beta * r4.z; v[j + 3] += beta * r4.w;
+    }
+  } else {
+    // constant indices keep v[] in registers
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) v[j] += beta * load_scalar(rp, j, dt);
+  }
 }
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -81,7 +139,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint64_t* acc_full = bars + 2 * GEMM_MAX_STAGES;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-  uint8_t* stage_out = tiles + (size_t)g.stages * stage_bytes + 1024;  // 2 x 16 KB, 128-byte swizzled
+  // per-tile column coefficients (scale, bias); present only when the launch has any
+  float* coef = reinterpret_cast<float*>(tiles + (size_t)g.stages * stage_bytes + 1024);
+  uint8_t* stage_out = tiles + (size_t)g.stages * stage_bytes + 1024 + g.coef_bytes;  // 2 x 16 KB, 128-byte swizzled
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -93,7 +153,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 128);
+      mbar_init(&acc_empty[b], GEMM_EPI_THREADS);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -184,14 +244,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;  // tcgen05.ld: warp w may touch lanes [32*(w%4), +32)
+    const int colhalf = (warp - 2) >> 2;  // the two warps of a quarter take alternate 32-column chunks
     int acc = 0;
     uint32_t acc_phase = 0;
     uint32_t out_blocks = 0;
-    for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+    uint32_t tile_iter = 0;
+    const bool has_coef = g.col_scale != nullptr || (g.bias != nullptr && !g.bias_per_row);
+    for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++tile_iter) {
       const int bz = tile / tiles_per_batch;
       const int t = tile - bz * tiles_per_batch;
       const int m0 = (t % g.tiles_m) * GEMM_BM;
       const int n0 = (t / g.tiles_m) * g.tile_n;
+      const float* cs = coef;
+      if (has_coef) {
+        // every thread has passed a barrier after its last read of the previous tile's coefficients
+        float* wsc = coef;
+        for (int ci = threadIdx.x - 64; ci < g.tile_n; ci += GEMM_EPI_THREADS) {
+          const int n = n0 + ci;
+          wsc[ci] = (g.col_scale && n < g.N) ? g.col_scale[n] : 1.f;
+          wsc[256 + ci] = (g.bias && !g.bias_per_row && n < g.N) ? load_scalar(g.bias, n, g.bias_dtype) : 0.f;
+        }
+        named_barrier(2, GEMM_EPI_THREADS);
+      }
       if (!mbar_wait(&acc_full[acc], acc_phase, g.err, ERR_TIMEOUT_TMEM_FULL)) { failed = true; break; }
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
@@ -209,9 +283,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int cb = 0; cb < g.tile_n; cb += 64) {
           uint8_t* sbuf = stage_out + (out_blocks & 1) * 16384;
           if (issuer) tma_store_wait_read<1>();
-          named_barrier(1, 128);
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
+          named_barrier(1, GEMM_EPI_THREADS);
+          {
+            const int half = colhalf;
             const int c = cb + half * 32;
             uint32_t r[32];
             tmem_ld32(tmem_base + acc * GEMM_ACC_STRIDE + ((uint32_t)(quarter * 32) << 16) + c, r);
@@ -220,42 +294,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = (g.kind == 2 ? (float)(int)r[j] : __uint_as_float(r[j])) * g.alpha;
-            if (g.col_scale) {
+            if (has_coef) apply_coef(v, cs + c, cs + 256 + c);
+            if (g.bias && g.bias_per_row) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) if (n_base + j < g.N) v[j] *= g.col_scale[n_base + j];
+              for (int j = 0; j < 32; ++j) v[j] += row_bias;
             }
-            if (g.bias) {
-              if (g.bias_per_row) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] += row_bias;
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) if (n_base + j < g.N) v[j] += load_scalar(g.bias, n_base + j, g.bias_dtype);
-              }
-            }
-            if (rrow && row_ok) {
-              for (int j = 0; j < 32; ++j)
-                if (n_base + j < g.N) v[j] += g.beta * load_scalar(rrow, n_base + j, g.res_dtype);
-            }
+            if (rrow && row_ok && n_base < g.N)
+              add_residual(v, rrow + (size_t)n_base * (g.res_dtype == B200_F32 ? 4 : 2), min(32, g.N - n_base), g.res_dtype, g.beta);
             if (g.act) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], g.act);
             }
-            alignas(16) uint16_t h[32];
-            if (g.d_dtype == B200_BF16) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) h[j] = __bfloat16_as_ushort(__float2bfloat16(v[j]));
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) h[j] = __half_as_ushort(__float2half(v[j]));
-            }
+            uint32_t pk[16];
+            pack16(v, pk, g.d_dtype);
             uint8_t* srow = sbuf + rr_ * 128;
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-              *reinterpret_cast<uint4*>(srow + (((half * 4 + k) ^ (rr_ & 7)) * 16)) = reinterpret_cast<const uint4*>(h)[k];
+              *reinterpret_cast<uint4*>(srow + (((half * 4 + k) ^ (rr_ & 7)) * 16)) =
+                  make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
           }
           fence_proxy_async_smem();
-          named_barrier(1, 128);
+          named_barrier(1, GEMM_EPI_THREADS);
           if (issuer) {
             tma_store_3d(&tmD, sbuf, n0 + cb, m0, bz);
             tma_store_commit();
@@ -267,7 +326,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         continue;
       }
-      for (int c = 0; c < g.tile_n; c += 32) {
+      for (int c = colhalf * 32; c < g.tile_n; c += 64) {
         uint32_t r[32];
         tmem_ld32(tmem_base + acc * GEMM_ACC_STRIDE + ((uint32_t)(quarter * 32) << 16) + c, r);
         tmem_ld_wait();
@@ -277,26 +336,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = (g.kind == 2 ? (float)(int)r[j] : __uint_as_float(r[j])) * g.alpha;
         const int valid = min(32, g.N - n_base);
-        if (g.col_scale) {
+        if (has_coef) apply_coef(v, cs + c, cs + 256 + c);
+        if (g.bias && g.bias_per_row) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < valid) v[j] *= g.col_scale[n_base + j];
+          for (int j = 0; j < 32; ++j) v[j] += row_bias;
         }
-        if (g.bias) {
-          if (g.bias_per_row) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += row_bias;
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < valid) v[j] += load_scalar(g.bias, n_base + j, g.bias_dtype);
-          }
-        }
-        if (rrow) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < valid) v[j] += g.beta * load_scalar(rrow, n_base + j, g.res_dtype);
-        }
+        if (rrow) add_residual(v, rrow + (size_t)n_base * (g.res_dtype == B200_F32 ? 4 : 2), valid, g.res_dtype, g.beta);
         if (g.act) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], g.act);
@@ -308,29 +353,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int j = 0; j < 32; j += 4)
               *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
           } else {
-            for (int j = 0; j < valid; ++j) o[j] = v[j];
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < valid) o[j] = v[j];
           }
         } else {
-          alignas(16) uint16_t h[32];
-          if (g.d_dtype == B200_BF16) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) h[j] = __bfloat16_as_ushort(__float2bfloat16(v[j]));
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) h[j] = __half_as_ushort(__float2half(v[j]));
-          }
+          uint32_t pk[16];
+          pack16(v, pk, g.d_dtype);
           uint16_t* o = reinterpret_cast<uint16_t*>(drow) + n_base;
           if (valid == 32 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(o)[j] = reinterpret_cast<const uint4*>(h)[j];
+            for (int j = 0; j < 4; ++j)
+              reinterpret_cast<uint4*>(o)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
           } else {
-            for (int j = 0; j < valid; ++j) o[j] = h[j];
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < valid) o[j] = (uint16_t)(pk[j >> 1] >> ((j & 1) * 16));
           }
         }
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      if (has_coef) named_barrier(2, GEMM_EPI_THREADS);
     }
   }
 
@@ -433,12 +478,13 @@ extern "C" int b200_gemm(const B200GemmParams* p, void* stream) {
   g.tma_store = (p->d_dtype != B200_F32 && g.tile_n % 64 == 0 && (p->ldd * 2) % 16 == 0 && (p->stride_d * 2) % 16 == 0 &&
                  (reinterpret_cast<uintptr_t>(p->D) & 15) == 0)
                     ? 1 : 0;
-  const int smem_budget = 227 * 1024 - 2048 - 1024 - (g.tma_store ? 32768 : 0);
+  g.coef_bytes = (p->col_scale || (p->bias && !p->bias_per_row)) ? 2048 : 0;
+  const int smem_budget = 227 * 1024 - 2048 - g.coef_bytes - (g.tma_store ? 32768 : 0);
   g.stages = smem_budget / stage_bytes;
   if (g.stages > GEMM_MAX_STAGES) g.stages = GEMM_MAX_STAGES;
   if (g.stages > g.k_blocks + 1) g.stages = g.k_blocks + 1 < 2 ? 2 : g.k_blocks + 1;
   if (g.stages < 2) g.stages = 2;
-  const size_t smem = (size_t)g.stages * stage_bytes + 1024 /*align*/ + 1024 /*barriers*/ + (g.tma_store ? 32768 : 0);
+  const size_t smem = (size_t)g.stages * stage_bytes + 1024 /*align*/ + 1024 /*barriers*/ + g.coef_bytes + (g.tma_store ? 32768 : 0);
 
   CUtensorMap tmA, tmB;
   const uint64_t batch_a = (uint64_t)(p->batch > 1 ? p->stride_a : (int64_t)p->lda * (p->a_mn_major ? p->K : p->M));

@@ -144,7 +144,14 @@ class RunnerCache {
   int64_t registerFusion(const Node* node) {
     std::shared_ptr<Graph> g = node->g(attr::Subgraph)->copy();
     std::shared_ptr<Graph> canon = Canonicalize(g, /*keep_unique_names=*/false);
-    const std::string text = canon->toString(/*print_source_locations=*/false);
+    std::string text = canon->toString(/*print_source_locations=*/false);
+    // The printed graph shows tensor constants as <Tensor>: two modules with the same structure
+    // but different weights print alike, so the key also names the constant tensors themselves.
+    // A cached runner keeps its graph (and so these tensors) alive, which keeps the addresses unique.
+    for (const Node* n : g->nodes()) {
+      if (n->kind() != prim::Constant || !n->hasAttribute(attr::value) || n->kindOf(attr::value) != AttributeKind::t) continue;
+      text += "|" + std::to_string(reinterpret_cast<uintptr_t>(n->t(attr::value).unsafeGetTensorImpl()));
+    }
     std::lock_guard<std::mutex> lk(mu_);
     auto it = by_text_.find(text);
     if (it != by_text_.end()) return it->second;

@@ -72,12 +72,38 @@ void remove_contiguous(Block* block) {
   }
 }
 
+// Tracing records convolutions as the 13-argument aten::_convolution; the fusion patterns
+// are written against aten::conv2d, so non-transposed 2-D instances are rewritten to it.
+void canonicalize_convolution(std::shared_ptr<Graph>& graph) {
+  const std::string traced = R"IR(
+    graph(%x, %w, %b, %s, %p, %d, %t, %op, %g, %bm, %det, %cud, %tf32):
+      %y = aten::_convolution(%x, %w, %b, %s, %p, %d, %t, %op, %g, %bm, %det, %cud, %tf32)
+      return (%y))IR";
+  const std::string plain = R"IR(
+    graph(%x, %w, %b, %s, %p, %d, %t, %op, %g, %bm, %det, %cud, %tf32):
+      %y = aten::conv2d(%x, %w, %b, %s, %p, %d, %g)
+      return (%y))IR";
+  auto is_plain_2d = [](const Match& m, const std::unordered_map<std::string, Value*>& vmap) {
+    auto t = toIValue(m.values_map.at(vmap.at("t")));
+    auto s = toIValue(m.values_map.at(vmap.at("s")));
+    auto p = toIValue(m.values_map.at(vmap.at("p")));
+    auto d = toIValue(m.values_map.at(vmap.at("d")));
+    return t.has_value() && t->isBool() && !t->toBool() && s.has_value() && s->isIntList() && s->toIntList().size() == 2 &&
+           p.has_value() && p->isIntList() && p->toIntList().size() == 2 && d.has_value() && d->isIntList() &&
+           d->toIntList().size() == 2;
+  };
+  SubgraphRewriter rw;
+  rw.RegisterRewritePattern(traced, plain);
+  rw.runOnGraph(graph, is_plain_2d);
+}
+
 }  // namespace
 
 void LowerGraph(std::shared_ptr<Graph>& graph) {
   if (!fusion_enabled()) return;
   Inline(*graph);
   LowerSimpleTuples(graph);
+  canonicalize_convolution(graph);
   eliminate_exception_ifs(graph->block());
   removeDropout(graph);
   RemoveTensorMutation(graph);

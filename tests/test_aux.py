@@ -100,6 +100,20 @@ def test_fusion_passes_rewrite_and_segment():
     assert after["compiles"] >= before["compiles"] + 1  # a new shape compiles a new plan
 
 
+def test_fusion_of_traced_module_rewrites_underscore_convolution():
+    # torch.jit.trace records aten::_convolution; lowering has to turn it into the form the
+    # conv+add+relu patterns match, otherwise every relu / add stays a separate kernel.
+    torch.manual_seed(0)
+    m = Block().eval()
+    x = torch.randn(2, 8, 12, 12)
+    ref = m(x)
+    opt = jit.optimize(torch.jit.trace(m, x))
+    inner = "".join(str(n.g("Subgraph")) for n in opt.graph.nodes() if n.kind() == "catch_b200::FusionGroup")
+    assert inner.count("catch_b200::conv_bn_act") == 3
+    assert "aten::_convolution" not in inner and "aten::relu(" not in inner and "aten::add(" not in inner
+    assert torch.allclose(opt(x), ref, atol=1e-4)
+
+
 def test_fusion_toggle_and_forced_fallback():
     m = torch.jit.script(Block().eval())
     jit.set_fusion_enabled(False)
