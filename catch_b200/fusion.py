@@ -25,9 +25,9 @@ import torch.nn.functional as F
 
 class _BNActFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, running_mean, running_var, residual, training, momentum, eps, act):
+    def forward(ctx, x, weight, bias, running_mean, running_var, residual, training, momentum, eps, act, sums=None):
         out, mean, invstd = torch.ops.catch_b200.batch_norm_act(x, weight, bias, running_mean, running_var, residual,
-                                                                training, momentum, eps, act)
+                                                                training, momentum, eps, act, sums)
         ctx.save_for_backward(out, x, weight, running_mean, mean, invstd)
         ctx.cfg = (training, act, residual is not None)
         return out
@@ -39,7 +39,49 @@ class _BNActFn(torch.autograd.Function):
         dx, dgamma, dbeta, dres = torch.ops.catch_b200.batch_norm_act_backward(
             grad_out, out, x, weight, running_mean, mean, invstd, training, act, has_res)
         return (dx, dgamma if weight is not None else None, dbeta if weight is not None else None, None, None,
-                dres if has_res else None, None, None, None, None)
+                dres if has_res else None, None, None, None, None, None)
+
+
+class _ConvStatsFn(torch.autograd.Function):
+    """Convolution whose epilogue also accumulates per-channel sum / sum of squares of the output."""
+
+    @staticmethod
+    def forward(ctx, x, weight, stride, padding):
+        y, sums = torch.ops.catch_b200.conv2d_stats(x, weight, stride, padding)
+        ctx.save_for_backward(x, weight)
+        ctx.cfg = (stride, padding)
+        ctx.mark_non_differentiable(sums)
+        return y, sums
+
+    @staticmethod
+    def backward(ctx, grad_y, _grad_sums):
+        x, weight = ctx.saved_tensors
+        stride, padding = ctx.cfg
+        dx, dw, _ = torch.ops.aten.convolution_backward(
+            grad_y, x, weight, None, stride, padding, [1, 1], False, [0, 0], 1,
+            [ctx.needs_input_grad[0], ctx.needs_input_grad[1], False])
+        return dx, dw, None, None
+
+
+class StatsConv2d(nn.Conv2d):
+    """``Conv2d`` feeding a batch norm: in training it hands the batch norm the channel sums of its
+    output (computed in the convolution epilogue), which saves the batch norm's statistics pass over
+    the activation.  The sums travel as an attribute of the returned tensor object."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if (self.training and _device_kernels_available(x) and x.dim() == 4 and self.bias is None and self.groups == 1
+                and self.padding_mode == "zeros" and self.dilation == (1, 1) and not isinstance(self.padding, str)
+                and all(s in (1, 2) for s in self.stride) and self.in_channels % 8 == 0 and self.out_channels % 64 == 0
+                and x.numel() > 0):
+            w = self.weight
+            if torch.is_autocast_enabled("blackwell"):
+                dt = torch.get_autocast_dtype("blackwell")
+                x, w = x.to(dt), w.to(dt)
+            if x.dtype in (torch.bfloat16, torch.float16) and w.dtype == x.dtype:
+                y, sums = _ConvStatsFn.apply(x, w, list(self.stride), list(self.padding))
+                y._b200_channel_sums = sums
+                return y
+        return super().forward(x)
 
 
 def _device_kernels_available(x: torch.Tensor) -> bool:
@@ -64,11 +106,17 @@ class BatchNormAct2d(nn.BatchNorm2d):
         if (_device_kernels_available(x) and x.dim() == 4 and x.shape[1] % c_vec == 0
                 and x.dtype in (torch.float32, torch.bfloat16, torch.float16) and x.numel() > 0
                 and (residual is None or (residual.shape == x.shape and residual.dtype == x.dtype))):
-            return _BNActFn.apply(x, self.weight, self.bias, rm, rv, residual, training, momentum, self.eps, self.act)
+            sums = getattr(x, "_b200_channel_sums", None) if training else None
+            return _BNActFn.apply(x, self.weight, self.bias, rm, rv, residual, training, momentum, self.eps, self.act,
+                                  sums)
         y = F.batch_norm(x, rm, rv, self.weight, self.bias, training, momentum, self.eps)
         if residual is not None:
             y = y + residual
         return F.relu(y) if self.act == 1 else y
+
+
+def _feeds_only(node: fx.Node, consumer: fx.Node) -> bool:
+    return len(node.users) == 1 and next(iter(node.users)) is consumer
 
 
 def _is_relu(node: fx.Node, modules) -> bool:
@@ -90,27 +138,35 @@ def _is_add(node: fx.Node) -> bool:
 
 
 def fuse_bn_act(model: nn.Module) -> fx.GraphModule:
-    """Return an fx GraphModule of ``model`` with BN(+add)+ReLU chains fused (see module docstring)."""
+    """Return an fx GraphModule of ``model`` with BN(+add)+ReLU chains fused (see module docstring).
+
+    A ``Conv2d`` whose only consumer is a batch norm becomes a ``StatsConv2d`` and that batch norm a
+    ``BatchNormAct2d`` (with ``act = 0`` when no ReLU follows), so the convolution's epilogue supplies
+    the batch statistics."""
     gm = fx.symbolic_trace(model)
     modules = dict(gm.named_modules())
     fused = 0
     for node in list(gm.graph.nodes):
         if node.op != "call_module" or type(modules[node.target]) is not nn.BatchNorm2d:
             continue
-        if len(node.users) != 1:
-            continue
-        user = next(iter(node.users))
+        bn = modules[node.target]
+        src = node.args[0] if node.args else None
+        if (isinstance(src, fx.Node) and src.op == "call_module" and type(modules[src.target]) is nn.Conv2d
+                and _feeds_only(src, node)):
+            modules[src.target].__class__ = StatsConv2d
+            bn.__class__ = BatchNormAct2d  # consumes the statistics; stays activation-free unless a chain is fused below
+            bn.act = 0
+        user = next(iter(node.users)) if len(node.users) == 1 else None
         residual, relu_node, add_node = None, None, None
-        if _is_relu(user, modules):
+        if user is not None and _is_relu(user, modules):
             relu_node = user
-        elif _is_add(user) and len(user.users) == 1 and _is_relu(next(iter(user.users)), modules):
+        elif (user is not None and _is_add(user) and len(user.users) == 1 and _is_relu(next(iter(user.users)), modules)):
             add_node, relu_node = user, next(iter(user.users))
             residual = user.args[1] if user.args[0] is node else user.args[0]
             if residual is node:
                 continue
         else:
             continue
-        bn = modules[node.target]
         bn.__class__ = BatchNormAct2d
         bn.act = 1
         # the residual must be computed before the fused node: place the fused call where the ReLU was

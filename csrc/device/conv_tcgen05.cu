@@ -54,6 +54,7 @@ struct ConvArgs {
   int res_dtype;
   int act;
   float alpha;
+  double* stats;                // optional [2 * Cout]: per-channel sum and sum of squares of the stored outputs
   int b_res_bytes;              // > 0: weights of one output-channel tile stay resident in shared memory
   int coef_bytes;               // shared memory reserved for per-channel scale / bias (0 or 2048)
   int tma_store;                // epilogue stages 64-channel blocks in shared memory and stores them by TMA
@@ -268,8 +269,29 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
     const int r = quarter * 32 + lane;
     // origin of this warp's 32 pixels inside the tile's pixel box (all extents are powers of two)
     const int w_off = (quarter * 32) % g.bw, h_off = ((quarter * 32) / g.bw) % g.bh, n_off = (quarter * 32) / (g.bw * g.bh);
+    // Channel statistics (for a following batch norm): lane L keeps the running sum and sum of
+    // squares of channels 2L, 2L+1 of each 64-channel block this warp stores, over all pixel
+    // tiles of one output-channel tile, and adds them to the fp64 totals when that tile changes.
+    float st_s[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, st_q[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    int st_ct = -1;
+    auto flush_stats = [&]() {
+      if (st_ct < 0) return;
+#pragma unroll
+      for (int bi = 0; bi < 2; ++bi) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int ch = st_ct * g.tile_n + colhalf * 64 + bi * 128 + 2 * lane + e;
+          if (colhalf * 64 + bi * 128 < g.tile_n && ch < g.Cout) {
+            atomicAdd(g.stats + ch, (double)st_s[bi][e]);
+            atomicAdd(g.stats + g.Cout + ch, (double)st_q[bi][e]);
+          }
+          st_s[bi][e] = 0.f; st_q[bi][e] = 0.f;
+        }
+      }
+    };
     for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
       const int pt = tile % pix_tiles, ct = tile / pix_tiles;
+      if (g.stats && ct != st_ct) { flush_stats(); st_ct = ct; }
       const int q0 = (pt % g.tiles_q) * g.bw;
       const int p0 = ((pt / g.tiles_q) % g.tiles_p) * g.bh;
       const int n0 = (pt / (g.tiles_q * g.tiles_p)) * g.bni;
@@ -306,10 +328,18 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
         }
+        if (g.stats && !row_ok) {
+          // pixels outside the output are clipped by the store but must not count in the statistics
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
       };
 
       if (g.tma_store) {
-        for (int cb = colhalf * 64; cb < g.tile_n; cb += 128) {
+#pragma unroll
+        for (int bi = 0; bi < 2; ++bi) {
+          const int cb = colhalf * 64 + bi * 128;
+          if (cb >= g.tile_n) break;
           uint32_t ra[32], rb[32];
           tmem_ld32(t_addr + cb, ra);
           tmem_ld32(t_addr + cb + 32, rb);
@@ -331,6 +361,24 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
             *reinterpret_cast<uint4*>(srow + (((4 + k) ^ (lane & 7)) * 16)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
           fence_proxy_async_smem();
           __syncwarp();
+          if (g.stats) {
+            // Column sums over the 32 staged pixels (the rounded values that were stored; pixels
+            // outside the tensor were zeroed above).
+            float s0 = 0.f, s1 = 0.f, q0s = 0.f, q1s = 0.f;
+#pragma unroll 8
+            for (int rw = 0; rw < 32; ++rw) {
+              const uint32_t w2 = *reinterpret_cast<const uint32_t*>(sbuf + rw * 128 + (((lane >> 2) ^ (rw & 7)) * 16) + (lane & 3) * 4);
+              float a, b;
+              if (g.out_dtype == B200_BF16) {
+                a = __uint_as_float(w2 << 16); b = __uint_as_float(w2 & 0xffff0000u);
+              } else {
+                const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w2));
+                a = f2.x; b = f2.y;
+              }
+              s0 += a; q0s = fmaf(a, a, q0s); s1 += b; q1s = fmaf(b, b, q1s);
+            }
+            st_s[bi][0] += s0; st_s[bi][1] += s1; st_q[bi][0] += q0s; st_q[bi][1] += q1s;
+          }
           if (lane == 0) {
             // rows / channels outside the tensor are clipped by the store
             tma_store_4d(&maps.out, sbuf, co0 + cb, q0 + w_off, p0 + h_off, n0 + n_off);
@@ -379,6 +427,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       if (has_coef) named_barrier(2, CONV_EPI_THREADS);
     }
+    if (g.stats) flush_stats();
     if (g.tma_store && lane == 0) tma_store_wait_all<0>();  // stores must be complete before shared memory goes away
   }
 
@@ -645,6 +694,7 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p_in, void* stream) {
   g.scale = static_cast<const float*>(p->scale);
   g.bias = p->bias; g.bias_dtype = p->bias_dtype;
   g.residual = p->residual; g.res_dtype = p->res_dtype; g.act = p->act;
+  g.stats = static_cast<double*>(p->stats);
   g.alpha = p->alpha == 0.f ? 1.f : p->alpha;
   g.err = error_flag_ptr();
   if (!g.err) return (int)cudaErrorInvalidDevice;
@@ -654,6 +704,7 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p_in, void* stream) {
   // Weights of one output-channel tile (every tap and channel block) stay in shared memory when
   // they are small and each CTA reuses them over several pixel tiles; the stages then hold only
   // activations, which puts more of them in flight.
+  if (g.stats && !g.tma_store) return (int)cudaErrorInvalidValue;  // statistics come from the staged tiles
   const long b_tile_bytes = (long)g.ntaps * g.c_blocks * g.tile_n * 128;
   g.b_res_bytes = (b_tile_bytes <= 96 * 1024 && pix_tiles >= 2L * sms) ? (int)b_tile_bytes : 0;
   const int stage_bytes = CONV_A_BYTES + (g.b_res_bytes ? 0 : g.tile_n * 128);

@@ -155,6 +155,10 @@ typedef struct B200ConvParams {
   int act;               // 0 none, 1 relu
   int tile_n;            // 0 = automatic
   float alpha;           // accumulator multiplier applied first (0 is treated as 1)
+  // Optional fp64 [2 * Cout], zeroed by the caller: the kernel adds, per output channel, the sum
+  // and the sum of squares of the values it stores (16-bit outputs, Cout a multiple of 8, tile
+  // widths that are multiples of 64 only) so that a following batch norm needs no statistics pass.
+  double* stats;
 } B200ConvParams;
 B200_API int b200_conv_fprop(const B200ConvParams* p, void* stream);
 

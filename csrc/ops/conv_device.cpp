@@ -146,7 +146,8 @@ Tensor pack_stem_weight(const Tensor& weight, const ConvGeom& g, at::ScalarType 
 }
 
 Tensor forward_impl(const Tensor& input, const Tensor& weight, const std::optional<Tensor>& bias, const ConvGeom& g,
-                    const float* scale, const Tensor* residual, int act, at::ScalarType out_dtype) {
+                    const float* scale, const Tensor* residual, int act, at::ScalarType out_dtype,
+                    double* stats = nullptr) {
   const at::ScalarType dt = compute_dtype(input.scalar_type());
   OpScope scope("conv_fprop", input);
   Tensor out = empty_b200({g.N, g.K, g.P, g.Q}, out_dtype, input.device().index(), at::MemoryFormat::ChannelsLast);
@@ -192,6 +193,7 @@ Tensor forward_impl(const Tensor& input, const Tensor& weight, const std::option
     p.res_dtype = to_b200_dtype(res.scalar_type());
   }
   p.act = act;
+  p.stats = stats;
   TORCH_CHECK(p.ntaps > 0, "b200 conv: empty tap list");
   B200_KERNEL_CHECK(b200_conv_fprop(&p, scope.stream()));
   return out;
@@ -347,6 +349,22 @@ at::Tensor conv_bn_act_device(const at::Tensor& input, const at::Tensor& weight,
   }
   const at::Tensor* res = (residual.has_value() && residual->defined()) ? &*residual : nullptr;
   return forward_impl(input, weight, bias, g, scp, res, (int)act, input.scalar_type());
+}
+
+// Convolution that also returns the per-channel sum / sum of squares of its output
+// ([2 * Cout] fp64), accumulated in the epilogue, for the batch norm that follows it.
+std::tuple<at::Tensor, at::Tensor> conv_stats_device(const at::Tensor& input, const at::Tensor& weight,
+                                                     at::IntArrayRef stride, at::IntArrayRef padding) {
+  const int64_t ones[2] = {1, 1};
+  check_supported(input, weight, stride, padding, at::IntArrayRef(ones, 2), false, 1);
+  TORCH_CHECK(input.scalar_type() != at::kFloat, "conv2d_stats: 16-bit activations only");
+  TORCH_CHECK(input.size(1) == weight.size(1), "conv: channel mismatch");
+  ConvGeom g = geom(input, weight, stride, padding);
+  TORCH_CHECK(g.P > 0 && g.Q > 0, "conv: output size is too small");
+  TORCH_CHECK(g.K % 64 == 0, "conv2d_stats: output channels must be a multiple of 64");
+  at::Tensor sums = at::zeros({2 * g.K}, input.options().dtype(at::kDouble));
+  at::Tensor out = forward_impl(input, weight, std::nullopt, g, nullptr, nullptr, 0, input.scalar_type(), sums.data_ptr<double>());
+  return {out, sums};
 }
 
 }  // namespace ops

@@ -30,7 +30,10 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> batch_norm_act(const at::Tensor& 
                                                               const std::optional<at::Tensor>& running_mean,
                                                               const std::optional<at::Tensor>& running_var,
                                                               const std::optional<at::Tensor>& residual, bool training,
-                                                              double momentum, double eps, int64_t act);
+                                                              double momentum, double eps, int64_t act,
+                                                              const std::optional<at::Tensor>& channel_sums);
+std::tuple<at::Tensor, at::Tensor> conv_stats_device(const at::Tensor& input, const at::Tensor& weight, at::IntArrayRef stride,
+                                                     at::IntArrayRef padding);
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_backward(
     const at::Tensor& grad_out, const at::Tensor& out, const at::Tensor& input, const std::optional<at::Tensor>& weight,
     const std::optional<at::Tensor>& running_mean, const at::Tensor& save_mean, const at::Tensor& save_invstd, bool training,
@@ -74,7 +77,9 @@ TORCH_LIBRARY(catch_b200, m) {
         "float beta1, float beta2, float eps, float weight_decay, int step, float grad_scale, bool adam_l2_mode) -> ()");
   m.def("dump(Tensor t) -> bool");
   m.def("batch_norm_act(Tensor input, Tensor? weight, Tensor? bias, Tensor(a!)? running_mean, Tensor(b!)? running_var, "
-        "Tensor? residual, bool training, float momentum, float eps, int act) -> (Tensor, Tensor, Tensor)");
+        "Tensor? residual, bool training, float momentum, float eps, int act, Tensor? channel_sums=None) -> (Tensor, Tensor, Tensor)");
+  // convolution (no bias, 16-bit) that also returns fp64 [2 * Cout] channel sums / sums of squares of its output
+  m.def("conv2d_stats(Tensor input, Tensor weight, int[] stride, int[] padding) -> (Tensor, Tensor)");
   m.def("batch_norm_act_backward(Tensor grad_out, Tensor out, Tensor input, Tensor? weight, Tensor? running_mean, "
         "Tensor save_mean, Tensor save_invstd, bool training, int act, bool has_residual) -> (Tensor, Tensor, Tensor, Tensor)");
 }
@@ -87,6 +92,7 @@ TORCH_LIBRARY_IMPL(catch_b200, CompositeExplicitAutograd, m) {
   m.impl("fused_adamw_step", TORCH_FN(fused_adamw_step));
   m.impl("dump", TORCH_FN(dump_tensor_device));
   m.impl("batch_norm_act", TORCH_FN(batch_norm_act));
+  m.impl("conv2d_stats", TORCH_FN(conv_stats_device));
   m.impl("batch_norm_act_backward", TORCH_FN(batch_norm_act_backward));
 }
 

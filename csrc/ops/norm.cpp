@@ -225,7 +225,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> batch_norm_act(const at::Tensor& 
                                                               const std::optional<at::Tensor>& running_mean,
                                                               const std::optional<at::Tensor>& running_var,
                                                               const std::optional<at::Tensor>& residual, bool training,
-                                                              double momentum, double eps, int64_t act) {
+                                                              double momentum, double eps, int64_t act,
+                                                              const std::optional<at::Tensor>& channel_sums) {
   const bool has_res = residual.has_value() && residual->defined();
   auto compose = [&]() {
     auto r = at::native_batch_norm(input, weight, bias, running_mean, running_var, training, momentum, eps);
@@ -261,8 +262,17 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> batch_norm_act(const at::Tensor& 
   if (training) {
     save_mean = at::empty({C}, fopt);
     save_invstd = at::empty({C}, fopt);
-    at::Tensor sums = at::zeros({2 * C}, input.options().dtype(at::kDouble));
-    B200_KERNEL_CHECK(b200_bn_stats(v.t.data_ptr(), xdt, v.rows, C, sums.data_ptr<double>(), scope.stream()));
+    // sums supplied by the producing convolution make the statistics pass unnecessary
+    at::Tensor sums;
+    if (channel_sums.has_value() && channel_sums->defined()) {
+      TORCH_CHECK(is_b200(*channel_sums) && channel_sums->scalar_type() == at::kDouble && channel_sums->numel() == 2 * C &&
+                      channel_sums->is_contiguous(),
+                  "batch_norm_act: channel_sums must be a contiguous fp64 tensor of 2 * C elements on the device");
+      sums = *channel_sums;
+    } else {
+      sums = at::zeros({2 * C}, input.options().dtype(at::kDouble));
+      B200_KERNEL_CHECK(b200_bn_stats(v.t.data_ptr(), xdt, v.rows, C, sums.data_ptr<double>(), scope.stream()));
+    }
     void* rm = nullptr;
     void* rv = nullptr;
     int rdt = B200_F32;

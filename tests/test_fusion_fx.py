@@ -5,7 +5,7 @@ import torch
 import torchvision
 
 import catch_b200  # noqa: F401
-from catch_b200.fusion import BatchNormAct2d, fuse_bn_act
+from catch_b200.fusion import BatchNormAct2d, StatsConv2d, fuse_bn_act
 
 
 def test_fuse_resnet_keeps_semantics_and_state_dict():
@@ -14,7 +14,10 @@ def test_fuse_resnet_keeps_semantics_and_state_dict():
     fused = fuse_bn_act(copy.deepcopy(ref))
     assert fused.fused_bn_act_count == 1 + 8 + 8  # stem + conv1 of every block + the residual joins
     assert set(fused.state_dict()) == set(ref.state_dict())
-    assert sum(isinstance(m, BatchNormAct2d) for m in fused.modules()) == 17
+    # the three downsample batch norms have no ReLU but still take their statistics from the convolution
+    assert sum(isinstance(m, BatchNormAct2d) for m in fused.modules()) == 20
+    assert sum(isinstance(m, BatchNormAct2d) and m.act == 0 for m in fused.modules()) == 3
+    assert sum(isinstance(m, StatsConv2d) for m in fused.modules()) == 20
     x = torch.randn(4, 3, 64, 64)
     y_ref, y = ref(x), fused(x)
     assert torch.allclose(y, y_ref, atol=1e-5)

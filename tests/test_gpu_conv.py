@@ -76,3 +76,22 @@ def test_conv_bias():
     dconv.load_state_dict(conv.state_dict())
     out = dconv.to(DEV)(x.to(DEV))
     assert_tensors_equal(out, ref, prec=2e-2, use_MSE=True)
+
+
+@pytest.mark.parametrize("case", [(8, 64, 56, 56, 64, 3, 1, 1), (8, 64, 28, 28, 256, 1, 1, 0), (4, 128, 30, 30, 128, 3, 2, 1),
+                                  (3, 256, 14, 14, 320, 1, 1, 0), (64, 512, 7, 7, 512, 3, 1, 1)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_conv2d_stats_matches_output(case, dtype):
+    """The channel sums accumulated in the epilogue equal sums over the stored output."""
+    N, C, H, W, K, R, stride, pad = case
+    torch.manual_seed(1)
+    x = (torch.randn(N, C, H, W) + 0.3).to(dtype).to(DEV).contiguous(memory_format=torch.channels_last)
+    w = (torch.randn(K, C, R, R) / (C * R * R) ** 0.5).to(dtype).to(DEV).contiguous(memory_format=torch.channels_last)
+    y, sums = torch.ops.catch_b200.conv2d_stats(x, w, [stride, stride], [pad, pad])
+    ref = F.conv2d(x.cpu().float(), w.cpu().float(), None, stride, pad)
+    assert_tensors_equal(y, ref, prec=2e-2, use_MSE=True, msg="fprop")
+    yd = y.cpu().double()
+    s_ref = torch.cat([yd.sum((0, 2, 3)), (yd * yd).sum((0, 2, 3))])
+    assert sums.dtype == torch.float64 and sums.shape == (2 * K,)
+    rel = (sums.cpu() - s_ref).abs() / (s_ref.abs() + 1e-2 * s_ref.abs().max())
+    assert rel.max().item() < 5e-5, rel.max().item()

@@ -252,3 +252,45 @@ def test_fused_bn_act_matches_unfused():
     assert_tensors_equal(fb.weight.grad, bn.weight.grad, prec=3e-3, use_MSE=True)
     assert_tensors_equal(fb.bias.grad, bn.bias.grad, prec=3e-3, use_MSE=True)
     assert_tensors_equal(fb.running_var, bn.running_var, prec=3e-3, use_MSE=True)
+
+
+def test_conv_statistics_feed_batch_norm_under_autocast():
+    """bf16 autocast: convolutions hand their channel sums to the following batch norm; the
+    running statistics and the loss must match the model that runs the separate statistics pass."""
+    import torchvision
+    import catch_b200
+    from catch_b200.fusion import StatsConv2d, fuse_bn_act
+
+    torch.manual_seed(9)
+    ref = torchvision.models.resnet18(num_classes=16)
+    fused = fuse_bn_act(copy.deepcopy(ref)).to(DEV).to(memory_format=torch.channels_last)
+    assert sum(isinstance(m, StatsConv2d) for m in fused.modules()) == 20
+    # same fused model with plain convolutions: the only difference is where the statistics come from
+    base = copy.deepcopy(fused)
+    for m in base.modules():
+        if isinstance(m, StatsConv2d):
+            m.__class__ = torch.nn.Conv2d
+    x = torch.randn(16, 3, 64, 64).to(DEV)
+    t = torch.randint(0, 16, (16,)).to(DEV)
+    launches = []
+    losses = []
+    for m in (base, fused):
+        catch_b200._C._reset_kernel_launch_count()
+        with torch.autocast(DEV, dtype=torch.bfloat16):
+            loss = F.cross_entropy(m(x), t)
+        loss.backward()
+        launches.append(catch_b200._C._kernel_launch_count())
+        losses.append(loss.item())
+    assert abs(losses[0] - losses[1]) < 1e-2, losses
+    assert launches[1] <= launches[0] - 19  # one statistics kernel fewer per convolution that feeds a batch norm
+    for (n, a), (_, b) in zip(base.named_buffers(), fused.named_buffers()):
+        assert_tensors_equal(b.float(), a.float(), prec=2e-2, use_MSE=True, msg=n)
+    bad = {}
+    for (n, a), (_, b) in zip(base.named_parameters(), fused.named_parameters()):
+        ga, gb = a.grad.double().flatten().cpu(), b.grad.double().flatten().cpu()
+        cos = (ga @ gb / (ga.norm() * gb.norm() + 1e-30)).item()
+        # the sums agree to ~1e-5; after bf16 rounding that is enough to flip a few ReLU masks, which
+        # is what limits the agreement of whole-network bf16 gradients
+        if cos < 0.96:
+            bad[n] = round(cos, 4)
+    assert not bad, bad
