@@ -388,6 +388,46 @@ B200_API int b200_quantize_int8_rows(const void* w, int w_dtype, long long rows,
 // abs-max of a tensor into *out (fp32, must be zero-initialised; uses an atomic max on the bit pattern)
 B200_API int b200_absmax(const void* x, int x_dtype, long long n, float* out, void* stream);
 
+// ---- indexing, sorting, resampling, NMS, depthwise convolution (indexing.cu) ------------
+// Gather / scatter along dimension `dim`.  `sizes` is the shape of the (contiguous) index tensor;
+// a = the indexed tensor, b = the tensor shaped like the index, both addressed with element strides.
+// mode 0: b[i] = a[index[i]]; 1: a[index[i]] = b[i]; 2: a[index[i]] += b[i] (fp32).  An index out of
+// range sets *bad_flag (device int) and is skipped.
+B200_API int b200_dim_index(void* a, void* b, int elem_bytes, const long long* index, int ndim, int dim,
+                            const long long* sizes, const long long* a_strides, const long long* b_strides,
+                            long long dim_size, int mode, int* bad_flag, void* stream);
+// out[o][n][:] = src[o][idx[n]][:] for src of shape [outer][n_src][row_bytes]
+B200_API int b200_take_rows(const void* src, const long long* idx, long long outer, long long n_src, long long n_idx,
+                            long long row_bytes, void* out, int* bad_flag, void* stream);
+// dst[o][idx[n]][:] = (or += for fp32 when accumulate) values[o][n][:]
+B200_API int b200_put_rows(void* dst, const long long* idx, long long outer, long long n_dst, long long n_idx,
+                           long long row_elems, int elem_bytes, const void* values, int accumulate, int* bad_flag,
+                           void* stream);
+// nonzero in two passes over a contiguous tensor of n elements; workspace holds
+// b200_nonzero_workspace_elems(n) int64 values, the last of which receives the count after pass 1.
+B200_API long long b200_nonzero_workspace_elems(long long n);
+B200_API int b200_nonzero_count(const void* x, int elem_bytes, int is_float, long long n, long long* workspace, void* stream);
+B200_API int b200_nonzero_write(const void* x, int elem_bytes, int is_float, long long n, const long long* workspace,
+                                int ndim, const long long* sizes, long long* out, void* stream);
+B200_API int b200_arange(void* out, int dtype, long long n, double start, double step, void* stream);
+B200_API int b200_tri(const void* in, void* out, int elem_bytes, long long batch, long long rows, long long cols,
+                      long long k, int upper, void* stream);
+B200_API int b200_sort_rows_max_len(void);
+B200_API int b200_sort_rows(const void* x, int dtype, int elem_bytes, long long rows, int len, int descending, int k,
+                            void* values, long long* indices, void* stream);
+// mode 0 nearest, 1 bilinear; backward: `out` holds the output gradient and the input gradient is
+// accumulated into in_acc (zeroed fp32, contiguous NCHW).  sizes = {N, C, H, W, OH, OW}.
+B200_API int b200_resample2d(const void* in, void* out, int dtype, const long long* sizes, const long long* in_strides,
+                             const long long* out_strides, double scale_h, double scale_w, int align_corners, int mode,
+                             int backward, float* in_acc, void* stream);
+// boxes (x1, y1, x2, y2) fp32 sorted by descending score; mask is [n][ceil(n/64)] words
+B200_API int b200_nms_mask(const float* sorted_boxes, int n, float iou_threshold, unsigned long long* mask, void* stream);
+// dims = {N, C, H, W, K, P, Q}; conv = {R, S, stride_h, stride_w, pad_h, pad_w}; weight contiguous [K][1][R][S].
+// pass 0: y = conv(x, w).  pass 1: x is the input-gradient buffer to fill, y the output gradient.
+// pass 2: w is the fp32 [K][R][S] weight-gradient buffer to fill, y the output gradient, x the input.
+B200_API int b200_depthwise_conv(int pass, const void* x, const void* w, void* y, int dtype, const long long* dims,
+                                 const int* conv, const long long* x_strides, const long long* y_strides, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

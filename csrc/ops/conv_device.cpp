@@ -305,11 +305,116 @@ Tensor wgrad_impl(const Tensor& grad_in, const Tensor& input, const Tensor& weig
   return out;
 }
 
+
+// ---- depthwise (groups == Cin, one filter per output channel): direct CUDA-core kernels ----
+bool is_depthwise(const Tensor& input, const Tensor& weight, int64_t groups) {
+  return groups > 1 && groups == input.size(1) && weight.size(1) == 1 && weight.size(0) % groups == 0;
+}
+void check_depthwise(const Tensor& input, at::IntArrayRef dilation, bool transposed) {
+  TORCH_CHECK(!transposed && dilation[0] == 1 && dilation[1] == 1, "b200 depthwise conv: no dilation / transposition on the device");
+  const auto t = input.scalar_type();
+  TORCH_CHECK(t == at::kFloat || t == at::kBFloat16 || t == at::kHalf, "b200 depthwise conv: unsupported dtype ", t);
+  TORCH_CHECK(input.dim() == 4, "b200 depthwise conv: 4-D input expected");
+}
+struct DwCall {
+  long long dims[7];
+  int conv[6];
+  std::vector<long long> xs, ys;
+};
+DwCall dw_call(const ConvGeom& g, const Tensor& x_like, const Tensor& y_like) {
+  DwCall c;
+  const long long d[7] = {g.N, g.C, g.H, g.W, g.K, g.P, g.Q};
+  std::copy(d, d + 7, c.dims);
+  const int cv[6] = {(int)g.R, (int)g.S, (int)g.sh, (int)g.sw, (int)g.ph, (int)g.pw};
+  std::copy(cv, cv + 6, c.conv);
+  c.xs.assign(x_like.strides().begin(), x_like.strides().end());
+  c.ys.assign(y_like.strides().begin(), y_like.strides().end());
+  return c;
+}
+Tensor depthwise_forward(const Tensor& input, const Tensor& weight, const std::optional<Tensor>& bias, const ConvGeom& g) {
+  OpScope scope("depthwise_conv", input);
+  Tensor out = empty_b200({g.N, g.K, g.P, g.Q}, input.scalar_type(), input.device().index(), input.suggest_memory_format());
+  Tensor w = weight.to(input.scalar_type()).contiguous();
+  DwCall c = dw_call(g, input, out);
+  B200_KERNEL_CHECK(b200_depthwise_conv(0, input.data_ptr(), w.data_ptr(), out.data_ptr(), to_b200_dtype(input.scalar_type()), c.dims,
+                                        c.conv, c.xs.data(), c.ys.data(), scope.stream()));
+  if (bias.has_value() && bias->defined()) out.add_(bias->view({1, -1, 1, 1}));
+  return out;
+}
+std::tuple<Tensor, Tensor, Tensor> depthwise_backward(const Tensor& grad_in, const Tensor& input, const Tensor& weight,
+                                                      const ConvGeom& g, std::array<bool, 3> mask) {
+  OpScope scope("depthwise_conv_backward", grad_in);
+  Tensor grad = grad_in.to(input.scalar_type());
+  Tensor dx, dw, db;
+  const int dt = to_b200_dtype(input.scalar_type());
+  if (mask[0]) {
+    dx = at::empty_strided(input.sizes(), input.strides(), input.options());
+    if (!dx.is_non_overlapping_and_dense()) dx = at::empty_like(input, at::MemoryFormat::Contiguous);
+    Tensor w = weight.to(input.scalar_type()).contiguous();
+    DwCall c = dw_call(g, dx, grad);
+    B200_KERNEL_CHECK(b200_depthwise_conv(1, dx.data_ptr(), w.data_ptr(), grad.data_ptr(), dt, c.dims, c.conv, c.xs.data(),
+                                          c.ys.data(), scope.stream()));
+  }
+  if (mask[1]) {
+    Tensor acc = at::empty({g.K, 1, g.R, g.S}, input.options().dtype(at::kFloat));
+    DwCall c = dw_call(g, input, grad);
+    B200_KERNEL_CHECK(b200_depthwise_conv(2, input.data_ptr(), acc.data_ptr(), grad.data_ptr(), dt, c.dims, c.conv, c.xs.data(),
+                                          c.ys.data(), scope.stream()));
+    dw = acc.to(weight.scalar_type());
+  }
+  if (mask[2]) db = grad_in.sum({0, 2, 3});
+  return {dx, dw, db};
+}
+
+// ---- transposed convolution = the data gradient of the matching forward convolution ----
+ConvGeom transposed_geom(const Tensor& input, const Tensor& weight, at::IntArrayRef stride, at::IntArrayRef padding,
+                         at::IntArrayRef output_padding) {
+  // weight [Cin, Cout, R, S]; the matching forward convolution maps [N, Cout, Hout, Wout] -> [N, Cin, H, W]
+  ConvGeom g;
+  g.N = input.size(0); g.K = weight.size(0); g.C = weight.size(1); g.R = weight.size(2); g.S = weight.size(3);
+  g.sh = stride[0]; g.sw = stride[1]; g.ph = padding[0]; g.pw = padding[1];
+  g.P = input.size(2); g.Q = input.size(3);
+  g.H = (g.P - 1) * g.sh - 2 * g.ph + g.R + (output_padding.empty() ? 0 : output_padding[0]);
+  g.W = (g.Q - 1) * g.sw - 2 * g.pw + g.S + (output_padding.empty() ? 0 : output_padding[1]);
+  return g;
+}
+
 }  // namespace
 
 at::Tensor conv_forward_device(const at::Tensor& input, const at::Tensor& weight, const std::optional<at::Tensor>& bias,
                                at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation,
-                               bool transposed, at::IntArrayRef, int64_t groups) {
+                               bool transposed, at::IntArrayRef output_padding, int64_t groups) {
+  if (transposed) {
+    TORCH_CHECK(groups == 1 && input.dim() == 4 && weight.dim() == 4 && dilation[0] == 1 && dilation[1] == 1,
+                "b200 transposed conv: only dense 2-D transposed convolutions without dilation run on the device");
+    TORCH_CHECK(stride[0] >= 1 && stride[0] <= 2 && stride[1] >= 1 && stride[1] <= 2, "b200 conv: stride must be 1 or 2");
+    TORCH_CHECK(input.size(1) == weight.size(0), "conv_transpose: channel mismatch");
+    TORCH_CHECK(weight.size(0) % 8 == 0 && weight.size(1) % 8 == 0, "b200 transposed conv: channel counts must be multiples of 8");
+    ConvGeom g = transposed_geom(input, weight, stride, padding, output_padding);
+    TORCH_CHECK(g.H > 0 && g.W > 0, "conv_transpose: output size is too small");
+    at::Tensor out = dgrad_impl(input, weight, g, input.scalar_type());
+    if (bias.has_value() && bias->defined()) out.add_(bias->view({1, -1, 1, 1}));
+    return out;
+  }
+  if (is_depthwise(input, weight, groups)) {
+    check_depthwise(input, dilation, transposed);
+    ConvGeom g = geom(input, weight, stride, padding);
+    TORCH_CHECK(g.P > 0 && g.Q > 0, "conv: output size is too small");
+    return depthwise_forward(input, weight, bias, g);
+  }
+  if (groups > 1) {
+    // grouped: one dense convolution per group on channel slices
+    TORCH_CHECK(input.size(1) % groups == 0 && weight.size(0) % groups == 0, "conv: channels not divisible by groups");
+    const int64_t cg = input.size(1) / groups, kg = weight.size(0) / groups;
+    std::vector<at::Tensor> outs;
+    for (int64_t i = 0; i < groups; ++i) {
+      std::optional<at::Tensor> bg;
+      if (bias.has_value() && bias->defined()) bg = bias->narrow(0, i * kg, kg);
+      outs.push_back(conv_forward_device(input.narrow(1, i * cg, cg), weight.narrow(0, i * kg, kg), bg, stride, padding, dilation,
+                                         false, output_padding, 1));
+    }
+    return at::cat(outs, 1);
+  }
   check_supported(input, weight, stride, padding, dilation, transposed, groups);
   TORCH_CHECK(input.size(1) == weight.size(1), "conv: channel mismatch");
   ConvGeom g = geom(input, weight, stride, padding);
@@ -319,8 +424,41 @@ at::Tensor conv_forward_device(const at::Tensor& input, const at::Tensor& weight
 
 std::tuple<at::Tensor, at::Tensor, at::Tensor> conv_backward_device(
     const at::Tensor& grad, const at::Tensor& input, const at::Tensor& weight, at::IntArrayRef stride,
-    at::IntArrayRef padding, at::IntArrayRef dilation, bool transposed, at::IntArrayRef, int64_t groups,
+    at::IntArrayRef padding, at::IntArrayRef dilation, bool transposed, at::IntArrayRef output_padding, int64_t groups,
     std::array<bool, 3> mask) {
+  if (transposed) {
+    TORCH_CHECK(groups == 1 && dilation[0] == 1 && dilation[1] == 1 && input.dim() == 4,
+                "b200 transposed conv backward: only dense 2-D transposed convolutions run on the device");
+    TORCH_CHECK(weight.size(0) % 8 == 0 && weight.size(1) % 8 == 0, "b200 transposed conv: channel counts must be multiples of 8");
+    ConvGeom g = transposed_geom(input, weight, stride, padding, output_padding);
+    TORCH_CHECK(g.H == grad.size(2) && g.W == grad.size(3), "conv_transpose backward: gradient shape mismatch");
+    at::Tensor dx, dw, db;
+    // d(input) is the forward convolution of the output gradient; d(weight) is the weight gradient of
+    // that convolution with the roles of activation and gradient exchanged
+    if (mask[0]) dx = forward_impl(grad, weight, std::nullopt, g, nullptr, nullptr, 0, input.scalar_type());
+    if (mask[1]) dw = wgrad_impl(input, grad, weight, g);
+    if (mask[2]) db = grad.sum({0, 2, 3});
+    return {dx, dw, db};
+  }
+  if (is_depthwise(input, weight, groups)) {
+    check_depthwise(input, dilation, transposed);
+    return depthwise_backward(grad, input, weight, geom(input, weight, stride, padding), mask);
+  }
+  if (groups > 1) {
+    const int64_t cg = input.size(1) / groups, kg = weight.size(0) / groups;
+    std::vector<at::Tensor> dxs, dws;
+    for (int64_t i = 0; i < groups; ++i) {
+      auto r = conv_backward_device(grad.narrow(1, i * kg, kg), input.narrow(1, i * cg, cg), weight.narrow(0, i * kg, kg), stride,
+                                    padding, dilation, false, output_padding, 1, {mask[0], mask[1], false});
+      if (mask[0]) dxs.push_back(std::get<0>(r));
+      if (mask[1]) dws.push_back(std::get<1>(r));
+    }
+    at::Tensor dx, dw, db;
+    if (mask[0]) dx = at::cat(dxs, 1);
+    if (mask[1]) dw = at::cat(dws, 0);
+    if (mask[2]) db = grad.sum({0, 2, 3});
+    return {dx, dw, db};
+  }
   check_supported(input, weight, stride, padding, dilation, transposed, groups);
   ConvGeom g = geom(input, weight, stride, padding);
   at::Tensor dx, dw, db;

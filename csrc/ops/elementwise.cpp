@@ -198,6 +198,7 @@ B200_UNARY(floor, EW_FLOOR, false)
 B200_UNARY(round, EW_ROUND, false)
 B200_UNARY(trunc, EW_TRUNC, false)
 B200_UNARY(sign, EW_SIGN, false)
+B200_UNARY(sgn, EW_SIGN, false)  // real types only: identical to sign
 B200_UNARY(erf, EW_ERF, true)
 B200_UNARY(bitwise_not, EW_BIT_NOT, false)
 B200_UNARY(hardswish, EW_HARDSWISH, true)
@@ -469,7 +470,7 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   REG_UNARY(neg) REG_UNARY(abs) REG_UNARY(sqrt) REG_UNARY(rsqrt) REG_UNARY(reciprocal) REG_UNARY(exp)
   REG_UNARY(log) REG_UNARY(log2) REG_UNARY(log10) REG_UNARY(log1p) REG_UNARY(expm1) REG_UNARY(sin) REG_UNARY(cos)
   REG_UNARY(tanh) REG_UNARY(sigmoid) REG_UNARY(silu) REG_UNARY(ceil) REG_UNARY(floor) REG_UNARY(trunc)
-  REG_UNARY(sign) REG_UNARY(erf) REG_UNARY(bitwise_not) REG_UNARY(hardswish) REG_UNARY(hardsigmoid)
+  REG_UNARY(sign) REG_UNARY(sgn) REG_UNARY(erf) REG_UNARY(bitwise_not) REG_UNARY(hardswish) REG_UNARY(hardsigmoid)
   m.impl("round", TORCH_FN(round));
   m.impl("round_", TORCH_FN(round_));
   m.impl("round.out", TORCH_FN(round_out));
