@@ -67,13 +67,16 @@ def test_collectives_two_ranks():
     run_ranks(_collectives, world=2)
 
 
-def _ddp(rank, world):
+def _ddp(rank, world, hook=None):
     _init(rank, world)
     torch.manual_seed(0)
     net = torch.nn.Sequential(torch.nn.Linear(10, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4))
     ref = torch.nn.Sequential(torch.nn.Linear(10, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4))
     ref.load_state_dict(net.state_dict())
     ddp = torch.nn.parallel.DistributedDataParallel(net.to(DEV))
+    if hook is not None:
+        from catch_b200.parallel import hooks
+        ddp.register_comm_hook(None, getattr(hooks, hook))
     opt = torch.optim.SGD(ddp.parameters(), lr=0.05, momentum=0.9)
     opt_ref = torch.optim.SGD(ref.parameters(), lr=0.05, momentum=0.9)
     g = torch.Generator().manual_seed(1)
@@ -87,13 +90,27 @@ def _ddp(rank, world):
         opt.zero_grad()
         torch.nn.functional.mse_loss(ddp(xs), ys).backward()
         opt.step()
+    tol = 3e-2 if hook == "bf16_compress_hook" else 3e-3
     for a, b in zip(ref.parameters(), ddp.module.parameters()):
-        assert (a - b.cpu()).abs().max().item() < 3e-3
+        assert (a - b.cpu()).abs().max().item() < tol
     dist.destroy_process_group()
 
 
 def test_ddp_matches_single_process_cpu():
     run_ranks(_ddp, world=2)
+
+
+def _ddp_allreduce_hook(rank, world):
+    _ddp(rank, world, "allreduce_hook")
+
+
+def _ddp_bf16_hook(rank, world):
+    _ddp(rank, world, "bf16_compress_hook")
+
+
+def test_ddp_comm_hooks():
+    run_ranks(_ddp_allreduce_hook, world=2)
+    run_ranks(_ddp_bf16_hook, world=2)
 
 
 def _missing_peer(rank, world):
