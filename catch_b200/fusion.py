@@ -26,9 +26,10 @@ import torch.nn.functional as F
 class _BNActFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, running_mean, running_var, residual, training, momentum, eps, act, sums=None):
-        out, mean, invstd = torch.ops.catch_b200.batch_norm_act(x, weight, bias, running_mean, running_var, residual,
-                                                                training, momentum, eps, act, sums)
-        ctx.save_for_backward(out, x, weight, running_mean, mean, invstd)
+        out, mean, invstd, mask = torch.ops.catch_b200.batch_norm_act_mask(x, weight, bias, running_mean, running_var,
+                                                                           residual, training, momentum, eps, act, sums)
+        # with a ReLU the backward only needs to know which outputs were positive: one bit each
+        ctx.save_for_backward(mask if mask.numel() else out, x, weight, running_mean, mean, invstd)
         ctx.cfg = (training, act, residual is not None)
         return out
 

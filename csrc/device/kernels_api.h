@@ -203,6 +203,12 @@ B200_API int b200_bn_invstd_from_var(const void* var, int var_dtype, int C, floa
 B200_API int b200_bn_apply(const void* x, int x_dtype, void* y, int y_dtype, long long rows, int C, const void* mean,
                            int mean_dtype, const float* invstd, const void* gamma, const void* beta, int param_dtype,
                            const void* residual, int res_dtype, int act, void* stream);
+// Same, and with act == 1 on 16-bit activations also writes one bit per element (byte i holds elements
+// 8i .. 8i+7, bit set when the output is positive) to relu_mask: the backward kernels accept that mask in
+// place of the ReLU output (pass it as relu_out with dtype B200_U8) and then read 1/16 of the bytes.
+B200_API int b200_bn_apply_mask(const void* x, int x_dtype, void* y, int y_dtype, long long rows, int C, const void* mean,
+                                int mean_dtype, const float* invstd, const void* gamma, const void* beta, int param_dtype,
+                                const void* residual, int res_dtype, int act, void* relu_mask, void* stream);
 // Backward reductions (fp64, zero `sums` first): sums[c] = sum dy, sums[C+c] = sum dy * xhat.
 // If `relu_out` is given dy is first masked by relu_out > 0 (fused ReLU backward).
 B200_API int b200_bn_backward_reduce(const void* dy, int dy_dtype, const void* x, int x_dtype, const void* mean,

@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(const TX* x, TY* y, long 
 template <typename T>
 __global__ void __launch_bounds__(RED_THREADS)
 bn_bwd_reduce_kernel(const T* dy, const T* x, const void* mean, int mdt, const float* invstd, const T* relu_out,
-                     long long rows, int C, double* sums) {
+                     const uint8_t* relu_mask, long long rows, int C, double* sums) {
   constexpr int V = VecOf<T>::N;
   // accumulates sum(dy) and sum(dy * (x - mean)); the second is scaled by invstd when folded
   column_reduce<T, 2>(
@@ -201,10 +201,12 @@ bn_bwd_reduce_kernel(const T* dy, const T* x, const void* mean, int mdt, const f
         load_vec<T>(dy + r * C + c0, g);
         load_vec<T>(x + r * C + c0, v);
         if (relu_out) load_vec<T>(relu_out + r * C + c0, o);
+        const unsigned bits = relu_mask ? relu_mask[(r * C + c0) / V] : 0xffu;
 #pragma unroll
         for (int i = 0; i < V; ++i) {
           float gi = g[i];
           if (relu_out && !(o[i] > 0.f)) gi = 0.f;
+          if (!((bits >> i) & 1u)) gi = 0.f;
           acc[0][i] += gi;
           acc[1][i] += gi * (v[i] - mu[i]);
         }
@@ -252,7 +254,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 bn_apply_fast_kernel(const T* __restrict__ x, T* __restrict__ y, unsigned nvec, int C, const void* mean, int mdt,
                      const float* invstd, const void* gamma, const void* beta, int pdt, const T* __restrict__ res,
-                     int act) {
+                     int act, uint8_t* __restrict__ relu_mask) {
   constexpr int V = VecOf<T>::N;
   extern __shared__ float coef[];
   float* S = coef;
@@ -269,14 +271,19 @@ bn_apply_fast_kernel(const T* __restrict__ x, T* __restrict__ y, unsigned nvec, 
     float v[V], r[V];
     load_vec<T>(x + (size_t)i * V, v);
     if (res) load_vec<T>(res + (size_t)i * V, r);
+    unsigned bits = 0;
 #pragma unroll
     for (int k = 0; k < V; ++k) {
       float t = fmaf(v[k], S[c0 + k], Tc[c0 + k]);
       if (res) t += r[k];
-      if (act == 1) t = t > 0.f ? t : 0.f;
+      if (act == 1) {
+        bits |= (t > 0.f ? 1u : 0u) << k;
+        t = t > 0.f ? t : 0.f;
+      }
       v[k] = t;
     }
     store_vec<T>(y + (size_t)i * V, v);
+    if (relu_mask) relu_mask[i] = (uint8_t)bits;  // one bit per element (V == 8): all the backward needs of the output
   }
 }
 
@@ -286,7 +293,7 @@ __global__ void __launch_bounds__(256)
 bn_bwd_apply_fast_kernel(const T* __restrict__ dy, const T* __restrict__ x, const void* mean, int mdt,
                          const float* invstd, const void* gamma, int pdt, const T* __restrict__ relu_out,
                          const double* sums, long long rows, int C, int training, T* __restrict__ dx, unsigned nvec,
-                         T* __restrict__ dres) {
+                         T* __restrict__ dres, const uint8_t* __restrict__ relu_mask) {
   constexpr int V = VecOf<T>::N;
   extern __shared__ float coef[];
   float* A = coef;
@@ -318,6 +325,12 @@ bn_bwd_apply_fast_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
 #pragma unroll
       for (int k = 0; k < V; ++k)
         if (!(o[k] > 0.f)) g[k] = 0.f;
+    }
+    if (relu_mask) {
+      const unsigned bits = relu_mask[i];
+#pragma unroll
+      for (int k = 0; k < V; ++k)
+        if (!((bits >> k) & 1u)) g[k] = 0.f;
     }
     if (dres) store_vec<T>(dres + (size_t)i * V, g);  // gradient of the fused residual input: the masked dy
 #pragma unroll
@@ -467,10 +480,19 @@ extern "C" int b200_bn_invstd_from_var(const void* var, int dt, int C, float eps
   return (int)cudaGetLastError();
 }
 
+extern "C" int b200_bn_apply_mask(const void* x, int xdt, void* y, int ydt, long long rows, int C, const void* mean, int mdt,
+                                  const float* invstd, const void* gamma, const void* beta, int pdt, const void* res,
+                                  int rdt, int act, void* relu_mask, void* stream);
 extern "C" int b200_bn_apply(const void* x, int xdt, void* y, int ydt, long long rows, int C, const void* mean, int mdt,
                              const float* invstd, const void* gamma, const void* beta, int pdt, const void* res,
                              int rdt, int act, void* stream) {
+  return b200_bn_apply_mask(x, xdt, y, ydt, rows, C, mean, mdt, invstd, gamma, beta, pdt, res, rdt, act, nullptr, stream);
+}
+extern "C" int b200_bn_apply_mask(const void* x, int xdt, void* y, int ydt, long long rows, int C, const void* mean, int mdt,
+                                  const float* invstd, const void* gamma, const void* beta, int pdt, const void* res,
+                                  int rdt, int act, void* relu_mask, void* stream) {
   if (rows <= 0 || C <= 0) return 0;
+  if (relu_mask && (xdt == B200_F32 || act != 1)) return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   const long long n = rows * C;
   // fast path: same 16-bit / fp32 type in and out, coefficients fit in shared memory
@@ -481,10 +503,11 @@ extern "C" int b200_bn_apply(const void* x, int xdt, void* y, int ydt, long long
       const size_t sm = sizeof(float) * 2 * C;
       DISPATCH_FLOAT(xdt, T, (bn_apply_fast_kernel<T><<<ew_grid_u(nvec), 256, sm, s>>>(
                                  static_cast<const T*>(x), static_cast<T*>(y), nvec, C, mean, mdt, invstd, gamma, beta,
-                                 pdt, static_cast<const T*>(res), act)));
+                                 pdt, static_cast<const T*>(res), act, V == 8 ? static_cast<uint8_t*>(relu_mask) : nullptr)));
       return (int)cudaGetLastError();
     }
   }
+  if (relu_mask) return (int)cudaErrorInvalidValue;  // the mask is produced by the fast path only
 #define BN_APPLY(TX, TY)                                                                                            \
   {                                                                                                                 \
     constexpr int V = VecOf<TX>::N > VecOf<TY>::N ? VecOf<TY>::N : VecOf<TX>::N;                                    \
@@ -508,14 +531,17 @@ extern "C" int b200_bn_backward_reduce(const void* dy, int dt, const void* x, in
                                        const float* invstd, const void* relu_out, int rdt, long long rows, int C,
                                        double* sums, void* stream) {
   if (rows <= 0 || C <= 0) return 0;
-  if (dt != xdt || (relu_out && rdt != dt)) return (int)cudaErrorInvalidValue;
+  // rdt == B200_U8: relu_out is a bit mask (one byte per 8 consecutive elements, 16-bit activations only)
+  const bool is_mask = relu_out && rdt == B200_U8;
+  if (dt != xdt || (relu_out && !is_mask && rdt != dt) || (is_mask && dt == B200_F32)) return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   DISPATCH_FLOAT(dt, T, {
     constexpr int V = VecOf<T>::N;
     if (C % V) return (int)cudaErrorInvalidValue;
     bn_bwd_reduce_kernel<T><<<red_grid(rows), RED_THREADS, red_smem(C, V, 2), s>>>(
-        static_cast<const T*>(dy), static_cast<const T*>(x), mean, mdt, invstd, static_cast<const T*>(relu_out), rows, C,
-        sums);
+        static_cast<const T*>(dy), static_cast<const T*>(x), mean, mdt, invstd,
+        is_mask ? nullptr : static_cast<const T*>(relu_out), (is_mask && V == 8) ? static_cast<const uint8_t*>(relu_out) : nullptr,
+        rows, C, sums);
   });
   return (int)cudaGetLastError();
 }
@@ -525,9 +551,11 @@ extern "C" int b200_bn_backward_apply(const void* dy, int dt, const void* x, int
                                       const double* sums, long long rows, int C, int training, void* dx, int dxdt,
                                       float* dgamma, float* dbeta, void* dres, void* stream) {
   if (rows <= 0 || C <= 0) return 0;
-  if (dt != xdt || (relu_out && rdt != dt)) return (int)cudaErrorInvalidValue;
+  const bool is_mask = relu_out && rdt == B200_U8;
+  if (dt != xdt || (relu_out && !is_mask && rdt != dt) || (is_mask && dt == B200_F32)) return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   const long long n = rows * C;
+  if (is_mask && !(dx && dxdt == dt && C <= 8192 && C % 8 == 0 && n / 8 < 0xffffffffLL)) return (int)cudaErrorInvalidValue;
   if (dres && !(dx && dxdt == dt && C <= 8192 && C % (dt == B200_F32 ? 4 : 8) == 0)) return (int)cudaErrorInvalidValue;
   if (dx && dxdt == dt && C <= 8192 && C % (dt == B200_F32 ? 4 : 8) == 0 && n / (dt == B200_F32 ? 4 : 8) < 0xffffffffLL) {
     const int V = dt == B200_F32 ? 4 : 8;
@@ -535,8 +563,9 @@ extern "C" int b200_bn_backward_apply(const void* dy, int dt, const void* x, int
     const size_t sm = sizeof(float) * 3 * C;
     DISPATCH_FLOAT(dt, T, (bn_bwd_apply_fast_kernel<T><<<ew_grid_u(nvec), 256, sm, s>>>(
                                static_cast<const T*>(dy), static_cast<const T*>(x), mean, mdt, invstd, gamma, pdt,
-                               static_cast<const T*>(relu_out), sums, rows, C, training, static_cast<T*>(dx), nvec,
-                               static_cast<T*>(dres))));
+                               is_mask ? nullptr : static_cast<const T*>(relu_out), sums, rows, C, training,
+                               static_cast<T*>(dx), nvec, static_cast<T*>(dres),
+                               (is_mask && V == 8) ? static_cast<const uint8_t*>(relu_out) : nullptr)));
     dx = nullptr;  // done
   }
   if (dx) {

@@ -32,6 +32,11 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> batch_norm_act(const at::Tensor& 
                                                               const std::optional<at::Tensor>& residual, bool training,
                                                               double momentum, double eps, int64_t act,
                                                               const std::optional<at::Tensor>& channel_sums);
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_mask(
+    const at::Tensor& input, const std::optional<at::Tensor>& weight, const std::optional<at::Tensor>& bias,
+    const std::optional<at::Tensor>& running_mean, const std::optional<at::Tensor>& running_var,
+    const std::optional<at::Tensor>& residual, bool training, double momentum, double eps, int64_t act,
+    const std::optional<at::Tensor>& channel_sums);
 std::tuple<at::Tensor, at::Tensor> conv_stats_device(const at::Tensor& input, const at::Tensor& weight, at::IntArrayRef stride,
                                                      at::IntArrayRef padding);
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_backward(
@@ -78,6 +83,10 @@ TORCH_LIBRARY(catch_b200, m) {
   m.def("dump(Tensor t) -> bool");
   m.def("batch_norm_act(Tensor input, Tensor? weight, Tensor? bias, Tensor(a!)? running_mean, Tensor(b!)? running_var, "
         "Tensor? residual, bool training, float momentum, float eps, int act, Tensor? channel_sums=None) -> (Tensor, Tensor, Tensor)");
+  // like batch_norm_act; the 4th result is a bit mask of the positive outputs (empty if not produced) that
+  // batch_norm_act_backward accepts in place of `out`
+  m.def("batch_norm_act_mask(Tensor input, Tensor? weight, Tensor? bias, Tensor(a!)? running_mean, Tensor(b!)? running_var, "
+        "Tensor? residual, bool training, float momentum, float eps, int act, Tensor? channel_sums=None) -> (Tensor, Tensor, Tensor, Tensor)");
   // convolution (no bias, 16-bit) that also returns fp64 [2 * Cout] channel sums / sums of squares of its output
   m.def("conv2d_stats(Tensor input, Tensor weight, int[] stride, int[] padding) -> (Tensor, Tensor)");
   m.def("batch_norm_act_backward(Tensor grad_out, Tensor out, Tensor input, Tensor? weight, Tensor? running_mean, "
@@ -93,6 +102,7 @@ TORCH_LIBRARY_IMPL(catch_b200, CompositeExplicitAutograd, m) {
   m.impl("dump", TORCH_FN(dump_tensor_device));
   m.impl("batch_norm_act", TORCH_FN(batch_norm_act));
   m.impl("conv2d_stats", TORCH_FN(conv_stats_device));
+  m.impl("batch_norm_act_mask", TORCH_FN(batch_norm_act_mask));
   m.impl("batch_norm_act_backward", TORCH_FN(batch_norm_act_backward));
 }
 

@@ -220,13 +220,14 @@ std::tuple<Tensor, Tensor, Tensor> k_native_batch_norm_backward(
 // the residual add costs a pass over the activation.
 }  // namespace
 
-std::tuple<at::Tensor, at::Tensor, at::Tensor> batch_norm_act(const at::Tensor& input, const std::optional<at::Tensor>& weight,
+static std::tuple<at::Tensor, at::Tensor, at::Tensor> batch_norm_act_impl(const at::Tensor& input, const std::optional<at::Tensor>& weight,
                                                               const std::optional<at::Tensor>& bias,
                                                               const std::optional<at::Tensor>& running_mean,
                                                               const std::optional<at::Tensor>& running_var,
                                                               const std::optional<at::Tensor>& residual, bool training,
                                                               double momentum, double eps, int64_t act,
-                                                              const std::optional<at::Tensor>& channel_sums) {
+                                                              const std::optional<at::Tensor>& channel_sums,
+                                                              at::Tensor* relu_mask) {
   const bool has_res = residual.has_value() && residual->defined();
   auto compose = [&]() {
     auto r = at::native_batch_norm(input, weight, bias, running_mean, running_var, training, momentum, eps);
@@ -295,10 +296,40 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> batch_norm_act(const at::Tensor& 
     mean_ptr = rmk.data_ptr();
     mdt = to_b200_dtype(rmk.scalar_type());
   }
-  B200_KERNEL_CHECK(b200_bn_apply(v.t.data_ptr(), xdt, out.data_ptr(), xdt, v.rows, C, mean_ptr, mdt,
-                                  save_invstd.data_ptr<float>(), gamma, beta, pdt, has_res ? res.data_ptr() : nullptr, xdt,
-                                  (int)act, scope.stream()));
+  void* mask_ptr = nullptr;
+  if (relu_mask && act == 1 && input.scalar_type() != at::kFloat && C % 8 == 0 && C <= 8192 && (v.rows * C) / 8 < 0xffffffffLL) {
+    // one bit per element of the ReLU output: what the backward needs instead of the output itself
+    *relu_mask = at::empty({v.rows * C / 8}, input.options().dtype(at::kByte));
+    mask_ptr = relu_mask->data_ptr();
+  }
+  B200_KERNEL_CHECK(b200_bn_apply_mask(v.t.data_ptr(), xdt, out.data_ptr(), xdt, v.rows, C, mean_ptr, mdt,
+                                       save_invstd.data_ptr<float>(), gamma, beta, pdt, has_res ? res.data_ptr() : nullptr, xdt,
+                                       (int)act, mask_ptr, scope.stream()));
   return {out, save_mean, save_invstd};
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> batch_norm_act(const at::Tensor& input, const std::optional<at::Tensor>& weight,
+                                                              const std::optional<at::Tensor>& bias,
+                                                              const std::optional<at::Tensor>& running_mean,
+                                                              const std::optional<at::Tensor>& running_var,
+                                                              const std::optional<at::Tensor>& residual, bool training,
+                                                              double momentum, double eps, int64_t act,
+                                                              const std::optional<at::Tensor>& channel_sums) {
+  return batch_norm_act_impl(input, weight, bias, running_mean, running_var, residual, training, momentum, eps, act, channel_sums,
+                             nullptr);
+}
+
+// Same, plus a bit mask of the positive outputs (empty when the fast kernel does not apply): pass it to
+// batch_norm_act_backward in place of the output.
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_mask(
+    const at::Tensor& input, const std::optional<at::Tensor>& weight, const std::optional<at::Tensor>& bias,
+    const std::optional<at::Tensor>& running_mean, const std::optional<at::Tensor>& running_var,
+    const std::optional<at::Tensor>& residual, bool training, double momentum, double eps, int64_t act,
+    const std::optional<at::Tensor>& channel_sums) {
+  at::Tensor mask = at::empty({0}, input.options().dtype(at::kByte));
+  auto r = batch_norm_act_impl(input, weight, bias, running_mean, running_var, residual, training, momentum, eps, act, channel_sums,
+                               &mask);
+  return {std::get<0>(r), std::get<1>(r), std::get<2>(r), mask};
 }
 
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_backward(
@@ -313,7 +344,9 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_backwa
     if (t.sizes() == xv.t.sizes() && t.strides() == xv.t.strides()) return t;
     return at::empty_strided(xv.t.sizes(), xv.t.strides(), t.options()).copy_(t);
   };
-  at::Tensor dy = same_layout(grad_out), y = same_layout(out);
+  // `out` is either the forward output or, as a uint8 tensor, the bit mask of its positive elements
+  const bool bitmask = out.scalar_type() == at::kByte && act == 1;
+  at::Tensor dy = same_layout(grad_out), y = bitmask ? out.contiguous() : same_layout(out);
   auto fopt = input.options().dtype(at::kFloat);
   at::Tensor wk;
   const void* gamma = opt_ptr(weight, wk);
@@ -327,11 +360,13 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_backwa
   at::Tensor dgamma = at::empty({C}, fopt), dbeta = at::empty({C}, fopt);
   at::Tensor sums = at::zeros({2 * C}, input.options().dtype(at::kDouble));
   const void* mask = act == 1 ? y.data_ptr() : nullptr;
+  const int mask_dt = bitmask ? (int)B200_U8 : xdt;
+  if (bitmask) TORCH_CHECK(y.numel() * 8 == xv.rows * C, "batch_norm_act_backward: mask size does not match the input");
   B200_KERNEL_CHECK(b200_bn_backward_reduce(dy.data_ptr(), xdt, xv.t.data_ptr(), xdt, mean_t.data_ptr(), mdt,
-                                            invstd.data_ptr<float>(), mask, xdt, xv.rows, C, sums.data_ptr<double>(),
+                                            invstd.data_ptr<float>(), mask, mask_dt, xv.rows, C, sums.data_ptr<double>(),
                                             scope.stream()));
   B200_KERNEL_CHECK(b200_bn_backward_apply(dy.data_ptr(), xdt, xv.t.data_ptr(), xdt, mean_t.data_ptr(), mdt,
-                                           invstd.data_ptr<float>(), gamma, pdt, mask, xdt, sums.data_ptr<double>(), xv.rows, C,
+                                           invstd.data_ptr<float>(), gamma, pdt, mask, mask_dt, sums.data_ptr<double>(), xv.rows, C,
                                            training ? 1 : 0, dx.data_ptr(), xdt, dgamma.data_ptr<float>(),
                                            dbeta.data_ptr<float>(), has_residual ? dres.data_ptr() : nullptr, scope.stream()));
   if (weight.has_value() && weight->defined() && weight->scalar_type() != at::kFloat) {
