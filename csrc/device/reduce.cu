@@ -180,10 +180,73 @@ __global__ void reduce_final_kernel(const B200ReduceParams p) {
   }
 }
 
+// Sum / mean over the rows of a dense [n_red, n_out] view (bias gradients, channel sums): a warp reads
+// 32 adjacent columns of a row, eight warps take different rows, so every load is coalesced.
+__global__ void __launch_bounds__(256) reduce_outer_kernel(const B200ReduceParams p) {
+  __shared__ float sh[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const long long col = (long long)blockIdx.x * 32 + tx;
+  const long long per = (p.n_red + p.splits - 1) / p.splits;
+  const long long r0 = (long long)blockIdx.y * per;
+  const long long r1 = r0 + per < p.n_red ? r0 + per : p.n_red;
+  float acc = 0.f;
+  if (col < p.n_out) {
+    long long r = r0 + ty;
+    for (; r + 24 < r1; r += 32) {
+      const float a = ldf(p.in, r * p.n_out + col, p.in_dtype), b = ldf(p.in, (r + 8) * p.n_out + col, p.in_dtype);
+      const float c = ldf(p.in, (r + 16) * p.n_out + col, p.in_dtype), d = ldf(p.in, (r + 24) * p.n_out + col, p.in_dtype);
+      acc += (a + b) + (c + d);
+    }
+    for (; r < r1; r += 8) acc += ldf(p.in, r * p.n_out + col, p.in_dtype);
+  }
+  sh[ty][tx] = acc;
+  __syncthreads();
+  if (ty != 0 || col >= p.n_out) return;
+  float s = 0.f;
+#pragma unroll
+  for (int y = 0; y < 8; ++y) s += sh[y][tx];
+  if (p.splits > 1) p.workspace[(long long)blockIdx.y * p.n_out + col] = s;
+  else st_out(p.out, col, p.out_dtype, finish(p.op, s, p.n_red));
+}
+__global__ void reduce_outer_final_kernel(const B200ReduceParams p) {
+  const long long col = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= p.n_out) return;
+  float s = 0.f;
+  for (int k = 0; k < p.splits; ++k) s += p.workspace[(long long)k * p.n_out + col];
+  st_out(p.out, col, p.out_dtype, finish(p.op, s, p.n_red));
+}
+
+// true when the kept dimensions are one dense inner block and the reduced ones one dense outer block
+static bool is_outer_reduction(const B200ReduceParams* p) {
+  if (p->op != RED_SUM && p->op != RED_MEAN) return false;
+  if (p->n_kept < 1 || p->n_reduced < 1 || p->n_out < 32 || p->n_red < 64) return false;
+  long long expect = 1;
+  for (int d = p->n_kept - 1; d >= 0; --d) {
+    if (p->kept_size[d] != 1 && p->kept_in_stride[d] != expect) return false;
+    expect *= p->kept_size[d];
+  }
+  for (int d = p->n_reduced - 1; d >= 0; --d) {
+    if (p->red_size[d] != 1 && p->red_in_stride[d] != expect) return false;
+    expect *= p->red_size[d];
+  }
+  return true;
+}
+
 }  // namespace
 
 extern "C" int b200_reduce_plan(B200ReduceParams* p) {
   p->splits = 1;
+  p->outer = 0;
+  if (is_outer_reduction(p)) {
+    p->outer = 1;
+    const long long col_blocks = (p->n_out + 31) / 32;
+    long long s = (148 * 4 + col_blocks - 1) / col_blocks;
+    const long long max_s = p->n_red / 64;
+    if (s > max_s) s = max_s;
+    if (s > 256) s = 256;
+    p->splits = s > 1 ? (int)s : 1;
+    return p->splits > 1 ? (int)(p->n_out * p->splits) : 0;
+  }
   if (p->n_out < 148 * 2 && p->n_red >= 1 << 16) {
     long long s = (148 * 4) / (p->n_out > 0 ? p->n_out : 1);
     const long long max_s = p->n_red / 8192;
@@ -200,6 +263,12 @@ extern "C" int b200_reduce(const B200ReduceParams* p, void* stream) {
   if (p->n_kept > B200_RED_MAX_DIMS || p->n_reduced > B200_RED_MAX_DIMS) return (int)cudaErrorInvalidValue;
   if (p->n_out > 2147483647LL) return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
+  if (p->outer) {
+    dim3 ogrid((unsigned)((p->n_out + 31) / 32), (unsigned)p->splits);
+    reduce_outer_kernel<<<ogrid, 256, 0, s>>>(*p);
+    if (p->splits > 1) reduce_outer_final_kernel<<<(unsigned)((p->n_out + 127) / 128), 128, 0, s>>>(*p);
+    return (int)cudaGetLastError();
+  }
   const int threads = p->n_red >= 1024 ? 256 : (p->n_red >= 128 ? 128 : 32);
   dim3 grid((unsigned)p->n_out, (unsigned)p->splits);
   reduce_kernel<<<grid, threads, 0, s>>>(*p);

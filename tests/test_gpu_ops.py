@@ -294,3 +294,17 @@ def test_conv_statistics_feed_batch_norm_under_autocast():
         if cos < 0.96:
             bad[n] = round(cos, 4)
     assert not bad, bad
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_outer_reductions_take_the_coalesced_path(dtype):
+    """Sum / mean over leading dimensions of dense tensors (bias gradients) against the CPU."""
+    torch.manual_seed(10)
+    for shape, dims in [((4096, 768), (0,)), ((8, 512, 96), (0, 1)), ((100, 33), (0,)), ((7, 64, 5, 40), (0, 1)), ((70, 3000), (0,))]:
+        x = torch.randn(*shape).to(dtype)
+        ref_s, ref_m = x.float().sum(dims), x.float().mean(dims)
+        xd = x.to(DEV)
+        prec = 3e-2 if dtype == torch.bfloat16 else 1e-4
+        assert_tensors_equal(xd.sum(dims).float(), ref_s, prec=prec, use_MSE=True, msg=f"sum {shape}")
+        assert_tensors_equal(xd.mean(dims).float(), ref_m, prec=prec, use_MSE=True, msg=f"mean {shape}")
+        assert_tensors_equal(xd.sum(dims, keepdim=True).float(), x.float().sum(dims, keepdim=True), prec=prec, use_MSE=True)
