@@ -1,5 +1,7 @@
 #include "process_group.h"
 
+#include <cstdlib>
+
 #include <ATen/ATen.h>
 #include <c10/util/Exception.h>
 #include <cstring>
@@ -224,9 +226,78 @@ ProcessGroupB200::ProcessGroupB200(const c10::intrusive_ptr<c10d::Store>& store,
     : c10d::Backend(rank, size), store_(store), timeout_(timeout), send_seq_(size, 0), recv_seq_(size, 0) {
   uid_ = "bwccl/" + std::to_string(next_process_group_id());
   B200LOG(INFO) << "ProcessGroupB200 rank " << rank << "/" << size << " uid " << uid_;
+  if (const char* e = std::getenv("CATCH_B200_HEARTBEAT_MS")) hb_interval_ms_ = std::atoll(e);
+  if (const char* e = std::getenv("CATCH_B200_HEARTBEAT_TIMEOUT_MS")) hb_timeout_ms_ = std::atoll(e);
+  if (size > 1 && hb_interval_ms_ > 0) start_watchdog();
+}
+
+void ProcessGroupB200::start_watchdog() {
+  watchdog_ = std::thread([this] {
+    try {
+      watchdog_loop();
+    } catch (const std::exception& e) {
+      B200LOG(INFO) << "bwccl watchdog of rank " << rank_ << " stopped: " << e.what();
+    } catch (...) {
+    }
+  });
+}
+
+void ProcessGroupB200::watchdog_loop() {
+  using clock = std::chrono::steady_clock;
+  auto hb_key = [&](int r) { return uid_ + "/hb/" + std::to_string(r); };
+  auto bye_key = [&](int r) { return uid_ + "/bye/" + std::to_string(r); };
+  std::vector<int64_t> last(size_, -1);
+  std::vector<clock::time_point> changed(size_, clock::now());
+  std::vector<bool> gone(size_, false);
+  for (;;) {
+    {
+      std::unique_lock<std::mutex> lk(wd_mu_);
+      if (wd_cv_.wait_for(lk, std::chrono::milliseconds(hb_interval_ms_), [this] { return wd_stop_; })) break;
+    }
+    store_->add(hb_key(rank_), 1);
+    const auto now = clock::now();
+    for (int r = 0; r < size_; ++r) {
+      if (r == rank_ || gone[r]) continue;
+      const int64_t v = store_->add(hb_key(r), 0);
+      if (v != last[r]) {
+        last[r] = v;
+        changed[r] = now;
+        continue;
+      }
+      if (now - changed[r] < std::chrono::milliseconds(hb_timeout_ms_)) continue;
+      if (store_->add(bye_key(r), 0) > 0) {  // it finished and said so
+        gone[r] = true;
+        continue;
+      }
+      int64_t expect = -1;
+      if (dead_peer_.compare_exchange_strong(expect, r))
+        B200LOG(ERROR) << "bwccl: rank " << r << " has sent no heartbeat for " << hb_timeout_ms_ << " ms (seen from rank " << rank_
+                       << "); further collectives of this group raise.";
+    }
+    if (arena_ && !status_logged_.load()) {
+      const int s = *((volatile int*)arena_->status_host());
+      if (s != 0) {
+        status_logged_.store(true);
+        B200LOG(ERROR) << "bwccl: a device-side wait of rank " << rank_ << " ran out waiting for rank " << ((s >> 8) & 0xff)
+                       << " (status word " << s << ").";
+      }
+    }
+  }
 }
 
 ProcessGroupB200::~ProcessGroupB200() {
+  if (watchdog_.joinable()) {
+    {
+      std::lock_guard<std::mutex> lk(wd_mu_);
+      wd_stop_ = true;
+    }
+    wd_cv_.notify_all();
+    watchdog_.join();
+    try {
+      store_->add(uid_ + "/bye/" + std::to_string(rank_), 1);
+    } catch (...) {
+    }
+  }
   try {
     if (arena_) {
       comm_q_.synchronize();
@@ -261,6 +332,9 @@ void ProcessGroupB200::check_single(const std::vector<at::Tensor>& tensors) cons
 }
 
 void ProcessGroupB200::throw_if_failed() const {
+  const int64_t dead = dead_peer_.load();
+  TORCH_CHECK_WITH(DistBackendError, dead < 0, "bwccl: rank ", dead, " stopped sending heartbeats (it left or died); ",
+                   "nothing was launched.");
   if (arena_ && *((volatile int*)arena_->status_host()) != 0) {
     const int s = *((volatile int*)arena_->status_host());
     TORCH_CHECK_WITH(DistBackendError, false, "bwccl: a previous collective failed (device wait timed out waiting for rank ",
@@ -315,6 +389,7 @@ std::vector<std::vector<uint8_t>> ProcessGroupB200::store_exchange(const std::ve
 
 c10::intrusive_ptr<c10d::Work> ProcessGroupB200::hostsim_collective(c10d::OpType op, std::vector<at::Tensor> outs,
                                                                     std::function<void()> fn) {
+  throw_if_failed();
   auto work = c10::make_intrusive<WorkB200>(rank_, op, std::move(outs), device_, nullptr, timeout_);
   try {
     fn();

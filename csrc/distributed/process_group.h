@@ -14,6 +14,10 @@
 // Under host simulation the same class moves bytes through the Store, so rank
 // logic, ordering, time-outs and failure handling are testable without GPUs.
 #pragma once
+#include <atomic>
+#include <condition_variable>
+#include <mutex>
+#include <thread>
 #include <torch/csrc/distributed/c10d/Backend.hpp>
 #include <torch/csrc/distributed/c10d/Store.hpp>
 #include <torch/csrc/distributed/c10d/Work.hpp>
@@ -99,6 +103,8 @@ class ProcessGroupB200 : public c10d::Backend {
   int64_t status_word() const;
   void clear_status();
   int device_index() const { return device_; }
+  // Rank whose heartbeat stopped (it left without saying goodbye), or -1.  Set by the watchdog thread.
+  int64_t dead_peer() const { return dead_peer_.load(); }
 
  private:
   void ensure_arena(int device);
@@ -122,6 +128,19 @@ class ProcessGroupB200 : public c10d::Backend {
   std::vector<uint64_t> send_seq_, recv_seq_;
   uint64_t host_seq_ = 0;
   std::string uid_;
+
+  // ---- watchdog: one host thread per group.  It publishes this rank's heartbeat counter in the Store,
+  // watches the peers' counters and the device status word, and records a failure so that the next
+  // collective raises before anything is launched.
+  void start_watchdog();
+  void watchdog_loop();
+  std::thread watchdog_;
+  std::mutex wd_mu_;
+  std::condition_variable wd_cv_;
+  bool wd_stop_ = false;
+  std::atomic<int64_t> dead_peer_{-1};
+  std::atomic<bool> status_logged_{false};
+  int64_t hb_interval_ms_ = 1000, hb_timeout_ms_ = 15000;
 };
 
 // Number of ProcessGroupB200 objects created so far in this process (names Store keys).

@@ -28,6 +28,7 @@ void bind_extras(py::module& m) {
       .def("fused_allreduce_step", &ProcessGroupB200::fused_allreduce_step, py::call_guard<py::gil_scoped_release>())
       .def("set_wait_limit_ms", &ProcessGroupB200::set_wait_limit_ms)
       .def("status_word", &ProcessGroupB200::status_word)
+      .def("dead_peer", &ProcessGroupB200::dead_peer)
       .def("clear_status", &ProcessGroupB200::clear_status)
       .def("device_index", &ProcessGroupB200::device_index);
   m.def("_kernel_launch_count", [] { return ops::kernel_launch_count(); });

@@ -129,3 +129,33 @@ def _missing_peer(rank, world):
 
 def test_rank_that_leaves_is_detected():
     run_ranks(_missing_peer, world=2, timeout=60)
+
+
+def _heartbeat(rank, world):
+    import time
+
+    _init(rank, world, timeout_s=30)
+    from catch_b200.distributed import get_backend
+
+    t = torch.ones(4, device=DEV)
+    dist.all_reduce(t)
+    pg = get_backend()
+    assert pg.dead_peer() == -1
+    if rank == 1:
+        os._exit(0)  # leaves between steps without a goodbye
+    deadline = time.time() + 20
+    while pg.dead_peer() < 0 and time.time() < deadline:
+        time.sleep(0.1)
+    assert pg.dead_peer() == 1, "the watchdog did not notice the missing heartbeat"
+    t0 = time.time()
+    try:
+        dist.all_reduce(t)
+    except Exception as e:  # raised on the host, before anything is launched and without waiting for the group timeout
+        assert "heartbeat" in str(e), str(e)
+        assert time.time() - t0 < 5
+        os._exit(0)
+    os._exit(3)
+
+
+def test_watchdog_reports_a_rank_that_stopped_heartbeating():
+    run_ranks(_heartbeat, world=2, env={"CATCH_B200_HEARTBEAT_MS": "200", "CATCH_B200_HEARTBEAT_TIMEOUT_MS": "1500"})
