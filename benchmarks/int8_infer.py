@@ -39,7 +39,13 @@ def main():
     args = ap.parse_args()
     dev = torch.device("blackwell", 0)
     torch.manual_seed(0)
+    # batch norms are folded into the convolutions first (both arms), as any deployment flow does
+    from torch.fx.experimental.optimization import fuse as fold_conv_bn
     model = torchvision.models.resnet50().eval()
+    for m in model.modules():
+        if isinstance(m, torch.nn.BatchNorm2d):
+            m.running_mean.normal_(0, 0.1); m.running_var.uniform_(0.5, 1.5)
+    model = fold_conv_bn(model)
     mixed = {"conv1": "float"}  # the 3-channel first layer stays in floating point
     calib = quantize_dynamic(model, {"per_channel": True, "iteration": 8}, dtype="int8", gen_quant=True, mixed_layer=mixed)
     calib = calib.half().to(dev).to(memory_format=torch.channels_last)
@@ -51,8 +57,8 @@ def main():
     qmodel = quantize_dynamic(model, mixed_layer=mixed)
     qmodel.load_state_dict(sd, strict=False)
     qmodel = qmodel.half().to(dev).to(memory_format=torch.channels_last)
-    fmodel = torchvision.models.resnet50().eval()
-    fmodel.load_state_dict({k: v for k, v in model.state_dict().items()})
+    import copy
+    fmodel = copy.deepcopy(model)
     fmodel = fmodel.half().to(dev).to(memory_format=torch.channels_last)
     x = torch.randn(args.batch, 3, 224, 224, generator=torch.Generator().manual_seed(2)).half().to(dev)
     x = x.contiguous(memory_format=torch.channels_last)

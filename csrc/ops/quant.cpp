@@ -28,7 +28,8 @@ using at::Tensor;
 
 struct QWeight {
   Tensor q;        // int8, same memory layout as the dense source
-  Tensor inv;      // fp32 [rows]: 1 / (input_scale * row_scale), filled per call
+  Tensor inv;      // fp32 [rows]: 1 / (input_scale * row_scale) for the input scale `inv_s_in`
+  double inv_s_in = 0.0;
   Tensor scale;    // fp32 [rows]: 127 / absmax(row)
   uint32_t version = 0;
   const void* ptr = nullptr;
@@ -36,6 +37,33 @@ struct QWeight {
 
 std::mutex g_mu;
 std::unordered_map<const void*, QWeight> g_cache;
+
+// Host copies of the small scale / mode tensors.  Reading them from the device costs a synchronisation,
+// so the values are cached per (storage address, version) and re-read only when the tensor changes.
+struct HostVals {
+  std::vector<double> v;
+  uint32_t version = 0;
+  int64_t numel = 0;
+};
+std::unordered_map<const void*, HostVals> g_host_vals;
+std::vector<double> host_values(const Tensor& t) {
+  if (!t.defined() || t.numel() == 0) return {};
+  const void* key = t.data_ptr();
+  {
+    std::lock_guard<std::mutex> g(g_mu);
+    auto it = g_host_vals.find(key);
+    if (it != g_host_vals.end() && it->second.version == t._version() && it->second.numel == t.numel()) return it->second.v;
+  }
+  Tensor h = t.detach().cpu().to(at::kDouble).contiguous().view({-1});
+  HostVals hv;
+  hv.v.assign(h.data_ptr<double>(), h.data_ptr<double>() + h.numel());
+  hv.version = t._version();
+  hv.numel = t.numel();
+  std::lock_guard<std::mutex> g(g_mu);
+  if (g_host_vals.size() > 8192) g_host_vals.clear();
+  g_host_vals[key] = hv;
+  return hv.v;
+}
 
 // `w2d`: dense [rows, cols] view of the weight in the memory order the kernel reads.
 QWeight quantize_weight(const Tensor& weight, const Tensor& w2d, bool per_channel, double tensor_scale,
@@ -66,10 +94,20 @@ QWeight quantize_weight(const Tensor& weight, const Tensor& w2d, bool per_channe
   return qw;
 }
 
+// 1 / (input scale * weight row scale): computed once per (weight, input scale)
+Tensor dequant_scale(const Tensor& weight, QWeight& qw, double s_in) {
+  if (qw.inv.defined() && qw.inv_s_in == s_in) return qw.inv;
+  qw.inv = at::reciprocal(qw.scale * s_in);
+  qw.inv_s_in = s_in;
+  std::lock_guard<std::mutex> g(g_mu);
+  auto it = g_cache.find(weight.data_ptr());
+  if (it != g_cache.end() && it->second.version == qw.version) { it->second.inv = qw.inv; it->second.inv_s_in = s_in; }
+  return qw.inv;
+}
+
 bool quant_active(const std::optional<Tensor>& q_scale, const std::optional<Tensor>& q_mode) {
   if (!q_scale.has_value() || !q_scale->defined() || q_scale->numel() == 0) return false;
-  if (q_mode.has_value() && q_mode->defined() && q_mode->numel() > 0 && q_mode->cpu().to(at::kLong)[0].item<int64_t>() == 0)
-    return false;
+  if (q_mode.has_value() && q_mode->defined() && q_mode->numel() > 0 && (int64_t)host_values(*q_mode)[0] == 0) return false;
   return true;
 }
 
@@ -84,9 +122,9 @@ Tensor qconv2d_device(const Tensor& input, const Tensor& weight, const std::opti
   TORCH_CHECK(C % 16 == 0 && K % 8 == 0, "b200 quantized conv2d: channels must be multiples of 16 (in) and 8 (out)");
   const at::ScalarType ft = input.scalar_type();
   TORCH_CHECK(ft == at::kHalf || ft == at::kBFloat16 || ft == at::kFloat, "b200 quantized conv2d: unsupported dtype ", ft);
-  Tensor sc = q_scale.cpu().to(at::kDouble);
-  const double s_in = sc[0].item<double>();
-  const double s_w = sc.numel() > 1 ? sc[1].item<double>() : 1.0;
+  const std::vector<double> sc = host_values(q_scale);
+  const double s_in = sc[0];
+  const double s_w = sc.size() > 1 ? sc[1] : 1.0;
   OpScope scope("quantized_conv2d", input);
   const int64_t P = (H + 2 * padding[0] - R) / stride[0] + 1, Q = (W + 2 * padding[1] - S) / stride[1] + 1;
   Tensor x = input.contiguous(at::MemoryFormat::ChannelsLast);
@@ -97,7 +135,7 @@ Tensor qconv2d_device(const Tensor& input, const Tensor& weight, const std::opti
   if (R == 1 && S == 1) wcl = empty_b200(weight.sizes(), weight.scalar_type(), weight.device().index(), at::MemoryFormat::ChannelsLast).copy_(weight);
   Tensor w2d = wcl.permute({0, 2, 3, 1}).reshape({K, R * S * C});  // a view: memory is [K][R][S][C]
   QWeight qw = quantize_weight(weight, w2d, mode != 1, s_w, scope);
-  Tensor inv = at::reciprocal(qw.scale * s_in);
+  Tensor inv = dequant_scale(weight, qw, s_in);
   const at::ScalarType ot = ft == at::kFloat ? at::kHalf : ft;
   Tensor out = empty_b200({N, K, P, Q}, ot, input.device().index(), at::MemoryFormat::ChannelsLast);
   B200ConvParams p;
@@ -151,9 +189,9 @@ Tensor qlinear_device(const Tensor& input, const Tensor& weight, const std::opti
   TORCH_CHECK(ft == at::kHalf || ft == at::kBFloat16 || ft == at::kFloat, "b200 quantized linear: unsupported dtype ", ft);
   const int64_t K = input.size(-1), Nout = weight.size(0);
   TORCH_CHECK(weight.dim() == 2 && weight.size(1) == K && K % 16 == 0, "b200 quantized linear: in_features must be a multiple of 16");
-  Tensor sc = q_scale.cpu().to(at::kDouble);
-  const double s_in = sc[0].item<double>();
-  const double s_w = sc.numel() > 1 ? sc[1].item<double>() : 1.0;
+  const std::vector<double> sc = host_values(q_scale);
+  const double s_in = sc[0];
+  const double s_w = sc.size() > 1 ? sc[1] : 1.0;
   OpScope scope("quantized_linear", input);
   Tensor x = input.reshape({-1, K}).contiguous();
   const int64_t M = x.size(0);
@@ -161,7 +199,7 @@ Tensor qlinear_device(const Tensor& input, const Tensor& weight, const std::opti
   B200_KERNEL_CHECK(b200_quantize_int8(x.data_ptr(), to_b200_dtype(ft), x.numel(), (float)s_in, xq.data_ptr(), scope.stream()));
   Tensor w = weight.contiguous();
   QWeight qw = quantize_weight(weight, w, mode != 1, s_w, scope);
-  Tensor inv = at::reciprocal(qw.scale * s_in);
+  Tensor inv = dequant_scale(weight, qw, s_in);
   const at::ScalarType ot = ft;
   Tensor out = empty_b200({M, Nout}, ot, input.device().index());
   B200GemmParams p;
@@ -186,7 +224,7 @@ Tensor qlinear_device(const Tensor& input, const Tensor& weight, const std::opti
 
 int64_t mode_of(const std::optional<Tensor>& q_mode) {
   if (!q_mode.has_value() || !q_mode->defined() || q_mode->numel() == 0) return 1;
-  return q_mode->cpu().to(at::kLong).view({-1})[0].item<int64_t>();
+  return (int64_t)host_values(*q_mode)[0];
 }
 
 // Fake-quantized reference used on the CPU path and when the device kernel rejects a shape.
