@@ -130,7 +130,27 @@ def write_ninja(verbose: bool = False) -> Path:
         ld.append(f"-Wl,-rpath,{p}")
     lines.append(f"build {HOST_LIB}: link_host {' '.join(map(str, host_objs))} | {DEVICE_LIB}")
     lines.append(f"  ldflags = {' '.join(ld)}")
-    lines.append(f"default {DEVICE_LIB} {HOST_LIB}")
+    # C++ test program of the runtime (no Python): runtime objects + test main
+    test_bin = PKG / "lib" / "b200_runtime_test"
+    test_objs = []
+    for src in sorted((CSRC / "test").glob("*.cpp")):
+        obj = BUILD / "host" / "test" / (src.stem + ".o")
+        test_objs.append(obj)
+        lines.append(f"build {obj}: cxx {src}")
+    if test_objs:
+        rt_objs = [o for o in host_objs if o.parent.name == "runtime"]
+        ld_test = [f"-L{p}" for p in lib] + ["-lc10", "-ltorch_cpu", "-ltorch", f"-L{PKG / 'lib'}", "-lcatch_b200_device",
+                                             "-Wl,-rpath,'$$ORIGIN'", "-Wl,--no-as-needed", "-lpthread"]
+        for p in lib:
+            ld_test.append(f"-Wl,-rpath,{p}")
+        lines.insert(lines.index("rule link_host"), "rule link_exe")
+        lines.insert(lines.index("rule link_host"), "  command = $cxx -o $out $in $ldflags")
+        lines.insert(lines.index("rule link_host"), "  description = LINK $out")
+        lines.append(f"build {test_bin}: link_exe {' '.join(map(str, test_objs + rt_objs))} | {DEVICE_LIB}")
+        lines.append(f"  ldflags = {' '.join(ld_test)}")
+        lines.append(f"default {DEVICE_LIB} {HOST_LIB} {test_bin}")
+    else:
+        lines.append(f"default {DEVICE_LIB} {HOST_LIB}")
     path = BUILD / "build.ninja"
     text = "\n".join(lines) + "\n"
     if not path.exists() or path.read_text() != text:
