@@ -34,7 +34,7 @@ BASELINE_IMAGES_PER_SEC = None  # the reference publishes no throughput number
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=256, help="per-GPU batch size")
@@ -58,7 +58,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -66,9 +66,10 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
-    def stop(self) -> dict:
+    def stop(self, t0: float = 0.0, t1: float = float("inf")) -> dict:
+        """Summarise the samples taken between host times t0 and t1 (the timed region)."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()  # the exact child started above
@@ -77,7 +78,9 @@ class ClockSampler:
         except Exception:
             pass
         sm, mx, reasons = [], [], set()
-        for ln in self.lines:
+        for ts, ln in self.lines:
+            if ts < t0 or ts > t1:
+                continue
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -180,16 +183,18 @@ def main():
             ms = t.item()
         return ms, out
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()  # started before the warm-up: nvidia-smi needs a moment before its first sample
     for _ in range(max(args.warmup, 3)):
         resident_step()
     barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     catch_b200._C._reset_kernel_launch_count()
+    t_begin = time.time()
     ms, loss = timed(resident_step, args.steps)
+    t_end = time.time()
     launches = catch_b200._C._kernel_launch_count()
-    clocks = sampler.stop() if rank == 0 else {}
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else {}
     e2e_steps(2)
     ms_e2e, _ = timed(e2e_steps, args.steps, whole_loop=True)
 
