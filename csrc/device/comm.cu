@@ -136,29 +136,51 @@ __global__ void __launch_bounds__(512) allreduce_kernel(const B200CommCtx c, siz
   const long long per = (nvec + c.world - 1) / c.world;
   const long long v0 = per * c.rank, v1 = (v0 + per < nvec) ? v0 + per : nvec;
   const bool avg = op == COMM_AVG;
-  for (long long i = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < v1; i += (long long)gridDim.x * blockDim.x) {
-    A acc[V];
-    alignas(16) T tmp[V];
+  // Four 16-byte vectors per thread and step: the four peer loads of a round are in flight together,
+  // which is what keeps enough bytes on the links to cover their latency.
+  constexpr int U = 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < v1; i0 += stride * U) {
+    A acc[U][V];
+    uint4 raw[U];
     // read the peers in a rotated order so the ranks do not all hit the same peer at once
     for (int p = 0; p < c.world; ++p) {
       const int peer = (c.rank + p) % c.world;
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(c.arena[peer]) + offset) + i;
-      *reinterpret_cast<uint4*>(tmp) = *src;
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(c.arena[peer]) + offset);
 #pragma unroll
-      for (int k = 0; k < V; ++k) {
-        const A v = widen<T, A>(tmp[k]);
-        acc[k] = p == 0 ? v : comb<A>(avg ? COMM_SUM : op, acc[k], v);
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < v1) raw[u] = src[i];
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const T* tv = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          const A v = widen<T, A>(tv[k]);
+          acc[u][k] = p == 0 ? v : comb<A>(avg ? COMM_SUM : op, acc[u][k], v);
+        }
       }
     }
 #pragma unroll
-    for (int k = 0; k < V; ++k) {
-      if (scale != 1.f) acc[k] = (A)(acc[k] * (A)scale);
-      if (avg) acc[k] = acc[k] / (A)c.world;
-      tmp[k] = narrow<T, A>(acc[k]);
+    for (int u = 0; u < U; ++u) {
+      T* tv = reinterpret_cast<T*>(&raw[u]);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        A a = acc[u][k];
+        if (scale != 1.f) a = (A)(a * (A)scale);
+        if (avg) a = a / (A)c.world;
+        tv[k] = narrow<T, A>(a);
+      }
     }
     for (int p = 0; p < c.world; ++p) {
       const int peer = (c.rank + p) % c.world;
-      reinterpret_cast<uint4*>(static_cast<char*>(c.arena[peer]) + offset)[i] = *reinterpret_cast<const uint4*>(tmp);
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(c.arena[peer]) + offset);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < v1) dst[i] = raw[u];
+      }
     }
   }
   end_barrier(c, seq, limit);
@@ -290,7 +312,8 @@ extern "C" int b200_comm_allreduce(const B200CommCtx* ctx, size_t offset, long l
   COMM_DISPATCH(dtype, T, {
     const long long per = (((n + Vec<T>::N - 1) / Vec<T>::N) + ctx->world - 1) / ctx->world;
     // enough CTAs to saturate NVLink, few enough that all of them are resident
-    const int grid = comm_grid(per, 512, 64);
+    // large messages are bound by link bandwidth: more CTAs put more loads in flight
+    const int grid = comm_grid((per + 3) / 4, 512, per * 16 >= (8LL << 20) ? 128 : 64);
     allreduce_kernel<T><<<grid, 512, 0, s>>>(*ctx, offset, n, op, scale, seq, no_signal);
   });
   return (int)cudaGetLastError();

@@ -18,6 +18,7 @@
 // (tap, input-channel) axis, K = pixels (64 per stage).  Both operands are MN-major
 // (channels contiguous) straight out of the NHWC tensors.  CTAs split the pixel
 // range and add their partial tiles to an fp32 buffer.
+#include <algorithm>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "kernels_api.h"
@@ -55,6 +56,15 @@ struct ConvArgs {
   int act;
   float alpha;
   double* stats;                // optional [2 * Cout]: per-channel sum and sum of squares of the stored outputs
+  // Halo mode (single channel block, every tap on one view, resident weights): per pixel tile (8 wide,
+  // 16 high) one column tile of 8 x halo_h pixels is loaded for each distinct horizontal tap offset; a
+  // tap's A operand is the window of its column tile shifted down by whole pixel rows (8 x 128 bytes =
+  // one swizzle repeat, so the window stays aligned).  Activations cross L2 -> shared memory once per
+  // horizontal offset instead of once per tap.  (A single tile with windows shifted sideways by 128-byte
+  // steps was tried: a descriptor that starts off the 1024-byte swizzle repeat gave wrong products even
+  // with its base-offset field set, so that variant is not used.)
+  int halo, halo_h, halo_stage_bytes, dw_min, dh_min;
+  int halo_ndw, halo_col_bytes;
   int b_res_bytes;              // > 0: weights of one output-channel tile stay resident in shared memory
   int coef_bytes;               // shared memory reserved for per-channel scale / bias (0 or 2048)
   int tma_store;                // epilogue stages 64-channel blocks in shared memory and stores them by TMA
@@ -131,7 +141,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
   // Resident mode : a stage holds only the A tile; the weights of the current output-channel
   //                 tile (all taps, all channel blocks) stay in shared memory across pixel tiles.
   const int b_blk_bytes = g.tile_n * 128;
-  const int stage_bytes = CONV_A_BYTES + (g.b_res_bytes ? 0 : b_blk_bytes);
+  const int stage_bytes = g.halo ? g.halo_stage_bytes : CONV_A_BYTES + (g.b_res_bytes ? 0 : b_blk_bytes);
   uint8_t* bres = smem;
   uint8_t* stage0 = smem + g.b_res_bytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(stage0 + (size_t)g.stages * stage_bytes);
@@ -198,6 +208,16 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
           }
           cur_ct = ct;
         }
+        if (g.halo) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, g.err, ERR_TIMEOUT_EMPTY)) { failed = true; break; }
+          // channel coordinate 0; the pixel origin may be negative (zero filled)
+          mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)(g.halo_ndw * g.halo_col_bytes));
+          for (int j = 0; j < g.halo_ndw; ++j)
+            tma_load_4d(stage0 + (size_t)stage * stage_bytes + (size_t)j * g.halo_col_bytes, &maps.a[1], &full_bar[stage], 0,
+                        q0 + g.dw_min + j, p0 + g.dh_min, n0);
+          if (++stage == g.stages) { stage = 0; phase ^= 1; }
+          continue;
+        }
         for (int it = 0; it < k_iters; ++it) {
           const int tap = it / g.c_blocks, cb = it - tap * g.c_blocks;
           const B200ConvTap tp = g.taps[tap];
@@ -221,6 +241,13 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
       int cur_ct = -1; uint32_t b_phase = 0;
+      // descriptor templates and addresses in 16-byte units: per K block the issue loop only adds
+      uint32_t a_lo0, a_hi, b_lo0, b_hi;
+      split_desc(make_smem_desc_sw128(0, 16, 1024), &a_lo0, &a_hi);
+      split_desc(g.b_mn ? make_smem_desc_sw128(0, 8192, 1024) : make_smem_desc_sw128(0, 16, 1024), &b_lo0, &b_hi);
+      const uint32_t b_step = g.b_mn ? 128u : 2u;  // 2048 or 32 bytes per K = 16 step
+      const uint32_t stage0_16 = smem_u32(stage0) >> 4, stage_16 = (uint32_t)stage_bytes >> 4;
+      const uint32_t bres_16 = smem_u32(bres) >> 4, bblk_16 = (uint32_t)b_blk_bytes >> 4;
       for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
         const int ct = tile / pix_tiles;
         if (g.b_res_bytes && ct != cur_ct) {
@@ -231,21 +258,44 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, g.err, ERR_TIMEOUT_TMEM_EMPTY)) { failed = true; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * 256;
+        if (g.halo) {
+          if (!mbar_wait(&full_bar[stage], phase, g.err, ERR_TIMEOUT_FULL)) { failed = true; break; }
+          tc_fence_after();
+          const uint32_t tile0_16 = stage0_16 + (uint32_t)stage * stage_16;
+          for (int tap = 0; tap < g.ntaps; ++tap) {
+            const B200ConvTap tp = g.taps[tap];
+            // column tile of this tap's dw, shifted down by (dh - dh_min) pixel rows of 1024 bytes
+            const uint32_t a0_16 = tile0_16 + (uint32_t)(((tp.dw - g.dw_min) * g.halo_col_bytes + (tp.dh - g.dh_min) * 1024) >> 4);
+            umma_x4<0>(d_tmem, a_lo0 + a0_16, a_hi, 2, b_lo0 + bres_16 + (uint32_t)tap * bblk_16, b_hi, b_step, g.idesc,
+                       tap > 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == g.stages) { stage = 0; phase ^= 1; }
+          umma_commit(&acc_full[acc]);
+          if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+          continue;
+        }
         for (int it = 0; it < k_iters; ++it) {
           if (!mbar_wait(&full_bar[stage], phase, g.err, ERR_TIMEOUT_FULL)) { failed = true; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(stage0 + (size_t)stage * stage_bytes);
-          const uint32_t sb = g.b_res_bytes ? smem_u32(bres + (size_t)it * b_blk_bytes) : sa + CONV_A_BYTES;
+          const uint32_t sa_16 = stage0_16 + (uint32_t)stage * stage_16;
+          const uint32_t sb_16 = g.b_res_bytes ? bres_16 + (uint32_t)it * bblk_16 : sa_16 + (CONV_A_BYTES >> 4);
+#ifdef B200_AB_OLD_ISSUE
+          {
+            const uint32_t sa = sa_16 << 4, sb = sb_16 << 4;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t bdesc = g.b_mn ? make_smem_desc_sw128(sb + k * 2048, 8192, 1024)
-                                          : make_smem_desc_sw128(sb + k * 32, 16, 1024);
-            if (g.kind == 2)
-              umma_i8(d_tmem, make_smem_desc_sw128(sa + k * 32, 16, 1024), bdesc, g.idesc, (it > 0 || k > 0) ? 1u : 0u);
-            else
-              umma_f16(d_tmem, make_smem_desc_sw128(sa + k * 32, 16, 1024), bdesc, g.idesc,
-                       (it > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < 4; ++k) {
+              const uint64_t bdesc = g.b_mn ? make_smem_desc_sw128(sb + k * 2048, 8192, 1024) : make_smem_desc_sw128(sb + k * 32, 16, 1024);
+              if (g.kind == 2) umma_i8(d_tmem, make_smem_desc_sw128(sa + k * 32, 16, 1024), bdesc, g.idesc, (it > 0 || k > 0) ? 1u : 0u);
+              else umma_f16(d_tmem, make_smem_desc_sw128(sa + k * 32, 16, 1024), bdesc, g.idesc, (it > 0 || k > 0) ? 1u : 0u);
+            }
           }
+#else
+          if (g.kind == 2)
+            umma_x4<2>(d_tmem, a_lo0 + sa_16, a_hi, 2, b_lo0 + sb_16, b_hi, b_step, g.idesc, it > 0 ? 1u : 0u);
+          else
+            umma_x4<0>(d_tmem, a_lo0 + sa_16, a_hi, 2, b_lo0 + sb_16, b_hi, b_step, g.idesc, it > 0 ? 1u : 0u);
+#endif
           umma_commit(&empty_bar[stage]);
           if (++stage == g.stages) { stage = 0; phase ^= 1; }
         }
@@ -318,8 +368,17 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
 
       // accumulator chunk (32 channels starting at tile column c) -> alpha, scale/bias, residual, activation
       auto finish = [&](const uint32_t (&rr)[32], int c, float (&v)[32]) {
+        if (g.kind == 2) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = (g.kind == 2 ? (float)(int)rr[j] : __uint_as_float(rr[j])) * g.alpha;
+          for (int j = 0; j < 32; ++j) v[j] = (float)(int)rr[j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rr[j]);
+        }
+        if (g.alpha != 1.f) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] *= g.alpha;
+        }
         if (has_coef) apply_coef(v, cs + c, cbias + c);
         const int cbase = co0 + c;
         if (g.residual && row_ok && cbase < g.Cout)
@@ -361,24 +420,35 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
             *reinterpret_cast<uint4*>(srow + (((4 + k) ^ (lane & 7)) * 16)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
           fence_proxy_async_smem();
           __syncwarp();
+#ifndef B200_AB_NO_STATS
           if (g.stats) {
             // Column sums over the 32 staged pixels (the rounded values that were stored; pixels
             // outside the tensor were zeroed above).
-            float s0 = 0.f, s1 = 0.f, q0s = 0.f, q1s = 0.f;
+            // packed fp32 pairs: one add and one fma per two elements
+            unsigned long long s2 = 0ull, q2 = 0ull;
 #pragma unroll 8
             for (int rw = 0; rw < 32; ++rw) {
               const uint32_t w2 = *reinterpret_cast<const uint32_t*>(sbuf + rw * 128 + (((lane >> 2) ^ (rw & 7)) * 16) + (lane & 3) * 4);
-              float a, b;
+              uint32_t lo, hi;
               if (g.out_dtype == B200_BF16) {
-                a = __uint_as_float(w2 << 16); b = __uint_as_float(w2 & 0xffff0000u);
+                lo = w2 << 16; hi = w2 & 0xffff0000u;
               } else {
                 const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w2));
-                a = f2.x; b = f2.y;
+                lo = __float_as_uint(f2.x); hi = __float_as_uint(f2.y);
               }
-              s0 += a; q0s = fmaf(a, a, q0s); s1 += b; q1s = fmaf(b, b, q1s);
+              unsigned long long ab;
+              asm("mov.b64 %0, {%1, %2};" : "=l"(ab) : "r"(lo), "r"(hi));
+              asm("add.rn.f32x2 %0, %0, %1;" : "+l"(s2) : "l"(ab));
+              asm("fma.rn.f32x2 %0, %1, %1, %0;" : "+l"(q2) : "l"(ab));
             }
+            uint32_t s_lo, s_hi, q_lo, q_hi;
+            asm("mov.b64 {%0, %1}, %2;" : "=r"(s_lo), "=r"(s_hi) : "l"(s2));
+            asm("mov.b64 {%0, %1}, %2;" : "=r"(q_lo), "=r"(q_hi) : "l"(q2));
+            const float s0 = __uint_as_float(s_lo), s1 = __uint_as_float(s_hi);
+            const float q0s = __uint_as_float(q_lo), q1s = __uint_as_float(q_hi);
             st_s[bi][0] += s0; st_s[bi][1] += s1; st_q[bi][0] += q0s; st_q[bi][1] += q1s;
           }
+#endif
           if (lane == 0) {
             // rows / channels outside the tensor are clipped by the store
             tma_store_4d(&maps.out, sbuf, co0 + cb, q0 + w_off, p0 + h_off, n0 + n_off);
@@ -528,17 +598,16 @@ conv_wgrad_kernel(const __grid_constant__ WgradMaps maps, const __grid_constant_
   } else if (warp == 1) {
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
+      uint32_t d_lo0, d_hi;
+      split_desc(make_smem_desc_sw128(0, blk_bytes, 1024), &d_lo0, &d_hi);
+      const uint32_t smem0_16 = smem_u32(smem) >> 4, stage_16 = (uint32_t)stage_bytes >> 4;
       for (int ch = chunk_begin; ch < chunk_end; ++ch) {
         if (!mbar_wait(&full_bar[stage], phase, g.err, ERR_TIMEOUT_FULL)) { failed = true; break; }
         tc_fence_after();
-        const uint32_t sa = smem_u32(smem + (size_t)stage * stage_bytes);
-        const uint32_t sb = sa + 2 * blk_bytes;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          // MN-major operands: 16 pixels (K) per MMA = 2048 B; blocks of 64 channels 8 KB apart.
-          umma_f16(tmem_base, make_smem_desc_sw128(sa + k * 2048, blk_bytes, 1024),
-                   make_smem_desc_sw128(sb + k * 2048, blk_bytes, 1024), g.idesc, (ch > chunk_begin || k > 0) ? 1u : 0u);
-        }
+        // MN-major operands: 16 pixels (K) per MMA = 2048 B; blocks of 64 channels 8 KB apart.
+        const uint32_t sa_16 = smem0_16 + (uint32_t)stage * stage_16;
+        umma_x4<0>(tmem_base, d_lo0 + sa_16, d_hi, 128, d_lo0 + sa_16 + (uint32_t)(2 * blk_bytes >> 4), d_hi, 128, g.idesc,
+                   ch > chunk_begin ? 1u : 0u);
         umma_commit(&empty_bar[stage]);
         if (++stage == g.stages) { stage = 0; phase ^= 1; }
       }
@@ -666,7 +735,7 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p_in, void* stream) {
   g.tiles_q = (p->Q + g.bw - 1) / g.bw;
   g.tiles_p = (p->P + g.bh - 1) / g.bh;
   g.tiles_n = (p->N + g.bni - 1) / g.bni;
-  const long pix_tiles = (long)g.tiles_q * g.tiles_p * g.tiles_n;
+  long pix_tiles = (long)g.tiles_q * g.tiles_p * g.tiles_n;
   if (p->tile_n > 0) {
     g.tile_n = p->tile_n;
   } else {
@@ -707,7 +776,28 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p_in, void* stream) {
   if (g.stats && !g.tma_store) return (int)cudaErrorInvalidValue;  // statistics come from the staged tiles
   const long b_tile_bytes = (long)g.ntaps * g.c_blocks * g.tile_n * 128;
   g.b_res_bytes = (b_tile_bytes <= 96 * 1024 && pix_tiles >= 2L * sms) ? (int)b_tile_bytes : 0;
-  const int stage_bytes = CONV_A_BYTES + (g.b_res_bytes ? 0 : g.tile_n * 128);
+  // Halo mode: see ConvArgs.  The pixel box is fixed to 8 x 16 x 1 so that the 16 row groups of the
+  // MMA's A operand are the 16 image rows of the tile.
+  g.halo = 0;
+  if (g.b_res_bytes && g.c_blocks == 1 && g.ntaps > 1 && p->num_views == 1 && g.kind == 0 && p->Q >= 8 && p->P >= 8) {
+    int dw0 = 1 << 20, dw1 = -(1 << 20), dh0 = 1 << 20, dh1 = -(1 << 20);
+    bool one_view = true;
+    for (int i = 0; i < p->ntaps; ++i) {
+      dw0 = std::min<int>(dw0, p->taps[i].dw); dw1 = std::max<int>(dw1, p->taps[i].dw);
+      dh0 = std::min<int>(dh0, p->taps[i].dh); dh1 = std::max<int>(dh1, p->taps[i].dh);
+      one_view = one_view && p->taps[i].map == 0;
+    }
+    const int hh = 16 + dh1 - dh0;
+    if (one_view && hh <= 24 && dw1 - dw0 < 4) {
+      g.halo = 1; g.halo_h = hh; g.dw_min = dw0; g.dh_min = dh0;
+      g.halo_ndw = dw1 - dw0 + 1; g.halo_col_bytes = 8 * hh * 128;
+      g.halo_stage_bytes = g.halo_ndw * g.halo_col_bytes;
+      g.bw = 8; g.bh = 16; g.bni = 1;
+      g.tiles_q = (p->Q + 7) / 8; g.tiles_p = (p->P + 15) / 16; g.tiles_n = p->N;
+      pix_tiles = (long)g.tiles_q * g.tiles_p * g.tiles_n;
+    }
+  }
+  const int stage_bytes = g.halo ? g.halo_stage_bytes : CONV_A_BYTES + (g.b_res_bytes ? 0 : g.tile_n * 128);
   g.stages = (smem_cap - g.b_res_bytes) / stage_bytes;
   if (g.stages > CONV_MAX_STAGES) g.stages = CONV_MAX_STAGES;
   if (g.stages < 2) g.stages = 2;
@@ -731,6 +821,10 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p_in, void* stream) {
     if (rc) return rc;
   }
   for (int i = p->num_views; i < B200_CONV_MAX_MAPS; ++i) maps.a[i] = maps.a[0];
+  if (g.halo) {
+    int rc = encode_view(&maps.a[1], p->views[0], dt, g.cblk, 8, g.halo_h, 1, es);
+    if (rc) return rc;
+  }
   {
     int rc;
     if (!g.b_mn) {

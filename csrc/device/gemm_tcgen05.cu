@@ -213,6 +213,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
+      // descriptor templates and addresses in 16-byte units: per K block the issue loop only adds
+      uint32_t a_lo0, a_hi, b_lo0, b_hi;
+      split_desc(g.a_mn ? make_smem_desc_sw128(0, g.mn_lbo, g.mn_sbo) : make_smem_desc_sw128(0, 16, 1024), &a_lo0, &a_hi);
+      split_desc(g.b_mn ? make_smem_desc_sw128(0, g.mn_lbo, g.mn_sbo) : make_smem_desc_sw128(0, 16, 1024), &b_lo0, &b_hi);
+      const uint32_t a_step = g.a_mn ? (uint32_t)g.mn_kstep >> 4 : 2u, b_step = g.b_mn ? (uint32_t)g.mn_kstep >> 4 : 2u;
+      const uint32_t tiles_16 = smem_u32(tiles) >> 4, stage_16 = (uint32_t)stage_bytes >> 4;
       for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, g.err, ERR_TIMEOUT_TMEM_EMPTY)) { failed = true; break; }
         tc_fence_after();
@@ -220,19 +226,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int kb = 0; kb < g.k_blocks; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, g.err, ERR_TIMEOUT_FULL)) { failed = true; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(tiles + (size_t)stage * stage_bytes);
-          const uint32_t sb = sa + GEMM_A_STAGE_BYTES;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t adesc = g.a_mn ? make_smem_desc_sw128(sa + k * g.mn_kstep, g.mn_lbo, g.mn_sbo)
-                                          : make_smem_desc_sw128(sa + k * 32, 16, 1024);
-            const uint64_t bdesc = g.b_mn ? make_smem_desc_sw128(sb + k * g.mn_kstep, g.mn_lbo, g.mn_sbo)
-                                          : make_smem_desc_sw128(sb + k * 32, 16, 1024);
-            const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
-            if (g.kind == 1) umma_tf32(d_tmem, adesc, bdesc, g.idesc, accum);
-            else if (g.kind == 2) umma_i8(d_tmem, adesc, bdesc, g.idesc, accum);
-            else umma_f16(d_tmem, adesc, bdesc, g.idesc, accum);
-          }
+          const uint32_t sa_16 = tiles_16 + (uint32_t)stage * stage_16;
+          const uint32_t sb_16 = sa_16 + (GEMM_A_STAGE_BYTES >> 4);
+          const uint32_t accum = kb > 0 ? 1u : 0u;
+          if (g.kind == 1) umma_x4<1>(d_tmem, a_lo0 + sa_16, a_hi, a_step, b_lo0 + sb_16, b_hi, b_step, g.idesc, accum);
+          else if (g.kind == 2) umma_x4<2>(d_tmem, a_lo0 + sa_16, a_hi, a_step, b_lo0 + sb_16, b_hi, b_step, g.idesc, accum);
+          else umma_x4<0>(d_tmem, a_lo0 + sa_16, a_hi, a_step, b_lo0 + sb_16, b_hi, b_step, g.idesc, accum);
           umma_commit(&empty_bar[stage]);  // frees the smem stage once the MMAs have read it
           if (++stage == g.stages) { stage = 0; phase ^= 1; }
         }
@@ -247,7 +246,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int colhalf = (warp - 2) >> 2;  // the two warps of a quarter take alternate 32-column chunks
     int acc = 0;
     uint32_t acc_phase = 0;
-    uint32_t out_blocks = 0;
     uint32_t tile_iter = 0;
     const bool has_coef = g.col_scale != nullptr || (g.bias != nullptr && !g.bias_per_row);
     for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++tile_iter) {
@@ -278,52 +276,62 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                                  (g.res_dtype == B200_F32 ? 4 : 2)
                                        : nullptr;
       if (g.tma_store) {
-        const bool issuer = threadIdx.x == 64;
-        const int rr_ = quarter * 32 + lane;
-        for (int cb = 0; cb < g.tile_n; cb += 64) {
-          uint8_t* sbuf = stage_out + (out_blocks & 1) * 16384;
-          if (issuer) tma_store_wait_read<1>();
-          named_barrier(1, GEMM_EPI_THREADS);
-          {
-            const int half = colhalf;
-            const int c = cb + half * 32;
-            uint32_t r[32];
-            tmem_ld32(tmem_base + acc * GEMM_ACC_STRIDE + ((uint32_t)(quarter * 32) << 16) + c, r);
-            tmem_ld_wait();
-            const int n_base = n0 + c;
-            float v[32];
+        // Each epilogue warp stages its own 32 rows x 64 columns (4 KB, 128-byte swizzle) and issues its own
+        // tensor-map store; the two warps of a lane quarter take alternate 64-column blocks.  No barrier
+        // across warps is needed.
+        uint8_t* sbuf = stage_out + (warp - 2) * 4096;
+        auto finish = [&](const uint32_t (&r)[32], int c, float (&v)[32]) {
+          const int n_base = n0 + c;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = (g.kind == 2 ? (float)(int)r[j] : __uint_as_float(r[j])) * g.alpha;
-            if (has_coef) apply_coef(v, cs + c, cs + 256 + c);
-            if (g.bias && g.bias_per_row) {
+          for (int jj = 0; jj < 32; ++jj) v[jj] = g.kind == 2 ? (float)(int)r[jj] : __uint_as_float(r[jj]);
+          if (g.alpha != 1.f) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] += row_bias;
-            }
-            if (rrow && row_ok && n_base < g.N)
-              add_residual(v, rrow + (size_t)n_base * (g.res_dtype == B200_F32 ? 4 : 2), min(32, g.N - n_base), g.res_dtype, g.beta);
-            if (g.act) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], g.act);
-            }
-            uint32_t pk[16];
-            pack16(v, pk, g.d_dtype);
-            uint8_t* srow = sbuf + rr_ * 128;
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              *reinterpret_cast<uint4*>(srow + (((half * 4 + k) ^ (rr_ & 7)) * 16)) =
-                  make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
+            for (int jj = 0; jj < 32; ++jj) v[jj] *= g.alpha;
           }
+          if (has_coef) apply_coef(v, cs + c, cs + 256 + c);
+          if (g.bias && g.bias_per_row) {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) v[jj] += row_bias;
+          }
+          if (rrow && row_ok && n_base < g.N)
+            add_residual(v, rrow + (size_t)n_base * (g.res_dtype == B200_F32 ? 4 : 2), min(32, g.N - n_base), g.res_dtype, g.beta);
+          if (g.act) {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) v[jj] = apply_act(v[jj], g.act);
+          }
+        };
+        const uint32_t t_addr = tmem_base + acc * GEMM_ACC_STRIDE + ((uint32_t)(quarter * 32) << 16);
+        for (int cb = colhalf * 64; cb < g.tile_n; cb += 128) {
+          uint32_t ra[32], rb[32];
+          tmem_ld32(t_addr + cb, ra);
+          tmem_ld32(t_addr + cb + 32, rb);
+          tmem_ld_wait();
+          if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has read the buffer
+          __syncwarp();
+          uint8_t* srow = sbuf + lane * 128;
+          float v[32];
+          uint32_t pk[16];
+          finish(ra, cb, v);
+          pack16(v, pk, g.d_dtype);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            *reinterpret_cast<uint4*>(srow + ((k ^ (lane & 7)) * 16)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
+          finish(rb, cb + 32, v);
+          pack16(v, pk, g.d_dtype);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            *reinterpret_cast<uint4*>(srow + (((4 + k) ^ (lane & 7)) * 16)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
           fence_proxy_async_smem();
-          named_barrier(1, GEMM_EPI_THREADS);
-          if (issuer) {
-            tma_store_3d(&tmD, sbuf, n0 + cb, m0, bz);
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&tmD, sbuf, n0 + cb, m0 + quarter * 32, bz);  // rows / columns outside the matrix are clipped
             tma_store_commit();
           }
-          ++out_blocks;
         }
         tc_fence_before();
         mbar_arrive(&acc_empty[acc]);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        if (has_coef) named_barrier(2, GEMM_EPI_THREADS);
         continue;
       }
       for (int c = colhalf * 32; c < g.tile_n; c += 64) {
@@ -334,7 +342,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (!row_ok || n_base >= g.N) continue;
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = (g.kind == 2 ? (float)(int)r[j] : __uint_as_float(r[j])) * g.alpha;
+        for (int j = 0; j < 32; ++j) v[j] = g.kind == 2 ? (float)(int)r[j] : __uint_as_float(r[j]);
+        if (g.alpha != 1.f) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] *= g.alpha;
+        }
         const int valid = min(32, g.N - n_base);
         if (has_coef) apply_coef(v, cs + c, cs + 256 + c);
         if (g.bias && g.bias_per_row) {
@@ -380,7 +392,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 
   // ---------------------------------------------------------------- teardown
-  if (g.tma_store && threadIdx.x == 64) tma_store_wait_all<0>();
+  if (g.tma_store && warp >= 2 && lane == 0) tma_store_wait_all<0>();  // every issuing lane drains its own stores
   if (*((volatile int*)g.err) != 0) {
     // Error path: give copies that are still in flight time to land before the
     // shared memory goes away.
@@ -520,7 +532,7 @@ extern "C" int b200_gemm(const B200GemmParams* p, void* stream) {
     const CUtensorMapDataType ddt = p->d_dtype == B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     uint64_t dims[3] = {(uint64_t)p->N, (uint64_t)p->M, (uint64_t)p->batch};
     uint64_t str[2] = {(uint64_t)p->ldd * 2, (uint64_t)(p->batch > 1 ? p->stride_d : (int64_t)p->ldd * p->M) * 2};
-    uint32_t box[3] = {64, GEMM_BM, 1};
+    uint32_t box[3] = {64, 32, 1};  // one epilogue warp stores 32 rows at a time
     rc = encode_tiled(&tmD, ddt, 3, p->D, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   }

@@ -178,6 +178,40 @@ __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Four K = 16 steps of one 64-element K block with as few instructions per MMA as possible (the
+// issuing thread is a single lane: its instruction latency, not the tensor pipe, bounds small-N
+// tiles).  A descriptor is hi:lo with the start address (in 16-byte units) in the low 14 bits of
+// lo, so stepping along K is a 32-bit add.  kind: 0 f16 / bf16, 1 tf32, 2 i8.
+template <int KIND>
+__device__ __forceinline__ void umma_x4(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t a_step, uint32_t b_lo,
+                                        uint32_t b_hi, uint32_t b_step, uint32_t idesc, uint32_t accumulate_first) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    uint64_t ad, bd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ad) : "r"(a_lo + k * a_step), "r"(a_hi));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(bd) : "r"(b_lo + k * b_step), "r"(b_hi));
+    const uint32_t acc = k == 0 ? accumulate_first : 1u;
+    if (KIND == 1) {
+      asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                   "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d), "l"(ad), "l"(bd), "r"(idesc), "r"(acc)
+                   : "memory");
+    } else if (KIND == 2) {
+      asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                   "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d), "l"(ad), "l"(bd), "r"(idesc), "r"(acc)
+                   : "memory");
+    } else {
+      asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                   "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d), "l"(ad), "l"(bd), "r"(idesc), "r"(acc)
+                   : "memory");
+    }
+  }
+}
+// hi / lo words of a descriptor template (start address 0)
+__device__ __forceinline__ void split_desc(uint64_t d, uint32_t* lo, uint32_t* hi) {
+  *lo = (uint32_t)d;
+  *hi = (uint32_t)(d >> 32);
+}
+
 // Arrive on `bar` once every previously issued MMA of this thread has finished.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))

@@ -19,6 +19,10 @@ CASES = [
     (2, 512, 7, 7, 512, 3, 1, 1),
     (2, 3, 224, 224, 64, 7, 2, 3),
     (2, 64, 15, 15, 64, 3, 2, 1),
+    # large enough for the resident-weight / halo-tile mode of the single-channel-block 3x3 layers
+    (16, 64, 56, 56, 64, 3, 1, 1),
+    (24, 32, 30, 27, 64, 3, 1, 1),
+    (40, 64, 20, 36, 128, 3, 1, 1),
 ]
 
 
