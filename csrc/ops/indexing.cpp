@@ -457,6 +457,8 @@ TORCH_LIBRARY_FRAGMENT(catch_b200, m) {
   m.def("nms(Tensor boxes, Tensor scores, float iou_threshold) -> Tensor");
 }
 TORCH_LIBRARY_IMPL(catch_b200, CompositeExplicitAutograd, m) { m.impl("nms", TORCH_FN(nms)); }
+// torchvision.ops.nms on this device (torchvision defines the schema when it is imported)
+TORCH_LIBRARY_IMPL(torchvision, PrivateUse1, m) { m.impl("nms", TORCH_FN(nms)); }
 
 }  // namespace ops
 }  // namespace catch_b200

@@ -298,9 +298,45 @@ Tensor absmax(const Tensor& t) {
   return out;
 }
 
+// conv1d: the same kernels through a [N, C, 1, L] view.
+Tensor qconv1d(const Tensor& input, const Tensor& weight, const std::optional<Tensor>& bias, at::IntArrayRef padding,
+               at::IntArrayRef stride, at::IntArrayRef dilation, int64_t groups, const std::optional<Tensor>& q_scale,
+               const std::optional<Tensor>& q_mode) {
+  TORCH_CHECK(input.dim() == 3 && weight.dim() == 3, "catch_b200::conv1d expects [N, C, L] input and [K, C, S] weight");
+  const int64_t p[2] = {0, padding.empty() ? 0 : padding[0]}, st[2] = {1, stride.empty() ? 1 : stride[0]};
+  const int64_t d[2] = {1, dilation.empty() ? 1 : dilation[0]};
+  Tensor out = qconv2d(input.unsqueeze(2), weight.unsqueeze(2), bias, at::IntArrayRef(p, 2), at::IntArrayRef(st, 2),
+                       at::IntArrayRef(d, 2), groups, q_scale, q_mode);
+  return out.squeeze(2);
+}
+
+// conv3d: no int8 device kernel; quantized calls compute with fake-quantized operands (same rounding as
+// the int8 path) through the floating-point convolution.
+Tensor qconv3d(const Tensor& input, const Tensor& weight, const std::optional<Tensor>& bias, at::IntArrayRef padding,
+               at::IntArrayRef stride, at::IntArrayRef dilation, int64_t groups, const std::optional<Tensor>& q_scale,
+               const std::optional<Tensor>& q_mode) {
+  if (!quant_active(q_scale, q_mode)) return at::conv3d(input, weight, bias, stride, padding, dilation, groups);
+  const int64_t mode = mode_of(q_mode);
+  const std::vector<double> sc = host_values(*q_scale);
+  Tensor xf = input.to(at::kFloat), wf = weight.to(at::kFloat);
+  Tensor xq = fake_quant(xf, sc[0]);
+  Tensor wq = mode == 1 && sc.size() > 1 ? fake_quant(wf, sc[1]) : fake_quant_rows(wf);
+  std::optional<Tensor> b;
+  if (bias.has_value() && bias->defined()) b = bias->to(at::kFloat);
+  return at::conv3d(xq, wq, b, stride, padding, dilation, groups).to(input.scalar_type());
+}
+
+// view as a named op, so that fusion graphs can keep shape changes inside a fusion group
+Tensor view_op(const Tensor& self, at::IntArrayRef size) { return self.view(size); }
+
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(catch_b200, m) {
+  m.def("conv1d(Tensor input, Tensor weight, Tensor? bias, int[] padding, int[] stride, int[] dilation, int groups, "
+        "Tensor? q_scale, Tensor? q_mode) -> Tensor");
+  m.def("conv3d(Tensor input, Tensor weight, Tensor? bias, int[] padding, int[] stride, int[] dilation, int groups, "
+        "Tensor? q_scale, Tensor? q_mode) -> Tensor");
+  m.def("view(Tensor(a) self, int[] size) -> Tensor(a)");
   m.def("conv2d(Tensor input, Tensor weight, Tensor? bias, int[] padding, int[] stride, int[] dilation, int groups, "
         "Tensor? q_scale, Tensor? q_mode) -> Tensor");
   m.def("linear(Tensor input, Tensor weight, Tensor? bias, Tensor? q_scale, Tensor? q_mode) -> Tensor");
@@ -308,6 +344,9 @@ TORCH_LIBRARY_FRAGMENT(catch_b200, m) {
 }
 TORCH_LIBRARY_IMPL(catch_b200, CompositeExplicitAutograd, m) {
   m.impl("conv2d", TORCH_FN(qconv2d));
+  m.impl("conv1d", TORCH_FN(qconv1d));
+  m.impl("conv3d", TORCH_FN(qconv3d));
+  m.impl("view", TORCH_FN(view_op));
   m.impl("linear", TORCH_FN(qlinear));
   m.impl("absmax", TORCH_FN(absmax));
 }

@@ -63,3 +63,34 @@ def test_unquantized_module_runs_float():
     x = torch.randn(3, 16)
     assert not lin[0].is_quantized()
     assert torch.allclose(lin(x), torch.nn.functional.linear(x, lin[0].weight, lin[0].bias))
+
+
+def test_conv1d_conv3d_view_custom_ops():
+    """The remaining custom ops of the reference's namespace (torch.ops.torch_mlu.{conv1d,conv3d,view})."""
+    import torch.nn.functional as F
+
+    d = "blackwell"
+    torch.manual_seed(0)
+    x, w, b = torch.randn(2, 16, 20), torch.randn(8, 16, 3), torch.randn(8)
+    y = torch.ops.catch_b200.conv1d(x.to(d), w.to(d), b.to(d), [1], [2], [1], 1, None, None)
+    assert torch.allclose(y.cpu(), F.conv1d(x, w, b, 2, 1), atol=1e-5)
+    qs, qm = torch.tensor([127.0 / x.abs().max().item(), 127.0 / w.abs().max().item()]), torch.tensor([1])
+    yq = torch.ops.catch_b200.conv1d(x.to(d), w.to(d), b.to(d), [1], [2], [1], 1, qs, qm)
+    rel = (yq.cpu() - y.cpu()).norm() / y.cpu().norm()
+    assert 0 < rel < 5e-2  # quantized, close to the float result
+    x3, w3 = torch.randn(1, 4, 5, 6, 7), torch.randn(6, 4, 3, 3, 3)
+    y3 = torch.ops.catch_b200.conv3d(x3.to(d), w3.to(d), None, [1, 1, 1], [1, 1, 1], [1, 1, 1], 1, None, None)
+    assert torch.allclose(y3.cpu(), F.conv3d(x3, w3, None, 1, 1), atol=1e-4)
+    v = torch.ops.catch_b200.view(x.to(d), [2, 320])
+    assert v.shape == (2, 320) and v.data_ptr() == v._base.data_ptr() if v._base is not None else True
+
+
+def test_torchvision_nms_dispatches_to_the_backend():
+    import torchvision
+
+    torch.manual_seed(1)
+    xy, wh = torch.rand(40, 2) * 50, torch.rand(40, 2) * 20 + 1
+    boxes, scores = torch.cat([xy, xy + wh], 1), torch.rand(40)
+    keep = torchvision.ops.nms(boxes.to("blackwell"), scores.to("blackwell"), 0.4)
+    assert keep.device.type == "blackwell"
+    assert torch.equal(keep.cpu(), torchvision.ops.nms(boxes, scores, 0.4))
