@@ -280,22 +280,10 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
           tc_fence_after();
           const uint32_t sa_16 = stage0_16 + (uint32_t)stage * stage_16;
           const uint32_t sb_16 = g.b_res_bytes ? bres_16 + (uint32_t)it * bblk_16 : sa_16 + (CONV_A_BYTES >> 4);
-#ifdef B200_AB_OLD_ISSUE
-          {
-            const uint32_t sa = sa_16 << 4, sb = sb_16 << 4;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const uint64_t bdesc = g.b_mn ? make_smem_desc_sw128(sb + k * 2048, 8192, 1024) : make_smem_desc_sw128(sb + k * 32, 16, 1024);
-              if (g.kind == 2) umma_i8(d_tmem, make_smem_desc_sw128(sa + k * 32, 16, 1024), bdesc, g.idesc, (it > 0 || k > 0) ? 1u : 0u);
-              else umma_f16(d_tmem, make_smem_desc_sw128(sa + k * 32, 16, 1024), bdesc, g.idesc, (it > 0 || k > 0) ? 1u : 0u);
-            }
-          }
-#else
           if (g.kind == 2)
             umma_x4<2>(d_tmem, a_lo0 + sa_16, a_hi, 2, b_lo0 + sb_16, b_hi, b_step, g.idesc, it > 0 ? 1u : 0u);
           else
             umma_x4<0>(d_tmem, a_lo0 + sa_16, a_hi, 2, b_lo0 + sb_16, b_hi, b_step, g.idesc, it > 0 ? 1u : 0u);
-#endif
           umma_commit(&empty_bar[stage]);
           if (++stage == g.stages) { stage = 0; phase ^= 1; }
         }
@@ -395,7 +383,9 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
       };
 
       if (g.tma_store) {
-#pragma unroll
+        // not unrolled: the body is large and the epilogue warps share the instruction cache with the
+        // producer and MMA roles
+#pragma unroll 1
         for (int bi = 0; bi < 2; ++bi) {
           const int cb = colhalf * 64 + bi * 128;
           if (cb >= g.tile_n) break;
@@ -406,21 +396,22 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
           if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has read the buffer
           __syncwarp();
           uint8_t* srow = sbuf + lane * 128;
-          float v[32];
-          uint32_t pk[16];
-          finish(ra, cb, v);
-          pack16(v, pk, g.out_dtype);
+          // the two 32-column halves run through one copy of the code (the second half is moved into the
+          // first half's registers): the loop is deliberately not unrolled to keep the kernel's hot code small
+#pragma unroll 1
+          for (int h = 0; h < 2; ++h) {
+            float v[32];
+            uint32_t pk[16];
+            finish(ra, cb + 32 * h, v);
+            pack16(v, pk, g.out_dtype);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            *reinterpret_cast<uint4*>(srow + ((k ^ (lane & 7)) * 16)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
-          finish(rb, cb + 32, v);
-          pack16(v, pk, g.out_dtype);
+            for (int k = 0; k < 4; ++k)
+              *reinterpret_cast<uint4*>(srow + (((4 * h + k) ^ (lane & 7)) * 16)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            *reinterpret_cast<uint4*>(srow + (((4 + k) ^ (lane & 7)) * 16)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
+            for (int j = 0; j < 32; ++j) ra[j] = rb[j];
+          }
           fence_proxy_async_smem();
           __syncwarp();
-#ifndef B200_AB_NO_STATS
           if (g.stats) {
             // Column sums over the 32 staged pixels (the rounded values that were stored; pixels
             // outside the tensor were zeroed above).
@@ -446,9 +437,10 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
             asm("mov.b64 {%0, %1}, %2;" : "=r"(q_lo), "=r"(q_hi) : "l"(q2));
             const float s0 = __uint_as_float(s_lo), s1 = __uint_as_float(s_hi);
             const float q0s = __uint_as_float(q_lo), q1s = __uint_as_float(q_hi);
-            st_s[bi][0] += s0; st_s[bi][1] += s1; st_q[bi][0] += q0s; st_q[bi][1] += q1s;
+            // bi is a run-time loop index: select the accumulator set explicitly so that both stay in registers
+            if (bi == 0) { st_s[0][0] += s0; st_s[0][1] += s1; st_q[0][0] += q0s; st_q[0][1] += q1s; }
+            else { st_s[1][0] += s0; st_s[1][1] += s1; st_q[1][0] += q0s; st_q[1][1] += q1s; }
           }
-#endif
           if (lane == 0) {
             // rows / channels outside the tensor are clipped by the store
             tma_store_4d(&maps.out, sbuf, co0 + cb, q0 + w_off, p0 + h_off, n0 + n_off);
@@ -532,6 +524,7 @@ struct WgradArgs {
 struct WgradMaps {
   CUtensorMap x[B200_CONV_MAX_MAPS];
   CUtensorMap dy;
+  CUtensorMap dw;  // fp32 [Cout][wtaps * Cin] accumulation buffer, box 32 x 32
 };
 
 __global__ void __launch_bounds__(CONV_THREADS, 1)
@@ -546,6 +539,8 @@ conv_wgrad_kernel(const __grid_constant__ WgradMaps maps, const __grid_constant_
   uint64_t* empty_bar = bars + CONV_MAX_STAGES;
   uint64_t* acc_full = bars + 2 * CONV_MAX_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 2);
+  // four 4 KB staging buffers (32 channels x 32 fp32 columns, 128-byte swizzle), one per epilogue warp
+  uint8_t* stage_out = reinterpret_cast<uint8_t*>(bars) + 1024;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -553,6 +548,7 @@ conv_wgrad_kernel(const __grid_constant__ WgradMaps maps, const __grid_constant_
     mbar_init(&acc_full[0], 1);
     mbar_fence_init();
     tma_prefetch_desc(&maps.dy);
+    tma_prefetch_desc(&maps.dw);
     tma_prefetch_desc(&maps.x[0]);
   }
   if (warp == 1) tmem_alloc(tmem_slot, 256);
@@ -617,38 +613,35 @@ conv_wgrad_kernel(const __grid_constant__ WgradMaps maps, const __grid_constant_
     const int quarter = warp & 3;
     if (mbar_wait(&acc_full[0], 0, g.err, ERR_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
-      const int co = co0 + quarter * 32 + lane;
+      // Each warp adds its 32 output channels x 32 columns at a time into the fp32 buffer with one
+      // tensor-map reduction (full 128-byte lines) instead of per-thread 16-byte atomics.  Channels past
+      // Cout and columns past the row end are clipped; columns past Cin inside a tap slot are zero
+      // (their input channels were zero filled), so adding them into the next tap's columns is harmless.
+      uint8_t* sbuf = stage_out + (warp - 2) * 4096;
       const int ncols = nblk * 64;
-      for (int c = 0; c < g.n_blocks_per_tile * 64; c += 32) {
-        if (c >= ncols) break;
+      for (int c = 0; c < ncols; c += 32) {
         uint32_t rr[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c, rr);
         tmem_ld_wait();
-        if (co >= g.Cout) continue;
         // flattened column -> (tap slot, channel): blocks never straddle a tap
         const int nb = nb0 + c / 64;
         const int tap = nb / g.c_blocks, cb = nb - tap * g.c_blocks;
         const int ci = cb * 64 + (c % 64);
-        if (ci >= g.Cin) continue;
-        float* dst = g.dw_acc + (long long)co * g.dw_ld + (long long)g.taps[tap].wtap * g.Cin + ci;
-        const int valid = min(32, g.Cin - ci);
-        if (g.splits == 1) {
+        if (ci >= g.Cin) continue;  // warp-uniform
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+        uint8_t* srow = sbuf + lane * 128;
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < valid) dst[j] = __uint_as_float(rr[j]);
-        } else if (valid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "r"(rr[j]), "r"(rr[j + 1]),
-                         "r"(rr[j + 2]), "r"(rr[j + 3])
-                         : "memory");
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < valid) atomicAdd(dst + j, __uint_as_float(rr[j]));
+        for (int k = 0; k < 8; ++k)
+          *reinterpret_cast<uint4*>(srow + ((k ^ (lane & 7)) * 16)) = make_uint4(rr[4 * k], rr[4 * k + 1], rr[4 * k + 2], rr[4 * k + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_reduce_add_2d(&maps.dw, sbuf, g.taps[tap].wtap * g.Cin + ci, co0 + quarter * 32);
+          tma_store_commit();
         }
       }
+      if (lane == 0) tma_store_wait_all<0>();
     }
   }
   if (*((volatile int*)g.err) != 0) {
@@ -877,7 +870,9 @@ extern "C" int b200_conv_wgrad(const B200ConvWgradParams* p, void* stream) {
   const long base_items = (long)g.m_tiles * g.n_tiles;
   int splits = p->splits;
   if (splits <= 0) {
-    splits = (int)((2L * sms + base_items - 1) / base_items);  // about two waves of CTAs
+    // one wave of CTAs: a second wave doubles the partial tiles that have to be added into the buffer and
+    // measured slower on every layer shape (e.g. 256x14x14 3x3: 138 us -> 103 us)
+    splits = (int)(sms / base_items);
     const long max_splits = (chunks + 15) / 16;                // at least 16 chunks per split
     if (splits > max_splits) splits = (int)max_splits;
     if (splits < 1) splits = 1;
@@ -894,7 +889,7 @@ extern "C" int b200_conv_wgrad(const B200ConvWgradParams* p, void* stream) {
   g.err = error_flag_ptr();
   if (!g.err) return (int)cudaErrorInvalidDevice;
   const int stage_bytes = (2 + g.n_blocks_per_tile) * 64 * 128;
-  g.stages = (200 * 1024) / stage_bytes;
+  g.stages = (227 * 1024 - 2048 - 4 * 4096 - 1024) / stage_bytes;
   if (g.stages > CONV_MAX_STAGES) g.stages = CONV_MAX_STAGES;
 
   WgradMaps maps;
@@ -911,10 +906,17 @@ extern "C" int b200_conv_wgrad(const B200ConvWgradParams* p, void* stream) {
     int rc = encode_view(&maps.dy, v, dt, 64, g.bw, g.bh, g.bni);
     if (rc) return rc;
   }
+  {
+    uint64_t dims[2] = {(uint64_t)g.dw_ld, (uint64_t)p->Cout};
+    uint64_t str[1] = {(uint64_t)g.dw_ld * 4};
+    uint32_t box[2] = {32, 32};
+    int rc = encode_tiled(&maps.dw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, p->dw_acc, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  }
   static bool attr_done[64] = {false};
   int rc = set_smem_attr_once((const void*)conv_wgrad_kernel, dev, attr_done);
   if (rc) return rc;
-  const size_t smem = (size_t)g.stages * stage_bytes + 1024 + 256;
+  const size_t smem = (size_t)g.stages * stage_bytes + 1024 /*align*/ + 1024 /*barriers*/ + 4 * 4096 /*staging*/;
   const long items = base_items * g.splits;
   conv_wgrad_kernel<<<(int)items, CONV_THREADS, smem, (cudaStream_t)stream>>>(maps, g);
   return (int)cudaGetLastError();

@@ -309,18 +309,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has read the buffer
           __syncwarp();
           uint8_t* srow = sbuf + lane * 128;
-          float v[32];
-          uint32_t pk[16];
-          finish(ra, cb, v);
-          pack16(v, pk, g.d_dtype);
+          // one copy of the code for both 32-column halves (the second half is moved into the first half's
+          // registers); not unrolled, to keep the hot code small
+#pragma unroll 1
+          for (int h = 0; h < 2; ++h) {
+            float v[32];
+            uint32_t pk[16];
+            finish(ra, cb + 32 * h, v);
+            pack16(v, pk, g.d_dtype);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            *reinterpret_cast<uint4*>(srow + ((k ^ (lane & 7)) * 16)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
-          finish(rb, cb + 32, v);
-          pack16(v, pk, g.d_dtype);
+            for (int k = 0; k < 4; ++k)
+              *reinterpret_cast<uint4*>(srow + (((4 * h + k) ^ (lane & 7)) * 16)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            *reinterpret_cast<uint4*>(srow + (((4 + k) ^ (lane & 7)) * 16)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
+            for (int j = 0; j < 32; ++j) ra[j] = rb[j];
+          }
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
