@@ -33,6 +33,7 @@ struct QWeight {
   Tensor scale;    // fp32 [rows]: 127 / absmax(row)
   uint32_t version = 0;
   const void* ptr = nullptr;
+  Tensor keep;     // the source weight: keeps its storage (and so the cache key) from being reused
 };
 
 std::mutex g_mu;
@@ -44,10 +45,15 @@ struct HostVals {
   std::vector<double> v;
   uint32_t version = 0;
   int64_t numel = 0;
+  Tensor keep;  // keeps the storage alive so that its address cannot be handed to another tensor while cached
 };
 std::unordered_map<const void*, HostVals> g_host_vals;
 std::vector<double> host_values(const Tensor& t) {
   if (!t.defined() || t.numel() == 0) return {};
+  if (t.device().is_cpu()) {  // nothing to synchronise with: read it directly
+    Tensor h = t.detach().to(at::kDouble).contiguous().view({-1});
+    return std::vector<double>(h.data_ptr<double>(), h.data_ptr<double>() + h.numel());
+  }
   const void* key = t.data_ptr();
   {
     std::lock_guard<std::mutex> g(g_mu);
@@ -59,6 +65,7 @@ std::vector<double> host_values(const Tensor& t) {
   hv.v.assign(h.data_ptr<double>(), h.data_ptr<double>() + h.numel());
   hv.version = t._version();
   hv.numel = t.numel();
+  hv.keep = t.detach();
   std::lock_guard<std::mutex> g(g_mu);
   if (g_host_vals.size() > 8192) g_host_vals.clear();
   g_host_vals[key] = hv;
@@ -78,6 +85,7 @@ QWeight quantize_weight(const Tensor& weight, const Tensor& w2d, bool per_channe
   QWeight qw;
   qw.ptr = key;
   qw.version = weight._version();
+  qw.keep = weight.detach();
   qw.q = empty_b200(w2d.sizes(), at::kChar, weight.device().index());
   qw.scale = empty_b200({w2d.size(0)}, at::kFloat, weight.device().index());
   if (per_channel) {
