@@ -44,24 +44,32 @@ class _BNActFn(torch.autograd.Function):
 
 
 class _ConvStatsFn(torch.autograd.Function):
-    """Convolution whose epilogue also accumulates per-channel sum / sum of squares of the output."""
+    """Convolution whose epilogue also accumulates per-channel sum / sum of squares of the output.
+
+    ``weight`` is the (fp32) parameter itself; it is cast to ``compute_dtype`` here, and the backward returns its
+    gradient in fp32 straight from the weight-gradient kernel's accumulation buffer (no rounding to 16 bits and
+    no cast kernels in between)."""
 
     @staticmethod
-    def forward(ctx, x, weight, stride, padding):
-        y, sums = torch.ops.catch_b200.conv2d_stats(x, weight, stride, padding)
-        ctx.save_for_backward(x, weight)
-        ctx.cfg = (stride, padding)
+    def forward(ctx, x, weight, stride, padding, compute_dtype):
+        w = weight if weight.dtype == compute_dtype else weight.to(compute_dtype)
+        y, sums = torch.ops.catch_b200.conv2d_stats(x, w, stride, padding)
+        ctx.save_for_backward(x, w)
+        ctx.cfg = (stride, padding, weight.dtype)
         ctx.mark_non_differentiable(sums)
         return y, sums
 
     @staticmethod
     def backward(ctx, grad_y, _grad_sums):
-        x, weight = ctx.saved_tensors
-        stride, padding = ctx.cfg
-        dx, dw, _ = torch.ops.aten.convolution_backward(
-            grad_y, x, weight, None, stride, padding, [1, 1], False, [0, 0], 1,
-            [ctx.needs_input_grad[0], ctx.needs_input_grad[1], False])
-        return dx, dw, None, None
+        x, w = ctx.saved_tensors
+        stride, padding, wdtype = ctx.cfg
+        need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        if wdtype == torch.float32:
+            dx, dw = torch.ops.catch_b200.conv2d_backward_fp32w(grad_y, x, w, stride, padding, need_dx, need_dw)
+        else:
+            dx, dw, _ = torch.ops.aten.convolution_backward(grad_y, x, w, None, stride, padding, [1, 1], False, [0, 0], 1,
+                                                            [need_dx, need_dw, False])
+        return dx, dw, None, None, None
 
 
 class StatsConv2d(nn.Conv2d):
@@ -74,12 +82,12 @@ class StatsConv2d(nn.Conv2d):
                 and self.padding_mode == "zeros" and self.dilation == (1, 1) and not isinstance(self.padding, str)
                 and all(s in (1, 2) for s in self.stride) and self.in_channels % 8 == 0 and self.out_channels % 64 == 0
                 and x.numel() > 0):
-            w = self.weight
-            if torch.is_autocast_enabled("blackwell"):
-                dt = torch.get_autocast_dtype("blackwell")
-                x, w = x.to(dt), w.to(dt)
-            if x.dtype in (torch.bfloat16, torch.float16) and w.dtype == x.dtype:
-                y, sums = _ConvStatsFn.apply(x, w, list(self.stride), list(self.padding))
+            autocast = torch.is_autocast_enabled("blackwell")
+            if autocast:
+                x = x.to(torch.get_autocast_dtype("blackwell"))
+            if x.dtype in (torch.bfloat16, torch.float16) and (self.weight.dtype == x.dtype or
+                                                              (autocast and self.weight.dtype == torch.float32)):
+                y, sums = _ConvStatsFn.apply(x, self.weight, list(self.stride), list(self.padding), x.dtype)
                 y._b200_channel_sums = sums
                 return y
         return super().forward(x)

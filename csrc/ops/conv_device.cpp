@@ -263,7 +263,10 @@ Tensor dgrad_impl(const Tensor& grad_in, const Tensor& weight, const ConvGeom& g
   return dx;
 }
 
-Tensor wgrad_impl(const Tensor& grad_in, const Tensor& input, const Tensor& weight, const ConvGeom& g) {
+// fp32_result: hand back the fp32 accumulation buffer itself (viewed as [K, C, R, S] in channels-last
+// memory) instead of a copy in the weight's dtype -- for callers that accumulate into fp32 master gradients.
+Tensor wgrad_impl(const Tensor& grad_in, const Tensor& input, const Tensor& weight, const ConvGeom& g,
+                  bool fp32_result = false) {
   const at::ScalarType dt = compute_dtype(grad_in.scalar_type());
   const double gscale = fp16_safe_scale(grad_in);
   const Tensor grad = gscale == 1.0 ? grad_in : grad_in * gscale;
@@ -300,6 +303,7 @@ Tensor wgrad_impl(const Tensor& grad_in, const Tensor& input, const Tensor& weig
     // acc [K][R][S][C] is the channels-last memory of a [K, C, R, S] tensor
     dw = acc.view({g.K, g.R, g.S, g.C}).permute({0, 3, 1, 2});
   }
+  if (fp32_result) return gscale == 1.0 ? dw : dw * (1.0 / gscale);
   Tensor out = at::empty_like(weight, weight.options(), weight.suggest_memory_format());
   out.copy_(gscale == 1.0 ? dw : dw * (1.0 / gscale));
   return out;
@@ -487,6 +491,24 @@ at::Tensor conv_bn_act_device(const at::Tensor& input, const at::Tensor& weight,
   }
   const at::Tensor* res = (residual.has_value() && residual->defined()) ? &*residual : nullptr;
   return forward_impl(input, weight, bias, g, scp, res, (int)act, input.scalar_type());
+}
+
+// Backward of a dense 16-bit convolution whose weight gradient is returned in fp32 (the accumulation
+// buffer of the weight-gradient kernel, no rounding to the activation dtype): used when the parameter
+// and its gradient are fp32 and only the compute copy of the weight is 16-bit.
+std::tuple<at::Tensor, at::Tensor> conv_backward_fp32w_device(const at::Tensor& grad, const at::Tensor& input,
+                                                              const at::Tensor& weight, at::IntArrayRef stride,
+                                                              at::IntArrayRef padding, bool need_dx, bool need_dw) {
+  const int64_t ones[2] = {1, 1};
+  check_supported(input, weight, stride, padding, at::IntArrayRef(ones, 2), false, 1);
+  ConvGeom g = geom(input, weight, stride, padding);
+  at::Tensor dx, dw;
+  if (need_dx) {
+    TORCH_CHECK(g.C % 8 == 0, "b200 conv dgrad: input channels must be a multiple of 8");
+    dx = dgrad_impl(grad, weight, g, input.scalar_type());
+  }
+  if (need_dw) dw = wgrad_impl(grad, input, weight, g, /*fp32_result=*/true);
+  return {dx, dw};
 }
 
 // Convolution that also returns the per-channel sum / sum of squares of its output

@@ -37,6 +37,9 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_mask(
     const std::optional<at::Tensor>& running_mean, const std::optional<at::Tensor>& running_var,
     const std::optional<at::Tensor>& residual, bool training, double momentum, double eps, int64_t act,
     const std::optional<at::Tensor>& channel_sums);
+std::tuple<at::Tensor, at::Tensor> conv_backward_fp32w_device(const at::Tensor& grad, const at::Tensor& input,
+                                                              const at::Tensor& weight, at::IntArrayRef stride,
+                                                              at::IntArrayRef padding, bool need_dx, bool need_dw);
 std::tuple<at::Tensor, at::Tensor> conv_stats_device(const at::Tensor& input, const at::Tensor& weight, at::IntArrayRef stride,
                                                      at::IntArrayRef padding);
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_backward(
@@ -89,6 +92,9 @@ TORCH_LIBRARY(catch_b200, m) {
         "Tensor? residual, bool training, float momentum, float eps, int act, Tensor? channel_sums=None) -> (Tensor, Tensor, Tensor, Tensor)");
   // convolution (no bias, 16-bit) that also returns fp64 [2 * Cout] channel sums / sums of squares of its output
   m.def("conv2d_stats(Tensor input, Tensor weight, int[] stride, int[] padding) -> (Tensor, Tensor)");
+  // (grad_input, grad_weight) of a dense 16-bit convolution; grad_weight is fp32 (undefined results where not needed)
+  m.def("conv2d_backward_fp32w(Tensor grad, Tensor input, Tensor weight, int[] stride, int[] padding, bool need_dx, "
+        "bool need_dw) -> (Tensor, Tensor)");
   m.def("batch_norm_act_backward(Tensor grad_out, Tensor out, Tensor input, Tensor? weight, Tensor? running_mean, "
         "Tensor save_mean, Tensor save_invstd, bool training, int act, bool has_residual) -> (Tensor, Tensor, Tensor, Tensor)");
 }
@@ -102,6 +108,7 @@ TORCH_LIBRARY_IMPL(catch_b200, CompositeExplicitAutograd, m) {
   m.impl("dump", TORCH_FN(dump_tensor_device));
   m.impl("batch_norm_act", TORCH_FN(batch_norm_act));
   m.impl("conv2d_stats", TORCH_FN(conv_stats_device));
+  m.impl("conv2d_backward_fp32w", TORCH_FN(conv_backward_fp32w_device));
   m.impl("batch_norm_act_mask", TORCH_FN(batch_norm_act_mask));
   m.impl("batch_norm_act_backward", TORCH_FN(batch_norm_act_backward));
 }

@@ -10,6 +10,7 @@
 #include <ATen/core/op_registration/op_registration.h>
 #include <torch/library.h>
 
+#include "../runtime/caching_allocator.h"
 #include "common.h"
 #include "kernels.h"
 
@@ -23,17 +24,24 @@ bool float_type(at::ScalarType t) { return t == at::kFloat || t == at::kBFloat16
 
 // One int32 flag per device that the kernels set when they meet an index out of range (the access
 // is skipped).  It is read, reported and cleared when the backend runs in synchronous mode.
-Tensor& bad_index_flag(int device) {
-  static std::mutex mu;
-  static std::vector<Tensor> flags(64);
-  std::lock_guard<std::mutex> lk(mu);
-  Tensor& f = flags[device & 63];
+std::mutex g_flag_mu;
+std::vector<Tensor> g_flags(64);
+const bool g_flag_dropper = [] {
+  registerCacheDropper([] {  // torch.blackwell.empty_cache() releases the flags; they are recreated on demand
+    std::lock_guard<std::mutex> lk(g_flag_mu);
+    for (auto& f : g_flags) f = Tensor();
+  });
+  return true;
+}();
+Tensor bad_index_flag(int device) {
+  std::lock_guard<std::mutex> lk(g_flag_mu);
+  Tensor& f = g_flags[device & 63];
   if (!f.defined()) f = at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(c10::Device(c10::DeviceType::PrivateUse1, device)));
   return f;
 }
 void check_bad_index(const char* op, int device) {
   if (!flags().async_disable) return;
-  Tensor& f = bad_index_flag(device);
+  Tensor f = bad_index_flag(device);
   if (f.item<int>() != 0) {
     f.zero_();
     TORCH_CHECK_INDEX(false, op, ": index out of range");

@@ -17,6 +17,7 @@
 #include <mutex>
 #include <unordered_map>
 
+#include "../runtime/caching_allocator.h"
 #include "common.h"
 #include "kernels.h"
 
@@ -48,6 +49,16 @@ struct HostVals {
   Tensor keep;  // keeps the storage alive so that its address cannot be handed to another tensor while cached
 };
 std::unordered_map<const void*, HostVals> g_host_vals;
+
+// torch.blackwell.empty_cache() also empties these caches (they keep device tensors alive)
+const bool g_dropper_registered = [] {
+  registerCacheDropper([] {
+    std::lock_guard<std::mutex> g(g_mu);
+    g_cache.clear();
+    g_host_vals.clear();
+  });
+  return true;
+}();
 std::vector<double> host_values(const Tensor& t) {
   if (!t.defined() || t.numel() == 0) return {};
   if (t.device().is_cpu()) {  // nothing to synchronise with: read it directly

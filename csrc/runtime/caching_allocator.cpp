@@ -1,5 +1,7 @@
 #include "caching_allocator.h"
 
+#include <functional>
+
 #include <c10/core/CPUAllocator.h>
 #include <c10/util/Exception.h>
 #include <algorithm>
@@ -435,7 +437,23 @@ void* raw_alloc(size_t bytes, int device, const Queue& q) { return alloc().mallo
 void raw_free(void* ptr) { alloc().free_block(ptr); }
 void recordQueue(const c10::DataPtr& ptr, const Queue& q) { alloc().record_queue(ptr.get(), q); }
 void recordQueueRaw(void* ptr, const Queue& q) { alloc().record_queue(ptr, q); }
-void emptyCache() { alloc().empty_cache(); }
+namespace {
+std::mutex g_dropper_mu;
+std::vector<std::function<void()>> g_droppers;
+}  // namespace
+void registerCacheDropper(std::function<void()> fn) {
+  std::lock_guard<std::mutex> lk(g_dropper_mu);
+  g_droppers.push_back(std::move(fn));
+}
+void emptyCache() {
+  std::vector<std::function<void()>> fns;
+  {
+    std::lock_guard<std::mutex> lk(g_dropper_mu);
+    fns = g_droppers;
+  }
+  for (auto& f : fns) f();  // upper layers release the device tensors their own caches keep alive
+  alloc().empty_cache();
+}
 MemoryStats memoryStats(int device) { return alloc().stats(device); }
 void resetPeakStats(int device) { alloc().reset_peak(device); }
 void setNativeMemoryStrategy(bool native) { alloc().set_native(native); }

@@ -16,6 +16,7 @@
 // The data structures are this project's own (intrusive doubly linked segment
 // lists plus two ordered sets per device).
 #pragma once
+#include <functional>
 #include <c10/core/Allocator.h>
 #include <cstddef>
 #include <cstdint>
@@ -52,6 +53,9 @@ void raw_free(void* ptr);
 void recordQueue(const c10::DataPtr& ptr, const Queue& q);
 void recordQueueRaw(void* ptr, const Queue& q);
 void emptyCache();
+// Layers above the runtime that cache device tensors (quantized weights, scale copies) register a
+// function that drops them; emptyCache() runs these first so that the memory really returns.
+void registerCacheDropper(std::function<void()> fn);
 MemoryStats memoryStats(int device);
 void resetPeakStats(int device);
 // true = allocate exactly what is asked from the driver (no over-sized

@@ -99,3 +99,26 @@ def test_conv2d_stats_matches_output(case, dtype):
     assert sums.dtype == torch.float64 and sums.shape == (2 * K,)
     rel = (sums.cpu() - s_ref).abs() / (s_ref.abs() + 1e-2 * s_ref.abs().max())
     assert rel.max().item() < 5e-5, rel.max().item()
+
+
+def test_conv_backward_with_fp32_weight_gradient():
+    """conv2d_backward_fp32w: data gradient in the activation dtype, weight gradient in fp32 straight from the
+    accumulation buffer, laid out like a channels-last weight."""
+    torch.manual_seed(3)
+    N, C, H, W, K, R = 8, 64, 28, 28, 128, 3
+    x = torch.randn(N, C, H, W).bfloat16()
+    w = (torch.randn(K, C, R, R) / (C * R * R) ** 0.5).bfloat16()
+    xr, wr = x.float().requires_grad_(), w.float().requires_grad_()
+    y = F.conv2d(xr, wr, None, 1, 1)
+    gy = torch.randn_like(y).bfloat16()
+    y.backward(gy.float())
+    xd = x.to(DEV).contiguous(memory_format=torch.channels_last)
+    wd = w.to(DEV).contiguous(memory_format=torch.channels_last)
+    gd = gy.to(DEV).contiguous(memory_format=torch.channels_last)
+    dx, dw = torch.ops.catch_b200.conv2d_backward_fp32w(gd, xd, wd, [1, 1], [1, 1], True, True)
+    assert dx.dtype == torch.bfloat16 and dw.dtype == torch.float32 and dw.shape == w.shape
+    assert dw.is_contiguous(memory_format=torch.channels_last)
+    assert_tensors_equal(dx, xr.grad, prec=2e-2, use_MSE=True, msg="dx")
+    assert_tensors_equal(dw, wr.grad, prec=3e-3, use_MSE=True, msg="dw")  # fp32 accumulation, no 16-bit rounding
+    dx2, dw2 = torch.ops.catch_b200.conv2d_backward_fp32w(gd, xd, wd, [1, 1], [1, 1], False, True)
+    assert_tensors_equal(dw2, wr.grad, prec=3e-3, use_MSE=True, msg="dw only")

@@ -116,16 +116,20 @@ def test_caching_allocator_stats():
     base_a, base_r = bw.memory_allocated(d), bw.memory_reserved(d)
     x = torch.empty(1000, device=DEV)  # 4000 B -> rounded to 4096, from a 2 MiB segment
     assert bw.memory_allocated(d) == base_a + 4096
-    assert bw.memory_reserved(d) >= base_r + (2 << 20)
+    # a new 2 MiB segment, unless a segment kept alive by tensors of earlier tests still had room
+    assert bw.memory_reserved(d) >= max(base_r, 2 << 20)
+    small_growth = bw.memory_reserved(d) - base_r
+    assert small_growth in (0, 2 << 20)
     y = torch.empty(3 << 20, dtype=torch.uint8, device=DEV)  # large pool: a 20 MiB segment
-    assert bw.memory_reserved(d) >= base_r + (22 << 20)
+    assert bw.memory_reserved(d) >= base_r + small_growth + (20 << 20)
     peak = bw.max_memory_allocated(d)
     assert peak >= bw.memory_allocated(d)
     del x, y
     assert bw.memory_allocated(d) == base_a
-    assert bw.memory_reserved(d) >= base_r + (22 << 20)  # cached, not returned
+    assert bw.memory_reserved(d) >= base_r + small_growth + (20 << 20)  # cached, not returned
+    grown = bw.memory_reserved(d)
     z = torch.empty(1000, device=DEV)
-    assert bw.memory_reserved(d) >= base_r + (22 << 20)  # reuse, no growth
+    assert bw.memory_reserved(d) == grown  # reuse, no growth
     del z
     bw.empty_cache()
     assert bw.memory_reserved(d) == base_r
