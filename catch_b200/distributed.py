@@ -36,3 +36,10 @@ def get_backend(group=None) -> "_C.ProcessGroupB200":
 
 
 register()
+
+# Watchdog threads use the Store; they must be gone before the interpreter tears down the objects they use
+# (a group can outlive destroy_process_group() when something else still references its backend).
+import atexit  # noqa: E402
+
+if hasattr(_C, "_stop_all_watchdogs"):  # absent only while an older native library is being rebuilt
+    atexit.register(_C._stop_all_watchdogs)

@@ -1,6 +1,7 @@
 #include "process_group.h"
 
 #include <cstdlib>
+#include <set>
 
 #include <ATen/ATen.h>
 #include <c10/util/Exception.h>
@@ -221,6 +222,11 @@ c10::intrusive_ptr<c10::ivalue::Future> WorkB200::getFuture() {
 }
 
 // ------------------------------------------------------------------ ProcessGroupB200
+namespace {
+std::mutex g_groups_mu;
+std::set<ProcessGroupB200*> g_groups;
+}  // namespace
+
 ProcessGroupB200::ProcessGroupB200(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size,
                                    std::chrono::milliseconds timeout)
     : c10d::Backend(rank, size), store_(store), timeout_(timeout), send_seq_(size, 0), recv_seq_(size, 0) {
@@ -228,6 +234,10 @@ ProcessGroupB200::ProcessGroupB200(const c10::intrusive_ptr<c10d::Store>& store,
   B200LOG(INFO) << "ProcessGroupB200 rank " << rank << "/" << size << " uid " << uid_;
   if (const char* e = std::getenv("CATCH_B200_HEARTBEAT_MS")) hb_interval_ms_ = std::atoll(e);
   if (const char* e = std::getenv("CATCH_B200_HEARTBEAT_TIMEOUT_MS")) hb_timeout_ms_ = std::atoll(e);
+  {
+    std::lock_guard<std::mutex> lk(g_groups_mu);
+    g_groups.insert(this);
+  }
   if (size > 1 && hb_interval_ms_ > 0) start_watchdog();
 }
 
@@ -285,18 +295,34 @@ void ProcessGroupB200::watchdog_loop() {
   }
 }
 
+void stop_all_watchdogs() {
+  std::vector<ProcessGroupB200*> groups;
+  {
+    std::lock_guard<std::mutex> lk(g_groups_mu);
+    groups.assign(g_groups.begin(), g_groups.end());
+  }
+  for (auto* g : groups) g->stop_watchdog();
+}
+
+void ProcessGroupB200::stop_watchdog() {
+  if (!watchdog_.joinable()) return;
+  {
+    std::lock_guard<std::mutex> lk(wd_mu_);
+    wd_stop_ = true;
+  }
+  wd_cv_.notify_all();
+  watchdog_.join();
+  try {
+    store_->add(uid_ + "/bye/" + std::to_string(rank_), 1);
+  } catch (...) {
+  }
+}
+
 ProcessGroupB200::~ProcessGroupB200() {
-  if (watchdog_.joinable()) {
-    {
-      std::lock_guard<std::mutex> lk(wd_mu_);
-      wd_stop_ = true;
-    }
-    wd_cv_.notify_all();
-    watchdog_.join();
-    try {
-      store_->add(uid_ + "/bye/" + std::to_string(rank_), 1);
-    } catch (...) {
-    }
+  stop_watchdog();
+  {
+    std::lock_guard<std::mutex> lk(g_groups_mu);
+    g_groups.erase(this);
   }
   try {
     if (arena_) {

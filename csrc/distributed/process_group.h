@@ -134,6 +134,10 @@ class ProcessGroupB200 : public c10d::Backend {
   // collective raises before anything is launched.
   void start_watchdog();
   void watchdog_loop();
+ public:
+  // Stops and joins the watchdog thread and posts this rank's goodbye (idempotent).
+  void stop_watchdog();
+ private:
   std::thread watchdog_;
   std::mutex wd_mu_;
   std::condition_variable wd_cv_;
@@ -142,6 +146,10 @@ class ProcessGroupB200 : public c10d::Backend {
   std::atomic<bool> status_logged_{false};
   int64_t hb_interval_ms_ = 1000, hb_timeout_ms_ = 15000;
 };
+
+// Stops the watchdog thread of every live group: run at interpreter exit, before static objects (the
+// Store server among them) go away under a thread that still uses them.
+void stop_all_watchdogs();
 
 // Number of ProcessGroupB200 objects created so far in this process (names Store keys).
 int next_process_group_id();
