@@ -1,6 +1,6 @@
 """Summarise an `ncu --metrics gpu__time_duration.sum --csv` launch list by kernel.
 
-    python benchmarks/summarize_launches.py gpurun_out/launches.csv [top_n]
+    python benchmarks/summarize_launches.py launches.csv [top_n]
 """
 import collections
 import csv
