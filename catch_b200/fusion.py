@@ -25,9 +25,11 @@ import torch.nn.functional as F
 
 class _BNActFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, running_mean, running_var, residual, training, momentum, eps, act, sums=None):
+    def forward(ctx, x, weight, bias, running_mean, running_var, residual, training, momentum, eps, act, sums=None,
+                num_batches_tracked=None):
         out, mean, invstd, mask = torch.ops.catch_b200.batch_norm_act_mask(x, weight, bias, running_mean, running_var,
-                                                                           residual, training, momentum, eps, act, sums)
+                                                                           residual, training, momentum, eps, act, sums,
+                                                                           num_batches_tracked)
         # with a ReLU the backward only needs to know which outputs were positive: one bit each
         ctx.save_for_backward(mask if mask.numel() else out, x, weight, running_mean, mean, invstd)
         ctx.cfg = (training, act, residual is not None)
@@ -40,22 +42,31 @@ class _BNActFn(torch.autograd.Function):
         dx, dgamma, dbeta, dres = torch.ops.catch_b200.batch_norm_act_backward(
             grad_out, out, x, weight, running_mean, mean, invstd, training, act, has_res)
         return (dx, dgamma if weight is not None else None, dbeta if weight is not None else None, None, None,
-                dres if has_res else None, None, None, None, None, None)
+                dres if has_res else None, None, None, None, None, None, None)
 
 
 class _ConvStatsFn(torch.autograd.Function):
     """Convolution whose epilogue also accumulates per-channel sum / sum of squares of the output.
 
-    ``weight`` is the (fp32) parameter itself; it is cast to ``compute_dtype`` here, and the backward returns its
-    gradient in fp32 straight from the weight-gradient kernel's accumulation buffer (no rounding to 16 bits and
-    no cast kernels in between)."""
+    ``weight`` is the (fp32) parameter itself.  Its 16-bit compute copy is ``weight._b200_lowp`` when a data-parallel
+    wrapper maintains one (refreshed by the optimizer kernel), else a cast made here.  The backward returns the
+    weight gradient in fp32 straight from the weight-gradient kernel's accumulation buffer (no rounding to 16 bits,
+    no cast kernels); when the parameter's gradient lives in a flat bucket (``weight._b200_grad_acc``) the kernel
+    adds into that bucket directly and the bucket's owner is told that the gradient is ready."""
 
     @staticmethod
     def forward(ctx, x, weight, stride, padding, compute_dtype):
-        w = weight if weight.dtype == compute_dtype else weight.to(compute_dtype)
+        lowp = getattr(weight, "_b200_lowp", None)
+        if weight.dtype == compute_dtype:
+            w = weight
+        elif lowp is not None and lowp.dtype == compute_dtype and lowp.shape == weight.shape:
+            w = lowp
+        else:
+            w = weight.to(compute_dtype)
         y, sums = torch.ops.catch_b200.conv2d_stats(x, w, stride, padding)
         ctx.save_for_backward(x, w)
         ctx.cfg = (stride, padding, weight.dtype)
+        ctx.param = weight
         ctx.mark_non_differentiable(sums)
         return y, sums
 
@@ -65,6 +76,15 @@ class _ConvStatsFn(torch.autograd.Function):
         stride, padding, wdtype = ctx.cfg
         need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         if wdtype == torch.float32:
+            acc = getattr(ctx.param, "_b200_grad_acc", None) if need_dw else None
+            p = ctx.param
+            # the bucket slice must hold the gradient as [K][R][S][C]: channels-last parameters and 1x1 filters do
+            if (acc is not None and p.grad is not None and p.grad.dtype == torch.float32 and p.dim() == 4
+                    and (p.shape[2] * p.shape[3] == 1 or p.is_contiguous(memory_format=torch.channels_last))):
+                flat, ready = acc
+                dx, _ = torch.ops.catch_b200.conv2d_backward_fp32w(grad_y, x, w, stride, padding, need_dx, True, flat)
+                ready(ctx.param)
+                return dx, None, None, None, None
             dx, dw = torch.ops.catch_b200.conv2d_backward_fp32w(grad_y, x, w, stride, padding, need_dx, need_dw)
         else:
             dx, dw, _ = torch.ops.aten.convolution_backward(grad_y, x, w, None, stride, padding, [1, 1], False, [0, 0], 1,
@@ -105,10 +125,12 @@ class BatchNormAct2d(nn.BatchNorm2d):
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         training = self.training or (self.running_mean is None and self.running_var is None)
         momentum = 0.0 if self.momentum is None else self.momentum
-        if self.training and self.track_running_stats and self.num_batches_tracked is not None:
+        count_batch = self.training and self.track_running_stats and self.num_batches_tracked is not None
+        if count_batch and self.momentum is None:
+            # cumulative moving average: the count is needed on the host
             self.num_batches_tracked.add_(1)
-            if self.momentum is None:
-                momentum = 1.0 / float(self.num_batches_tracked)
+            momentum = 1.0 / float(self.num_batches_tracked)
+            count_batch = False
         rm = self.running_mean if (not self.training or self.track_running_stats) else None
         rv = self.running_var if (not self.training or self.track_running_stats) else None
         c_vec = 4 if x.dtype == torch.float32 else 8
@@ -116,8 +138,11 @@ class BatchNormAct2d(nn.BatchNorm2d):
                 and x.dtype in (torch.float32, torch.bfloat16, torch.float16) and x.numel() > 0
                 and (residual is None or (residual.shape == x.shape and residual.dtype == x.dtype))):
             sums = getattr(x, "_b200_channel_sums", None) if training else None
+            # the fused kernel also increments num_batches_tracked (no separate tiny launch per batch norm)
             return _BNActFn.apply(x, self.weight, self.bias, rm, rv, residual, training, momentum, self.eps, self.act,
-                                  sums)
+                                  sums, self.num_batches_tracked if count_batch else None)
+        if count_batch:
+            self.num_batches_tracked.add_(1)
         y = F.batch_norm(x, rm, rv, self.weight, self.bias, training, momentum, self.eps)
         if residual is not None:
             y = y + residual

@@ -36,8 +36,6 @@ def lib() -> C.CDLL:
     if not getattr(l, "_catch_b200_typed", False):
         l.b200_gemm.argtypes = [C.POINTER(GemmParams), C.c_void_p]
         l.b200_gemm.restype = C.c_int
-        l.b200_gemm_debug_override.argtypes = [C.c_int, C.c_int, C.c_int]
-        l.b200_gemm_debug_override.restype = None
         l.b200_read_and_clear_error_flag.argtypes = [C.POINTER(C.c_int)]
         l.b200_read_and_clear_error_flag.restype = C.c_int
         l.b200_error_string.argtypes = [C.c_int]

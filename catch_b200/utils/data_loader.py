@@ -32,9 +32,14 @@ class PrefetchLoader:
 
     ``use_io_queue`` (default: the ``USE_IO_QUEUE`` environment variable, ON unless set
     to OFF) selects the overlapped path; otherwise batches are copied synchronously.
+    ``depth`` batches are kept in flight on the IO queue (two by default, so a copy that takes
+    longer than one step does not stall the next one).  ``transform`` (optional) is applied to
+    each device batch on the IO queue, e.g. a cast to the compute dtype and memory format, which
+    takes that pass off the compute queue.
     """
 
-    def __init__(self, loader: Iterable, device="blackwell", use_io_queue=None, pin: bool = True):
+    def __init__(self, loader: Iterable, device="blackwell", use_io_queue=None, pin: bool = True, depth: int = 2,
+                 transform=None):
         self.loader = loader
         self.device = torch.device(device)
         if self.device.index is None:
@@ -43,6 +48,8 @@ class PrefetchLoader:
             use_io_queue = os.environ.get("USE_IO_QUEUE", "ON").upper() != "OFF"
         self.use_io_queue = use_io_queue
         self.pin = pin
+        self.depth = max(1, int(depth))
+        self.transform = transform
 
     def __len__(self):
         return len(self.loader)
@@ -60,7 +67,8 @@ class PrefetchLoader:
     def __iter__(self) -> Iterator:
         if not self.use_io_queue:
             for batch in self.loader:
-                yield self._to_device(batch, None)
+                moved = self._to_device(batch, None)
+                yield self.transform(moved) if self.transform is not None else moved
             return
         io_queue = torch.b200.queue_from_pool(self.device)
         it = iter(self.loader)
@@ -69,17 +77,29 @@ class PrefetchLoader:
             try:
                 batch = next(it)
             except StopIteration:
-                return None, None
+                return None
             with torch.b200.stream(io_queue):
                 moved = self._to_device(batch, io_queue)
+                if self.transform is not None:
+                    moved = self.transform(moved)
+                    _map(moved, lambda t: torch.b200.record_queue(t, io_queue) or t)
                 done = torch.b200.Notifier(enable_timing=False)
                 done.place(io_queue)
             return moved, done
 
-        nxt, ev = prefetch()
-        while nxt is not None:
-            cur, cur_ev = nxt, ev
-            nxt, ev = prefetch()                       # overlaps with the consumer's compute
+        import collections
+
+        inflight = collections.deque()
+        for _ in range(self.depth):
+            item = prefetch()
+            if item is None:
+                break
+            inflight.append(item)
+        while inflight:
+            cur, cur_ev = inflight.popleft()
+            item = prefetch()                          # overlaps with the consumer's compute
+            if item is not None:
+                inflight.append(item)
             cur_ev.wait(torch.b200.current_queue(self.device))  # device-side hand-off
             _map(cur, lambda t: torch.b200.record_queue(t, torch.b200.current_queue(self.device)) or t)
             yield cur

@@ -18,7 +18,8 @@
 
 namespace {
 
-constexpr int READY = 0, DONE = 16, COUNTER = 64;  // slots 32..63: point-to-point ready / done
+constexpr int READY = 0, DONE = 16, COUNTER = B200_COMM_COUNTER_SLOT;  // slots 32..63: point-to-point ready / done;
+                                                                    // COUNTER + 1: CTAs done with the cast phase
 constexpr unsigned long long kDefaultTimeoutNs = 10000000000ull;
 
 __device__ __forceinline__ unsigned long long gtimer() {
@@ -81,6 +82,11 @@ template <typename A> __device__ __forceinline__ A comb(int op, A a, A b) {
     default: return a + b;
   }
 }
+// scale is a float; integer accumulators are scaled in double so that 1/world does not truncate to zero
+template <typename A> __device__ __forceinline__ A apply_scale(A a, float scale) { return (A)(a * (A)scale); }
+template <> __device__ __forceinline__ long long apply_scale<long long>(long long a, float scale) {
+  return (long long)llrint((double)a * (double)scale);
+}
 template <typename T, typename A> __device__ __forceinline__ A widen(T v) { return (A)v; }
 template <> __device__ __forceinline__ float widen<__nv_bfloat16, float>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <> __device__ __forceinline__ float widen<__half, float>(__half v) { return __half2float(v); }
@@ -88,13 +94,15 @@ template <typename T, typename A> __device__ __forceinline__ T narrow(A v) { ret
 template <> __device__ __forceinline__ __nv_bfloat16 narrow<__nv_bfloat16, float>(float v) { return __float2bfloat16(v); }
 template <> __device__ __forceinline__ __half narrow<__half, float>(float v) { return __float2half(v); }
 
-// Start barrier: block 0 announces "my data is ready" to every peer; every block waits
-// for every peer's announcement.  Returns false if a wait gave up.
-__device__ bool start_barrier(const B200CommCtx& c, unsigned long long seq, int no_signal, unsigned long long limit) {
+// Start barrier: one CTA (`this_cta_announces`) tells every peer "my data is ready"; every CTA waits for
+// every peer's announcement.  no_signal (tests only) suppresses the announcement so that peers run into
+// their bounded wait.  Returns false if a wait gave up.
+__device__ bool start_barrier(const B200CommCtx& c, unsigned long long seq, int no_signal, unsigned long long limit,
+                              bool this_cta_announces) {
   __shared__ int ok_sh;
   if (threadIdx.x == 0) ok_sh = 1;
   __syncthreads();
-  if (blockIdx.x == 0 && threadIdx.x < c.world && !no_signal) {
+  if (this_cta_announces && threadIdx.x < c.world && !no_signal) {
     __threadfence_system();
     st_release_sys(c.flags[threadIdx.x] + READY + c.rank, seq);
   }
@@ -104,25 +112,32 @@ __device__ bool start_barrier(const B200CommCtx& c, unsigned long long seq, int 
   __syncthreads();
   return ok_sh != 0;
 }
+__device__ bool start_barrier(const B200CommCtx& c, unsigned long long seq, int no_signal, unsigned long long limit) {
+  return start_barrier(c, seq, no_signal, limit, blockIdx.x == 0);
+}
 
-// End barrier: the last block to finish tells every peer "I am done writing to you" and
-// waits until every peer has said the same, so the kernel only completes when this
-// rank's arena holds the full result and nobody still reads it.
-__device__ void end_barrier(const B200CommCtx& c, unsigned long long seq, unsigned long long limit) {
+// End barrier: the last CTA to finish tells every peer "I am done reading from and writing to you" and
+// waits until every peer has said the same, so the kernel only completes when this rank's arena holds
+// the full result and nobody still reads it.  With all_ctas_wait every CTA waits for the peers (and
+// may then reuse memory that the peers were reading); returns false if a wait gave up.
+__device__ bool end_barrier(const B200CommCtx& c, unsigned long long seq, unsigned long long limit, bool all_ctas_wait) {
   __threadfence_system();
   __syncthreads();
-  __shared__ int last_sh;
+  __shared__ int last_sh, ok_sh;
   if (threadIdx.x == 0) {
     const unsigned long long old = atomicAdd(c.flags[c.rank] + COUNTER, 1ull);
     last_sh = (old == gridDim.x - 1) ? 1 : 0;
     if (last_sh) c.flags[c.rank][COUNTER] = 0;
+    ok_sh = 1;
   }
   __syncthreads();
-  if (!last_sh) return;
+  if (last_sh && threadIdx.x < c.world) st_release_sys(c.flags[threadIdx.x] + DONE + c.rank, seq);
+  if (!last_sh && !all_ctas_wait) return true;
   if (threadIdx.x < c.world) {
-    st_release_sys(c.flags[threadIdx.x] + DONE + c.rank, seq);
-    bounded_wait(c.flags[c.rank] + DONE + threadIdx.x, seq, c.status, threadIdx.x, limit);
+    if (!bounded_wait(c.flags[c.rank] + DONE + threadIdx.x, seq, c.status, threadIdx.x, limit)) ok_sh = 0;
   }
+  __syncthreads();
+  return ok_sh != 0;
 }
 
 template <typename T>
@@ -168,7 +183,7 @@ __global__ void __launch_bounds__(512) allreduce_kernel(const B200CommCtx c, siz
 #pragma unroll
       for (int k = 0; k < V; ++k) {
         A a = acc[u][k];
-        if (scale != 1.f) a = (A)(a * (A)scale);
+        if (scale != 1.f) a = apply_scale<A>(a, scale);
         if (avg) a = a / (A)c.world;
         tv[k] = narrow<T, A>(a);
       }
@@ -183,70 +198,162 @@ __global__ void __launch_bounds__(512) allreduce_kernel(const B200CommCtx c, siz
       }
     }
   }
-  end_barrier(c, seq, limit);
+  end_barrier(c, seq, limit, false);
 }
 
+// One element of the optimizer update on the fp32 master parameter `wk` with reduced gradient `d`
+// (already scaled); `s` indexes this rank's state shards.
+__device__ __forceinline__ float opt_update(const B200FusedOptArgs& o, float wk, float d, long long s) {
+  if (o.kind == 0) {
+    d += o.weight_decay * wk;
+    if (o.momentum != 0.f) {
+      const float b = o.first_step ? d : o.momentum * o.state1[s] + (1.f - o.dampening) * d;
+      o.state1[s] = b;
+      d = o.nesterov ? d + o.momentum * b : b;
+    }
+    return wk - o.lr * d;
+  }
+  wk *= 1.f - o.lr * o.weight_decay;
+  const float a = o.beta1 * o.state1[s] + (1.f - o.beta1) * d;
+  const float v = o.beta2 * o.state2[s] + (1.f - o.beta2) * d * d;
+  o.state1[s] = a;
+  o.state2[s] = v;
+  return wk - (o.lr / o.bc1) * (a / (sqrtf(v) / o.bc2_sqrt + o.eps));
+}
+
+// Fused bucket step.  T is the dtype of the gradients that cross NVLink.
+//   phase 0 (only with o.cast_src): every CTA converts its slice of this rank's local fp32 gradients
+//            into the T-typed exchange region of the arena and clears the source; the CTA that finishes
+//            last announces "ready" (so peers only ever read a complete exchange region);
+//   phase 1: reduce-scatter of the exchange regions (U vectors per thread in flight per peer), scale,
+//            optimizer update of this rank's shard of the fp32 master parameters;
+//   phase 2: the updated shard (and its optional 16-bit copy) is written to every peer;
+//   phase 3 (only with o.zero_grads and no cast_src): once every peer has said "done", nobody reads this
+//            rank's gradient region any more and the CTAs clear it for the next backward pass.
 template <typename T>
 __global__ void __launch_bounds__(512) allreduce_opt_kernel(const B200CommCtx c, size_t goff, size_t poff, long long n,
                                                             float scale, const B200FusedOptArgs o,
                                                             unsigned long long seq) {
   constexpr int V = Vec<T>::N;
+  constexpr int U = V == 4 ? 4 : 2;   // 16 floats of gradient per thread and step either way
   const unsigned long long limit = c.timeout_ns ? c.timeout_ns : kDefaultTimeoutNs;
-  if (!start_barrier(c, seq, 0, limit)) return;
   const long long nvec = (n + V - 1) / V;
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  __shared__ int flag_sh;
+  if (o.cast_src) {
+    T* mine = reinterpret_cast<T*>(static_cast<char*>(c.arena[c.rank]) + goff);
+    float* src = o.cast_src;
+    for (long long i = gtid; i < nvec; i += gstride) {
+      alignas(16) T tmp[V];
+#pragma unroll
+      for (int k = 0; k < V; k += 4) {
+        // the fp32 source is padded to whole vectors like every arena region
+        const float4 f = *reinterpret_cast<const float4*>(src + i * V + k);
+        tmp[k] = from_f<T>(f.x); tmp[k + 1] = from_f<T>(f.y); tmp[k + 2] = from_f<T>(f.z); tmp[k + 3] = from_f<T>(f.w);
+        if (o.zero_grads) *reinterpret_cast<float4*>(src + i * V + k) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      reinterpret_cast<uint4*>(mine)[i] = *reinterpret_cast<const uint4*>(tmp);
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned long long old = atomicAdd(c.flags[c.rank] + COUNTER + 1, 1ull);
+      flag_sh = old == gridDim.x - 1;
+      if (flag_sh) c.flags[c.rank][COUNTER + 1] = 0;
+    }
+    __syncthreads();
+    // only the last CTA may announce that the exchange region is complete
+    if (!start_barrier(c, seq, 0, limit, flag_sh != 0)) return;
+  } else {
+    if (!start_barrier(c, seq, 0, limit)) return;
+  }
   const long long per = (nvec + c.world - 1) / c.world;
   const long long v0 = per * c.rank, v1 = (v0 + per < nvec) ? v0 + per : nvec;
-  for (long long i = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < v1; i += (long long)gridDim.x * blockDim.x) {
-    float g[V];
-    alignas(16) T tmp[V];
+  for (long long i0 = v0 + gtid; i0 < v1; i0 += gstride * U) {
+    float g[U][V];
     for (int p = 0; p < c.world; ++p) {
       const int peer = (c.rank + p) % c.world;
-      *reinterpret_cast<uint4*>(tmp) = reinterpret_cast<const uint4*>(static_cast<const char*>(c.arena[peer]) + goff)[i];
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(c.arena[peer]) + goff);
+      uint4 raw[U];
 #pragma unroll
-      for (int k = 0; k < V; ++k) g[k] = p == 0 ? to_f<T>(tmp[k]) : g[k] + to_f<T>(tmp[k]);
-    }
-    // optimizer on this rank's shard of the fp32 master parameters (local arena)
-    float* pw = reinterpret_cast<float*>(static_cast<char*>(c.arena[c.rank]) + poff) + i * V;
-    const long long s = (i - v0) * V;  // index into the local state shards
-    alignas(16) float w[V];
-#pragma unroll
-    for (int k = 0; k < V; ++k) {
-      float wk = pw[k];
-      float d = g[k] * scale;
-      if (o.kind == 0) {
-        d += o.weight_decay * wk;
-        if (o.momentum != 0.f) {
-          const float b = o.first_step ? d : o.momentum * o.state1[s + k] + (1.f - o.dampening) * d;
-          o.state1[s + k] = b;
-          d = o.nesterov ? d + o.momentum * b : b;
-        }
-        wk -= o.lr * d;
-      } else {
-        wk *= 1.f - o.lr * o.weight_decay;
-        const float a = o.beta1 * o.state1[s + k] + (1.f - o.beta1) * d;
-        const float v = o.beta2 * o.state2[s + k] + (1.f - o.beta2) * d * d;
-        o.state1[s + k] = a;
-        o.state2[s + k] = v;
-        wk -= (o.lr / o.bc1) * (a / (sqrtf(v) / o.bc2_sqrt + o.eps));
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * gstride;
+        if (i < v1) raw[u] = src[i];
       }
-      w[k] = wk;
-    }
-    // all-gather of the updated parameters: push to every peer (fp32 master copy and
-    // the optional 16-bit copy used by autocast forward passes)
-    for (int p = 0; p < c.world; ++p) {
-      const int peer = (c.rank + p) % c.world;
-      float* dst = reinterpret_cast<float*>(static_cast<char*>(c.arena[peer]) + poff) + i * V;
 #pragma unroll
-      for (int k = 0; k < V; k += 4) *reinterpret_cast<float4*>(dst + k) = *reinterpret_cast<const float4*>(w + k);
+      for (int u = 0; u < U; ++u) {
+        const T* tv = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+        for (int k = 0; k < V; ++k) g[u][k] = p == 0 ? to_f<T>(tv[k]) : g[u][k] + to_f<T>(tv[k]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * gstride;
+      if (i >= v1) continue;
+      // optimizer on this rank's shard of the fp32 master parameters (local arena)
+      const float* pw = reinterpret_cast<const float*>(static_cast<const char*>(c.arena[c.rank]) + poff) + i * V;
+      const long long s = (i - v0) * V;  // index into the local state shards
+      alignas(16) float w[V];
+#pragma unroll
+      for (int k = 0; k < V; k += 4) *reinterpret_cast<float4*>(w + k) = *reinterpret_cast<const float4*>(pw + k);
+#pragma unroll
+      for (int k = 0; k < V; ++k) w[k] = opt_update(o, w[k], g[u][k] * scale, s + k);
+      alignas(16) unsigned short lw[V];
       if (o.lowp_offset) {
-        unsigned short* lp = reinterpret_cast<unsigned short*>(static_cast<char*>(c.arena[peer]) + o.lowp_offset) + i * V;
 #pragma unroll
         for (int k = 0; k < V; ++k)
-          lp[k] = o.lowp_dtype == B200_BF16 ? __bfloat16_as_ushort(__float2bfloat16(w[k])) : __half_as_ushort(__float2half(w[k]));
+          lw[k] = o.lowp_dtype == B200_BF16 ? __bfloat16_as_ushort(__float2bfloat16(w[k])) : __half_as_ushort(__float2half(w[k]));
+      }
+      // all-gather of the updated parameters: push to every peer (fp32 master copy and the optional
+      // 16-bit copy that autocast forward passes read)
+      for (int p = 0; p < c.world; ++p) {
+        const int peer = (c.rank + p) % c.world;
+        float* dst = reinterpret_cast<float*>(static_cast<char*>(c.arena[peer]) + poff) + i * V;
+#pragma unroll
+        for (int k = 0; k < V; k += 4) *reinterpret_cast<float4*>(dst + k) = *reinterpret_cast<const float4*>(w + k);
+        if (o.lowp_offset) {
+          unsigned short* lp = reinterpret_cast<unsigned short*>(static_cast<char*>(c.arena[peer]) + o.lowp_offset) + i * V;
+          if (V == 8) *reinterpret_cast<uint4*>(lp) = *reinterpret_cast<const uint4*>(lw);
+          else *reinterpret_cast<uint2*>(lp) = *reinterpret_cast<const uint2*>(lw);
+        }
       }
     }
   }
-  end_barrier(c, seq, limit);
+  if (o.zero_grads && !o.cast_src) {
+    // Every CTA waits for every peer's "done": the grid is at most 128 CTAs of 512 threads, all of which
+    // become resident on an otherwise idle GPU, and compute kernels never wait on this one.
+    const bool ok = end_barrier(c, seq, limit, /*all_ctas_wait=*/true);
+    if (!ok) return;
+    uint4* mine = reinterpret_cast<uint4*>(static_cast<char*>(c.arena[c.rank]) + goff);
+    for (long long i = gtid; i < nvec; i += gstride) mine[i] = make_uint4(0u, 0u, 0u, 0u);
+  } else {
+    end_barrier(c, seq, limit, false);
+  }
+}
+
+// out[i - e0] = op over ranks of arena[rank][offset + i] for i in [e0, e1): the pull half of reduce
+// (root: the whole message, everybody else: nothing) and of reduce_scatter (rank r: piece r).  Ranks
+// with an empty range still take part in the two barriers.
+template <typename T>
+__global__ void __launch_bounds__(512) reduce_range_kernel(const B200CommCtx c, size_t offset, long long e0, long long e1,
+                                                           T* out, int op, unsigned long long seq) {
+  using A = typename AccOf<T>::type;
+  const unsigned long long limit = c.timeout_ns ? c.timeout_ns : kDefaultTimeoutNs;
+  if (!start_barrier(c, seq, 0, limit)) return;
+  const bool avg = op == COMM_AVG;
+  for (long long i = e0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < e1; i += (long long)gridDim.x * blockDim.x) {
+    A acc = 0;
+    for (int p = 0; p < c.world; ++p) {
+      const int peer = (c.rank + p) % c.world;
+      const A v = widen<T, A>(reinterpret_cast<const T*>(static_cast<const char*>(c.arena[peer]) + offset)[i]);
+      acc = p == 0 ? v : comb<A>(avg ? COMM_SUM : op, acc, v);
+    }
+    if (avg) acc = acc / (A)c.world;
+    out[i - e0] = narrow<T, A>(acc);
+  }
+  end_barrier(c, seq, limit, false);
 }
 
 __global__ void signal_kernel(const B200CommCtx c, int which, int peer, unsigned long long seq) {
@@ -322,26 +429,36 @@ extern "C" int b200_comm_allreduce(const B200CommCtx* ctx, size_t offset, long l
 extern "C" int b200_comm_allreduce_opt(const B200CommCtx* ctx, size_t goff, size_t poff, long long n, int grad_dtype,
                                        float scale, const B200FusedOptArgs* opt, unsigned long long seq, void* stream) {
   if (n <= 0) return 0;
-  if (ctx->world > B200_COMM_MAX_RANKS || (goff & 15) || (poff & 15)) return (int)cudaErrorInvalidValue;
+  if (ctx->world > B200_COMM_MAX_RANKS || (goff & 15) || (poff & 15) || (opt->lowp_offset & 15)) return (int)cudaErrorInvalidValue;
+  if (opt->cast_src && (reinterpret_cast<uintptr_t>(opt->cast_src) & 15)) return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
+  // Grid: enough CTAs to keep the links busy (the same sizing as the plain all-reduce), never more than
+  // 128 so that all of them are resident at once (the cast phase and the clearing phase rely on that).
+  const int V = grad_dtype == B200_F32 ? 4 : 8, U = grad_dtype == B200_F32 ? 4 : 2;
+  const long long nvec = (n + V - 1) / V;
+  const long long per = (nvec + ctx->world - 1) / ctx->world;
+  long long work = (per + U - 1) / U;
+  if (opt->cast_src || opt->zero_grads) work = work > nvec / 8 ? work : nvec / 8;  // the local passes cover the whole bucket
+  const int grid = comm_grid(work, 512, per * 16 >= (2LL << 20) ? 128 : 64);
   switch (grad_dtype) {
-    case B200_F32: {
-      const long long per = (((n + 3) / 4) + ctx->world - 1) / ctx->world;
-      allreduce_opt_kernel<float><<<comm_grid(per, 512, 64), 512, 0, s>>>(*ctx, goff, poff, n, scale, *opt, seq);
+    case B200_F32:
+      if (opt->cast_src) return (int)cudaErrorInvalidValue;  // fp32 gradients are exchanged in place
+      allreduce_opt_kernel<float><<<grid, 512, 0, s>>>(*ctx, goff, poff, n, scale, *opt, seq);
       break;
-    }
-    case B200_BF16: {
-      const long long per = (((n + 7) / 8) + ctx->world - 1) / ctx->world;
-      allreduce_opt_kernel<__nv_bfloat16><<<comm_grid(per, 512, 64), 512, 0, s>>>(*ctx, goff, poff, n, scale, *opt, seq);
-      break;
-    }
-    case B200_F16: {
-      const long long per = (((n + 7) / 8) + ctx->world - 1) / ctx->world;
-      allreduce_opt_kernel<__half><<<comm_grid(per, 512, 64), 512, 0, s>>>(*ctx, goff, poff, n, scale, *opt, seq);
-      break;
-    }
+    case B200_BF16: allreduce_opt_kernel<__nv_bfloat16><<<grid, 512, 0, s>>>(*ctx, goff, poff, n, scale, *opt, seq); break;
+    case B200_F16: allreduce_opt_kernel<__half><<<grid, 512, 0, s>>>(*ctx, goff, poff, n, scale, *opt, seq); break;
     default: return (int)cudaErrorInvalidValue;
   }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_comm_reduce_range(const B200CommCtx* ctx, size_t offset, long long e0, long long e1, void* out,
+                                      int dtype, int op, unsigned long long seq, void* stream) {
+  if (ctx->world > B200_COMM_MAX_RANKS) return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long n = e1 > e0 ? e1 - e0 : 0;
+  COMM_DISPATCH(dtype, T, (reduce_range_kernel<T><<<comm_grid(n, 512, 128), 512, 0, s>>>(*ctx, offset, e0, e1,
+                                                                                         static_cast<T*>(out), op, seq)));
   return (int)cudaGetLastError();
 }
 

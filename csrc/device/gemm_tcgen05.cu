@@ -409,8 +409,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
-static int g_dbg_lbo = -1, g_dbg_sbo = -1, g_dbg_kstep = -1;
-
 static int pick_tile_n(int M, int N, int sms) {
   // Candidates are multiples of 32 up to 256; prefer the one with the fewest
   // waves of CTAs, then the least padding, then the widest tile.
@@ -432,12 +430,6 @@ static int pick_tile_n(int M, int N, int sms) {
 }
 
 }  // namespace b200
-
-extern "C" void b200_gemm_debug_override(int lbo, int sbo, int kstep) {
-  b200::g_dbg_lbo = lbo;
-  b200::g_dbg_sbo = sbo;
-  b200::g_dbg_kstep = kstep;
-}
 
 extern "C" int b200_gemm(const B200GemmParams* p, void* stream) {
   using namespace b200;
@@ -478,9 +470,9 @@ extern "C" int b200_gemm(const B200GemmParams* p, void* stream) {
   g.idesc = make_idesc(g.kind == 2 ? 2 : 1, fmt, fmt, g.a_mn, g.b_mn, GEMM_BM, g.tile_n);
   // MN-major: 8-row K groups are 1024 B apart, 128-byte MN blocks are one
   // k-block (bk rows x 128 B) apart, one MMA consumes 32 B of K = (32/es) rows.
-  g.mn_sbo = g_dbg_sbo >= 0 ? g_dbg_sbo : 1024;
-  g.mn_lbo = g_dbg_lbo >= 0 ? g_dbg_lbo : bk * 128;
-  g.mn_kstep = g_dbg_kstep >= 0 ? g_dbg_kstep : (32 / es) * 128;
+  g.mn_sbo = 1024;
+  g.mn_lbo = bk * 128;
+  g.mn_kstep = (32 / es) * 128;
   g.D = p->D; g.ldd = p->ldd; g.stride_d = p->stride_d; g.d_dtype = p->d_dtype;
   g.bias = p->bias; g.bias_dtype = p->bias_dtype; g.bias_per_row = p->bias_per_row;
   g.residual = p->residual; g.ldr = p->ldr; g.stride_r = p->stride_r; g.res_dtype = p->res_dtype;

@@ -102,8 +102,6 @@ typedef struct B200GemmParams {
   const float* col_scale;                // optional fp32 multiplier per output column (applied after alpha)
 } B200GemmParams;
 B200_API int b200_gemm(const B200GemmParams* p, void* stream);
-// Test hook: override the MN-major descriptor fields (bytes); negative = default.
-B200_API void b200_gemm_debug_override(int lbo, int sbo, int kstep);
 
 // ---- tcgen05 implicit-GEMM convolution --------------------------------------------------
 // Activations are NHWC 16-bit tensors.  The kernel walks a list of filter taps; for
@@ -209,6 +207,14 @@ B200_API int b200_bn_apply(const void* x, int x_dtype, void* y, int y_dtype, lon
 B200_API int b200_bn_apply_mask(const void* x, int x_dtype, void* y, int y_dtype, long long rows, int C, const void* mean,
                                 int mean_dtype, const float* invstd, const void* gamma, const void* beta, int param_dtype,
                                 const void* residual, int res_dtype, int act, void* relu_mask, void* stream);
+// Training-mode forward in one launch: mean / invstd are computed from the channel sums inside the kernel
+// (CTA 0 stores them and updates the running statistics), then y = act((x - mean) * invstd * gamma + beta +
+// residual) and, if relu_mask is given, the bit mask of the positive outputs.  x, y and residual share one dtype.
+// Returns cudaErrorNotSupported (801) when the shape does not qualify for the vector kernel.
+B200_API int b200_bn_apply_fused(const void* x, int dtype, void* y, long long rows, int C, const double* sums, float eps,
+                                 float momentum, float* save_mean, float* save_invstd, void* running_mean, void* running_var,
+                                 int running_dtype, const void* gamma, const void* beta, int param_dtype, const void* residual,
+                                 int act, void* relu_mask, long long* batch_counter /* optional, += 1 */, void* stream);
 // Backward reductions (fp64, zero `sums` first): sums[c] = sum dy, sums[C+c] = sum dy * xhat.
 // If `relu_out` is given dy is first masked by relu_out > 0 (fused ReLU backward).
 B200_API int b200_bn_backward_reduce(const void* dy, int dy_dtype, const void* x, int x_dtype, const void* mean,
@@ -222,6 +228,14 @@ B200_API int b200_bn_backward_apply(const void* dy, int dy_dtype, const void* x,
                                     const void* relu_out, int relu_dtype, const double* sums, long long rows, int C,
                                     int training, void* dx, int dx_dtype, float* dgamma, float* dbeta, void* dres,
                                     void* stream);
+
+// Same; with `clear_counter` (a zeroed device word, left zeroed) the kernel also clears `sums` after every CTA
+// has read them, so a persistent scratch buffer is ready for the next call without a memset launch.
+B200_API int b200_bn_backward_apply2(const void* dy, int dy_dtype, const void* x, int x_dtype, const void* mean,
+                                     int mean_dtype, const float* invstd, const void* gamma, int param_dtype,
+                                     const void* relu_out, int relu_dtype, double* sums, long long rows, int C,
+                                     int training, void* dx, int dx_dtype, float* dgamma, float* dbeta, void* dres,
+                                     unsigned* clear_counter, void* stream);
 
 // ---- layer norm over the last dimension ---------------------------------------------------
 B200_API int b200_layernorm_fwd(const void* x, int dtype, long long rows, int cols, const void* gamma, const void* beta,
@@ -343,6 +357,7 @@ B200_API int b200_dump_device(const void* x, int dtype, long long count, void* s
 #define B200_COMM_MAX_RANKS 16
 #define B200_COMM_TIMEOUT 1
 #define B200_COMM_FLAG_BYTES 4096
+#define B200_COMM_COUNTER_SLOT 64   // 64-bit slot of the flag block that counts CTAs arriving at the end barrier
 typedef struct B200CommCtx {
   int rank, world;
   void* arena[B200_COMM_MAX_RANKS];                 // peer staging bases (arena[rank] is local)
@@ -371,11 +386,19 @@ typedef struct B200FusedOptArgs {
   float* state2;             // exp_avg_sq shard
   size_t lowp_offset;        // optional 16-bit parameter copy region in the arena (0 = none)
   int lowp_dtype;
+  float* cast_src;           // optional: this rank's local fp32 gradients; the kernel converts them into the
+                             // grad_dtype exchange region at grad_offset before the ranks exchange anything
+  int zero_grads;            // clear the gradients for the next backward pass (cast_src if given, else the
+                             // exchange region once every peer has finished reading it)
 } B200FusedOptArgs;
 B200_API long long b200_comm_shard_elems(long long n, int world, int dtype);
 B200_API int b200_comm_allreduce_opt(const B200CommCtx* ctx, size_t grad_offset, size_t param_offset, long long n,
                                      int grad_dtype, float scale, const B200FusedOptArgs* opt, unsigned long long seq,
                                      void* stream);
+// out[i - e0] = op over ranks of the element i of the message at arena + offset, for i in [e0, e1)
+// (`out` is local memory).  Every rank of the group must call it, ranks with e0 >= e1 only synchronise.
+B200_API int b200_comm_reduce_range(const B200CommCtx* ctx, size_t offset, long long e0, long long e1, void* out,
+                                    int dtype, int op, unsigned long long seq, void* stream);
 // Building blocks for broadcast / all-gather / reduce / send / recv.
 B200_API int b200_comm_signal(const B200CommCtx* ctx, int which /*0 ready, 1 done, 2 p2p ready, 3 p2p done*/, int peer /*-1 = all*/,
                               unsigned long long seq, void* stream);

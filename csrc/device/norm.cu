@@ -76,15 +76,19 @@ __device__ void column_reduce(long long rows, int C, double* sums, F f, P prep, 
   const long long rows_per_cta = (rows + gridDim.x - 1) / gridDim.x;
   const long long r0 = (long long)blockIdx.x * rows_per_cta;
   const long long r1 = r0 + rows_per_cta < rows ? r0 + rows_per_cta : rows;
-  for (int cv = tx; cv < cvecs; cv += tx_n) {
+  // every thread runs the same number of trips (the loop body contains barriers); `on` guards the work
+  for (int cv0 = 0; cv0 < cvecs; cv0 += tx_n) {
+    const int cv = cv0 + tx;
+    const bool on = ty < ty_n && cv < cvecs;
     float acc[NQ][V];
 #pragma unroll
     for (int q = 0; q < NQ; ++q)
 #pragma unroll
       for (int i = 0; i < V; ++i) acc[q][i] = 0.f;
     float ctx[V];
-    prep(cv * V, ctx);  // per-column constants, loaded once instead of once per row
-    if (ty < ty_n) {
+    if (on) {
+      prep(cv * V, ctx);  // per-column constants, loaded once instead of once per row
+#pragma unroll 4
       for (long long r = r0 + ty; r < r1; r += ty_n) f(r, cv * V, acc, ctx);
     }
     // fold the ty_n partials
@@ -96,7 +100,7 @@ __device__ void column_reduce(long long rows, int C, double* sums, F f, P prep, 
         for (int i = 0; i < V; ++i) mine[q * V + i] = acc[q][i];
     }
     __syncthreads();
-    if (ty == 0) {
+    if (ty == 0 && cv < cvecs) {
 #pragma unroll
       for (int q = 0; q < NQ; ++q)
 #pragma unroll
@@ -248,52 +252,229 @@ __global__ void bn_param_grads_kernel(const double* sums, int C, float* dgamma, 
 }
 
 
-// ---- fast paths: per-channel coefficients precomputed into shared memory ------------
+// ---- fast paths ---------------------------------------------------------------------------
+// Streaming kernels over a [rows][C] activation with 16-byte vectors.  What keeps them at the memory
+// system's speed rather than at a fraction of it:
+//  * U vectors per thread are loaded before any of them is used, so every thread has U (x number of
+//    input tensors) 16-byte loads in flight;
+//  * the grid stride is a multiple of the number of channel vectors whenever that number divides the CTA
+//    size, so a thread meets the same channels in every iteration and keeps their coefficients in
+//    registers (no index division, no shared-memory reads in the loop);
+//  * small per-channel kernels are folded in: the forward kernel turns the channel sums into mean / inverse
+//    standard deviation itself (CTA 0 stores them and updates the running statistics), the backward kernel
+//    writes the parameter gradients and clears the sums for the next call.
+constexpr int BN_U = 4;
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+template <typename T>
+__device__ __forceinline__ void unpack_vec(const uint4& raw, float* f) {
+  constexpr int V = VecOf<T>::N;
+  const T* t = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < V; ++i) f[i] = Cv<T>::to(t[i]);
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack_vec(const float* f) {
+  constexpr int V = VecOf<T>::N;
+  uint4 raw;
+  T* t = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < V; ++i) t[i] = Cv<T>::from(f[i]);
+  return raw;
+}
+
+// Forward statistics of channel c from its sums (fp64, as accumulated by the statistics pass or by the
+// producing convolution's epilogue).
+__device__ __forceinline__ void bn_moments(const double* sums, int C, int c, long long rows, float eps, float* mean,
+                                           float* invstd, double* var_out) {
+  const double m = sums[c] / (double)rows;
+  double var = sums[C + c] / (double)rows - m * m;
+  if (var < 0) var = 0;
+  *mean = (float)m;
+  *invstd = (float)(1.0 / sqrt(var + (double)eps));
+  if (var_out) *var_out = var;
+}
+
+struct BnFinalize {          // optional: statistics come from `sums` instead of mean / invstd tensors
+  const double* sums;        // [2 * C] sum and sum of squares; nullptr = use the mean / invstd arguments
+  long long rows;
+  float eps, momentum;
+  float* save_mean;          // written by CTA 0
+  float* save_invstd;
+  void* rmean;               // running statistics, updated by CTA 0 (may be null)
+  void* rvar;
+  int rdt;
+  long long* batch_counter;  // optional: num_batches_tracked, incremented by CTA 0
+};
+
 // y = act(x * S[c] + T[c] + residual) with S = invstd * gamma, T = beta - mean * S
 template <typename T>
 __global__ void __launch_bounds__(256)
 bn_apply_fast_kernel(const T* __restrict__ x, T* __restrict__ y, unsigned nvec, int C, const void* mean, int mdt,
                      const float* invstd, const void* gamma, const void* beta, int pdt, const T* __restrict__ res,
-                     int act, uint8_t* __restrict__ relu_mask) {
+                     int act, uint8_t* __restrict__ relu_mask, const BnFinalize fz) {
   constexpr int V = VecOf<T>::N;
   extern __shared__ float coef[];
   float* S = coef;
   float* Tc = coef + C;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    const float sc = invstd[c] * (gamma ? ldf(gamma, c, pdt) : 1.f);
+    float mu, is;
+    if (fz.sums) {
+      double var;
+      bn_moments(fz.sums, C, c, fz.rows, fz.eps, &mu, &is, &var);
+      if (blockIdx.x == 0) {
+        fz.save_mean[c] = mu;
+        fz.save_invstd[c] = is;
+        if (fz.rmean) {
+          const double unbiased = fz.rows > 1 ? var * (double)fz.rows / (double)(fz.rows - 1) : var;
+          const double m = fz.sums[c] / (double)fz.rows;
+          stf(fz.rmean, c, fz.rdt, (float)((1.0 - fz.momentum) * ldf(fz.rmean, c, fz.rdt) + fz.momentum * m));
+          stf(fz.rvar, c, fz.rdt, (float)((1.0 - fz.momentum) * ldf(fz.rvar, c, fz.rdt) + fz.momentum * unbiased));
+        }
+      }
+    } else {
+      mu = ldf(mean, c, mdt);
+      is = invstd[c];
+    }
+    const float sc = is * (gamma ? ldf(gamma, c, pdt) : 1.f);
     S[c] = sc;
-    Tc[c] = (beta ? ldf(beta, c, pdt) : 0.f) - ldf(mean, c, mdt) * sc;
+    Tc[c] = (beta ? ldf(beta, c, pdt) : 0.f) - mu * sc;
   }
+  if (fz.batch_counter && blockIdx.x == 0 && threadIdx.x == 0) *fz.batch_counter += 1;
   __syncthreads();
   const unsigned cvecs = C / V;
-  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += gridDim.x * blockDim.x) {
-    const int c0 = (int)(i % cvecs) * V;
-    float v[V], r[V];
-    load_vec<T>(x + (size_t)i * V, v);
-    if (res) load_vec<T>(res + (size_t)i * V, r);
-    unsigned bits = 0;
+  const bool fixed = (256u % cvecs) == 0;            // this thread's channels never change
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t first = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  float s_r[V], t_r[V];
+  if (fixed) {
+    const int c0 = (int)(threadIdx.x % cvecs) * V;
 #pragma unroll
-    for (int k = 0; k < V; ++k) {
-      float t = fmaf(v[k], S[c0 + k], Tc[c0 + k]);
-      if (res) t += r[k];
-      if (act == 1) {
-        bits |= (t > 0.f ? 1u : 0u) << k;
-        t = t > 0.f ? t : 0.f;
+    for (int k = 0; k < V; ++k) { s_r[k] = S[c0 + k]; t_r[k] = Tc[c0 + k]; }
+  }
+  for (size_t i0 = first; i0 < nvec; i0 += stride * BN_U) {
+    uint4 xr[BN_U], rr[BN_U];
+#pragma unroll
+    for (int u = 0; u < BN_U; ++u) {
+      const size_t i = i0 + u * stride;
+      if (i < nvec) {
+        xr[u] = ld_stream(x + i * V);
+        if (res) rr[u] = ld_stream(res + i * V);
       }
-      v[k] = t;
     }
-    store_vec<T>(y + (size_t)i * V, v);
-    if (relu_mask) relu_mask[i] = (uint8_t)bits;  // one bit per element (V == 8): all the backward needs of the output
+#pragma unroll
+    for (int u = 0; u < BN_U; ++u) {
+      const size_t i = i0 + u * stride;
+      if (i >= nvec) break;
+      float v[V], r[V];
+      unpack_vec<T>(xr[u], v);
+      if (res) unpack_vec<T>(rr[u], r);
+      if (!fixed) {
+        const int c0 = (int)(i % cvecs) * V;
+#pragma unroll
+        for (int k = 0; k < V; ++k) { s_r[k] = S[c0 + k]; t_r[k] = Tc[c0 + k]; }
+      }
+      unsigned bits = 0;
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        float t = fmaf(v[k], s_r[k], t_r[k]);
+        if (res) t += r[k];
+        if (act == 1) {
+          bits |= (t > 0.f ? 1u : 0u) << k;
+          t = t > 0.f ? t : 0.f;
+        }
+        v[k] = t;
+      }
+      *reinterpret_cast<uint4*>(y + i * V) = pack_vec<T>(v);
+      if (relu_mask) relu_mask[i] = (uint8_t)bits;  // one bit per element (V == 8): all the backward needs of the output
+    }
   }
 }
 
-// dx = A[c] * dy + B[c] * x + D[c]   (training), dx = A[c] * dy (eval)
+// sums[c] += sum(dy), sums[C + c] += invstd[c] * sum(dy * (x - mean[c])) under the ReLU mask; 16-byte vectors,
+// BN_U rows per thread in flight.  Thread (tx, ty) owns channel vector tx of rows ty, ty + ty_n, ...
+template <typename T>
+__global__ void __launch_bounds__(RED_THREADS)
+bn_bwd_reduce_fast_kernel(const T* __restrict__ dy, const T* __restrict__ x, const void* mean, int mdt,
+                          const float* invstd, const uint8_t* __restrict__ relu_mask, long long rows, int C, double* sums) {
+  constexpr int V = VecOf<T>::N;
+  const int cvecs = C / V;  // divides RED_THREADS or is a multiple of it (checked by the launcher)
+  const int tx_n = cvecs < RED_THREADS ? cvecs : RED_THREADS;
+  const int ty_n = RED_THREADS / tx_n;
+  const int tx = threadIdx.x % tx_n, ty = threadIdx.x / tx_n;
+  extern __shared__ float sh[];  // [ty_n][tx_n * V * 2]
+  const long long rows_per_cta = (rows + gridDim.x - 1) / gridDim.x;
+  const long long r0 = (long long)blockIdx.x * rows_per_cta;
+  const long long r1 = r0 + rows_per_cta < rows ? r0 + rows_per_cta : rows;
+  for (int cv = tx; cv < cvecs; cv += tx_n) {  // cvecs % tx_n == 0: the same trip count for every thread
+    float a0[V], a1[V], mu[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) { a0[k] = 0.f; a1[k] = 0.f; mu[k] = ldf(mean, cv * V + k, mdt); }
+    for (long long rb = r0 + ty; rb < r1; rb += (long long)ty_n * BN_U) {
+      uint4 gr[BN_U], xr[BN_U];
+      unsigned bits[BN_U];
+#pragma unroll
+      for (int u = 0; u < BN_U; ++u) {
+        const long long r = rb + (long long)u * ty_n;
+        if (r < r1) {
+          const size_t i = (size_t)r * cvecs + cv;
+          gr[u] = ld_stream(dy + i * V);
+          xr[u] = ld_stream(x + i * V);
+          bits[u] = relu_mask ? relu_mask[i] : 0xffu;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < BN_U; ++u) {
+        const long long r = rb + (long long)u * ty_n;
+        if (r >= r1) break;
+        float g[V], v[V];
+        unpack_vec<T>(gr[u], g);
+        unpack_vec<T>(xr[u], v);
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          const float gi = ((bits[u] >> k) & 1u) ? g[k] : 0.f;
+          a0[k] += gi;
+          a1[k] = fmaf(gi, v[k] - mu[k], a1[k]);
+        }
+      }
+    }
+    float* mine = sh + ((size_t)ty * tx_n + tx) * V * 2;
+#pragma unroll
+    for (int k = 0; k < V; ++k) { mine[k] = a0[k]; mine[V + k] = a1[k]; }
+    __syncthreads();
+    if (ty == 0) {
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        double s0 = 0.0, s1 = 0.0;
+        for (int yy = 0; yy < ty_n; ++yy) {
+          const float* q = sh + ((size_t)yy * tx_n + tx) * V * 2;
+          s0 += q[k];
+          s1 += q[V + k];
+        }
+        const int c = cv * V + k;
+        atomicAdd(&sums[c], s0);
+        atomicAdd(&sums[C + c], s1 * (double)invstd[c]);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// dx = A[c] * dy + B[c] * x + D[c]   (training), dx = A[c] * dy (eval); dy is masked by the ReLU first.
+// CTA 0 also writes the parameter gradients; with `clear_sums` the CTA that finishes last zeroes the sums
+// (they are a scratch buffer that the next backward pass expects to find cleared).
 template <typename T>
 __global__ void __launch_bounds__(256)
 bn_bwd_apply_fast_kernel(const T* __restrict__ dy, const T* __restrict__ x, const void* mean, int mdt,
                          const float* invstd, const void* gamma, int pdt, const T* __restrict__ relu_out,
-                         const double* sums, long long rows, int C, int training, T* __restrict__ dx, unsigned nvec,
-                         T* __restrict__ dres, const uint8_t* __restrict__ relu_mask) {
+                         double* sums, long long rows, int C, int training, T* __restrict__ dx, unsigned nvec,
+                         T* __restrict__ dres, const uint8_t* __restrict__ relu_mask, float* dgamma, float* dbeta,
+                         unsigned* clear_counter) {
   constexpr int V = VecOf<T>::N;
   extern __shared__ float coef[];
   float* A = coef;
@@ -303,6 +484,10 @@ bn_bwd_apply_fast_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
     const float is = invstd[c];
     const float a = (gamma ? ldf(gamma, c, pdt) : 1.f) * is;
     A[c] = a;
+    if (blockIdx.x == 0) {
+      if (dbeta) dbeta[c] = (float)sums[c];
+      if (dgamma) dgamma[c] = (float)sums[C + c];
+    }
     if (training) {
       const float sdy = (float)(sums[c] / (double)rows), sdx = (float)(sums[C + c] / (double)rows);
       const float b = -a * is * sdx;
@@ -314,28 +499,69 @@ bn_bwd_apply_fast_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
     }
   }
   __syncthreads();
+  if (clear_counter) {
+    // every CTA has read the sums once it is past the barrier above; the last one to get here clears them
+    __shared__ int last_sh;
+    if (threadIdx.x == 0) {
+      __threadfence();
+      last_sh = atomicAdd(clear_counter, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (last_sh) {
+      for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) sums[c] = 0.0;
+      if (threadIdx.x == 0) *clear_counter = 0u;
+    }
+  }
   const unsigned cvecs = C / V;
-  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += gridDim.x * blockDim.x) {
-    const int c0 = (int)(i % cvecs) * V;
-    float g[V], v[V], o[V];
-    load_vec<T>(dy + (size_t)i * V, g);
-    load_vec<T>(x + (size_t)i * V, v);
-    if (relu_out) {
-      load_vec<T>(relu_out + (size_t)i * V, o);
+  const bool fixed = (256u % cvecs) == 0;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t first = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  float a_r[V], b_r[V], d_r[V];
+  if (fixed) {
+    const int c0 = (int)(threadIdx.x % cvecs) * V;
+#pragma unroll
+    for (int k = 0; k < V; ++k) { a_r[k] = A[c0 + k]; b_r[k] = B[c0 + k]; d_r[k] = D[c0 + k]; }
+  }
+  for (size_t i0 = first; i0 < nvec; i0 += stride * BN_U) {
+    uint4 gr[BN_U], xr[BN_U], orr[BN_U];
+    unsigned bits[BN_U];
+#pragma unroll
+    for (int u = 0; u < BN_U; ++u) {
+      const size_t i = i0 + u * stride;
+      if (i < nvec) {
+        gr[u] = ld_stream(dy + i * V);
+        xr[u] = ld_stream(x + i * V);
+        if (relu_out) orr[u] = ld_stream(relu_out + i * V);
+        bits[u] = relu_mask ? relu_mask[i] : 0xffu;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < BN_U; ++u) {
+      const size_t i = i0 + u * stride;
+      if (i >= nvec) break;
+      float g[V], v[V];
+      unpack_vec<T>(gr[u], g);
+      unpack_vec<T>(xr[u], v);
+      if (relu_out) {
+        float o[V];
+        unpack_vec<T>(orr[u], o);
+#pragma unroll
+        for (int k = 0; k < V; ++k)
+          if (!(o[k] > 0.f)) g[k] = 0.f;
+      }
 #pragma unroll
       for (int k = 0; k < V; ++k)
-        if (!(o[k] > 0.f)) g[k] = 0.f;
-    }
-    if (relu_mask) {
-      const unsigned bits = relu_mask[i];
+        if (!((bits[u] >> k) & 1u)) g[k] = 0.f;
+      if (dres) *reinterpret_cast<uint4*>(dres + i * V) = pack_vec<T>(g);  // gradient of the fused residual input: the masked dy
+      if (!fixed) {
+        const int c0 = (int)(i % cvecs) * V;
 #pragma unroll
-      for (int k = 0; k < V; ++k)
-        if (!((bits >> k) & 1u)) g[k] = 0.f;
-    }
-    if (dres) store_vec<T>(dres + (size_t)i * V, g);  // gradient of the fused residual input: the masked dy
+        for (int k = 0; k < V; ++k) { a_r[k] = A[c0 + k]; b_r[k] = B[c0 + k]; d_r[k] = D[c0 + k]; }
+      }
 #pragma unroll
-    for (int k = 0; k < V; ++k) g[k] = fmaf(A[c0 + k], g[k], fmaf(B[c0 + k], v[k], D[c0 + k]));
-    store_vec<T>(dx + (size_t)i * V, g);
+      for (int k = 0; k < V; ++k) g[k] = fmaf(a_r[k], g[k], fmaf(b_r[k], v[k], d_r[k]));
+      *reinterpret_cast<uint4*>(dx + i * V) = pack_vec<T>(g);
+    }
   }
 }
 
@@ -488,11 +714,10 @@ extern "C" int b200_bn_apply(const void* x, int xdt, void* y, int ydt, long long
                              int rdt, int act, void* stream) {
   return b200_bn_apply_mask(x, xdt, y, ydt, rows, C, mean, mdt, invstd, gamma, beta, pdt, res, rdt, act, nullptr, stream);
 }
-extern "C" int b200_bn_apply_mask(const void* x, int xdt, void* y, int ydt, long long rows, int C, const void* mean, int mdt,
-                                  const float* invstd, const void* gamma, const void* beta, int pdt, const void* res,
-                                  int rdt, int act, void* relu_mask, void* stream) {
-  if (rows <= 0 || C <= 0) return 0;
-  if (relu_mask && (xdt == B200_F32 || act != 1)) return (int)cudaErrorInvalidValue;
+static int bn_apply_launch(const void* x, int xdt, void* y, int ydt, long long rows, int C, const void* mean, int mdt,
+                           const float* invstd, const void* gamma, const void* beta, int pdt, const void* res, int rdt,
+                           int act, void* relu_mask, const BnFinalize& fz, void* stream, bool* done) {
+  *done = false;
   cudaStream_t s = (cudaStream_t)stream;
   const long long n = rows * C;
   // fast path: same 16-bit / fp32 type in and out, coefficients fit in shared memory
@@ -503,9 +728,42 @@ extern "C" int b200_bn_apply_mask(const void* x, int xdt, void* y, int ydt, long
       const size_t sm = sizeof(float) * 2 * C;
       DISPATCH_FLOAT(xdt, T, (bn_apply_fast_kernel<T><<<ew_grid_u(nvec), 256, sm, s>>>(
                                  static_cast<const T*>(x), static_cast<T*>(y), nvec, C, mean, mdt, invstd, gamma, beta,
-                                 pdt, static_cast<const T*>(res), act, V == 8 ? static_cast<uint8_t*>(relu_mask) : nullptr)));
-      return (int)cudaGetLastError();
+                                 pdt, static_cast<const T*>(res), act, V == 8 ? static_cast<uint8_t*>(relu_mask) : nullptr, fz)));
+      *done = true;
     }
+  }
+  return (int)cudaGetLastError();
+}
+
+// Training-mode forward in one launch: statistics from the channel sums, running-statistics update,
+// normalisation, optional residual add, optional ReLU and its bit mask.  Returns cudaErrorNotSupported
+// when the shape does not qualify for the vector kernel (the caller then runs finalize + apply).
+extern "C" int b200_bn_apply_fused(const void* x, int dt, void* y, long long rows, int C, const double* sums, float eps,
+                                   float momentum, float* save_mean, float* save_invstd, void* rmean, void* rvar, int rdt,
+                                   const void* gamma, const void* beta, int pdt, const void* res, int act, void* relu_mask,
+                                   long long* batch_counter, void* stream) {
+  if (rows <= 0 || C <= 0) return (int)cudaErrorNotSupported;
+  if (relu_mask && (dt == B200_F32 || act != 1)) return (int)cudaErrorInvalidValue;
+  BnFinalize fz{sums, rows, eps, momentum, save_mean, save_invstd, rmean, rvar, rdt, batch_counter};
+  bool done = false;
+  const int rc = bn_apply_launch(x, dt, y, dt, rows, C, nullptr, B200_F32, nullptr, gamma, beta, pdt, res, dt, act, relu_mask,
+                                 fz, stream, &done);
+  if (rc) return rc;
+  return done ? 0 : (int)cudaErrorNotSupported;
+}
+
+extern "C" int b200_bn_apply_mask(const void* x, int xdt, void* y, int ydt, long long rows, int C, const void* mean, int mdt,
+                                  const float* invstd, const void* gamma, const void* beta, int pdt, const void* res,
+                                  int rdt, int act, void* relu_mask, void* stream) {
+  if (rows <= 0 || C <= 0) return 0;
+  if (relu_mask && (xdt == B200_F32 || act != 1)) return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long n = rows * C;
+  {
+    bool done = false;
+    const int rc = bn_apply_launch(x, xdt, y, ydt, rows, C, mean, mdt, invstd, gamma, beta, pdt, res, rdt, act, relu_mask,
+                                   BnFinalize{}, stream, &done);
+    if (rc || done) return rc;
   }
   if (relu_mask) return (int)cudaErrorInvalidValue;  // the mask is produced by the fast path only
 #define BN_APPLY(TX, TY)                                                                                            \
@@ -538,18 +796,28 @@ extern "C" int b200_bn_backward_reduce(const void* dy, int dt, const void* x, in
   DISPATCH_FLOAT(dt, T, {
     constexpr int V = VecOf<T>::N;
     if (C % V) return (int)cudaErrorInvalidValue;
-    bn_bwd_reduce_kernel<T><<<red_grid(rows), RED_THREADS, red_smem(C, V, 2), s>>>(
-        static_cast<const T*>(dy), static_cast<const T*>(x), mean, mdt, invstd,
-        is_mask ? nullptr : static_cast<const T*>(relu_out), (is_mask && V == 8) ? static_cast<const uint8_t*>(relu_out) : nullptr,
-        rows, C, sums);
+    const int cvecs = C / V;
+    const bool fast = (!relu_out || (is_mask && V == 8)) && (RED_THREADS % cvecs == 0 || cvecs % RED_THREADS == 0);
+    if (fast) {
+      bn_bwd_reduce_fast_kernel<T><<<red_grid(rows), RED_THREADS, red_smem(C, V, 2), s>>>(
+          static_cast<const T*>(dy), static_cast<const T*>(x), mean, mdt, invstd,
+          is_mask ? static_cast<const uint8_t*>(relu_out) : nullptr, rows, C, sums);
+    } else {
+      bn_bwd_reduce_kernel<T><<<red_grid(rows), RED_THREADS, red_smem(C, V, 2), s>>>(
+          static_cast<const T*>(dy), static_cast<const T*>(x), mean, mdt, invstd,
+          is_mask ? nullptr : static_cast<const T*>(relu_out), (is_mask && V == 8) ? static_cast<const uint8_t*>(relu_out) : nullptr,
+          rows, C, sums);
+    }
   });
   return (int)cudaGetLastError();
 }
 
-extern "C" int b200_bn_backward_apply(const void* dy, int dt, const void* x, int xdt, const void* mean, int mdt,
-                                      const float* invstd, const void* gamma, int pdt, const void* relu_out, int rdt,
-                                      const double* sums, long long rows, int C, int training, void* dx, int dxdt,
-                                      float* dgamma, float* dbeta, void* dres, void* stream) {
+// `clear_counter` (optional, a zeroed device word that the kernel leaves zeroed): the sums are a scratch
+// buffer and are cleared by the kernel once every CTA has read them.
+extern "C" int b200_bn_backward_apply2(const void* dy, int dt, const void* x, int xdt, const void* mean, int mdt,
+                                       const float* invstd, const void* gamma, int pdt, const void* relu_out, int rdt,
+                                       double* sums, long long rows, int C, int training, void* dx, int dxdt,
+                                       float* dgamma, float* dbeta, void* dres, unsigned* clear_counter, void* stream) {
   if (rows <= 0 || C <= 0) return 0;
   const bool is_mask = relu_out && rdt == B200_U8;
   if (dt != xdt || (relu_out && !is_mask && rdt != dt) || (is_mask && dt == B200_F32)) return (int)cudaErrorInvalidValue;
@@ -565,9 +833,11 @@ extern "C" int b200_bn_backward_apply(const void* dy, int dt, const void* x, int
                                static_cast<const T*>(dy), static_cast<const T*>(x), mean, mdt, invstd, gamma, pdt,
                                is_mask ? nullptr : static_cast<const T*>(relu_out), sums, rows, C, training,
                                static_cast<T*>(dx), nvec, static_cast<T*>(dres),
-                               (is_mask && V == 8) ? static_cast<const uint8_t*>(relu_out) : nullptr)));
-    dx = nullptr;  // done
+                               (is_mask && V == 8) ? static_cast<const uint8_t*>(relu_out) : nullptr, dgamma, dbeta,
+                               clear_counter)));
+    return (int)cudaGetLastError();
   }
+  if (clear_counter) return (int)cudaErrorNotSupported;  // only the vector kernel clears the sums
   if (dx) {
 #define BN_BWD(T, TO)                                                                                                  \
   bn_bwd_apply_kernel<T, TO><<<ew_grid(n), 256, 0, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x), mean, mdt, \
@@ -581,6 +851,14 @@ extern "C" int b200_bn_backward_apply(const void* dy, int dt, const void* x, int
   }
   if (dgamma || dbeta) bn_param_grads_kernel<<<(C + 127) / 128, 128, 0, s>>>(sums, C, dgamma, dbeta);
   return (int)cudaGetLastError();
+}
+
+extern "C" int b200_bn_backward_apply(const void* dy, int dt, const void* x, int xdt, const void* mean, int mdt,
+                                      const float* invstd, const void* gamma, int pdt, const void* relu_out, int rdt,
+                                      const double* sums, long long rows, int C, int training, void* dx, int dxdt,
+                                      float* dgamma, float* dbeta, void* dres, void* stream) {
+  return b200_bn_backward_apply2(dy, dt, x, xdt, mean, mdt, invstd, gamma, pdt, relu_out, rdt, const_cast<double*>(sums), rows, C,
+                                 training, dx, dxdt, dgamma, dbeta, dres, nullptr, stream);
 }
 
 extern "C" int b200_layernorm_fwd(const void* x, int dt, long long rows, int cols, const void* gamma, const void* beta,

@@ -137,6 +137,7 @@ class SymmetricArena {
     return static_cast<size_t>(c - local());
   }
   int* status_host() const { return status_host_; }
+  void* counter_ptr() const { return local() + total_ - B200_COMM_FLAG_BYTES + B200_COMM_COUNTER_SLOT * 8; }
   void set_timeout_ns(unsigned long long ns) { ctx_.timeout_ns = ns; }
 
  private:
@@ -346,6 +347,7 @@ void ProcessGroupB200::ensure_arena(int device) {
   device_ = device;
   DeviceSwitch sw(device);
   arena_ = std::make_unique<SymmetricArena>(device, rank_, size_, store_, uid_, timeout_);
+  apply_wait_limit();
   comm_q_ = getQueueFromPool(device);
   send_q_ = getQueueFromPool(device);
   recv_q_ = getQueueFromPool(device);
@@ -397,7 +399,12 @@ std::vector<std::vector<uint8_t>> ProcessGroupB200::store_exchange(const std::ve
                                                                    int root) {
   const uint64_t s = ++host_seq_;
   auto key = [&](uint64_t seq, int r) { return uid_ + "/x/" + std::to_string(seq) + "/" + std::to_string(r); };
-  if (everyone_sends || rank_ == root) store_->set(key(s, rank_), mine);
+  auto ack = [&](uint64_t seq, int r) { return uid_ + "/xa/" + std::to_string(seq) + "/" + std::to_string(r); };
+  const bool i_send = everyone_sends || rank_ == root;
+  if (i_send) {
+    store_->set(key(s, rank_), mine);
+    posted_.push_back(s);
+  }
   std::vector<std::vector<uint8_t>> all(size_);
   for (int r = 0; r < size_; ++r) {
     if (!everyone_sends && r != root) continue;
@@ -407,9 +414,17 @@ std::vector<std::vector<uint8_t>> ProcessGroupB200::store_exchange(const std::ve
     }
     store_->wait({key(s, r)}, timeout_);  // throws on timeout: a missing peer is detected here
     all[r] = store_->get(key(s, r));
+    store_->add(ack(s, r), 1);            // tell the sender that this reader is done with the key
   }
-  // everybody has posted round s, hence finished reading round s-2
-  if (s > 2) store_->deleteKey(key(s - 2, rank_));
+  // A posted message is deleted once every other rank has acknowledged it.  (Counting rounds is not
+  // enough: the root of a broadcast waits for nobody, so it can be several rounds ahead of a reader.)
+  while (!posted_.empty()) {
+    const uint64_t old = posted_.front();
+    if (store_->add(ack(old, rank_), 0) < size_ - 1) break;
+    store_->deleteKey(key(old, rank_));
+    store_->deleteKey(ack(old, rank_));
+    posted_.pop_front();
+  }
   return all;
 }
 
@@ -572,6 +587,8 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupB200::reduce(std::vector<at::Tensor>&
     });
   }
   at::Tensor work_t = arithmetic_view(t);
+  // Every rank stages its message in its arena; only the root pulls and combines (peers move no result
+  // bytes at all, they just take part in the two barriers of the kernel).
   return run_on_comm(c10d::OpType::REDUCE, {t, work_t}, [&, work_t](void* stream) mutable {
     const B200CommCtx ctx = arena_->ctx();
     const size_t es = work_t.element_size();
@@ -580,14 +597,36 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupB200::reduce(std::vector<at::Tensor>&
     for (int64_t done = 0; done < work_t.numel(); done += max_elems) {
       const int64_t n = std::min<int64_t>(max_elems, work_t.numel() - done);
       COMM_CHECK(b200_comm_copy(arena_->local(), p + done * es, n * es, stream));
-      COMM_CHECK(b200_comm_allreduce(&ctx, 0, n, dtype_code(work_t.scalar_type()), op, 1.0f, ++seq_, 0, stream));
-      if (rank_ == root) COMM_CHECK(b200_comm_copy(p + done * es, arena_->local(), n * es, stream));
+      COMM_CHECK(b200_comm_reduce_range(&ctx, 0, 0, rank_ == root ? n : 0, p + done * es, dtype_code(work_t.scalar_type()), op,
+                                        ++seq_, stream));
     }
     if (rank_ == root && !work_t.is_same(t)) {
       QueueGuard g(comm_q_);
       t.copy_(work_t);
     }
   });
+}
+
+// Stages `in` in this rank's arena and pulls every peer's message straight into dsts[peer] (device pointers
+// of `bytes` each): no flat temporary, no second copy.
+void ProcessGroupB200::gather_into(const at::Tensor& in, const std::vector<char*>& dsts, void* stream) {
+  const B200CommCtx ctx = arena_->ctx();
+  const size_t cap = arena_->staging_bytes();
+  const size_t total = in.nbytes();
+  char* src = static_cast<char*>(in.data_ptr());
+  for (size_t done = 0; done < total; done += cap) {
+    const size_t n = std::min(cap, total - done);
+    const uint64_t s = ++seq_;
+    COMM_CHECK(b200_comm_copy(arena_->local(), src + done, n, stream));
+    COMM_CHECK(b200_comm_signal(&ctx, 0, -1, s, stream));
+    COMM_CHECK(b200_comm_wait(&ctx, 0, -1, s, stream));
+    for (int i = 0; i < size_; ++i) {
+      const int p = (rank_ + i) % size_;
+      COMM_CHECK(b200_comm_copy(dsts[p] + done, ctx.arena[p], n, stream));
+    }
+    COMM_CHECK(b200_comm_signal(&ctx, 1, -1, s, stream));
+    COMM_CHECK(b200_comm_wait(&ctx, 1, -1, s, stream));
+  }
 }
 
 c10::intrusive_ptr<c10d::Work> ProcessGroupB200::_allgather_base(at::Tensor& output, at::Tensor& input,
@@ -606,24 +645,9 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupB200::_allgather_base(at::Tensor& out
   TORCH_CHECK(output.is_contiguous(), "bwccl: all_gather output must be contiguous");
   at::Tensor in = input.contiguous();
   return run_on_comm(c10d::OpType::_ALLGATHER_BASE, {output, in}, [&, in](void* stream) mutable {
-    const B200CommCtx ctx = arena_->ctx();
-    const size_t cap = arena_->staging_bytes();
-    const size_t total = in.nbytes();
-    char* src = static_cast<char*>(in.data_ptr());
-    char* dst = static_cast<char*>(output.data_ptr());
-    for (size_t done = 0; done < total; done += cap) {
-      const size_t n = std::min(cap, total - done);
-      const uint64_t s = ++seq_;
-      COMM_CHECK(b200_comm_copy(arena_->local(), src + done, n, stream));
-      COMM_CHECK(b200_comm_signal(&ctx, 0, -1, s, stream));
-      COMM_CHECK(b200_comm_wait(&ctx, 0, -1, s, stream));
-      for (int i = 0; i < size_; ++i) {
-        const int p = (rank_ + i) % size_;
-        COMM_CHECK(b200_comm_copy(dst + p * total + done, ctx.arena[p], n, stream));
-      }
-      COMM_CHECK(b200_comm_signal(&ctx, 1, -1, s, stream));
-      COMM_CHECK(b200_comm_wait(&ctx, 1, -1, s, stream));
-    }
+    std::vector<char*> dsts(size_);
+    for (int r = 0; r < size_; ++r) dsts[r] = static_cast<char*>(output.data_ptr()) + (size_t)r * in.nbytes();
+    gather_into(in, dsts, stream);
   });
 }
 
@@ -637,43 +661,75 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupB200::allgather(std::vector<std::vect
   for (auto& o : outputs[0])
     TORCH_CHECK(o.sizes() == in.sizes() && o.scalar_type() == in.scalar_type(), "bwccl: all_gather output shape / dtype mismatch");
   ensure_arena(in.device().index());
-  // gather straight into one flat tensor, then hand out the pieces
-  at::Tensor flat = at::empty({size_, in.numel()}, in.options());
-  auto work = _allgather_base(flat, in, opts);
   if (hostsim()) {
-    for (int r = 0; r < size_; ++r) outputs[0][r].copy_(flat[r].view(in.sizes()));
-    return work;
+    return hostsim_collective(c10d::OpType::ALLGATHER, outputs[0], [&] {
+      auto all = store_exchange(to_bytes(in), true, 0);
+      for (int r = 0; r < size_; ++r) outputs[0][r].copy_(from_bytes(all[r], in));
+    });
   }
-  {
+  // Contiguous outputs receive the peers' bytes directly; a strided output goes through a dense temporary.
+  at::Tensor src = in.contiguous();
+  std::vector<at::Tensor> dense(size_);
+  std::vector<at::Tensor> used{src};
+  for (int r = 0; r < size_; ++r) {
+    at::Tensor& o = outputs[0][r];
+    dense[r] = o.is_contiguous() ? o : at::empty_like(o, at::MemoryFormat::Contiguous);
+    used.push_back(o);
+    if (!dense[r].is_same(o)) used.push_back(dense[r]);
+  }
+  return run_on_comm(c10d::OpType::ALLGATHER, used, [&, src, dense](void* stream) mutable {
+    std::vector<char*> dsts(size_);
+    for (int r = 0; r < size_; ++r) dsts[r] = static_cast<char*>(dense[r].data_ptr());
+    gather_into(src, dsts, stream);
     QueueGuard g(comm_q_);
-    for (int r = 0; r < size_; ++r) outputs[0][r].copy_(flat[r].view(in.sizes()));
-  }
-  auto w = c10::static_intrusive_pointer_cast<WorkB200>(work);
-  w->keep_alive_.push_back(flat);
-  w->notifier_.place(comm_q_);
-  return work;
+    for (int r = 0; r < size_; ++r)
+      if (!dense[r].is_same(outputs[0][r])) outputs[0][r].copy_(dense[r]);
+  });
 }
 
 c10::intrusive_ptr<c10d::Work> ProcessGroupB200::_reduce_scatter_base(at::Tensor& output, at::Tensor& input,
                                                                       const c10d::ReduceScatterOptions& opts) {
-  TORCH_CHECK(input.numel() == output.numel() * size_, "bwccl: reduce_scatter input must hold world_size outputs");
-  at::Tensor tmp = input.clone();
-  std::vector<at::Tensor> v{tmp};
-  c10d::AllreduceOptions ao;
-  ao.reduceOp = opts.reduceOp;
-  auto work = allreduce(v, ao);
+  TORCH_CHECK(is_b200(input) && is_b200(output), "bwccl: tensors must live on the blackwell device");
+  TORCH_CHECK(input.numel() == output.numel() * size_ && input.scalar_type() == output.scalar_type(),
+              "bwccl: reduce_scatter input must hold world_size outputs");
+  ensure_arena(input.device().index());
+  const int op = op_code(opts.reduceOp);
   if (hostsim()) {
-    output.copy_(tmp.view({size_, -1})[rank_].view(output.sizes()));
-    return work;
+    return hostsim_collective(c10d::OpType::_REDUCE_SCATTER_BASE, {output}, [&] {
+      auto all = store_exchange(to_bytes(input), true, 0);
+      std::vector<at::Tensor> parts;
+      for (auto& b : all) parts.push_back(from_bytes(b, input));
+      at::Tensor red = cpu_reduce(parts, op, size_);
+      output.copy_(red.view({size_, -1})[rank_].view(output.sizes()));
+    });
   }
-  {
-    QueueGuard g(comm_q_);
-    output.copy_(tmp.view({size_, -1})[rank_].view(output.sizes()));
-  }
-  auto w = c10::static_intrusive_pointer_cast<WorkB200>(work);
-  w->keep_alive_.push_back(tmp);
-  w->notifier_.place(comm_q_);
-  return work;
+  // Each rank stages its whole input and reduces only its own piece, pulling that piece from every peer:
+  // (world - 1) / world of one message crosses NVLink per rank instead of a full all-reduce.
+  at::Tensor in = arithmetic_view(input);
+  at::Tensor out = (output.is_contiguous() && dtype_code(output.scalar_type()) >= 0)
+                       ? output : at::empty(output.sizes(), in.options());
+  const int64_t piece = output.numel();
+  return run_on_comm(c10d::OpType::_REDUCE_SCATTER_BASE, {output, in, out}, [&, in, out, piece](void* stream) mutable {
+    const B200CommCtx ctx = arena_->ctx();
+    const size_t es = in.element_size();
+    // chunk the pieces so that world * chunk elements fit the staging window
+    int64_t max_chunk = std::max<int64_t>(1, static_cast<int64_t>(arena_->staging_bytes() / es) / size_);
+    if (max_chunk > 16) max_chunk = max_chunk / 16 * 16;  // slots stay 16-byte aligned
+    char* src = static_cast<char*>(in.data_ptr());
+    char* dst = static_cast<char*>(out.data_ptr());
+    for (int64_t done = 0; done < piece || done == 0; done += max_chunk) {
+      const int64_t n = std::min<int64_t>(max_chunk, piece - done);
+      for (int r = 0; r < size_; ++r)  // staging layout: [rank 0's chunk | rank 1's chunk | ...], 16-byte aligned slots
+        COMM_CHECK(b200_comm_copy(arena_->local() + (size_t)r * max_chunk * es, src + ((size_t)r * piece + done) * es, n * es, stream));
+      COMM_CHECK(b200_comm_reduce_range(&ctx, (size_t)rank_ * max_chunk * es, 0, n, dst + done * es, dtype_code(in.scalar_type()), op,
+                                        ++seq_, stream));
+      if (piece == 0) break;
+    }
+    if (!out.is_same(output)) {
+      QueueGuard g(comm_q_);
+      output.copy_(out);
+    }
+  });
 }
 
 c10::intrusive_ptr<c10d::Work> ProcessGroupB200::reduce_scatter(std::vector<at::Tensor>& outputs,
@@ -790,7 +846,8 @@ int64_t ProcessGroupB200::shard_elems(int64_t numel, at::ScalarType dtype) const
 c10::intrusive_ptr<c10d::Work> ProcessGroupB200::fused_allreduce_step(
     const at::Tensor& grads, const at::Tensor& params, const at::Tensor& state1, const at::Tensor& state2, int64_t kind,
     double lr, double momentum, double dampening, double weight_decay, double beta1, double beta2, double eps,
-    int64_t step, bool nesterov, bool first_step, double scale) {
+    int64_t step, bool nesterov, bool first_step, double scale, const std::optional<at::Tensor>& lowp,
+    const std::optional<at::Tensor>& cast_src, bool zero_grads) {
   TORCH_CHECK(!hostsim() && arena_, "fused_allreduce_step needs the CUDA backend");
   TORCH_CHECK(params.scalar_type() == at::kFloat && grads.numel() == params.numel(), "fused_allreduce_step: params must be fp32 and match grads");
   const int64_t shard = shard_elems(grads.numel(), grads.scalar_type());
@@ -806,7 +863,23 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupB200::fused_allreduce_step(
   o.nesterov = nesterov; o.first_step = first_step;
   o.state1 = state1.data_ptr<float>();
   o.state2 = state2.defined() && state2.numel() ? state2.data_ptr<float>() : nullptr;
-  return run_on_comm(c10d::OpType::ALLREDUCE, {grads, params, state1}, [&, goff, poff, o](void* stream) {
+  std::vector<at::Tensor> used{grads, params, state1};
+  if (lowp.has_value() && lowp->defined()) {
+    TORCH_CHECK(lowp->numel() == params.numel() && (lowp->scalar_type() == at::kBFloat16 || lowp->scalar_type() == at::kHalf),
+                "fused_allreduce_step: the 16-bit parameter copy must match the parameters");
+    o.lowp_offset = arena_->offset_of(lowp->data_ptr());
+    o.lowp_dtype = dtype_code(lowp->scalar_type());
+    used.push_back(*lowp);
+  }
+  if (cast_src.has_value() && cast_src->defined()) {
+    TORCH_CHECK(cast_src->scalar_type() == at::kFloat && cast_src->numel() >= shard * size_ && grads.scalar_type() != at::kFloat &&
+                    is_b200(*cast_src) && cast_src->is_contiguous(),
+                "fused_allreduce_step: cast_src must be a padded fp32 device tensor and the exchange dtype 16-bit");
+    o.cast_src = cast_src->data_ptr<float>();
+    used.push_back(*cast_src);
+  }
+  o.zero_grads = zero_grads ? 1 : 0;
+  return run_on_comm(c10d::OpType::ALLREDUCE, used, [&, goff, poff, o](void* stream) {
     const B200CommCtx ctx = arena_->ctx();
     COMM_CHECK(b200_comm_allreduce_opt(&ctx, goff, poff, grads.numel(), dtype_code(grads.scalar_type()), (float)scale, &o,
                                        ++seq_, stream));
@@ -814,11 +887,33 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupB200::fused_allreduce_step(
 }
 
 void ProcessGroupB200::set_wait_limit_ms(int64_t ms) {
-  if (arena_) arena_->set_timeout_ns(static_cast<unsigned long long>(ms) * 1000000ull);
+  // remembered when the arena does not exist yet (it is created by the first collective)
+  wait_limit_ms_ = ms;
+  apply_wait_limit();
+}
+void ProcessGroupB200::setTimeout(std::chrono::milliseconds timeout) {
+  timeout_ = timeout;
+  apply_wait_limit();
+}
+// Device-side waits run out after the explicit limit if one was set, else after the group's own
+// timeout (init_process_group(timeout=...)): a peer that is late by less than that (a checkpoint
+// save on rank 0, a slow first step) must not poison the communicator.
+void ProcessGroupB200::apply_wait_limit() {
+  if (!arena_) return;
+  const int64_t ms = wait_limit_ms_ > 0 ? wait_limit_ms_ : static_cast<int64_t>(timeout_.count());
+  arena_->set_timeout_ns(ms > 0 ? static_cast<unsigned long long>(ms) * 1000000ull : 0ull);
 }
 int64_t ProcessGroupB200::status_word() const { return arena_ ? *((volatile int*)arena_->status_host()) : 0; }
 void ProcessGroupB200::clear_status() {
-  if (arena_) *((volatile int*)arena_->status_host()) = 0;
+  if (!arena_) return;
+  // A kernel in which only some CTAs gave up leaves the CTA-arrival counter of the end barrier
+  // non-zero; it has to start from zero again or the next collective signals "done" early.
+  DeviceSwitch sw(device_);
+  comm_q_.synchronize();
+  COMM_CHECK(b200_memset_async(arena_->counter_ptr(), 0, 16, nullptr));  // both CTA counters
+  COMM_CHECK(b200_device_synchronize());
+  *((volatile int*)arena_->status_host()) = 0;
+  status_logged_.store(false);
 }
 
 }  // namespace catch_b200

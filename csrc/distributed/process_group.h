@@ -16,6 +16,7 @@
 #pragma once
 #include <atomic>
 #include <condition_variable>
+#include <deque>
 #include <mutex>
 #include <thread>
 #include <torch/csrc/distributed/c10d/Backend.hpp>
@@ -66,7 +67,7 @@ class ProcessGroupB200 : public c10d::Backend {
   ~ProcessGroupB200() override;
 
   const std::string getBackendName() const override { return "bwccl"; }
-  void setTimeout(std::chrono::milliseconds timeout) override { timeout_ = timeout; }
+  void setTimeout(std::chrono::milliseconds timeout) override;
 
   c10::intrusive_ptr<c10d::Work> broadcast(std::vector<at::Tensor>& tensors, const c10d::BroadcastOptions& opts) override;
   c10::intrusive_ptr<c10d::Work> allreduce(std::vector<at::Tensor>& tensors, const c10d::AllreduceOptions& opts) override;
@@ -91,11 +92,18 @@ class ProcessGroupB200 : public c10d::Backend {
   at::Tensor symm_empty(int64_t numel, at::ScalarType dtype);
   // reduce-scatter of `grads` (a symm_empty tensor) * scale, optimizer step on this
   // rank's shard of `params` (a symm_empty fp32 tensor), all-gather of the parameters.
+  // lowp: symm_empty 16-bit copy of the parameters, refreshed on every rank in the same pass.
+  // cast_src: local fp32 gradients (padded to shard_elems * world) that the kernel first converts into
+  // `grads` (16-bit), so that only 16-bit values cross NVLink.  zero_grads: the kernel leaves the
+  // gradients (cast_src if given, else `grads`) cleared for the next backward pass.
   c10::intrusive_ptr<c10d::Work> fused_allreduce_step(const at::Tensor& grads, const at::Tensor& params,
                                                       const at::Tensor& state1, const at::Tensor& state2, int64_t kind,
                                                       double lr, double momentum, double dampening, double weight_decay,
                                                       double beta1, double beta2, double eps, int64_t step,
-                                                      bool nesterov, bool first_step, double scale);
+                                                      bool nesterov, bool first_step, double scale,
+                                                      const std::optional<at::Tensor>& lowp = std::nullopt,
+                                                      const std::optional<at::Tensor>& cast_src = std::nullopt,
+                                                      bool zero_grads = false);
   int64_t shard_elems(int64_t numel, at::ScalarType dtype) const;
   // all-reduce in place on a symm_empty tensor (no staging copies)
   c10::intrusive_ptr<c10d::Work> allreduce_symm(const at::Tensor& t, int64_t op, double scale, bool test_no_signal);
@@ -108,12 +116,14 @@ class ProcessGroupB200 : public c10d::Backend {
 
  private:
   void ensure_arena(int device);
+  void apply_wait_limit();
   void check_single(const std::vector<at::Tensor>& tensors) const;
   c10::intrusive_ptr<WorkB200> make_work(c10d::OpType op, std::vector<at::Tensor> outputs);
   // runs fn(stream) on the comm queue ordered after the current compute queue
   template <typename F>
   c10::intrusive_ptr<c10d::Work> run_on_comm(c10d::OpType op, std::vector<at::Tensor> tensors, F&& fn, Queue* q = nullptr);
   void throw_if_failed() const;
+  void gather_into(const at::Tensor& in, const std::vector<char*>& dsts, void* stream);
   // host-simulated transport
   std::vector<std::vector<uint8_t>> store_exchange(const std::vector<uint8_t>& mine, bool everyone_sends, int root);
   c10::intrusive_ptr<c10d::Work> hostsim_collective(c10d::OpType op, std::vector<at::Tensor> outs,
@@ -127,6 +137,8 @@ class ProcessGroupB200 : public c10d::Backend {
   uint64_t seq_ = 0;
   std::vector<uint64_t> send_seq_, recv_seq_;
   uint64_t host_seq_ = 0;
+  std::deque<uint64_t> posted_;   // host-simulated transport: rounds whose message is still in the Store
+  int64_t wait_limit_ms_ = 0;     // explicit device-side wait limit (0 = follow timeout_)
   std::string uid_;
 
   // ---- watchdog: one host thread per group.  It publishes this rank's heartbeat counter in the Store,

@@ -55,9 +55,11 @@ class FusedRunner {
       auto it = plans_.find(spec);
       if (it != plans_.end()) plan = it->second;
     }
-    Stack saved;
+    // The interpreter consumes the group's inputs from the stack, so they are kept aside: the
+    // op-by-op fallback (and the debug comparison) start again from them.
+    const Stack saved(stack.end() - n_in, stack.end());
+    const size_t base = stack.size() - n_in;
     const char* dbg = std::getenv("CATCH_B200_FUSED_KERNEL_DEBUG");
-    if (dbg) saved.assign(stack.end() - n_in, stack.end());
     try {
       if (!plan) plan = compile(spec, stack, n_in);
       InterpreterState(*plan).run(stack);
@@ -66,7 +68,8 @@ class FusedRunner {
     } catch (const std::exception& e) {
       TORCH_WARN("b200 fusion group failed (", e.what(), "); running it op by op instead.");
       g_fallbacks++;
-      run_fallback(stack, n_in, saved);
+      stack.resize(base);  // drop whatever the failed plan left behind
+      run_fallback(stack, saved);
       return;
     }
     if (dbg) debug_compare(dbg, saved, stack);
@@ -93,9 +96,8 @@ class FusedRunner {
     return code;
   }
 
-  void run_fallback(Stack& stack, size_t n_in, const Stack& saved) {
-    (void)saved;
-    (void)n_in;
+  void run_fallback(Stack& stack, const Stack& saved) {
+    stack.insert(stack.end(), saved.begin(), saved.end());
     InterpreterState(fallback_).run(stack);
   }
 

@@ -265,8 +265,10 @@ Tensor dgrad_impl(const Tensor& grad_in, const Tensor& weight, const ConvGeom& g
 
 // fp32_result: hand back the fp32 accumulation buffer itself (viewed as [K, C, R, S] in channels-last
 // memory) instead of a copy in the weight's dtype -- for callers that accumulate into fp32 master gradients.
+// accum_into: an fp32 tensor holding [K][R][S][C] (the channels-last memory of the weight gradient) that the
+// kernel adds its result to, e.g. a view of a flat gradient bucket; nothing is returned then.
 Tensor wgrad_impl(const Tensor& grad_in, const Tensor& input, const Tensor& weight, const ConvGeom& g,
-                  bool fp32_result = false) {
+                  bool fp32_result = false, const Tensor* accum_into = nullptr) {
   const at::ScalarType dt = compute_dtype(grad_in.scalar_type());
   const double gscale = fp16_safe_scale(grad_in);
   const Tensor grad = gscale == 1.0 ? grad_in : grad_in * gscale;
@@ -287,7 +289,15 @@ Tensor wgrad_impl(const Tensor& grad_in, const Tensor& input, const Tensor& weig
     build_forward_taps(p, x, g);
     cin_k = g.C; wtaps = g.R * g.S;
   }
-  Tensor acc = at::zeros({g.K, wtaps * cin_k}, grad.options().dtype(at::kFloat));
+  const bool direct = accum_into && !stem && gscale == 1.0;
+  Tensor acc;
+  if (direct) {
+    TORCH_CHECK(accum_into->scalar_type() == at::kFloat && accum_into->numel() == g.K * wtaps * cin_k,
+                "conv wgrad: the accumulation target must be fp32 with the weight's number of elements");
+    acc = *accum_into;
+  } else {
+    acc = at::zeros({g.K, wtaps * cin_k}, grad.options().dtype(at::kFloat));
+  }
   p.N = (int)g.N; p.P = (int)g.P; p.Q = (int)g.Q; p.Cin = (int)cin_k; p.Cout = (int)g.K;
   p.ab_dtype = to_b200_dtype(dt);
   p.dy = dy.data_ptr();
@@ -295,6 +305,7 @@ Tensor wgrad_impl(const Tensor& grad_in, const Tensor& input, const Tensor& weig
   p.dw_acc = acc.data_ptr<float>();
   p.wtaps = (int)wtaps;
   if (p.ntaps > 0) B200_KERNEL_CHECK(b200_conv_wgrad(&p, scope.stream()));
+  if (direct) return Tensor();
   Tensor dw;
   if (stem) {
     // acc [K][R][8(s)][8(c)] -> [K, C, R, S]
@@ -302,6 +313,11 @@ Tensor wgrad_impl(const Tensor& grad_in, const Tensor& input, const Tensor& weig
   } else {
     // acc [K][R][S][C] is the channels-last memory of a [K, C, R, S] tensor
     dw = acc.view({g.K, g.R, g.S, g.C}).permute({0, 3, 1, 2});
+  }
+  if (accum_into) {  // the kernel could not add in place (first-layer packing or a rescaled gradient)
+    at::Tensor target = accum_into->dim() == 4 ? *accum_into : accum_into->view({g.K, g.R, g.S, g.C}).permute({0, 3, 1, 2});
+    target.add_(gscale == 1.0 ? dw : dw * (1.0 / gscale));
+    return Tensor();
   }
   if (fp32_result) return gscale == 1.0 ? dw : dw * (1.0 / gscale);
   Tensor out = at::empty_like(weight, weight.options(), weight.suggest_memory_format());
@@ -496,9 +512,12 @@ at::Tensor conv_bn_act_device(const at::Tensor& input, const at::Tensor& weight,
 // Backward of a dense 16-bit convolution whose weight gradient is returned in fp32 (the accumulation
 // buffer of the weight-gradient kernel, no rounding to the activation dtype): used when the parameter
 // and its gradient are fp32 and only the compute copy of the weight is 16-bit.
+// With `accum`, the weight gradient is added straight into that fp32 buffer (a flat view of memory laid out
+// [K][R][S][C]) and the second result is undefined: no temporary, no separate accumulation kernel.
 std::tuple<at::Tensor, at::Tensor> conv_backward_fp32w_device(const at::Tensor& grad, const at::Tensor& input,
                                                               const at::Tensor& weight, at::IntArrayRef stride,
-                                                              at::IntArrayRef padding, bool need_dx, bool need_dw) {
+                                                              at::IntArrayRef padding, bool need_dx, bool need_dw,
+                                                              const std::optional<at::Tensor>& accum) {
   const int64_t ones[2] = {1, 1};
   check_supported(input, weight, stride, padding, at::IntArrayRef(ones, 2), false, 1);
   ConvGeom g = geom(input, weight, stride, padding);
@@ -507,7 +526,15 @@ std::tuple<at::Tensor, at::Tensor> conv_backward_fp32w_device(const at::Tensor& 
     TORCH_CHECK(g.C % 8 == 0, "b200 conv dgrad: input channels must be a multiple of 8");
     dx = dgrad_impl(grad, weight, g, input.scalar_type());
   }
-  if (need_dw) dw = wgrad_impl(grad, input, weight, g, /*fp32_result=*/true);
+  if (need_dw) {
+    const bool has_acc = accum.has_value() && accum->defined();
+    at::Tensor flat;
+    if (has_acc) {
+      TORCH_CHECK(is_b200(*accum) && accum->is_contiguous() && accum->dim() == 1, "conv2d_backward_fp32w: accum must be a flat device tensor");
+      flat = *accum;
+    }
+    dw = wgrad_impl(grad, input, weight, g, /*fp32_result=*/true, has_acc ? &flat : nullptr);
+  }
   return {dx, dw};
 }
 

@@ -36,10 +36,11 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_mask(
     const at::Tensor& input, const std::optional<at::Tensor>& weight, const std::optional<at::Tensor>& bias,
     const std::optional<at::Tensor>& running_mean, const std::optional<at::Tensor>& running_var,
     const std::optional<at::Tensor>& residual, bool training, double momentum, double eps, int64_t act,
-    const std::optional<at::Tensor>& channel_sums);
+    const std::optional<at::Tensor>& channel_sums, const std::optional<at::Tensor>& num_batches_tracked);
 std::tuple<at::Tensor, at::Tensor> conv_backward_fp32w_device(const at::Tensor& grad, const at::Tensor& input,
                                                               const at::Tensor& weight, at::IntArrayRef stride,
-                                                              at::IntArrayRef padding, bool need_dx, bool need_dw);
+                                                              at::IntArrayRef padding, bool need_dx, bool need_dw,
+                                                              const std::optional<at::Tensor>& accum);
 std::tuple<at::Tensor, at::Tensor> conv_stats_device(const at::Tensor& input, const at::Tensor& weight, at::IntArrayRef stride,
                                                      at::IntArrayRef padding);
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_backward(
@@ -87,14 +88,16 @@ TORCH_LIBRARY(catch_b200, m) {
   m.def("batch_norm_act(Tensor input, Tensor? weight, Tensor? bias, Tensor(a!)? running_mean, Tensor(b!)? running_var, "
         "Tensor? residual, bool training, float momentum, float eps, int act, Tensor? channel_sums=None) -> (Tensor, Tensor, Tensor)");
   // like batch_norm_act; the 4th result is a bit mask of the positive outputs (empty if not produced) that
-  // batch_norm_act_backward accepts in place of `out`
+  // batch_norm_act_backward accepts in place of `out`; num_batches_tracked (int64, optional) is incremented
   m.def("batch_norm_act_mask(Tensor input, Tensor? weight, Tensor? bias, Tensor(a!)? running_mean, Tensor(b!)? running_var, "
-        "Tensor? residual, bool training, float momentum, float eps, int act, Tensor? channel_sums=None) -> (Tensor, Tensor, Tensor, Tensor)");
+        "Tensor? residual, bool training, float momentum, float eps, int act, Tensor? channel_sums=None, "
+        "Tensor(c!)? num_batches_tracked=None) -> (Tensor, Tensor, Tensor, Tensor)");
   // convolution (no bias, 16-bit) that also returns fp64 [2 * Cout] channel sums / sums of squares of its output
   m.def("conv2d_stats(Tensor input, Tensor weight, int[] stride, int[] padding) -> (Tensor, Tensor)");
-  // (grad_input, grad_weight) of a dense 16-bit convolution; grad_weight is fp32 (undefined results where not needed)
+  // (grad_input, grad_weight) of a dense 16-bit convolution; grad_weight is fp32 (undefined results where not
+  // needed).  With `accum` (flat fp32, memory order [K][R][S][C]) the weight gradient is added into it in place.
   m.def("conv2d_backward_fp32w(Tensor grad, Tensor input, Tensor weight, int[] stride, int[] padding, bool need_dx, "
-        "bool need_dw) -> (Tensor, Tensor)");
+        "bool need_dw, Tensor(a!)? accum=None) -> (Tensor, Tensor)");
   m.def("batch_norm_act_backward(Tensor grad_out, Tensor out, Tensor input, Tensor? weight, Tensor? running_mean, "
         "Tensor save_mean, Tensor save_invstd, bool training, int act, bool has_residual) -> (Tensor, Tensor, Tensor, Tensor)");
 }

@@ -3,6 +3,10 @@
 // Parity: torch_mlu/csrc/aten/operators/cnnl/native_batch_norm.cpp:77,
 // native_batch_norm_backward.cpp:85 (train / eval, 2-5-D inputs viewed as
 // channels-last 4-D).  LayerNorm is new (the reference has no device kernel).
+#include <map>
+#include <mutex>
+
+#include "../runtime/caching_allocator.h"
 #include "common.h"
 #include "kernels.h"
 
@@ -220,6 +224,38 @@ std::tuple<Tensor, Tensor, Tensor> k_native_batch_norm_backward(
 // the residual add costs a pass over the activation.
 }  // namespace
 
+namespace {
+// Zeroed fp64 scratch (2 x 8192 channel sums) and a zeroed counter word per (device, queue).  Contract: whoever
+// takes it finds it cleared and leaves it cleared (b200_bn_backward_apply2 does the clearing on the device).
+struct BnScratch {
+  at::Tensor sums, counter;
+};
+std::mutex g_bn_scratch_mu;
+std::map<std::pair<int, void*>, BnScratch> g_bn_scratch;
+const bool g_bn_scratch_dropper = [] {
+  registerCacheDropper([] {
+    std::lock_guard<std::mutex> lk(g_bn_scratch_mu);
+    g_bn_scratch.clear();
+  });
+  return true;
+}();
+BnScratch* bn_scratch(int device, void* stream) {
+  std::lock_guard<std::mutex> lk(g_bn_scratch_mu);
+  auto key = std::make_pair(device, stream);
+  auto it = g_bn_scratch.find(key);
+  if (it == g_bn_scratch.end()) {
+    auto opt = at::TensorOptions().device(c10::Device(c10::DeviceType::PrivateUse1, device));
+    BnScratch sc{at::zeros({2 * 8192}, opt.dtype(at::kDouble)), at::zeros({1}, opt.dtype(at::kInt))};
+    it = g_bn_scratch.emplace(key, std::move(sc)).first;
+  }
+  return &it->second;
+}
+void bn_scratch_drop(int device, void* stream) {
+  std::lock_guard<std::mutex> lk(g_bn_scratch_mu);
+  g_bn_scratch.erase(std::make_pair(device, stream));
+}
+}  // namespace
+
 static std::tuple<at::Tensor, at::Tensor, at::Tensor> batch_norm_act_impl(const at::Tensor& input, const std::optional<at::Tensor>& weight,
                                                               const std::optional<at::Tensor>& bias,
                                                               const std::optional<at::Tensor>& running_mean,
@@ -227,7 +263,10 @@ static std::tuple<at::Tensor, at::Tensor, at::Tensor> batch_norm_act_impl(const 
                                                               const std::optional<at::Tensor>& residual, bool training,
                                                               double momentum, double eps, int64_t act,
                                                               const std::optional<at::Tensor>& channel_sums,
-                                                              at::Tensor* relu_mask) {
+                                                              at::Tensor* relu_mask, const at::Tensor* batch_counter = nullptr,
+                                                              bool* counted = nullptr) {
+  // batch_counter (num_batches_tracked): incremented by the fused kernel when that runs (*counted = true);
+  // otherwise the caller adds one itself
   const bool has_res = residual.has_value() && residual->defined();
   auto compose = [&]() {
     auto r = at::native_batch_norm(input, weight, bias, running_mean, running_var, training, momentum, eps);
@@ -282,6 +321,27 @@ static std::tuple<at::Tensor, at::Tensor, at::Tensor> batch_norm_act_impl(const 
       rv = running_var->data_ptr();
       rdt = to_b200_dtype(running_mean->scalar_type());
     }
+    // One launch: statistics from the sums, running-statistics update, normalisation (+ residual, ReLU, mask).
+    void* fused_mask = nullptr;
+    if (relu_mask && act == 1 && input.scalar_type() != at::kFloat && C % 8 == 0 && C <= 8192 && (v.rows * C) / 8 < 0xffffffffLL) {
+      *relu_mask = at::empty({v.rows * C / 8}, input.options().dtype(at::kByte));
+      fused_mask = relu_mask->data_ptr();
+    }
+    long long* counter_ptr = nullptr;
+    if (batch_counter && batch_counter->defined() && is_b200(*batch_counter) && batch_counter->scalar_type() == at::kLong &&
+        batch_counter->numel() == 1)
+      counter_ptr = reinterpret_cast<long long*>(batch_counter->data_ptr());
+    const int frc = b200_bn_apply_fused(v.t.data_ptr(), xdt, out.data_ptr(), v.rows, C, sums.data_ptr<double>(), (float)eps,
+                                        (float)momentum, save_mean.data_ptr<float>(), save_invstd.data_ptr<float>(), rm, rv, rdt,
+                                        gamma, beta, pdt, has_res ? res.data_ptr() : nullptr, (int)act, fused_mask, counter_ptr,
+                                        scope.stream());
+    if (frc == 0) {
+      if (counted) *counted = counter_ptr != nullptr;
+      note_kernel_launch();
+      return {out, save_mean, save_invstd};
+    }
+    TORCH_CHECK(frc == 801, "b200 batch_norm_act: ", device_error_string(frc));
+    if (relu_mask) *relu_mask = at::empty({0}, input.options().dtype(at::kByte));
     B200_KERNEL_CHECK(b200_bn_finalize(sums.data_ptr<double>(), v.rows, C, (float)eps, (float)momentum,
                                        save_mean.data_ptr<float>(), save_invstd.data_ptr<float>(), rm, rv, rdt, scope.stream()));
     mean_ptr = save_mean.data_ptr();
@@ -325,10 +385,13 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_mask(
     const at::Tensor& input, const std::optional<at::Tensor>& weight, const std::optional<at::Tensor>& bias,
     const std::optional<at::Tensor>& running_mean, const std::optional<at::Tensor>& running_var,
     const std::optional<at::Tensor>& residual, bool training, double momentum, double eps, int64_t act,
-    const std::optional<at::Tensor>& channel_sums) {
+    const std::optional<at::Tensor>& channel_sums, const std::optional<at::Tensor>& num_batches_tracked) {
   at::Tensor mask = at::empty({0}, input.options().dtype(at::kByte));
+  const at::Tensor* nbt = (num_batches_tracked.has_value() && num_batches_tracked->defined()) ? &*num_batches_tracked : nullptr;
+  bool counted = false;
   auto r = batch_norm_act_impl(input, weight, bias, running_mean, running_var, residual, training, momentum, eps, act, channel_sums,
-                               &mask);
+                               &mask, nbt, &counted);
+  if (nbt && !counted) const_cast<at::Tensor*>(nbt)->add_(1);
   return {std::get<0>(r), std::get<1>(r), std::get<2>(r), mask};
 }
 
@@ -358,17 +421,28 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_backwa
   at::Tensor dx = at::empty_strided(xv.t.sizes(), xv.t.strides(), input.options());
   at::Tensor dres = has_residual ? at::empty_strided(xv.t.sizes(), xv.t.strides(), input.options()) : at::Tensor();
   at::Tensor dgamma = at::empty({C}, fopt), dbeta = at::empty({C}, fopt);
-  at::Tensor sums = at::zeros({2 * C}, input.options().dtype(at::kDouble));
   const void* mask = act == 1 ? y.data_ptr() : nullptr;
   const int mask_dt = bitmask ? (int)B200_U8 : xdt;
   if (bitmask) TORCH_CHECK(y.numel() * 8 == xv.rows * C, "batch_norm_act_backward: mask size does not match the input");
-  B200_KERNEL_CHECK(b200_bn_backward_reduce(dy.data_ptr(), xdt, xv.t.data_ptr(), xdt, mean_t.data_ptr(), mdt,
-                                            invstd.data_ptr<float>(), mask, mask_dt, xv.rows, C, sums.data_ptr<double>(),
-                                            scope.stream()));
-  B200_KERNEL_CHECK(b200_bn_backward_apply(dy.data_ptr(), xdt, xv.t.data_ptr(), xdt, mean_t.data_ptr(), mdt,
-                                           invstd.data_ptr<float>(), gamma, pdt, mask, mask_dt, sums.data_ptr<double>(), xv.rows, C,
-                                           training ? 1 : 0, dx.data_ptr(), xdt, dgamma.data_ptr<float>(),
-                                           dbeta.data_ptr<float>(), has_residual ? dres.data_ptr() : nullptr, scope.stream()));
+  // The fp64 sums live in a per-queue scratch buffer that the apply kernel clears after use, which saves a
+  // memset launch per batch norm.  If anything throws in between, the buffer is dropped (it may be dirty).
+  const bool vec_ok = C <= 8192 && C % (xdt == B200_F32 ? 4 : 8) == 0 && (xv.rows * C) / (xdt == B200_F32 ? 4 : 8) < 0xffffffffLL;
+  BnScratch* scratch = vec_ok ? bn_scratch(input.device().index(), scope.stream()) : nullptr;
+  at::Tensor sums = scratch ? scratch->sums : at::zeros({2 * C}, input.options().dtype(at::kDouble));
+  try {
+    B200_KERNEL_CHECK(b200_bn_backward_reduce(dy.data_ptr(), xdt, xv.t.data_ptr(), xdt, mean_t.data_ptr(), mdt,
+                                              invstd.data_ptr<float>(), mask, mask_dt, xv.rows, C, sums.data_ptr<double>(),
+                                              scope.stream()));
+    B200_KERNEL_CHECK(b200_bn_backward_apply2(dy.data_ptr(), xdt, xv.t.data_ptr(), xdt, mean_t.data_ptr(), mdt,
+                                              invstd.data_ptr<float>(), gamma, pdt, mask, mask_dt, sums.data_ptr<double>(), xv.rows, C,
+                                              training ? 1 : 0, dx.data_ptr(), xdt, dgamma.data_ptr<float>(),
+                                              dbeta.data_ptr<float>(), has_residual ? dres.data_ptr() : nullptr,
+                                              scratch ? reinterpret_cast<unsigned*>(scratch->counter.data_ptr()) : nullptr,
+                                              scope.stream()));
+  } catch (...) {
+    if (scratch) bn_scratch_drop(input.device().index(), scope.stream());
+    throw;
+  }
   if (weight.has_value() && weight->defined() && weight->scalar_type() != at::kFloat) {
     dgamma = dgamma.to(weight->scalar_type());
     dbeta = dbeta.to(weight->scalar_type());

@@ -25,7 +25,11 @@ void bind_extras(py::module& m) {
       .def("shard_elems", &ProcessGroupB200::shard_elems)
       .def("allreduce_symm", &ProcessGroupB200::allreduce_symm, py::arg("tensor"), py::arg("op") = 0, py::arg("scale") = 1.0,
            py::arg("test_no_signal") = false, py::call_guard<py::gil_scoped_release>())
-      .def("fused_allreduce_step", &ProcessGroupB200::fused_allreduce_step, py::call_guard<py::gil_scoped_release>())
+      .def("fused_allreduce_step", &ProcessGroupB200::fused_allreduce_step, py::arg("grads"), py::arg("params"),
+           py::arg("state1"), py::arg("state2"), py::arg("kind"), py::arg("lr"), py::arg("momentum"), py::arg("dampening"),
+           py::arg("weight_decay"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("step"), py::arg("nesterov"),
+           py::arg("first_step"), py::arg("scale"), py::arg("lowp") = std::nullopt, py::arg("cast_src") = std::nullopt,
+           py::arg("zero_grads") = false, py::call_guard<py::gil_scoped_release>())
       .def("set_wait_limit_ms", &ProcessGroupB200::set_wait_limit_ms)
       .def("status_word", &ProcessGroupB200::status_word)
       .def("dead_peer", &ProcessGroupB200::dead_peer)

@@ -93,7 +93,6 @@ def test_fusion_passes_rewrite_and_segment():
     assert "aten::conv2d" not in inner and "aten::relu" not in inner.replace("relu_", "")
     out = opt(x)
     assert torch.allclose(out, ref, atol=1e-4), (out - ref).abs().max()
-    dev_out = opt.to(DEV)(x.to(DEV)) if False else None  # module.to on a frozen module is checked on the GPU
     before = jit.fusion_stats()
     opt(x); opt(torch.randn(3, 8, 12, 12))
     after = jit.fusion_stats()

@@ -58,6 +58,13 @@ def _collectives(rank, world):
     dist.reduce(z, 0)
     if rank == 0:
         assert torch.equal(z.cpu(), torch.full((4,), float(sum(range(1, world + 1)))))
+    zi = torch.full((5,), (rank + 1) * world, dtype=torch.int64).to(DEV)
+    dist.all_reduce(zi, op=dist.ReduceOp.AVG)
+    assert torch.equal(zi.cpu(), torch.full((5,), sum(range(1, world + 1)), dtype=torch.int64))
+    strided = [torch.empty(6, 2, device=DEV)[:, 0] for _ in range(world)]
+    dist.all_gather(strided, torch.full((6,), float(rank), device=DEV))
+    for r in range(world):
+        assert torch.equal(strided[r].cpu(), torch.full((6,), float(r)))
     rs = torch.empty(3, device=DEV)
     dist.reduce_scatter_tensor(rs, torch.arange(world * 3, dtype=torch.float32, device=DEV))
     assert torch.equal(rs.cpu(), world * torch.arange(rank * 3, rank * 3 + 3).float())
@@ -106,8 +113,10 @@ def test_stock_ddp_matches_cpu():
     run_ranks(_ddp, world=WORLD, env=ENV, timeout=240)
 
 
-def _fused(rank, world, kind):
+def _fused(rank, world, kind, grad_dtype="fp32"):
     from catch_b200.parallel import FusedDataParallel
+
+    gd = torch.bfloat16 if grad_dtype == "bf16" else torch.float32
 
     _init(rank, world)
     torch.manual_seed(0)
@@ -115,24 +124,42 @@ def _fused(rank, world, kind):
     ref = torch.nn.Sequential(torch.nn.Linear(64, 256), torch.nn.Tanh(), torch.nn.Linear(256, 8))
     ref.load_state_dict(net.state_dict())
     if kind == "sgd":
-        fdp = FusedDataParallel(net.to(DEV), "sgd", lr=0.05, momentum=0.9, weight_decay=1e-4, bucket_mb=0.005)
+        fdp = FusedDataParallel(net.to(DEV), "sgd", lr=0.05, momentum=0.9, weight_decay=1e-4, bucket_mb=0.005, grad_dtype=gd)
         opt_ref = torch.optim.SGD(ref.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-4)
     else:
-        fdp = FusedDataParallel(net.to(DEV), "adamw", lr=1e-3, weight_decay=0.01, bucket_mb=0.005)
+        fdp = FusedDataParallel(net.to(DEV), "adamw", lr=1e-3, weight_decay=0.01, bucket_mb=0.005, grad_dtype=gd)
         opt_ref = torch.optim.AdamW(ref.parameters(), lr=1e-3, weight_decay=0.01)
     assert len(fdp.buckets) > 1
     g = torch.Generator().manual_seed(1)
-    for _ in range(5):
+    for it in range(5):
         x = torch.randn(16 * world, 64, generator=g)
         y = torch.randn(16 * world, 8, generator=g)
         opt_ref.zero_grad()
         torch.nn.functional.mse_loss(ref(x), y).backward()
         opt_ref.step()
-        torch.nn.functional.mse_loss(fdp(x[rank * 16:(rank + 1) * 16].to(DEV)), y[rank * 16:(rank + 1) * 16].to(DEV)).backward()
+        xs, ys = x[rank * 16:(rank + 1) * 16].to(DEV), y[rank * 16:(rank + 1) * 16].to(DEV)
+        if it == 2:  # the same batch as two accumulated halves
+            with fdp.no_sync():
+                (0.5 * torch.nn.functional.mse_loss(fdp(xs[:8]), ys[:8])).backward()
+            (0.5 * torch.nn.functional.mse_loss(fdp(xs[8:]), ys[8:])).backward()
+        else:
+            torch.nn.functional.mse_loss(fdp(xs), ys).backward()
         fdp.step()
     torch.b200.synchronize()
+    tol = 3e-3 if grad_dtype == "fp32" else 2e-2
     for a, b in zip(ref.parameters(), fdp.module.parameters()):
-        assert (a - b.cpu()).abs().max().item() < 3e-3, (a - b.cpu()).abs().max().item()
+        assert (a - b.cpu()).abs().max().item() < tol, (a - b.cpu()).abs().max().item()
+    for p in fdp.module.parameters():  # 16-bit copies written by the peers' kernels
+        assert torch.equal(p._b200_lowp.cpu(), p.detach().to(torch.bfloat16).cpu())
+    for bk in fdp.buckets:  # cleared by the kernel
+        assert float(bk.grads.abs().max()) == 0.0
+    # optimizer state gathered from the shards loads into the stock optimizer
+    sd = fdp.optimizer_state_dict()
+    opt_chk = type(opt_ref)(ref.parameters(), **{k: v for k, v in opt_ref.defaults.items() if k in ("lr", "momentum", "weight_decay")})
+    opt_chk.load_state_dict(sd)
+    key = "momentum_buffer" if kind == "sgd" else "exp_avg"
+    for pr in ref.parameters():
+        assert (opt_chk.state[pr][key] - opt_ref.state[pr][key]).abs().max().item() < tol
     # every rank holds bit-identical parameters
     flat = torch.cat([p.detach().reshape(-1) for p in fdp.module.parameters()])
     outs = [torch.empty_like(flat) for _ in range(world)]
@@ -142,9 +169,9 @@ def _fused(rank, world, kind):
 
 
 @needs2
-@pytest.mark.parametrize("kind", ["sgd", "adamw"])
-def test_fused_allreduce_optimizer(kind):
-    run_ranks(_fused, world=WORLD, args=(kind,), env=ENV, timeout=240)
+@pytest.mark.parametrize("kind,grad_dtype", [("sgd", "fp32"), ("adamw", "fp32"), ("sgd", "bf16")])
+def test_fused_allreduce_optimizer(kind, grad_dtype):
+    run_ranks(_fused, world=WORLD, args=(kind, grad_dtype), env=ENV, timeout=240)
 
 
 def _bounded_wait(rank, world):

@@ -1,0 +1,148 @@
+"""FusedDataParallel on one GPU (world size one: the same bucket bookkeeping, fused single-device
+optimizer kernels): 16-bit parameter copies, convolution weight gradients added straight into the
+buckets, gradient accumulation under no_sync(), bucket launch order with unused parameters, and an
+optimizer state dict that torch.optim.SGD / AdamW can load."""
+import copy
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from common import assert_tensors_equal
+
+pytestmark = pytest.mark.gpu
+DEV = "blackwell"
+
+
+def _small_convnet():
+    import torchvision
+
+    torch.manual_seed(3)
+    return torchvision.models.resnet18(num_classes=16)
+
+
+def test_direct_weight_gradients_and_lowp_copies_match_plain_training():
+    """The fused wrapper (weight gradients added into the buckets by the kernel, bf16 weight copies written
+    by the optimizer kernel) must take the same steps as FusedSGD on the plain fused model."""
+    from catch_b200.fusion import StatsConv2d, fuse_bn_act
+    from catch_b200.optim import FusedSGD
+    from catch_b200.parallel import FusedDataParallel
+
+    ref = _small_convnet()
+    a = fuse_bn_act(copy.deepcopy(ref)).to(DEV).to(memory_format=torch.channels_last)
+    b = fuse_bn_act(copy.deepcopy(ref)).to(DEV).to(memory_format=torch.channels_last)
+    opt = FusedSGD(a.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-4)
+    fdp = FusedDataParallel(b, "sgd", lr=0.05, momentum=0.9, weight_decay=1e-4, bucket_mb=1.0)
+    assert len(fdp.buckets) > 2
+    convs = [m for m in b.modules() if isinstance(m, StatsConv2d)]
+    assert all(hasattr(m.weight, "_b200_lowp") and m.weight._b200_lowp.dtype == torch.bfloat16 for m in convs)
+    g = torch.Generator().manual_seed(5)
+    for _ in range(3):
+        x = torch.randn(8, 3, 64, 64, generator=g).to(DEV)
+        t = torch.randint(0, 16, (8,), generator=g).to(DEV)
+        with torch.autocast(DEV, dtype=torch.bfloat16):
+            la = F.cross_entropy(a(x), t)
+            lb = F.cross_entropy(fdp(x), t)
+        opt.zero_grad()
+        la.backward(); opt.step()
+        lb.backward(); fdp.step()
+        assert abs(la.item() - lb.item()) < 2e-2, (la.item(), lb.item())
+    for (n, p), (_, q) in zip(a.named_parameters(), b.named_parameters()):
+        assert_tensors_equal(q, p, prec=2e-2, use_MSE=True, msg=n)
+    for m in convs:  # the 16-bit copies follow the masters
+        assert torch.equal(m.weight._b200_lowp.cpu(), m.weight.detach().to(torch.bfloat16).cpu())
+    for bk in fdp.buckets:  # gradients are cleared for the next step
+        assert float(bk.grads.abs().max()) == 0.0
+
+
+def test_no_sync_accumulates_and_second_backward_raises():
+    from catch_b200.parallel import FusedDataParallel
+
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.Tanh(), torch.nn.Linear(64, 4))
+    ref = copy.deepcopy(net)
+    fdp = FusedDataParallel(net.to(DEV), "sgd", lr=0.1, momentum=0.9, bucket_mb=0.001, lowp_dtype=None)
+    opt = torch.optim.SGD(ref.parameters(), lr=0.1, momentum=0.9)
+    g = torch.Generator().manual_seed(1)
+    for _ in range(3):
+        xs = [torch.randn(8, 32, generator=g) for _ in range(2)]
+        opt.zero_grad()
+        for x in xs:
+            ref(x).pow(2).mean().backward()
+        opt.step()
+        with fdp.no_sync():
+            fdp(xs[0].to(DEV)).pow(2).mean().backward()
+        fdp(xs[1].to(DEV)).pow(2).mean().backward()
+        fdp.step()
+    for p, q in zip(ref.parameters(), fdp.module.parameters()):
+        assert_tensors_equal(q, p, prec=3e-3)
+    fdp(torch.randn(8, 32).to(DEV)).sum().backward()
+    with pytest.raises(RuntimeError, match="no_sync"):
+        fdp(torch.randn(8, 32).to(DEV)).sum().backward()
+
+
+def test_buckets_launch_in_order_with_unused_parameters():
+    from catch_b200.parallel import FusedDataParallel
+
+    class Two(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = torch.nn.Linear(16, 16)
+            self.unused = torch.nn.Linear(16, 16)
+            self.b = torch.nn.Linear(16, 4)
+
+        def forward(self, x):
+            return self.b(torch.tanh(self.a(x)))
+
+    torch.manual_seed(0)
+    net = Two()
+    before = copy.deepcopy(net.state_dict())
+    fdp = FusedDataParallel(net.to(DEV), "sgd", lr=0.1, bucket_mb=0.0005, lowp_dtype=None)
+    order = []
+    launch = fdp._launch
+    fdp._launch = lambda b: (order.append(b.index), launch(b))[1]
+    fdp(torch.randn(4, 16).to(DEV)).sum().backward()
+    fdp.step()
+    assert order == sorted(order) and len(order) == len(fdp.buckets), order
+    after = fdp.module.state_dict()
+    assert torch.equal(after["unused.weight"].cpu(), before["unused.weight"])   # zero gradient, no weight decay
+    assert not torch.equal(after["a.weight"].cpu(), before["a.weight"])
+
+
+@pytest.mark.parametrize("kind", ["sgd", "adamw"])
+def test_optimizer_state_dict_loads_into_stock_optimizer(kind):
+    from catch_b200.parallel import FusedDataParallel
+
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.Tanh(), torch.nn.Linear(64, 4))
+    ref = copy.deepcopy(net)
+    if kind == "sgd":
+        fdp = FusedDataParallel(net.to(DEV), "sgd", lr=0.05, momentum=0.9, weight_decay=1e-4, bucket_mb=0.001)
+        mk = lambda ps: torch.optim.SGD(ps, lr=0.05, momentum=0.9, weight_decay=1e-4)  # noqa: E731
+    else:
+        fdp = FusedDataParallel(net.to(DEV), "adamw", lr=1e-2, weight_decay=0.01, bucket_mb=0.001)
+        mk = lambda ps: torch.optim.AdamW(ps, lr=1e-2, weight_decay=0.01)  # noqa: E731
+    opt = mk(ref.parameters())
+    g = torch.Generator().manual_seed(2)
+    data = [torch.randn(8, 32, generator=g) for _ in range(6)]
+    for x in data[:3]:
+        opt.zero_grad(); ref(x).pow(2).mean().backward(); opt.step()
+        fdp(x.to(DEV)).pow(2).mean().backward(); fdp.step()
+    # the wrapper's state loads into a fresh stock optimizer, which then continues identically
+    sd = fdp.optimizer_state_dict()
+    resumed = copy.deepcopy(ref)
+    resumed.load_state_dict({k: v.cpu() for k, v in fdp.module.state_dict().items()})
+    opt2 = mk(resumed.parameters())
+    opt2.load_state_dict(sd)
+    # ... and the stock optimizer's state loads into a fresh wrapper
+    net3 = copy.deepcopy(ref)
+    fdp3 = FusedDataParallel(net3.to(DEV), kind, **({"lr": 0.05, "momentum": 0.9, "weight_decay": 1e-4} if kind == "sgd"
+                                                    else {"lr": 1e-2, "weight_decay": 0.01}), bucket_mb=0.002)
+    fdp3.load_optimizer_state_dict(opt.state_dict())
+    for x in data[3:]:
+        opt.zero_grad(); ref(x).pow(2).mean().backward(); opt.step()
+        opt2.zero_grad(); resumed(x).pow(2).mean().backward(); opt2.step()
+        fdp3(x.to(DEV)).pow(2).mean().backward(); fdp3.step()
+    for p, q, r in zip(ref.parameters(), resumed.parameters(), fdp3.module.parameters()):
+        assert_tensors_equal(q, p, prec=3e-3)
+        assert_tensors_equal(r, p, prec=3e-3)
