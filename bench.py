@@ -375,11 +375,17 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
-    # host threads and the pinned staging buffers stay on the GPU's NUMA node
-    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-    from catch_b200.utils.numa import bind_to_device_node
+    # Host threads and the pinned staging buffers stay on the GPU's NUMA node.  The helper is loaded from its
+    # file: importing the catch_b200 package registers the blackwell device with PyTorch, after which autograd
+    # on torch.cuda tensors no longer works in this process, and the stock arm has to run before that.
+    import importlib.util
 
-    numa_node = bind_to_device_node(local_rank)
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, here)
+    spec = importlib.util.spec_from_file_location("_bench_numa", os.path.join(here, "catch_b200", "utils", "numa.py"))
+    numa = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(numa)
+    numa_node = numa.bind_to_device_node(local_rank)
     store = None
     if world > 1:
         store = make_store(rank, world)

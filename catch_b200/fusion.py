@@ -51,8 +51,8 @@ class _ConvStatsFn(torch.autograd.Function):
     ``weight`` is the (fp32) parameter itself.  Its 16-bit compute copy is ``weight._b200_lowp`` when a data-parallel
     wrapper maintains one (refreshed by the optimizer kernel), else a cast made here.  The backward returns the
     weight gradient in fp32 straight from the weight-gradient kernel's accumulation buffer (no rounding to 16 bits,
-    no cast kernels); when the parameter's gradient lives in a flat bucket (``weight._b200_grad_acc``) the kernel
-    adds into that bucket directly and the bucket's owner is told that the gradient is ready."""
+    no cast kernels); when the parameter's gradient lives in a flat bucket (``weight._b200_grad_acc``, the flat
+    fp32 slice behind ``weight.grad``) the kernel adds into that bucket directly."""
 
     @staticmethod
     def forward(ctx, x, weight, stride, padding, compute_dtype):
@@ -81,9 +81,9 @@ class _ConvStatsFn(torch.autograd.Function):
             # the bucket slice must hold the gradient as [K][R][S][C]: channels-last parameters and 1x1 filters do
             if (acc is not None and p.grad is not None and p.grad.dtype == torch.float32 and p.dim() == 4
                     and (p.shape[2] * p.shape[3] == 1 or p.is_contiguous(memory_format=torch.channels_last))):
-                flat, ready = acc
-                dx, _ = torch.ops.catch_b200.conv2d_backward_fp32w(grad_y, x, w, stride, padding, need_dx, True, flat)
-                ready(ctx.param)
+                # The parameter's post-accumulate-grad hook still fires for the undefined gradient returned
+                # here, after this function has queued the kernel: that is what tells the bucket's owner.
+                dx, _ = torch.ops.catch_b200.conv2d_backward_fp32w(grad_y, x, w, stride, padding, need_dx, True, acc)
                 return dx, None, None, None, None
             dx, dw = torch.ops.catch_b200.conv2d_backward_fp32w(grad_y, x, w, stride, padding, need_dx, need_dw)
         else:

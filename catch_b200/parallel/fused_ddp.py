@@ -203,7 +203,7 @@ class FusedDataParallel(torch.nn.Module):
             for p, g, fg in zip(b.params, b.grad_views, b.flat_grads):
                 p.grad = g
                 # modules that can add their gradient into the bucket themselves look for this
-                p._b200_grad_acc = (fg, self._grad_ready)
+                p._b200_grad_acc = fg
 
     # ---------------------------------------------------------------- backward
     @contextlib.contextmanager
@@ -315,7 +315,7 @@ class FusedDataParallel(torch.nn.Module):
         else:
             group = {"lr": self.lr, "betas": tuple(self.betas), "eps": self.eps, "weight_decay": self.weight_decay,
                      "amsgrad": False, "maximize": False, "foreach": None, "capturable": False,
-                     "differentiable": False, "fused": None}
+                     "differentiable": False, "fused": None, "decoupled_weight_decay": True}
         group["params"] = list(range(len(order)))
         return {"state": state, "param_groups": [group]}
 

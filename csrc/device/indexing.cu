@@ -523,6 +523,37 @@ __global__ void dw_wgrad_kernel(const void* dy, const void* x, float* dw, int dt
 
 }  // namespace
 
+namespace {
+template <typename E>
+__global__ void index_fill_kernel(E* dst, const long long* idx, long long outer, long long n_dst, long long n_idx, long long inner,
+                                  E fill, int* bad_flag) {
+  const long long total = outer * n_idx * inner;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long in = i % inner, j = (i / inner) % n_idx, o = i / (inner * n_idx);
+    long long t = idx[j];
+    if (t < 0) t += n_dst;
+    if (t < 0 || t >= n_dst) { if (bad_flag) *bad_flag = 1; continue; }
+    dst[(o * n_dst + t) * inner + in] = fill;
+  }
+}
+}  // namespace
+
+extern "C" int b200_index_fill(void* dst, int elem_bytes, const long long* idx, long long outer, long long n_dst,
+                               long long n_idx, long long inner, unsigned long long fill_bits, int* bad_flag, void* stream) {
+  const long long total = outer * n_idx * inner;
+  if (total <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int grid = grid_for(total, 256);
+  switch (elem_bytes) {
+    case 1: index_fill_kernel<unsigned char><<<grid, 256, 0, s>>>((unsigned char*)dst, idx, outer, n_dst, n_idx, inner, (unsigned char)fill_bits, bad_flag); break;
+    case 2: index_fill_kernel<unsigned short><<<grid, 256, 0, s>>>((unsigned short*)dst, idx, outer, n_dst, n_idx, inner, (unsigned short)fill_bits, bad_flag); break;
+    case 4: index_fill_kernel<unsigned><<<grid, 256, 0, s>>>((unsigned*)dst, idx, outer, n_dst, n_idx, inner, (unsigned)fill_bits, bad_flag); break;
+    case 8: index_fill_kernel<unsigned long long><<<grid, 256, 0, s>>>((unsigned long long*)dst, idx, outer, n_dst, n_idx, inner, fill_bits, bad_flag); break;
+    default: return (int)cudaErrorInvalidValue;
+  }
+  return (int)cudaGetLastError();
+}
+
 extern "C" int b200_sort_rows_max_len(void) { return kSortMax; }
 // Sorts each of `rows` rows of `len` (<= 4096) elements; writes the first k sorted values (dtype of x)
 // and their int64 positions.  Ties keep the lower position first.

@@ -111,7 +111,7 @@ B200_API int b200_gemm(const B200GemmParams* p, void* stream);
 // parity.  The same kernel serves the data gradient (input = dy, flipped weights,
 // optional strided output addressing).
 #define B200_CONV_MAX_TAPS 49
-#define B200_CONV_MAX_MAPS 4
+#define B200_CONV_MAX_MAPS 16   // input views: one per parity of a stride up to 4 x 4
 typedef struct B200ConvTap {
   short dh, dw;   // offset added to the tile's (h, w) origin in the tap's view
   short map;      // which input view
@@ -263,6 +263,26 @@ B200_API int b200_avgpool2d_bwd(const B200PoolParams* p, const void* dy, void* d
 // adaptive average pooling: windows [floor(i*H/P), ceil((i+1)*H/P))
 B200_API int b200_adaptive_avgpool2d_fwd(const B200PoolParams* p, const void* x, void* y, void* stream);
 B200_API int b200_adaptive_avgpool2d_bwd(const B200PoolParams* p, const void* dy, void* dx, void* stream);
+
+// ---- pooling over three spatial dimensions (pooling3d.cu) ------------------------------------
+// One parameter block for max / average / adaptive-average / adaptive-max pooling of a 5-D tensor
+// (N, C, D, H, W); 2-D adaptive max pooling uses it with D = 1.  Indices are flattened (d*H + h)*W + w.
+typedef struct B200Pool3Params {
+  int N, C;
+  int in[3], out[3];      // D, H, W and their pooled extents
+  int k[3], s[3], p[3], dil[3];
+  long long in_s[5];      // element strides of N, C, D, H, W
+  long long out_s[5];
+  int channels_last;      // iterate with C fastest
+  int dtype;
+  int is_max;             // 1 = max (with indices), 0 = average
+  int adaptive;           // windows [floor(o*I/O), ceil((o+1)*I/O)) instead of kernel / stride / padding
+  int count_include_pad;
+  int divisor_override;   // 0 = none
+} B200Pool3Params;
+B200_API int b200_pool3d_fwd(const B200Pool3Params* p, const void* x, void* y, long long* indices /* max only */, void* stream);
+B200_API int b200_pool3d_bwd(const B200Pool3Params* p, const void* dy, const long long* indices /* max only */, void* dx,
+                             void* stream);
 
 // ---- softmax / losses over contiguous rows ---------------------------------------------------
 B200_API int b200_softmax_fwd(const void* x, int in_dtype, void* y, int out_dtype, long long rows, int cols, int log_mode,
@@ -445,6 +465,18 @@ B200_API int b200_tri(const void* in, void* out, int elem_bytes, long long batch
 B200_API int b200_sort_rows_max_len(void);
 B200_API int b200_sort_rows(const void* x, int dtype, int elem_bytes, long long rows, int len, int descending, int k,
                             void* values, long long* indices, void* stream);
+// Rows of any length and any orderable dtype (sort_scan.cu): `workspace` holds b200_sort_long_workspace_bytes
+// bytes; values / indices may be null; equal keys keep their order; NaN sorts as the largest value.
+B200_API long long b200_sort_long_workspace_bytes(long long rows, long long len);
+B200_API int b200_sort_long(const void* x, int dtype, int elem_bytes, long long rows, long long len, int descending,
+                            long long k, void* values, long long* indices, void* workspace, void* stream);
+// out[i] = in[0] + ... + in[i] over int64; workspace: b200_scan_workspace_elems(n) int64 values
+B200_API long long b200_scan_workspace_elems(long long n);
+B200_API int b200_inclusive_scan_i64(const long long* in, long long* out, long long n, long long* workspace, void* stream);
+// dst[o][idx[j]][:] = fill for dst of shape [outer][n_dst][inner] (elements of elem_bytes <= 8 bytes, value given as
+// its bit pattern); an index out of range sets *bad_flag and is skipped
+B200_API int b200_index_fill(void* dst, int elem_bytes, const long long* idx, long long outer, long long n_dst,
+                             long long n_idx, long long inner, unsigned long long fill_bits, int* bad_flag, void* stream);
 // mode 0 nearest, 1 bilinear; backward: `out` holds the output gradient and the input gradient is
 // accumulated into in_acc (zeroed fp32, contiguous NCHW).  sizes = {N, C, H, W, OH, OW}.
 B200_API int b200_resample2d(const void* in, void* out, int dtype, const long long* sizes, const long long* in_strides,

@@ -21,12 +21,38 @@ using at::Tensor;
 struct ConvGeom {
   int64_t N, C, H, W, K, R, S, P, Q;
   int64_t sh, sw, ph, pw;
+  int64_t dlh = 1, dlw = 1;  // dilation
 };
 
 inline int64_t floordiv(int64_t a, int64_t b) { return (a >= 0) ? a / b : -((-a + b - 1) / b); }
 inline int64_t ceildiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
-at::ScalarType compute_dtype(at::ScalarType t) { return t == at::kBFloat16 ? at::kBFloat16 : at::kHalf; }
+// Tensor-core operand type: 16-bit inputs run as they are.  fp32 inputs are split into two bf16 terms
+// (x = hi + lo, hi = bf16(x), lo = bf16(x - hi)) and a convolution becomes three tensor-core passes
+// hi*hi + lo*hi + hi*lo accumulated in fp32: bf16 has fp32's exponent range, so values above 65504 or below
+// 1e-7 survive, and the two terms carry 16 mantissa bits (more than a TF32 path would).
+at::ScalarType compute_dtype(at::ScalarType t) { return t == at::kHalf ? at::kHalf : at::kBFloat16; }
+struct Split {
+  Tensor hi, lo;  // lo is undefined for 16-bit sources
+};
+Split split_operand(const Tensor& x) {
+  Split s;
+  if (x.scalar_type() != at::kFloat) {
+    s.hi = x;
+    return s;
+  }
+  s.hi = x.to(at::kBFloat16);
+  s.lo = (x - s.hi.to(at::kFloat)).to(at::kBFloat16);
+  return s;
+}
+// The (a, b) operand pairs of the passes, the full-precision one last (it carries bias / activation).
+std::vector<std::pair<Tensor, Tensor>> split_passes(const Split& a, const Split& b) {
+  std::vector<std::pair<Tensor, Tensor>> v;
+  if (a.lo.defined()) v.emplace_back(a.lo, b.hi);
+  if (b.lo.defined()) v.emplace_back(a.hi, b.lo);
+  v.emplace_back(a.hi, b.hi);
+  return v;
+}
 
 // channels-last (dense NHWC) tensor of dtype `dt`
 Tensor to_nhwc(const Tensor& x, at::ScalarType dt) {
@@ -45,22 +71,27 @@ void check_supported(const Tensor& input, const Tensor& weight, at::IntArrayRef 
   TORCH_CHECK(input.dim() == 4 && weight.dim() == 4, "b200 conv: only 2-D convolutions run on the device");
   TORCH_CHECK(!transposed, "b200 conv: transposed convolution has no device kernel");
   TORCH_CHECK(groups == 1, "b200 conv: grouped convolution has no device kernel");
-  TORCH_CHECK(dilation[0] == 1 && dilation[1] == 1, "b200 conv: dilation has no device kernel");
-  TORCH_CHECK(stride[0] >= 1 && stride[0] <= 2 && stride[1] >= 1 && stride[1] <= 2, "b200 conv: stride must be 1 or 2");
+  TORCH_CHECK(dilation[0] >= 1 && dilation[1] >= 1, "b200 conv: invalid dilation");
+  TORCH_CHECK(stride[0] >= 1 && stride[0] <= 4 && stride[1] >= 1 && stride[1] <= 4, "b200 conv: strides above 4 have no device kernel");
+  TORCH_CHECK(weight.size(2) * weight.size(3) <= B200_CONV_MAX_TAPS, "b200 conv: filters with more than ", B200_CONV_MAX_TAPS,
+              " taps have no device kernel");
   const auto t = input.scalar_type();
   TORCH_CHECK(t == at::kBFloat16 || t == at::kHalf || t == at::kFloat, "b200 conv: unsupported dtype ", t);
   TORCH_CHECK(weight.size(0) % 8 == 0, "b200 conv: output channels must be a multiple of 8");
   const int64_t C = input.size(1);
-  TORCH_CHECK(C % 8 == 0 || (C <= 8 && weight.size(3) <= 8), "b200 conv: input channels must be a multiple of 8 (or <= 8)");
+  TORCH_CHECK(C % 8 == 0 || (C <= 8 && weight.size(3) <= 8 && dilation[0] == 1 && dilation[1] == 1 && stride[0] <= 2 && stride[1] <= 2),
+              "b200 conv: input channels must be a multiple of 8 (or <= 8 with an undilated filter of width <= 8 and stride <= 2)");
 }
 
-ConvGeom geom(const Tensor& input, const Tensor& weight, at::IntArrayRef stride, at::IntArrayRef padding) {
+ConvGeom geom(const Tensor& input, const Tensor& weight, at::IntArrayRef stride, at::IntArrayRef padding,
+              at::IntArrayRef dilation = {}) {
   ConvGeom g;
   g.N = input.size(0); g.C = input.size(1); g.H = input.size(2); g.W = input.size(3);
   g.K = weight.size(0); g.R = weight.size(2); g.S = weight.size(3);
   g.sh = stride[0]; g.sw = stride[1]; g.ph = padding[0]; g.pw = padding[1];
-  g.P = (g.H + 2 * g.ph - g.R) / g.sh + 1;
-  g.Q = (g.W + 2 * g.pw - g.S) / g.sw + 1;
+  if (dilation.size() == 2) { g.dlh = dilation[0]; g.dlw = dilation[1]; }
+  g.P = (g.H + 2 * g.ph - g.dlh * (g.R - 1) - 1) / g.sh + 1;
+  g.Q = (g.W + 2 * g.pw - g.dlw * (g.S - 1) - 1) / g.sw + 1;
   return g;
 }
 
@@ -72,7 +103,9 @@ void build_forward_taps(Params& p, const Tensor& x, const ConvGeom& g) {
   const int64_t x_sn = x.stride(0), x_sh = x.stride(2), x_sw = x.stride(3);
   const char* base = static_cast<const char*>(x.data_ptr());
   p.num_views = (int)(g.sh * g.sw);
-  bool view_ok[B200_CONV_MAX_MAPS] = {false, false, false, false};
+  TORCH_CHECK(p.num_views <= B200_CONV_MAX_MAPS, "b200 conv: stride ", g.sh, "x", g.sw, " needs more input views than the kernel has");
+  bool view_ok[B200_CONV_MAX_MAPS];
+  std::fill(view_ok, view_ok + B200_CONV_MAX_MAPS, false);
   for (int64_t a = 0; a < g.sh; ++a) {
     for (int64_t b = 0; b < g.sw; ++b) {
       const int idx = (int)(a * g.sw + b);
@@ -87,7 +120,7 @@ void build_forward_taps(Params& p, const Tensor& x, const ConvGeom& g) {
   p.ntaps = 0;
   for (int64_t r = 0; r < g.R; ++r) {
     for (int64_t s = 0; s < g.S; ++s) {
-      const int64_t oh = r - g.ph, ow = s - g.pw;
+      const int64_t oh = r * g.dlh - g.ph, ow = s * g.dlw - g.pw;
       const int64_t a = ((oh % g.sh) + g.sh) % g.sh, b = ((ow % g.sw) + g.sw) % g.sw;
       const int idx = (int)(a * g.sw + b);
       if (!view_ok[idx]) continue;
@@ -145,13 +178,10 @@ Tensor pack_stem_weight(const Tensor& weight, const ConvGeom& g, at::ScalarType 
   return wp;
 }
 
-Tensor forward_impl(const Tensor& input, const Tensor& weight, const std::optional<Tensor>& bias, const ConvGeom& g,
-                    const float* scale, const Tensor* residual, int act, at::ScalarType out_dtype,
-                    double* stats = nullptr) {
-  const at::ScalarType dt = compute_dtype(input.scalar_type());
-  OpScope scope("conv_fprop", input);
-  Tensor out = empty_b200({g.N, g.K, g.P, g.Q}, out_dtype, input.device().index(), at::MemoryFormat::ChannelsLast);
-  if (out.numel() == 0) return out;
+// One tensor-core pass: out = act((x * w) * scale + bias + residual); x and w are 16-bit tensors of one dtype.
+void forward_pass(const Tensor& input, const Tensor& weight, const Tensor* bias, const ConvGeom& g, const float* scale,
+                  const Tensor* residual, int act, Tensor& out, double* stats, const OpScope& scope) {
+  const at::ScalarType dt = input.scalar_type();
   B200ConvParams p;
   std::memset(&p, 0, sizeof(p));
   Tensor x, w;
@@ -175,91 +205,116 @@ Tensor forward_impl(const Tensor& input, const Tensor& weight, const std::option
   }
   p.N = (int)g.N; p.P = (int)g.P; p.Q = (int)g.Q; p.Cout = (int)g.K;
   p.ab_dtype = to_b200_dtype(dt);
-  p.out = out.data_ptr(); p.out_dtype = to_b200_dtype(out_dtype);
+  p.out = out.data_ptr(); p.out_dtype = to_b200_dtype(out.scalar_type());
   p.o_sn = out.stride(0); p.o_sh = out.stride(2); p.o_sw = out.stride(3);
   p.o_mul_h = 1; p.o_mul_w = 1;
   p.scale = scale;
   Tensor b;
-  if (bias.has_value() && bias->defined()) {
+  if (bias) {
     b = bias->contiguous();
     p.bias = b.data_ptr();
     p.bias_dtype = to_b200_dtype(b.scalar_type());
   }
-  Tensor res;
   if (residual) {
-    res = to_nhwc(*residual, residual->scalar_type());
-    TORCH_CHECK(res.sizes() == out.sizes(), "conv residual shape mismatch");
-    p.residual = res.data_ptr();
-    p.res_dtype = to_b200_dtype(res.scalar_type());
+    TORCH_CHECK(residual->sizes() == out.sizes() && residual->strides() == out.strides(), "conv residual layout mismatch");
+    p.residual = residual->data_ptr();
+    p.res_dtype = to_b200_dtype(residual->scalar_type());
   }
   p.act = act;
   p.stats = stats;
   TORCH_CHECK(p.ntaps > 0, "b200 conv: empty tap list");
   B200_KERNEL_CHECK(b200_conv_fprop(&p, scope.stream()));
+}
+
+Tensor forward_impl(const Tensor& input, const Tensor& weight, const std::optional<Tensor>& bias, const ConvGeom& g,
+                    const float* scale, const Tensor* residual, int act, at::ScalarType out_dtype,
+                    double* stats = nullptr) {
+  OpScope scope("conv_fprop", input);
+  Tensor out = empty_b200({g.N, g.K, g.P, g.Q}, out_dtype, input.device().index(), at::MemoryFormat::ChannelsLast);
+  if (out.numel() == 0) return out;
+  const at::ScalarType dt = compute_dtype(input.scalar_type());
+  Tensor res;
+  if (residual) {
+    res = to_nhwc(*residual, residual->scalar_type());
+    TORCH_CHECK(res.sizes() == out.sizes(), "conv residual shape mismatch");
+  }
+  const Tensor* bptr = (bias.has_value() && bias->defined()) ? &*bias : nullptr;
+  if (input.scalar_type() != at::kFloat) {
+    Tensor w = weight.scalar_type() == dt ? weight : weight.to(dt);
+    forward_pass(input, w, bptr, g, scale, residual ? &res : nullptr, act, out, stats, scope);
+    return out;
+  }
+  // fp32: three bf16 passes accumulated through the epilogue's residual input; the per-channel scale applies to
+  // every partial sum, bias / activation (and a caller's residual, added first) only once
+  TORCH_CHECK(!stats && out_dtype == at::kFloat, "b200 conv: fp32 inputs produce fp32 outputs without channel statistics");
+  auto passes = split_passes(split_operand(input), split_operand(weight.to(at::kFloat)));
+  for (size_t i = 0; i < passes.size(); ++i) {
+    const bool first = i == 0, last = i + 1 == passes.size();
+    const Tensor* r = first ? (residual ? &res : nullptr) : &out;
+    forward_pass(passes[i].first, passes[i].second, last ? bptr : nullptr, g, scale, r, last ? act : 0, out, nullptr, scope);
+  }
   return out;
 }
 
-// fp32 gradients are computed on fp16 tensor cores; a power-of-two scale moves
-// them into fp16's normal range first (gradients of a mean-reduced loss are tiny)
-// and is divided out again in the epilogue.
-double fp16_safe_scale(const Tensor& grad) {
-  if (grad.scalar_type() != at::kFloat || grad.numel() == 0) return 1.0;
-  const double amax = grad.abs().max().item<double>();
-  if (!(amax > 0.0) || !std::isfinite(amax)) return 1.0;
-  return std::exp2(std::floor(std::log2(1024.0 / amax)));
-}
-
 Tensor dgrad_impl(const Tensor& grad_in, const Tensor& weight, const ConvGeom& g, at::ScalarType out_dtype) {
-  const at::ScalarType dt = compute_dtype(grad_in.scalar_type());
-  const double gscale = fp16_safe_scale(grad_in);
-  const Tensor grad = gscale == 1.0 ? grad_in : grad_in * gscale;
-  OpScope scope("conv_dgrad", grad);
-  Tensor dx = empty_b200({g.N, g.C, g.H, g.W}, out_dtype, grad.device().index(), at::MemoryFormat::ChannelsLast);
+  OpScope scope("conv_dgrad", grad_in);
+  Tensor dx = empty_b200({g.N, g.C, g.H, g.W}, out_dtype, grad_in.device().index(), at::MemoryFormat::ChannelsLast);
   if (dx.numel() == 0) return dx;
-  Tensor dy = to_nhwc(grad, dt);
-  Tensor w = to_nhwc(weight, dt);
-  bool need_zero = false;
-  struct Launch { B200ConvParams p; };
-  std::vector<B200ConvParams> launches;
-  for (int64_t a = 0; a < g.sh; ++a) {
-    for (int64_t b = 0; b < g.sw; ++b) {
-      const int64_t Pa = ceildiv(g.H - a, g.sh), Qb = ceildiv(g.W - b, g.sw);
-      if (Pa <= 0 || Qb <= 0) continue;
-      B200ConvParams p;
-      std::memset(&p, 0, sizeof(p));
-      p.ntaps = 0;
-      for (int64_t r = 0; r < g.R; ++r) {
-        if ((a + g.ph - r) % g.sh != 0) continue;
-        for (int64_t s = 0; s < g.S; ++s) {
-          if ((b + g.pw - s) % g.sw != 0) continue;
-          B200ConvTap& t = p.taps[p.ntaps++];
-          t.dh = (short)floordiv(a + g.ph - r, g.sh);
-          t.dw = (short)floordiv(b + g.pw - s, g.sw);
-          t.map = 0;
-          t.wtap = (short)(r * g.S + s);
+  const bool fp32 = grad_in.scalar_type() == at::kFloat;
+  const at::ScalarType dt = compute_dtype(grad_in.scalar_type());
+  TORCH_CHECK(!fp32 || out_dtype == at::kFloat, "b200 conv dgrad: fp32 gradients produce fp32 input gradients");
+  auto passes = fp32 ? split_passes(split_operand(grad_in), split_operand(weight.to(at::kFloat)))
+                     : std::vector<std::pair<Tensor, Tensor>>{{grad_in, weight.scalar_type() == dt ? weight : weight.to(dt)}};
+  bool zeroed = false;
+  for (size_t pass = 0; pass < passes.size(); ++pass) {
+    Tensor dy = to_nhwc(passes[pass].first, dt);
+    Tensor w = to_nhwc(passes[pass].second, dt);
+    bool need_zero = false;
+    std::vector<B200ConvParams> launches;
+    for (int64_t a = 0; a < g.sh; ++a) {
+      for (int64_t b = 0; b < g.sw; ++b) {
+        const int64_t Pa = ceildiv(g.H - a, g.sh), Qb = ceildiv(g.W - b, g.sw);
+        if (Pa <= 0 || Qb <= 0) continue;
+        B200ConvParams p;
+        std::memset(&p, 0, sizeof(p));
+        p.ntaps = 0;
+        for (int64_t r = 0; r < g.R; ++r) {
+          if ((a + g.ph - r * g.dlh) % g.sh != 0) continue;
+          for (int64_t s = 0; s < g.S; ++s) {
+            if ((b + g.pw - s * g.dlw) % g.sw != 0) continue;
+            B200ConvTap& t = p.taps[p.ntaps++];
+            t.dh = (short)floordiv(a + g.ph - r * g.dlh, g.sh);
+            t.dw = (short)floordiv(b + g.pw - s * g.dlw, g.sw);
+            t.map = 0;
+            t.wtap = (short)(r * g.S + s);
+          }
         }
+        if (p.ntaps == 0) { need_zero = true; continue; }
+        p.N = (int)g.N; p.P = (int)Pa; p.Q = (int)Qb;
+        p.Cin = (int)g.K; p.Cout = (int)g.C;
+        p.ab_dtype = to_b200_dtype(dt);
+        p.num_views = 1;
+        p.views[0].base = dy.data_ptr();
+        p.views[0].dims[0] = g.K; p.views[0].dims[1] = g.Q; p.views[0].dims[2] = g.P; p.views[0].dims[3] = g.N;
+        p.views[0].strides[0] = dy.stride(3); p.views[0].strides[1] = dy.stride(2); p.views[0].strides[2] = dy.stride(0);
+        p.weight = w.data_ptr();
+        // element (tap, n = ci, k = co) of the channels-last filter [K][R][S][C]
+        p.w_stride_n = 1; p.w_stride_k = g.R * g.S * g.C; p.w_stride_tap = g.C;
+        p.wtaps = (int)(g.R * g.S);
+        p.out = dx.data_ptr(); p.out_dtype = to_b200_dtype(out_dtype);
+        p.o_sn = dx.stride(0); p.o_sh = dx.stride(2); p.o_sw = dx.stride(3);
+        p.o_mul_h = (int)g.sh; p.o_off_h = (int)a; p.o_mul_w = (int)g.sw; p.o_off_w = (int)b;
+        p.alpha = 1.f;
+        if (pass > 0) {  // later passes add to what the earlier ones wrote
+          p.residual = dx.data_ptr();
+          p.res_dtype = to_b200_dtype(out_dtype);
+        }
+        launches.push_back(p);
       }
-      if (p.ntaps == 0) { need_zero = true; continue; }
-      p.N = (int)g.N; p.P = (int)Pa; p.Q = (int)Qb;
-      p.Cin = (int)g.K; p.Cout = (int)g.C;
-      p.ab_dtype = to_b200_dtype(dt);
-      p.num_views = 1;
-      p.views[0].base = dy.data_ptr();
-      p.views[0].dims[0] = g.K; p.views[0].dims[1] = g.Q; p.views[0].dims[2] = g.P; p.views[0].dims[3] = g.N;
-      p.views[0].strides[0] = dy.stride(3); p.views[0].strides[1] = dy.stride(2); p.views[0].strides[2] = dy.stride(0);
-      p.weight = w.data_ptr();
-      // element (tap, n = ci, k = co) of the channels-last filter [K][R][S][C]
-      p.w_stride_n = 1; p.w_stride_k = g.R * g.S * g.C; p.w_stride_tap = g.C;
-      p.wtaps = (int)(g.R * g.S);
-      p.out = dx.data_ptr(); p.out_dtype = to_b200_dtype(out_dtype);
-      p.o_sn = dx.stride(0); p.o_sh = dx.stride(2); p.o_sw = dx.stride(3);
-      p.o_mul_h = (int)g.sh; p.o_off_h = (int)a; p.o_mul_w = (int)g.sw; p.o_off_w = (int)b;
-      p.alpha = (float)(1.0 / gscale);
-      launches.push_back(p);
     }
+    if (need_zero && !zeroed) { dx.zero_(); zeroed = true; }
+    for (auto& p : launches) B200_KERNEL_CHECK(b200_conv_fprop(&p, scope.stream()));
   }
-  if (need_zero) dx.zero_();
-  for (auto& p : launches) B200_KERNEL_CHECK(b200_conv_fprop(&p, scope.stream()));
   return dx;
 }
 
@@ -269,42 +324,43 @@ Tensor dgrad_impl(const Tensor& grad_in, const Tensor& weight, const ConvGeom& g
 // kernel adds its result to, e.g. a view of a flat gradient bucket; nothing is returned then.
 Tensor wgrad_impl(const Tensor& grad_in, const Tensor& input, const Tensor& weight, const ConvGeom& g,
                   bool fp32_result = false, const Tensor* accum_into = nullptr) {
-  const at::ScalarType dt = compute_dtype(grad_in.scalar_type());
-  const double gscale = fp16_safe_scale(grad_in);
-  const Tensor grad = gscale == 1.0 ? grad_in : grad_in * gscale;
-  OpScope scope("conv_wgrad", grad);
-  Tensor dy = to_nhwc(grad, dt);
-  B200ConvWgradParams p;
-  std::memset(&p, 0, sizeof(p));
-  Tensor x;
-  StemPack sp;
+  OpScope scope("conv_wgrad", grad_in);
+  const bool fp32 = grad_in.scalar_type() == at::kFloat || input.scalar_type() == at::kFloat;
+  const at::ScalarType dt = compute_dtype(fp32 ? at::kFloat : grad_in.scalar_type());
   const bool stem = g.C % 8 != 0 || g.C < 8;
-  int64_t cin_k, wtaps;
-  if (stem) {
-    sp = pack_stem_input(input, g, dt, scope);
-    build_stem_taps(p, sp, g);
-    cin_k = 64; wtaps = g.R;
-  } else {
-    x = to_nhwc(input, dt);
-    build_forward_taps(p, x, g);
-    cin_k = g.C; wtaps = g.R * g.S;
-  }
-  const bool direct = accum_into && !stem && gscale == 1.0;
+  const int64_t cin_k = stem ? 64 : g.C, wtaps = stem ? g.R : g.R * g.S;
+  const bool direct = accum_into && !stem;
   Tensor acc;
   if (direct) {
     TORCH_CHECK(accum_into->scalar_type() == at::kFloat && accum_into->numel() == g.K * wtaps * cin_k,
                 "conv wgrad: the accumulation target must be fp32 with the weight's number of elements");
     acc = *accum_into;
   } else {
-    acc = at::zeros({g.K, wtaps * cin_k}, grad.options().dtype(at::kFloat));
+    acc = at::zeros({g.K, wtaps * cin_k}, grad_in.options().dtype(at::kFloat));
   }
-  p.N = (int)g.N; p.P = (int)g.P; p.Q = (int)g.Q; p.Cin = (int)cin_k; p.Cout = (int)g.K;
-  p.ab_dtype = to_b200_dtype(dt);
-  p.dy = dy.data_ptr();
-  p.dy_sn = dy.stride(0); p.dy_sh = dy.stride(2); p.dy_sw = dy.stride(3);
-  p.dw_acc = acc.data_ptr<float>();
-  p.wtaps = (int)wtaps;
-  if (p.ntaps > 0) B200_KERNEL_CHECK(b200_conv_wgrad(&p, scope.stream()));
+  auto passes = fp32 ? split_passes(split_operand(grad_in.to(at::kFloat)), split_operand(input.to(at::kFloat)))
+                     : std::vector<std::pair<Tensor, Tensor>>{{grad_in, input.scalar_type() == dt ? input : input.to(dt)}};
+  for (auto& pr : passes) {
+    Tensor dy = to_nhwc(pr.first, dt);
+    B200ConvWgradParams p;
+    std::memset(&p, 0, sizeof(p));
+    Tensor x;
+    StemPack sp;
+    if (stem) {
+      sp = pack_stem_input(pr.second, g, dt, scope);
+      build_stem_taps(p, sp, g);
+    } else {
+      x = to_nhwc(pr.second, dt);
+      build_forward_taps(p, x, g);
+    }
+    p.N = (int)g.N; p.P = (int)g.P; p.Q = (int)g.Q; p.Cin = (int)cin_k; p.Cout = (int)g.K;
+    p.ab_dtype = to_b200_dtype(dt);
+    p.dy = dy.data_ptr();
+    p.dy_sn = dy.stride(0); p.dy_sh = dy.stride(2); p.dy_sw = dy.stride(3);
+    p.dw_acc = acc.data_ptr<float>();
+    p.wtaps = (int)wtaps;
+    if (p.ntaps > 0) B200_KERNEL_CHECK(b200_conv_wgrad(&p, scope.stream()));
+  }
   if (direct) return Tensor();
   Tensor dw;
   if (stem) {
@@ -314,14 +370,14 @@ Tensor wgrad_impl(const Tensor& grad_in, const Tensor& input, const Tensor& weig
     // acc [K][R][S][C] is the channels-last memory of a [K, C, R, S] tensor
     dw = acc.view({g.K, g.R, g.S, g.C}).permute({0, 3, 1, 2});
   }
-  if (accum_into) {  // the kernel could not add in place (first-layer packing or a rescaled gradient)
+  if (accum_into) {  // the first-layer packing cannot add in place
     at::Tensor target = accum_into->dim() == 4 ? *accum_into : accum_into->view({g.K, g.R, g.S, g.C}).permute({0, 3, 1, 2});
-    target.add_(gscale == 1.0 ? dw : dw * (1.0 / gscale));
+    target.add_(dw);
     return Tensor();
   }
-  if (fp32_result) return gscale == 1.0 ? dw : dw * (1.0 / gscale);
+  if (fp32_result) return dw;
   Tensor out = at::empty_like(weight, weight.options(), weight.suggest_memory_format());
-  out.copy_(gscale == 1.0 ? dw : dw * (1.0 / gscale));
+  out.copy_(dw);
   return out;
 }
 
@@ -388,14 +444,15 @@ std::tuple<Tensor, Tensor, Tensor> depthwise_backward(const Tensor& grad_in, con
 
 // ---- transposed convolution = the data gradient of the matching forward convolution ----
 ConvGeom transposed_geom(const Tensor& input, const Tensor& weight, at::IntArrayRef stride, at::IntArrayRef padding,
-                         at::IntArrayRef output_padding) {
+                         at::IntArrayRef output_padding, at::IntArrayRef dilation) {
   // weight [Cin, Cout, R, S]; the matching forward convolution maps [N, Cout, Hout, Wout] -> [N, Cin, H, W]
   ConvGeom g;
   g.N = input.size(0); g.K = weight.size(0); g.C = weight.size(1); g.R = weight.size(2); g.S = weight.size(3);
   g.sh = stride[0]; g.sw = stride[1]; g.ph = padding[0]; g.pw = padding[1];
   g.P = input.size(2); g.Q = input.size(3);
-  g.H = (g.P - 1) * g.sh - 2 * g.ph + g.R + (output_padding.empty() ? 0 : output_padding[0]);
-  g.W = (g.Q - 1) * g.sw - 2 * g.pw + g.S + (output_padding.empty() ? 0 : output_padding[1]);
+  if (dilation.size() == 2) { g.dlh = dilation[0]; g.dlw = dilation[1]; }
+  g.H = (g.P - 1) * g.sh - 2 * g.ph + g.dlh * (g.R - 1) + 1 + (output_padding.empty() ? 0 : output_padding[0]);
+  g.W = (g.Q - 1) * g.sw - 2 * g.pw + g.dlw * (g.S - 1) + 1 + (output_padding.empty() ? 0 : output_padding[1]);
   return g;
 }
 
@@ -405,12 +462,13 @@ at::Tensor conv_forward_device(const at::Tensor& input, const at::Tensor& weight
                                at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation,
                                bool transposed, at::IntArrayRef output_padding, int64_t groups) {
   if (transposed) {
-    TORCH_CHECK(groups == 1 && input.dim() == 4 && weight.dim() == 4 && dilation[0] == 1 && dilation[1] == 1,
-                "b200 transposed conv: only dense 2-D transposed convolutions without dilation run on the device");
-    TORCH_CHECK(stride[0] >= 1 && stride[0] <= 2 && stride[1] >= 1 && stride[1] <= 2, "b200 conv: stride must be 1 or 2");
+    TORCH_CHECK(groups == 1 && input.dim() == 4 && weight.dim() == 4,
+                "b200 transposed conv: only dense 2-D transposed convolutions run on the device");
+    TORCH_CHECK(stride[0] >= 1 && stride[0] <= 4 && stride[1] >= 1 && stride[1] <= 4, "b200 conv: strides above 4 have no device kernel");
+    TORCH_CHECK(weight.size(2) * weight.size(3) <= B200_CONV_MAX_TAPS, "b200 conv: too many filter taps for the device kernel");
     TORCH_CHECK(input.size(1) == weight.size(0), "conv_transpose: channel mismatch");
     TORCH_CHECK(weight.size(0) % 8 == 0 && weight.size(1) % 8 == 0, "b200 transposed conv: channel counts must be multiples of 8");
-    ConvGeom g = transposed_geom(input, weight, stride, padding, output_padding);
+    ConvGeom g = transposed_geom(input, weight, stride, padding, output_padding, dilation);
     TORCH_CHECK(g.H > 0 && g.W > 0, "conv_transpose: output size is too small");
     at::Tensor out = dgrad_impl(input, weight, g, input.scalar_type());
     if (bias.has_value() && bias->defined()) out.add_(bias->view({1, -1, 1, 1}));
@@ -437,7 +495,7 @@ at::Tensor conv_forward_device(const at::Tensor& input, const at::Tensor& weight
   }
   check_supported(input, weight, stride, padding, dilation, transposed, groups);
   TORCH_CHECK(input.size(1) == weight.size(1), "conv: channel mismatch");
-  ConvGeom g = geom(input, weight, stride, padding);
+  ConvGeom g = geom(input, weight, stride, padding, dilation);
   TORCH_CHECK(g.P > 0 && g.Q > 0, "conv: output size is too small");
   return forward_impl(input, weight, bias, g, nullptr, nullptr, 0, input.scalar_type());
 }
@@ -447,10 +505,12 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> conv_backward_device(
     at::IntArrayRef padding, at::IntArrayRef dilation, bool transposed, at::IntArrayRef output_padding, int64_t groups,
     std::array<bool, 3> mask) {
   if (transposed) {
-    TORCH_CHECK(groups == 1 && dilation[0] == 1 && dilation[1] == 1 && input.dim() == 4,
+    TORCH_CHECK(groups == 1 && input.dim() == 4,
                 "b200 transposed conv backward: only dense 2-D transposed convolutions run on the device");
+    TORCH_CHECK(stride[0] <= 4 && stride[1] <= 4 && weight.size(2) * weight.size(3) <= B200_CONV_MAX_TAPS,
+                "b200 transposed conv backward: stride / filter size has no device kernel");
     TORCH_CHECK(weight.size(0) % 8 == 0 && weight.size(1) % 8 == 0, "b200 transposed conv: channel counts must be multiples of 8");
-    ConvGeom g = transposed_geom(input, weight, stride, padding, output_padding);
+    ConvGeom g = transposed_geom(input, weight, stride, padding, output_padding, dilation);
     TORCH_CHECK(g.H == grad.size(2) && g.W == grad.size(3), "conv_transpose backward: gradient shape mismatch");
     at::Tensor dx, dw, db;
     // d(input) is the forward convolution of the output gradient; d(weight) is the weight gradient of
@@ -480,7 +540,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> conv_backward_device(
     return {dx, dw, db};
   }
   check_supported(input, weight, stride, padding, dilation, transposed, groups);
-  ConvGeom g = geom(input, weight, stride, padding);
+  ConvGeom g = geom(input, weight, stride, padding, dilation);
   at::Tensor dx, dw, db;
   if (mask[0]) {
     TORCH_CHECK(g.C % 8 == 0, "b200 conv dgrad: input channels must be a multiple of 8");
@@ -498,7 +558,7 @@ at::Tensor conv_bn_act_device(const at::Tensor& input, const at::Tensor& weight,
                               at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation, int64_t groups,
                               int64_t act) {
   check_supported(input, weight, stride, padding, dilation, false, groups);
-  ConvGeom g = geom(input, weight, stride, padding);
+  ConvGeom g = geom(input, weight, stride, padding, dilation);
   at::Tensor sc;
   const float* scp = nullptr;
   if (scale.has_value() && scale->defined()) {

@@ -291,11 +291,10 @@ Tensor& k_triu_(Tensor& self, int64_t k) { self.copy_(k_triu(self, k)); return s
 // ---- sort / topk -------------------------------------------------------------------------
 std::tuple<Tensor, Tensor> sort_rows_device(const Tensor& self, int64_t dim, bool descending, int64_t k, const char* name) {
   const auto t = self.scalar_type();
-  TORCH_CHECK(float_type(t) || t == at::kByte || t == at::kChar || t == at::kBool, "b200 ", name, ": dtype ", t, " has no device kernel");
+  TORCH_CHECK(to_b200_dtype(t) >= 0 && !self.is_complex(), "b200 ", name, ": dtype ", t, " has no device kernel");
   Tensor x0 = self.dim() == 0 ? self.unsqueeze(0) : self;
   dim = at::maybe_wrap_dim(dim, x0.dim());
   const int64_t len = x0.size(dim);
-  TORCH_CHECK(len <= b200_sort_rows_max_len(), "b200 ", name, ": rows longer than ", b200_sort_rows_max_len(), " elements have no device kernel");
   if (k < 0) k = len;
   TORCH_CHECK(k <= len, name, ": k out of range");
   OpScope scope(name, self);
@@ -305,9 +304,19 @@ std::tuple<Tensor, Tensor> sort_rows_device(const Tensor& self, int64_t dim, boo
   Tensor values = empty_b200(shape, t, self.device().index());
   Tensor indices = empty_b200(shape, at::kLong, self.device().index());
   const int64_t rows = len ? x.numel() / len : 0;
-  if (rows > 0 && k > 0)
-    B200_KERNEL_CHECK(b200_sort_rows(x.data_ptr(), to_b200_dtype(t), (int)x.element_size(), rows, (int)len, descending ? 1 : 0, (int)k,
-                                     values.data_ptr(), i64ptr(indices), scope.stream()));
+  // short rows of types that fit a float key: one shared-memory bitonic sort per row; everything else
+  // (long rows, 64-bit keys, integers that a float cannot hold): the multi-pass sort over a workspace
+  const bool small = len <= b200_sort_rows_max_len() && (float_type(t) || t == at::kByte || t == at::kChar || t == at::kBool);
+  if (rows > 0 && k > 0) {
+    if (small) {
+      B200_KERNEL_CHECK(b200_sort_rows(x.data_ptr(), to_b200_dtype(t), (int)x.element_size(), rows, (int)len, descending ? 1 : 0, (int)k,
+                                       values.data_ptr(), i64ptr(indices), scope.stream()));
+    } else {
+      Workspace ws((size_t)b200_sort_long_workspace_bytes(rows, len), scope);
+      B200_KERNEL_CHECK(b200_sort_long(x.data_ptr(), to_b200_dtype(t), (int)x.element_size(), rows, len, descending ? 1 : 0, k,
+                                       values.data_ptr(), i64ptr(indices), ws.get(), scope.stream()));
+    }
+  }
   values = values.movedim(-1, dim);
   indices = indices.movedim(-1, dim);
   if (self.dim() == 0) return {values.squeeze(0), indices.squeeze(0)};
