@@ -226,7 +226,7 @@ def run_stock(args, rank, local_rank, world, store, sampler):
         identical = all(bool((w == allw[0]).all()) for w in allw)
     res = {"value": round(world * B * args.steps / (ms / 1e3), 1), "ms_per_step": round(ms / args.steps, 3),
            "e2e_value": round(world * B * args.steps / (ms_e2e / 1e3), 1), "e2e_ms_per_step": round(ms_e2e / args.steps, 3),
-           "final_loss": float(loss), "params_identical_across_ranks": identical,
+           "final_loss": float(loss.detach()), "params_identical_across_ranks": identical,
            "clocks": sampler.summary(t0, t1) if sampler is not None else {},
            "stack": f"torch {torch.__version__}, cuDNN {torch.backends.cudnn.version()}, NCCL "
                     f"{'.'.join(map(str, torch.cuda.nccl.version()))}, SGD(fused=True), channels_last, cudnn.benchmark"}

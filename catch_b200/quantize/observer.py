@@ -1,7 +1,8 @@
 """Observers that collect activation / weight ranges during calibration.
 
 Parity: torch_mlu/core/quantized/observer.py:72-322 (abs-max with optional running
-average and ``data_scale``, per-channel abs-max, a norm-based variant, a no-op).  The
+average and ``data_scale``, per-channel abs-max, a norm-based variant, the squared-range
+observer for LRN inputs, a no-op).  The
 scale convention is the reference's: ``scale = qmax / absmax`` with qmax 127 (int8) or
 32767 (int16).
 """
@@ -45,7 +46,18 @@ class MinMaxObserver(ObserverBase):
         return x
 
     def scale(self) -> torch.Tensor:
-        amax = (self.absmax / self.data_scale).clamp_min(1e-12)
+        # data_scale multiplies the observed range, as in the reference (observer.py:154-155): a value
+        # above one widens the range and lowers the scale
+        amax = (self.absmax * self.data_scale).clamp_min(1e-12)
+        return (self.qmax / amax).reshape(1)
+
+
+class LrnObserver(MinMaxObserver):
+    """Range observer for the input of a local-response normalisation: the layer squares its input, so the
+    scale is taken from the squared extremes (reference: MLULrnObserver, observer.py:172-200)."""
+
+    def scale(self) -> torch.Tensor:
+        amax = ((self.absmax * self.data_scale) ** 2).clamp_min(1e-12)
         return (self.qmax / amax).reshape(1)
 
 

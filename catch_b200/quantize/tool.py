@@ -13,9 +13,10 @@ Same flow and signature as the reference's ``quantize_dynamic_mlu``
     infer.load_state_dict(sd)
     infer.to("blackwell")(x)          # int8 tcgen05 convolutions / linears
 
-qconfig keys: ``iteration``, ``use_avg``, ``data_scale``, ``per_channel``, ``method``
-("minmax" or "norm"); ``mixed_layer`` maps module names to "float" to keep them
-unquantized (e.g. the 3-channel first convolution).
+qconfig keys (the reference's, torch_mlu/core/quantized/qscheme.py:11-19): ``iteration``, ``use_avg``,
+``data_scale``, ``per_channel``, ``method`` ("minmax", "norm" or "lrn"), ``firstconv`` with ``mean`` / ``std``
+(per-channel values in [0, 1]; the first ``Conv2d`` then normalises raw 0..255 inputs itself at inference
+time); ``mixed_layer`` maps module names to "float" to keep them unquantized.
 """
 from __future__ import annotations
 
@@ -25,10 +26,10 @@ from typing import Dict, Optional
 import torch
 import torch.nn as nn
 
-from .modules import QuantConv2d, QuantLinear
-from .observer import MinMaxObserver, NormObserver
+from .modules import _FIRSTCONV_ERROR, QuantConv1d, QuantConv2d, QuantConv3d, QuantLinear, QuantModule
+from .observer import LrnObserver, MinMaxObserver, NormObserver
 
-DEFAULT_MODULE_MAPPING = {nn.Conv2d: QuantConv2d, nn.Linear: QuantLinear}
+DEFAULT_MODULE_MAPPING = {nn.Conv1d: QuantConv1d, nn.Conv2d: QuantConv2d, nn.Conv3d: QuantConv3d, nn.Linear: QuantLinear}
 
 
 def _layer_qconfig(qconfig_spec: Optional[dict], dtype: Optional[str]) -> dict:
@@ -39,6 +40,9 @@ def _layer_qconfig(qconfig_spec: Optional[dict], dtype: Optional[str]) -> dict:
     method = cfg.get("method", "minmax")
     if method == "norm":
         cfg["activation_observer_factory"] = lambda: NormObserver(cfg["dtype"])
+    elif method == "lrn":
+        cfg["activation_observer_factory"] = lambda: LrnObserver(cfg["dtype"], cfg.get("use_avg", False),
+                                                                cfg.get("data_scale", 1.0), cfg.get("iteration", 1))
     elif method == "minmax":
         cfg["activation_observer_factory"] = lambda: MinMaxObserver(cfg["dtype"], cfg.get("use_avg", False),
                                                                    cfg.get("data_scale", 1.0), cfg.get("iteration", 1))
@@ -47,21 +51,44 @@ def _layer_qconfig(qconfig_spec: Optional[dict], dtype: Optional[str]) -> dict:
     return cfg
 
 
-def _convert(module: nn.Module, mapping: Dict, cfg: dict, gen_quant: bool, mixed_layer: Optional[dict], prefix: str = ""):
+def _first_conv_setup(q: QuantModule, cfg: dict, state: dict) -> None:
+    """The first Conv2d met during conversion takes the qconfig's mean / std (reference: conv.py:203-247)."""
+    if not isinstance(q, QuantConv2d) or state.get("seen_first_conv"):
+        return
+    state["seen_first_conv"] = True
+    if not cfg.get("firstconv"):
+        return
+    mean, std = cfg.get("mean"), cfg.get("std")
+    if mean is None or std is None:
+        raise AssertionError(_FIRSTCONV_ERROR)
+    if q.in_channels not in (1, 3, 4):
+        raise AssertionError("firstconv: the first Conv2d must take 1 (gray), 3 (RGB) or 4 (RGBA) input channels, "
+                             f"not {q.in_channels}; set firstconv False for a generic convolution")
+    if not (min(mean) >= 0 and max(mean) <= 1 and min(std) >= 0 and max(std) <= 1):
+        raise AssertionError(f"firstconv: mean and std must lie in [0, 1] (they are multiplied by 255 for inference); "
+                             f"mean is {mean}, std is {std}")
+    q.set_mean_std(torch.tensor(mean, dtype=torch.float32), torch.tensor(std, dtype=torch.float32))
+
+
+def _convert(module: nn.Module, mapping: Dict, cfg: dict, gen_quant: bool, mixed_layer: Optional[dict], prefix: str = "",
+             state: Optional[dict] = None):
+    state = {} if state is None else state
     for name, child in list(module.named_children()):
         full = prefix + name
         target = mapping.get(type(child))
         keep_float = mixed_layer is not None and str(mixed_layer.get(full, "")).strip() in ("float", "fp32", "fp16")
-        if target is not None and not keep_float and not isinstance(child, (QuantConv2d, QuantLinear)):
+        if target is not None and not keep_float and not isinstance(child, QuantModule):
             try:
                 layer_cfg = dict(cfg)
                 layer_cfg["activation_observer"] = cfg["activation_observer_factory"]() if gen_quant else None
                 q = target.from_float(child, layer_cfg, gen_quant)
             except ValueError:
                 continue  # unsupported layer variant stays in floating point
+            if gen_quant:
+                _first_conv_setup(q, cfg, state)
             setattr(module, name, q)
         else:
-            _convert(child, mapping, cfg, gen_quant, mixed_layer, full + ".")
+            _convert(child, mapping, cfg, gen_quant, mixed_layer, full + ".", state)
 
 
 def quantize_dynamic(model: nn.Module, qconfig_spec: Optional[dict] = None, dtype: Optional[str] = None,

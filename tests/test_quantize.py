@@ -94,3 +94,68 @@ def test_torchvision_nms_dispatches_to_the_backend():
     keep = torchvision.ops.nms(boxes.to("blackwell"), scores.to("blackwell"), 0.4)
     assert keep.device.type == "blackwell"
     assert torch.equal(keep.cpu(), torchvision.ops.nms(boxes, scores, 0.4))
+
+
+def test_data_scale_widens_the_range_like_the_reference():
+    from catch_b200.quantize import LrnObserver, MinMaxObserver
+
+    x = torch.tensor([-2.0, 0.5, 4.0])
+    plain, wide, lrn = MinMaxObserver(), MinMaxObserver(data_scale=2.0), LrnObserver()
+    for o in (plain, wide, lrn):
+        o(x)
+    assert abs(plain.scale().item() - 127.0 / 4.0) < 1e-6
+    assert abs(wide.scale().item() - 127.0 / 8.0) < 1e-6      # min / max are multiplied by data_scale
+    assert abs(lrn.scale().item() - 127.0 / 16.0) < 1e-6      # the LRN input is squared by the layer
+
+
+def test_conv1d_conv3d_modules_and_first_conv():
+    """Conv1d / Conv3d are swapped like Conv2d; the first Conv2d carries input_mean / input_std (x 255) through
+    the state dict and normalises raw inputs itself at inference time."""
+    import pytest
+    from catch_b200.quantize import QuantConv1d, QuantConv2d, QuantConv3d
+
+    class Multi(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.c1 = torch.nn.Conv1d(8, 8, 3, padding=1)
+            self.c3 = torch.nn.Conv3d(4, 8, 3, padding=1)
+
+        def forward(self, a, b):
+            return self.c1(a).mean(), self.c3(b).mean()
+
+    torch.manual_seed(0)
+    m = Multi().eval()
+    calib = quantize_dynamic(m, {"iteration": 2}, gen_quant=True)
+    assert isinstance(calib.c1, QuantConv1d) and isinstance(calib.c3, QuantConv3d)
+    a, b = torch.randn(2, 8, 16), torch.randn(1, 4, 5, 6, 7)
+    calib(a, b)
+    sd = calib.state_dict()
+    infer = quantize_dynamic(m)
+    infer.load_state_dict(sd, strict=False)
+    assert infer.c1.is_quantized() and infer.c3.is_quantized()
+    out = infer.to("blackwell")(a.to("blackwell"), b.to("blackwell"))
+    ref = m(a, b)
+    for o, r in zip(out, ref):
+        assert abs(o.item() - r.item()) < 5e-2 * (abs(r.item()) + 1e-2) + 2e-3
+
+    net = Net().eval()
+    with pytest.raises(AssertionError, match="firstconv"):
+        quantize_dynamic(net, {"firstconv": True}, gen_quant=True)
+    mean, std = [0.485, 0.456, 0.406], [0.229, 0.224, 0.225]
+    calib = quantize_dynamic(net, {"firstconv": True, "mean": mean, "std": std, "iteration": 2}, gen_quant=True)
+    g = torch.Generator().manual_seed(3)
+    raw = torch.rand(4, 3, 16, 16, generator=g) * 255.0
+    norm = (raw / 255.0 - torch.tensor(mean).view(1, 3, 1, 1)) / torch.tensor(std).view(1, 3, 1, 1)
+    calib(norm)                                   # calibration sees normalised inputs
+    sd = calib.state_dict()
+    assert torch.allclose(sd["conv1.input_mean"].flatten(), torch.tensor(mean) * 255)
+    assert torch.allclose(sd["conv1.input_std"].flatten(), torch.tensor(std) * 255)
+    assert "conv2.input_mean" not in sd           # only the first convolution
+    infer = quantize_dynamic(net)
+    missing, unexpected = infer.load_state_dict(sd, strict=False)
+    assert not missing and not unexpected
+    assert isinstance(infer.conv1, QuantConv2d) and infer.conv1.input_std is not None
+    out = infer.to("blackwell")(raw.to("blackwell"))  # inference takes the raw 0..255 image
+    assert_tensors_equal(out, net(norm), prec=3e-2, use_MSE=True)
+    sd2 = infer.state_dict()                      # an inference module saves the values as loaded
+    assert torch.allclose(sd2["conv1.input_mean"].cpu().flatten(), torch.tensor(mean) * 255)
