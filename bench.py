@@ -126,7 +126,7 @@ def checksum_words(tensors):
 
     h = hashlib.sha1()
     for t in tensors:
-        h.update(t.detach().to("cpu").contiguous().view(torch.uint8).numpy().tobytes())
+        h.update(t.detach().to("cpu").reshape(-1).contiguous().view(torch.uint8).numpy().tobytes())
     d = h.digest()
     return [int.from_bytes(d[i:i + 4], "little") for i in range(0, 20, 4)]
 
@@ -409,7 +409,12 @@ def main():
         except Exception as e:  # the stock arm must never take the main arm down with it
             if args.impl == "stock":
                 raise
+            import traceback
+
+            traceback.print_exc(file=sys.stderr)
             stock = {"error": f"{type(e).__name__}: {e}"[:300]}
+            if dist.is_initialized():
+                dist.destroy_process_group()
     if args.impl == "stock":
         if rank == 0:
             line = dict(common, impl="stock", value=stock["value"], ms_per_step=stock["ms_per_step"],

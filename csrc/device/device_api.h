@@ -69,6 +69,20 @@ B200_API int b200_enable_peer_access(int peer);
 B200_API int b200_ipc_get_handle(void* ptr, char handle[64]);
 B200_API int b200_ipc_open_handle(const char handle[64], void** ptr);
 B200_API int b200_ipc_close_handle(void* ptr);
+// Symmetric memory through the virtual-memory-management API (vmm.cu): allocations that are shared as POSIX
+// file descriptors and bound to an NVSwitch multicast object, so that one address names the same offset of
+// every rank's buffer (multimem.ld_reduce / multimem.st).  b200_vmm_import / b200_mc_import close the descriptor.
+B200_API int b200_vmm_multicast_supported(int device, int* supported);
+B200_API int b200_vmm_round_size(int device, int ndevices, size_t bytes, size_t* rounded);
+B200_API int b200_vmm_alloc(size_t bytes, int device, void** ptr, unsigned long long* handle, int* fd);
+B200_API int b200_vmm_import(int fd, size_t bytes, int device, void** ptr, unsigned long long* handle);
+B200_API int b200_vmm_release(void* ptr, size_t bytes, unsigned long long handle);
+B200_API int b200_mc_create(int ndevices, size_t bytes, unsigned long long* mc, int* fd);
+B200_API int b200_mc_import(int fd, unsigned long long* mc);
+B200_API int b200_mc_add_device(unsigned long long mc, int device);
+B200_API int b200_mc_bind(unsigned long long mc, unsigned long long mem_handle, size_t bytes);
+B200_API int b200_mc_map(unsigned long long mc, size_t bytes, int device, void** ptr);
+B200_API int b200_mc_release(void* ptr, size_t bytes, unsigned long long mc, int device, int bound);
 // Host-mapped (zero-copy) status words: kernels write, the host polls.
 B200_API int b200_host_alloc_mapped(void** host_ptr, void** dev_ptr, size_t bytes);
 

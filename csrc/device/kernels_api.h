@@ -384,6 +384,8 @@ typedef struct B200CommCtx {
   unsigned long long* flags[B200_COMM_MAX_RANKS];   // peer flag blocks: ready[16], done[16], p2p ready[16], p2p done[16], counter
   int* status;                                      // host-mapped status word
   unsigned long long timeout_ns;                    // wait limit (0 = 10 s)
+  void* mc;                                         // multicast address of the arena (null without NVLS): a
+                                                    // multimem access at mc + off reaches arena[r] + off on every rank
 } B200CommCtx;
 enum B200CommOp { COMM_SUM = 0, COMM_PROD = 1, COMM_MIN = 2, COMM_MAX = 3, COMM_AVG = 4 };
 

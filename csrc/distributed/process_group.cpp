@@ -1,12 +1,19 @@
 #include "process_group.h"
 
+#include <cstddef>
 #include <cstdlib>
+#include <map>
 #include <set>
 
 #include <ATen/ATen.h>
 #include <c10/util/Exception.h>
 #include <cstring>
 #include <thread>
+
+#include <poll.h>
+#include <sys/socket.h>
+#include <sys/un.h>
+#include <unistd.h>
 
 #include "../runtime/caching_allocator.h"
 #include "../runtime/device.h"
@@ -58,8 +65,102 @@ std::atomic<int> g_pg_counter{0};
 
 int next_process_group_id() { return g_pg_counter.fetch_add(1); }
 
+// ------------------------------------------------------------------------ FdExchange
+// Passes file descriptors (shareable handles of device memory) between the ranks of one host over
+// abstract-namespace Unix sockets with SCM_RIGHTS.  Every rank listens on "\0<token>/<rank>"; a sender
+// connects, sends {source rank, tag} with the descriptor attached, and closes.  Connections queue in the
+// listener's backlog, so everybody can send first and receive afterwards without a helper thread.
+class FdExchange {
+ public:
+  FdExchange(const std::string& token, int rank) : token_(token), rank_(rank) {
+    listen_fd_ = ::socket(AF_UNIX, SOCK_STREAM, 0);
+    TORCH_CHECK(listen_fd_ >= 0, "bwccl: cannot create a Unix socket");
+    sockaddr_un addr;
+    const socklen_t len = fill(addr, rank);
+    TORCH_CHECK(::bind(listen_fd_, reinterpret_cast<sockaddr*>(&addr), len) == 0, "bwccl: cannot bind the handle-exchange socket");
+    TORCH_CHECK(::listen(listen_fd_, 128) == 0, "bwccl: cannot listen on the handle-exchange socket");
+  }
+  ~FdExchange() {
+    for (auto& kv : stash_) ::close(kv.second);
+    if (listen_fd_ >= 0) ::close(listen_fd_);
+  }
+  void send(int dst, int tag, int fd) {
+    const int s = ::socket(AF_UNIX, SOCK_STREAM, 0);
+    TORCH_CHECK(s >= 0, "bwccl: cannot create a Unix socket");
+    sockaddr_un addr;
+    const socklen_t len = fill(addr, dst);
+    int rc = -1;
+    for (int attempt = 0; attempt < 2000 && rc != 0; ++attempt) {  // the peer may not be listening yet
+      rc = ::connect(s, reinterpret_cast<sockaddr*>(&addr), len);
+      if (rc != 0) std::this_thread::sleep_for(std::chrono::milliseconds(5));
+    }
+    TORCH_CHECK(rc == 0, "bwccl: cannot reach rank ", dst, " to hand over a memory handle");
+    int payload[2] = {rank_, tag};
+    iovec iov{payload, sizeof(payload)};
+    char ctrl[CMSG_SPACE(sizeof(int))];
+    std::memset(ctrl, 0, sizeof(ctrl));
+    msghdr msg{};
+    msg.msg_iov = &iov; msg.msg_iovlen = 1;
+    msg.msg_control = ctrl; msg.msg_controllen = sizeof(ctrl);
+    cmsghdr* c = CMSG_FIRSTHDR(&msg);
+    c->cmsg_level = SOL_SOCKET; c->cmsg_type = SCM_RIGHTS; c->cmsg_len = CMSG_LEN(sizeof(int));
+    std::memcpy(CMSG_DATA(c), &fd, sizeof(int));
+    const ssize_t n = ::sendmsg(s, &msg, 0);
+    ::close(s);
+    TORCH_CHECK(n == (ssize_t)sizeof(payload), "bwccl: sending a memory handle to rank ", dst, " failed");
+  }
+  int recv(int src, int tag, std::chrono::milliseconds timeout) {
+    const auto key = std::make_pair(src, tag);
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+      auto it = stash_.find(key);
+      if (it != stash_.end()) {
+        const int fd = it->second;
+        stash_.erase(it);
+        return fd;
+      }
+      TORCH_CHECK(std::chrono::steady_clock::now() - t0 < timeout, "bwccl: timed out waiting for a memory handle from rank ", src);
+      pollfd p{listen_fd_, POLLIN, 0};
+      if (::poll(&p, 1, 100) <= 0) continue;
+      const int cfd = ::accept(listen_fd_, nullptr, nullptr);
+      if (cfd < 0) continue;
+      int payload[2] = {-1, -1};
+      iovec iov{payload, sizeof(payload)};
+      char ctrl[CMSG_SPACE(sizeof(int))];
+      msghdr msg{};
+      msg.msg_iov = &iov; msg.msg_iovlen = 1;
+      msg.msg_control = ctrl; msg.msg_controllen = sizeof(ctrl);
+      const ssize_t n = ::recvmsg(cfd, &msg, 0);
+      ::close(cfd);
+      cmsghdr* c = CMSG_FIRSTHDR(&msg);
+      if (n != (ssize_t)sizeof(payload) || !c || c->cmsg_type != SCM_RIGHTS) continue;
+      int fd = -1;
+      std::memcpy(&fd, CMSG_DATA(c), sizeof(int));
+      stash_[std::make_pair(payload[0], payload[1])] = fd;
+    }
+  }
+
+ private:
+  socklen_t fill(sockaddr_un& addr, int rank) const {
+    std::memset(&addr, 0, sizeof(addr));
+    addr.sun_family = AF_UNIX;
+    const std::string name = token_ + "/" + std::to_string(rank);
+    TORCH_CHECK(name.size() + 2 < sizeof(addr.sun_path), "bwccl: socket name too long");
+    std::memcpy(addr.sun_path + 1, name.data(), name.size());  // leading NUL: abstract namespace
+    return static_cast<socklen_t>(offsetof(sockaddr_un, sun_path) + 1 + name.size());
+  }
+  std::string token_;
+  int rank_;
+  int listen_fd_ = -1;
+  std::map<std::pair<int, int>, int> stash_;
+};
+
 // ------------------------------------------------------------------ SymmetricArena
 // Layout of one rank's arena: [staging | p2p mailbox | user region | flag block].
+// Two ways to make it visible to the peers: cudaMalloc + CUDA IPC handles through the Store (always works),
+// or, when every rank's GPU supports NVSwitch multicast and CATCH_B200_NVLS is not 0, a cuMemCreate
+// allocation shared as a file descriptor and bound to one multicast object, which adds `mc` (an address
+// that reaches the same offset on every rank) for the in-switch reduction kernels.
 class SymmetricArena {
  public:
   SymmetricArena(int device, int rank, int world, const c10::intrusive_ptr<c10d::Store>& store, const std::string& uid,
@@ -71,7 +172,42 @@ class SymmetricArena {
     user_ = env_mb("CATCH_B200_SYMM_USER_MB", 1536) << 20;
     total_ = staging_ + mailbox_ + user_ + B200_COMM_FLAG_BYTES;
     DeviceSwitch sw(device);
-    COMM_CHECK(b200_malloc(&base_, total_));
+    std::memset(&ctx_, 0, sizeof(ctx_));
+    ctx_.rank = rank;
+    ctx_.world = world;
+    auto barrier = [&](const std::string& name) {
+      store->add(uid + "/" + name, 1);
+      const auto t0 = std::chrono::steady_clock::now();
+      while (store->add(uid + "/" + name, 0) < world) {
+        TORCH_CHECK(std::chrono::steady_clock::now() - t0 < timeout, "bwccl: timed out waiting for peers (", name, ")");
+        std::this_thread::sleep_for(std::chrono::milliseconds(2));
+      }
+    };
+    // every rank votes; the multicast path is taken only if all of them can
+    int mine = 0;
+    const char* env = std::getenv("CATCH_B200_NVLS");
+    if (!(env && std::string(env) == "0") && world > 1) b200_vmm_multicast_supported(device, &mine);
+    store->add(uid + "/vmm_votes", mine);
+    barrier("vmm_voted");
+    vmm_ = store->add(uid + "/vmm_votes", 0) == world;
+    if (vmm_) {
+      try {
+        setup_vmm(store, uid, timeout, barrier);
+      } catch (const std::exception& e) {
+        // all ranks run the same steps on the same kind of GPU, so they fail (or not) together
+        B200LOG(WARNING) << "bwccl: multicast set-up failed (" << e.what() << "); using CUDA IPC peer mappings only.";
+        teardown_vmm();
+        vmm_ = false;
+      }
+      // agree on the outcome: one failing rank sends everybody back to the IPC path
+      store->add(uid + "/vmm_ok", vmm_ ? 1 : 0);
+      barrier("vmm_done");
+      if (store->add(uid + "/vmm_ok", 0) != world && vmm_) {
+        teardown_vmm();
+        vmm_ = false;
+      }
+    }
+    if (!vmm_) setup_ipc(store, uid, timeout);
     COMM_CHECK(b200_memset_async(static_cast<char*>(base_) + total_ - B200_COMM_FLAG_BYTES, 0, B200_COMM_FLAG_BYTES, nullptr));
     COMM_CHECK(b200_device_synchronize());
     void* host = nullptr;
@@ -79,46 +215,30 @@ class SymmetricArena {
     COMM_CHECK(b200_host_alloc_mapped(&host, &dev, 64));
     status_host_ = static_cast<int*>(host);
     status_dev_ = static_cast<int*>(dev);
-    // exchange IPC handles through the store
-    char handle[64];
-    COMM_CHECK(b200_ipc_get_handle(base_, handle));
-    store->set(uid + "/ipc/" + std::to_string(rank), std::vector<uint8_t>(handle, handle + 64));
-    std::memset(&ctx_, 0, sizeof(ctx_));
-    ctx_.rank = rank;
-    ctx_.world = world;
     ctx_.status = status_dev_;
-    for (int p = 0; p < world; ++p) {
-      void* ptr = base_;
-      if (p != rank) {
-        const std::string key = uid + "/ipc/" + std::to_string(p);
-        store->wait({key}, timeout);
-        auto h = store->get(key);
-        TORCH_CHECK(h.size() == 64, "bwccl: malformed IPC handle from rank ", p);
-        COMM_CHECK(b200_ipc_open_handle(reinterpret_cast<const char*>(h.data()), &ptr));
-        opened_.push_back(ptr);
-      }
-      ctx_.arena[p] = ptr;
-      ctx_.flags[p] = reinterpret_cast<unsigned long long*>(static_cast<char*>(ptr) + total_ - B200_COMM_FLAG_BYTES);
-    }
+    for (int p = 0; p < world; ++p)
+      ctx_.flags[p] = reinterpret_cast<unsigned long long*>(static_cast<char*>(ctx_.arena[p]) + total_ - B200_COMM_FLAG_BYTES);
     // nobody may signal before every rank has zeroed its flags and mapped its peers
-    store->add(uid + "/mapped", 1);
-    const auto t0 = std::chrono::steady_clock::now();
-    while (store->add(uid + "/mapped", 0) < world) {
-      TORCH_CHECK(std::chrono::steady_clock::now() - t0 < timeout, "bwccl: timed out waiting for peers to map the arena");
-      std::this_thread::sleep_for(std::chrono::milliseconds(2));
-    }
+    barrier("mapped");
+    B200LOG(INFO) << "bwccl arena of rank " << rank << ": " << (total_ >> 20) << " MiB, "
+                  << (vmm_ ? "multicast (NVLS) mapping" : "CUDA IPC peer mappings");
   }
   ~SymmetricArena() {
     try {
       DeviceSwitch sw(device_);
       b200_device_synchronize();
-      for (void* p : opened_) b200_ipc_close_handle(p);
-      b200_free(base_);
+      if (vmm_) {
+        teardown_vmm();
+      } else {
+        for (void* p : opened_) b200_ipc_close_handle(p);
+        b200_free(base_);
+      }
       b200_host_free(status_host_);
     } catch (...) {
     }
   }
   B200CommCtx ctx() const { return ctx_; }
+  bool multicast() const { return vmm_ && ctx_.mc != nullptr; }
   char* local() const { return static_cast<char*>(base_); }
   size_t staging_bytes() const { return staging_; }
   size_t mailbox_offset() const { return staging_; }
@@ -141,6 +261,86 @@ class SymmetricArena {
   void set_timeout_ns(unsigned long long ns) { ctx_.timeout_ns = ns; }
 
  private:
+  void setup_ipc(const c10::intrusive_ptr<c10d::Store>& store, const std::string& uid, std::chrono::milliseconds timeout) {
+    COMM_CHECK(b200_malloc(&base_, total_));
+    char handle[64];
+    COMM_CHECK(b200_ipc_get_handle(base_, handle));
+    store->set(uid + "/ipc/" + std::to_string(rank_), std::vector<uint8_t>(handle, handle + 64));
+    for (int p = 0; p < world_; ++p) {
+      void* ptr = base_;
+      if (p != rank_) {
+        const std::string key = uid + "/ipc/" + std::to_string(p);
+        store->wait({key}, timeout);
+        auto h = store->get(key);
+        TORCH_CHECK(h.size() == 64, "bwccl: malformed IPC handle from rank ", p);
+        COMM_CHECK(b200_ipc_open_handle(reinterpret_cast<const char*>(h.data()), &ptr));
+        opened_.push_back(ptr);
+      }
+      ctx_.arena[p] = ptr;
+    }
+  }
+  template <typename Barrier>
+  void setup_vmm(const c10::intrusive_ptr<c10d::Store>& store, const std::string& uid, std::chrono::milliseconds timeout,
+                 Barrier&& barrier) {
+    // a token that only this job's ranks know names the sockets
+    if (rank_ == 0) {
+      const std::string tok = "bwccl-" + std::to_string(::getpid()) + "-" + std::to_string(std::chrono::steady_clock::now().time_since_epoch().count());
+      store->set(uid + "/fdtoken", std::vector<uint8_t>(tok.begin(), tok.end()));
+    }
+    store->wait({uid + "/fdtoken"}, timeout);
+    auto tokv = store->get(uid + "/fdtoken");
+    FdExchange fdx(std::string(tokv.begin(), tokv.end()), rank_);
+    COMM_CHECK(b200_vmm_round_size(device_, world_, total_, &mapped_bytes_));
+    int fd = -1;
+    COMM_CHECK(b200_vmm_alloc(mapped_bytes_, device_, &base_, &mem_handle_, &fd));
+    barrier("fd_listening");  // every rank's socket exists
+    for (int p = 0; p < world_; ++p)
+      if (p != rank_) fdx.send(p, /*tag=*/0, fd);
+    ::close(fd);
+    peer_ptr_.assign(world_, nullptr);
+    peer_handle_.assign(world_, 0);
+    for (int p = 0; p < world_; ++p) {
+      if (p == rank_) {
+        ctx_.arena[p] = base_;
+        continue;
+      }
+      const int pfd = fdx.recv(p, 0, timeout);
+      COMM_CHECK(b200_vmm_import(pfd, mapped_bytes_, device_, &peer_ptr_[p], &peer_handle_[p]));
+      ctx_.arena[p] = peer_ptr_[p];
+    }
+    // one multicast object: created by rank 0, imported by the others, every device added, every allocation bound
+    if (rank_ == 0) {
+      int mfd = -1;
+      COMM_CHECK(b200_mc_create(world_, mapped_bytes_, &mc_handle_, &mfd));
+      for (int p = 1; p < world_; ++p) fdx.send(p, /*tag=*/1, mfd);
+      ::close(mfd);
+    } else {
+      const int mfd = fdx.recv(0, 1, timeout);
+      COMM_CHECK(b200_mc_import(mfd, &mc_handle_));
+    }
+    COMM_CHECK(b200_mc_add_device(mc_handle_, device_));
+    barrier("mc_added");
+    COMM_CHECK(b200_mc_bind(mc_handle_, mem_handle_, mapped_bytes_));
+    mc_bound_ = true;
+    barrier("mc_bound");
+    void* mc_ptr = nullptr;
+    COMM_CHECK(b200_mc_map(mc_handle_, mapped_bytes_, device_, &mc_ptr));
+    ctx_.mc = mc_ptr;
+  }
+  void teardown_vmm() {
+    if (ctx_.mc || mc_handle_) b200_mc_release(ctx_.mc, mapped_bytes_, mc_handle_, device_, mc_bound_ ? 1 : 0);
+    ctx_.mc = nullptr;
+    mc_handle_ = 0;
+    mc_bound_ = false;
+    for (size_t p = 0; p < peer_ptr_.size(); ++p)
+      if (peer_ptr_[p]) b200_vmm_release(peer_ptr_[p], mapped_bytes_, peer_handle_[p]);
+    peer_ptr_.clear();
+    peer_handle_.clear();
+    if (base_ && mem_handle_) b200_vmm_release(base_, mapped_bytes_, mem_handle_);
+    base_ = nullptr;
+    mem_handle_ = 0;
+  }
+
   int device_, rank_, world_;
   void* base_ = nullptr;
   size_t staging_, mailbox_, user_, total_, user_used_ = 0;
@@ -148,6 +348,12 @@ class SymmetricArena {
   int* status_dev_ = nullptr;
   std::vector<void*> opened_;
   B200CommCtx ctx_;
+  // multicast path
+  bool vmm_ = false, mc_bound_ = false;
+  size_t mapped_bytes_ = 0;
+  unsigned long long mem_handle_ = 0, mc_handle_ = 0;
+  std::vector<void*> peer_ptr_;
+  std::vector<unsigned long long> peer_handle_;
 };
 
 // ------------------------------------------------------------------------- WorkB200

@@ -143,6 +143,9 @@ def test_optimizer_state_dict_loads_into_stock_optimizer(kind):
         opt.zero_grad(); ref(x).pow(2).mean().backward(); opt.step()
         opt2.zero_grad(); resumed(x).pow(2).mean().backward(); opt2.step()
         fdp3(x.to(DEV)).pow(2).mean().backward(); fdp3.step()
+    # fp32 linears run as TF32 on the device: where a gradient is within rounding of zero Adam's normalised step
+    # can take the other sign (a difference of 2 * lr in that element), so AdamW is compared by relative RMS
+    kw = dict(prec=3e-3) if kind == "sgd" else dict(prec=1e-2, use_MSE=True)
     for p, q, r in zip(ref.parameters(), resumed.parameters(), fdp3.module.parameters()):
-        assert_tensors_equal(q, p, prec=3e-3)
-        assert_tensors_equal(r, p, prec=3e-3)
+        assert_tensors_equal(q, p, **kw)
+        assert_tensors_equal(r, p, **kw)

@@ -170,7 +170,7 @@ def test_linspace_equal_diag_cumsum():
         for args in ((0, 1, 11), (-3, 7, 50), (5, 5, 1), (2, -2, 4), (0, 10, 0), (0, 100, 1001)):
             ref = torch.linspace(*args, dtype=dtype)
             got = torch.linspace(*args, dtype=dtype, device=DEV)
-            assert_tensors_equal(got, ref, prec=1e-6 if dtype in (torch.float32, torch.float64) else (0.5 if dtype == torch.bfloat16 else 0))
+            assert_tensors_equal(got, ref, prec={torch.float32: 1e-5, torch.float64: 1e-9, torch.bfloat16: 0.5}.get(dtype, 0))
     out = torch.empty(9, device=DEV)
     torch.linspace(1, 2, 9, out=out)
     assert_tensors_equal(out, torch.linspace(1, 2, 9), prec=1e-6)
