@@ -2,9 +2,11 @@
 // vendor collective library (cnclAllReduce / Broadcast / Reduce / AllGather / Send /
 // Recv, torch_mlu/csrc/distributed/process_group_cncl.cpp:349-572).
 //
-// Transport: plain global loads and stores on peer pointers obtained through CUDA IPC;
-// through NVSwitch every peer is reachable at full NVLink bandwidth.  No copy-engine
-// or tensor-map loads touch peer memory.  Synchronisation: per-peer 64-bit sequence
+// Transport: plain global loads and stores on peer pointers (CUDA IPC or shared cuMemCreate
+// allocations); through NVSwitch every peer is reachable at full NVLink bandwidth.  When the
+// arena is also bound to an NVSwitch multicast object, sums of floating types use multimem
+// loads / stores (reduction and broadcast inside the switch).  No copy-engine or tensor-map
+// loads touch peer memory.  Synchronisation: per-peer 64-bit sequence
 // flags written with st.release.sys and polled with ld.acquire.sys; polls are bounded
 // and report a timeout in a host-mapped status word instead of hanging.
 //
@@ -14,6 +16,7 @@
 // parameters, and pushes the result to every peer with 16-byte stores.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <stdlib.h>
 #include "kernels_api.h"
 
 namespace {
@@ -34,6 +37,43 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
   unsigned long long v;
   asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
+}
+
+// ---- NVSwitch multicast accesses -------------------------------------------------------------------
+// A multimem load with .add on a multicast address returns the SUM over every rank's copy of that 16-byte
+// vector, computed inside the switch; a multimem store writes every rank's copy.  The per-rank link
+// traffic of an all-reduce drops from 2 * (world - 1) / world to about one message size per direction.
+template <typename T> struct Multimem;
+template <> struct Multimem<float> {
+  static __device__ __forceinline__ uint4 ld_sum(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+};
+template <> struct Multimem<__nv_bfloat16> {
+  static __device__ __forceinline__ uint4 ld_sum(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+};
+template <> struct Multimem<__half> {
+  static __device__ __forceinline__ uint4 ld_sum(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+};
+__device__ __forceinline__ void multimem_st16(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void multimem_st8(void* mc, const uint2& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(mc), "r"(v.x), "r"(v.y) : "memory");
 }
 
 // Wait until *flag >= seq.  Returns false on timeout (status set) or if another
@@ -201,6 +241,44 @@ __global__ void __launch_bounds__(512) allreduce_kernel(const B200CommCtx c, siz
   end_barrier(c, seq, limit, false);
 }
 
+// In-switch all-reduce (sum / average of fp32, bf16 or fp16): rank r reduces shard r with multimem loads
+// and publishes it with multimem stores.  Same barriers as the peer-memory kernel.
+template <typename T>
+__global__ void __launch_bounds__(512) allreduce_nvls_kernel(const B200CommCtx c, size_t offset, long long n, int op,
+                                                             float scale, unsigned long long seq, int no_signal) {
+  constexpr int V = Vec<T>::N;
+  constexpr int U = 4;
+  const unsigned long long limit = c.timeout_ns ? c.timeout_ns : kDefaultTimeoutNs;
+  if (!start_barrier(c, seq, no_signal, limit)) return;
+  const long long nvec = (n + V - 1) / V;
+  const long long per = (nvec + c.world - 1) / c.world;
+  const long long v0 = per * c.rank, v1 = (v0 + per < nvec) ? v0 + per : nvec;
+  float mul = scale;
+  if (op == COMM_AVG) mul /= (float)c.world;
+  char* mc = static_cast<char*>(c.mc) + offset;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < v1; i0 += stride * U) {
+    uint4 raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < v1) raw[u] = Multimem<T>::ld_sum(mc + i * 16);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= v1) break;
+      if (mul != 1.f) {
+        T* tv = reinterpret_cast<T*>(&raw[u]);
+#pragma unroll
+        for (int k = 0; k < V; ++k) tv[k] = from_f<T>(to_f<T>(tv[k]) * mul);
+      }
+      multimem_st16(mc + i * 16, raw[u]);
+    }
+  }
+  end_barrier(c, seq, limit, false);
+}
+
 // One element of the optimizer update on the fp32 master parameter `wk` with reduced gradient `d`
 // (already scaled); `s` indexes this rank's state shards.
 __device__ __forceinline__ float opt_update(const B200FusedOptArgs& o, float wk, float d, long long s) {
@@ -230,7 +308,10 @@ __device__ __forceinline__ float opt_update(const B200FusedOptArgs& o, float wk,
 //   phase 2: the updated shard (and its optional 16-bit copy) is written to every peer;
 //   phase 3 (only with o.zero_grads and no cast_src): once every peer has said "done", nobody reads this
 //            rank's gradient region any more and the CTAs clear it for the next backward pass.
-template <typename T>
+//
+// NVLS: with a multicast mapping of the arena the reduce-scatter is one multimem load per vector (the
+// switch adds the ranks' gradients) and the parameter all-gather one multimem store.
+template <typename T, bool NVLS>
 __global__ void __launch_bounds__(512) allreduce_opt_kernel(const B200CommCtx c, size_t goff, size_t poff, long long n,
                                                             float scale, const B200FusedOptArgs o,
                                                             unsigned long long seq) {
@@ -272,20 +353,36 @@ __global__ void __launch_bounds__(512) allreduce_opt_kernel(const B200CommCtx c,
   const long long v0 = per * c.rank, v1 = (v0 + per < nvec) ? v0 + per : nvec;
   for (long long i0 = v0 + gtid; i0 < v1; i0 += gstride * U) {
     float g[U][V];
-    for (int p = 0; p < c.world; ++p) {
-      const int peer = (c.rank + p) % c.world;
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(c.arena[peer]) + goff);
+    if (NVLS) {
+      const char* mcg = static_cast<const char*>(c.mc) + goff;
       uint4 raw[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const long long i = i0 + u * gstride;
-        if (i < v1) raw[u] = src[i];
+        if (i < v1) raw[u] = Multimem<T>::ld_sum(mcg + i * 16);
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const T* tv = reinterpret_cast<const T*>(&raw[u]);
 #pragma unroll
-        for (int k = 0; k < V; ++k) g[u][k] = p == 0 ? to_f<T>(tv[k]) : g[u][k] + to_f<T>(tv[k]);
+        for (int k = 0; k < V; ++k) g[u][k] = to_f<T>(tv[k]);
+      }
+    } else {
+      for (int p = 0; p < c.world; ++p) {
+        const int peer = (c.rank + p) % c.world;
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(c.arena[peer]) + goff);
+        uint4 raw[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * gstride;
+          if (i < v1) raw[u] = src[i];
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const T* tv = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+          for (int k = 0; k < V; ++k) g[u][k] = p == 0 ? to_f<T>(tv[k]) : g[u][k] + to_f<T>(tv[k]);
+        }
       }
     }
 #pragma unroll
@@ -308,6 +405,17 @@ __global__ void __launch_bounds__(512) allreduce_opt_kernel(const B200CommCtx c,
       }
       // all-gather of the updated parameters: push to every peer (fp32 master copy and the optional
       // 16-bit copy that autocast forward passes read)
+      if (NVLS) {
+        char* mcp = static_cast<char*>(c.mc) + poff + (size_t)i * V * 4;
+#pragma unroll
+        for (int k = 0; k < V; k += 4) multimem_st16(mcp + k * 4, *reinterpret_cast<const uint4*>(w + k));
+        if (o.lowp_offset) {
+          char* mcl = static_cast<char*>(c.mc) + o.lowp_offset + (size_t)i * V * 2;
+          if (V == 8) multimem_st16(mcl, *reinterpret_cast<const uint4*>(lw));
+          else multimem_st8(mcl, *reinterpret_cast<const uint2*>(lw));
+        }
+        continue;
+      }
       for (int p = 0; p < c.world; ++p) {
         const int peer = (c.rank + p) % c.world;
         float* dst = reinterpret_cast<float*>(static_cast<char*>(c.arena[peer]) + poff) + i * V;
@@ -404,6 +512,15 @@ inline int comm_grid(long long work_items, int threads, int cap) {
     default: return (int)cudaErrorInvalidValue;                      \
   }
 
+// Smallest message that takes the in-switch path (CATCH_B200_NVLS_MIN_KB, default 256 KiB).
+extern "C" long long b200_comm_nvls_min_bytes(void) {
+  static const long long v = [] {
+    const char* e = getenv("CATCH_B200_NVLS_MIN_KB");
+    return (e && *e) ? atoll(e) * 1024 : 256LL * 1024;
+  }();
+  return v;
+}
+
 extern "C" long long b200_comm_shard_elems(long long n, int world, int dtype) {
   const int es = (dtype == B200_F32 || dtype == B200_I32) ? 4 : ((dtype == B200_F64 || dtype == B200_I64) ? 8 : 2);
   const int V = 16 / es;
@@ -416,6 +533,20 @@ extern "C" int b200_comm_allreduce(const B200CommCtx* ctx, size_t offset, long l
   if (n <= 0) return 0;
   if (ctx->world > B200_COMM_MAX_RANKS || (offset & 15)) return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
+  // In-switch reduction for sums / averages of floating types once the message is large enough for the
+  // switch's higher per-access latency to pay off.
+  const bool nvls = ctx->mc != nullptr && (op == COMM_SUM || op == COMM_AVG) &&
+                    (dtype == B200_F32 || dtype == B200_BF16 || dtype == B200_F16) &&
+                    n * (dtype == B200_F32 ? 4 : 2) >= b200_comm_nvls_min_bytes();
+  if (nvls) {
+    const int V = dtype == B200_F32 ? 4 : 8;
+    const long long per = (((n + V - 1) / V) + ctx->world - 1) / ctx->world;
+    const int grid = comm_grid((per + 3) / 4, 512, 128);
+    if (dtype == B200_F32) allreduce_nvls_kernel<float><<<grid, 512, 0, s>>>(*ctx, offset, n, op, scale, seq, no_signal);
+    else if (dtype == B200_BF16) allreduce_nvls_kernel<__nv_bfloat16><<<grid, 512, 0, s>>>(*ctx, offset, n, op, scale, seq, no_signal);
+    else allreduce_nvls_kernel<__half><<<grid, 512, 0, s>>>(*ctx, offset, n, op, scale, seq, no_signal);
+    return (int)cudaGetLastError();
+  }
   COMM_DISPATCH(dtype, T, {
     const long long per = (((n + Vec<T>::N - 1) / Vec<T>::N) + ctx->world - 1) / ctx->world;
     // enough CTAs to saturate NVLink, few enough that all of them are resident
@@ -440,15 +571,22 @@ extern "C" int b200_comm_allreduce_opt(const B200CommCtx* ctx, size_t goff, size
   long long work = (per + U - 1) / U;
   if (opt->cast_src || opt->zero_grads) work = work > nvec / 8 ? work : nvec / 8;  // the local passes cover the whole bucket
   const int grid = comm_grid(work, 512, per * 16 >= (2LL << 20) ? 128 : 64);
+  const bool nvls = ctx->mc != nullptr && n * (grad_dtype == B200_F32 ? 4 : 2) >= b200_comm_nvls_min_bytes();
+#define OPT_LAUNCH(T)                                                                                          \
+  do {                                                                                                         \
+    if (nvls) allreduce_opt_kernel<T, true><<<grid, 512, 0, s>>>(*ctx, goff, poff, n, scale, *opt, seq);       \
+    else allreduce_opt_kernel<T, false><<<grid, 512, 0, s>>>(*ctx, goff, poff, n, scale, *opt, seq);           \
+  } while (0)
   switch (grad_dtype) {
     case B200_F32:
       if (opt->cast_src) return (int)cudaErrorInvalidValue;  // fp32 gradients are exchanged in place
-      allreduce_opt_kernel<float><<<grid, 512, 0, s>>>(*ctx, goff, poff, n, scale, *opt, seq);
+      OPT_LAUNCH(float);
       break;
-    case B200_BF16: allreduce_opt_kernel<__nv_bfloat16><<<grid, 512, 0, s>>>(*ctx, goff, poff, n, scale, *opt, seq); break;
-    case B200_F16: allreduce_opt_kernel<__half><<<grid, 512, 0, s>>>(*ctx, goff, poff, n, scale, *opt, seq); break;
+    case B200_BF16: OPT_LAUNCH(__nv_bfloat16); break;
+    case B200_F16: OPT_LAUNCH(__half); break;
     default: return (int)cudaErrorInvalidValue;
   }
+#undef OPT_LAUNCH
   return (int)cudaGetLastError();
 }
 

@@ -54,6 +54,9 @@ struct GemmKernelArgs {
   int act;
   int coef_bytes;       // shared memory reserved for column scale / bias (0 or 2048)
   int tma_store;        // epilogue stages 64-column blocks in shared memory and stores them by TMA
+  int reduce_add;       // fp32 D += result: 32 x 32 blocks are added to global memory with tensor-map reductions
+  int splits;           // the K loop is divided among `splits` work items per output tile (reduce_add only)
+  int kb_per_split;
   int* err;
 };
 
@@ -166,7 +169,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t tmem_base = *tmem_slot;
 
   const int tiles_per_batch = g.tiles_m * g.tiles_n;
-  const int total_tiles = tiles_per_batch * g.batch;
+  // a work item is (output tile, K split); splits of one tile are adjacent so that they run at the same time
+  const int total_tiles = tiles_per_batch * g.batch * g.splits;
   const int bk_elems = 128 / g.elem_bytes;          // K elements per k-block
   const int mn_block = 128 / g.elem_bytes;          // MN elements per 128-byte row (MN-major)
   bool failed = false;
@@ -177,12 +181,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       const uint32_t tx_bytes = (uint32_t)stage_bytes;
-      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < total_tiles && !failed; item += gridDim.x) {
+        const int tile = item / g.splits, split = item - tile * g.splits;
         const int bz = tile / tiles_per_batch;
         const int t = tile - bz * tiles_per_batch;
         const int m0 = (t % g.tiles_m) * GEMM_BM;
         const int n0 = (t / g.tiles_m) * g.tile_n;
-        for (int kb = 0; kb < g.k_blocks; ++kb) {
+        const int kb0 = split * g.kb_per_split, kb1 = min(g.k_blocks, kb0 + g.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, g.err, ERR_TIMEOUT_EMPTY)) { failed = true; break; }
           mbar_arrive_expect_tx(&full_bar[stage], tx_bytes);
           uint8_t* sa = tiles + (size_t)stage * stage_bytes;
@@ -219,16 +225,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       split_desc(g.b_mn ? make_smem_desc_sw128(0, g.mn_lbo, g.mn_sbo) : make_smem_desc_sw128(0, 16, 1024), &b_lo0, &b_hi);
       const uint32_t a_step = g.a_mn ? (uint32_t)g.mn_kstep >> 4 : 2u, b_step = g.b_mn ? (uint32_t)g.mn_kstep >> 4 : 2u;
       const uint32_t tiles_16 = smem_u32(tiles) >> 4, stage_16 = (uint32_t)stage_bytes >> 4;
-      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < total_tiles && !failed; item += gridDim.x) {
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, g.err, ERR_TIMEOUT_TMEM_EMPTY)) { failed = true; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * GEMM_ACC_STRIDE;
-        for (int kb = 0; kb < g.k_blocks; ++kb) {
+        const int split = item % g.splits;
+        const int kb0 = split * g.kb_per_split, kb1 = min(g.k_blocks, kb0 + g.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, g.err, ERR_TIMEOUT_FULL)) { failed = true; break; }
           tc_fence_after();
           const uint32_t sa_16 = tiles_16 + (uint32_t)stage * stage_16;
           const uint32_t sb_16 = sa_16 + (GEMM_A_STAGE_BYTES >> 4);
-          const uint32_t accum = kb > 0 ? 1u : 0u;
+          const uint32_t accum = kb > kb0 ? 1u : 0u;
           if (g.kind == 1) umma_x4<1>(d_tmem, a_lo0 + sa_16, a_hi, a_step, b_lo0 + sb_16, b_hi, b_step, g.idesc, accum);
           else if (g.kind == 2) umma_x4<2>(d_tmem, a_lo0 + sa_16, a_hi, a_step, b_lo0 + sb_16, b_hi, b_step, g.idesc, accum);
           else umma_x4<0>(d_tmem, a_lo0 + sa_16, a_hi, a_step, b_lo0 + sb_16, b_hi, b_step, g.idesc, accum);
@@ -248,7 +256,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t acc_phase = 0;
     uint32_t tile_iter = 0;
     const bool has_coef = g.col_scale != nullptr || (g.bias != nullptr && !g.bias_per_row);
-    for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++tile_iter) {
+    for (int item = blockIdx.x; item < total_tiles && !failed; item += gridDim.x, ++tile_iter) {
+      const int tile = item / g.splits;
       const int bz = tile / tiles_per_batch;
       const int t = tile - bz * tiles_per_batch;
       const int m0 = (t % g.tiles_m) * GEMM_BM;
@@ -275,6 +284,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                              ((size_t)bz * g.stride_r + (size_t)row * g.ldr) *
                                                  (g.res_dtype == B200_F32 ? 4 : 2)
                                        : nullptr;
+      if (g.reduce_add) {
+        // fp32 accumulation into global memory: each warp stages 32 rows x 32 fp32 columns (4 KB, 128-byte swizzle) and
+        // adds them with one tensor-map reduction; rows / columns outside the matrix are clipped.  K splits of one tile and
+        // whatever the destination already holds simply add up.
+        uint8_t* sbuf = stage_out + (warp - 2) * 4096;
+        const uint32_t t_addr = tmem_base + acc * GEMM_ACC_STRIDE + ((uint32_t)(quarter * 32) << 16);
+        for (int c = colhalf * 32; c < g.tile_n; c += 64) {
+          uint32_t r[32];
+          tmem_ld32(t_addr + c, r);
+          tmem_ld_wait();
+          if (n0 + c >= g.N) continue;  // warp-uniform
+          if (g.alpha != 1.f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * g.alpha);
+          }
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+          uint8_t* srow = sbuf + lane * 128;
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            *reinterpret_cast<uint4*>(srow + ((k ^ (lane & 7)) * 16)) = make_uint4(r[4 * k], r[4 * k + 1], r[4 * k + 2], r[4 * k + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_reduce_add_3d(&tmD, sbuf, n0 + c, m0 + quarter * 32, bz);
+            tma_store_commit();
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&acc_empty[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        if (has_coef) named_barrier(2, GEMM_EPI_THREADS);
+        continue;
+      }
       if (g.tma_store) {
         // Each epilogue warp stages its own 32 rows x 64 columns (4 KB, 128-byte swizzle) and issues its own
         // tensor-map store; the two warps of a lane quarter take alternate 64-column blocks.  No barrier
@@ -394,7 +437,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 
   // ---------------------------------------------------------------- teardown
-  if (g.tma_store && warp >= 2 && lane == 0) tma_store_wait_all<0>();  // every issuing lane drains its own stores
+  if ((g.tma_store || g.reduce_add) && warp >= 2 && lane == 0) tma_store_wait_all<0>();  // every issuing lane drains its own stores
   if (*((volatile int*)g.err) != 0) {
     // Error path: give copies that are still in flight time to land before the
     // shared memory goes away.
@@ -484,13 +527,37 @@ extern "C" int b200_gemm(const B200GemmParams* p, void* stream) {
   g.tma_store = (p->d_dtype != B200_F32 && g.tile_n % 64 == 0 && (p->ldd * 2) % 16 == 0 && (p->stride_d * 2) % 16 == 0 &&
                  (reinterpret_cast<uintptr_t>(p->D) & 15) == 0)
                     ? 1 : 0;
+  g.reduce_add = 0;
+  g.splits = 1;
+  g.kb_per_split = g.k_blocks;
+  if (p->accumulate) {
+    // D (fp32) += alpha * A * B: no bias / residual / activation (they would be applied once per K split)
+    if (p->d_dtype != B200_F32 || p->bias || p->residual || p->act || p->col_scale || (p->ldd * 4) % 16 || (p->stride_d * 4) % 16 ||
+        (reinterpret_cast<uintptr_t>(p->D) & 15))
+      return (int)cudaErrorInvalidValue;
+    g.reduce_add = 1;
+    g.tma_store = 0;
+    int splits = p->splits;
+    if (splits <= 0) {
+      // fill the GPU once: as many K splits as it takes for every SM to have a work item, at least 4 K blocks each
+      const long tiles = (long)g.tiles_m * g.tiles_n * g.batch;
+      splits = (int)(sms / tiles);
+      const int max_splits = (g.k_blocks + 3) / 4;
+      if (splits > max_splits) splits = max_splits;
+      if (splits < 1) splits = 1;
+    }
+    if (splits > g.k_blocks) splits = g.k_blocks;
+    g.kb_per_split = (g.k_blocks + splits - 1) / splits;
+    g.splits = (g.k_blocks + g.kb_per_split - 1) / g.kb_per_split;
+  }
   g.coef_bytes = (p->col_scale || (p->bias && !p->bias_per_row)) ? 2048 : 0;
-  const int smem_budget = 227 * 1024 - 2048 - g.coef_bytes - (g.tma_store ? 32768 : 0);
+  const int smem_budget = 227 * 1024 - 2048 - g.coef_bytes - ((g.tma_store || g.reduce_add) ? 32768 : 0);
   g.stages = smem_budget / stage_bytes;
   if (g.stages > GEMM_MAX_STAGES) g.stages = GEMM_MAX_STAGES;
-  if (g.stages > g.k_blocks + 1) g.stages = g.k_blocks + 1 < 2 ? 2 : g.k_blocks + 1;
+  if (g.stages > g.kb_per_split + 1) g.stages = g.kb_per_split + 1 < 2 ? 2 : g.kb_per_split + 1;
   if (g.stages < 2) g.stages = 2;
-  const size_t smem = (size_t)g.stages * stage_bytes + 1024 /*align*/ + 1024 /*barriers*/ + g.coef_bytes + (g.tma_store ? 32768 : 0);
+  const size_t smem = (size_t)g.stages * stage_bytes + 1024 /*align*/ + 1024 /*barriers*/ + g.coef_bytes +
+                      ((g.tma_store || g.reduce_add) ? 32768 : 0);
 
   CUtensorMap tmA, tmB;
   const uint64_t batch_a = (uint64_t)(p->batch > 1 ? p->stride_a : (int64_t)p->lda * (p->a_mn_major ? p->K : p->M));
@@ -530,13 +597,20 @@ extern "C" int b200_gemm(const B200GemmParams* p, void* stream) {
     rc = encode_tiled(&tmD, ddt, 3, p->D, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   }
+  if (g.reduce_add) {
+    uint64_t dims[3] = {(uint64_t)p->N, (uint64_t)p->M, (uint64_t)p->batch};
+    uint64_t str[2] = {(uint64_t)p->ldd * 4, (uint64_t)(p->batch > 1 ? p->stride_d : (int64_t)p->ldd * p->M) * 4};
+    uint32_t box[3] = {32, 32, 1};
+    rc = encode_tiled(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, p->D, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  }
   static bool attr_set[64] = {false};
   if (!attr_set[dev & 63]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return (int)e;
     attr_set[dev & 63] = true;
   }
-  const long total_tiles = (long)g.tiles_m * g.tiles_n * g.batch;
+  const long total_tiles = (long)g.tiles_m * g.tiles_n * g.batch * g.splits;
   int ctas = p->max_ctas > 0 ? p->max_ctas : sms;
   if (ctas > total_tiles) ctas = (int)total_tiles;
   gemm_tcgen05_kernel<<<ctas, GEMM_THREADS, smem, (cudaStream_t)stream>>>(tmA, tmB, tmD, g);

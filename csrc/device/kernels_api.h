@@ -100,6 +100,9 @@ typedef struct B200GemmParams {
   int tile_n;                            // 0 = choose automatically (32..256, multiple of 32)
   int max_ctas;                          // 0 = one per SM
   const float* col_scale;                // optional fp32 multiplier per output column (applied after alpha)
+  int accumulate;                        // 1: D (fp32) += alpha * A * B, added with tensor-map reductions (no bias /
+                                         // residual / activation); the K loop may then be split among CTAs
+  int splits;                            // accumulate only: K splits per output tile (0 = fill the GPU once)
 } B200GemmParams;
 B200_API int b200_gemm(const B200GemmParams* p, void* stream);
 
@@ -414,6 +417,7 @@ typedef struct B200FusedOptArgs {
                              // exchange region once every peer has finished reading it)
 } B200FusedOptArgs;
 B200_API long long b200_comm_shard_elems(long long n, int world, int dtype);
+B200_API long long b200_comm_nvls_min_bytes(void);  // messages at least this large use multimem when ctx->mc is set
 B200_API int b200_comm_allreduce_opt(const B200CommCtx* ctx, size_t grad_offset, size_t param_offset, long long n,
                                      int grad_dtype, float scale, const B200FusedOptArgs* opt, unsigned long long seq,
                                      void* stream);

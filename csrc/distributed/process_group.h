@@ -111,6 +111,8 @@ class ProcessGroupB200 : public c10d::Backend {
   int64_t status_word() const;
   void clear_status();
   int device_index() const { return device_; }
+  // True when the arena is bound to an NVSwitch multicast object (in-switch reductions are in use).
+  bool multicast_enabled();
   // Rank whose heartbeat stopped (it left without saying goodbye), or -1.  Set by the watchdog thread.
   int64_t dead_peer() const { return dead_peer_.load(); }
 

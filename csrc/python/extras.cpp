@@ -34,7 +34,8 @@ void bind_extras(py::module& m) {
       .def("status_word", &ProcessGroupB200::status_word)
       .def("dead_peer", &ProcessGroupB200::dead_peer)
       .def("clear_status", &ProcessGroupB200::clear_status)
-      .def("device_index", &ProcessGroupB200::device_index);
+      .def("device_index", &ProcessGroupB200::device_index)
+      .def("multicast_enabled", &ProcessGroupB200::multicast_enabled, py::call_guard<py::gil_scoped_release>());
   m.def("_stop_all_watchdogs", [] { stop_all_watchdogs(); }, py::call_guard<py::gil_scoped_release>());
   m.def("_kernel_launch_count", [] { return ops::kernel_launch_count(); });
   m.def("_reset_kernel_launch_count", [] { ops::reset_kernel_launch_count(); });

@@ -20,7 +20,11 @@ def _ngpu():
 
 WORLD = min(int(os.environ.get("CATCH_B200_TEST_WORLD", "2")), max(_ngpu(), 1))
 needs2 = pytest.mark.skipif(_ngpu() < 2, reason="needs two GPUs")
-ENV = {"NCCL_NVLS_ENABLE": "0"}
+# NCCL's own NVLS stays off in these child processes.  This backend's multicast mapping is forced on (by default it
+# starts at four ranks) wherever the GPUs support it, except in the test that makes a wait run out: that one runs
+# on plain peer loads and stores.
+ENV = {"NCCL_NVLS_ENABLE": "0", "CATCH_B200_NVLS": "1"}
+ENV_NO_MULTICAST = {"NCCL_NVLS_ENABLE": "0", "CATCH_B200_NVLS": "0"}
 
 
 def _init(rank, world):
@@ -202,4 +206,39 @@ def _bounded_wait(rank, world):
 
 @needs2
 def test_device_wait_is_bounded():
-    run_ranks(_bounded_wait, world=WORLD, env=ENV, timeout=240)
+    run_ranks(_bounded_wait, world=WORLD, env=ENV_NO_MULTICAST, timeout=240)
+
+
+def _multicast(rank, world, expect_on):
+    from catch_b200.distributed import get_backend
+
+    _init(rank, world)
+    pg = get_backend()
+    on = pg.multicast_enabled()
+    if not expect_on:
+        assert not on
+    # sums and averages of every floating type through whichever path the arena has, below and above the
+    # size at which the in-switch kernels take over
+    for dtype, tol in ((torch.float32, 1e-6), (torch.bfloat16, 2e-2), (torch.float16, 2e-3)):
+        for n in (1000, 70001, (1 << 20) + 8, 3 << 20):
+            torch.manual_seed(n)
+            base = torch.randn(n)
+            t = pg.symm_empty(n, dtype)
+            t.copy_((base * (rank + 1)).to(dtype))
+            dist.barrier()
+            pg.allreduce_symm(t, 0, 0.5).wait()
+            torch.b200.synchronize()
+            ref = sum((base * (r + 1)).to(dtype).float() for r in range(world)) * 0.5
+            err = (t.float().cpu() - ref).abs().max().item()
+            assert err <= tol * max(1.0, ref.abs().max().item()), (dtype, n, err, on)
+    dist.barrier()
+    torch.b200.synchronize()
+    if rank == 0:
+        print(f"multicast mapping in use: {on}")
+    dist.destroy_process_group()
+
+
+@needs2
+@pytest.mark.parametrize("multicast", [True, False])
+def test_allreduce_with_and_without_multicast(multicast):
+    run_ranks(_multicast, world=WORLD, args=(multicast,), env=ENV if multicast else ENV_NO_MULTICAST, timeout=240)
