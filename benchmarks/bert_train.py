@@ -35,6 +35,7 @@ def main():
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--seq", type=int, default=128)
     ap.add_argument("--layers", type=int, default=12)
+    ap.add_argument("--no-fuse", action="store_true", help="ours: keep the unfused module definitions")
     args = ap.parse_args()
     rank, local, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     torch.manual_seed(0)
@@ -63,6 +64,8 @@ def main():
         if world > 1:
             os.environ.setdefault("CATCH_B200_SYMM_USER_MB", "2048")
             dist.init_process_group("bwccl")
+        if not args.no_fuse:
+            _bert.fuse_bert(model)   # fused residual blocks, copy-free attention products, linears with bucket gradients
         net = FusedDataParallel(model.to(dev), "adamw", lr=2e-5, weight_decay=0.01)
         sync, mk, rec = torch.b200.synchronize, (lambda: torch.b200.Notifier()), (lambda e: e.place())
         finish = net.step
@@ -89,9 +92,18 @@ def main():
     ms = torch.tensor([a.elapsed_time(b) / args.steps], device=dev)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    launches = None
+    if not args.stock:
+        import catch_b200 as _pkg
+
+        _pkg._C._reset_kernel_launch_count()
+        step()
+        sync()
+        launches = int(_pkg._C._kernel_launch_count())
     if rank == 0:
         print(f"{'stock' if args.stock else 'catch_b200'} BERT-base x{world}: {ms.item():.2f} ms/step, "
-              f"{world * args.batch / ms.item() * 1e3:.1f} sequences/sec, loss {loss.item():.4f}")
+              f"{world * args.batch / ms.item() * 1e3:.1f} sequences/sec, loss {loss.item():.4f}"
+              + (f", {launches} kernel launches per step" if launches is not None else ""))
     if world > 1:
         dist.destroy_process_group()
 

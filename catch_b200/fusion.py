@@ -149,6 +149,142 @@ class BatchNormAct2d(nn.BatchNorm2d):
         return F.relu(y) if self.act == 1 else y
 
 
+class _LinearFn(torch.autograd.Function):
+    """``x @ weight^T + bias`` in a 16-bit compute dtype with fp32 master parameters.
+
+    Forward reads the parameter's 16-bit copy (``weight._b200_lowp``, kept current by the data-parallel wrapper's
+    optimizer kernel) instead of casting the weight; backward computes the weight gradient in fp32 with the K
+    dimension (all tokens) split over the whole GPU and adds it, like the bias gradient, straight into the
+    parameter's gradient bucket when there is one (``param._b200_grad_acc``)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, compute_dtype):
+        lowp = getattr(weight, "_b200_lowp", None)
+        if weight.dtype == compute_dtype:
+            w = weight
+        elif lowp is not None and lowp.dtype == compute_dtype and lowp.shape == weight.shape:
+            w = lowp
+        else:
+            w = weight.to(compute_dtype)
+        y = torch.ops.catch_b200.linear_act(x, w, bias, 0)
+        ctx.save_for_backward(x, w)
+        ctx.params = (weight, bias)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad):
+        x, w = ctx.saved_tensors
+        weight, bias = ctx.params
+        need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        need_db = bias is not None and ctx.needs_input_grad[2]
+
+        def bucket(p, need):
+            acc = getattr(p, "_b200_grad_acc", None) if (need and p is not None) else None
+            return acc if (acc is not None and p.grad is not None and p.grad.dtype == torch.float32 and p.dtype == torch.float32) else None
+
+        acc_w, acc_b = bucket(weight, need_dw), bucket(bias, need_db)
+        dx, dw, db = torch.ops.catch_b200.linear_backward_fp32w(grad, x, w, need_dx, need_dw, need_db, acc_w, acc_b)
+        if dw is not None and weight.dtype != torch.float32:
+            dw = dw.to(weight.dtype)
+        if db is not None and bias.dtype != torch.float32:
+            db = db.to(bias.dtype)
+        # gradients that went into a bucket come back undefined; the parameters' post-accumulate hooks still fire
+        return dx, dw, db, None
+
+
+class FusedLinear(nn.Linear):
+    """``nn.Linear`` whose autocast path runs through ``_LinearFn`` (same parameters, same state dict)."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if _device_kernels_available(x) and x.numel() > 0 and self.in_features % 8 == 0 and self.out_features % 8 == 0:
+            autocast = torch.is_autocast_enabled("blackwell")
+            cd = torch.get_autocast_dtype("blackwell") if autocast else x.dtype
+            if cd in (torch.bfloat16, torch.float16) and (autocast or self.weight.dtype == x.dtype):
+                if x.dtype != cd:
+                    x = x.to(cd)
+                with torch.autocast("blackwell", enabled=False):
+                    return _LinearFn.apply(x, self.weight, self.bias, cd)
+        return super().forward(x)
+
+
+def fuse_linear(model: nn.Module) -> nn.Module:
+    """Switch every plain ``nn.Linear`` of ``model`` to ``FusedLinear`` in place (returns the model)."""
+    for m in model.modules():
+        if type(m) is nn.Linear:
+            m.__class__ = FusedLinear
+    return model
+
+
+class _MatmulNdFn(torch.autograd.Function):
+    """``alpha * a @ b`` over 4-D operands with arbitrary batch strides (``torch.ops.catch_b200.gemm_nd``).
+
+    Head-split views ``[batch, heads, seq, dim]`` of ``[batch, seq, heads * dim]`` activations are multiplied as they
+    are; gradients are produced in the memory layout of the operand they belong to, so the view / permute nodes
+    around the call never have to copy either."""
+
+    @staticmethod
+    def forward(ctx, a, b, alpha, out_strides):
+        ctx.save_for_backward(a, b)
+        ctx.alpha = alpha
+        out = None
+        if out_strides is not None:
+            out = torch.empty_strided(a.shape[:3] + b.shape[3:], out_strides, dtype=a.dtype, device=a.device)
+        return torch.ops.catch_b200.gemm_nd(a, b, out, alpha)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, b = ctx.saved_tensors
+        da = db = None
+        if ctx.needs_input_grad[0]:
+            da = torch.empty_strided(a.shape, a.stride(), dtype=a.dtype, device=a.device) if a.is_non_overlapping_and_dense() \
+                else torch.empty_like(a)
+            torch.ops.catch_b200.gemm_nd(g, b.transpose(-1, -2), da, ctx.alpha)
+        if ctx.needs_input_grad[1]:
+            db = torch.empty_strided(b.shape, b.stride(), dtype=b.dtype, device=b.device) if b.is_non_overlapping_and_dense() \
+                else torch.empty_like(b)
+            if db.stride(-1) != 1:   # the kernel writes rows: produce the transposed product into the transposed view
+                torch.ops.catch_b200.gemm_nd(g.transpose(-1, -2), a, db.transpose(-1, -2), ctx.alpha)
+            else:
+                torch.ops.catch_b200.gemm_nd(a.transpose(-1, -2), g, db, ctx.alpha)
+        return da, db, None, None
+
+
+def matmul_nd(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, out_strides=None) -> torch.Tensor:
+    """Batched ``alpha * a @ b`` for 4-D 16-bit tensors on the device without copying strided operands.
+    ``out_strides`` (optional, innermost 1) chooses the memory layout of the result, e.g. that of a
+    ``[batch, seq, heads, dim]`` buffer seen as ``[batch, heads, seq, dim]``."""
+    return _MatmulNdFn.apply(a, b, alpha, out_strides)
+
+
+class _DropoutAddLayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, residual, weight, bias, p, training, eps):
+        y, s, mask, mean, rstd = torch.ops.catch_b200.dropout_add_layer_norm(h, residual, weight, bias, p, training, eps)
+        ctx.save_for_backward(s, mask, weight, mean, rstd)
+        ctx.p = p if training else 0.0
+        ctx.params = (weight, bias)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        s, mask, weight, mean, rstd = ctx.saved_tensors
+        ds, dh, dgamma, dbeta = torch.ops.catch_b200.dropout_add_layer_norm_backward(dy, s, mask, weight, mean, rstd, ctx.p)
+        w, b = ctx.params
+        return (dh, ds, dgamma.to(w.dtype) if w is not None else None, dbeta.to(b.dtype) if b is not None else None,
+                None, None, None)
+
+
+def dropout_add_layer_norm(h: torch.Tensor, residual: torch.Tensor, norm: nn.LayerNorm, p: float, training: bool) -> torch.Tensor:
+    """``norm(residual + dropout(h))`` as one kernel (forward) and one kernel (backward) on the device."""
+    ok = (_device_kernels_available(h) and h.dtype in (torch.bfloat16, torch.float16, torch.float32) and h.dtype == residual.dtype
+          and h.shape == residual.shape and len(norm.normalized_shape) == 1 and h.shape[-1] % 4 == 0 and h.shape[-1] <= 1536
+          and h.numel() > 0)
+    if not ok:
+        return norm(residual + F.dropout(h, p, training))
+    with torch.autocast("blackwell", enabled=False):
+        return _DropoutAddLayerNormFn.apply(h, residual, norm.weight, norm.bias, float(p), bool(training), float(norm.eps))
+
+
 def _feeds_only(node: fx.Node, consumer: fx.Node) -> bool:
     return len(node.users) == 1 and next(iter(node.users)) is consumer
 

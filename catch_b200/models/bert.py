@@ -92,6 +92,60 @@ class BertLayer(nn.Module):
         return self.out_norm(x + self.dropout(self.output(self.act(self.intermediate(x)))))
 
 
+class FusedBertSelfAttention(BertSelfAttention):
+    """Same parameters; the head split is a view and the two batched products read / write those views directly
+    (``catch_b200.fusion.matmul_nd``), so no [batch * heads, seq, dim] copies are made in either direction."""
+
+    def forward(self, x, mask=None):
+        from catch_b200.fusion import matmul_nd
+
+        if x.device.type != "blackwell" or not torch.is_autocast_enabled("blackwell"):
+            return super().forward(x, mask)
+        B, L, H = x.shape
+        cd = torch.get_autocast_dtype("blackwell")
+
+        def heads(t):  # [B, L, H] -> [B, h, L, d] view
+            return t.to(cd).view(B, L, self.h, self.d).permute(0, 2, 1, 3)
+
+        q, k, v = heads(self.query(x)), heads(self.key(x)), heads(self.value(x))
+        scores = matmul_nd(q, k.transpose(-1, -2), 1.0 / math.sqrt(self.d))
+        if mask is not None:
+            scores = scores + mask.to(scores.dtype)
+        with torch.autocast("blackwell", enabled=False):  # the softmax kernel computes in fp32 whatever the storage type
+            probs = torch.softmax(scores, dim=-1)
+        probs = self.dropout(probs)
+        # the context is produced straight in [B, L, h, d] memory, seen as [B, h, L, d] by the product
+        ctx = matmul_nd(probs, v, 1.0, (L * H, self.d, H, 1))
+        return ctx.permute(0, 2, 1, 3).reshape(B, L, H)
+
+
+class FusedBertLayer(BertLayer):
+    """Same parameters; ``norm(x + dropout(h))`` runs as one fused kernel per direction."""
+
+    def forward(self, x, mask=None):
+        from catch_b200.fusion import dropout_add_layer_norm
+
+        if x.device.type != "blackwell":
+            return super().forward(x, mask)
+        h = self.attn_out(self.attention(x, mask))
+        x = dropout_add_layer_norm(h, x.to(h.dtype), self.attn_norm, self.dropout.p, self.training)
+        h = self.output(self.act(self.intermediate(x)))
+        return dropout_add_layer_norm(h, x.to(h.dtype), self.out_norm, self.dropout.p, self.training)
+
+
+def fuse_bert(model: nn.Module) -> nn.Module:
+    """Switch the layers of a BERT model to their fused forms and its linears to ``FusedLinear`` (in place; the
+    parameters and the state dict are unchanged)."""
+    from catch_b200.fusion import fuse_linear
+
+    for m in model.modules():
+        if type(m) is BertLayer:
+            m.__class__ = FusedBertLayer
+        elif type(m) is BertSelfAttention:
+            m.__class__ = FusedBertSelfAttention
+    return fuse_linear(model)
+
+
 class BertForSequenceClassification(nn.Module):
     def __init__(self, config: BertConfig = None):
         super().__init__()

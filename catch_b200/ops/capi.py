@@ -27,7 +27,8 @@ class GemmParams(C.Structure):
         ("bias", C.c_void_p), ("bias_dtype", C.c_int), ("bias_per_row", C.c_int),
         ("residual", C.c_void_p), ("ldr", C.c_int64), ("stride_r", C.c_int64), ("res_dtype", C.c_int),
         ("alpha", C.c_float), ("beta", C.c_float), ("act", C.c_int), ("tile_n", C.c_int), ("max_ctas", C.c_int),
-        ("col_scale", C.c_void_p), ("accumulate", C.c_int), ("splits", C.c_int),
+        ("col_scale", C.c_void_p), ("batch_inner", C.c_int), ("stride_a2", C.c_int64), ("stride_b2", C.c_int64),
+        ("stride_d2", C.c_int64), ("stride_r2", C.c_int64), ("accumulate", C.c_int), ("splits", C.c_int),
     ]
 
 

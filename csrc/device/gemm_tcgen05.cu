@@ -43,12 +43,13 @@ struct GemmKernelArgs {
   uint32_t idesc;
   int mn_lbo, mn_sbo, mn_kstep;  // descriptor fields of MN-major operands (bytes)
   void* D;
-  int64_t ldd, stride_d;
+  int64_t ldd, stride_d, stride_d2;
+  int batch_inner;      // the batch index bz splits into (bz / batch_inner, bz % batch_inner): two batch strides per operand
   int d_dtype;
   const void* bias;
   int bias_dtype, bias_per_row;
   const void* residual;
-  int64_t ldr, stride_r;
+  int64_t ldr, stride_r, stride_r2;
   int res_dtype;
   float alpha, beta;
   int act;
@@ -184,6 +185,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int item = blockIdx.x; item < total_tiles && !failed; item += gridDim.x) {
         const int tile = item / g.splits, split = item - tile * g.splits;
         const int bz = tile / tiles_per_batch;
+        const int bo = bz / g.batch_inner, bi = bz - bo * g.batch_inner;
         const int t = tile - bz * tiles_per_batch;
         const int m0 = (t % g.tiles_m) * GEMM_BM;
         const int n0 = (t / g.tiles_m) * g.tile_n;
@@ -195,18 +197,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           uint8_t* sb = sa + GEMM_A_STAGE_BYTES;
           const int k0 = kb * bk_elems;
           if (!g.a_mn) {
-            tma_load_3d(sa, &tmA, &full_bar[stage], k0, m0, bz);
+            tma_load_4d(sa, &tmA, &full_bar[stage], k0, m0, bi, bo);
           } else {
             const int blk_bytes = bk_elems * 128;
             for (int i = 0; i < GEMM_BM / mn_block; ++i)
-              tma_load_3d(sa + i * blk_bytes, &tmA, &full_bar[stage], m0 + i * mn_block, k0, bz);
+              tma_load_4d(sa + i * blk_bytes, &tmA, &full_bar[stage], m0 + i * mn_block, k0, bi, bo);
           }
           if (!g.b_mn) {
-            tma_load_3d(sb, &tmB, &full_bar[stage], k0, n0, bz);
+            tma_load_4d(sb, &tmB, &full_bar[stage], k0, n0, bi, bo);
           } else {
             const int blk_bytes = bk_elems * 128;
             for (int i = 0; i < g.tile_n / mn_block; ++i)
-              tma_load_3d(sb + i * blk_bytes, &tmB, &full_bar[stage], n0 + i * mn_block, k0, bz);
+              tma_load_4d(sb + i * blk_bytes, &tmB, &full_bar[stage], n0 + i * mn_block, k0, bi, bo);
           }
           if (++stage == g.stages) { stage = 0; phase ^= 1; }
         }
@@ -259,6 +261,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (int item = blockIdx.x; item < total_tiles && !failed; item += gridDim.x, ++tile_iter) {
       const int tile = item / g.splits;
       const int bz = tile / tiles_per_batch;
+      const int bo = bz / g.batch_inner, bi = bz - bo * g.batch_inner;
       const int t = tile - bz * tiles_per_batch;
       const int m0 = (t % g.tiles_m) * GEMM_BM;
       const int n0 = (t / g.tiles_m) * g.tile_n;
@@ -279,9 +282,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const bool row_ok = row < g.M;
       const float row_bias = (g.bias && g.bias_per_row && row_ok) ? load_scalar(g.bias, row, g.bias_dtype) : 0.f;
       uint8_t* drow = static_cast<uint8_t*>(g.D) +
-                      ((size_t)bz * g.stride_d + (size_t)row * g.ldd) * (g.d_dtype == B200_F32 ? 4 : 2);
+                      ((size_t)bi * g.stride_d + (size_t)bo * g.stride_d2 + (size_t)row * g.ldd) * (g.d_dtype == B200_F32 ? 4 : 2);
       const uint8_t* rrow = g.residual ? static_cast<const uint8_t*>(g.residual) +
-                                             ((size_t)bz * g.stride_r + (size_t)row * g.ldr) *
+                                             ((size_t)bi * g.stride_r + (size_t)bo * g.stride_r2 + (size_t)row * g.ldr) *
                                                  (g.res_dtype == B200_F32 ? 4 : 2)
                                        : nullptr;
       if (g.reduce_add) {
@@ -308,7 +311,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_reduce_add_3d(&tmD, sbuf, n0 + c, m0 + quarter * 32, bz);
+            tma_reduce_add_4d(&tmD, sbuf, n0 + c, m0 + quarter * 32, bi, bo);
             tma_store_commit();
           }
         }
@@ -369,7 +372,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_3d(&tmD, sbuf, n0 + cb, m0 + quarter * 32, bz);  // rows / columns outside the matrix are clipped
+            tma_store_4d(&tmD, sbuf, n0 + cb, m0 + quarter * 32, bi, bo);  // rows / columns outside the matrix are clipped
             tma_store_commit();
           }
         }
@@ -488,8 +491,12 @@ extern "C" int b200_gemm(const B200GemmParams* p, void* stream) {
                                                            : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   auto ok16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   if (!ok16(p->A) || !ok16(p->B) || (p->lda * es) % 16 || (p->ldb * es) % 16 || (p->stride_a * es) % 16 ||
-      (p->stride_b * es) % 16)
+      (p->stride_b * es) % 16 || (p->stride_a2 * es) % 16 || (p->stride_b2 * es) % 16)
     return (int)cudaErrorInvalidValue;
+  // batch = outer x inner; with batch_inner == 0 (the usual case) there is one batch stride per operand
+  const int inner = p->batch_inner > 0 ? p->batch_inner : p->batch;
+  if (p->batch % inner) return (int)cudaErrorInvalidValue;
+  const int outer = p->batch / inner;
 
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -516,15 +523,17 @@ extern "C" int b200_gemm(const B200GemmParams* p, void* stream) {
   g.mn_sbo = 1024;
   g.mn_lbo = bk * 128;
   g.mn_kstep = (32 / es) * 128;
-  g.D = p->D; g.ldd = p->ldd; g.stride_d = p->stride_d; g.d_dtype = p->d_dtype;
+  g.D = p->D; g.ldd = p->ldd; g.stride_d = p->stride_d; g.stride_d2 = p->stride_d2; g.d_dtype = p->d_dtype;
+  g.batch_inner = inner;
   g.bias = p->bias; g.bias_dtype = p->bias_dtype; g.bias_per_row = p->bias_per_row;
-  g.residual = p->residual; g.ldr = p->ldr; g.stride_r = p->stride_r; g.res_dtype = p->res_dtype;
+  g.residual = p->residual; g.ldr = p->ldr; g.stride_r = p->stride_r; g.stride_r2 = p->stride_r2; g.res_dtype = p->res_dtype;
   g.alpha = p->alpha; g.beta = p->beta; g.act = p->act;
   g.err = error_flag_ptr();
   if (!g.err) return (int)cudaErrorInvalidDevice;
 
   const int stage_bytes = GEMM_A_STAGE_BYTES + g.tile_n * 128;
   g.tma_store = (p->d_dtype != B200_F32 && g.tile_n % 64 == 0 && (p->ldd * 2) % 16 == 0 && (p->stride_d * 2) % 16 == 0 &&
+                 (p->stride_d2 * 2) % 16 == 0 &&
                  (reinterpret_cast<uintptr_t>(p->D) & 15) == 0)
                     ? 1 : 0;
   g.reduce_add = 0;
@@ -560,48 +569,58 @@ extern "C" int b200_gemm(const B200GemmParams* p, void* stream) {
                       ((g.tma_store || g.reduce_add) ? 32768 : 0);
 
   CUtensorMap tmA, tmB;
-  const uint64_t batch_a = (uint64_t)(p->batch > 1 ? p->stride_a : (int64_t)p->lda * (p->a_mn_major ? p->K : p->M));
-  const uint64_t batch_b = (uint64_t)(p->batch > 1 ? p->stride_b : (int64_t)p->ldb * (p->b_mn_major ? p->K : p->N));
+  // batch strides: a single-level batch of one matrix still needs a non-zero, 16-byte-multiple stride in the map
+  auto bstride = [&](int64_t given, int64_t dflt) { return (uint64_t)((given > 0 ? given : dflt) * es); };
+  const int64_t span_a = (int64_t)p->lda * (p->a_mn_major ? p->K : p->M), span_b = (int64_t)p->ldb * (p->b_mn_major ? p->K : p->N);
+  const uint64_t ba1 = bstride(p->stride_a, span_a), ba2 = bstride(p->stride_a2, span_a * inner);
+  const uint64_t bb1 = bstride(p->stride_b, span_b), bb2 = bstride(p->stride_b2, span_b * inner);
   int rc;
   if (!p->a_mn_major) {
-    uint64_t dims[3] = {(uint64_t)p->K, (uint64_t)p->M, (uint64_t)p->batch};
-    uint64_t str[2] = {(uint64_t)p->lda * es, batch_a * es};
-    uint32_t box[3] = {(uint32_t)bk, GEMM_BM, 1};
-    rc = encode_tiled(&tmA, dt, 3, p->A, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
+    uint64_t dims[4] = {(uint64_t)p->K, (uint64_t)p->M, (uint64_t)inner, (uint64_t)outer};
+    uint64_t str[3] = {(uint64_t)p->lda * es, ba1, ba2};
+    uint32_t box[4] = {(uint32_t)bk, GEMM_BM, 1, 1};
+    rc = encode_tiled(&tmA, dt, 4, p->A, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
   } else {
-    uint64_t dims[3] = {(uint64_t)p->M, (uint64_t)p->K, (uint64_t)p->batch};
-    uint64_t str[2] = {(uint64_t)p->lda * es, batch_a * es};
-    uint32_t box[3] = {(uint32_t)mn_block, (uint32_t)bk, 1};
-    rc = encode_tiled(&tmA, dt, 3, p->A, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
+    uint64_t dims[4] = {(uint64_t)p->M, (uint64_t)p->K, (uint64_t)inner, (uint64_t)outer};
+    uint64_t str[3] = {(uint64_t)p->lda * es, ba1, ba2};
+    uint32_t box[4] = {(uint32_t)mn_block, (uint32_t)bk, 1, 1};
+    rc = encode_tiled(&tmA, dt, 4, p->A, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
   }
   if (rc) return rc;
   if (!p->b_mn_major) {
-    uint64_t dims[3] = {(uint64_t)p->K, (uint64_t)p->N, (uint64_t)p->batch};
-    uint64_t str[2] = {(uint64_t)p->ldb * es, batch_b * es};
-    uint32_t box[3] = {(uint32_t)bk, (uint32_t)g.tile_n, 1};
-    rc = encode_tiled(&tmB, dt, 3, p->B, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
+    uint64_t dims[4] = {(uint64_t)p->K, (uint64_t)p->N, (uint64_t)inner, (uint64_t)outer};
+    uint64_t str[3] = {(uint64_t)p->ldb * es, bb1, bb2};
+    uint32_t box[4] = {(uint32_t)bk, (uint32_t)g.tile_n, 1, 1};
+    rc = encode_tiled(&tmB, dt, 4, p->B, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
   } else {
-    uint64_t dims[3] = {(uint64_t)p->N, (uint64_t)p->K, (uint64_t)p->batch};
-    uint64_t str[2] = {(uint64_t)p->ldb * es, batch_b * es};
-    uint32_t box[3] = {(uint32_t)mn_block, (uint32_t)bk, 1};
-    rc = encode_tiled(&tmB, dt, 3, p->B, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
+    uint64_t dims[4] = {(uint64_t)p->N, (uint64_t)p->K, (uint64_t)inner, (uint64_t)outer};
+    uint64_t str[3] = {(uint64_t)p->ldb * es, bb1, bb2};
+    uint32_t box[4] = {(uint32_t)mn_block, (uint32_t)bk, 1, 1};
+    rc = encode_tiled(&tmB, dt, 4, p->B, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
   }
   if (rc) return rc;
 
+  const int64_t span_d = (int64_t)p->ldd * p->M;
+  g.stride_d = p->stride_d > 0 ? p->stride_d : span_d;
+  g.stride_d2 = p->stride_d2 > 0 ? p->stride_d2 : g.stride_d * inner;
+  if (p->residual) {
+    g.stride_r = p->batch > 1 ? p->stride_r : 0;
+    g.stride_r2 = p->stride_r2 > 0 ? p->stride_r2 : g.stride_r * inner;
+  }
   CUtensorMap tmD = tmA;
   if (g.tma_store) {
     const CUtensorMapDataType ddt = p->d_dtype == B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-    uint64_t dims[3] = {(uint64_t)p->N, (uint64_t)p->M, (uint64_t)p->batch};
-    uint64_t str[2] = {(uint64_t)p->ldd * 2, (uint64_t)(p->batch > 1 ? p->stride_d : (int64_t)p->ldd * p->M) * 2};
-    uint32_t box[3] = {64, 32, 1};  // one epilogue warp stores 32 rows at a time
-    rc = encode_tiled(&tmD, ddt, 3, p->D, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
+    uint64_t dims[4] = {(uint64_t)p->N, (uint64_t)p->M, (uint64_t)inner, (uint64_t)outer};
+    uint64_t str[3] = {(uint64_t)p->ldd * 2, (uint64_t)g.stride_d * 2, (uint64_t)g.stride_d2 * 2};
+    uint32_t box[4] = {64, 32, 1, 1};  // one epilogue warp stores 32 rows at a time
+    rc = encode_tiled(&tmD, ddt, 4, p->D, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   }
   if (g.reduce_add) {
-    uint64_t dims[3] = {(uint64_t)p->N, (uint64_t)p->M, (uint64_t)p->batch};
-    uint64_t str[2] = {(uint64_t)p->ldd * 4, (uint64_t)(p->batch > 1 ? p->stride_d : (int64_t)p->ldd * p->M) * 4};
-    uint32_t box[3] = {32, 32, 1};
-    rc = encode_tiled(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, p->D, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
+    uint64_t dims[4] = {(uint64_t)p->N, (uint64_t)p->M, (uint64_t)inner, (uint64_t)outer};
+    uint64_t str[3] = {(uint64_t)p->ldd * 4, (uint64_t)g.stride_d * 4, (uint64_t)g.stride_d2 * 4};
+    uint32_t box[4] = {32, 32, 1, 1};
+    rc = encode_tiled(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p->D, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   }
   static bool attr_set[64] = {false};

@@ -100,6 +100,10 @@ typedef struct B200GemmParams {
   int tile_n;                            // 0 = choose automatically (32..256, multiple of 32)
   int max_ctas;                          // 0 = one per SM
   const float* col_scale;                // optional fp32 multiplier per output column (applied after alpha)
+  // Two-level batches (e.g. [batch, heads] views of [batch, seq, heads, dim] tensors): batch = outer x batch_inner and
+  // matrix (o, i) of an operand starts at i * stride_x + o * stride_x2.  batch_inner == 0: one level (stride_x only).
+  int batch_inner;
+  int64_t stride_a2, stride_b2, stride_d2, stride_r2;
   int accumulate;                        // 1: D (fp32) += alpha * A * B, added with tensor-map reductions (no bias /
                                          // residual / activation); the K loop may then be split among CTAs
   int splits;                            // accumulate only: K splits per output tile (0 = fill the GPU once)
@@ -367,6 +371,22 @@ B200_API int b200_rng_bernoulli(void* out, int dtype, long long n, unsigned long
 // y = x * mask / (1-p); mask is uint8 (bool)
 B200_API int b200_dropout_fwd(const void* x, int dtype, long long n, unsigned long long seed, unsigned long long offset,
                               float p, void* y, unsigned char* mask, void* stream);
+
+// dx = dy * mask * scale (mask: one byte per element)
+B200_API int b200_dropout_bwd(const void* dy, const unsigned char* mask, int dtype, long long n, float scale, void* dx,
+                              void* stream);
+// Fused transformer residual block (fused_norm.cu): s = residual + dropout(h); y = LayerNorm(s) * gamma + beta.
+// mask holds one byte per vector of four elements (bit k = element k kept); cols % 4 == 0 and
+// cols <= b200_dropout_add_layernorm_max_cols().  Backward: ds (gradient of s, i.e. of the residual) and
+// dh = ds * keep / (1 - p); dgamma / dbeta (fp32, zeroed by the caller) are accumulated with atomics.
+B200_API int b200_dropout_add_layernorm_max_cols(void);
+B200_API int b200_dropout_add_layernorm_fwd(const void* h, const void* residual, int dtype, long long rows, int cols, float p,
+                                            unsigned long long seed, unsigned long long offset, const void* gamma,
+                                            const void* beta, int param_dtype, float eps, void* y, void* s_out,
+                                            unsigned char* mask, float* mean, float* rstd, void* stream);
+B200_API int b200_dropout_add_layernorm_bwd(const void* dy, const void* s, const unsigned char* mask, int dtype, long long rows,
+                                            int cols, float p, const void* gamma, int param_dtype, const float* mean,
+                                            const float* rstd, void* ds, void* dh, float* dgamma, float* dbeta, void* stream);
 
 // ---- debug dump kernel ---------------------------------------------------------------------------------------
 // Prints up to `count` elements of a device tensor with device-side printf.

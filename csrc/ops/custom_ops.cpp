@@ -43,6 +43,17 @@ std::tuple<at::Tensor, at::Tensor> conv_backward_fp32w_device(const at::Tensor& 
                                                               const std::optional<at::Tensor>& accum);
 std::tuple<at::Tensor, at::Tensor> conv_stats_device(const at::Tensor& input, const at::Tensor& weight, at::IntArrayRef stride,
                                                      at::IntArrayRef padding);
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> dropout_add_layer_norm(
+    const at::Tensor& h, const at::Tensor& residual, const std::optional<at::Tensor>& weight, const std::optional<at::Tensor>& bias,
+    double p, bool training, double eps);
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> dropout_add_layer_norm_backward(
+    const at::Tensor& dy, const at::Tensor& s, const at::Tensor& mask, const std::optional<at::Tensor>& weight,
+    const at::Tensor& mean, const at::Tensor& rstd, double p);
+at::Tensor gemm_nd(const at::Tensor& a, const at::Tensor& b, const std::optional<at::Tensor>& out, double alpha);
+std::tuple<at::Tensor, at::Tensor, at::Tensor> linear_backward_fp32w(const at::Tensor& grad, const at::Tensor& x, const at::Tensor& w,
+                                                                     bool need_dx, bool need_dw, bool need_db,
+                                                                     const std::optional<at::Tensor>& accum_w,
+                                                                     const std::optional<at::Tensor>& accum_b);
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_backward(
     const at::Tensor& grad_out, const at::Tensor& out, const at::Tensor& input, const std::optional<at::Tensor>& weight,
     const std::optional<at::Tensor>& running_mean, const at::Tensor& save_mean, const at::Tensor& save_invstd, bool training,
@@ -98,6 +109,18 @@ TORCH_LIBRARY(catch_b200, m) {
   // needed).  With `accum` (flat fp32, memory order [K][R][S][C]) the weight gradient is added into it in place.
   m.def("conv2d_backward_fp32w(Tensor grad, Tensor input, Tensor weight, int[] stride, int[] padding, bool need_dx, "
         "bool need_dw, Tensor(a!)? accum=None) -> (Tensor, Tensor)");
+  // backward of a 16-bit linear layer with fp32 master weights: (grad_input, grad_weight fp32, grad_bias fp32); with
+  // accum_w / accum_b the parameter gradients are added into those flat fp32 buffers and not returned
+  m.def("linear_backward_fp32w(Tensor grad, Tensor input, Tensor weight, bool need_dx, bool need_dw, bool need_db, "
+        "Tensor(a!)? accum_w=None, Tensor(b!)? accum_b=None) -> (Tensor, Tensor, Tensor)");
+  // alpha * a @ b over 4-D operands [B1, B2, M, K] x [B1, B2, K, N] with arbitrary batch strides (no head-split copies);
+  // `out` may be a strided [B1, B2, M, N] view
+  m.def("gemm_nd(Tensor a, Tensor b, Tensor(a!)? out=None, float alpha=1.0) -> Tensor");
+  // s = residual + dropout(h); y = layer_norm(s): (y, s, mask, mean, rstd), one kernel; and its backward (ds, dh, dgamma, dbeta)
+  m.def("dropout_add_layer_norm(Tensor h, Tensor residual, Tensor? weight, Tensor? bias, float p, bool training, float eps) -> "
+        "(Tensor, Tensor, Tensor, Tensor, Tensor)");
+  m.def("dropout_add_layer_norm_backward(Tensor dy, Tensor s, Tensor mask, Tensor? weight, Tensor mean, Tensor rstd, float p) -> "
+        "(Tensor, Tensor, Tensor, Tensor)");
   m.def("batch_norm_act_backward(Tensor grad_out, Tensor out, Tensor input, Tensor? weight, Tensor? running_mean, "
         "Tensor save_mean, Tensor save_invstd, bool training, int act, bool has_residual) -> (Tensor, Tensor, Tensor, Tensor)");
 }
@@ -113,6 +136,10 @@ TORCH_LIBRARY_IMPL(catch_b200, CompositeExplicitAutograd, m) {
   m.impl("conv2d_stats", TORCH_FN(conv_stats_device));
   m.impl("conv2d_backward_fp32w", TORCH_FN(conv_backward_fp32w_device));
   m.impl("batch_norm_act_mask", TORCH_FN(batch_norm_act_mask));
+  m.impl("linear_backward_fp32w", TORCH_FN(linear_backward_fp32w));
+  m.impl("gemm_nd", TORCH_FN(gemm_nd));
+  m.impl("dropout_add_layer_norm", TORCH_FN(dropout_add_layer_norm));
+  m.impl("dropout_add_layer_norm_backward", TORCH_FN(dropout_add_layer_norm_backward));
   m.impl("batch_norm_act_backward", TORCH_FN(batch_norm_act_backward));
 }
 

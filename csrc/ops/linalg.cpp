@@ -57,8 +57,9 @@ Operand prep(const Tensor& x, int64_t rows_dim, int64_t k_dim) {
 }
 
 // out[b, M, N] = act(alpha * a @ b + bias + beta * res)
+// accumulate: out is fp32 and receives out += alpha * a @ b (K may be split among CTAs)
 void run_gemm(const Tensor& a, const Tensor& b, Tensor& out, const Tensor* bias, const Tensor* res, double alpha,
-              double beta, int act) {
+              double beta, int act, bool accumulate = false) {
   const bool batched = a.dim() == 3;
   const int64_t M = a.size(-2), K = a.size(-1), N = b.size(-1);
   OpScope scope("gemm", out);
@@ -84,6 +85,7 @@ void run_gemm(const Tensor& a, const Tensor& b, Tensor& out, const Tensor* bias,
     p.res_dtype = to_b200_dtype(res->scalar_type());
   }
   p.alpha = (float)alpha; p.beta = (float)beta; p.act = act;
+  p.accumulate = accumulate ? 1 : 0;
   B200_KERNEL_CHECK(b200_gemm(&p, scope.stream()));
 }
 
@@ -208,6 +210,109 @@ at::Tensor linear_act(const at::Tensor& x, const at::Tensor& w, const std::optio
     run_gemm(x2, bt, out, bp, nullptr, 1.0, 0.0, (int)act);
   }
   return out.reshape(osz);
+}
+
+// out[o, i] = alpha * a[o, i] @ b[o, i] over 4-D operands [B1, B2, M, K] x [B1, B2, K, N] with arbitrary batch strides:
+// head-split views of [batch, seq, heads * dim] activations multiply without being copied into [batch * heads, ...]
+// first, and `out` may itself be such a view (16-bit or, with accumulate, fp32 that is added to).
+at::Tensor gemm_nd(const at::Tensor& a, const at::Tensor& b, const std::optional<at::Tensor>& out_opt, double alpha) {
+  TORCH_CHECK(a.dim() == 4 && b.dim() == 4 && a.size(0) == b.size(0) && a.size(1) == b.size(1) && a.size(3) == b.size(2),
+              "gemm_nd: expected [B1, B2, M, K] x [B1, B2, K, N], got ", a.sizes(), " and ", b.sizes());
+  TORCH_CHECK(a.scalar_type() == b.scalar_type() && (a.scalar_type() == at::kBFloat16 || a.scalar_type() == at::kHalf),
+              "gemm_nd: 16-bit operands of one dtype expected");
+  const int64_t B1 = a.size(0), B2 = a.size(1), M = a.size(2), K = a.size(3), N = b.size(3);
+  at::Tensor out = (out_opt.has_value() && out_opt->defined()) ? *out_opt : empty_b200({B1, B2, M, N}, a.scalar_type(), a.device().index());
+  TORCH_CHECK(out.dim() == 4 && out.size(0) == B1 && out.size(1) == B2 && out.size(2) == M && out.size(3) == N && out.stride(3) == 1,
+              "gemm_nd: out must be [B1, B2, M, N] with a unit innermost stride");
+  if (out.numel() == 0) return out;
+  TORCH_CHECK(!use_cpu_path() && is_b200(a), "gemm_nd runs on the device only");
+  if (K == 0) return out.zero_();
+  const int64_t es = 2;
+  struct Op4 { at::Tensor t; int64_t ld; int mn; int64_t s1, s2; };
+  auto prep4 = [&](const at::Tensor& x, int rows_dim, int k_dim) {
+    auto ok = [&](int64_t ld) {
+      return reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0 && (ld * es) % 16 == 0 && (x.stride(0) * es) % 16 == 0 &&
+             (x.stride(1) * es) % 16 == 0 && ld > 0 && x.stride(0) > 0 && x.stride(1) > 0;
+    };
+    if (x.stride(k_dim) == 1 && x.size(k_dim) > 1 && ok(x.stride(rows_dim)) && x.stride(rows_dim) >= x.size(k_dim))
+      return Op4{x, x.stride(rows_dim), 0, x.stride(1), x.stride(0)};
+    if (x.stride(rows_dim) == 1 && x.size(rows_dim) > 1 && ok(x.stride(k_dim)) && x.stride(k_dim) >= x.size(rows_dim))
+      return Op4{x, x.stride(k_dim), 1, x.stride(1), x.stride(0)};
+    // irregular: a dense K-major copy with a 16-byte aligned row pitch
+    const int64_t rows = x.size(rows_dim), k = x.size(k_dim), ld = (k + 7) / 8 * 8;
+    at::Tensor buf = empty_b200({x.size(0), x.size(1), rows, ld}, x.scalar_type(), x.device().index());
+    buf.narrow(3, 0, k).copy_(rows_dim > k_dim ? x.transpose(2, 3) : x);
+    return Op4{buf, ld, 0, rows * ld, x.size(1) * rows * ld};
+  };
+  Op4 A = prep4(a, 2, 3), Bm = prep4(b, 3, 2);
+  OpScope scope("gemm_nd", out);
+  B200GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)(B1 * B2); p.batch_inner = (int)B2;
+  p.A = A.t.data_ptr(); p.B = Bm.t.data_ptr(); p.D = out.data_ptr();
+  p.lda = A.ld; p.ldb = Bm.ld; p.ldd = out.stride(2);
+  p.stride_a = A.s1; p.stride_a2 = A.s2; p.stride_b = Bm.s1; p.stride_b2 = Bm.s2;
+  p.stride_d = out.stride(1); p.stride_d2 = out.stride(0);
+  p.a_mn_major = A.mn; p.b_mn_major = Bm.mn;
+  p.ab_dtype = to_b200_dtype(a.scalar_type());
+  p.d_dtype = to_b200_dtype(out.scalar_type());
+  p.alpha = (float)alpha;
+  B200_KERNEL_CHECK(b200_gemm(&p, scope.stream()));
+  return out;
+}
+
+// Backward of y = x @ w^T + bias for 16-bit x / w whose master weight (and its gradient) are fp32:
+//   dx = grad @ w                               (16-bit, like x)
+//   dw = grad^T @ x  in fp32, K split over the GPU, added straight into `accum_w` (a flat fp32 [N * K] view of
+//        the gradient bucket) when that is given, else returned as a new fp32 tensor;
+//   db = column sums of grad in fp32, added into `accum_b` or returned.
+// Undefined results stand for "not needed" or "added in place".
+std::tuple<at::Tensor, at::Tensor, at::Tensor> linear_backward_fp32w(const at::Tensor& grad, const at::Tensor& x, const at::Tensor& w,
+                                                                     bool need_dx, bool need_dw, bool need_db,
+                                                                     const std::optional<at::Tensor>& accum_w,
+                                                                     const std::optional<at::Tensor>& accum_b) {
+  TORCH_CHECK(!use_cpu_path() && is_b200(grad), "linear_backward_fp32w runs on the device only");
+  TORCH_CHECK(grad.scalar_type() == x.scalar_type() && x.scalar_type() == w.scalar_type() &&
+                  (x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf),
+              "linear_backward_fp32w: 16-bit operands of one dtype expected");
+  const int64_t N = w.size(0), K = w.size(1);
+  at::Tensor g2 = grad.reshape({-1, N}), x2 = x.reshape({-1, K});
+  if (!g2.is_contiguous()) g2 = g2.contiguous();
+  if (!x2.is_contiguous()) x2 = x2.contiguous();
+  at::Tensor dx, dw, db;
+  if (need_dx) {
+    at::Tensor out = empty_b200({g2.size(0), K}, x.scalar_type(), x.device().index());
+    if (out.numel()) run_gemm(g2, w, out, nullptr, nullptr, 1.0, 0.0, 0);
+    dx = out.reshape(x.sizes());
+  }
+  if (need_dw) {
+    const bool direct = accum_w.has_value() && accum_w->defined();
+    at::Tensor acc;
+    if (direct) {
+      TORCH_CHECK(accum_w->scalar_type() == at::kFloat && accum_w->numel() == N * K && accum_w->is_contiguous() && K % 4 == 0,
+                  "linear_backward_fp32w: accum_w must be a contiguous fp32 tensor of the weight's size");
+      acc = accum_w->view({N, K});
+    } else {
+      acc = at::zeros({N, K}, grad.options().dtype(at::kFloat));
+    }
+    if (g2.size(0) > 0) {
+      at::Tensor gt = g2.t();
+      if (K % 4 == 0) {
+        run_gemm(gt, x2, acc, nullptr, nullptr, 1.0, 0.0, 0, /*accumulate=*/true);
+      } else {
+        at::Tensor tmp = empty_b200({N, K}, at::kFloat, x.device().index());
+        run_gemm(gt, x2, tmp, nullptr, nullptr, 1.0, 0.0, 0);
+        acc.add_(tmp);
+      }
+    }
+    if (!direct) dw = acc;
+  }
+  if (need_db) {
+    at::Tensor s = g2.sum({0}, /*keepdim=*/false, at::kFloat);
+    if (accum_b.has_value() && accum_b->defined()) const_cast<at::Tensor&>(*accum_b).view({N}).add_(s);
+    else db = s;
+  }
+  return {dx, dw, db};
 }
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {

@@ -140,10 +140,78 @@ std::tuple<Tensor, Tensor> k_native_dropout(const Tensor& input, double p, std::
   return {y, mask};
 }
 Tensor k_native_dropout_backward(const Tensor& grad, const Tensor& mask, double scale) {
+  if (f_ok(grad.scalar_type()) && mask.scalar_type() == at::kBool && grad.is_contiguous() && mask.is_contiguous() &&
+      grad.numel() == mask.numel() && is_b200(grad) && !use_cpu_path()) {
+    OpScope scope("native_dropout_backward", grad);
+    Tensor dx = at::empty_like(grad);
+    B200_KERNEL_CHECK(b200_dropout_bwd(grad.data_ptr(), static_cast<const unsigned char*>(mask.data_ptr()),
+                                       to_b200_dtype(grad.scalar_type()), grad.numel(), (float)scale, dx.data_ptr(), scope.stream()));
+    return dx;
+  }
   return grad * mask.to(grad.scalar_type()) * scale;
 }
 
 }  // namespace
+
+// ---- fused transformer residual block ---------------------------------------------------------
+// s = residual + dropout(h); y = layer_norm(s).  Returns (y, s, mask, mean, rstd); mask has one byte per four elements.
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> dropout_add_layer_norm(
+    const at::Tensor& h, const at::Tensor& residual, const std::optional<at::Tensor>& weight, const std::optional<at::Tensor>& bias,
+    double p, bool training, double eps) {
+  TORCH_CHECK(!use_cpu_path() && is_b200(h), "dropout_add_layer_norm runs on the device only");
+  TORCH_CHECK(h.sizes() == residual.sizes() && h.scalar_type() == residual.scalar_type() && f_ok(h.scalar_type()) && h.dim() >= 1,
+              "dropout_add_layer_norm: h and residual must match");
+  const int64_t cols = h.size(-1), rows = cols ? h.numel() / cols : 0;
+  TORCH_CHECK(cols % 4 == 0 && cols <= b200_dropout_add_layernorm_max_cols(), "dropout_add_layer_norm: unsupported row length ", cols);
+  OpScope scope("dropout_add_layer_norm", h);
+  at::Tensor hc = h.contiguous(), rc = residual.contiguous();
+  at::Tensor y = at::empty_like(hc), s = at::empty_like(hc);
+  auto fopt = h.options().dtype(at::kFloat);
+  at::Tensor mean = at::empty({rows}, fopt), rstd = at::empty({rows}, fopt);
+  const float pp = training ? (float)p : 0.f;
+  at::Tensor mask = at::empty({pp > 0.f ? rows * cols / 4 : 0}, h.options().dtype(at::kByte));
+  std::pair<uint64_t, uint64_t> so{0, 0};
+  if (pp > 0.f) so = philox(std::nullopt, h, (uint64_t)hc.numel());
+  at::Tensor wk, bk;
+  const void* gamma = nullptr;
+  const void* beta = nullptr;
+  int pdt = B200_F32;
+  if (weight.has_value() && weight->defined()) { wk = weight->contiguous(); gamma = wk.data_ptr(); pdt = to_b200_dtype(wk.scalar_type()); }
+  if (bias.has_value() && bias->defined()) {
+    bk = bias->contiguous();
+    TORCH_CHECK(!gamma || bk.scalar_type() == wk.scalar_type(), "dropout_add_layer_norm: weight and bias dtypes differ");
+    beta = bk.data_ptr(); pdt = to_b200_dtype(bk.scalar_type());
+  }
+  B200_KERNEL_CHECK(b200_dropout_add_layernorm_fwd(hc.data_ptr(), rc.data_ptr(), to_b200_dtype(h.scalar_type()), rows, (int)cols, pp,
+                                                   so.first, so.second, gamma, beta, pdt, (float)eps, y.data_ptr(), s.data_ptr(),
+                                                   mask.numel() ? static_cast<unsigned char*>(mask.data_ptr()) : nullptr,
+                                                   mean.data_ptr<float>(), rstd.data_ptr<float>(), scope.stream()));
+  return {y, s, mask, mean, rstd};
+}
+
+// (ds, dh, dgamma, dbeta); ds is also the gradient of the residual input
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> dropout_add_layer_norm_backward(
+    const at::Tensor& dy, const at::Tensor& s, const at::Tensor& mask, const std::optional<at::Tensor>& weight,
+    const at::Tensor& mean, const at::Tensor& rstd, double p) {
+  TORCH_CHECK(!use_cpu_path() && is_b200(dy), "dropout_add_layer_norm_backward runs on the device only");
+  const int64_t cols = s.size(-1), rows = cols ? s.numel() / cols : 0;
+  OpScope scope("dropout_add_layer_norm_backward", dy);
+  at::Tensor g = dy.contiguous();
+  TORCH_CHECK(g.scalar_type() == s.scalar_type() && g.numel() == s.numel() && s.is_contiguous(), "dropout_add_layer_norm_backward: shape / dtype mismatch");
+  at::Tensor ds = at::empty_like(s), dh = at::empty_like(s);
+  auto fopt = s.options().dtype(at::kFloat);
+  at::Tensor dgamma = at::zeros({cols}, fopt), dbeta = at::zeros({cols}, fopt);
+  at::Tensor wk;
+  const void* gamma = nullptr;
+  int pdt = B200_F32;
+  if (weight.has_value() && weight->defined()) { wk = weight->contiguous(); gamma = wk.data_ptr(); pdt = to_b200_dtype(wk.scalar_type()); }
+  const bool has_mask = mask.numel() > 0;
+  B200_KERNEL_CHECK(b200_dropout_add_layernorm_bwd(g.data_ptr(), s.data_ptr(), has_mask ? static_cast<const unsigned char*>(mask.data_ptr()) : nullptr,
+                                                   to_b200_dtype(s.scalar_type()), rows, (int)cols, has_mask ? (float)p : 0.f, gamma, pdt,
+                                                   mean.data_ptr<float>(), rstd.data_ptr<float>(), ds.data_ptr(), dh.data_ptr(),
+                                                   dgamma.data_ptr<float>(), dbeta.data_ptr<float>(), scope.stream()));
+  return {ds, dh, dgamma, dbeta};
+}
 
 // ---- custom ops (namespace catch_b200) ------------------------------------------------------
 bool dump_tensor_device(const at::Tensor& t) {
