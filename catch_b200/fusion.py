@@ -215,6 +215,14 @@ def fuse_linear(model: nn.Module) -> nn.Module:
     return model
 
 
+def _empty_with_layout_of(t: torch.Tensor) -> torch.Tensor:
+    """An uninitialised tensor with t's shape and, when t is a dense permutation of its memory, t's strides."""
+    extent = 1 + sum((n - 1) * st for n, st in zip(t.shape, t.stride()))
+    if t.numel() > 0 and all(st > 0 for st in t.stride()) and extent == t.numel():
+        return torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=t.device)
+    return torch.empty_like(t, memory_format=torch.contiguous_format)
+
+
 class _MatmulNdFn(torch.autograd.Function):
     """``alpha * a @ b`` over 4-D operands with arbitrary batch strides (``torch.ops.catch_b200.gemm_nd``).
 
@@ -236,12 +244,10 @@ class _MatmulNdFn(torch.autograd.Function):
         a, b = ctx.saved_tensors
         da = db = None
         if ctx.needs_input_grad[0]:
-            da = torch.empty_strided(a.shape, a.stride(), dtype=a.dtype, device=a.device) if a.is_non_overlapping_and_dense() \
-                else torch.empty_like(a)
+            da = _empty_with_layout_of(a)
             torch.ops.catch_b200.gemm_nd(g, b.transpose(-1, -2), da, ctx.alpha)
         if ctx.needs_input_grad[1]:
-            db = torch.empty_strided(b.shape, b.stride(), dtype=b.dtype, device=b.device) if b.is_non_overlapping_and_dense() \
-                else torch.empty_like(b)
+            db = _empty_with_layout_of(b)
             if db.stride(-1) != 1:   # the kernel writes rows: produce the transposed product into the transposed view
                 torch.ops.catch_b200.gemm_nd(g.transpose(-1, -2), a, db.transpose(-1, -2), ctx.alpha)
             else:

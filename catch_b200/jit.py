@@ -43,6 +43,34 @@ def segment_graph(graph) -> None:
     _C._jit_pass_segment_graph(graph)
 
 
+def unfuse_graph(graph) -> None:
+    _C._jit_pass_unfuse_graph(graph)
+
+
+def save(module: torch.jit.ScriptModule, f, _extra_files=None) -> None:
+    """``torch.jit.save`` for a module that went through ``optimize``: fusion groups are dissolved first (a group's
+    subgraph cannot be written to a file); the fused operators themselves (``catch_b200::conv_bn_act`` ...) are
+    ordinary registered operators and are saved as they are.  The groups of ``module`` are rebuilt after the file
+    is written.  Load with ``catch_b200.jit.load`` (or ``torch.jit.load`` after importing this package)."""
+    graph = module.forward.graph if hasattr(module, "forward") else None
+    if graph is not None:
+        unfuse_graph(graph)
+    try:
+        torch.jit.save(module, f, _extra_files=_extra_files)
+    finally:
+        if graph is not None and fusion_enabled():
+            segment_graph(graph)
+
+
+def load(f, map_location=None, _extra_files=None) -> torch.jit.ScriptModule:
+    """``torch.jit.load`` followed by the segmentation pass (parameters and constants go to ``map_location``, e.g.
+    ``"blackwell"``)."""
+    m = torch.jit.load(f, map_location=map_location, _extra_files=_extra_files)
+    if fusion_enabled() and hasattr(m, "forward"):
+        segment_graph(m.forward.graph)
+    return m
+
+
 def fusion_stats() -> dict:
     return {"runners": _C._jit_fusion_cache_size(), "compiles": _C._jit_fusion_compile_count(),
             "fallbacks": _C._jit_fusion_fallback_count()}

@@ -46,8 +46,15 @@ class _Bucket:
     def __init__(self, index: int, params: List[torch.nn.Parameter]):
         self.index = index
         self.params = params
-        self.numel = sum(p.numel() for p in params)
+        # every parameter starts on a 16-byte boundary of the flat fp32 buffers (kernels that add gradients into
+        # the bucket address it with tensor maps); the few padding elements stay zero
         self.offsets: List[int] = []
+        off = 0
+        for p in params:
+            off = (off + 3) // 4 * 4
+            self.offsets.append(off)
+            off += p.numel()
+        self.numel = off
         self.pending = 0
         self.launched = False
         self.grads = None      # flat fp32 gradient buffer (p.grad are views of it)
@@ -160,11 +167,12 @@ class FusedDataParallel(torch.nn.Module):
         b.comm = self._alloc(n_pad, self.grad_dtype) if comm16 else None
         if self.lowp_dtype is not None:
             b.lowp = self._alloc(n_pad, self.lowp_dtype)[:b.numel]
-        off = 0
+        b.flat.zero_()
+        if b.lowp is not None:
+            b.lowp.zero_()
         b.grad_views, b.flat_grads = [], []
-        for p in b.params:
+        for p, off in zip(b.params, b.offsets):
             n = p.numel()
-            b.offsets.append(off)
             view = _view_like(b.flat[off:off + n], p.data)
             view.copy_(p.data)
             b.grad_views.append(_view_like(b.grads[off:off + n], p.data))
@@ -173,7 +181,6 @@ class FusedDataParallel(torch.nn.Module):
             if b.lowp is not None:
                 p._b200_lowp = _view_like(b.lowp[off:off + n], p.data)
             self._param_bucket[p] = b
-            off += n
         ex_dtype = self.grad_dtype if comm16 else torch.float32
         shard = self.pg.shard_elems(b.numel, ex_dtype) if self.pg is not None else b.numel
         b.state1 = torch.zeros(shard, dtype=torch.float32, device=self.device)

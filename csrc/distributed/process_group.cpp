@@ -18,6 +18,7 @@
 #include "../runtime/caching_allocator.h"
 #include "../runtime/device.h"
 #include "../runtime/log.h"
+#include "../runtime/profiler.h"
 #include "../runtime/tensor_impl.h"
 
 namespace catch_b200 {
@@ -56,6 +57,7 @@ size_t env_mb(const char* name, size_t dflt) {
 #define COMM_CHECK(expr)                                                                         \
   do {                                                                                           \
     ::catch_b200::ops::note_kernel_launch();                                                     \
+    ::catch_b200::KernelTraceScope _trace(#expr);                                                \
     int _e = (expr);                                                                             \
     TORCH_CHECK(_e == 0, "bwccl: device call failed: ", device_error_string(_e), " (", #expr, ")"); \
   } while (0)

@@ -26,6 +26,7 @@ void set_fusion_enabled(bool on);
 void LowerGraph(std::shared_ptr<torch::jit::Graph>& graph);
 void FuseKernels(std::shared_ptr<torch::jit::Graph>& graph);   // pattern rewrite to fused ops
 void SegmentGraph(std::shared_ptr<torch::jit::Graph>& graph);  // build FusionGroup nodes
+void UnfuseGraph(std::shared_ptr<torch::jit::Graph>& graph);   // dissolve them again (needed before saving a module)
 bool isSupported(const torch::jit::Node* n);
 
 void register_passes();  // idempotent: registers the pre-passes with the graph executor

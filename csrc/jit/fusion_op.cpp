@@ -143,7 +143,7 @@ class RunnerCache {
     static RunnerCache c;
     return c;
   }
-  int64_t registerFusion(const Node* node) {
+  std::shared_ptr<FusedRunner> registerFusion(const Node* node) {
     std::shared_ptr<Graph> g = node->g(attr::Subgraph)->copy();
     std::shared_ptr<Graph> canon = Canonicalize(g, /*keep_unique_names=*/false);
     std::string text = canon->toString(/*print_source_locations=*/false);
@@ -156,35 +156,35 @@ class RunnerCache {
     }
     std::lock_guard<std::mutex> lk(mu_);
     auto it = by_text_.find(text);
-    if (it != by_text_.end()) return it->second;
-    const int64_t key = static_cast<int64_t>(runners_.size());
-    runners_.push_back(std::make_shared<FusedRunner>(g));
-    by_text_[text] = key;
-    return key;
-  }
-  std::shared_ptr<FusedRunner> retrieve(int64_t key) {
-    std::lock_guard<std::mutex> lk(mu_);
-    TORCH_CHECK(key >= 0 && key < static_cast<int64_t>(runners_.size()), "b200 fusion: unknown runner key ", key);
-    return runners_[key];
+    if (it != by_text_.end()) {
+      if (auto live = it->second.lock()) return live;
+      by_text_.erase(it);
+    }
+    // The cache only observes runners: the operator closures of the graph executors own them, so the
+    // device constants of a deleted module are released with its last executor.
+    for (auto e = by_text_.begin(); e != by_text_.end();) e = e->second.expired() ? by_text_.erase(e) : std::next(e);
+    auto runner = std::make_shared<FusedRunner>(g);
+    by_text_[text] = runner;
+    return runner;
   }
   int64_t size() {
     std::lock_guard<std::mutex> lk(mu_);
-    return static_cast<int64_t>(runners_.size());
+    int64_t n = 0;
+    for (auto& e : by_text_) n += e.second.expired() ? 0 : 1;
+    return n;
   }
   void clear() {
     std::lock_guard<std::mutex> lk(mu_);
-    by_text_.clear();  // existing closures keep their runners alive through the vector
+    by_text_.clear();  // existing closures keep their own runners
   }
 
  private:
   std::mutex mu_;
-  std::unordered_map<std::string, int64_t> by_text_;
-  std::vector<std::shared_ptr<FusedRunner>> runners_;
+  std::unordered_map<std::string, std::weak_ptr<FusedRunner>> by_text_;
 };
 
 Operation create_fusion_operation(const Node* node) {
-  const int64_t key = RunnerCache::get().registerFusion(node);
-  auto runner = RunnerCache::get().retrieve(key);
+  auto runner = RunnerCache::get().registerFusion(node);
   return [runner](Stack& stack) { runner->run(stack); };
 }
 

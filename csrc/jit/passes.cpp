@@ -343,6 +343,21 @@ void SegmentGraph(std::shared_ptr<Graph>& graph) {
   EliminateDeadCode(graph);
 }
 
+// Inverse of SegmentGraph: the nodes of every fusion group go back into the surrounding graph.  A module
+// has to be in this form to be serialised (a subgraph attribute has no textual form in a saved module).
+void UnfuseGraph(std::shared_ptr<Graph>& graph) {
+  std::function<void(Block*)> walk = [&](Block* block) {
+    for (auto it = block->nodes().begin(); it != block->nodes().end();) {
+      Node* n = *it;
+      ++it;
+      for (Block* b : n->blocks()) walk(b);
+      if (n->kind() == fusion_kind()) SubgraphUtils::unmergeSubgraph(n);
+    }
+  };
+  walk(graph->block());
+  EliminateDeadCode(graph);
+}
+
 void register_passes() {
   static std::once_flag once;
   std::call_once(once, [] {

@@ -46,6 +46,7 @@ class OpScope {
 
  private:
   const char* name_;
+  const char* prev_op_ = "";
   int device_;
   DeviceSwitch sw_;
 };

@@ -3,6 +3,7 @@
 #include <ATen/ATen.h>
 #include <ATen/TensorIterator.h>
 #include "../device/kernels_api.h"
+#include "../runtime/profiler.h"
 #include "common.h"
 
 namespace catch_b200 {
@@ -16,6 +17,7 @@ void reset_kernel_launch_count();
 #define B200_KERNEL_CHECK(expr)                                                                     \
   do {                                                                                              \
     ::catch_b200::ops::note_kernel_launch();                                                        \
+    ::catch_b200::KernelTraceScope _trace(#expr); /* two notifiers around the launch while tracing */ \
     int _e = (expr);                                                                                \
     TORCH_CHECK(_e == 0, "b200 kernel launch failed: ", ::catch_b200::device_error_string(_e), " (", \
                 #expr, ")");                                                                        \

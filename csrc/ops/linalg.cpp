@@ -289,7 +289,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> linear_backward_fp32w(const at::T
     const bool direct = accum_w.has_value() && accum_w->defined();
     at::Tensor acc;
     if (direct) {
-      TORCH_CHECK(accum_w->scalar_type() == at::kFloat && accum_w->numel() == N * K && accum_w->is_contiguous() && K % 4 == 0,
+      TORCH_CHECK(accum_w->scalar_type() == at::kFloat && accum_w->numel() == N * K && accum_w->is_contiguous(),
                   "linear_backward_fp32w: accum_w must be a contiguous fp32 tensor of the weight's size");
       acc = accum_w->view({N, K});
     } else {
@@ -297,7 +297,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> linear_backward_fp32w(const at::T
     }
     if (g2.size(0) > 0) {
       at::Tensor gt = g2.t();
-      if (K % 4 == 0) {
+      // the reduce-add epilogue addresses the target through a tensor map: 16-byte aligned base and rows
+      if (K % 4 == 0 && reinterpret_cast<uintptr_t>(acc.data_ptr()) % 16 == 0) {
         run_gemm(gt, x2, acc, nullptr, nullptr, 1.0, 0.0, 0, /*accumulate=*/true);
       } else {
         at::Tensor tmp = empty_b200({N, K}, at::kFloat, x.device().index());

@@ -19,6 +19,7 @@
 
 #include "../runtime/host_allocator.h"
 #include "common.h"
+#include "../runtime/profiler.h"
 #include "kernels.h"
 
 namespace catch_b200 {
@@ -31,8 +32,10 @@ static int device_of_tensor(const at::Tensor& t) {
 OpScope::OpScope(const char* name, const at::Tensor& t) : OpScope(name, device_of_tensor(t)) {}
 OpScope::OpScope(const char* name, int device) : name_(name), device_(device), sw_(device) {
   B200LOG(DBG) << "op " << name << " on b200:" << device;
+  prev_op_ = trace_set_current_op(name);
 }
 OpScope::~OpScope() noexcept(false) {
+  trace_set_current_op(prev_op_);
   if (flags().async_disable && !hostsim()) getCurrentQueue(device_).synchronize();
 }
 

@@ -6,6 +6,7 @@
 
 #include "../jit/fusion.h"
 #include "../runtime/dumper.h"
+#include "../runtime/profiler.h"
 
 namespace py = pybind11;
 
@@ -23,6 +24,21 @@ void bind_aux(py::module& m) {
   m.def("_jit_fusion_fallback_count", &jit::fusion_fallback_count);
   m.def("_jit_pass_lower_graph", [](std::shared_ptr<torch::jit::Graph>& g) { jit::LowerGraph(g); });
   m.def("_jit_pass_fuse_kernels", [](std::shared_ptr<torch::jit::Graph>& g) { jit::FuseKernels(g); });
+  m.def("_jit_pass_unfuse_graph", [](std::shared_ptr<torch::jit::Graph>& g) { jit::UnfuseGraph(g); });
+  m.def("_kernel_trace_start", &kernel_trace_start);
+  m.def("_kernel_trace_stop", [] {
+    std::vector<KernelEvent> evs;
+    {
+      py::gil_scoped_release nogil;
+      evs = kernel_trace_stop();
+    }
+    py::list out;
+    for (auto& e : evs) out.append(py::make_tuple(e.name, e.op, e.kind, e.device, e.queue, e.cpu_ns, e.start_us, e.dur_us));
+    return out;
+  });
+  m.def("_trace_mark", [](const std::string& s) { trace_mark(s.c_str()); });
+  m.def("_trace_range_push", [](const std::string& s) { trace_range_push(s.c_str()); });
+  m.def("_trace_range_pop", &trace_range_pop);
   m.def("_jit_pass_segment_graph", [](std::shared_ptr<torch::jit::Graph>& g) { jit::SegmentGraph(g); });
 }
 }  // namespace catch_b200

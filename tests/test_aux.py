@@ -113,6 +113,42 @@ def test_fusion_of_traced_module_rewrites_underscore_convolution():
     assert torch.allclose(opt(x), ref, atol=1e-4)
 
 
+def test_torchscript_save_load_roundtrip_and_unfuse(tmp_path):
+    """Reference test strategy: test/torch_native_ci/jit/test_save_load.py -- scripted modules round-trip through
+    files, to and from the device; an optimised module is saved without its fusion groups and gets them back."""
+    import io
+
+    torch.manual_seed(0)
+    m = Block().eval()
+    x = torch.randn(2, 8, 12, 12)
+    ref = m(x)
+    # plain scripted module: host file -> device, device file -> host / device
+    buf = io.BytesIO(); torch.jit.save(torch.jit.script(m), buf); buf.seek(0)
+    dm = torch.jit.load(buf, map_location="blackwell")
+    assert next(dm.parameters()).device.type == "blackwell"
+    assert torch.allclose(dm(x.to("blackwell")).cpu(), ref, atol=1e-4)
+    path = tmp_path / "on_device.pt"
+    torch.jit.save(torch.jit.script(Block().eval()).to("blackwell"), str(path))
+    assert next(torch.jit.load(str(path), map_location="cpu").parameters()).device.type == "cpu"
+    assert next(torch.jit.load(str(path)).parameters()).device.type == "blackwell"
+    # optimised module: groups are dissolved for the file and rebuilt on both sides
+    opt = jit.optimize(torch.jit.script(m))
+    n_groups = str(opt.graph).count("catch_b200::FusionGroup")
+    assert n_groups >= 1
+    path2 = tmp_path / "optimised.pt"
+    jit.save(opt, str(path2))
+    assert str(opt.graph).count("catch_b200::FusionGroup") == n_groups
+    back = jit.load(str(path2), map_location="blackwell")
+    g = str(back.graph)
+    assert "catch_b200::FusionGroup" in g
+    inner = "".join(str(n.g("Subgraph")) for n in back.graph.nodes() if n.kind() == "catch_b200::FusionGroup")
+    assert inner.count("catch_b200::conv_bn_act") == 3
+    assert torch.allclose(back(x.to("blackwell")).cpu(), ref, atol=1e-4)
+    jit.unfuse_graph(back.graph)
+    assert "FusionGroup" not in str(back.graph) and str(back.graph).count("catch_b200::conv_bn_act") == 3
+    assert torch.allclose(back(x.to("blackwell")).cpu(), ref, atol=1e-4)
+
+
 def test_fusion_toggle_and_forced_fallback():
     m = torch.jit.script(Block().eval())
     jit.set_fusion_enabled(False)

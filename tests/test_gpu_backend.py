@@ -121,3 +121,43 @@ def test_queues_and_notifiers():
         y = x + 1
     side.synchronize()
     assert_tensors_equal(y, x.cpu() + 1, prec=1e-6)
+
+
+def test_profiler_lists_kernels_with_device_times(tmp_path):
+    """The profiler preset records operators through the stock profiler and, next to them, every kernel launch with a
+    positive device time; the Chrome trace gets a device row per queue."""
+    import json
+
+    from catch_b200 import profiler
+
+    x = torch.randn(512, 512, device=DEV)
+    w = torch.randn(512, 512, device=DEV)
+    torch.b200.synchronize()
+    with profiler.profile(record_shapes=True) as prof:
+        with profiler.range("step"):
+            y = torch.relu(x @ w)
+            profiler.mark("after relu")
+            z = y.sum()
+    assert z.device.type == DEV
+    assert {"aten::mm", "aten::relu"} <= {e.name for e in prof.function_events}
+    mm = [e for e in prof.function_events if e.name == "aten::mm"]
+    assert mm and mm[0].device_time > 0                      # operator-level device time from the stock profiler
+    kt = prof.kernels
+    names = [e.name for e in kt.kernels]
+    assert "b200_gemm" in names and any(n.startswith("b200_elementwise") or "reduce" in n for n in names), names
+    assert all(e.dur_us > 0 for e in kt.kernels)
+    assert all(e.op for e in kt.kernels)                     # each launch knows the operator that issued it
+    gemm = next(e for e in kt.kernels if e.name == "b200_gemm")
+    assert gemm.op == "gemm" and gemm.start_us >= 0
+    rng = [e for e in kt.events if e.kind == "range"]
+    assert len(rng) == 1 and rng[0].name == "step" and rng[0].dur_us >= sum(e.dur_us for e in kt.kernels) * 0.5
+    assert [e.name for e in kt.events if e.kind == "mark"] == ["after relu"]
+    assert "b200_gemm" in kt.table() and kt.total_device_time_us() > 0
+    path = str(tmp_path / "trace.json")
+    prof.export_chrome_trace(path)
+    events = json.load(open(path))["traceEvents"]
+    assert any(e.get("pid") == "blackwell:0" and e.get("name") == "b200_gemm" and e.get("dur", 0) > 0 for e in events)
+    # outside a trace nothing is recorded and launches cost nothing extra
+    with profiler.kernel_trace() as kt2:
+        pass
+    assert kt2.events == []
