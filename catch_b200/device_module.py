@@ -385,6 +385,12 @@ def memory_debug(tensor: Optional[torch.Tensor] = None):
     return checked, corrupted, detail
 
 
+def memory_debug_origin(tensor: torch.Tensor) -> str:
+    """Where the block behind ``tensor`` was allocated (Python frames, then native frames); ``""`` unless the
+    debug allocator was on when it was allocated.  The same text is part of every corruption report."""
+    return _C._memory_debug_origin(tensor)
+
+
 def pin_memory(tensor: torch.Tensor) -> torch.Tensor:
     return _C._pin_memory(tensor)
 

@@ -135,6 +135,29 @@ PYBIND11_MODULE(_C, m) {
   });
   m.def("_set_memory_strategy", [](bool native) { setNativeMemoryStrategy(native); });
   m.def("_get_memory_strategy", [] { return nativeMemoryStrategy(); });
+  // Python frames of the allocating thread for the debug allocator's origin records.
+  setAllocationContextHook(+[]() -> std::string {
+    if (!Py_IsInitialized() || _Py_IsFinalizing()) return std::string();
+    py::gil_scoped_acquire gil;  // most allocations come from bindings that released the interpreter lock
+    std::string out;
+    PyFrameObject* f = PyEval_GetFrame();  // borrowed
+    Py_XINCREF(f);
+    for (int depth = 0; f && depth < 12; ++depth) {
+      PyCodeObject* code = PyFrame_GetCode(f);
+      const char* file = PyUnicode_AsUTF8(code->co_filename);
+      const char* name = PyUnicode_AsUTF8(code->co_name);
+      out += "    " + std::string(file ? file : "?") + ":" + std::to_string(PyFrame_GetLineNumber(f)) + " in " +
+             std::string(name ? name : "?") + "\n";
+      Py_DECREF(code);
+      PyFrameObject* back = PyFrame_GetBack(f);
+      Py_DECREF(f);
+      f = back;
+    }
+    Py_XDECREF(f);
+    if (PyErr_Occurred()) PyErr_Clear();
+    return out;
+  });
+  m.def("_memory_debug_origin", [](const at::Tensor& t) { return memoryDebugOrigin(t.storage().data()); });
   m.def("_set_memory_debug", [](bool on) { setMemoryDebug(on); });
   m.def("_memory_debug_enabled", [] { return memoryDebugEnabled(); });
   m.def("_memory_debug", [](std::optional<at::Tensor> t) {

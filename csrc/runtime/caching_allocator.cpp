@@ -4,7 +4,12 @@
 
 #include <c10/core/CPUAllocator.h>
 #include <c10/util/Exception.h>
+#include <c10/util/Type.h>
+#include <execinfo.h>
 #include <algorithm>
+#include <atomic>
+#include <cstdlib>
+#include <vector>
 #include <array>
 #include <cstring>
 #include <deque>
@@ -31,6 +36,7 @@ constexpr size_t kMidSegment = 20 << 20;
 constexpr size_t kLargeRound = 2 << 20;        // bigger segments are rounded to 2 MiB
 constexpr size_t kGuard = 512;                 // debug guard region on each side
 constexpr uint8_t kGuardByte = 0xA5;
+std::atomic<AllocationContextHook> g_context_hook{nullptr};
 
 inline size_t round_up(size_t n, size_t m) { return (n + m - 1) / m * m; }
 
@@ -46,6 +52,9 @@ struct Block {
   int pending_events = 0;  // outstanding cross-queue notifiers
   std::unordered_set<uint64_t> other_queues;  // queues recorded through recordQueue
   size_t requested = 0;    // user-visible size (debug report)
+  // debug mode: where the block was handed out (native return addresses, context text of the hook)
+  std::vector<void*> origin_frames;
+  std::string origin_context;
 };
 
 struct BlockLess {
@@ -74,6 +83,12 @@ class CachingAllocator final : public c10::Allocator {
 
   // ---------------------------------------------------------------- allocate
   void* malloc_block(size_t bytes, int device, const Queue& q) {
+    // The context hook may take the interpreter lock: it runs before this allocator's own lock is taken, so a
+    // thread that holds the interpreter lock and waits for the allocator cannot deadlock with this one.
+    std::string context;
+    if (debug_) {
+      if (AllocationContextHook hook = g_context_hook.load()) context = hook();
+    }
     std::lock_guard<std::recursive_mutex> g(mu_);
     DeviceState& st = state(device);
     drain_pending(st);
@@ -116,7 +131,10 @@ class CachingAllocator final : public c10::Allocator {
     st.stats.max_allocated = std::max(st.stats.max_allocated, st.stats.allocated);
     st.stats.num_alloc++;
     char* user = blk->ptr + (debug_ ? kGuard : 0);
-    if (debug_) paint_guards(blk, q);
+    if (debug_) {
+      paint_guards(blk, q);
+      record_origin(blk, std::move(context));
+    }
     live_[user] = blk;
     c10::reportMemoryUsageToProfiler(user, static_cast<int64_t>(blk->size), st.stats.allocated, st.stats.reserved,
                                      make_device(device));
@@ -141,6 +159,8 @@ class CachingAllocator final : public c10::Allocator {
       }
     }
     blk->in_use = false;
+    blk->origin_frames.clear();
+    blk->origin_context.clear();
     st.stats.allocated -= static_cast<int64_t>(blk->size);
     st.stats.num_free++;
     c10::reportMemoryUsageToProfiler(user, -static_cast<int64_t>(blk->size), st.stats.allocated, st.stats.reserved,
@@ -235,6 +255,12 @@ class CachingAllocator final : public c10::Allocator {
       for (auto& kv : live_) check(kv.second);
     }
     return r;
+  }
+
+  std::string origin_of(const void* user) {
+    std::lock_guard<std::recursive_mutex> g(mu_);
+    auto it = live_.find(const_cast<void*>(user));
+    return it == live_.end() ? std::string() : format_origin(it->second);
   }
 
   std::string summary(int device) {
@@ -375,6 +401,30 @@ class CachingAllocator final : public c10::Allocator {
   }
 
   // ------------------------------------------------------------- debug mode
+  void record_origin(Block* b, std::string context) {
+    void* frames[24];
+    const int n = ::backtrace(frames, 24);
+    b->origin_frames.assign(frames + std::min(n, 2), frames + n);  // without this function and malloc_block()
+    b->origin_context = std::move(context);
+  }
+  static std::string format_origin(const Block* b) {
+    if (b->origin_frames.empty() && b->origin_context.empty()) return "";
+    std::ostringstream os;
+    os << "  allocated at:\n";
+    if (!b->origin_context.empty()) os << b->origin_context;
+    char** names = ::backtrace_symbols(b->origin_frames.data(), static_cast<int>(b->origin_frames.size()));
+    for (size_t i = 0; names && i < b->origin_frames.size(); ++i) {
+      // "module(mangled+0x12) [addr]" -> demangle the part between '(' and '+'
+      std::string line = names[i];
+      const size_t l = line.find('('), r = line.find('+', l == std::string::npos ? 0 : l);
+      if (l != std::string::npos && r != std::string::npos && r > l + 1) {
+        line = line.substr(0, l + 1) + c10::demangle(line.substr(l + 1, r - l - 1).c_str()) + line.substr(r);
+      }
+      os << "    " << line << "\n";
+    }
+    std::free(names);
+    return os.str();
+  }
   void paint_guards(Block* b, const Queue& q) {
     DeviceSwitch sw(b->device);
     backend().memset_async(b->ptr, kGuardByte, kGuard, q.handle());
@@ -404,6 +454,8 @@ class CachingAllocator final : public c10::Allocator {
        << b->device << ")";
     if (head_bad >= 0) os << " header guard damaged " << (kGuard - head_bad) << " B before the block";
     if (tail_bad >= 0) os << " footer guard damaged " << tail_bad << " B after the rounded block end";
+    const std::string origin = format_origin(b);
+    if (!origin.empty()) os << "\n" << origin;
     *why = os.str();
     return false;
   }
@@ -461,6 +513,8 @@ bool nativeMemoryStrategy() { return alloc().native(); }
 void setMemoryDebug(bool on) { alloc().set_debug(on); }
 bool memoryDebugEnabled() { return alloc().debug(); }
 DebugReport memoryDebugCheck(const void* ptr) { return alloc().debug_check(ptr); }
+void setAllocationContextHook(AllocationContextHook hook) { g_context_hook.store(hook); }
+std::string memoryDebugOrigin(const void* ptr) { return alloc().origin_of(ptr); }
 std::string memorySummary(int device) { return alloc().summary(device); }
 
 }  // namespace catch_b200

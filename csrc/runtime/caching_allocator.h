@@ -66,6 +66,13 @@ bool nativeMemoryStrategy();
 void setMemoryDebug(bool on);
 bool memoryDebugEnabled();
 DebugReport memoryDebugCheck(const void* ptr = nullptr);  // nullptr = every live block
+// In memory-debug mode every block remembers where it was allocated (reference: the debug allocator's recorded
+// backtraces, torch_mlu/csrc/aten/core/caching_allocator.cpp:633): the native return addresses, symbolised only when a
+// report is written, plus the text this hook returns at allocation time (the binding layer installs one that walks
+// the Python frames of the calling thread).
+using AllocationContextHook = std::string (*)();
+void setAllocationContextHook(AllocationContextHook hook);
+std::string memoryDebugOrigin(const void* ptr);  // "" when the block has no record
 std::string memorySummary(int device);
 
 }  // namespace catch_b200

@@ -142,6 +142,8 @@ def test_fused_bert_layer_matches_plain_definition():
     assert abs(losses[0] - losses[1]) < 2e-2, losses
     bad = {}
     for (n, a), (_, b) in zip(plain.named_parameters(), fused.named_parameters()):
+        if n.endswith("attention.key.bias"):
+            continue  # softmax is invariant to a shift of all scores of a query: this gradient is rounding noise in both
         ga, gb = a.grad.double().flatten().cpu(), b.grad.double().flatten().cpu()
         cos = (ga @ gb / (ga.norm() * gb.norm() + 1e-30)).item()
         if cos < 0.98:

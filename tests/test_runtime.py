@@ -196,8 +196,14 @@ def test_debug_allocator_detects_overrun():
         assert checked == 1 and corrupted == 0
         # host simulation: device memory is host memory, so an overrun can be staged from here
         ctypes.memset(x.data_ptr() + 512, 0, 8)  # first bytes after the rounded block
-        with pytest.raises(RuntimeError, match="out-of-bounds"):
+        with pytest.raises(RuntimeError, match="out-of-bounds") as err:
             bw.memory_debug(x)
+        # the report says where the damaged block came from: this test function, then native frames
+        msg = str(err.value)
+        del err  # its traceback keeps the frame that holds the tensor alive
+        assert "allocated at:" in msg and "test_debug_allocator_detects_overrun" in msg
+        origin = bw.memory_debug_origin(x)
+        assert "test_runtime.py" in origin and "catch_b200" in origin
         ctypes.memset(x.data_ptr() + 512, 0xA5, 8)
         bw.memory_debug()
         del x
