@@ -4,8 +4,9 @@
 
 Per-channel symmetric int8 weights, per-tensor activation scales calibrated on 8
 batches of 32 N(0,1) inputs (seed 1); evaluation on fresh N(0,1) inputs.  Reports
-images/sec of the int8 model and of the fp16 eager model on this backend, and the
-top-1 agreement between them.
+images/sec of the int8 and fp16 models on this backend, eager and traced + fused
+(catch_b200.jit.optimize: conv + add + ReLU in one kernel; quantized layers hand int8
+to each other), and the top-1 agreement with fp16 eager.
 """
 import argparse
 import os
@@ -62,14 +63,27 @@ def main():
     fmodel = fmodel.half().to(dev).to(memory_format=torch.channels_last)
     x = torch.randn(args.batch, 3, 224, 224, generator=torch.Generator().manual_seed(2)).half().to(dev)
     x = x.contiguous(memory_format=torch.channels_last)
+    from catch_b200 import jit
+
     with torch.no_grad():
         ms_q, out_q = bench(lambda: qmodel(x), args.iters)
         ms_f, out_f = bench(lambda: fmodel(x), args.iters)
-    agree = (out_q.argmax(1) == out_f.argmax(1)).float().mean().item()
-    rel = ((out_q.float() - out_f.float()).norm() / out_f.float().norm()).item()
+        qjit = jit.optimize(torch.jit.trace(qmodel, x))
+        fjit = jit.optimize(torch.jit.trace(fmodel, x))
+        ms_qj, out_qj = bench(lambda: qjit(x), args.iters)
+        ms_fj, out_fj = bench(lambda: fjit(x), args.iters)
+
+    def cmp(o):
+        return ((o.argmax(1) == out_f.argmax(1)).float().mean().item(),
+                ((o.float() - out_f.float()).norm() / out_f.float().norm()).item())
+
     nq = sum(1 for m in qmodel.modules() if getattr(m, "is_quantized", lambda: False)())
-    print(f"int8: {ms_q:.3f} ms, {args.batch / ms_q * 1e3:.1f} images/sec ({nq} quantized layers); "
-          f"fp16: {ms_f:.3f} ms, {args.batch / ms_f * 1e3:.1f} images/sec; top-1 agreement {agree:.3f}, rel-RMS {rel:.3e}")
+    print(f"ResNet-50 inference, batch {args.batch}, {nq} quantized layers; images/sec (ms per batch); "
+          f"top-1 agreement with / relative RMS to fp16 eager")
+    for name, ms, o in (("fp16 eager", ms_f, out_f), ("fp16 fused", ms_fj, out_fj), ("int8 eager", ms_q, out_q),
+                        ("int8 fused", ms_qj, out_qj)):
+        a, r = cmp(o)
+        print(f"{name}: {args.batch / ms * 1e3:9.1f} ({ms:.3f} ms); {a:.3f} / {r:.3e}")
 
 
 if __name__ == "__main__":

@@ -370,7 +370,8 @@ def set_memory_strategy(native_memory_strategy: bool) -> None:
 
 
 def set_memory_debug(enable: bool) -> None:
-    """Switch the guard-word debug allocator on or off (no b200 tensor may be alive)."""
+    """Switch the guard-word debug allocator on or off.  Tensors allocated while it is on carry guard regions (and an
+    allocation record) until they are freed; tensors allocated while it is off are not checked."""
     _C._set_memory_debug(bool(enable))
 
 
@@ -389,6 +390,128 @@ def memory_debug_origin(tensor: torch.Tensor) -> str:
     """Where the block behind ``tensor`` was allocated (Python frames, then native frames); ``""`` unless the
     debug allocator was on when it was allocated.  The same text is part of every corruption report."""
     return _C._memory_debug_origin(tensor)
+
+
+class Graph:
+    """A sequence of device launches captured once and replayed with a single submission.
+
+    ::
+
+        g = torch.b200.Graph()
+        static_x = torch.empty_like(x)            # inputs live outside the graph
+        with torch.b200.graph(g):                 # runs the body once on a side queue while recording it
+            static_y = model(static_x)
+        static_x.copy_(x); g.replay()             # static_y now holds model(x)
+
+    Memory allocated inside the ``with`` block belongs to the graph (a private pool of the caching allocator);
+    tensors created there and still alive afterwards are overwritten by every replay.  The body must not wait for
+    the device (``.item()``, ``.cpu()``, ``synchronize()``) and must make the same launches for the same shapes.
+    """
+
+    def __init__(self):
+        self._native = _C._Graph()
+
+    def capture_begin(self) -> None:
+        self._native.capture_begin()
+
+    def capture_end(self) -> bool:
+        return self._native.capture_end()
+
+    def replay(self) -> None:
+        self._native.replay()
+
+    def reset(self) -> None:
+        self._native.reset()
+
+    @property
+    def valid(self) -> bool:
+        return self._native.valid
+
+    @property
+    def num_nodes(self) -> int:
+        return self._native.num_nodes
+
+
+class graph:
+    """Context manager that captures its body into ``g`` on a queue from the pool (the default queue cannot be
+    captured).  Work already submitted to the previous current queue is waited for on the device first; after the
+    block the previous queue waits for the side queue.  Raises if the body could not be captured."""
+
+    def __init__(self, g: Graph, queue: Optional["Queue"] = None):
+        self.g = g
+        self._side = queue._native if queue is not None else _C._getQueueFromPool(-1)
+        self._prev = None
+
+    def __enter__(self):
+        import gc
+
+        gc.collect()  # tensors that die during capture would return their blocks to the wrong place in time
+        self._prev = _C._getCurrentQueue(-1)
+        n = _C._Notifier(False)
+        n.place(self._prev)
+        n.wait(self._side)
+        _C._setCurrentQueue(self._side)
+        try:
+            self.g.capture_begin()
+        except Exception:
+            _C._setCurrentQueue(self._prev)
+            raise
+        return self.g
+
+    def __exit__(self, exc_type, exc, tb):
+        try:
+            if exc_type is not None:
+                self.g._native.capture_abort()
+                return False
+            ok = self.g.capture_end()
+        finally:
+            _C._setCurrentQueue(self._prev)
+        n = _C._Notifier(False)
+        n.place(self._side)
+        n.wait(self._prev)
+        if not ok:
+            raise RuntimeError("b200 graph capture failed: the captured region waited for the device or used a call "
+                               "that cannot be recorded")
+        return False
+
+
+def graphs_supported() -> bool:
+    """False under host simulation (work runs when it is submitted: there is nothing to record)."""
+    return _C._graphs_supported()
+
+
+def make_graphed_callable(fn, sample_args, warmup: int = 2):
+    """Inference-only analogue of ``torch.cuda.make_graphed_callables``: runs ``fn(*sample_args)`` ``warmup`` times,
+    captures one more run into a :class:`Graph` and returns a callable that copies its tensor arguments into the
+    captured inputs, replays, and returns the captured outputs (overwritten by the next call: clone what has to
+    live longer).  Arguments must keep the sample's shapes and dtypes.  Without graph support (host simulation)
+    ``fn`` itself is returned."""
+    if not graphs_supported():
+        return fn
+    sample_args = tuple(sample_args)
+    with torch.no_grad():
+        for _ in range(max(warmup, 1)):
+            fn(*sample_args)
+        static_in = tuple(a.clone() if isinstance(a, torch.Tensor) else a for a in sample_args)
+        g = Graph()
+        with graph(g):
+            static_out = fn(*static_in)
+
+    def run(*args):
+        if len(args) != len(static_in):
+            raise TypeError(f"graphed callable takes {len(static_in)} arguments")
+        for dst, src in zip(static_in, args):
+            if isinstance(dst, torch.Tensor):
+                if src.shape != dst.shape or src.dtype != dst.dtype:
+                    raise ValueError(f"graphed callable captured {tuple(dst.shape)} {dst.dtype}, got {tuple(src.shape)} {src.dtype}")
+                if src.data_ptr() != dst.data_ptr():
+                    dst.copy_(src, non_blocking=True)
+        g.replay()
+        return static_out
+
+    run.graph = g
+    run.static_inputs = static_in
+    return run
 
 
 def pin_memory(tensor: torch.Tensor) -> torch.Tensor:

@@ -10,6 +10,10 @@
 * The same passes are registered as graph-executor pre-passes, so a scripted module
   that was not explicitly optimised still gets fusion groups on its first run.
 
+* A fusion group whose inputs are all device tensors is captured as a device graph on its third call with the same
+  shapes; later calls copy the inputs into the graph's buffers and replay it with one submission
+  (``CATCH_B200_JIT_GRAPHS=0`` keeps the interpreter).
+
 Environment: ``CATCH_B200_FORCED_FALLBACK_OPS=a,b`` keeps the listed ops out of fusion
 groups; ``CATCH_B200_FUSED_KERNEL_DEBUG=cpu`` also runs every group on the CPU and
 writes both results to ``fused_kernel_<n>_{device,cpu}.pt``.
@@ -73,7 +77,8 @@ def load(f, map_location=None, _extra_files=None) -> torch.jit.ScriptModule:
 
 def fusion_stats() -> dict:
     return {"runners": _C._jit_fusion_cache_size(), "compiles": _C._jit_fusion_compile_count(),
-            "fallbacks": _C._jit_fusion_fallback_count()}
+            "fallbacks": _C._jit_fusion_fallback_count(), "graph_captures": _C._jit_fusion_graph_capture_count(),
+            "graph_replays": _C._jit_fusion_graph_replay_count()}
 
 
 def optimize(module: torch.jit.ScriptModule, preserved_attrs=None) -> torch.jit.ScriptModule:

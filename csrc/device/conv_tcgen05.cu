@@ -56,6 +56,7 @@ struct ConvArgs {
   int act;
   float alpha;
   double* stats;                // optional [2 * Cout]: per-channel sum and sum of squares of the stored outputs
+  float out_qscale;             // int8 outputs: multiplier before rounding
   // Halo mode (single channel block, every tap on one view, resident weights): per pixel tile (8 wide,
   // 16 high) one column tile of 8 x halo_h pixels is loaded for each distinct horizontal tap offset; a
   // tap's A operand is the window of its column tile shifted down by whole pixel rows (8 x 128 bytes =
@@ -301,7 +302,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
     const int colhalf = (warp - 2) >> 2;
     uint8_t* sbuf = stage_out + (warp - 2) * 4096;
     int acc = 0; uint32_t acc_phase = 0;
-    const int esz = g.out_dtype == B200_F32 ? 4 : 2;
+    const int esz = g.out_dtype == B200_F32 ? 4 : g.out_dtype == B200_I8 ? 1 : 2;
     const int rsz = g.res_dtype == B200_F32 ? 4 : 2;
     const bool has_coef = g.scale != nullptr || g.bias != nullptr;
     const int r = quarter * 32 + lane;
@@ -458,7 +459,28 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
           float v[32];
           finish(rr, c, v);
           uint8_t* op = static_cast<uint8_t*>(g.out) + (off + cbase) * esz;
-          if (g.out_dtype == B200_F32) {
+          if (g.out_dtype == B200_I8) {
+            // quantized for the consumer: four signed bytes per word
+            uint32_t pk[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              uint32_t w = 0;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float qv = fminf(fmaxf(rintf(v[4 * j + e] * g.out_qscale), -127.f), 127.f);
+                w |= ((uint32_t)(int)qv & 0xffu) << (8 * e);
+              }
+              pk[j] = w;
+            }
+            if (valid == 32 && ((reinterpret_cast<uintptr_t>(op) & 15) == 0)) {
+              reinterpret_cast<uint4*>(op)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              reinterpret_cast<uint4*>(op)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < valid) op[j] = (uint8_t)(pk[j >> 2] >> ((j & 3) * 8));
+            }
+          } else if (g.out_dtype == B200_F32) {
             float* o = reinterpret_cast<float*>(op);
             if (valid == 32 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
 #pragma unroll
@@ -760,7 +782,9 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p_in, void* stream) {
   g.alpha = p->alpha == 0.f ? 1.f : p->alpha;
   g.err = error_flag_ptr();
   if (!g.err) return (int)cudaErrorInvalidDevice;
-  g.tma_store = (p->out_dtype != B200_F32 && g.tile_n % 64 == 0 && p->Cout % 8 == 0) ? 1 : 0;
+  g.out_qscale = p->out_qscale;
+  if (p->out_dtype == B200_I8 && !(p->out_qscale > 0.f)) return (int)cudaErrorInvalidValue;
+  g.tma_store = (p->out_dtype != B200_F32 && p->out_dtype != B200_I8 && g.tile_n % 64 == 0 && p->Cout % 8 == 0) ? 1 : 0;
   g.coef_bytes = (p->scale || p->bias) ? 2048 : 0;
   const int smem_cap = 227 * 1024 - 2048 - g.coef_bytes - (g.tma_store ? 32768 : 0);
   // Weights of one output-channel tile (every tap and channel block) stay in shared memory when

@@ -56,6 +56,15 @@ B200_API int b200_stream_synchronize(void* stream);
 B200_API int b200_stream_query(void* stream);  // 0 = done, 1 = busy, <0 = -error
 B200_API int b200_stream_wait_event(void* stream, void* event);
 
+// Stream capture into an executable graph.  Capture runs in relaxed mode (the caching allocator may still ask the
+// driver for memory while a queue is capturing).  b200_graph_end_capture instantiates the captured graph; when
+// the capture was invalidated (a synchronising call inside it) it returns the error and leaves *exec null.
+B200_API int b200_graph_begin_capture(void* stream);
+B200_API int b200_graph_end_capture(void* stream, void** exec, int* num_nodes);
+B200_API int b200_graph_launch(void* exec, void* stream);
+B200_API int b200_graph_destroy(void* exec);
+B200_API int b200_stream_is_capturing(void* stream, int* capturing);
+
 B200_API int b200_event_create(void** event, int enable_timing);
 B200_API int b200_event_destroy(void* event);
 B200_API int b200_event_record(void* event, void* stream);

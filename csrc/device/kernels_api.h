@@ -149,7 +149,7 @@ typedef struct B200ConvParams {
   // element (n,p,q,c) of the result goes to
   //   out + n*o_sn + (p*o_mul_h + o_off_h)*o_sh + (q*o_mul_w + o_off_w)*o_sw + c
   void* out;
-  int out_dtype;
+  int out_dtype;         // B200_BF16 / B200_F16 / B200_F32 / B200_I8 (see out_qscale)
   long long o_sn, o_sh, o_sw;
   int o_mul_h, o_off_h, o_mul_w, o_off_w;
   const void* scale;     // optional per-Cout fp32 multiplier (folded batch norm)
@@ -164,6 +164,9 @@ typedef struct B200ConvParams {
   // and the sum of squares of the values it stores (16-bit outputs, Cout a multiple of 8, tile
   // widths that are multiples of 64 only) so that a following batch norm needs no statistics pass.
   double* stats;
+  // out_dtype == B200_I8: the finished value (after scale / bias / residual / activation) is stored as
+  // clamp(round(v * out_qscale), -127, 127), i.e. already quantized for a consumer whose input scale is out_qscale.
+  float out_qscale;
 } B200ConvParams;
 B200_API int b200_conv_fprop(const B200ConvParams* p, void* stream);
 

@@ -85,6 +85,36 @@ int b200_stream_create(void** stream, int priority) {
   *stream = (void*)s;
   return (int)e;
 }
+int b200_graph_begin_capture(void* stream) {
+  return (int)cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeRelaxed);
+}
+int b200_graph_end_capture(void* stream, void** exec, int* num_nodes) {
+  *exec = nullptr;
+  if (num_nodes) *num_nodes = 0;
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture((cudaStream_t)stream, &graph);
+  if (e != cudaSuccess || !graph) {
+    cudaGetLastError();  // an invalidated capture leaves a sticky-looking (but recoverable) error behind
+    return (int)(e != cudaSuccess ? e : cudaErrorStreamCaptureInvalidated);
+  }
+  size_t n = 0;
+  cudaGraphGetNodes(graph, nullptr, &n);
+  if (num_nodes) *num_nodes = (int)n;
+  cudaGraphExec_t ex = nullptr;
+  e = cudaGraphInstantiate(&ex, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) return (int)e;
+  *exec = (void*)ex;
+  return 0;
+}
+int b200_graph_launch(void* exec, void* stream) { return (int)cudaGraphLaunch((cudaGraphExec_t)exec, (cudaStream_t)stream); }
+int b200_graph_destroy(void* exec) { return (int)cudaGraphExecDestroy((cudaGraphExec_t)exec); }
+int b200_stream_is_capturing(void* stream, int* capturing) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  cudaError_t e = cudaStreamIsCapturing((cudaStream_t)stream, &st);
+  *capturing = st == cudaStreamCaptureStatusActive ? 1 : 0;
+  return (int)e;
+}
 int b200_stream_destroy(void* stream) { return (int)cudaStreamDestroy((cudaStream_t)stream); }
 int b200_stream_synchronize(void* stream) { return (int)cudaStreamSynchronize((cudaStream_t)stream); }
 int b200_stream_query(void* stream) {

@@ -34,6 +34,8 @@ int64_t fusion_cache_size();
 void fusion_cache_clear();
 int64_t fusion_compile_count();
 int64_t fusion_fallback_count();
+int64_t fusion_graph_capture_count();  // fusion groups captured as device graphs
+int64_t fusion_graph_replay_count();
 
 }  // namespace jit
 }  // namespace catch_b200

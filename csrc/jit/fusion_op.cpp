@@ -14,7 +14,12 @@
 #include <sstream>
 #include <unordered_map>
 
+#include "../runtime/backend.h"
+#include "../runtime/device.h"
+#include "../runtime/graph.h"
 #include "../runtime/log.h"
+#include "../runtime/notifier.h"
+#include "../runtime/queue.h"
 #include "../runtime/tensor_impl.h"
 #include "fusion.h"
 
@@ -25,7 +30,26 @@ using namespace torch::jit;
 
 namespace {
 
-std::atomic<int64_t> g_compiles{0}, g_fallbacks{0};
+std::atomic<int64_t> g_compiles{0}, g_fallbacks{0}, g_graph_captures{0}, g_graph_replays{0};
+
+// A compiled group plus, once the same argument shapes have been seen a few times, its captured device graph:
+// the group then costs one submission instead of one per kernel.  CATCH_B200_JIT_GRAPHS=0 keeps the interpreter.
+struct Plan {
+  std::shared_ptr<Code> code;
+  std::mutex mu;                 // the static buffers of a captured plan serve one call at a time
+  int eager_runs = 0;
+  int graph_state = 0;           // 0 undecided, 1 captured, -1 cannot be captured
+  std::unique_ptr<DeviceGraph> graph;
+  std::vector<at::Tensor> static_in, static_out;
+};
+
+bool graphs_wanted() {
+  static const bool on = [] {
+    const char* e = std::getenv("CATCH_B200_JIT_GRAPHS");
+    return !(e && std::string(e) == "0");
+  }();
+  return on && backend().supports_graphs();
+}
 
 std::string arg_spec(const Stack& stack, size_t n_inputs) {
   std::ostringstream os;
@@ -49,7 +73,7 @@ class FusedRunner {
   void run(Stack& stack) {
     const size_t n_in = graph_->inputs().size();
     const std::string spec = arg_spec(stack, n_in);
-    std::shared_ptr<Code> plan;
+    std::shared_ptr<Plan> plan;
     {
       std::lock_guard<std::mutex> g(mu_);
       auto it = plans_.find(spec);
@@ -62,7 +86,9 @@ class FusedRunner {
     const char* dbg = std::getenv("CATCH_B200_FUSED_KERNEL_DEBUG");
     try {
       if (!plan) plan = compile(spec, stack, n_in);
-      InterpreterState(*plan).run(stack);
+      if (!dbg && graphs_wanted() && run_graphed(*plan, stack, saved, base)) return;
+      InterpreterState(*plan->code).run(stack);
+      plan->eager_runs++;
     } catch (const c10::OutOfMemoryError&) {
       throw;
     } catch (const std::exception& e) {
@@ -81,7 +107,82 @@ class FusedRunner {
   }
 
  private:
-  std::shared_ptr<Code> compile(const std::string& spec, const Stack& stack, size_t n_in) {
+  // Replays (after capturing, on the third call with these shapes) the plan's device graph.  Returns false when
+  // this call has to go through the interpreter; the stack is untouched then.
+  bool run_graphed(Plan& plan, Stack& stack, const Stack& inputs, size_t base) {
+    if (plan.graph_state < 0 || (plan.graph_state == 0 && plan.eager_runs < 2)) return false;
+    int device = -1;
+    for (const IValue& v : inputs) {
+      if (!v.isTensor() || !v.toTensor().defined()) return false;  // scalars would be baked into the graph
+      const at::Tensor& t = v.toTensor();
+      if (!is_b200(t) || (device >= 0 && t.device().index() != device)) return false;
+      if (t.requires_grad() && at::GradMode::is_enabled()) return false;
+      device = t.device().index();
+    }
+    if (device < 0) return false;
+    std::lock_guard<std::mutex> lk(plan.mu);
+    if (plan.graph_state == 0 && !capture(plan, inputs, device)) return false;
+    if (plan.graph_state != 1) return false;
+    for (size_t i = 0; i < inputs.size(); ++i) {
+      const at::Tensor& src = inputs[i].toTensor();
+      if (src.data_ptr() != plan.static_in[i].data_ptr()) plan.static_in[i].copy_(src, /*non_blocking=*/true);
+    }
+    plan.graph->replay();
+    g_graph_replays++;
+    stack.resize(base);
+    // the static outputs are overwritten by the next call: hand out copies
+    for (const at::Tensor& o : plan.static_out) stack.emplace_back(o.clone());
+    return true;
+  }
+
+  bool capture(Plan& plan, const Stack& inputs, int device) {
+    plan.graph_state = -1;  // until proven otherwise
+    DeviceSwitch sw(device);
+    std::vector<at::Tensor> statics;
+    for (const IValue& v : inputs) statics.push_back(v.toTensor().clone());
+    const Queue main = getCurrentQueue(device), side = getQueueFromPool(device);
+    {
+      Notifier ready(false);
+      ready.place(main);
+      ready.wait(side);
+    }
+    auto graph = std::make_unique<DeviceGraph>();
+    Stack st;
+    bool ok = false;
+    {
+      QueueGuard qg(side);
+      try {
+        graph->capture_begin();
+        for (const at::Tensor& t : statics) st.emplace_back(t);
+        InterpreterState(*plan.code).run(st);
+        ok = graph->capture_end();
+      } catch (const std::exception& e) {
+        graph->capture_abort();
+        B200LOG(DBG) << "fusion group not captured as a device graph: " << e.what();
+        ok = false;
+      }
+    }
+    {
+      Notifier done(false);
+      done.place(side);
+      done.wait(main);
+    }
+    if (!ok) return false;
+    std::vector<at::Tensor> outs;
+    for (const IValue& v : st) {
+      if (!v.isTensor() || !v.toTensor().defined()) return false;  // graph dropped with `graph`
+      outs.push_back(v.toTensor());
+    }
+    plan.graph = std::move(graph);
+    plan.static_in = std::move(statics);
+    plan.static_out = std::move(outs);
+    plan.graph_state = 1;
+    g_graph_captures++;
+    B200LOG(DBG) << "fusion group captured as a device graph with " << plan.graph->num_nodes() << " nodes";
+    return true;
+  }
+
+  std::shared_ptr<Plan> compile(const std::string& spec, const Stack& stack, size_t n_in) {
     // specialise a copy of the subgraph: concrete input types, fused kernels
     std::shared_ptr<Graph> g = graph_->copy();
     for (size_t i = 0; i < n_in; ++i) {
@@ -89,11 +190,12 @@ class FusedRunner {
       if (v.isTensor() && v.toTensor().defined()) g->inputs()[i]->setType(TensorType::create(v.toTensor()));
     }
     FuseKernels(g);
-    auto code = std::make_shared<Code>(g, "b200_fusion_group");
+    auto plan = std::make_shared<Plan>();
+    plan->code = std::make_shared<Code>(g, "b200_fusion_group");
     g_compiles++;
     std::lock_guard<std::mutex> lk(mu_);
-    plans_[spec] = code;
-    return code;
+    plans_[spec] = plan;
+    return plan;
   }
 
   void run_fallback(Stack& stack, const Stack& saved) {
@@ -134,7 +236,7 @@ class FusedRunner {
   std::shared_ptr<Graph> graph_;
   Code fallback_;
   std::mutex mu_;
-  std::unordered_map<std::string, std::shared_ptr<Code>> plans_;
+  std::unordered_map<std::string, std::shared_ptr<Plan>> plans_;
 };
 
 class RunnerCache {
@@ -197,6 +299,8 @@ int64_t fusion_cache_size() { return RunnerCache::get().size(); }
 void fusion_cache_clear() { RunnerCache::get().clear(); }
 int64_t fusion_compile_count() { return g_compiles.load(); }
 int64_t fusion_fallback_count() { return g_fallbacks.load(); }
+int64_t fusion_graph_capture_count() { return g_graph_captures.load(); }
+int64_t fusion_graph_replay_count() { return g_graph_replays.load(); }
 
 }  // namespace jit
 }  // namespace catch_b200

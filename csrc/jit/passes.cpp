@@ -114,6 +114,52 @@ void LowerGraph(std::shared_ptr<Graph>& graph) {
 }
 
 // -------------------------------------------------------------------- kernel fusion
+namespace {
+
+// Input scale of a quantized convolution node when it is known at pass time (frozen module: the scale and mode
+// tensors are constants) and the layer is active; 0 otherwise.
+double constant_input_scale(Node* n) {
+  static const Symbol qconv = Symbol::fromQualString("catch_b200::qconv_act");
+  if (n->kind() != qconv) return 0.0;
+  auto qs = toIValue(n->input(7));
+  auto qm = toIValue(n->input(8));
+  if (!qs.has_value() || !qs->isTensor() || qs->toTensor().numel() == 0) return 0.0;
+  if (qm.has_value() && qm->isTensor() && qm->toTensor().numel() > 0 &&
+      qm->toTensor().cpu().to(at::kDouble).view({-1})[0].item<double>() == 0.0) return 0.0;
+  if (qm.has_value() && !qm->isTensor() && !qm->isNone()) return 0.0;
+  if (!qm.has_value()) return 0.0;  // mode decided at run time
+  return qs->toTensor().cpu().to(at::kDouble).view({-1})[0].item<double>();
+}
+
+// A quantized convolution whose result is consumed only as the input of quantized convolutions that share one
+// input scale emits int8 quantized with that scale: the consumers skip their quantization pass and the
+// activation crosses memory at one byte per element.
+void chain_quantized(Block* block) {
+  static const Symbol qconv = Symbol::fromQualString("catch_b200::qconv_act");
+  for (Node* n : block->nodes()) {
+    for (Block* b : n->blocks()) chain_quantized(b);
+    if (n->kind() != qconv) continue;
+    auto os = toIValue(n->input(11));
+    if (!os.has_value() || !os->isDouble() || os->toDouble() != 0.0) continue;
+    if (constant_input_scale(n) == 0.0) continue;  // an unquantized producer keeps its floating-point result
+    const auto& uses = n->output()->uses();
+    if (uses.empty()) continue;
+    double scale = 0.0;
+    bool ok = true;
+    for (const Use& u : uses) {
+      const double s = u.offset == 0 ? constant_input_scale(u.user) : 0.0;
+      if (s == 0.0 || (scale != 0.0 && s != scale)) { ok = false; break; }
+      scale = s;
+    }
+    if (!ok) continue;
+    WithInsertPoint guard(n);
+    n->replaceInput(11, block->owningGraph()->insertConstant(scale));
+    n->output()->setType(TensorType::get());
+  }
+}
+
+}  // namespace
+
 void FuseKernels(std::shared_ptr<Graph>& graph) {
   if (!fusion_enabled()) return;
   // Longest chains first.  `%none` placeholders are created inside the replacement.
@@ -180,6 +226,38 @@ void FuseKernels(std::shared_ptr<Graph>& graph) {
       %y = catch_b200::linear_act(%x, %w, %b, %act)
       return (%y))IR";
 
+  // Quantized convolutions (catch_b200::conv2d carries the calibrated scales): the same three chains.
+  const std::string qconv_args = "%x, %w, %b, %p, %s, %d, %g, %qs, %qm";
+  const std::string qconv_add_relu = "graph(" + qconv_args + R"IR(, %res, %alpha):
+      %y = catch_b200::conv2d()IR" + qconv_args + R"IR()
+      %z = aten::add(%y, %res, %alpha)
+      %r = aten::relu(%z)
+      return (%r))IR";
+  const std::string qconv_add_relu_fused = "graph(" + qconv_args + R"IR(, %res, %alpha):
+      %act : int = prim::Constant[value=1]()
+      %os : float = prim::Constant[value=0.]()
+      %r = catch_b200::qconv_act()IR" + qconv_args + R"IR(, %res, %act, %os)
+      return (%r))IR";
+  const std::string qconv_relu = "graph(" + qconv_args + R"IR():
+      %y = catch_b200::conv2d()IR" + qconv_args + R"IR()
+      %r = aten::relu(%y)
+      return (%r))IR";
+  const std::string qconv_relu_fused = "graph(" + qconv_args + R"IR():
+      %none : NoneType = prim::Constant()
+      %act : int = prim::Constant[value=1]()
+      %os : float = prim::Constant[value=0.]()
+      %r = catch_b200::qconv_act()IR" + qconv_args + R"IR(, %none, %act, %os)
+      return (%r))IR";
+  const std::string qconv_only = "graph(" + qconv_args + R"IR():
+      %y = catch_b200::conv2d()IR" + qconv_args + R"IR()
+      return (%y))IR";
+  const std::string qconv_only_fused = "graph(" + qconv_args + R"IR():
+      %none : NoneType = prim::Constant()
+      %act : int = prim::Constant[value=0]()
+      %os : float = prim::Constant[value=0.]()
+      %y = catch_b200::qconv_act()IR" + qconv_args + R"IR(, %none, %act, %os)
+      return (%y))IR";
+
   // the residual pattern only applies when alpha == 1
   auto alpha_is_one = [](const Match& m, const std::unordered_map<std::string, Value*>& vmap) {
     Value* a = m.values_map.at(vmap.at("alpha"));
@@ -194,11 +272,13 @@ void FuseKernels(std::shared_ptr<Graph>& graph) {
   {
     SubgraphRewriter rw;
     rw.RegisterRewritePattern(conv_add_relu, conv_add_relu_fused);
+    rw.RegisterRewritePattern(qconv_add_relu, qconv_add_relu_fused);
     rw.runOnGraph(graph, alpha_is_one);
   }
   {
     SubgraphRewriter rw;
     rw.RegisterRewritePattern(conv_relu, conv_relu_fused);
+    rw.RegisterRewritePattern(qconv_relu, qconv_relu_fused);
     rw.RegisterRewritePattern(linear_relu, linear_relu_fused);
     rw.runOnGraph(graph);
   }
@@ -210,9 +290,11 @@ void FuseKernels(std::shared_ptr<Graph>& graph) {
   {
     SubgraphRewriter rw;
     rw.RegisterRewritePattern(conv_only, conv_only_fused);
+    rw.RegisterRewritePattern(qconv_only, qconv_only_fused);
     rw.RegisterRewritePattern(linear_only, linear_only_fused);
     rw.runOnGraph(graph);
   }
+  chain_quantized(graph->block());
   EliminateDeadCode(graph);
 }
 
@@ -238,7 +320,8 @@ std::unordered_set<std::string> forced_fallback_ops() {
 
 const std::unordered_set<std::string>& supported_ops() {
   static const std::unordered_set<std::string> ops = {
-      "catch_b200::conv_bn_act", "catch_b200::linear_act", "aten::relu", "aten::relu_", "aten::hardtanh",
+      "catch_b200::conv_bn_act", "catch_b200::linear_act", "catch_b200::qconv_act", "catch_b200::conv2d",
+      "catch_b200::linear", "aten::relu", "aten::relu_", "aten::hardtanh",
       "aten::hardtanh_", "aten::batch_norm", "aten::cat", "aten::conv2d", "aten::_convolution", "aten::add",
       "aten::sub", "aten::mul", "aten::div", "aten::floor", "aten::addmm", "aten::linear", "aten::matmul",
       "aten::max_pool2d", "aten::avg_pool2d", "aten::adaptive_avg_pool2d", "aten::reshape", "aten::view",

@@ -19,6 +19,7 @@
 
 #include "../runtime/host_allocator.h"
 #include "common.h"
+#include "../runtime/graph.h"
 #include "../runtime/profiler.h"
 #include "kernels.h"
 
@@ -36,7 +37,7 @@ OpScope::OpScope(const char* name, int device) : name_(name), device_(device), s
 }
 OpScope::~OpScope() noexcept(false) {
   trace_set_current_op(prev_op_);
-  if (flags().async_disable && !hostsim()) getCurrentQueue(device_).synchronize();
+  if (flags().async_disable && !hostsim() && !graphCaptureActive()) getCurrentQueue(device_).synchronize();
 }
 
 std::string describe(const at::Tensor& t) {

@@ -130,16 +130,21 @@ bool quant_active(const std::optional<Tensor>& q_scale, const std::optional<Tens
   return true;
 }
 
+// input: floating point (quantized here with q_scale[0]) or int8 that a producer already quantized with that scale.
+// residual / act: added / applied to the de-quantized result in the epilogue.  out_scale > 0: the result leaves the
+// kernel as int8, quantized with out_scale (the input scale of the consumer), instead of as a 16-bit tensor.
 Tensor qconv2d_device(const Tensor& input, const Tensor& weight, const std::optional<Tensor>& bias,
                       at::IntArrayRef padding, at::IntArrayRef stride, at::IntArrayRef dilation, int64_t groups,
-                      const Tensor& q_scale, int64_t mode) {
+                      const Tensor& q_scale, int64_t mode, const std::optional<Tensor>& residual = std::nullopt,
+                      int64_t act = 0, double out_scale = 0.0) {
   TORCH_CHECK(input.dim() == 4 && weight.dim() == 4 && groups == 1 && dilation[0] == 1 && dilation[1] == 1,
               "b200 quantized conv2d: only dense 2-D convolutions");
   TORCH_CHECK(stride[0] >= 1 && stride[0] <= 2 && stride[1] >= 1 && stride[1] <= 2, "b200 quantized conv2d: stride 1 or 2");
   const int64_t N = input.size(0), C = input.size(1), H = input.size(2), W = input.size(3);
   const int64_t K = weight.size(0), R = weight.size(2), S = weight.size(3);
   TORCH_CHECK(C % 16 == 0 && K % 8 == 0, "b200 quantized conv2d: channels must be multiples of 16 (in) and 8 (out)");
-  const at::ScalarType ft = input.scalar_type();
+  const bool pre_quantized = input.scalar_type() == at::kChar;
+  const at::ScalarType ft = pre_quantized ? weight.scalar_type() : input.scalar_type();
   TORCH_CHECK(ft == at::kHalf || ft == at::kBFloat16 || ft == at::kFloat, "b200 quantized conv2d: unsupported dtype ", ft);
   const std::vector<double> sc = host_values(q_scale);
   const double s_in = sc[0];
@@ -147,15 +152,18 @@ Tensor qconv2d_device(const Tensor& input, const Tensor& weight, const std::opti
   OpScope scope("quantized_conv2d", input);
   const int64_t P = (H + 2 * padding[0] - R) / stride[0] + 1, Q = (W + 2 * padding[1] - S) / stride[1] + 1;
   Tensor x = input.contiguous(at::MemoryFormat::ChannelsLast);
-  if (C == 1 || (H == 1 && W == 1)) x = empty_b200(input.sizes(), ft, input.device().index(), at::MemoryFormat::ChannelsLast).copy_(input);
-  Tensor xq = empty_b200(x.sizes(), at::kChar, input.device().index(), at::MemoryFormat::ChannelsLast);
-  B200_KERNEL_CHECK(b200_quantize_int8(x.data_ptr(), to_b200_dtype(ft), x.numel(), (float)s_in, xq.data_ptr(), scope.stream()));
+  if (C == 1 || (H == 1 && W == 1)) x = empty_b200(input.sizes(), input.scalar_type(), input.device().index(), at::MemoryFormat::ChannelsLast).copy_(input);
+  Tensor xq = x;
+  if (!pre_quantized) {
+    xq = empty_b200(x.sizes(), at::kChar, input.device().index(), at::MemoryFormat::ChannelsLast);
+    B200_KERNEL_CHECK(b200_quantize_int8(x.data_ptr(), to_b200_dtype(ft), x.numel(), (float)s_in, xq.data_ptr(), scope.stream()));
+  }
   Tensor wcl = weight.contiguous(at::MemoryFormat::ChannelsLast);
   if (R == 1 && S == 1) wcl = empty_b200(weight.sizes(), weight.scalar_type(), weight.device().index(), at::MemoryFormat::ChannelsLast).copy_(weight);
   Tensor w2d = wcl.permute({0, 2, 3, 1}).reshape({K, R * S * C});  // a view: memory is [K][R][S][C]
   QWeight qw = quantize_weight(weight, w2d, mode != 1, s_w, scope);
   Tensor inv = dequant_scale(weight, qw, s_in);
-  const at::ScalarType ot = ft == at::kFloat ? at::kHalf : ft;
+  const at::ScalarType ot = out_scale > 0 ? at::kChar : ft == at::kFloat ? at::kHalf : ft;
   Tensor out = empty_b200({N, K, P, Q}, ot, input.device().index(), at::MemoryFormat::ChannelsLast);
   B200ConvParams p;
   std::memset(&p, 0, sizeof(p));
@@ -198,8 +206,19 @@ Tensor qconv2d_device(const Tensor& input, const Tensor& weight, const std::opti
     p.bias = b.data_ptr();
     p.bias_dtype = B200_F32;
   }
+  Tensor res;
+  if (residual.has_value() && residual->defined()) {
+    TORCH_CHECK(residual->sizes() == out.sizes(), "b200 quantized conv2d: the residual must have the output's shape");
+    res = residual->scalar_type() == at::kFloat || residual->scalar_type() == at::kHalf || residual->scalar_type() == at::kBFloat16
+              ? *residual : residual->to(ft == at::kFloat ? at::kHalf : ft);
+    res = res.contiguous(at::MemoryFormat::ChannelsLast);  // addressed with the output's element offsets
+    p.residual = res.data_ptr();
+    p.res_dtype = to_b200_dtype(res.scalar_type());
+  }
+  p.act = (int)act;
+  p.out_qscale = (float)out_scale;
   B200_KERNEL_CHECK(b200_conv_fprop(&p, scope.stream()));
-  return ft == at::kFloat ? out.to(at::kFloat) : out;
+  return ft == at::kFloat && out_scale <= 0 ? out.to(at::kFloat) : out;
 }
 
 Tensor qlinear_device(const Tensor& input, const Tensor& weight, const std::optional<Tensor>& bias, const Tensor& q_scale,
@@ -277,6 +296,46 @@ Tensor qconv2d(const Tensor& input, const Tensor& weight, const std::optional<Te
   } catch (const std::exception& e) {
     if (!flags().op_trycatch) throw;
     B200LOG(DBG) << "quantized conv2d: device kernel rejected the configuration (" << e.what() << "); emulating.";
+    return reference();
+  }
+}
+
+// conv2d (quantized or not) + residual + ReLU + optional re-quantization for the next quantized layer: what the
+// fusion pass makes of catch_b200::conv2d -> add -> relu chains (the reference folds the same chain into one
+// quantized convolution node: torch_mlu/csrc/jit/codegen/convertion/ops/conv.cpp:180-216).
+Tensor qconv_act(const Tensor& input, const Tensor& weight, const std::optional<Tensor>& bias, at::IntArrayRef padding,
+                 at::IntArrayRef stride, at::IntArrayRef dilation, int64_t groups, const std::optional<Tensor>& q_scale,
+                 const std::optional<Tensor>& q_mode, const std::optional<Tensor>& residual, int64_t act, double out_scale) {
+  const bool pre_quantized = input.scalar_type() == at::kChar;
+  const bool quant = quant_active(q_scale, q_mode);
+  TORCH_CHECK(quant || !pre_quantized, "catch_b200::qconv_act: an int8 input needs the layer's quantization scale");
+  const at::ScalarType ft = pre_quantized ? weight.scalar_type() : input.scalar_type();
+  auto finish = [&](Tensor y) {
+    if (residual.has_value() && residual->defined()) y = y + residual->to(y.scalar_type());
+    if (act == 1) y = at::relu(y);
+    if (out_scale > 0) return at::clamp(at::round(y.to(at::kFloat) * out_scale), -127, 127).to(at::kChar);
+    return y;
+  };
+  if (!quant) return finish(at::conv2d(input, weight, bias, stride, padding, dilation, groups));
+  const int64_t mode = mode_of(q_mode);
+  auto reference = [&]() {
+    Tensor sc = q_scale->cpu().to(at::kDouble);
+    const double s_in = sc[0].item<double>();
+    Tensor xq = pre_quantized ? input.to(at::kFloat) / s_in : fake_quant(input.to(at::kFloat), s_in);
+    Tensor wf = weight.to(at::kFloat);
+    Tensor wq = mode == 1 && sc.numel() > 1 ? fake_quant(wf, sc[1].item<double>()) : fake_quant_rows(wf);
+    std::optional<Tensor> b;
+    if (bias.has_value() && bias->defined()) b = bias->to(at::kFloat);
+    return finish(at::conv2d(xq, wq, b, stride, padding, dilation, groups).to(ft));
+  };
+  if (use_cpu_path() || !is_b200(input)) return reference();
+  try {
+    return qconv2d_device(input, weight, bias, padding, stride, dilation, groups, *q_scale, mode, residual, act, out_scale);
+  } catch (const c10::OutOfMemoryError&) {
+    throw;
+  } catch (const std::exception& e) {
+    if (!flags().op_trycatch) throw;
+    B200LOG(DBG) << "qconv_act: device kernel rejected the configuration (" << e.what() << "); emulating.";
     return reference();
   }
 }
@@ -360,9 +419,12 @@ TORCH_LIBRARY_FRAGMENT(catch_b200, m) {
         "Tensor? q_scale, Tensor? q_mode) -> Tensor");
   m.def("linear(Tensor input, Tensor weight, Tensor? bias, Tensor? q_scale, Tensor? q_mode) -> Tensor");
   m.def("absmax(Tensor t) -> Tensor");
+  m.def("qconv_act(Tensor input, Tensor weight, Tensor? bias, int[] padding, int[] stride, int[] dilation, int groups, "
+        "Tensor? q_scale, Tensor? q_mode, Tensor? residual, int act, float out_scale) -> Tensor");
 }
 TORCH_LIBRARY_IMPL(catch_b200, CompositeExplicitAutograd, m) {
   m.impl("conv2d", TORCH_FN(qconv2d));
+  m.impl("qconv_act", TORCH_FN(qconv_act));
   m.impl("conv1d", TORCH_FN(qconv1d));
   m.impl("conv3d", TORCH_FN(qconv3d));
   m.impl("view", TORCH_FN(view_op));

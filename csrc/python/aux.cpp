@@ -20,6 +20,8 @@ void bind_aux(py::module& m) {
   m.def("_jit_register_passes", &jit::register_passes);
   m.def("_jit_fusion_cache_size", &jit::fusion_cache_size);
   m.def("_jit_fusion_cache_clear", &jit::fusion_cache_clear);
+  m.def("_jit_fusion_graph_capture_count", &jit::fusion_graph_capture_count);
+  m.def("_jit_fusion_graph_replay_count", &jit::fusion_graph_replay_count);
   m.def("_jit_fusion_compile_count", &jit::fusion_compile_count);
   m.def("_jit_fusion_fallback_count", &jit::fusion_fallback_count);
   m.def("_jit_pass_lower_graph", [](std::shared_ptr<torch::jit::Graph>& g) { jit::LowerGraph(g); });

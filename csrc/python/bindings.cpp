@@ -10,6 +10,7 @@
 #include "../runtime/caching_allocator.h"
 #include "../runtime/device.h"
 #include "../runtime/generator.h"
+#include "../runtime/graph.h"
 #include "../runtime/host_allocator.h"
 #include "../runtime/log.h"
 #include "../runtime/notifier.h"
@@ -87,6 +88,26 @@ PYBIND11_MODULE(_C, m) {
   m.def("_getCurrentQueue", [](int d) { return getCurrentQueue(d); }, py::arg("device") = -1);
   m.def("_getQueueById", [](int d, int id) { return getQueueById(d, id); });
   m.def("_setCurrentQueue", [](const Queue& q) { setCurrentQueue(q); });
+
+  // ---- executable graphs
+  py::class_<DeviceGraph>(m, "_Graph")
+      .def(py::init<>())
+      .def("capture_begin", &DeviceGraph::capture_begin)
+      .def("capture_end", &DeviceGraph::capture_end)
+      .def("capture_abort", &DeviceGraph::capture_abort)
+      .def("replay", &DeviceGraph::replay)
+      .def("reset", [](DeviceGraph& g) {
+        py::gil_scoped_release nogil;
+        g.reset();
+      })
+      .def_property_readonly("valid", &DeviceGraph::valid)
+      .def_property_readonly("num_nodes", &DeviceGraph::num_nodes);
+  // allocator pools behind graph capture (exposed for tests of the pool bookkeeping without a device)
+  m.def("_new_private_pool", [] { return newPrivatePool(); });
+  m.def("_set_thread_private_pool", [](uint64_t p) { return setThreadPrivatePool(p); });
+  m.def("_retire_private_pool", [](uint64_t p) { retirePrivatePool(p); });
+  m.def("_graphs_supported", [] { return backend().supports_graphs(); });
+  m.def("_graph_capture_active", [] { return graphCaptureActive(); });
 
   // ---- notifiers
   py::class_<PyNotifier>(m, "_Notifier")

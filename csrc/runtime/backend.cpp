@@ -80,6 +80,19 @@ class CudaBackend final : public Backend {
   }
   void stream_wait_event(void* s, void* e) override { B200_DEVICE_CHECK(b200_stream_wait_event(s, e)); }
 
+  bool supports_graphs() const override { return true; }
+  void graph_begin_capture(void* s) override { B200_DEVICE_CHECK(b200_graph_begin_capture(s)); }
+  void* graph_end_capture(void* s, int* num_nodes) override {
+    void* exec = nullptr;
+    const int rc = b200_graph_end_capture(s, &exec, num_nodes);
+    if (rc != 0) {
+      B200LOG(DBG) << "graph capture did not produce a graph: " << b200_error_string(rc);
+      return nullptr;
+    }
+    return exec;
+  }
+  void graph_launch(void* exec, void* s) override { B200_DEVICE_CHECK(b200_graph_launch(exec, s)); }
+  void graph_destroy(void* exec) override { B200_DEVICE_WARN(b200_graph_destroy(exec)); }
   void* event_create(bool timing) override {
     void* e = nullptr;
     B200_DEVICE_CHECK(b200_event_create(&e, timing ? 1 : 0));
@@ -199,6 +212,12 @@ class HostSimBackend final : public Backend {
   bool stream_query(void*) override { return true; }
   void stream_wait_event(void*, void*) override {}
 
+  // Simulated work runs when it is submitted, so there is nothing to capture or replay.
+  bool supports_graphs() const override { return false; }
+  void graph_begin_capture(void*) override { TORCH_CHECK(false, "b200(hostsim): graph capture needs a device"); }
+  void* graph_end_capture(void*, int*) override { return nullptr; }
+  void graph_launch(void*, void*) override { TORCH_CHECK(false, "b200(hostsim): graph replay needs a device"); }
+  void graph_destroy(void*) override {}
   void* event_create(bool) override { return new SimEvent(); }
   void event_destroy(void* e) override { delete static_cast<SimEvent*>(e); }
   void event_record(void* e, void*) override {

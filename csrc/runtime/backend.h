@@ -57,6 +57,13 @@ class Backend {
   virtual bool stream_query(void* s) = 0;
   virtual void stream_wait_event(void* s, void* e) = 0;
 
+  // Stream capture (executable graphs).  graph_end_capture returns null when the capture was invalidated.
+  virtual bool supports_graphs() const = 0;
+  virtual void graph_begin_capture(void* s) = 0;
+  virtual void* graph_end_capture(void* s, int* num_nodes) = 0;
+  virtual void graph_launch(void* exec, void* s) = 0;
+  virtual void graph_destroy(void* exec) = 0;
+
   virtual void* event_create(bool timing) = 0;
   virtual void event_destroy(void* e) = 0;
   virtual void event_record(void* e, void* s) = 0;

@@ -36,6 +36,7 @@ constexpr size_t kMidSegment = 20 << 20;
 constexpr size_t kLargeRound = 2 << 20;        // bigger segments are rounded to 2 MiB
 constexpr size_t kGuard = 512;                 // debug guard region on each side
 constexpr uint8_t kGuardByte = 0xA5;
+thread_local uint64_t t_private_pool = 0;  // pool that this thread's allocations use (graph capture)
 std::atomic<AllocationContextHook> g_context_hook{nullptr};
 
 inline size_t round_up(size_t n, size_t m) { return (n + m - 1) / m * m; }
@@ -55,10 +56,16 @@ struct Block {
   // debug mode: where the block was handed out (native return addresses, context text of the hook)
   std::vector<void*> origin_frames;
   std::string origin_context;
+  // 0 = the shared cache; otherwise the private pool of a captured graph: its free blocks serve only
+  // allocations made while that graph is being captured, so memory whose address is baked into the graph is
+  // never handed to anybody else while the graph exists
+  uint64_t pool = 0;
+  bool guarded = false;    // handed out in debug mode: guard regions on both sides of the user range
 };
 
 struct BlockLess {
   bool operator()(const Block* a, const Block* b) const {
+    if (a->pool != b->pool) return a->pool < b->pool;
     if (a->queue_key != b->queue_key) return a->queue_key < b->queue_key;
     if (a->size != b->size) return a->size < b->size;
     return a->ptr < b->ptr;
@@ -100,9 +107,10 @@ class CachingAllocator final : public c10::Allocator {
     key.queue_key = q.pack();
     key.size = want;
     key.ptr = nullptr;
+    key.pool = t_private_pool;
     Block* blk = nullptr;
     auto it = pool.lower_bound(&key);
-    if (it != pool.end() && (*it)->queue_key == key.queue_key) {
+    if (it != pool.end() && (*it)->queue_key == key.queue_key && (*it)->pool == key.pool) {
       blk = *it;
       pool.erase(it);
     } else {
@@ -115,6 +123,7 @@ class CachingAllocator final : public c10::Allocator {
       Block* rest = new Block();
       rest->device = device;
       rest->queue_key = blk->queue_key;
+      rest->pool = blk->pool;
       rest->size = remain;
       rest->ptr = blk->ptr + want;
       rest->small = small;
@@ -130,6 +139,7 @@ class CachingAllocator final : public c10::Allocator {
     st.stats.allocated += static_cast<int64_t>(blk->size);
     st.stats.max_allocated = std::max(st.stats.max_allocated, st.stats.allocated);
     st.stats.num_alloc++;
+    blk->guarded = debug_;
     char* user = blk->ptr + (debug_ ? kGuard : 0);
     if (debug_) {
       paint_guards(blk, q);
@@ -150,7 +160,7 @@ class CachingAllocator final : public c10::Allocator {
     Block* blk = it->second;
     live_.erase(it);
     DeviceState& st = state(blk->device);
-    if (debug_) {
+    if (blk->guarded) {
       std::string why;
       if (!verify_guards(blk, &why)) {
         B200LOG(ERROR) << "memory debug: out-of-bounds write detected on free: " << why;
@@ -159,12 +169,14 @@ class CachingAllocator final : public c10::Allocator {
       }
     }
     blk->in_use = false;
+    blk->guarded = false;
     blk->origin_frames.clear();
     blk->origin_context.clear();
     st.stats.allocated -= static_cast<int64_t>(blk->size);
     st.stats.num_free++;
     c10::reportMemoryUsageToProfiler(user, -static_cast<int64_t>(blk->size), st.stats.allocated, st.stats.reserved,
                                      make_device(blk->device));
+    if (!blk->other_queues.empty() && t_private_pool != 0) blk->other_queues.clear();  // no notifiers inside a capture
     if (!blk->other_queues.empty()) {
       // The block was also used on other queues: give it back only after
       // everything those queues have been asked to do so far has finished.
@@ -215,20 +227,39 @@ class CachingAllocator final : public c10::Allocator {
     s.max_reserved = s.reserved;
   }
 
-  void set_native(bool v) { native_ = v; }
-  bool native() const { return native_; }
-  void set_debug(bool v) {
+  // ------------------------------------------------------- graph-private pools
+  uint64_t new_pool() {
     std::lock_guard<std::recursive_mutex> g(mu_);
-    TORCH_CHECK(live_.empty() || v == debug_, "memory debug mode can only be switched while no b200 block is alive");
-    if (v != debug_) {
-      // Cached blocks were sized without guards (or with): drop them.
-      for (int d = 0; d < kMaxDevices; ++d) {
-        if (!states_[d]) continue;
-        sync_pending(*states_[d]);
-        release_segments(*states_[d], states_[d]->small_free, d);
-        release_segments(*states_[d], states_[d]->large_free, d);
+    return ++next_pool_;
+  }
+  // The graph that owned `pool` was destroyed: its free blocks join the shared cache now, blocks still in use
+  // (tensors the capture returned) follow when they are freed.
+  void retire_pool(uint64_t pool) {
+    if (pool == 0) return;
+    std::lock_guard<std::recursive_mutex> g(mu_);
+    retired_pools_.insert(pool);
+    for (int d = 0; d < kMaxDevices; ++d) {
+      if (!states_[d]) continue;
+      for (Pool* fp : {&states_[d]->small_free, &states_[d]->large_free}) {
+        std::vector<Block*> mine;
+        for (Block* b : *fp)
+          if (b->pool == pool) mine.push_back(b);
+        // free neighbours were merged when they were freed, so relabelling is all that is needed
+        for (Block* b : mine) {
+          fp->erase(b);
+          b->pool = 0;
+          fp->insert(b);
+        }
       }
     }
+  }
+
+  void set_native(bool v) { native_ = v; }
+  bool native() const { return native_; }
+  // Blocks handed out before the switch keep their layout (each block remembers whether it has guards), so the
+  // mode can change while tensors are alive; only blocks allocated in debug mode are checked.
+  void set_debug(bool v) {
+    std::lock_guard<std::recursive_mutex> g(mu_);
     debug_ = v;
   }
   bool debug() const { return debug_; }
@@ -240,6 +271,7 @@ class CachingAllocator final : public c10::Allocator {
     if (corrupted_on_free_) r.detail = "(freed) " + last_corruption_ + "\n";
     if (!debug_) return r;
     auto check = [&](Block* b) {
+      if (!b->guarded) return;
       r.blocks_checked++;
       std::string why;
       if (!verify_guards(b, &why)) {
@@ -329,6 +361,7 @@ class CachingAllocator final : public c10::Allocator {
     Block* b = new Block();
     b->device = device;
     b->queue_key = q.pack();
+    b->pool = t_private_pool;
     b->size = seg;
     b->ptr = static_cast<char*>(p);
     b->small = small;
@@ -340,6 +373,7 @@ class CachingAllocator final : public c10::Allocator {
 
   void release_to_pool(Block* blk) {
     DeviceState& st = state(blk->device);
+    if (blk->pool != 0 && retired_pools_.count(blk->pool)) blk->pool = 0;  // its graph is gone: back to the shared cache
     Pool& pool = blk->small ? st.small_free : st.large_free;
     // Merge with free neighbours of the same segment.
     auto absorb = [&](Block* nb, bool nb_is_prev) {
@@ -388,7 +422,7 @@ class CachingAllocator final : public c10::Allocator {
     DeviceSwitch sw(device);
     for (auto it = pool.begin(); it != pool.end();) {
       Block* b = *it;
-      if (b->prev == nullptr && b->next == nullptr) {  // a whole segment is free
+      if (b->prev == nullptr && b->next == nullptr && b->pool == 0) {  // a whole segment is free (graph pools keep theirs)
         backend().free(b->ptr);
         st.stats.reserved -= static_cast<int64_t>(b->size);
         st.stats.num_segments--;
@@ -463,6 +497,8 @@ class CachingAllocator final : public c10::Allocator {
   std::recursive_mutex mu_;
   std::array<std::unique_ptr<DeviceState>, kMaxDevices> states_;
   std::unordered_map<void*, Block*> live_;
+  uint64_t next_pool_ = 0;
+  std::unordered_set<uint64_t> retired_pools_;
   bool native_ = false;
   bool debug_ = false;
   int64_t corrupted_on_free_ = 0;
@@ -513,6 +549,13 @@ bool nativeMemoryStrategy() { return alloc().native(); }
 void setMemoryDebug(bool on) { alloc().set_debug(on); }
 bool memoryDebugEnabled() { return alloc().debug(); }
 DebugReport memoryDebugCheck(const void* ptr) { return alloc().debug_check(ptr); }
+uint64_t newPrivatePool() { return alloc().new_pool(); }
+uint64_t setThreadPrivatePool(uint64_t pool) {
+  const uint64_t prev = t_private_pool;
+  t_private_pool = pool;
+  return prev;
+}
+void retirePrivatePool(uint64_t pool) { alloc().retire_pool(pool); }
 void setAllocationContextHook(AllocationContextHook hook) { g_context_hook.store(hook); }
 std::string memoryDebugOrigin(const void* ptr) { return alloc().origin_of(ptr); }
 std::string memorySummary(int device) { return alloc().summary(device); }

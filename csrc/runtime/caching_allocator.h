@@ -70,6 +70,12 @@ DebugReport memoryDebugCheck(const void* ptr = nullptr);  // nullptr = every liv
 // backtraces, torch_mlu/csrc/aten/core/caching_allocator.cpp:633): the native return addresses, symbolised only when a
 // report is written, plus the text this hook returns at allocation time (the binding layer installs one that walks
 // the Python frames of the calling thread).
+// Private pools for captured graphs: while a thread has a pool set, its allocations come from (and its frees of
+// such blocks return to) segments that only this pool uses; retirePrivatePool hands them to the shared cache.
+uint64_t newPrivatePool();
+uint64_t setThreadPrivatePool(uint64_t pool);  // returns the previous value; 0 = shared cache
+void retirePrivatePool(uint64_t pool);
+
 using AllocationContextHook = std::string (*)();
 void setAllocationContextHook(AllocationContextHook hook);
 std::string memoryDebugOrigin(const void* ptr);  // "" when the block has no record

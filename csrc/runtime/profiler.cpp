@@ -19,6 +19,8 @@
 #include "notifier.h"
 #include "profiler.h"
 
+#include "graph.h"
+
 namespace catch_b200 {
 
 // ------------------------------------------------------------------------------ kernel trace
@@ -123,7 +125,7 @@ void trace_range_pop() {
   pe->end = place_now(pe->ev.device);
 }
 KernelTraceScope::KernelTraceScope(const char* launch_expr) {
-  if (!kernel_trace_enabled() || hostsim()) return;
+  if (!kernel_trace_enabled() || hostsim() || graphCaptureActive()) return;  // no timing notifiers inside a capture
   PendingEvent* pe = new_event(launcher_name(launch_expr).c_str(), 0);
   pe->ev.op = t_current_op;
   pe->start = place_now(pe->ev.device);

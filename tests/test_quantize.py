@@ -159,3 +159,62 @@ def test_conv1d_conv3d_modules_and_first_conv():
     assert_tensors_equal(out, net(norm), prec=3e-2, use_MSE=True)
     sd2 = infer.state_dict()                      # an inference module saves the values as loaded
     assert torch.allclose(sd2["conv1.input_mean"].cpu().flatten(), torch.tensor(mean) * 255)
+
+
+class ResBlockNet(torch.nn.Module):
+    """stem (float) -> [conv-relu-conv-relu-conv + skip, relu] -> conv -> pooled linear: every quantized chain shape."""
+
+    def __init__(self):
+        super().__init__()
+        self.stem = torch.nn.Conv2d(3, 16, 3, padding=1)
+        self.a = torch.nn.Conv2d(16, 16, 1)
+        self.b = torch.nn.Conv2d(16, 16, 3, padding=1)
+        self.c = torch.nn.Conv2d(16, 16, 1)
+        self.d = torch.nn.Conv2d(16, 32, 3, stride=2, padding=1)
+        self.fc = torch.nn.Linear(32, 10)
+        self.relu = torch.nn.ReLU(inplace=True)
+
+    def forward(self, x):
+        x = self.relu(self.stem(x))
+        y = self.relu(self.a(x))
+        y = self.relu(self.b(y))
+        y = self.c(y)
+        y += x
+        y = self.relu(y)
+        y = self.d(y)
+        return self.fc(y.mean((2, 3)))
+
+
+def test_quantized_trace_fuses_chains_and_requantizes_between_layers():
+    """Reference flow test/magicmind/test_quantization.py:44-75: calibrate -> state dict -> load -> trace -> compare;
+    the fusion pass folds conv + add + relu and hands int8 from layer to layer."""
+    from catch_b200 import jit
+
+    torch.manual_seed(0)
+    net = ResBlockNet().eval()
+    mixed = {"stem": "float"}
+    calib = quantize_dynamic(net, {"per_channel": True, "iteration": 4}, dtype="int8", gen_quant=True, mixed_layer=mixed)
+    g = torch.Generator().manual_seed(1)
+    for _ in range(4):
+        calib(torch.randn(8, 3, 16, 16, generator=g))
+    infer = quantize_dynamic(net, mixed_layer=mixed)
+    infer.load_state_dict(calib.state_dict(), strict=False)
+    infer = infer.eval().to("blackwell")
+    x = torch.randn(8, 3, 16, 16, generator=g)
+    xd = x.to("blackwell")
+    eager = infer(xd)
+    assert_tensors_equal(eager, net(x), prec=3e-2, use_MSE=True)
+    opt = jit.optimize(torch.jit.trace(infer, xd))
+    text = str(opt.graph)  # prints the groups' subgraphs as well
+    assert "catch_b200::FusionGroup" in text
+    assert text.count("catch_b200::qconv_act(") == 4 and "catch_b200::conv2d" not in text
+    assert "aten::relu" not in text.replace("relu_", "") and "aten::add(" not in text
+    # a -> b and b -> c hand over int8 (non-zero output scale); c feeds the skip connection and d the pooling: float
+    import re
+
+    scales = [float(v) for v in re.findall(r"float = prim::Constant\[value=([0-9.eE+-]+)\]", text)]
+    assert sum(1 for v in scales if v > 0) >= 2
+    out = opt(xd)
+    # same quantization points as the eager quantized model: only rounding-order differences remain
+    assert_tensors_equal(out, eager, prec=1e-2, use_MSE=True)
+    assert_tensors_equal(out, net(x), prec=3e-2, use_MSE=True)

@@ -181,14 +181,8 @@ def test_native_memory_strategy_and_oom():
 
 def test_debug_allocator_detects_overrun():
     import ctypes
-    import gc
 
-    import catch_b200
-
-    # blocks held by other tests' leftovers (module cycles, cached fusion runners with device constants)
-    catch_b200._C._jit_fusion_cache_clear()
-    gc.collect()
-    bw.empty_cache()
+    keep = torch.ones(10, device=DEV)  # allocated outside debug mode: stays valid, is not checked
     bw.set_memory_debug(True)
     try:
         x = torch.zeros(100, device=DEV)
@@ -206,10 +200,44 @@ def test_debug_allocator_detects_overrun():
         assert "test_runtime.py" in origin and "catch_b200" in origin
         ctypes.memset(x.data_ptr() + 512, 0xA5, 8)
         bw.memory_debug()
+        assert bw.memory_debug(keep)[0] == 0 and keep.sum().item() == 10.0
         del x
     finally:
         bw.empty_cache()
         bw.set_memory_debug(False)
+
+
+def test_private_pools_keep_graph_memory_apart():
+    """Blocks allocated while a thread has a private pool set (graph capture) are reused only inside that pool until
+    the pool is retired; then they serve everybody again."""
+    C = catch_b200._C
+    bw.empty_cache()
+    assert not bw.graphs_supported()  # host simulation: nothing to capture
+    f = lambda x: x + 1
+    assert bw.make_graphed_callable(f, (torch.zeros(2, device=DEV),)) is f
+    pool = C._new_private_pool()
+    assert C._set_thread_private_pool(pool) == 0
+    try:
+        a = torch.empty(3 << 20, dtype=torch.uint8, device=DEV)
+        pa = a.data_ptr()
+        del a
+        b = torch.empty(3 << 20, dtype=torch.uint8, device=DEV)  # reuse inside the pool
+        assert b.data_ptr() == pa
+        del b
+    finally:
+        assert C._set_thread_private_pool(0) == pool
+    reserved = bw.memory_reserved()
+    c = torch.empty(3 << 20, dtype=torch.uint8, device=DEV)  # the shared cache may not hand out the pool's block
+    assert c.data_ptr() != pa
+    del c
+    bw.empty_cache()
+    assert bw.memory_reserved() >= 20 << 20 and bw.memory_reserved() <= reserved + (20 << 20)  # pool segment survives
+    C._retire_private_pool(pool)
+    d = torch.empty(3 << 20, dtype=torch.uint8, device=DEV)
+    assert d.data_ptr() == pa  # back in the shared cache
+    del d
+    bw.empty_cache()
+    assert bw.memory_reserved() == 0 or bw.memory_reserved() < 20 << 20
 
 
 def test_pinned_memory():
