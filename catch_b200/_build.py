@@ -36,11 +36,20 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 # breaks iostreams inside a Python extension.
 CXX = os.environ.get("CATCH_B200_CXX", "/usr/bin/g++")
 
+# Build switches (environment), the counterpart of the reference's setup.py flags (setup.py:24-34,190-204):
+#   DEBUG=1                    host code with -O0 -g and assertions, device code with -G left off (-lineinfo stays)
+#   CATCH_B200_BUILD_ASAN=1    AddressSanitizer for the host libraries (host side only, like RUN_BUILD_ASAN_CHECK)
+#   CATCH_B200_BUILD_TEST=0    skip the C++ test program
+#   MAX_JOBS=n                 parallel compile jobs
+DEBUG = os.environ.get("DEBUG", "0") not in ("0", "", "OFF", "off")
+ASAN = os.environ.get("CATCH_B200_BUILD_ASAN", "0") not in ("0", "", "OFF", "off")
+BUILD_TEST = os.environ.get("CATCH_B200_BUILD_TEST", "1") not in ("0", "OFF", "off")
+
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "--expt-extended-lambda", "-Xcompiler", "-fPIC",
-    "-Xcompiler", "-fvisibility=hidden", "-DNDEBUG",
-]
+    "-Xcompiler", "-fvisibility=hidden",
+] + ([] if DEBUG else ["-DNDEBUG"])
 
 
 def _torch_paths():
@@ -81,7 +90,8 @@ def write_ninja(verbose: bool = False) -> Path:
     py_inc = sysconfig.get_paths()["include"]
     cxx_inc = " ".join(f"-isystem {p}" for p in inc + [py_inc] + ([nccl_inc] if nccl_inc else []))
     cxx_flags = (
-        "-O2 -std=c++17 -fPIC -fvisibility=hidden -Wall -Wno-unused-variable -Wno-unused-function "
+        ("-O0 -g " if DEBUG else "-O2 ") + ("-fsanitize=address -fno-omit-frame-pointer " if ASAN else "") +
+        "-std=c++17 -fPIC -fvisibility=hidden -Wall -Wno-unused-variable -Wno-unused-function "
         "-Wno-sign-compare -Wno-unknown-pragmas -D_GLIBCXX_USE_CXX11_ABI=1 -DTORCH_EXTENSION_NAME=_C "
         "-DTORCH_API_INCLUDE_EXTENSION_H"
     )
@@ -125,7 +135,7 @@ def write_ninja(verbose: bool = False) -> Path:
         "-lc10", "-ltorch_cpu", "-ltorch", "-ltorch_python",
         f"-L{PKG / 'lib'}", "-lcatch_b200_device",
         "-Wl,-rpath,$$ORIGIN/lib", "-Wl,--no-as-needed",
-    ]
+    ] + (["-fsanitize=address"] if ASAN else [])
     for p in lib:
         ld.append(f"-Wl,-rpath,{p}")
     lines.append(f"build {HOST_LIB}: link_host {' '.join(map(str, host_objs))} | {DEVICE_LIB}")
@@ -137,10 +147,10 @@ def write_ninja(verbose: bool = False) -> Path:
         obj = BUILD / "host" / "test" / (src.stem + ".o")
         test_objs.append(obj)
         lines.append(f"build {obj}: cxx {src}")
-    if test_objs:
-        rt_objs = [o for o in host_objs if o.parent.name == "runtime"]
+    if test_objs and BUILD_TEST:
+        rt_objs = [o for o in host_objs if o.parent.name in ("runtime", "jit")]
         ld_test = [f"-L{p}" for p in lib] + ["-lc10", "-ltorch_cpu", "-ltorch", f"-L{PKG / 'lib'}", "-lcatch_b200_device",
-                                             "-Wl,-rpath,'$$ORIGIN'", "-Wl,--no-as-needed", "-lpthread"]
+                                             "-Wl,-rpath,'$$ORIGIN'", "-Wl,--no-as-needed", "-lpthread"] + (["-fsanitize=address"] if ASAN else [])
         for p in lib:
             ld_test.append(f"-Wl,-rpath,{p}")
         lines.insert(lines.index("rule link_host"), "rule link_exe")

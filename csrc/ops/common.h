@@ -8,6 +8,7 @@
 // macro instead of five generated class layers.
 #pragma once
 #include <ATen/ATen.h>
+#include <cstdlib>
 #include <ATen/native/CPUFallback.h>
 #include <torch/library.h>
 
@@ -31,7 +32,16 @@ inline bool use_cpu_path() { return hostsim() || flags().test_cpu_dispatch; }
 // under host simulation or CATCH_B200_TEST_CPU_DISPATCH=1 (both decided when the
 // library is loaded) the registrations are skipped, so every compute op reaches
 // the boxed CPU fallback while factories, views and copies stay native.
-inline bool device_kernels_enabled() { return !use_cpu_path(); }
+// CATCH_B200_CHECK_REGISTRATIONS=1 registers them under host simulation as well: loading the library then checks
+// every kernel's C++ signature against its operator schema without a GPU (calling such a kernel fails, so the
+// switch is for registration checks and the operator coverage table only).
+inline bool device_kernels_enabled() {
+  static const bool check_only = [] {
+    const char* e = std::getenv("CATCH_B200_CHECK_REGISTRATIONS");
+    return e && e[0] == '1';
+  }();
+  return !use_cpu_path() || check_only;
+}
 
 // Sets the device of `t` current for the lifetime of the scope, logs the op
 // name, and synchronises on exit when CATCH_B200_ASYNC_DISABLE is set.

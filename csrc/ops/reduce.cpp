@@ -166,6 +166,26 @@ Tensor anyall(const Tensor& self, int op) {
   for (int64_t d = 0; d < self.dim(); ++d) m.set(d);
   return reduce_core(self, m, false, op, at::kBool, nullptr);
 }
+Tensor anyall_dim(const Tensor& self, int64_t dim, bool keepdim, int op) {
+  TORCH_CHECK(self.numel() > 0, "b200 any/all: empty input runs on the CPU path");
+  std::bitset<64> m;
+  if (self.dim() > 0) m.set(at::maybe_wrap_dim(dim, self.dim()));
+  return reduce_core(self, m, keepdim, op, at::kBool, nullptr);
+}
+Tensor k_any_dim(const Tensor& self, int64_t dim, bool keepdim) {
+  return B200_DISPATCH("any.dim", anyall_dim(self, dim, keepdim, RED_ANY), B200_CPU(any_dim, self, dim, keepdim));
+}
+Tensor k_all_dim(const Tensor& self, int64_t dim, bool keepdim) {
+  return B200_DISPATCH("all.dim", anyall_dim(self, dim, keepdim, RED_ALL), B200_CPU(all_dim, self, dim, keepdim));
+}
+Tensor k_prod_all(const Tensor& self, std::optional<at::ScalarType> dtype) {
+  return B200_DISPATCH("prod", sum_like(self, std::nullopt, false, dtype, RED_PROD), B200_CPU(prod, self, dtype));
+}
+Tensor k_norm_dim_dtype(const Tensor& self, const std::optional<at::Scalar>& p, at::IntArrayRef dim, bool keepdim,
+                        at::ScalarType dtype) {
+  return B200_DISPATCH("norm", norm_impl(self, p, dim, keepdim, dtype),
+                       B200_CPU(norm_ScalarOpt_dim_dtype, self, p, dim, keepdim, dtype));
+}
 Tensor k_any(const Tensor& self) { return B200_DISPATCH("any", anyall(self, RED_ANY), B200_CPU(any, self)); }
 Tensor k_all(const Tensor& self) { return B200_DISPATCH("all", anyall(self, RED_ALL), B200_CPU(all, self)); }
 
@@ -188,6 +208,10 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("linalg_vector_norm", TORCH_FN(k_linalg_vector_norm));
   m.impl("any", TORCH_FN(k_any));
   m.impl("all", TORCH_FN(k_all));
+  m.impl("any.dim", TORCH_FN(k_any_dim));
+  m.impl("all.dim", TORCH_FN(k_all_dim));
+  m.impl("prod", TORCH_FN(k_prod_all));
+  m.impl("norm.ScalarOpt_dim_dtype", TORCH_FN(k_norm_dim_dtype));
 }
 
 }  // namespace ops

@@ -27,7 +27,7 @@
 
 using namespace catch_b200;
 
-static int g_failures = 0, g_checks = 0;
+int g_failures = 0, g_checks = 0;  // shared with jit_test.cpp
 #define CHECK_T(cond)                                                              \
   do {                                                                             \
     ++g_checks;                                                                    \
@@ -250,13 +250,21 @@ static void test_tensors() {
   CHECK_T(!is_b200(cpu) && !is_b200(at::Tensor()));
 }
 
+void test_jit_lowering();
+void test_jit_partitioner();
+void test_jit_alias_safety();
+void test_jit_runner_cache();
+void test_check_util();
+
 int main() {
   struct Case { const char* name; void (*fn)(); };
   const Case cases[] = {{"device", test_device},           {"queues", test_queues},
                         {"notifiers", test_notifiers},     {"caching_allocator", test_caching_allocator},
                         {"debug_allocator", test_debug_allocator}, {"native_strategy", test_native_strategy},
                         {"pinned_allocator", test_pinned_allocator}, {"guard", test_guard},
-                        {"tensors", test_tensors}};
+                        {"tensors", test_tensors},         {"check_util", test_check_util},
+                        {"jit_lowering", test_jit_lowering}, {"jit_partitioner", test_jit_partitioner},
+                        {"jit_alias_safety", test_jit_alias_safety}, {"jit_runner_cache", test_jit_runner_cache}};
   for (const Case& c : cases) {
     const int before = g_failures;
     try {

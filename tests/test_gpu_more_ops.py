@@ -270,3 +270,65 @@ def test_fp32_convolution_keeps_fp32_range_and_precision():
     yr = F.conv_transpose2d(xt, wt, None, 3, 1, 1, 1, 2)
     yd = F.conv_transpose2d(dev(xt), dev(wt), None, 3, 1, 1, 1, 2)
     assert_tensors_equal(yd, yr, prec=2e-4, use_MSE=True)
+
+
+def test_out_variants_and_dim_reductions():
+    """out= overloads of the reference's list (gather.out, index_select.out, topk.values, max.dim_max,
+    sum.IntList_out, mean.out, ...) and the reductions along one dimension that used to fall back (all / any / prod /
+    norm with a dtype): device result against the CPU result, with out tensors that have to be resized."""
+    torch.manual_seed(0)
+    x = torch.randn(6, 10, 5)
+    xd = dev(x)
+    idx = torch.randint(0, 10, (6, 4, 5))
+    cases = [
+        ("gather", lambda t, o: torch.gather(t, 1, idx.to(t.device), out=o)),
+        ("index_select", lambda t, o: torch.index_select(t, 1, torch.tensor([7, 0, 3]).to(t.device), out=o)),
+        ("sum", lambda t, o: torch.sum(t, (0, 2), out=o)),
+        ("mean", lambda t, o: torch.mean(t, 1, keepdim=True, out=o)),
+        ("prod", lambda t, o: torch.prod(t, 2, out=o)),
+        ("clamp_min", lambda t, o: torch.clamp_min(t, 0.25, out=o)),
+        ("leaky_relu", lambda t, o: F.leaky_relu(t, 0.1) if o is None else torch._C._nn.leaky_relu(t, 0.1, out=o)),
+        ("threshold", lambda t, o: torch.threshold(t, 0.1, -1.0) if o is None else torch.threshold(t, 0.1, -1.0, out=o)),
+        ("masked_select", lambda t, o: torch.masked_select(t, t > 0.3, out=o)),
+        ("nonzero", lambda t, o: torch.nonzero(t > 1.0, out=o)),
+    ]
+    for name, fn in cases:
+        ref = fn(x, None)
+        out = torch.empty(0, dtype=ref.dtype, device=DEV)
+        got = fn(xd, out)
+        assert got.data_ptr() == out.data_ptr(), name
+        assert_tensors_equal(out.cpu().float(), ref.float(), prec=1e-5), name
+    # two-result overloads
+    v, i = torch.empty(0, device=DEV), torch.empty(0, dtype=torch.long, device=DEV)
+    torch.max(xd, 1, out=(v, i))
+    rv, ri = torch.max(x, 1)
+    assert torch.equal(v.cpu(), rv) and torch.equal(i.cpu(), ri)
+    torch.topk(xd, 3, dim=1, out=(v, i))
+    rv, ri = torch.topk(x, 3, dim=1)
+    assert torch.equal(v.cpu(), rv) and torch.equal(i.cpu(), ri)
+    # reductions along one dimension
+    b = x > 0.5
+    assert torch.equal(dev(b).all(1).cpu(), b.all(1)) and torch.equal(dev(b).any(2, keepdim=True).cpu(), b.any(2, keepdim=True))
+    o = torch.empty(0, dtype=torch.bool, device=DEV)
+    torch.all(dev(b), 0, out=o)
+    assert torch.equal(o.cpu(), b.all(0))
+    assert_tensors_equal(xd[:, :3].prod().cpu(), x[:, :3].prod(), prec=1e-4, use_MSE=True)
+    assert_tensors_equal(torch.norm(xd.half(), 2, [1], dtype=torch.float32).cpu(), torch.norm(x.half(), 2, [1], dtype=torch.float32),
+                         prec=1e-3, use_MSE=True)
+    y = xd.abs().clone()
+    y.pow_(2.0)
+    assert_tensors_equal(y.cpu(), x.abs().pow(2.0), prec=1e-5)
+    # pooling / resampling / loss out= forms
+    img = torch.randn(2, 8, 12, 12)
+    o = torch.empty(0, device=DEV)
+    torch._C._nn.adaptive_avg_pool2d(dev(img), (3, 3), out=o)
+    assert_tensors_equal(o.cpu(), F.adaptive_avg_pool2d(img, (3, 3)), prec=1e-5)
+    torch._C._nn.upsample_nearest2d(dev(img), (24, 24), out=o)
+    assert_tensors_equal(o.cpu(), F.interpolate(img, size=(24, 24), mode="nearest"), prec=1e-6)
+    torch._C._nn.upsample_bilinear2d(dev(img), (18, 18), False, out=o)
+    assert_tensors_equal(o.cpu(), F.interpolate(img, size=(18, 18), mode="bilinear", align_corners=False), prec=1e-5)
+    p, t = torch.rand(4, 7), torch.rand(4, 7)
+    torch._C._nn.binary_cross_entropy(dev(p), dev(t), out=o)
+    assert_tensors_equal(o.cpu(), F.binary_cross_entropy(p, t), prec=1e-5)
+    torch._C._nn.smooth_l1_loss(dev(p), dev(t), 1, 0.5, out=o)
+    assert_tensors_equal(o.cpu(), F.smooth_l1_loss(p, t, beta=0.5), prec=1e-5)
