@@ -868,11 +868,20 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p_in, void* stream) {
   return (int)cudaGetLastError();
 }
 
+namespace b200 {
+bool try_wgrad_halo(const B200ConvWgradParams* p, void* stream, int* rc);  // conv_wgrad_halo.cu
+}
+
 extern "C" int b200_conv_wgrad(const B200ConvWgradParams* p, void* stream) {
   using namespace b200;
   if (p->N <= 0 || p->P <= 0 || p->Q <= 0 || p->Cout <= 0 || p->Cin <= 0) return 0;
   if (p->ntaps <= 0 || p->ntaps > B200_CONV_MAX_TAPS || p->num_views <= 0 || p->num_views > B200_CONV_MAX_MAPS)
     return (int)cudaErrorInvalidValue;
+  {
+    // stride-1 multi-tap filters: shared activation windows (about half the L2 -> SM traffic)
+    int rc = 0;
+    if (try_wgrad_halo(p, stream, &rc)) return rc;
+  }
   if (p->Cin % 8 || p->Cout % 8 || p->ab_dtype == B200_F32) return (int)cudaErrorInvalidValue;
   const CUtensorMapDataType dt = p->ab_dtype == B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   int dev = 0, sms = 148;

@@ -187,6 +187,9 @@ typedef struct B200ConvWgradParams {
   int splits;            // 0 = automatic
 } B200ConvWgradParams;
 B200_API int b200_conv_wgrad(const B200ConvWgradParams* p, void* stream);
+// Stride-1 multi-tap weight gradients use the shared-window kernel (conv_wgrad_halo.cu): 0 = never, 1 = yes (default),
+// 2 = yes with one N = 64 MMA per window.  A negative argument only reads the setting; returns the previous one.
+B200_API int b200_conv_wgrad_halo_mode(int mode);
 
 // ---- layout helpers -----------------------------------------------------------------------
 // Pack an [N,C<=8,H,W] tensor with arbitrary element strides into a zero-bordered

@@ -4,6 +4,7 @@
 
 #include <torch/csrc/jit/python/pybind_utils.h>
 
+#include "../device/kernels_api.h"
 #include "../jit/fusion.h"
 #include "../runtime/dumper.h"
 #include "../runtime/profiler.h"
@@ -15,6 +16,8 @@ void bind_aux(py::module& m) {
   m.def("_dump_start", &dump_start, py::arg("dir"), py::arg("enable") = true, py::arg("use_cpu") = false, py::arg("level") = 0);
   m.def("_dump_finish", &dump_finish);
   m.def("_dump_running", &dump_running);
+  // kernel selection knob for benchmarks and tests: see b200_conv_wgrad_halo_mode
+  m.def("_conv_wgrad_halo_mode", [](int mode) { return b200_conv_wgrad_halo_mode(mode); }, py::arg("mode") = -1);
   m.def("_jit_can_fuse_on_b200", &jit::fusion_enabled);
   m.def("_jit_override_can_fuse_on_b200", &jit::set_fusion_enabled);
   m.def("_jit_register_passes", &jit::register_passes);

@@ -33,6 +33,12 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords and not has_gpu:
             item.add_marker(skip_gpu)
+    # The allocator tests count segments of the process-wide caching allocator: they run before tests that leave
+    # device tensors behind for the life of the process (TorchScript keeps the constants of frozen modules in its
+    # global compilation unit).
+    first = [i for i in items if i.fspath.basename == "test_runtime.py"]
+    rest = [i for i in items if i.fspath.basename != "test_runtime.py"]
+    items[:] = first + rest
 
 
 @pytest.fixture(scope="session")

@@ -122,3 +122,47 @@ def test_conv_backward_with_fp32_weight_gradient():
     assert_tensors_equal(dw, wr.grad, prec=3e-3, use_MSE=True, msg="dw")  # fp32 accumulation, no 16-bit rounding
     dx2, dw2 = torch.ops.catch_b200.conv2d_backward_fp32w(gd, xd, wd, [1, 1], [1, 1], False, True)
     assert_tensors_equal(dw2, wr.grad, prec=3e-3, use_MSE=True, msg="dw only")
+
+
+HALO_WGRAD_CASES = [
+    # N, C, H, W, K: stride-1 3x3 layers whose weight gradient takes the shared-window kernel
+    (8, 64, 56, 56, 64),     # one channel block, half-empty M tile
+    (6, 128, 28, 28, 128),   # two channel blocks per item (N = 384), W = 28 -> a partly empty column tile
+    (5, 256, 14, 14, 256),   # two M tiles, two channel groups, odd batch
+    (3, 512, 7, 7, 512),     # 7 rows per image: K steps straddle images, batch not a multiple of the chunk
+    (4, 192, 20, 12, 72),    # three channel blocks (last group has one), Cout not a multiple of 64
+]
+
+
+@pytest.mark.parametrize("mode", [1, 2, 0])
+@pytest.mark.parametrize("case", HALO_WGRAD_CASES)
+def test_wgrad_shared_window_kernel(case, mode):
+    """conv_wgrad_halo_kernel (mode 1: one N = 192 MMA over three overlapping windows; mode 2: one MMA per window)
+    and the plain kernel (mode 0) against the fp32 CPU gradient, added into an fp32 buffer that already holds
+    values (the bucket accumulation path) and returned as a tensor."""
+    import catch_b200
+
+    N, C, H, W, K = case
+    torch.manual_seed(2)
+    x = torch.randn(N, C, H, W).bfloat16()
+    w = (torch.randn(K, C, 3, 3) / (C * 9) ** 0.5).bfloat16()
+    gy = torch.randn(N, K, H, W).bfloat16()
+    wr = w.float().requires_grad_()
+    F.conv2d(x.float(), wr, None, 1, 1).backward(gy.float())
+    cl = torch.channels_last
+    xd, wd, gd = (t.to(DEV).contiguous(memory_format=cl) for t in (x, w, gy))
+    prev = catch_b200._C._conv_wgrad_halo_mode(mode)
+    try:
+        _, dw = torch.ops.catch_b200.conv2d_backward_fp32w(gd, xd, wd, [1, 1], [1, 1], False, True, None)
+        acc = torch.full((K * 9 * C,), 0.5, device=DEV)
+        torch.ops.catch_b200.conv2d_backward_fp32w(gd, xd, wd, [1, 1], [1, 1], False, True, acc)
+    finally:
+        catch_b200._C._conv_wgrad_halo_mode(prev)
+    assert dw.dtype == torch.float32
+    assert_tensors_equal(dw.cpu(), wr.grad, prec=1e-2, use_MSE=True, msg=f"mode {mode}")
+    got = acc.cpu().view(K, 3, 3, C).permute(0, 3, 1, 2) - 0.5
+    assert_tensors_equal(got, wr.grad, prec=1e-2, use_MSE=True, msg=f"mode {mode} accumulate")
+    from catch_b200.ops import capi
+
+    torch.b200.synchronize()
+    assert capi.read_error_flag() == 0

@@ -328,7 +328,7 @@ def test_out_variants_and_dim_reductions():
     torch._C._nn.upsample_bilinear2d(dev(img), (18, 18), False, out=o)
     assert_tensors_equal(o.cpu(), F.interpolate(img, size=(18, 18), mode="bilinear", align_corners=False), prec=1e-5)
     p, t = torch.rand(4, 7), torch.rand(4, 7)
-    torch._C._nn.binary_cross_entropy(dev(p), dev(t), out=o)
+    torch._C._nn.binary_cross_entropy(dev(p), dev(t), None, 1, out=o)
     assert_tensors_equal(o.cpu(), F.binary_cross_entropy(p, t), prec=1e-5)
     torch._C._nn.smooth_l1_loss(dev(p), dev(t), 1, 0.5, out=o)
     assert_tensors_equal(o.cpu(), F.smooth_l1_loss(p, t, beta=0.5), prec=1e-5)
