@@ -69,6 +69,7 @@ struct ConvArgs {
   int b_res_bytes;              // > 0: weights of one output-channel tile stay resident in shared memory
   int coef_bytes;               // shared memory reserved for per-channel scale / bias (0 or 2048)
   int tma_store;                // epilogue stages 64-channel blocks in shared memory and stores them by TMA
+  int epi_bufs;                 // staging buffers per epilogue warp (2 when shared memory allows: conversion overlaps the store)
   int* err;
 };
 
@@ -178,7 +179,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
   bool failed = false;
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (elect_one()) {  // one elected lane of the converged warp: the compiler keeps the issue path uniform
       int stage = 0; uint32_t phase = 0;
       int cur_ct = -1;
       for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
@@ -239,7 +240,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (elect_one()) {  // one elected lane of the converged warp: the compiler keeps the issue path uniform
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
       int cur_ct = -1; uint32_t b_phase = 0;
       // descriptor templates and addresses in 16-byte units: per K block the issue loop only adds
@@ -300,7 +301,9 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
     // x 64 channels (4 KB, 128-byte swizzle) and issues its own tensor-map store.
     const int quarter = warp & 3;
     const int colhalf = (warp - 2) >> 2;
-    uint8_t* sbuf = stage_out + (warp - 2) * 4096;
+    // two 4 KB staging buffers per warp: the next block is converted while the copy engine still reads the last one
+    uint8_t* sbuf0 = stage_out + (warp - 2) * 4096 * g.epi_bufs;
+    int sbuf_sel = 0;
     int acc = 0; uint32_t acc_phase = 0;
     const int esz = g.out_dtype == B200_F32 ? 4 : g.out_dtype == B200_I8 ? 1 : 2;
     const int rsz = g.res_dtype == B200_F32 ? 4 : 2;
@@ -394,8 +397,13 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
           tmem_ld32(t_addr + cb, ra);
           tmem_ld32(t_addr + cb + 32, rb);
           tmem_ld_wait();
-          if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has read the buffer
+          if (lane == 0) {  // the store that last used this buffer has read it
+            if (g.epi_bufs == 2) tma_store_wait_read<1>();
+            else tma_store_wait_read<0>();
+          }
           __syncwarp();
+          uint8_t* sbuf = sbuf0 + sbuf_sel * 4096;
+          if (g.epi_bufs == 2) sbuf_sel ^= 1;
           uint8_t* srow = sbuf + lane * 128;
           // the two 32-column halves run through one copy of the code (the second half is moved into the
           // first half's registers): the loop is deliberately not unrolled to keep the kernel's hot code small
@@ -593,7 +601,7 @@ conv_wgrad_kernel(const __grid_constant__ WgradMaps maps, const __grid_constant_
   bool failed = false;
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (elect_one()) {  // one elected lane of the converged warp: the compiler keeps the issue path uniform
       int stage = 0; uint32_t phase = 0;
       for (int ch = chunk_begin; ch < chunk_end; ++ch) {
         const int q0 = (ch % g.tiles_q) * g.bw;
@@ -614,7 +622,7 @@ conv_wgrad_kernel(const __grid_constant__ WgradMaps maps, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (elect_one()) {  // one elected lane of the converged warp: the compiler keeps the issue path uniform
       int stage = 0; uint32_t phase = 0;
       uint32_t d_lo0, d_hi;
       split_desc(make_smem_desc_sw128(0, blk_bytes, 1024), &d_lo0, &d_hi);
@@ -786,7 +794,9 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p_in, void* stream) {
   if (p->out_dtype == B200_I8 && !(p->out_qscale > 0.f)) return (int)cudaErrorInvalidValue;
   g.tma_store = (p->out_dtype != B200_F32 && p->out_dtype != B200_I8 && g.tile_n % 64 == 0 && p->Cout % 8 == 0) ? 1 : 0;
   g.coef_bytes = (p->scale || p->bias) ? 2048 : 0;
-  const int smem_cap = 227 * 1024 - 2048 - g.coef_bytes - (g.tma_store ? 32768 : 0);
+  // one 4 KB staging buffer per epilogue warp; a second one is added below when the pipeline keeps enough stages
+  g.epi_bufs = 1;
+  int smem_cap = 227 * 1024 - 2048 - g.coef_bytes - (g.tma_store ? 32768 : 0);
   // Weights of one output-channel tile (every tap and channel block) stay in shared memory when
   // they are small and each CTA reuses them over several pixel tiles; the stages then hold only
   // activations, which puts more of them in flight.
@@ -815,6 +825,10 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p_in, void* stream) {
     }
   }
   const int stage_bytes = g.halo ? g.halo_stage_bytes : CONV_A_BYTES + (g.b_res_bytes ? 0 : g.tile_n * 128);
+  if (g.tma_store && (smem_cap - 32768 - g.b_res_bytes) / stage_bytes >= (g.halo ? 2 : 4)) {
+    g.epi_bufs = 2;
+    smem_cap -= 32768;
+  }
   g.stages = (smem_cap - g.b_res_bytes) / stage_bytes;
   if (g.stages > CONV_MAX_STAGES) g.stages = CONV_MAX_STAGES;
   if (g.stages < 2) g.stages = 2;
@@ -861,7 +875,7 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p_in, void* stream) {
   int rc = set_smem_attr_once((const void*)conv_fprop_kernel, dev, attr_done);
   if (rc) return rc;
   const size_t smem = 1024 /*align*/ + (size_t)g.b_res_bytes + (size_t)g.stages * stage_bytes + 1024 /*barriers*/ +
-                      g.coef_bytes + (g.tma_store ? 32768 : 0);
+                      g.coef_bytes + (g.tma_store ? 32768 * g.epi_bufs : 0);
   const long total_tiles = pix_tiles * g.tiles_co;
   const int ctas = (int)(total_tiles < sms ? total_tiles : sms);
   conv_fprop_kernel<<<ctas, CONV_FPROP_THREADS, smem, (cudaStream_t)stream>>>(maps, g);

@@ -55,6 +55,7 @@ struct GemmKernelArgs {
   int act;
   int coef_bytes;       // shared memory reserved for column scale / bias (0 or 2048)
   int tma_store;        // epilogue stages 64-column blocks in shared memory and stores them by TMA
+  int epi_bufs;         // staging buffers per epilogue warp (1 or 2)
   int reduce_add;       // fp32 D += result: 32 x 32 blocks are added to global memory with tensor-map reductions
   int splits;           // the K loop is divided among `splits` work items per output tile (reduce_add only)
   int kb_per_split;
@@ -145,7 +146,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   // per-tile column coefficients (scale, bias); present only when the launch has any
   float* coef = reinterpret_cast<float*>(tiles + (size_t)g.stages * stage_bytes + 1024);
-  uint8_t* stage_out = tiles + (size_t)g.stages * stage_bytes + 1024 + g.coef_bytes;  // 2 x 16 KB, 128-byte swizzled
+  uint8_t* stage_out = tiles + (size_t)g.stages * stage_bytes + 1024 + g.coef_bytes;  // 8 warps x 2 buffers x 4 KB, 128-byte swizzled
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -178,7 +179,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (elect_one()) {  // one elected lane of the converged warp: the compiler keeps the issue path uniform
       int stage = 0;
       uint32_t phase = 0;
       const uint32_t tx_bytes = (uint32_t)stage_bytes;
@@ -216,7 +217,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    if (elect_one()) {  // one elected lane of the converged warp: the compiler keeps the issue path uniform
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -255,6 +256,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int quarter = warp & 3;  // tcgen05.ld: warp w may touch lanes [32*(w%4), +32)
     const int colhalf = (warp - 2) >> 2;  // the two warps of a quarter take alternate 32-column chunks
     int acc = 0;
+    int sbuf_sel = 0;
     uint32_t acc_phase = 0;
     uint32_t tile_iter = 0;
     const bool has_coef = g.col_scale != nullptr || (g.bias != nullptr && !g.bias_per_row);
@@ -291,7 +293,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         // fp32 accumulation into global memory: each warp stages 32 rows x 32 fp32 columns (4 KB, 128-byte swizzle) and
         // adds them with one tensor-map reduction; rows / columns outside the matrix are clipped.  K splits of one tile and
         // whatever the destination already holds simply add up.
-        uint8_t* sbuf = stage_out + (warp - 2) * 4096;
+        uint8_t* sbuf0 = stage_out + (warp - 2) * 4096 * g.epi_bufs;
         const uint32_t t_addr = tmem_base + acc * GEMM_ACC_STRIDE + ((uint32_t)(quarter * 32) << 16);
         for (int c = colhalf * 32; c < g.tile_n; c += 64) {
           uint32_t r[32];
@@ -302,8 +304,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
             for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * g.alpha);
           }
-          if (lane == 0) tma_store_wait_read<0>();
+          if (lane == 0) {
+            if (g.epi_bufs == 2) tma_store_wait_read<1>();
+            else tma_store_wait_read<0>();
+          }
           __syncwarp();
+          uint8_t* sbuf = sbuf0 + sbuf_sel * 4096;
+          if (g.epi_bufs == 2) sbuf_sel ^= 1;
           uint8_t* srow = sbuf + lane * 128;
 #pragma unroll
           for (int k = 0; k < 8; ++k)
@@ -325,7 +332,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         // Each epilogue warp stages its own 32 rows x 64 columns (4 KB, 128-byte swizzle) and issues its own
         // tensor-map store; the two warps of a lane quarter take alternate 64-column blocks.  No barrier
         // across warps is needed.
-        uint8_t* sbuf = stage_out + (warp - 2) * 4096;
+        uint8_t* sbuf0 = stage_out + (warp - 2) * 4096 * g.epi_bufs;  // two buffers per warp when they fit: convert while the last store is read
         auto finish = [&](const uint32_t (&r)[32], int c, float (&v)[32]) {
           const int n_base = n0 + c;
 #pragma unroll
@@ -352,8 +359,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tmem_ld32(t_addr + cb, ra);
           tmem_ld32(t_addr + cb + 32, rb);
           tmem_ld_wait();
-          if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has read the buffer
+          if (lane == 0) {  // the store that last used this buffer has read it
+            if (g.epi_bufs == 2) tma_store_wait_read<1>();
+            else tma_store_wait_read<0>();
+          }
           __syncwarp();
+          uint8_t* sbuf = sbuf0 + sbuf_sel * 4096;
+          if (g.epi_bufs == 2) sbuf_sel ^= 1;
           uint8_t* srow = sbuf + lane * 128;
           // one copy of the code for both 32-column halves (the second half is moved into the first half's
           // registers); not unrolled, to keep the hot code small
@@ -560,13 +572,19 @@ extern "C" int b200_gemm(const B200GemmParams* p, void* stream) {
     g.splits = (g.k_blocks + g.kb_per_split - 1) / g.kb_per_split;
   }
   g.coef_bytes = (p->col_scale || (p->bias && !p->bias_per_row)) ? 2048 : 0;
-  const int smem_budget = 227 * 1024 - 2048 - g.coef_bytes - ((g.tma_store || g.reduce_add) ? 32768 : 0);
+  const bool staged = g.tma_store || g.reduce_add;
+  int smem_budget = 227 * 1024 - 2048 - g.coef_bytes - (staged ? 32768 : 0);
+  g.epi_bufs = 1;
+  if (staged && (smem_budget - 32768) / stage_bytes >= 4) {  // a second staging buffer per warp when four stages still fit
+    g.epi_bufs = 2;
+    smem_budget -= 32768;
+  }
   g.stages = smem_budget / stage_bytes;
   if (g.stages > GEMM_MAX_STAGES) g.stages = GEMM_MAX_STAGES;
   if (g.stages > g.kb_per_split + 1) g.stages = g.kb_per_split + 1 < 2 ? 2 : g.kb_per_split + 1;
   if (g.stages < 2) g.stages = 2;
   const size_t smem = (size_t)g.stages * stage_bytes + 1024 /*align*/ + 1024 /*barriers*/ + g.coef_bytes +
-                      ((g.tma_store || g.reduce_add) ? 32768 : 0);
+                      (staged ? 32768 * g.epi_bufs : 0);
 
   CUtensorMap tmA, tmB;
   // batch strides: a single-level batch of one matrix still needs a non-zero, 16-byte-multiple stride in the map
