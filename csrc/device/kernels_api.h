@@ -334,6 +334,7 @@ typedef struct B200ReduceParams {
   float* workspace;                 // n_out * splits * 2 floats when splits > 1
   int splits;                       // filled by b200_reduce_plan
   int outer;                        // filled by b200_reduce_plan: sum / mean over the leading rows of a dense [rows, cols] view
+  int per_thread;                   // filled by b200_reduce_plan: short reductions with many outputs, one thread per output
 } B200ReduceParams;
 B200_API int b200_reduce_plan(B200ReduceParams* p);   // chooses splits; returns workspace floats needed
 B200_API int b200_reduce(const B200ReduceParams* p, void* stream);

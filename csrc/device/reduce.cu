@@ -159,6 +159,48 @@ __global__ void __launch_bounds__(256) reduce_kernel(const B200ReduceParams p) {
   }
 }
 
+// Short reductions with many outputs (global average pooling over a channels-last tensor: 49 elements per
+// output, half a million outputs): one thread per output, adjacent threads take adjacent outputs, so when the
+// innermost kept dimension is dense in memory every load of a warp is one coalesced line.
+__global__ void __launch_bounds__(256) reduce_per_thread_kernel(const B200ReduceParams p) {
+  const long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= p.n_out) return;
+  long long rem = o, base = 0;
+  for (int d = p.n_kept - 1; d >= 0; --d) {
+    base += (rem % p.kept_size[d]) * p.kept_in_stride[d];
+    rem /= p.kept_size[d];
+  }
+  Acc a = identity(p.op);
+  const bool mm = is_minmax(p.op);
+  if (p.n_reduced == 1) {
+    const long long st = p.red_in_stride[0];
+    for (long long j = 0; j < p.n_red; ++j) {
+      Acc b;
+      b.v = pre(p.op, ldf(p.in, base + j * st, p.in_dtype));
+      b.idx = mm ? j : -1;
+      a = combine(p.op, a, b);
+    }
+  } else {
+    for (long long j = 0; j < p.n_red; ++j) {
+      long long r = j, off = base;
+      for (int d = p.n_reduced - 1; d >= 0; --d) {
+        off += (r % p.red_size[d]) * p.red_in_stride[d];
+        r /= p.red_size[d];
+      }
+      Acc b;
+      b.v = pre(p.op, ldf(p.in, off, p.in_dtype));
+      b.idx = mm ? j : -1;
+      a = combine(p.op, a, b);
+    }
+  }
+  if (p.op == RED_ARGMAX || p.op == RED_ARGMIN) {
+    static_cast<long long*>(p.out)[o] = a.idx;
+  } else {
+    st_out(p.out, o, p.out_dtype, finish(p.op, a.v, p.n_red));
+    if (p.out_index) p.out_index[o] = a.idx;
+  }
+}
+
 __global__ void reduce_final_kernel(const B200ReduceParams p) {
   const long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (o >= p.n_out) return;
@@ -237,6 +279,17 @@ static bool is_outer_reduction(const B200ReduceParams* p) {
 extern "C" int b200_reduce_plan(B200ReduceParams* p) {
   p->splits = 1;
   p->outer = 0;
+  p->per_thread = 0;
+  if (p->n_red <= 512 && p->n_out >= 148 * 256 && p->n_kept >= 1 && p->n_reduced >= 1) {
+    // one thread per output pays off when adjacent outputs are adjacent in memory (else the block-per-output
+    // kernel reads lines at least as well)
+    int inner = p->n_kept - 1;
+    while (inner > 0 && p->kept_size[inner] == 1) --inner;
+    if (p->kept_in_stride[inner] == 1 && p->kept_size[inner] >= 32) {
+      p->per_thread = 1;
+      return 0;
+    }
+  }
   if (is_outer_reduction(p)) {
     p->outer = 1;
     const long long col_blocks = (p->n_out + 31) / 32;
@@ -263,6 +316,10 @@ extern "C" int b200_reduce(const B200ReduceParams* p, void* stream) {
   if (p->n_kept > B200_RED_MAX_DIMS || p->n_reduced > B200_RED_MAX_DIMS) return (int)cudaErrorInvalidValue;
   if (p->n_out > 2147483647LL) return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
+  if (p->per_thread) {
+    reduce_per_thread_kernel<<<(unsigned)((p->n_out + 255) / 256), 256, 0, s>>>(*p);
+    return (int)cudaGetLastError();
+  }
   if (p->outer) {
     dim3 ogrid((unsigned)((p->n_out + 31) / 32), (unsigned)p->splits);
     reduce_outer_kernel<<<ogrid, 256, 0, s>>>(*p);
