@@ -38,7 +38,7 @@ import time
 # Stock PyTorch (CUDA + cuDNN + NCCL DDP) on this pool's B200s, images/sec at 1 / 2 / 4 / 8 GPUs, measured
 # with ``bench.py --impl stock``.  The reference publishes no throughput number, so
 # ``vs_baseline`` is taken against these; a stock run made in the same invocation is reported next to it.
-STOCK_IMAGES_PER_SEC = {1: 4815.8}
+STOCK_IMAGES_PER_SEC = {1: 4826.0, 2: 9358.5, 4: 18660.2, 8: 37211.9}
 
 
 def parse_args():
@@ -182,13 +182,30 @@ def run_stock(args, rank, local_rank, world, store, sampler):
         q = [fetch() for _ in range(min(2, n))]
         issued = len(q)
         last = None
-        for _ in range(n):
+        # every step's loss is read back, one step late, through pinned memory on a side stream (the host stays one
+        # step ahead of the device); the last one is read before the timed region ends
+        side = torch.cuda.Stream(dev)
+        slots = [torch.zeros((), dtype=torch.float32).pin_memory() for _ in range(2)]
+        pending = None
+        for i in range(n):
             x, y, ev = q.pop(0)
             if issued < n:
                 q.append(fetch()); issued += 1
-            torch.cuda.current_stream(dev).wait_event(ev)
-            x.record_stream(torch.cuda.current_stream(dev)); y.record_stream(torch.cuda.current_stream(dev))
-            last = step(x, y).item()
+            cur = torch.cuda.current_stream(dev)
+            cur.wait_event(ev)
+            x.record_stream(cur); y.record_stream(cur)
+            loss = step(x, y)
+            ready = torch.cuda.Event(); ready.record(cur)
+            with torch.cuda.stream(side):
+                side.wait_event(ready)
+                loss.record_stream(side)
+                slots[i % 2].copy_(loss.detach().float(), non_blocking=True)
+                done = torch.cuda.Event(); done.record(side)
+            if pending is not None:
+                pending[0].synchronize(); last = float(pending[1])
+            pending = (done, slots[i % 2])
+        if pending is not None:
+            pending[0].synchronize(); last = float(pending[1])
         return last
 
     def barrier():
@@ -247,7 +264,7 @@ def run_ours(args, rank, local_rank, world, store, sampler):
     import catch_b200  # noqa: F401
     from catch_b200.fusion import fuse_bn_act
     from catch_b200.parallel import FusedDataParallel
-    from catch_b200.utils import PrefetchLoader
+    from catch_b200.utils import DelayedScalar, PrefetchLoader
 
     assert torch.b200.backend_name() == "cuda", "bench.py needs a GPU (the host-simulated device is for tests)"
     torch.b200.set_device(local_rank)
@@ -284,13 +301,18 @@ def run_ours(args, rank, local_rank, world, store, sampler):
 
     def e2e_steps(n):
         # Every step's batch is copied from pinned host memory inside the timed region; two batches are in
-        # flight on an IO queue while the host blocks on the previous step's loss.
+        # flight on an IO queue.
         last = None
         loader = PrefetchLoader(((host_x, host_y) for _ in range(n)), dev, use_io_queue=True, pin=False, depth=2,
                                 transform=to_compute_layout)
+        # every step's loss is read back, one step late, through pinned memory on a side queue (the host stays one
+        # step ahead of the device); the last one is read before the timed region ends
+        reader = DelayedScalar()
         for x, y in loader:
-            last = step(x, y).item()  # device -> host read of the result
-        return last
+            v = reader.push(step(x, y))  # device -> host read of the result
+            last = v if v is not None else last
+        v = reader.flush()
+        return v if v is not None else last
 
     def barrier():
         if world > 1:

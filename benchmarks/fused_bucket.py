@@ -8,7 +8,8 @@ fp32 parameters plus their bf16 copy out; with the multicast mapping the switch 
 rank receives 1/N of the gradients and sends 1/N of the parameters (the other direction carries the whole
 bucket once).  bound = bytes of the busier direction / 770 GB/s (the measured peer-copy rate per direction);
 the optimizer arithmetic is far below that (a few FLOP per byte), so the link is the roofline.
-Device-timed, max over ranks; CATCH_B200_NVLS=0 forces the peer-memory path.
+Device-timed, max over ranks.  The kernel uses peer loads / stores unless CATCH_B200_NVLS_FUSED=1 asks for the
+in-switch (multimem) variant.
 """
 import argparse
 import os
@@ -45,7 +46,7 @@ def main():
     params.normal_()
     (local_grads if local_grads is not None else comm).normal_()
     dist.barrier()
-    mc = pg.multicast_enabled()
+    mc = pg.multicast_enabled() and os.environ.get("CATCH_B200_NVLS_FUSED") == "1"
 
     def run(step):
         return pg.fused_allreduce_step(comm[:n], params, state, torch.empty(0, device=dev), 0, 0.1, 0.9, 0.0, 1e-4, 0.9, 0.999,

@@ -521,6 +521,17 @@ extern "C" long long b200_comm_nvls_min_bytes(void) {
   return v;
 }
 
+// The fused bucket kernel takes the in-switch path only on request (CATCH_B200_NVLS_FUSED=1): at the 25 MB bucket
+// size peer loads / stores are faster at 4 and 8 ranks (95.6 vs 111.0 us and 110.1 vs 115.8 us per bucket); the
+// in-switch reduction pays off from about 64 MB per message.
+static bool nvls_for_fused() {
+  static const bool v = [] {
+    const char* e = getenv("CATCH_B200_NVLS_FUSED");
+    return e && e[0] == '1';
+  }();
+  return v;
+}
+
 extern "C" long long b200_comm_shard_elems(long long n, int world, int dtype) {
   const int es = (dtype == B200_F32 || dtype == B200_I32) ? 4 : ((dtype == B200_F64 || dtype == B200_I64) ? 8 : 2);
   const int V = 16 / es;
@@ -571,7 +582,7 @@ extern "C" int b200_comm_allreduce_opt(const B200CommCtx* ctx, size_t goff, size
   long long work = (per + U - 1) / U;
   if (opt->cast_src || opt->zero_grads) work = work > nvec / 8 ? work : nvec / 8;  // the local passes cover the whole bucket
   const int grid = comm_grid(work, 512, per * 16 >= (2LL << 20) ? 128 : 64);
-  const bool nvls = ctx->mc != nullptr && n * (grad_dtype == B200_F32 ? 4 : 2) >= b200_comm_nvls_min_bytes();
+  const bool nvls = ctx->mc != nullptr && nvls_for_fused() && n * (grad_dtype == B200_F32 ? 4 : 2) >= b200_comm_nvls_min_bytes();
 #define OPT_LAUNCH(T)                                                                                          \
   do {                                                                                                         \
     if (nvls) allreduce_opt_kernel<T, true><<<grid, 512, 0, s>>>(*ctx, goff, poff, n, scale, *opt, seq);       \

@@ -408,6 +408,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
           tmem_ld32(t_addr + cb, ra);
           tmem_ld32(t_addr + cb + 32, rb);
           tmem_ld_wait();
+          if (g.dbg & 16) continue;  // timing experiment: tensor-memory reads only
           if (lane == 0) {  // the store that last used this buffer has read it
             if (g.epi_bufs == 2) tma_store_wait_read<1>();
             else tma_store_wait_read<0>();
@@ -422,15 +423,20 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
           for (int h = 0; h < 2; ++h) {
             float v[32];
             uint32_t pk[16];
-            finish(ra, cb + 32 * h, v);
-            pack16(v, pk, g.out_dtype);
+            if (g.dbg & 64) {  // timing experiment: no conversion
+#pragma unroll
+              for (int j = 0; j < 16; ++j) pk[j] = ra[j];
+            } else {
+              finish(ra, cb + 32 * h, v);
+              pack16(v, pk, g.out_dtype);
+            }
 #pragma unroll
             for (int k = 0; k < 4; ++k)
               *reinterpret_cast<uint4*>(srow + (((4 * h + k) ^ (lane & 7)) * 16)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
 #pragma unroll
             for (int j = 0; j < 32; ++j) ra[j] = rb[j];
           }
-          fence_proxy_async_smem();
+          if (!(g.dbg & 32)) fence_proxy_async_smem();
           __syncwarp();
           if (g.stats) {
             // Column sums over the 32 staged pixels (the rounded values that were stored; pixels

@@ -173,3 +173,14 @@ def test_lowering_removes_exception_ifs_and_dropout():
     jit.lower_graph(g)
     s = str(g)
     assert "prim::RaiseException" not in s and "aten::dropout" not in s and "aten::contiguous" not in s
+
+
+def test_delayed_scalar_returns_each_value_one_push_later():
+    from catch_b200.utils import DelayedScalar
+
+    r = DelayedScalar()
+    vals = [torch.tensor(float(i) + 0.5).to("blackwell") for i in range(5)]
+    got = [r.push(v) for v in vals]
+    assert got[0] is None and got[1:] == [0.5, 1.5, 2.5, 3.5]
+    assert r.flush() == 4.5 and r.flush() is None
+    assert r.push(torch.tensor([2.0]).to("blackwell").bfloat16().sum()) is None and r.flush() == 2.0

@@ -23,7 +23,7 @@ needs2 = pytest.mark.skipif(_ngpu() < 2, reason="needs two GPUs")
 # NCCL's own NVLS stays off in these child processes.  This backend's multicast mapping is forced on (by default it
 # starts at four ranks) wherever the GPUs support it, except in the test that makes a wait run out: that one runs
 # on plain peer loads and stores.
-ENV = {"NCCL_NVLS_ENABLE": "0", "CATCH_B200_NVLS": "1"}
+ENV = {"NCCL_NVLS_ENABLE": "0", "CATCH_B200_NVLS": "1", "CATCH_B200_NVLS_FUSED": "1"}
 ENV_NO_MULTICAST = {"NCCL_NVLS_ENABLE": "0", "CATCH_B200_NVLS": "0"}
 
 

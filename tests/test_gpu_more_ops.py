@@ -332,3 +332,25 @@ def test_out_variants_and_dim_reductions():
     assert_tensors_equal(o.cpu(), F.binary_cross_entropy(p, t), prec=1e-5)
     torch._C._nn.smooth_l1_loss(dev(p), dev(t), 1, 0.5, out=o)
     assert_tensors_equal(o.cpu(), F.smooth_l1_loss(p, t, beta=0.5), prec=1e-5)
+
+
+def test_short_reductions_with_many_outputs():
+    """Global average pooling over a channels-last tensor (mean over H, W: 49 elements per output, many outputs) and
+    its relatives take the one-thread-per-output reduction kernel."""
+    torch.manual_seed(0)
+    x = torch.randn(64, 256, 7, 7)
+    xc = x.contiguous(memory_format=torch.channels_last)
+    for t in (x, xc):
+        td = dev(t)
+        assert_tensors_equal(td.mean((2, 3)).cpu(), t.mean((2, 3)), prec=1e-5)
+        assert_tensors_equal(td.sum((2, 3), keepdim=True).cpu(), t.sum((2, 3), keepdim=True), prec=1e-4)
+        assert_tensors_equal(td.amax((2, 3)).cpu(), t.amax((2, 3)), prec=0)
+        v, i = td.flatten(2).max(2)
+        rv, ri = t.flatten(2).max(2)
+        assert torch.equal(v.cpu(), rv) and torch.equal(i.cpu(), ri)
+    xb = xc.bfloat16()
+    assert_tensors_equal(F.adaptive_avg_pool2d(dev(xb), 1).float().cpu(), F.adaptive_avg_pool2d(xb.float(), 1), prec=1e-2,
+                         use_MSE=True)
+    y = torch.randn(40000, 33)  # reduce the short inner dimension: outputs are not adjacent in memory -> other kernel
+    assert_tensors_equal(dev(y).sum(1).cpu(), y.sum(1), prec=1e-4)
+    assert_tensors_equal(dev(y.t().contiguous()).sum(0).cpu(), y.sum(1), prec=1e-4)
