@@ -315,7 +315,7 @@ struct BnFinalize {          // optional: statistics come from `sums` instead of
 
 // y = act(x * S[c] + T[c] + residual) with S = invstd * gamma, T = beta - mean * S
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)  // three CTAs per SM: 16 resident warps left the loads short of the copy bandwidth
 bn_apply_fast_kernel(const T* __restrict__ x, T* __restrict__ y, unsigned nvec, int C, const void* mean, int mdt,
                      const float* invstd, const void* gamma, const void* beta, int pdt, const T* __restrict__ res,
                      int act, uint8_t* __restrict__ relu_mask, const BnFinalize fz) {
@@ -578,6 +578,20 @@ inline int red_grid(long long rows) {
   if (g < 1) g = 1;
   return (int)g;
 }
+// Grid of a column-reduction kernel: every CTA owns an equal slice of the rows, so the grid is exactly one wave of
+// resident CTAs (a grid of 4 per SM with only 3 resident ran a one-third-full second wave: 0.65 of the copy
+// bandwidth for the batch-norm backward reduction).
+template <typename K>
+inline int red_grid_for(K kernel, size_t smem, long long rows) {
+  int dev = 0, sms = 148, per_sm = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, RED_THREADS, smem) != cudaSuccess || per_sm < 1) per_sm = 2;
+  long long g = (rows + 63) / 64;
+  if (g > (long long)sms * per_sm) g = (long long)sms * per_sm;
+  if (g < 1) g = 1;
+  return (int)g;
+}
 inline size_t red_smem(int C, int V, int NQ) {
   const int cvecs = C / V;
   const int tx_n = cvecs < RED_THREADS ? cvecs : RED_THREADS;
@@ -690,7 +704,8 @@ extern "C" int b200_bn_stats(const void* x, int dt, long long rows, int C, doubl
   DISPATCH_FLOAT(dt, T, {
     constexpr int V = VecOf<T>::N;
     if (C % V) return (int)cudaErrorInvalidValue;
-    bn_stats_kernel<T><<<red_grid(rows), RED_THREADS, red_smem(C, V, 2), s>>>(static_cast<const T*>(x), rows, C, sums);
+    bn_stats_kernel<T><<<red_grid_for(bn_stats_kernel<T>, red_smem(C, V, 2), rows), RED_THREADS, red_smem(C, V, 2), s>>>(
+        static_cast<const T*>(x), rows, C, sums);
   });
   return (int)cudaGetLastError();
 }
@@ -802,11 +817,12 @@ extern "C" int b200_bn_backward_reduce(const void* dy, int dt, const void* x, in
     if (fast) {
       // four rows in flight per thread, four CTAs per SM: eight rows or more CTAs measured the same or slower
       // (7.38 - 8.90 ms against 7.47 ms over ResNet-50's batch norms; more CTAs mean more fp64 atomics per channel)
-      bn_bwd_reduce_fast_kernel<T, 4><<<red_grid(rows), RED_THREADS, red_smem(C, V, 2), s>>>(
+      bn_bwd_reduce_fast_kernel<T, 4><<<red_grid_for(bn_bwd_reduce_fast_kernel<T, 4>, red_smem(C, V, 2), rows), RED_THREADS,
+                                        red_smem(C, V, 2), s>>>(
           static_cast<const T*>(dy), static_cast<const T*>(x), mean, mdt, invstd,
           is_mask ? static_cast<const uint8_t*>(relu_out) : nullptr, rows, C, sums);
     } else {
-      bn_bwd_reduce_kernel<T><<<red_grid(rows), RED_THREADS, red_smem(C, V, 2), s>>>(
+      bn_bwd_reduce_kernel<T><<<red_grid_for(bn_bwd_reduce_kernel<T>, red_smem(C, V, 2), rows), RED_THREADS, red_smem(C, V, 2), s>>>(
           static_cast<const T*>(dy), static_cast<const T*>(x), mean, mdt, invstd,
           is_mask ? nullptr : static_cast<const T*>(relu_out), (is_mask && V == 8) ? static_cast<const uint8_t*>(relu_out) : nullptr,
           rows, C, sums);
