@@ -137,6 +137,12 @@ __device__ __forceinline__ void add_residual(float (&v)[32], const uint8_t* rp, 
   }
 }
 
+// GENERAL: the epilogue applies alpha / per-channel scale and bias / residual / activation (I8: the accumulators
+// are int32); without it an accumulator is only rounded to the output type.  STATS: channel sums for a following
+// batch norm.  Compile-time switches: with run-time flags the compiler predicated the unrolled 32-element blocks of
+// every option instead of branching around them, and the plain 64 -> 256 channel 1x1 layer spent a third of its time
+// on instructions of options it did not use (145 -> 99 us).
+template <bool GENERAL, bool STATS, bool I8>
 __global__ void __launch_bounds__(CONV_FPROP_THREADS, 1)
 conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvArgs g) {
   extern __shared__ uint8_t smem_raw[];
@@ -343,7 +349,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
     };
     for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
       const int pt = tile % pix_tiles, ct = tile / pix_tiles;
-      if (g.stats && ct != st_ct) { flush_stats(); st_ct = ct; }
+      if (STATS && ct != st_ct) { flush_stats(); st_ct = ct; }
       const int q0 = (pt % g.tiles_q) * g.bw;
       const int p0 = ((pt / g.tiles_q) % g.tiles_p) * g.bh;
       const int n0 = (pt / (g.tiles_q * g.tiles_p)) * g.bni;
@@ -370,26 +376,28 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
 
       // accumulator chunk (32 channels starting at tile column c) -> alpha, scale/bias, residual, activation
       auto finish = [&](const uint32_t (&rr)[32], int c, float (&v)[32]) {
-        if (g.kind == 2) {
+        if (I8) {  // int32 accumulators of the int8 kind
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = (float)(int)rr[j];
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rr[j]);
         }
-        if (g.alpha != 1.f) {
+        if (GENERAL) {
+          if (g.alpha != 1.f) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] *= g.alpha;
-        }
-        if (has_coef) apply_coef(v, cs + c, cbias + c);
-        const int cbase = co0 + c;
-        if (g.residual && row_ok && cbase < g.Cout)
-          add_residual(v, static_cast<const uint8_t*>(g.residual) + (off + cbase) * rsz, min(32, g.Cout - cbase), g.res_dtype);
-        if (g.act == 1) {
+            for (int j = 0; j < 32; ++j) v[j] *= g.alpha;
+          }
+          if (has_coef) apply_coef(v, cs + c, cbias + c);
+          const int cbase = co0 + c;
+          if (g.residual && row_ok && cbase < g.Cout)
+            add_residual(v, static_cast<const uint8_t*>(g.residual) + (off + cbase) * rsz, min(32, g.Cout - cbase), g.res_dtype);
+          if (g.act == 1) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+            for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+          }
         }
-        if (g.stats && !row_ok) {
+        if (STATS && !row_ok) {
           // pixels outside the output are clipped by the store but must not count in the statistics
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0.f;
@@ -426,6 +434,13 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
             if (g.dbg & 64) {  // timing experiment: no conversion
 #pragma unroll
               for (int j = 0; j < 16; ++j) pk[j] = ra[j];
+            } else if (g.dbg & 128) {  // timing experiment: conversion without the epilogue arithmetic
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(ra[j]);
+              pack16(v, pk, g.out_dtype);
+            } else if (g.dbg & 256) {  // timing experiment: truncating pack on the integer pipe
+#pragma unroll
+              for (int j = 0; j < 16; ++j) pk[j] = __byte_perm(ra[2 * j], ra[2 * j + 1], 0x7632);
             } else {
               finish(ra, cb + 32 * h, v);
               pack16(v, pk, g.out_dtype);
@@ -438,7 +453,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
           }
           if (!(g.dbg & 32)) fence_proxy_async_smem();
           __syncwarp();
-          if (g.stats) {
+          if (STATS) {
             // Column sums over the 32 staged pixels (the rounded values that were stored; pixels
             // outside the tensor were zeroed above).
             // packed fp32 pairs: one add and one fma per two elements
@@ -536,7 +551,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       if (has_coef) named_barrier(2, CONV_EPI_THREADS);
     }
-    if (g.stats) flush_stats();
+    if (STATS) flush_stats();
     if (g.tma_store && lane == 0) tma_store_wait_all<0>();  // stores must be complete before shared memory goes away
   }
 
@@ -893,14 +908,24 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p_in, void* stream) {
     }
     if (rc) return rc;
   }
-  static bool attr_done[64] = {false};
-  int rc = set_smem_attr_once((const void*)conv_fprop_kernel, dev, attr_done);
+  const bool general = g.kind == 2 || g.alpha != 1.f || g.scale || g.bias || g.residual || g.act != 0;
+  const bool stats = g.stats != nullptr;
+  typedef void (*Kernel)(const ConvMaps, const ConvArgs);
+  const bool i8 = g.kind == 2;
+  const Kernel kernel = i8 ? (stats ? conv_fprop_kernel<true, true, true> : conv_fprop_kernel<true, false, true>)
+                        : general ? (stats ? conv_fprop_kernel<true, true, false> : conv_fprop_kernel<true, false, false>)
+                                  : (stats ? conv_fprop_kernel<false, true, false> : conv_fprop_kernel<false, false, false>);
+  int rc = 0;
+  {
+    static bool done[8][64] = {};
+    rc = set_smem_attr_once((const void*)kernel, dev, done[(i8 ? 4 : 0) + (general ? 2 : 0) + (stats ? 1 : 0)]);
+  }
   if (rc) return rc;
   const size_t smem = 1024 /*align*/ + (size_t)g.b_res_bytes + (size_t)g.stages * stage_bytes + 1024 /*barriers*/ +
                       g.coef_bytes + (g.tma_store ? 32768 * g.epi_bufs : 0);
   const long total_tiles = pix_tiles * g.tiles_co;
   const int ctas = (int)(total_tiles < sms ? total_tiles : sms);
-  conv_fprop_kernel<<<ctas, CONV_FPROP_THREADS, smem, (cudaStream_t)stream>>>(maps, g);
+  kernel<<<ctas, CONV_FPROP_THREADS, smem, (cudaStream_t)stream>>>(maps, g);
   return (int)cudaGetLastError();
 }
 

@@ -129,6 +129,10 @@ __device__ __forceinline__ void add_residual(float (&v)[32], const uint8_t* rp, 
   }
 }
 
+// GENERAL: the staged-store epilogue applies alpha / per-column scale and bias / per-row bias / residual / activation /
+// the int32 conversion; without it an accumulator is only rounded to the output type (compile-time switch: with
+// run-time flags the compiler predicated the unrolled blocks of every option instead of branching around them).
+template <bool GENERAL>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmD, const GemmKernelArgs g) {
@@ -335,6 +339,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         uint8_t* sbuf0 = stage_out + (warp - 2) * 4096 * g.epi_bufs;  // two buffers per warp when they fit: convert while the last store is read
         auto finish = [&](const uint32_t (&r)[32], int c, float (&v)[32]) {
           const int n_base = n0 + c;
+          if (!GENERAL) {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) v[jj] = __uint_as_float(r[jj]);
+            return;
+          }
 #pragma unroll
           for (int jj = 0; jj < 32; ++jj) v[jj] = g.kind == 2 ? (float)(int)r[jj] : __uint_as_float(r[jj]);
           if (g.alpha != 1.f) {
@@ -641,15 +650,18 @@ extern "C" int b200_gemm(const B200GemmParams* p, void* stream) {
     rc = encode_tiled(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p->D, dims, str, box, nullptr, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   }
-  static bool attr_set[64] = {false};
-  if (!attr_set[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  const bool general = !(g.tma_store && g.kind != 2 && g.alpha == 1.f && !g.col_scale && !g.bias && !g.residual && !g.act);
+  typedef void (*Kernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmKernelArgs);
+  const Kernel kernel = general ? gemm_tcgen05_kernel<true> : gemm_tcgen05_kernel<false>;
+  static bool attr_set[2][64] = {};
+  if (!attr_set[general ? 1 : 0][dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return (int)e;
-    attr_set[dev & 63] = true;
+    attr_set[general ? 1 : 0][dev & 63] = true;
   }
   const long total_tiles = (long)g.tiles_m * g.tiles_n * g.batch * g.splits;
   int ctas = p->max_ctas > 0 ? p->max_ctas : sms;
   if (ctas > total_tiles) ctas = (int)total_tiles;
-  gemm_tcgen05_kernel<<<ctas, GEMM_THREADS, smem, (cudaStream_t)stream>>>(tmA, tmB, tmD, g);
+  kernel<<<ctas, GEMM_THREADS, smem, (cudaStream_t)stream>>>(tmA, tmB, tmD, g);
   return (int)cudaGetLastError();
 }
