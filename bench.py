@@ -14,7 +14,7 @@ Arms (``--impl``):
              the stock arm runs first in the same invocation and its numbers are reported inside the
              line (``stock``), so the ratio is taken on one box, back to back.
   stock      stock PyTorch on ``torch.cuda``: cuDNN / cuBLAS kernels, ``torch.optim.SGD``,
-             ``DistributedDataParallel`` over NCCL -- the comparison point BASELINE.md names because the
+             ``DistributedDataParallel`` over NCCL -- the same-hardware comparison point, because the
              reference itself cannot run without Cambricon hardware.
   reference  prints why the reference cannot run here.
 
@@ -36,7 +36,7 @@ import threading
 import time
 
 # Stock PyTorch (CUDA + cuDNN + NCCL DDP) on this pool's B200s, images/sec at 1 / 2 / 4 / 8 GPUs, measured
-# with ``bench.py --impl stock`` (BASELINE.md row 2).  The reference publishes no throughput number, so
+# with ``bench.py --impl stock``.  The reference publishes no throughput number, so
 # ``vs_baseline`` is taken against these; a stock run made in the same invocation is reported next to it.
 STOCK_IMAGES_PER_SEC = {1: 4826.0, 2: 9358.5, 4: 18660.2, 8: 37211.9}
 
@@ -460,7 +460,7 @@ def main():
         line = dict(common, impl="ours", value=round(ips, 1), ms_per_step=round(ours["ms"] / args.steps, 3),
                     vs_baseline=round(ips / base, 4) if base else None,
                     baseline={"value": base, "what": "stock PyTorch CUDA + cuDNN + NCCL DDP, same config, same pool "
-                                                     "(bench.py --impl stock; BASELINE.md row 2)"},
+                                                     "(bench.py --impl stock)"},
                     config=dict(config, module_fusion="catch_b200.fusion.fuse_bn_act", grad_allreduce_dtype=args.grad_dtype),
                     clocks=ours["clocks"], gpu_launches=ours["launches"],
                     e2e={"value": round(ips_e2e, 1), "unit": "images/sec", "ms_per_step": round(ours["ms_e2e"] / args.steps, 3),

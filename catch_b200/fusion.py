@@ -23,16 +23,80 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 
+class _GradSink:
+    """Meeting point for the gradients that reach one activation tensor over several paths of a residual block.
+
+    A tensor that feeds a fused convolution (and, as the skip connection, a fused batch norm + add) would receive one
+    gradient per consumer and autograd would add them with an element-wise kernel per fork.  Instead every fused
+    convolution that consumes the tensor registers here in the forward pass; in the backward pass a consumer that is
+    not the last one to run parks its gradient here and returns none, and the last convolution hands the parked
+    gradient to its data-gradient kernel, whose epilogue adds it.  The skip connection's batch norm runs before the
+    convolutions of its block (it was created after them), so it always parks."""
+
+    __slots__ = ("consumers", "remaining", "pending")
+
+    def __init__(self):
+        self.consumers = 0
+        self.remaining = 0
+        self.pending = None
+
+    def park(self, grad):
+        self.pending = grad if self.pending is None else self.pending + grad
+        # every parked gradient has to be picked up before the backward pass ends: check when it does
+        if not _open_sinks:
+            torch.autograd.Variable._execution_engine.queue_callback(_check_sinks)
+        _open_sinks.append(self)
+
+    def take(self):
+        grad, self.pending = self.pending, None
+        return grad
+
+
+_SINKS_ENABLED = True
+_open_sinks = []
+
+
+def _check_sinks() -> None:
+    """Runs when a backward pass ends: a gradient that is still parked was never added to anything (a registered
+    consumer's backward did not run, e.g. because its output does not reach the loss)."""
+    lost = [s for s in _open_sinks if s.pending is not None]
+    for s in _open_sinks:
+        s.pending = None
+        s.remaining = s.consumers
+    _open_sinks.clear()
+    if lost:
+        raise RuntimeError("catch_b200.fusion: a gradient parked at a residual fork was not consumed in this backward pass "
+                           "(a fused convolution that reads the same tensor took no part in it); call "
+                           "catch_b200.fusion.set_gradient_sinks(False) for this model")
+
+
+def set_gradient_sinks(enabled: bool) -> None:
+    """Fold the gradient additions at residual forks into the data-gradient kernels (default on)."""
+    global _SINKS_ENABLED
+    _SINKS_ENABLED = bool(enabled)
+
+
+def _sink_for(x: torch.Tensor, create: bool) -> Optional["_GradSink"]:
+    if not (_SINKS_ENABLED and torch.is_grad_enabled() and x.requires_grad):
+        return None
+    sink = getattr(x, "_b200_grad_sink", None)
+    if sink is None and create:
+        sink = _GradSink()
+        x._b200_grad_sink = sink
+    return sink
+
+
 class _BNActFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, running_mean, running_var, residual, training, momentum, eps, act, sums=None,
-                num_batches_tracked=None):
+                num_batches_tracked=None, res_sink=None):
         out, mean, invstd, mask = torch.ops.catch_b200.batch_norm_act_mask(x, weight, bias, running_mean, running_var,
                                                                            residual, training, momentum, eps, act, sums,
                                                                            num_batches_tracked)
         # with a ReLU the backward only needs to know which outputs were positive: one bit each
         ctx.save_for_backward(mask if mask.numel() else out, x, weight, running_mean, mean, invstd)
         ctx.cfg = (training, act, residual is not None)
+        ctx.res_sink = res_sink
         return out
 
     @staticmethod
@@ -41,8 +105,12 @@ class _BNActFn(torch.autograd.Function):
         training, act, has_res = ctx.cfg
         dx, dgamma, dbeta, dres = torch.ops.catch_b200.batch_norm_act_backward(
             grad_out, out, x, weight, running_mean, mean, invstd, training, act, has_res)
+        sink = ctx.res_sink
+        if has_res and sink is not None and sink.remaining > 0:
+            sink.park(dres)  # a convolution that also consumes the skip tensor adds it in its data-gradient epilogue
+            dres = None
         return (dx, dgamma if weight is not None else None, dbeta if weight is not None else None, None, None,
-                dres if has_res else None, None, None, None, None, None, None)
+                dres if has_res else None, None, None, None, None, None, None, None)
 
 
 class _ConvStatsFn(torch.autograd.Function):
@@ -55,7 +123,8 @@ class _ConvStatsFn(torch.autograd.Function):
     fp32 slice behind ``weight.grad``) the kernel adds into that bucket directly."""
 
     @staticmethod
-    def forward(ctx, x, weight, stride, padding, compute_dtype):
+    def forward(ctx, x, weight, stride, padding, compute_dtype, sink=None):
+        ctx.sink = sink
         lowp = getattr(weight, "_b200_lowp", None)
         if weight.dtype == compute_dtype:
             w = weight
@@ -75,6 +144,22 @@ class _ConvStatsFn(torch.autograd.Function):
         x, w = ctx.saved_tensors
         stride, padding, wdtype = ctx.cfg
         need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        sink = ctx.sink if need_dx else None
+        parked = None
+        if sink is not None:
+            parked = sink.take()
+            sink.remaining -= 1
+
+        def finish(dx):
+            """Park the input gradient for a later consumer of the same tensor, or hand the total to autograd."""
+            if sink is None:
+                return dx
+            if sink.remaining > 0:
+                sink.park(dx)
+                return None
+            sink.remaining = sink.consumers  # ready for another backward pass over the same graph
+            return dx
+
         if wdtype == torch.float32:
             acc = getattr(ctx.param, "_b200_grad_acc", None) if need_dw else None
             p = ctx.param
@@ -83,13 +168,15 @@ class _ConvStatsFn(torch.autograd.Function):
                     and (p.shape[2] * p.shape[3] == 1 or p.is_contiguous(memory_format=torch.channels_last))):
                 # The parameter's post-accumulate-grad hook still fires for the undefined gradient returned
                 # here, after this function has queued the kernel: that is what tells the bucket's owner.
-                dx, _ = torch.ops.catch_b200.conv2d_backward_fp32w(grad_y, x, w, stride, padding, need_dx, True, acc)
-                return dx, None, None, None, None
-            dx, dw = torch.ops.catch_b200.conv2d_backward_fp32w(grad_y, x, w, stride, padding, need_dx, need_dw)
+                dx, _ = torch.ops.catch_b200.conv2d_backward_fp32w(grad_y, x, w, stride, padding, need_dx, True, acc, parked)
+                return finish(dx), None, None, None, None, None
+            dx, dw = torch.ops.catch_b200.conv2d_backward_fp32w(grad_y, x, w, stride, padding, need_dx, need_dw, None, parked)
         else:
             dx, dw, _ = torch.ops.aten.convolution_backward(grad_y, x, w, None, stride, padding, [1, 1], False, [0, 0], 1,
                                                             [need_dx, need_dw, False])
-        return dx, dw, None, None, None
+            if parked is not None and dx is not None:
+                dx = dx + parked
+        return finish(dx), dw, None, None, None, None
 
 
 class StatsConv2d(nn.Conv2d):
@@ -107,7 +194,11 @@ class StatsConv2d(nn.Conv2d):
                 x = x.to(torch.get_autocast_dtype("blackwell"))
             if x.dtype in (torch.bfloat16, torch.float16) and (self.weight.dtype == x.dtype or
                                                               (autocast and self.weight.dtype == torch.float32)):
-                y, sums = _ConvStatsFn.apply(x, self.weight, list(self.stride), list(self.padding), x.dtype)
+                sink = _sink_for(x, create=True)
+                if sink is not None:
+                    sink.consumers += 1
+                    sink.remaining += 1
+                y, sums = _ConvStatsFn.apply(x, self.weight, list(self.stride), list(self.padding), x.dtype, sink)
                 y._b200_channel_sums = sums
                 return y
         return super().forward(x)
@@ -139,8 +230,9 @@ class BatchNormAct2d(nn.BatchNorm2d):
                 and (residual is None or (residual.shape == x.shape and residual.dtype == x.dtype))):
             sums = getattr(x, "_b200_channel_sums", None) if training else None
             # the fused kernel also increments num_batches_tracked (no separate tiny launch per batch norm)
+            res_sink = _sink_for(residual, create=False) if residual is not None else None
             return _BNActFn.apply(x, self.weight, self.bias, rm, rv, residual, training, momentum, self.eps, self.act,
-                                  sums, self.num_batches_tracked if count_batch else None)
+                                  sums, self.num_batches_tracked if count_batch else None, res_sink)
         if count_batch:
             self.num_batches_tracked.add_(1)
         y = F.batch_norm(x, rm, rv, self.weight, self.bias, training, momentum, self.eps)

@@ -142,7 +142,7 @@ __device__ __forceinline__ void add_residual(float (&v)[32], const uint8_t* rp, 
 // batch norm.  Compile-time switches: with run-time flags the compiler predicated the unrolled 32-element blocks of
 // every option instead of branching around them, and the plain 64 -> 256 channel 1x1 layer spent a third of its time
 // on instructions of options it did not use (145 -> 99 us).
-template <bool GENERAL, bool STATS, bool I8>
+template <bool GENERAL, bool STATS, bool I8, bool RES>
 __global__ void __launch_bounds__(CONV_FPROP_THREADS, 1)
 conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvArgs g) {
   extern __shared__ uint8_t smem_raw[];
@@ -396,6 +396,10 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
           }
+        } else if (RES) {  // only a residual (a gradient that arrived over another path) is added
+          const int cbase = co0 + c;
+          if (row_ok && cbase < g.Cout)
+            add_residual(v, static_cast<const uint8_t*>(g.residual) + (off + cbase) * rsz, min(32, g.Cout - cbase), g.res_dtype);
         }
         if (STATS && !row_ok) {
           // pixels outside the output are clipped by the store but must not count in the statistics
@@ -908,17 +912,20 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p_in, void* stream) {
     }
     if (rc) return rc;
   }
-  const bool general = g.kind == 2 || g.alpha != 1.f || g.scale || g.bias || g.residual || g.act != 0;
+  const bool general = g.kind == 2 || g.alpha != 1.f || g.scale || g.bias || g.act != 0;
   const bool stats = g.stats != nullptr;
+  const bool res = g.residual != nullptr;
   typedef void (*Kernel)(const ConvMaps, const ConvArgs);
   const bool i8 = g.kind == 2;
-  const Kernel kernel = i8 ? (stats ? conv_fprop_kernel<true, true, true> : conv_fprop_kernel<true, false, true>)
-                        : general ? (stats ? conv_fprop_kernel<true, true, false> : conv_fprop_kernel<true, false, false>)
-                                  : (stats ? conv_fprop_kernel<false, true, false> : conv_fprop_kernel<false, false, false>);
+  Kernel kernel;
+  if (i8) kernel = stats ? conv_fprop_kernel<true, true, true, false> : conv_fprop_kernel<true, false, true, false>;
+  else if (general) kernel = stats ? conv_fprop_kernel<true, true, false, false> : conv_fprop_kernel<true, false, false, false>;
+  else if (res) kernel = stats ? conv_fprop_kernel<false, true, false, true> : conv_fprop_kernel<false, false, false, true>;
+  else kernel = stats ? conv_fprop_kernel<false, true, false, false> : conv_fprop_kernel<false, false, false, false>;
   int rc = 0;
   {
-    static bool done[8][64] = {};
-    rc = set_smem_attr_once((const void*)kernel, dev, done[(i8 ? 4 : 0) + (general ? 2 : 0) + (stats ? 1 : 0)]);
+    static bool done[16][64] = {};
+    rc = set_smem_attr_once((const void*)kernel, dev, done[(i8 ? 8 : 0) + (general ? 4 : 0) + (res ? 2 : 0) + (stats ? 1 : 0)]);
   }
   if (rc) return rc;
   const size_t smem = 1024 /*align*/ + (size_t)g.b_res_bytes + (size_t)g.stages * stage_bytes + 1024 /*barriers*/ +

@@ -256,10 +256,21 @@ Tensor forward_impl(const Tensor& input, const Tensor& weight, const std::option
   return out;
 }
 
-Tensor dgrad_impl(const Tensor& grad_in, const Tensor& weight, const ConvGeom& g, at::ScalarType out_dtype) {
+// add_to: a gradient of the same input that arrived over another path (the skip connection of a residual block);
+// it is added in the epilogue of the kernel instead of by a separate element-wise kernel afterwards.
+Tensor dgrad_impl(const Tensor& grad_in, const Tensor& weight, const ConvGeom& g, at::ScalarType out_dtype,
+                  const Tensor* add_to = nullptr) {
   OpScope scope("conv_dgrad", grad_in);
   Tensor dx = empty_b200({g.N, g.C, g.H, g.W}, out_dtype, grad_in.device().index(), at::MemoryFormat::ChannelsLast);
   if (dx.numel() == 0) return dx;
+  Tensor extra;
+  if (add_to && add_to->defined()) {
+    TORCH_CHECK(add_to->sizes() == dx.sizes(), "b200 conv dgrad: the gradient to add must have the input's shape");
+    extra = add_to->scalar_type() == out_dtype ? *add_to : add_to->to(out_dtype);
+    extra = extra.contiguous(at::MemoryFormat::ChannelsLast);
+  }
+  // the epilogue can add it when every input element is written by exactly one launch of the first pass
+  const bool fuse_extra = extra.defined() && g.sh == 1 && g.sw == 1 && out_dtype != at::kFloat;
   const bool fp32 = grad_in.scalar_type() == at::kFloat;
   const at::ScalarType dt = compute_dtype(grad_in.scalar_type());
   TORCH_CHECK(!fp32 || out_dtype == at::kFloat, "b200 conv dgrad: fp32 gradients produce fp32 input gradients");
@@ -308,6 +319,9 @@ Tensor dgrad_impl(const Tensor& grad_in, const Tensor& weight, const ConvGeom& g
         if (pass > 0) {  // later passes add to what the earlier ones wrote
           p.residual = dx.data_ptr();
           p.res_dtype = to_b200_dtype(out_dtype);
+        } else if (fuse_extra) {
+          p.residual = extra.data_ptr();
+          p.res_dtype = to_b200_dtype(out_dtype);
         }
         launches.push_back(p);
       }
@@ -315,6 +329,7 @@ Tensor dgrad_impl(const Tensor& grad_in, const Tensor& weight, const ConvGeom& g
     if (need_zero && !zeroed) { dx.zero_(); zeroed = true; }
     for (auto& p : launches) B200_KERNEL_CHECK(b200_conv_fprop(&p, scope.stream()));
   }
+  if (extra.defined() && !fuse_extra) dx.add_(extra);
   return dx;
 }
 
@@ -577,14 +592,16 @@ at::Tensor conv_bn_act_device(const at::Tensor& input, const at::Tensor& weight,
 std::tuple<at::Tensor, at::Tensor> conv_backward_fp32w_device(const at::Tensor& grad, const at::Tensor& input,
                                                               const at::Tensor& weight, at::IntArrayRef stride,
                                                               at::IntArrayRef padding, bool need_dx, bool need_dw,
-                                                              const std::optional<at::Tensor>& accum) {
+                                                              const std::optional<at::Tensor>& accum,
+                                                              const std::optional<at::Tensor>& dx_add) {
   const int64_t ones[2] = {1, 1};
   check_supported(input, weight, stride, padding, at::IntArrayRef(ones, 2), false, 1);
   ConvGeom g = geom(input, weight, stride, padding);
   at::Tensor dx, dw;
   if (need_dx) {
     TORCH_CHECK(g.C % 8 == 0, "b200 conv dgrad: input channels must be a multiple of 8");
-    dx = dgrad_impl(grad, weight, g, input.scalar_type());
+    const bool has_add = dx_add.has_value() && dx_add->defined();
+    dx = dgrad_impl(grad, weight, g, input.scalar_type(), has_add ? &*dx_add : nullptr);
   }
   if (need_dw) {
     const bool has_acc = accum.has_value() && accum->defined();

@@ -40,7 +40,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_mask(
 std::tuple<at::Tensor, at::Tensor> conv_backward_fp32w_device(const at::Tensor& grad, const at::Tensor& input,
                                                               const at::Tensor& weight, at::IntArrayRef stride,
                                                               at::IntArrayRef padding, bool need_dx, bool need_dw,
-                                                              const std::optional<at::Tensor>& accum);
+                                                              const std::optional<at::Tensor>& accum,
+                                                              const std::optional<at::Tensor>& dx_add);
 std::tuple<at::Tensor, at::Tensor> conv_stats_device(const at::Tensor& input, const at::Tensor& weight, at::IntArrayRef stride,
                                                      at::IntArrayRef padding);
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> dropout_add_layer_norm(
@@ -107,8 +108,9 @@ TORCH_LIBRARY(catch_b200, m) {
   m.def("conv2d_stats(Tensor input, Tensor weight, int[] stride, int[] padding) -> (Tensor, Tensor)");
   // (grad_input, grad_weight) of a dense 16-bit convolution; grad_weight is fp32 (undefined results where not
   // needed).  With `accum` (flat fp32, memory order [K][R][S][C]) the weight gradient is added into it in place.
+  // dx_add: another gradient of `input` (a skip connection's) that the data-gradient epilogue adds to grad_input.
   m.def("conv2d_backward_fp32w(Tensor grad, Tensor input, Tensor weight, int[] stride, int[] padding, bool need_dx, "
-        "bool need_dw, Tensor(a!)? accum=None) -> (Tensor, Tensor)");
+        "bool need_dw, Tensor(a!)? accum=None, Tensor? dx_add=None) -> (Tensor, Tensor)");
   // backward of a 16-bit linear layer with fp32 master weights: (grad_input, grad_weight fp32, grad_bias fp32); with
   // accum_w / accum_b the parameter gradients are added into those flat fp32 buffers and not returned
   m.def("linear_backward_fp32w(Tensor grad, Tensor input, Tensor weight, bool need_dx, bool need_dw, bool need_db, "

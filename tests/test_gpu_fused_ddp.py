@@ -149,3 +149,75 @@ def test_optimizer_state_dict_loads_into_stock_optimizer(kind):
     for p, q, r in zip(ref.parameters(), resumed.parameters(), fdp3.module.parameters()):
         assert_tensors_equal(q, p, **kw)
         assert_tensors_equal(r, p, **kw)
+
+
+def test_gradient_sinks_fold_the_fork_additions():
+    """The gradients that reach a residual block's input over the skip connection and over the first convolution are
+    added in that convolution's data-gradient epilogue (no element-wise add per fork): same parameter and input
+    gradients as with the additions left to autograd, also for a second backward pass over a retained graph."""
+    import copy
+
+    import catch_b200
+    import torchvision
+    from catch_b200 import fusion
+
+    torch.manual_seed(5)
+    ref = torchvision.models.resnet50(num_classes=8)
+    x = torch.randn(4, 3, 64, 64)
+    t = torch.randint(0, 8, (4,))
+    grads = {}
+    for sinks in (False, True):
+        fusion.set_gradient_sinks(sinks)
+        try:
+            m = fusion.fuse_bn_act(copy.deepcopy(ref)).to(DEV).to(memory_format=torch.channels_last)
+            xd = x.to(DEV).contiguous(memory_format=torch.channels_last).requires_grad_()
+            catch_b200._C._reset_kernel_launch_count()
+            with torch.autocast(DEV, dtype=torch.bfloat16):
+                loss = F.cross_entropy(m(xd), t.to(DEV))
+            loss.backward(retain_graph=sinks)
+            launches = catch_b200._C._kernel_launch_count()
+            g1 = {n: p.grad.detach().float().cpu().clone() for n, p in m.named_parameters()}
+            g1["input"] = xd.grad.detach().float().cpu().clone()
+            if sinks:  # a second pass over the same graph accumulates the same gradients again
+                loss.backward()
+                for n, p in m.named_parameters():
+                    assert_tensors_equal(p.grad.float().cpu(), 2 * g1[n], prec=2e-2, use_MSE=True, msg=f"second pass {n}")
+            grads[sinks] = (g1, launches, loss.item())
+        finally:
+            fusion.set_gradient_sinks(True)
+    assert abs(grads[True][2] - grads[False][2]) < 1e-3
+    assert grads[True][1] <= grads[False][1] - 12, (grads[True][1], grads[False][1])  # 16 fork additions are gone
+    for n, a in grads[False][0].items():
+        b = grads[True][0][n]
+        cos = (a.double().flatten() @ b.double().flatten() / (a.double().norm() * b.double().norm() + 1e-30)).item()
+        assert cos > 0.995, (n, cos)
+
+
+def test_parked_gradient_that_nobody_consumes_is_an_error():
+    from catch_b200 import fusion
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.unused = fusion.StatsConv2d(64, 64, 1, bias=False)
+            self.conv = fusion.StatsConv2d(64, 64, 3, padding=1, bias=False)
+            self.bn = fusion.BatchNormAct2d(64)
+
+        def forward(self, x):
+            self.unused(x)  # reads x, but its result never reaches the loss
+            return self.bn(self.conv(x), x)
+
+    net = Net().to(DEV).to(memory_format=torch.channels_last).train()
+    x = torch.randn(2, 64, 8, 8).to(DEV).bfloat16().contiguous(memory_format=torch.channels_last).requires_grad_()
+    with torch.autocast(DEV, dtype=torch.bfloat16):
+        y = net(x)
+    with pytest.raises(RuntimeError, match="parked"):
+        y.float().sum().backward()
+    # the next iteration starts clean
+    fusion.set_gradient_sinks(False)
+    try:
+        with torch.autocast(DEV, dtype=torch.bfloat16):
+            net(x).float().sum().backward()
+        assert x.grad is not None
+    finally:
+        fusion.set_gradient_sinks(True)
