@@ -79,7 +79,7 @@ def case_softmax_xent():
     logits = rnd(8192, 30522)  # 500 MB
     target = torch.randint(0, 30522, (8192,)).to(DEV)
     fn = lambda: torch.ops.catch_b200.softmax_cross_entropy(logits, target, -100, 0.0)
-    return fn, 0, logits.numel() * 2, "softmax_xent"
+    return fn, 0, logits.numel() * 2 * 2, "softmax_xent"  # logits read once, gradient written once
 
 
 def case_layernorm():

@@ -38,6 +38,9 @@ __device__ __forceinline__ float ldp(const void* p, int i, int dt) {
 }
 
 constexpr int MAXV = 12;  // vectors of 4 per lane kept in registers: rows of up to 32 * 4 * 12 = 1536 columns
+// The kernels are instantiated for 2, 4, 6, 8 and 12 vectors per lane and the launcher picks the smallest that holds a
+// row: with the row of a 768-wide layer in 24 registers instead of 48 three CTAs fit on an SM instead of one
+// (the forward kernel ran at 0.19 of the copy bandwidth with 200 registers per thread).
 
 template <typename T>
 __device__ __forceinline__ void ld4(const T* p, float (&v)[4]) {
@@ -71,7 +74,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // mask: one byte per vector of four elements, bit k set when element k is kept
-template <typename T>
+template <typename T, int NV>
 __global__ void __launch_bounds__(256)
 dropout_add_ln_fwd_kernel(const T* __restrict__ h, const T* __restrict__ res, long long rows, int cols, float p,
                           unsigned long long seed, unsigned long long offset, const void* gamma, const void* beta, int pdt,
@@ -81,10 +84,10 @@ dropout_add_ln_fwd_kernel(const T* __restrict__ h, const T* __restrict__ res, lo
   const int nvec = cols / 4;
   const float keep_scale = p < 1.f ? 1.f / (1.f - p) : 0.f;
   for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + warp; row < rows; row += (long long)gridDim.x * (blockDim.x >> 5)) {
-    float s[MAXV][4];
+    float s[NV][4];
     float sum = 0.f;
 #pragma unroll
-    for (int j = 0; j < MAXV; ++j) {
+    for (int j = 0; j < NV; ++j) {
       const int v = j * 32 + lane;
       if (v < nvec) {
         const long long e = row * cols + (long long)v * 4;
@@ -110,7 +113,7 @@ dropout_add_ln_fwd_kernel(const T* __restrict__ h, const T* __restrict__ res, lo
     const float m = warp_sum(sum) / (float)cols;
     float sq = 0.f;
 #pragma unroll
-    for (int j = 0; j < MAXV; ++j) {
+    for (int j = 0; j < NV; ++j) {
       if (j * 32 + lane < nvec) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) { const float d = s[j][k] - m; sq += d * d; }
@@ -119,7 +122,7 @@ dropout_add_ln_fwd_kernel(const T* __restrict__ h, const T* __restrict__ res, lo
     const float r = rsqrtf(warp_sum(sq) / (float)cols + eps);
     if (lane == 0) { mean[row] = m; rstd[row] = r; }
 #pragma unroll
-    for (int j = 0; j < MAXV; ++j) {
+    for (int j = 0; j < NV; ++j) {
       const int v = j * 32 + lane;
       if (v < nvec) {
         float o[4];
@@ -134,7 +137,7 @@ dropout_add_ln_fwd_kernel(const T* __restrict__ h, const T* __restrict__ res, lo
   }
 }
 
-template <typename T>
+template <typename T, int NV>
 __global__ void __launch_bounds__(256)
 dropout_add_ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ s_in, const unsigned char* __restrict__ mask,
                           long long rows, int cols, float p, const void* gamma, int pdt, const float* __restrict__ mean,
@@ -142,17 +145,17 @@ dropout_add_ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ s_in, 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nvec = cols / 4;
   const float keep_scale = p < 1.f ? 1.f / (1.f - p) : 0.f;
-  float pg[MAXV][4], pb[MAXV][4];
+  float pg[NV][4], pb[NV][4];
 #pragma unroll
-  for (int j = 0; j < MAXV; ++j)
+  for (int j = 0; j < NV; ++j)
 #pragma unroll
     for (int k = 0; k < 4; ++k) { pg[j][k] = 0.f; pb[j][k] = 0.f; }
   for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + warp; row < rows; row += (long long)gridDim.x * (blockDim.x >> 5)) {
     const float m = mean[row], r = rstd[row];
-    float g[MAXV][4], xh[MAXV][4];
+    float g[NV][4], xh[NV][4];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int j = 0; j < MAXV; ++j) {
+    for (int j = 0; j < NV; ++j) {
       const int v = j * 32 + lane;
       if (v < nvec) {
         const long long e = row * cols + (long long)v * 4;
@@ -173,7 +176,7 @@ dropout_add_ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ s_in, 
     s1 = warp_sum(s1) / (float)cols;
     s2 = warp_sum(s2) / (float)cols;
 #pragma unroll
-    for (int j = 0; j < MAXV; ++j) {
+    for (int j = 0; j < NV; ++j) {
       const int v = j * 32 + lane;
       if (v < nvec) {
         const long long e = row * cols + (long long)v * 4;
@@ -190,7 +193,7 @@ dropout_add_ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ s_in, 
     }
   }
 #pragma unroll
-  for (int j = 0; j < MAXV; ++j) {
+  for (int j = 0; j < NV; ++j) {
     const int v = j * 32 + lane;
     if (v < nvec) {
 #pragma unroll
@@ -231,9 +234,17 @@ extern "C" int b200_dropout_add_layernorm_fwd(const void* h, const void* residua
   const int warps = 8;
   long long grid = (rows + warps - 1) / warps;
   if (grid > 148 * 8) grid = 148 * 8;
-  DISPATCH16(dtype, T, (dropout_add_ln_fwd_kernel<T><<<(unsigned)grid, warps * 32, 0, (cudaStream_t)stream>>>(
-                           static_cast<const T*>(h), static_cast<const T*>(residual), rows, cols, p, seed, offset, gamma, beta,
-                           param_dtype, eps, static_cast<T*>(y), static_cast<T*>(s_out), mask, mean, rstd)));
+  const int per_lane = (cols / 4 + 31) / 32;
+#define LN_FWD(NV)                                                                                                     \
+  DISPATCH16(dtype, T, (dropout_add_ln_fwd_kernel<T, NV><<<(unsigned)grid, warps * 32, 0, (cudaStream_t)stream>>>(     \
+                           static_cast<const T*>(h), static_cast<const T*>(residual), rows, cols, p, seed, offset, gamma, beta, \
+                           param_dtype, eps, static_cast<T*>(y), static_cast<T*>(s_out), mask, mean, rstd)))
+  if (per_lane <= 2) { LN_FWD(2); }
+  else if (per_lane <= 4) { LN_FWD(4); }
+  else if (per_lane <= 6) { LN_FWD(6); }
+  else if (per_lane <= 8) { LN_FWD(8); }
+  else { LN_FWD(12); }
+#undef LN_FWD
   return (int)cudaGetLastError();
 }
 
@@ -245,9 +256,17 @@ extern "C" int b200_dropout_add_layernorm_bwd(const void* dy, const void* s, con
   const int warps = 8;
   long long grid = (rows + warps - 1) / warps;
   if (grid > 148 * 2) grid = 148 * 2;  // fewer, longer-lived warps: fewer atomics for the parameter gradients
-  DISPATCH16(dtype, T, (dropout_add_ln_bwd_kernel<T><<<(unsigned)grid, warps * 32, 0, (cudaStream_t)stream>>>(
-                           static_cast<const T*>(dy), static_cast<const T*>(s), mask, rows, cols, p, gamma, param_dtype, mean,
-                           rstd, static_cast<T*>(ds), static_cast<T*>(dh), dgamma, dbeta)));
+  const int per_lane = (cols / 4 + 31) / 32;
+#define LN_BWD(NV)                                                                                                     \
+  DISPATCH16(dtype, T, (dropout_add_ln_bwd_kernel<T, NV><<<(unsigned)grid, warps * 32, 0, (cudaStream_t)stream>>>(     \
+                           static_cast<const T*>(dy), static_cast<const T*>(s), mask, rows, cols, p, gamma, param_dtype, mean, \
+                           rstd, static_cast<T*>(ds), static_cast<T*>(dh), dgamma, dbeta)))
+  if (per_lane <= 2) { LN_BWD(2); }
+  else if (per_lane <= 4) { LN_BWD(4); }
+  else if (per_lane <= 6) { LN_BWD(6); }
+  else if (per_lane <= 8) { LN_BWD(8); }
+  else { LN_BWD(12); }
+#undef LN_BWD
   return (int)cudaGetLastError();
 }
 

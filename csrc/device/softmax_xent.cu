@@ -161,11 +161,172 @@ __global__ void __launch_bounds__(256) softmax_xent_kernel(const void* x, int dt
   }
 }
 
+// ---- rows cached in shared memory: one read of the input, 16-byte loads and stores --------------------------
+// The kernels above read a row three times, two bytes per thread and load.  For rows of some length (a 30522-word
+// vocabulary in bf16 is 61 KB) that is a third of the memory roofline at best and in practice far less; here a CTA
+// copies its row into shared memory with 16-byte loads while it takes the maximum, and the remaining passes run out of
+// shared memory.  Used when the row fits (up to 200 KB) and rows start on 16-byte boundaries.
+template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half(v); }
+
+// Copies cols elements of one row into shared memory and returns this thread's running maximum.  Rows need not
+// start on 16-byte boundaries (30522 bf16 columns do not): the shared copy is placed at the same 16-byte phase as
+// the source row, a scalar head runs up to the first boundary, 16-byte vectors follow, a scalar tail ends the row.
+template <typename T>
+__device__ __forceinline__ T* row_in_smem(unsigned char* smem, const T* src) {
+  return reinterpret_cast<T*>(smem + (reinterpret_cast<uintptr_t>(src) & 15));
+}
+template <typename T>
+__device__ __forceinline__ int head_elems(const T* p, int cols) {
+  const int h = (int)(((16 - (reinterpret_cast<uintptr_t>(p) & 15)) & 15) / sizeof(T));
+  return h < cols ? h : cols;
+}
+template <typename T>
+__device__ __forceinline__ float stage_row(const T* __restrict__ src, T* row, int cols) {
+  constexpr int V = Vec16<T>::N;
+  float m = -FLT_MAX;
+  const int head = head_elems(src, cols);
+  const int nvec = (cols - head) / V;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + head) + i);
+    reinterpret_cast<uint4*>(row + head)[i] = raw;
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int k = 0; k < V; ++k) m = fmaxf(m, to_f<T>(e[k]));
+  }
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    if (c >= head && c < head + nvec * V) continue;
+    const T v = src[c];
+    row[c] = v;
+    m = fmaxf(m, to_f<T>(v));
+  }
+  return m;
+}
+
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256) softmax_xent_smem_kernel(const T* __restrict__ x, const long long* target, int cols,
+                                                                long long ignore, float smooth, float* row_loss,
+                                                                const float* n_valid, TO* __restrict__ dl, float gscale) {
+  extern __shared__ __align__(16) unsigned char smem_row[];
+  __shared__ float sh[32];
+  const long long r = blockIdx.x, base = r * cols;
+  T* row = row_in_smem<T>(smem_row, x + base);
+  const long long t = target[r];
+  const bool valid = t != ignore && t >= 0 && t < cols;
+  float m = stage_row<T>(x + base, row, cols);
+  m = block_reduce(m, true, sh);  // its barriers also publish the staged row
+  float s = 0.f, sx = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float v = to_f<T>(row[c]) - m;
+    s += __expf(v);
+    sx += v;
+  }
+  s = block_reduce(s, false, sh);
+  sx = block_reduce(sx, false, sh);
+  const float ls = __logf(s);
+  if (threadIdx.x == 0) {
+    float l = 0.f;
+    if (valid) {
+      const float lp_t = to_f<T>(row[t]) - m - ls;
+      const float mean_lp = sx / cols - ls;
+      l = -((1.f - smooth) * lp_t + smooth * mean_lp);
+    }
+    row_loss[r] = l;
+  }
+  if (!dl) return;
+  const float scale = valid ? gscale / fmaxf(*n_valid, 1.f) : 0.f;
+  const float base_t = smooth / cols;
+  constexpr int VO = Vec16<TO>::N;
+  TO* out = dl + base;
+  const int head = head_elems(out, cols);
+  const int nvec = (cols - head) / VO;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    alignas(16) TO o[VO];
+#pragma unroll
+    for (int k = 0; k < VO; ++k) {
+      const int c = head + i * VO + k;
+      const float p = __expf(to_f<T>(row[c]) - m - ls);
+      o[k] = from_f<TO>((p - ((c == t ? 1.f - smooth : 0.f) + base_t)) * scale);
+    }
+    reinterpret_cast<uint4*>(out + head)[i] = *reinterpret_cast<const uint4*>(o);
+  }
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    if (c >= head && c < head + nvec * VO) continue;
+    const float p = __expf(to_f<T>(row[c]) - m - ls);
+    out[c] = from_f<TO>((p - ((c == t ? 1.f - smooth : 0.f) + base_t)) * scale);
+  }
+}
+
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256) softmax_fwd_smem_kernel(const T* __restrict__ x, TO* __restrict__ y, int cols, int log_mode) {
+  extern __shared__ __align__(16) unsigned char smem_row[];
+  __shared__ float sh[32];
+  const long long base = (long long)blockIdx.x * cols;
+  T* row = row_in_smem<T>(smem_row, x + base);
+  float m = stage_row<T>(x + base, row, cols);
+  m = block_reduce(m, true, sh);
+  float s = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) s += __expf(to_f<T>(row[c]) - m);
+  s = block_reduce(s, false, sh);
+  const float ls = __logf(s), inv = 1.f / s;
+  constexpr int VO = Vec16<TO>::N;
+  TO* out = y + base;
+  const int head = head_elems(out, cols);
+  const int nvec = (cols - head) / VO;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    alignas(16) TO o[VO];
+#pragma unroll
+    for (int k = 0; k < VO; ++k) {
+      const float v = to_f<T>(row[head + i * VO + k]) - m;
+      o[k] = from_f<TO>(log_mode ? v - ls : __expf(v) * inv);
+    }
+    reinterpret_cast<uint4*>(out + head)[i] = *reinterpret_cast<const uint4*>(o);
+  }
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    if (c >= head && c < head + nvec * VO) continue;
+    const float v = to_f<T>(row[c]) - m;
+    out[c] = from_f<TO>(log_mode ? v - ls : __expf(v) * inv);
+  }
+}
+
+constexpr int kMaxRowBytes = 200 * 1024;
+
+template <typename K>
+inline int allow_big_smem(K kernel, size_t bytes) {
+  if (bytes <= 48 * 1024) return 0;
+  return (int)cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxRowBytes);
+}
+
 }  // namespace
 
 extern "C" int b200_softmax_fwd(const void* x, int idt, void* y, int odt, long long rows, int cols, int log_mode,
                                 void* stream) {
   if (rows <= 0 || cols <= 0) return 0;
+  if (idt == odt && cols >= 1024 && (idt == B200_BF16 || idt == B200_F16 || idt == B200_F32)) {
+    const int es = idt == B200_F32 ? 4 : 2;
+    const size_t bytes = (size_t)cols * es + 16;  // + the row's 16-byte phase
+    if (bytes <= (size_t)kMaxRowBytes) {
+      int rc = 0;
+#define SM_FWD(T)                                                                                              \
+  do {                                                                                                         \
+    rc = allow_big_smem(softmax_fwd_smem_kernel<T, T>, bytes);                                                 \
+    if (!rc) softmax_fwd_smem_kernel<T, T><<<(unsigned)rows, 256, bytes, (cudaStream_t)stream>>>(              \
+        static_cast<const T*>(x), static_cast<T*>(y), cols, log_mode);                                         \
+  } while (0)
+      if (idt == B200_BF16) SM_FWD(__nv_bfloat16);
+      else if (idt == B200_F16) SM_FWD(__half);
+      else SM_FWD(float);
+#undef SM_FWD
+      return rc ? rc : (int)cudaGetLastError();
+    }
+  }
   softmax_fwd_kernel<<<(unsigned)rows, cols >= 256 ? 256 : (cols >= 64 ? 64 : 32), 0, (cudaStream_t)stream>>>(
       x, idt, y, odt, cols, log_mode);
   return (int)cudaGetLastError();
@@ -195,6 +356,23 @@ extern "C" int b200_softmax_xent(const void* logits, int dt, const long long* ta
   if (rows <= 0 || cols <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   count_valid_kernel<<<1, 256, 0, s>>>(target, rows, ignore, n_valid);
+  const int es = dt == B200_F32 ? 4 : 2;
+  const size_t bytes = (size_t)cols * es + 16;  // + the row's 16-byte phase
+  if (cols >= 1024 && (!dl || ddt == dt) && (dt == B200_BF16 || dt == B200_F16 || dt == B200_F32) &&
+      bytes <= (size_t)kMaxRowBytes) {
+    int rc = 0;
+#define SM_XENT(T)                                                                                                   \
+  do {                                                                                                               \
+    rc = allow_big_smem(softmax_xent_smem_kernel<T, T>, bytes);                                                      \
+    if (!rc) softmax_xent_smem_kernel<T, T><<<(unsigned)rows, 256, bytes, s>>>(                                      \
+        static_cast<const T*>(logits), target, cols, ignore, smooth, row_loss, n_valid, static_cast<T*>(dl), gscale); \
+  } while (0)
+    if (dt == B200_BF16) SM_XENT(__nv_bfloat16);
+    else if (dt == B200_F16) SM_XENT(__half);
+    else SM_XENT(float);
+#undef SM_XENT
+    return rc ? rc : (int)cudaGetLastError();
+  }
   softmax_xent_kernel<<<(unsigned)rows, 256, 0, s>>>(logits, dt, target, cols, ignore, smooth, row_loss, n_valid, dl, ddt,
                                                      gscale);
   return (int)cudaGetLastError();

@@ -354,3 +354,26 @@ def test_short_reductions_with_many_outputs():
     y = torch.randn(40000, 33)  # reduce the short inner dimension: outputs are not adjacent in memory -> other kernel
     assert_tensors_equal(dev(y).sum(1).cpu(), y.sum(1), prec=1e-4)
     assert_tensors_equal(dev(y.t().contiguous()).sum(0).cpu(), y.sum(1), prec=1e-4)
+
+
+@pytest.mark.parametrize("cols", [1030, 4096, 30522])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_softmax_and_cross_entropy_with_rows_cached_in_shared_memory(cols, dtype):
+    """Rows of 1024 columns and more are staged in shared memory (one read, 16-byte accesses); 1030 and 30522 columns
+    give rows that do not start on 16-byte boundaries."""
+    torch.manual_seed(0)
+    rows = 37
+    x = (torch.randn(rows, cols) * 3).to(dtype)
+    t = torch.randint(0, cols, (rows,))
+    t[3] = -100
+    xd, td = dev(x), dev(t)
+    prec = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    assert_tensors_equal(torch.softmax(xd, -1).float().cpu(), torch.softmax(x.float(), -1), prec=prec, use_MSE=True)
+    assert_tensors_equal(torch.log_softmax(xd, -1).float().cpu(), torch.log_softmax(x.float(), -1), prec=prec, use_MSE=True)
+    for smooth in (0.0, 0.1):
+        xr = x.float().clone().requires_grad_()
+        ref = F.cross_entropy(xr, t, label_smoothing=smooth)
+        ref.backward()
+        loss, grad = torch.ops.catch_b200.softmax_cross_entropy(xd, td, -100, smooth)  # (mean loss, d loss / d logits)
+        assert abs(loss.item() - ref.item()) < 1e-3 * abs(ref.item()), (loss.item(), ref.item())
+        assert_tensors_equal(grad.float().cpu(), xr.grad, prec=prec, use_MSE=True, msg=f"smooth {smooth}")
