@@ -17,6 +17,8 @@ from __future__ import annotations
 import operator
 from typing import Optional
 
+import os
+
 import torch
 import torch.fx as fx
 import torch.nn as nn
@@ -52,7 +54,7 @@ class _GradSink:
         return grad
 
 
-_SINKS_ENABLED = True
+_SINKS_ENABLED = os.environ.get("CATCH_B200_GRAD_SINKS", "1") != "0"
 _open_sinks = []
 
 

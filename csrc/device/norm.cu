@@ -566,17 +566,24 @@ bn_bwd_apply_fast_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
   }
 }
 
-inline int ew_grid_u(unsigned n) {
-  unsigned g = (n + 255) / 256;
-  if (g > 148 * 8) g = 148 * 8;
-  return g < 1 ? 1 : (int)g;
-}
-
 inline int red_grid(long long rows) {
   long long g = (rows + 63) / 64;
   if (g > 148 * 4) g = 148 * 4;
   if (g < 1) g = 1;
   return (int)g;
+}
+// Grid of a grid-stride apply kernel whose CTAs each rebuild the per-channel coefficients (from fp64 sums) before
+// they start: one resident wave, so that this prologue runs once per CTA slot instead of once per 256 x BN_U vectors
+// (small activations spent most of their time in it).
+template <typename K>
+inline int apply_grid_for(K kernel, size_t smem, unsigned nvec) {
+  int dev = 0, sms = 148, per_sm = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, smem) != cudaSuccess || per_sm < 1) per_sm = 2;
+  long long g = ((long long)nvec + 256 * BN_U - 1) / (256 * BN_U);
+  if (g > (long long)sms * per_sm) g = (long long)sms * per_sm;
+  return g < 1 ? 1 : (int)g;
 }
 // Grid of a column-reduction kernel: every CTA owns an equal slice of the rows, so the grid is exactly one wave of
 // resident CTAs (a grid of 4 per SM with only 3 resident ran a one-third-full second wave: 0.65 of the copy
@@ -742,7 +749,7 @@ static int bn_apply_launch(const void* x, int xdt, void* y, int ydt, long long r
     if (C % V == 0) {
       const unsigned nvec = (unsigned)(n / V);
       const size_t sm = sizeof(float) * 2 * C;
-      DISPATCH_FLOAT(xdt, T, (bn_apply_fast_kernel<T><<<ew_grid_u(nvec), 256, sm, s>>>(
+      DISPATCH_FLOAT(xdt, T, (bn_apply_fast_kernel<T><<<apply_grid_for(bn_apply_fast_kernel<T>, sm, nvec), 256, sm, s>>>(
                                  static_cast<const T*>(x), static_cast<T*>(y), nvec, C, mean, mdt, invstd, gamma, beta,
                                  pdt, static_cast<const T*>(res), act, V == 8 ? static_cast<uint8_t*>(relu_mask) : nullptr, fz)));
       *done = true;
@@ -848,7 +855,7 @@ extern "C" int b200_bn_backward_apply2(const void* dy, int dt, const void* x, in
     const int V = dt == B200_F32 ? 4 : 8;
     const unsigned nvec = (unsigned)(n / V);
     const size_t sm = sizeof(float) * 3 * C;
-    DISPATCH_FLOAT(dt, T, (bn_bwd_apply_fast_kernel<T><<<ew_grid_u(nvec), 256, sm, s>>>(
+    DISPATCH_FLOAT(dt, T, (bn_bwd_apply_fast_kernel<T><<<apply_grid_for(bn_bwd_apply_fast_kernel<T>, sm, nvec), 256, sm, s>>>(
                                static_cast<const T*>(dy), static_cast<const T*>(x), mean, mdt, invstd, gamma, pdt,
                                is_mask ? nullptr : static_cast<const T*>(relu_out), sums, rows, C, training,
                                static_cast<T*>(dx), nvec, static_cast<T*>(dres),
