@@ -71,8 +71,6 @@ struct ConvArgs {
   int coef_bytes;               // shared memory reserved for per-channel scale / bias (0 or 2048)
   int tma_store;                // epilogue stages 64-channel blocks in shared memory and stores them by TMA
   int epi_bufs;                 // staging buffers per epilogue warp (2 when shared memory allows: conversion overlaps the store)
-  int dbg;                      // timing experiments only (CATCH_B200_CONV_DBG; results are wrong): 1 no MMAs, 2 no activation
-                                // loads, 4 no output stores, 8 no epilogue work at all
   int* err;
 };
 
@@ -222,9 +220,8 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
         if (g.halo) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, g.err, ERR_TIMEOUT_EMPTY)) { failed = true; break; }
           // channel coordinate 0; the pixel origin may be negative (zero filled)
-          if (g.dbg & 2) mbar_arrive(&full_bar[stage]);
-          else mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)(g.halo_ndw * g.halo_col_bytes));
-          for (int j = 0; j < ((g.dbg & 2) ? 0 : g.halo_ndw); ++j)
+          mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)(g.halo_ndw * g.halo_col_bytes));
+          for (int j = 0; j < g.halo_ndw; ++j)
             tma_load_4d(stage0 + (size_t)stage * stage_bytes + (size_t)j * g.halo_col_bytes, &maps.a[1], &full_bar[stage], 0,
                         q0 + g.dw_min + j, p0 + g.dh_min, n0);
           if (++stage == g.stages) { stage = 0; phase ^= 1; }
@@ -234,11 +231,6 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
           const int tap = it / g.c_blocks, cb = it - tap * g.c_blocks;
           const B200ConvTap tp = g.taps[tap];
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, g.err, ERR_TIMEOUT_EMPTY)) { failed = true; break; }
-          if (g.dbg & 2) {
-            mbar_arrive(&full_bar[stage]);
-            if (++stage == g.stages) { stage = 0; phase ^= 1; }
-            continue;
-          }
           mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)stage_bytes);
           uint8_t* sa = stage0 + (size_t)stage * stage_bytes;
           tma_load_4d(sa, &maps.a[tp.map], &full_bar[stage], cb * g.cblk, q0 + tp.dw, p0 + tp.dh, n0);
@@ -279,7 +271,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
           if (!mbar_wait(&full_bar[stage], phase, g.err, ERR_TIMEOUT_FULL)) { failed = true; break; }
           tc_fence_after();
           const uint32_t tile0_16 = stage0_16 + (uint32_t)stage * stage_16;
-          for (int tap = 0; tap < ((g.dbg & 1) ? 0 : g.ntaps); ++tap) {
+          for (int tap = 0; tap < g.ntaps; ++tap) {
             const B200ConvTap tp = g.taps[tap];
             // column tile of this tap's dw, shifted down by (dh - dh_min) pixel rows of 1024 bytes
             const uint32_t a0_16 = tile0_16 + (uint32_t)(((tp.dw - g.dw_min) * g.halo_col_bytes + (tp.dh - g.dh_min) * 1024) >> 4);
@@ -297,8 +289,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
           tc_fence_after();
           const uint32_t sa_16 = stage0_16 + (uint32_t)stage * stage_16;
           const uint32_t sb_16 = g.b_res_bytes ? bres_16 + (uint32_t)it * bblk_16 : sa_16 + (CONV_A_BYTES >> 4);
-          if (g.dbg & 1) {
-          } else if (g.kind == 2)
+          if (g.kind == 2)
             umma_x4<2>(d_tmem, a_lo0 + sa_16, a_hi, 2, b_lo0 + sb_16, b_hi, b_step, g.idesc, it > 0 ? 1u : 0u);
           else
             umma_x4<0>(d_tmem, a_lo0 + sa_16, a_hi, 2, b_lo0 + sb_16, b_hi, b_step, g.idesc, it > 0 ? 1u : 0u);
@@ -408,8 +399,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
         }
       };
 
-      if (g.dbg & 8) {
-      } else if (g.tma_store) {
+      if (g.tma_store) {
         // not unrolled: the body is large and the epilogue warps share the instruction cache with the
         // producer and MMA roles
 #pragma unroll 1
@@ -420,7 +410,6 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
           tmem_ld32(t_addr + cb, ra);
           tmem_ld32(t_addr + cb + 32, rb);
           tmem_ld_wait();
-          if (g.dbg & 16) continue;  // timing experiment: tensor-memory reads only
           if (lane == 0) {  // the store that last used this buffer has read it
             if (g.epi_bufs == 2) tma_store_wait_read<1>();
             else tma_store_wait_read<0>();
@@ -435,27 +424,15 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
           for (int h = 0; h < 2; ++h) {
             float v[32];
             uint32_t pk[16];
-            if (g.dbg & 64) {  // timing experiment: no conversion
-#pragma unroll
-              for (int j = 0; j < 16; ++j) pk[j] = ra[j];
-            } else if (g.dbg & 128) {  // timing experiment: conversion without the epilogue arithmetic
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(ra[j]);
-              pack16(v, pk, g.out_dtype);
-            } else if (g.dbg & 256) {  // timing experiment: truncating pack on the integer pipe
-#pragma unroll
-              for (int j = 0; j < 16; ++j) pk[j] = __byte_perm(ra[2 * j], ra[2 * j + 1], 0x7632);
-            } else {
-              finish(ra, cb + 32 * h, v);
-              pack16(v, pk, g.out_dtype);
-            }
+            finish(ra, cb + 32 * h, v);
+            pack16(v, pk, g.out_dtype);
 #pragma unroll
             for (int k = 0; k < 4; ++k)
               *reinterpret_cast<uint4*>(srow + (((4 * h + k) ^ (lane & 7)) * 16)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
 #pragma unroll
             for (int j = 0; j < 32; ++j) ra[j] = rb[j];
           }
-          if (!(g.dbg & 32)) fence_proxy_async_smem();
+          fence_proxy_async_smem();
           __syncwarp();
           if (STATS) {
             // Column sums over the 32 staged pixels (the rounded values that were stored; pixels
@@ -486,7 +463,7 @@ conv_fprop_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__
             if (bi == 0) { st_s[0][0] += s0; st_s[0][1] += s1; st_q[0][0] += q0s; st_q[0][1] += q1s; }
             else { st_s[1][0] += s0; st_s[1][1] += s1; st_q[1][0] += q0s; st_q[1][1] += q1s; }
           }
-          if (lane == 0 && !(g.dbg & 4)) {
+          if (lane == 0) {
             // rows / channels outside the tensor are clipped by the store
             tma_store_4d(&maps.out, sbuf, co0 + cb, q0 + w_off, p0 + h_off, n0 + n_off);
             tma_store_commit();
@@ -827,11 +804,6 @@ extern "C" int b200_conv_fprop(const B200ConvParams* p_in, void* stream) {
   g.err = error_flag_ptr();
   if (!g.err) return (int)cudaErrorInvalidDevice;
   g.out_qscale = p->out_qscale;
-  static const int dbg = [] {
-    const char* e = std::getenv("CATCH_B200_CONV_DBG");
-    return e ? std::atoi(e) : 0;
-  }();
-  g.dbg = dbg;
   if (p->out_dtype == B200_I8 && !(p->out_qscale > 0.f)) return (int)cudaErrorInvalidValue;
   g.tma_store = (p->out_dtype != B200_F32 && p->out_dtype != B200_I8 && g.tile_n % 64 == 0 && p->Cout % 8 == 0) ? 1 : 0;
   g.coef_bytes = (p->scale || p->bias) ? 2048 : 0;

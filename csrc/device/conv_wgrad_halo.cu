@@ -40,7 +40,6 @@ struct WgradHaloArgs {
   int col_bytes;                  // bni * (bh + ndh - 1) * 1024: one activation column tile
   int stage_bytes;
   int sep_mma;                    // 1: one N = 64 MMA per (vertical tap, channel block) instead of one N = ndh * 64
-  int dbg;                        // timing experiments only (results are wrong): 1 skip MMAs, 2 skip loads, 4 skip epilogue
   uint32_t idesc;
   short wtap[4][4];               // [dw - dw_min][dh - dh_min] -> weight tap slot, -1 = no such tap
   float* dw_acc;
@@ -114,11 +113,6 @@ conv_wgrad_halo_kernel(const __grid_constant__ WgradHaloMaps maps, const __grid_
         const int p0 = ((ch / g.tiles_q) % g.tiles_p) * g.bh;
         const int n0 = (ch / (g.tiles_q * g.tiles_p)) * g.bni;
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, g.err, ERR_TIMEOUT_EMPTY)) { failed = true; break; }
-        if (g.dbg & 2) {
-          mbar_arrive(&full_bar[stage]);
-          if (++stage == g.stages) { stage = 0; phase ^= 1; }
-          continue;
-        }
         mbar_arrive_expect_tx(&full_bar[stage], tx);
         uint8_t* sa = smem + (size_t)stage * g.stage_bytes;
         tma_load_4d(sa, &maps.dy, &full_bar[stage], co0, q0, p0, n0);
@@ -142,7 +136,7 @@ conv_wgrad_halo_kernel(const __grid_constant__ WgradHaloMaps maps, const __grid_
         if (!mbar_wait(&full_bar[stage], phase, g.err, ERR_TIMEOUT_FULL)) { failed = true; break; }
         tc_fence_after();
         const uint32_t sa_16 = smem0_16 + (uint32_t)stage * stage_16;
-        for (int s = 0; s < ((g.dbg & 1) ? 0 : steps); ++s) {
+        for (int s = 0; s < steps; ++s) {
           const uint32_t acc = (ch > chunk_begin || s > 0) ? 1u : 0u;
           uint64_t ad;
           asm("mov.b64 %0, {%1, %2};" : "=l"(ad) : "r"(a_lo0 + sa_16 + (uint32_t)s * 128u), "r"(a_hi));
@@ -174,7 +168,7 @@ conv_wgrad_halo_kernel(const __grid_constant__ WgradHaloMaps maps, const __grid_
       // 32 output channels x 32 columns per tensor-map reduce-add; two staging buffers per warp so that the next
       // block is converted while the previous one is still being read by the copy engine
       uint8_t* sbuf0 = stage_out + (warp - 2) * 8192;
-      const int ncols = (g.dbg & 4) ? 0 : ncb * g.ndh * 64;
+      const int ncols = ncb * g.ndh * 64;
       int buf = 0;
       for (int c = 0; c < ncols; c += 32) {
         const int blk = c >> 6;
@@ -270,7 +264,6 @@ bool try_wgrad_halo(const B200ConvWgradParams* p, void* stream, int* rc) {
   if (g.stages > WH_MAX_STAGES) g.stages = WH_MAX_STAGES;
   if (g.stages < 2) return false;
   g.sep_mma = (mode & 3) == 2 ? 1 : 0;
-  g.dbg = mode >> 4;  // modes 16 + ... are timing experiments
 
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
