@@ -90,7 +90,7 @@ def write_ninja(verbose: bool = False) -> Path:
     py_inc = sysconfig.get_paths()["include"]
     cxx_inc = " ".join(f"-isystem {p}" for p in inc + [py_inc] + ([nccl_inc] if nccl_inc else []))
     cxx_flags = (
-        ("-O0 -g " if DEBUG else "-O2 ") + ("-fsanitize=address -fno-omit-frame-pointer " if ASAN else "") +
+        ("-O0 -g " if DEBUG else "-O2 -DNDEBUG ") + ("-fsanitize=address -fno-omit-frame-pointer " if ASAN else "") +
         "-std=c++17 -fPIC -fvisibility=hidden -Wall -Wno-unused-variable -Wno-unused-function "
         "-Wno-sign-compare -Wno-unknown-pragmas -D_GLIBCXX_USE_CXX11_ABI=1 -DTORCH_EXTENSION_NAME=_C "
         "-DTORCH_API_INCLUDE_EXTENSION_H"

@@ -16,6 +16,8 @@ void bind_aux(py::module& m) {
   m.def("_dump_start", &dump_start, py::arg("dir"), py::arg("enable") = true, py::arg("use_cpu") = false, py::arg("level") = 0);
   m.def("_dump_finish", &dump_finish);
   m.def("_dump_running", &dump_running);
+  m.def("_dump_gencase", &gencase_set, py::arg("level"), py::arg("dir") = "./gen_case");
+  m.def("_gencase_level", &gencase_level);
   // kernel selection knob for benchmarks and tests: see b200_conv_wgrad_halo_mode
   m.def("_conv_wgrad_halo_mode", [](int mode) { return b200_conv_wgrad_halo_mode(mode); }, py::arg("mode") = -1);
   m.def("_jit_can_fuse_on_b200", &jit::fusion_enabled);

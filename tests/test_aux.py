@@ -184,3 +184,50 @@ def test_delayed_scalar_returns_each_value_one_push_later():
     assert got[0] is None and got[1:] == [0.5, 1.5, 2.5, 3.5]
     assert r.flush() == 4.5 and r.flush() is None
     assert r.push(torch.tensor([2.0]).to("blackwell").bfloat16().sum()) is None and r.flush() == 2.0
+
+
+def test_kernel_case_generator_and_replay(tmp_path, capfd):
+    """Same flow as the reference's test/cnnl/test_dumptool.py:147-175: levels L1 / L2 write case files, L3 prints,
+    anything else raises; on top of that a written case can be replayed."""
+    import json
+
+    import pytest
+
+    a, b = torch.randn(2, 2, 6, 6), torch.randn(2, 2, 6, 6)
+    for level in ("L1", "L2"):
+        d = str(tmp_path / f"gen_case_{level}")
+        assert dumptool.dump_gencase(True, level, d) is True
+        (a.to(DEV) + b.to(DEV)).view(4, 36)
+        torch.nn.functional.conv2d(a.to(DEV).contiguous(memory_format=torch.channels_last), torch.randn(4, 2, 3, 3).to(DEV),
+                                   padding=1)
+        assert dumptool.dump_gencase(False) is False
+        assert os.path.isdir(d)
+        add_dir = os.path.join(d, "aten__add.Tensor")
+        cases = sorted(f for f in os.listdir(add_dir) if f.endswith(".json"))
+        assert cases
+        case = json.load(open(os.path.join(add_dir, cases[0])))
+        assert case["op"] == "aten::add.Tensor" and case["schema"].startswith("aten::add.Tensor(Tensor self")
+        assert case["args"][0]["shape"] == [2, 2, 6, 6] and case["args"][0]["dtype"] == "Float"
+        assert case["args"][2]["name"] == "alpha" and case["args"][2]["value"] == 1
+        assert ("data" in case["args"][0]) == (level == "L2")
+        dev, cpu, errs = dumptool.replay_case(os.path.join(add_dir, cases[0]))
+        assert dev[0].device.type == DEV and errs[0] < 1e-6
+        if level == "L2":  # the recorded bytes are the operands
+            assert torch.equal(cpu[0], a + b)
+        conv_dirs = [x for x in os.listdir(d) if "conv" in x]
+        assert conv_dirs
+        cdir = os.path.join(d, sorted(conv_dirs)[0])
+        ccase = json.load(open(os.path.join(cdir, sorted(f for f in os.listdir(cdir) if f.endswith(".json"))[0])))
+        assert ccase["args"][0]["format"] == "channels_last"
+    # nothing is written once the generator is off
+    n = sum(len(fs) for _, _, fs in os.walk(str(tmp_path)))
+    a.to(DEV) + b.to(DEV)
+    assert sum(len(fs) for _, _, fs in os.walk(str(tmp_path))) == n
+    capfd.readouterr()
+    assert dumptool.dump_gencase(True, "L3", str(tmp_path / "none"))
+    a.to(DEV) + b.to(DEV)
+    dumptool.dump_gencase(False)
+    assert "[gen_case]" in capfd.readouterr().err and not os.path.exists(str(tmp_path / "none"))
+    for level in ("L0", "l1", "L4"):
+        with pytest.raises(ValueError):
+            dumptool.dump_gencase(True, level)
