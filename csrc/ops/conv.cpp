@@ -40,11 +40,25 @@ std::tuple<Tensor, Tensor, Tensor> conv_backward_cpu(const Tensor& grad, const T
   return {mv(std::get<0>(r)), mv(std::get<1>(r)), mv(std::get<2>(r))};
 }
 
+// Memory format of a convolution result, by the stock rule: channels-last when the input or the weight is, else
+// contiguous.  The kernels work channels-last, so a script that keeps everything in the default format pays one
+// transposing copy per result; in exchange view() on the result behaves as it does on other devices.
+bool wants_channels_last(const Tensor& input, const Tensor& weight) {
+  return input.dim() == 4 && (input.suggest_memory_format() == at::MemoryFormat::ChannelsLast ||
+                              weight.suggest_memory_format() == at::MemoryFormat::ChannelsLast);
+}
+Tensor in_format(const Tensor& t, bool channels_last) {
+  if (!t.defined() || t.dim() != 4 || t.numel() == 0) return t;
+  return channels_last ? t.contiguous(at::MemoryFormat::ChannelsLast) : t.contiguous();
+}
+
 Tensor convolution_overrideable(const Tensor& input, const Tensor& weight, const std::optional<Tensor>& bias,
                                 at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation,
                                 bool transposed, at::IntArrayRef output_padding, int64_t groups) {
   return B200_DISPATCH("convolution",
-                       conv_forward_device(input, weight, bias, stride, padding, dilation, transposed, output_padding, groups),
+                       in_format(conv_forward_device(input, weight, bias, stride, padding, dilation, transposed, output_padding,
+                                                     groups),
+                                 wants_channels_last(input, weight)),
                        conv_cpu(input, weight, bias, stride, padding, dilation, transposed, output_padding, groups));
 }
 
@@ -52,9 +66,13 @@ std::tuple<Tensor, Tensor, Tensor> convolution_backward_overrideable(
     const Tensor& grad, const Tensor& input, const Tensor& weight, at::IntArrayRef stride, at::IntArrayRef padding,
     at::IntArrayRef dilation, bool transposed, at::IntArrayRef output_padding, int64_t groups,
     std::array<bool, 3> mask) {
+  auto device = [&]() {
+    auto r = conv_backward_device(grad, input, weight, stride, padding, dilation, transposed, output_padding, groups, mask);
+    std::get<0>(r) = in_format(std::get<0>(r), wants_channels_last(input, weight));
+    return r;
+  };
   return B200_DISPATCH(
-      "convolution_backward",
-      conv_backward_device(grad, input, weight, stride, padding, dilation, transposed, output_padding, groups, mask),
+      "convolution_backward", device(),
       conv_backward_cpu(grad, input, weight, stride, padding, dilation, transposed, output_padding, groups, mask));
 }
 

@@ -262,9 +262,19 @@ Tensor hardtanh_backward(const Tensor& grad, const Tensor& self, const Scalar& l
   run(iter, EW_HARDTANH_BWD, lo.toDouble(), hi.toDouble());
   return iter.output();
 }
-Tensor elu(const Tensor& a, const Scalar& alpha, const Scalar& scale, const Scalar& input_scale) {
-  TORCH_CHECK(scale.toDouble() == 1.0 && input_scale.toDouble() == 1.0, "b200 elu: only scale = input_scale = 1");
-  return unary(a, EW_ELU, true, alpha.toDouble());
+Tensor elu_any(const Tensor& a, const Scalar& alpha, const Scalar& scale, const Scalar& input_scale) {
+  if (scale.toDouble() == 1.0 && input_scale.toDouble() == 1.0) return unary(a, EW_ELU, true, alpha.toDouble());
+  // selu / celu: scale * (x > 0 ? x : alpha * (exp(x * input_scale) - 1)), from element-wise device kernels, in fp32
+  TORCH_CHECK(a.scalar_type() == at::kFloat || a.scalar_type() == at::kBFloat16 || a.scalar_type() == at::kHalf,
+              "b200 elu: unsupported dtype ", a.scalar_type());
+  Tensor x = a.scalar_type() == at::kFloat ? a : a.to(at::kFloat);
+  Tensor neg = at::sub(at::exp(at::mul(x, input_scale)), Scalar(1.0)).mul_(Scalar(alpha.toDouble() * scale.toDouble()));
+  Tensor r = at::where(at::gt(x, Scalar(0.0)), at::mul(x, scale), neg);
+  return r.scalar_type() == a.scalar_type() ? r : r.to(a.scalar_type());
+}
+Tensor& elu_(Tensor& a, const Scalar& alpha, const Scalar& scale, const Scalar& input_scale) {
+  a.copy_(elu_any(a, alpha, scale, input_scale));
+  return a;
 }
 Tensor sigmoid_backward(const Tensor& grad, const Tensor& out) { return binary(grad, out, EW_SIGMOID_BWD, Kind::Plain); }
 Tensor tanh_backward(const Tensor& grad, const Tensor& out) { return binary(grad, out, EW_TANH_BWD, Kind::Plain); }
@@ -494,7 +504,8 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("hardtanh", TORCH_FN(hardtanh));
   m.impl("hardtanh_", TORCH_FN(hardtanh_));
   m.impl("hardtanh_backward", TORCH_FN(hardtanh_backward));
-  m.impl("elu", TORCH_FN(elu));
+  m.impl("elu", TORCH_FN(elu_any));
+  m.impl("elu_", TORCH_FN(elu_));
   m.impl("sigmoid_backward", TORCH_FN(sigmoid_backward));
   m.impl("tanh_backward", TORCH_FN(tanh_backward));
   m.impl("silu_backward", TORCH_FN(silu_backward));

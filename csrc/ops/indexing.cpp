@@ -317,8 +317,8 @@ std::tuple<Tensor, Tensor> sort_rows_device(const Tensor& self, int64_t dim, boo
                                        values.data_ptr(), i64ptr(indices), ws.get(), scope.stream()));
     }
   }
-  values = values.movedim(-1, dim);
-  indices = indices.movedim(-1, dim);
+  values = values.movedim(-1, dim).contiguous();  // contiguous results, as from the stock kernels
+  indices = indices.movedim(-1, dim).contiguous();
   if (self.dim() == 0) return {values.squeeze(0), indices.squeeze(0)};
   return {values, indices};
 }

@@ -65,7 +65,7 @@ Tensor index_select_device(const Tensor& self, int64_t dim, const Tensor& index)
   const int64_t row = n_src ? x.numel() / n_src : 0;
   B200_KERNEL_CHECK(b200_index_select_rows(x.data_ptr(), (int)x.element_size(), i64ptr(idx), idx.numel(), row, n_src,
                                            out.data_ptr(), scope.stream()));
-  return out.movedim(0, dim);
+  return out.movedim(0, dim).contiguous();  // a contiguous result, as from the stock kernel
 }
 Tensor k_index_select(const Tensor& self, int64_t dim, const Tensor& index) {
   return B200_DISPATCH("index_select", index_select_device(self, dim, index), B200_CPU(index_select, self, dim, index));

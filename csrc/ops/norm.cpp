@@ -47,6 +47,15 @@ Tensor like_rows(const RowsView& v, const Tensor& x, at::ScalarType dt) {
   return at::empty_strided(v.t.sizes(), v.t.strides(), x.options().dtype(dt));
 }
 
+// Results follow the memory format of the input, as the stock kernels' do: channels-last inputs keep the layout
+// the kernels work in, anything else gets a contiguous result (composites such as group_norm call view() on it).
+Tensor in_format_of(const Tensor& t, const Tensor& like) {
+  if (!t.defined() || t.numel() == 0) return t;
+  if (like.dim() == 4 && like.suggest_memory_format() == at::MemoryFormat::ChannelsLast) return t;
+  if (like.dim() == 5 && like.suggest_memory_format() == at::MemoryFormat::ChannelsLast3d) return t;
+  return t.contiguous();
+}
+
 bool bn_dtype_ok(at::ScalarType t) { return t == at::kFloat || t == at::kBFloat16 || t == at::kHalf; }
 
 const void* opt_ptr(const std::optional<Tensor>& t, Tensor& keep) {
@@ -113,7 +122,7 @@ std::tuple<Tensor, Tensor, Tensor> batch_norm_device(const Tensor& input, const 
                                     to_b200_dtype(rm.scalar_type()), invstd.data_ptr<float>(), gamma, beta, pdt, nullptr,
                                     0, 0, scope.stream()));
   }
-  return {out, save_mean, save_invstd};
+  return {in_format_of(out, input), save_mean, save_invstd};
 }
 
 std::tuple<Tensor, Tensor, Tensor> k_native_batch_norm(const Tensor& input, const std::optional<Tensor>& weight,
@@ -201,7 +210,7 @@ std::tuple<Tensor, Tensor, Tensor> batch_norm_backward_device(
     if (dgamma.defined()) dgamma = dgamma.to(weight->scalar_type());
     if (dbeta.defined()) dbeta = dbeta.to(weight->scalar_type());
   }
-  return {dx, dgamma, dbeta};
+  return {in_format_of(dx, input), dgamma, dbeta};
 }
 
 std::tuple<Tensor, Tensor, Tensor> k_native_batch_norm_backward(

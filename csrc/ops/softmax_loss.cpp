@@ -21,7 +21,7 @@ Tensor rows_last(const Tensor& x, int64_t dim) {
 }
 Tensor restore(const Tensor& y, int64_t dim, int64_t ndim) {
   if (dim == ndim - 1) return y;
-  return y.transpose(dim, -1);
+  return y.transpose(dim, -1).contiguous();  // a contiguous result, as from the stock kernels (callers may view() it)
 }
 
 Tensor softmax_impl(const Tensor& self, int64_t dim, bool half_to_float, int log_mode) {
