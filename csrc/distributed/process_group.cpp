@@ -1037,9 +1037,89 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupB200::barrier(const c10d::BarrierOpti
 }
 
 // ---- fused DDP path -------------------------------------------------------------------------
+// The bucket kernel's steps on the host, for ranks that talk through the Store (host simulation): (cast the local
+// fp32 gradients to the exchange dtype and clear them) -> sum over ranks in fp32 -> scale -> optimizer update of this
+// rank's shard of the parameters, with the same arithmetic as opt_update() in the device code -> every rank receives
+// every shard (fp32 and the optional 16-bit copy) -> gradients cleared.  Optimizer state exists for the own shard only.
+void ProcessGroupB200::hostsim_fused_step(const at::Tensor& grads, const at::Tensor& params, const at::Tensor& state1,
+                                          const at::Tensor& state2, int64_t kind, double lr, double momentum, double dampening,
+                                          double weight_decay, double beta1, double beta2, double eps, int64_t step, bool nesterov,
+                                          bool first_step, double scale, const std::optional<at::Tensor>& lowp,
+                                          const std::optional<at::Tensor>& cast_src, bool zero_grads, int64_t shard) {
+  const int64_t n = grads.numel();
+  const bool has_src = cast_src.has_value() && cast_src->defined();
+  at::Tensor mine;
+  if (has_src) {
+    TORCH_CHECK(cast_src->scalar_type() == at::kFloat && cast_src->numel() >= n && grads.scalar_type() != at::kFloat,
+                "fused_allreduce_step: cast_src must be fp32 and the exchange dtype 16-bit");
+    mine = cast_src->narrow(0, 0, n).to(grads.scalar_type());  // rounded once, as in the exchange region
+    cast_src->zero_();
+  } else {
+    mine = grads;
+  }
+  auto all = store_exchange(to_bytes(mine), true, 0);
+  at::Tensor total = at::zeros({n}, at::TensorOptions().dtype(at::kFloat));
+  for (auto& b : all) total.add_(from_bytes(b, mine).to(at::kFloat));
+  const float* g = total.data_ptr<float>();
+  const int64_t begin = std::min<int64_t>(n, (int64_t)rank_ * shard), end = std::min<int64_t>(n, begin + shard);
+  // params / state live in host memory under host simulation
+  at::Tensor pc = params.cpu().contiguous();
+  float* w = pc.data_ptr<float>();
+  at::Tensor s1 = state1.cpu().contiguous(), s2 = state2.defined() && state2.numel() ? state2.cpu().contiguous() : at::Tensor();
+  float* m1 = s1.data_ptr<float>();
+  float* m2 = s2.defined() ? s2.data_ptr<float>() : nullptr;
+  const float flr = (float)lr, fmom = (float)momentum, fdamp = (float)dampening, fwd = (float)weight_decay, fb1 = (float)beta1,
+              fb2 = (float)beta2, feps = (float)eps, fscale = (float)scale;
+  const float bc1 = kind == 1 ? (float)(1.0 - std::pow(beta1, (double)step)) : 1.f;
+  const float bc2_sqrt = kind == 1 ? (float)std::sqrt(1.0 - std::pow(beta2, (double)step)) : 1.f;
+  for (int64_t i = begin; i < end; ++i) {
+    const int64_t s = i - begin;
+    float d = g[i] * fscale, wk = w[i];
+    if (kind == 0) {
+      d += fwd * wk;
+      if (fmom != 0.f) {
+        const float b = first_step ? d : fmom * m1[s] + (1.f - fdamp) * d;
+        m1[s] = b;
+        d = nesterov ? d + fmom * b : b;
+      }
+      w[i] = wk - flr * d;
+    } else {
+      TORCH_CHECK(m2 != nullptr, "fused_allreduce_step: AdamW needs the second-moment state");
+      wk *= 1.f - flr * fwd;
+      const float a = fb1 * m1[s] + (1.f - fb1) * d;
+      const float v = fb2 * m2[s] + (1.f - fb2) * d * d;
+      m1[s] = a;
+      m2[s] = v;
+      w[i] = wk - (flr / bc1) * (a / (std::sqrt(v) / bc2_sqrt + feps));
+    }
+  }
+  state1.copy_(s1);
+  if (s2.defined()) state2.copy_(s2);
+  // all-gather of the updated shards (every rank sends `shard` elements; the last one may be partly padding)
+  at::Tensor out_shard = at::zeros({shard}, at::TensorOptions().dtype(at::kFloat));
+  if (end > begin) out_shard.narrow(0, 0, end - begin).copy_(pc.narrow(0, begin, end - begin));
+  auto shards = store_exchange(to_bytes(out_shard), true, 0);
+  for (int r = 0; r < size_; ++r) {
+    const int64_t b0 = std::min<int64_t>(n, (int64_t)r * shard), e0 = std::min<int64_t>(n, b0 + shard);
+    if (e0 > b0) pc.narrow(0, b0, e0 - b0).copy_(from_bytes(shards[r], out_shard).narrow(0, 0, e0 - b0));
+  }
+  params.copy_(pc);
+  if (lowp.has_value() && lowp->defined()) {
+    TORCH_CHECK(lowp->numel() == n, "fused_allreduce_step: the 16-bit parameter copy must match the parameters");
+    lowp->copy_(pc);
+  }
+  if (zero_grads && !has_src) grads.zero_();
+}
+
 at::Tensor ProcessGroupB200::symm_empty(int64_t numel, at::ScalarType dtype) {
   ensure_arena(device_ >= 0 ? device_ : current_device());
-  TORCH_CHECK(!hostsim() && arena_, "symm_empty needs the CUDA backend");
+  if (hostsim()) {
+    // no peer mapping under host simulation (messages travel through the Store): an ordinary tensor, padded like
+    // the real one so that every rank's shard fits
+    at::Tensor t = at::empty({numel + 16 * size_}, at::TensorOptions().dtype(dtype).device(make_device(device_)));
+    return t.narrow(0, 0, numel);
+  }
+  TORCH_CHECK(arena_, "symm_empty needs an initialised arena");
   const size_t bytes = static_cast<size_t>(numel) * c10::elementSize(dtype);
   const size_t off = arena_->user_alloc(bytes + 16 * size_);  // room for shard padding
   void* ptr = arena_->local() + off;
@@ -1061,10 +1141,17 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupB200::fused_allreduce_step(
     double lr, double momentum, double dampening, double weight_decay, double beta1, double beta2, double eps,
     int64_t step, bool nesterov, bool first_step, double scale, const std::optional<at::Tensor>& lowp,
     const std::optional<at::Tensor>& cast_src, bool zero_grads) {
-  TORCH_CHECK(!hostsim() && arena_, "fused_allreduce_step needs the CUDA backend");
   TORCH_CHECK(params.scalar_type() == at::kFloat && grads.numel() == params.numel(), "fused_allreduce_step: params must be fp32 and match grads");
   const int64_t shard = shard_elems(grads.numel(), grads.scalar_type());
   TORCH_CHECK(state1.scalar_type() == at::kFloat && state1.numel() >= shard, "fused_allreduce_step: state shard too small");
+  if (hostsim()) {
+    ensure_arena(grads.device().index());
+    return hostsim_collective(c10d::OpType::ALLREDUCE, {grads, params, state1}, [&] {
+      hostsim_fused_step(grads, params, state1, state2, kind, lr, momentum, dampening, weight_decay, beta1, beta2, eps, step, nesterov,
+                         first_step, scale, lowp, cast_src, zero_grads, shard);
+    });
+  }
+  TORCH_CHECK(arena_, "fused_allreduce_step needs an initialised arena");
   const size_t goff = arena_->offset_of(grads.data_ptr()), poff = arena_->offset_of(params.data_ptr());
   B200FusedOptArgs o;
   std::memset(&o, 0, sizeof(o));

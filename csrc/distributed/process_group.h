@@ -130,6 +130,11 @@ class ProcessGroupB200 : public c10d::Backend {
   std::vector<std::vector<uint8_t>> store_exchange(const std::vector<uint8_t>& mine, bool everyone_sends, int root);
   c10::intrusive_ptr<c10d::Work> hostsim_collective(c10d::OpType op, std::vector<at::Tensor> outs,
                                                     std::function<void()> fn);
+  void hostsim_fused_step(const at::Tensor& grads, const at::Tensor& params, const at::Tensor& state1, const at::Tensor& state2,
+                          int64_t kind, double lr, double momentum, double dampening, double weight_decay, double beta1, double beta2,
+                          double eps, int64_t step, bool nesterov, bool first_step, double scale,
+                          const std::optional<at::Tensor>& lowp, const std::optional<at::Tensor>& cast_src, bool zero_grads,
+                          int64_t shard);
 
   c10::intrusive_ptr<c10d::Store> store_;
   std::chrono::milliseconds timeout_;

@@ -159,3 +159,136 @@ def _heartbeat(rank, world):
 
 def test_watchdog_reports_a_rank_that_stopped_heartbeating():
     run_ranks(_heartbeat, world=2, env={"CATCH_B200_HEARTBEAT_MS": "200", "CATCH_B200_HEARTBEAT_TIMEOUT_MS": "1500"})
+
+
+# ---- FusedDataParallel over several ranks (the bucket step runs on the host under host simulation) ----------
+def _fdp_net():
+    torch.manual_seed(11)
+    return torch.nn.Sequential(torch.nn.Conv2d(3, 8, 3, padding=1), torch.nn.ReLU(), torch.nn.Flatten(),
+                               torch.nn.Linear(8 * 6 * 6, 32), torch.nn.Tanh(), torch.nn.Linear(32, 5))
+
+
+def _fdp_data(steps, world, per_rank=4):
+    g = torch.Generator().manual_seed(12)
+    return [(torch.randn(world * per_rank, 3, 6, 6, generator=g), torch.randint(0, 5, (world * per_rank,), generator=g))
+            for _ in range(steps)]
+
+
+def _fdp(rank, world, kind, grad_dtype):
+    import copy
+
+    from catch_b200.parallel import FusedDataParallel
+
+    _init(rank, world)
+    ref = _fdp_net()
+    net = copy.deepcopy(ref).to(DEV)
+    if rank == 1:  # the wrapper has to take rank 0's parameters
+        with torch.no_grad():
+            for p in net.parameters():
+                p.add_(1.0)
+    hp = dict(lr=0.05, momentum=0.9, weight_decay=1e-4) if kind == "sgd" else dict(lr=1e-2, weight_decay=0.01)
+    fdp = FusedDataParallel(net, kind, bucket_mb=0.0005, grad_dtype=grad_dtype, **hp)
+    assert len(fdp.buckets) >= 3
+    opt = torch.optim.SGD(ref.parameters(), **hp) if kind == "sgd" else torch.optim.AdamW(ref.parameters(), **hp)
+    data = _fdp_data(5, world)
+    per = data[0][0].shape[0] // world
+    loss_fn = torch.nn.CrossEntropyLoss()
+    for it, (x, t) in enumerate(data[:4]):
+        opt.zero_grad()
+        loss_fn(ref(x), t).backward()          # the whole batch on one process
+        opt.step()
+        xs, ts = x[rank * per:(rank + 1) * per].to(DEV), t[rank * per:(rank + 1) * per].to(DEV)
+        if it == 2:                            # gradient accumulation: two half micro-batches, the first without exchange
+            h = per // 2
+            with fdp.no_sync():
+                (loss_fn(fdp(xs[:h]), ts[:h]) * 0.5).backward()
+            (loss_fn(fdp(xs[h:]), ts[h:]) * 0.5).backward()
+        else:
+            loss_fn(fdp(xs), ts).backward()
+        fdp.step()
+    tol = 2e-5 if grad_dtype == torch.float32 else 2e-2
+    for (n, p), q in zip(ref.named_parameters(), fdp.module.parameters()):
+        assert (p.detach() - q.detach().cpu()).abs().max().item() < tol * max(1.0, p.abs().max().item()), (n, kind, grad_dtype)
+        if fdp.lowp_dtype is not None:       # the 16-bit copies follow the masters on every rank
+            assert torch.equal(q._b200_lowp.cpu(), q.detach().to(fdp.lowp_dtype).cpu()), n
+    for bk in fdp.buckets:
+        assert float(bk.grads.abs().max()) == 0.0
+    # the sharded optimizer state gathers into the stock layout, and a stock optimizer continues from it
+    sd = fdp.optimizer_state_dict()
+    if grad_dtype == torch.float32:
+        resumed = _fdp_net()
+        resumed.load_state_dict({k: v.cpu() for k, v in fdp.module.state_dict().items()})
+        opt2 = torch.optim.SGD(resumed.parameters(), **hp) if kind == "sgd" else torch.optim.AdamW(resumed.parameters(), **hp)
+        opt2.load_state_dict(sd)
+        x, t = data[4]
+        for m, o in ((ref, opt), (resumed, opt2)):
+            o.zero_grad(); loss_fn(m(x), t).backward(); o.step()
+        for p, q in zip(ref.parameters(), resumed.parameters()):
+            assert (p - q).abs().max().item() < 5e-5 * max(1.0, p.abs().max().item())
+        # ... and loads back into a wrapper (each rank keeps its own shard)
+        fdp.load_optimizer_state_dict(opt.state_dict())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _fdp_sgd(rank, world):
+    _fdp(rank, world, "sgd", torch.float32)
+
+
+def _fdp_adamw(rank, world):
+    _fdp(rank, world, "adamw", torch.float32)
+
+
+def _fdp_sgd_bf16(rank, world):
+    _fdp(rank, world, "sgd", torch.bfloat16)
+
+
+def test_fused_data_parallel_matches_single_process():
+    """Two and three ranks (an odd world size exercises the shard padding), SGD and AdamW, fp32 and 16-bit exchange."""
+    run_ranks(_fdp_sgd, world=2)
+    run_ranks(_fdp_adamw, world=3)
+    run_ranks(_fdp_sgd_bf16, world=2)
+
+
+def _fdp_unused(rank, world):
+    from catch_b200.parallel import FusedDataParallel
+
+    class Two(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = torch.nn.Linear(16, 16)
+            self.unused = torch.nn.Linear(16, 16)
+            self.b = torch.nn.Linear(16, 4)
+
+        def forward(self, x):
+            return self.b(torch.tanh(self.a(x)))
+
+    _init(rank, world)
+    torch.manual_seed(0)
+    net = Two()
+    before = {k: v.clone() for k, v in net.state_dict().items()}
+    fdp = FusedDataParallel(net.to(DEV), "sgd", lr=0.1, bucket_mb=0.0005, lowp_dtype=None)
+    order = []
+    launch = fdp._launch
+    fdp._launch = lambda b: (order.append(b.index), launch(b))[1]
+    g = torch.Generator().manual_seed(rank)
+    fdp(torch.randn(4, 16, generator=g).to(DEV)).sum().backward()
+    fdp.step()
+    # every rank launches every bucket, in bucket order (ranks pair launches by sequence number)
+    assert order == sorted(order) and len(order) == len(fdp.buckets), order
+    after = {k: v.cpu() for k, v in fdp.module.state_dict().items()}
+    assert torch.equal(after["unused.weight"], before["unused.weight"])
+    assert not torch.equal(after["a.weight"], before["a.weight"])
+    # all ranks hold the same parameters afterwards
+    flat = torch.cat([v.flatten() for v in after.values()]).to(DEV)
+    both = [torch.empty_like(flat) for _ in range(world)]
+    dist.all_gather(both, flat)
+    assert all(torch.equal(both[0].cpu(), b.cpu()) for b in both[1:])
+    fdp(torch.randn(4, 16).to(DEV)).sum().backward()
+    with pytest.raises(RuntimeError, match="no_sync"):
+        fdp(torch.randn(4, 16).to(DEV)).sum().backward()
+    dist.destroy_process_group()
+
+
+def test_fused_data_parallel_unused_parameters_and_second_backward():
+    run_ranks(_fdp_unused, world=2)
