@@ -595,6 +595,30 @@ std::tuple<at::Tensor, at::Tensor> conv_backward_fp32w_device(const at::Tensor& 
                                                               const std::optional<at::Tensor>& accum,
                                                               const std::optional<at::Tensor>& dx_add) {
   const int64_t ones[2] = {1, 1};
+  if (use_cpu_path()) {
+    // Host path (host simulation, force-CPU mode): the same results from the stock convolution gradient in fp32.
+    const int64_t zeros[2] = {0, 0};
+    std::vector<int64_t> no_bias;
+    auto r = at::convolution_backward(grad.to(at::kFloat), input.to(at::kFloat), weight.to(at::kFloat), at::OptionalIntArrayRef(), stride,
+                                      padding, at::IntArrayRef(ones, 2), false, at::IntArrayRef(zeros, 2), 1,
+                                      {need_dx, need_dw, false});
+    at::Tensor dx, dw;
+    if (need_dx) {
+      dx = std::get<0>(r);
+      if (dx_add.has_value() && dx_add->defined()) dx = dx + dx_add->to(at::kFloat);
+      dx = dx.to(input.scalar_type()).contiguous(at::MemoryFormat::ChannelsLast);
+    }
+    if (need_dw) {
+      dw = std::get<1>(r);
+      if (accum.has_value() && accum->defined()) {  // flat fp32 in the memory order [K][R][S][C]
+        accum->view({dw.size(0), dw.size(2), dw.size(3), dw.size(1)}).add_(dw.permute({0, 2, 3, 1}));
+        dw = at::Tensor();
+      } else {
+        dw = dw.contiguous(at::MemoryFormat::ChannelsLast);
+      }
+    }
+    return {dx, dw};
+  }
   check_supported(input, weight, stride, padding, at::IntArrayRef(ones, 2), false, 1);
   ConvGeom g = geom(input, weight, stride, padding);
   at::Tensor dx, dw;
@@ -620,6 +644,13 @@ std::tuple<at::Tensor, at::Tensor> conv_backward_fp32w_device(const at::Tensor& 
 std::tuple<at::Tensor, at::Tensor> conv_stats_device(const at::Tensor& input, const at::Tensor& weight,
                                                      at::IntArrayRef stride, at::IntArrayRef padding) {
   const int64_t ones[2] = {1, 1};
+  if (use_cpu_path()) {
+    // Host path: the stock convolution, then the sums of the (rounded) result as the epilogue would have produced them
+    at::Tensor y = at::conv2d(input, weight, std::nullopt, stride, padding).contiguous(at::MemoryFormat::ChannelsLast);
+    at::Tensor yd = y.to(at::kDouble);
+    const std::vector<int64_t> rdims{0, 2, 3};
+    return {y, at::cat({yd.sum(rdims), (yd * yd).sum(rdims)})};
+  }
   check_supported(input, weight, stride, padding, at::IntArrayRef(ones, 2), false, 1);
   TORCH_CHECK(input.scalar_type() != at::kFloat, "conv2d_stats: 16-bit activations only");
   TORCH_CHECK(input.size(1) == weight.size(1), "conv: channel mismatch");

@@ -408,7 +408,29 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> batch_norm_act_backwa
     const at::Tensor& grad_out, const at::Tensor& out, const at::Tensor& input, const std::optional<at::Tensor>& weight,
     const std::optional<at::Tensor>& running_mean, const at::Tensor& save_mean, const at::Tensor& save_invstd, bool training,
     int64_t act, bool has_residual) {
-  TORCH_CHECK(!use_cpu_path() && is_b200(input), "batch_norm_act_backward runs on the device only");
+  if (use_cpu_path()) {
+    // Host path (host simulation, force-CPU mode): the same gradient from ordinary tensor operations.  The forward's
+    // host path returns an empty mask, so `out` is the forward output here.
+    TORCH_CHECK(out.scalar_type() != at::kByte, "batch_norm_act_backward (host path): expects the forward output, not a bit mask");
+    TORCH_CHECK(save_invstd.numel() == input.size(1), "batch_norm_act_backward (host path): needs the saved inverse standard deviation");
+    std::vector<int64_t> bshape(input.dim(), 1), rdims;
+    bshape[1] = input.size(1);
+    for (int64_t d = 0; d < input.dim(); ++d)
+      if (d != 1) rdims.push_back(d);
+    at::Tensor g = grad_out.to(at::kFloat);
+    if (act == 1) g = g * out.gt(0).to(at::kFloat);
+    at::Tensor dres = has_residual ? g.to(input.scalar_type()) : at::Tensor();
+    const at::Tensor mean = training ? save_mean : *running_mean;
+    at::Tensor invstd = save_invstd.to(at::kFloat).view(bshape);
+    at::Tensor xhat = (input.to(at::kFloat) - mean.to(at::kFloat).view(bshape)) * invstd;
+    at::Tensor dbeta = g.sum(rdims), dgamma = (g * xhat).sum(rdims);
+    at::Tensor scale = invstd;
+    if (weight.has_value() && weight->defined()) scale = scale * weight->to(at::kFloat).view(bshape);
+    const double m = (double)(input.numel() / std::max<int64_t>(1, input.size(1)));
+    at::Tensor dx = training ? scale * (g - dbeta.view(bshape) / m - xhat * (dgamma.view(bshape) / m)) : scale * g;
+    return {dx.to(input.scalar_type()), dgamma, dbeta, dres};
+  }
+  TORCH_CHECK(is_b200(input), "batch_norm_act_backward: the input must be on the device");
   OpScope scope("batch_norm_act_backward", input);
   RowsView xv = rows_view(input);
   const int C = (int)xv.C;

@@ -292,3 +292,54 @@ def _fdp_unused(rank, world):
 
 def test_fused_data_parallel_unused_parameters_and_second_backward():
     run_ranks(_fdp_unused, world=2)
+
+
+def _fdp_fused_convnet(rank, world):
+    """The fused convolution / batch-norm modules inside FusedDataParallel: weight gradients added straight into the
+    buckets, 16-bit weight copies written by the bucket step, gradient sinks.  Both ranks see the same batch, so the
+    averaged gradients equal those of one process and the runs can be compared step by step."""
+    import copy
+
+    import torchvision
+
+    from catch_b200 import fusion
+    from catch_b200.fusion import StatsConv2d, fuse_bn_act
+    from catch_b200.parallel import FusedDataParallel
+
+    _init(rank, world)
+    fusion.fused_ops_on_host(True)
+    torch.manual_seed(21)
+    base = torchvision.models.resnet.ResNet(torchvision.models.resnet.BasicBlock, [1, 1, 0, 0], num_classes=7)
+    base.layer3, base.layer4 = torch.nn.Identity(), torch.nn.Identity()
+    base.fc = torch.nn.Linear(128, 7)
+    ref = fuse_bn_act(copy.deepcopy(base)).to(DEV).to(memory_format=torch.channels_last)
+    net = fuse_bn_act(copy.deepcopy(base)).to(DEV).to(memory_format=torch.channels_last)
+    hp = dict(lr=0.02, momentum=0.9, weight_decay=1e-4)
+    opt = torch.optim.SGD(ref.parameters(), **hp)
+    fdp = FusedDataParallel(net, "sgd", bucket_mb=0.05, **hp)
+    assert len(fdp.buckets) >= 3
+    convs = [m for m in net.modules() if isinstance(m, StatsConv2d)]
+    assert all(m.weight._b200_lowp.dtype == torch.bfloat16 and m.weight._b200_grad_acc is not None for m in convs)
+    g = torch.Generator().manual_seed(22)
+    loss_fn = torch.nn.CrossEntropyLoss()
+    for _ in range(3):
+        x = torch.randn(4, 3, 32, 32, generator=g).to(DEV)
+        t = torch.randint(0, 7, (4,), generator=g).to(DEV)
+        with torch.autocast(DEV, dtype=torch.bfloat16):
+            la = loss_fn(ref(x), t)
+            lb = loss_fn(fdp(x), t)
+        opt.zero_grad()
+        la.backward(); opt.step()
+        lb.backward(); fdp.step()
+        assert abs(float(la.detach()) - float(lb.detach())) < 2e-2
+    for (n, p), q in zip(ref.named_parameters(), fdp.module.parameters()):
+        err = (p.detach().cpu() - q.detach().cpu()).norm() / (p.detach().cpu().norm() + 1e-6)
+        assert err < 2e-3, (n, float(err))
+    for m in convs:
+        assert torch.equal(m.weight._b200_lowp.cpu(), m.weight.detach().to(torch.bfloat16).cpu())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_fused_data_parallel_with_fused_convolution_modules():
+    run_ranks(_fdp_fused_convnet, world=2)
