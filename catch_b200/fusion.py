@@ -213,18 +213,13 @@ def fused_ops_on_host(enabled: bool) -> None:
     """Under host simulation the fused modules normally fall back to the stock layers.  With this switch (or
     ``CATCH_B200_FUSION_ON_HOSTSIM=1``) they take the same autograd functions as on the device, whose operators then
     run their host paths: for testing the bookkeeping around them (gradient sinks, direct accumulation into gradient
-    buckets, 16-bit weight copies) without a GPU."""
+    buckets, 16-bit weight copies, the transformer fusions) without a GPU."""
     global _FUSED_ON_HOST
     _FUSED_ON_HOST = bool(enabled)
 
 
 def _device_kernels_available(x: torch.Tensor) -> bool:
     return x.device.type == "blackwell" and (_FUSED_ON_HOST or not torch.b200.is_hostsim())
-
-
-def _on_real_device(x: torch.Tensor) -> bool:
-    """For the fused operators that have no host path (the transformer fusions)."""
-    return x.device.type == "blackwell" and not torch.b200.is_hostsim()
 
 
 class BatchNormAct2d(nn.BatchNorm2d):
@@ -307,7 +302,7 @@ class FusedLinear(nn.Linear):
     """``nn.Linear`` whose autocast path runs through ``_LinearFn`` (same parameters, same state dict)."""
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if _on_real_device(x) and x.numel() > 0 and self.in_features % 8 == 0 and self.out_features % 8 == 0:
+        if _device_kernels_available(x) and x.numel() > 0 and self.in_features % 8 == 0 and self.out_features % 8 == 0:
             autocast = torch.is_autocast_enabled("blackwell")
             cd = torch.get_autocast_dtype("blackwell") if autocast else x.dtype
             if cd in (torch.bfloat16, torch.float16) and (autocast or self.weight.dtype == x.dtype):
@@ -393,7 +388,7 @@ class _DropoutAddLayerNormFn(torch.autograd.Function):
 
 def dropout_add_layer_norm(h: torch.Tensor, residual: torch.Tensor, norm: nn.LayerNorm, p: float, training: bool) -> torch.Tensor:
     """``norm(residual + dropout(h))`` as one kernel (forward) and one kernel (backward) on the device."""
-    ok = (_on_real_device(h) and h.dtype in (torch.bfloat16, torch.float16, torch.float32) and h.dtype == residual.dtype
+    ok = (_device_kernels_available(h) and h.dtype in (torch.bfloat16, torch.float16, torch.float32) and h.dtype == residual.dtype
           and h.shape == residual.shape and len(norm.normalized_shape) == 1 and h.shape[-1] % 4 == 0 and h.shape[-1] <= 1536
           and h.numel() > 0)
     if not ok:

@@ -198,7 +198,10 @@ at::Tensor linear_act(const at::Tensor& x, const at::Tensor& w, const std::optio
   std::vector<int64_t> osz(x.sizes().begin(), x.sizes().end());
   osz.back() = w.size(0);
   if (use_cpu_path() || !gemm_dtype_ok(x.scalar_type()) || x.scalar_type() != w.scalar_type()) {
-    at::Tensor y = at::linear(x, w, bias);
+    // the fused kernel takes an fp32 bias next to 16-bit operands; the stock operator wants one dtype
+    std::optional<at::Tensor> b = bias;
+    if (b.has_value() && b->defined() && b->scalar_type() != x.scalar_type()) b = b->to(x.scalar_type());
+    at::Tensor y = at::linear(x, w, b);
     if (act == 1) y = at::relu(y);
     else if (act == 2) y = at::gelu(y);
     return y;
@@ -225,7 +228,11 @@ at::Tensor gemm_nd(const at::Tensor& a, const at::Tensor& b, const std::optional
   TORCH_CHECK(out.dim() == 4 && out.size(0) == B1 && out.size(1) == B2 && out.size(2) == M && out.size(3) == N && out.stride(3) == 1,
               "gemm_nd: out must be [B1, B2, M, N] with a unit innermost stride");
   if (out.numel() == 0) return out;
-  TORCH_CHECK(!use_cpu_path() && is_b200(a), "gemm_nd runs on the device only");
+  if (use_cpu_path()) {  // host path (host simulation, force-CPU mode): fp32 product, rounded once into `out`
+    out.copy_(at::matmul(a.to(at::kFloat), b.to(at::kFloat)).mul_(alpha));
+    return out;
+  }
+  TORCH_CHECK(is_b200(a), "gemm_nd: operands must be on the device");
   if (K == 0) return out.zero_();
   const int64_t es = 2;
   struct Op4 { at::Tensor t; int64_t ld; int mn; int64_t s1, s2; };
@@ -271,11 +278,33 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> linear_backward_fp32w(const at::T
                                                                      bool need_dx, bool need_dw, bool need_db,
                                                                      const std::optional<at::Tensor>& accum_w,
                                                                      const std::optional<at::Tensor>& accum_b) {
-  TORCH_CHECK(!use_cpu_path() && is_b200(grad), "linear_backward_fp32w runs on the device only");
   TORCH_CHECK(grad.scalar_type() == x.scalar_type() && x.scalar_type() == w.scalar_type() &&
                   (x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf),
               "linear_backward_fp32w: 16-bit operands of one dtype expected");
   const int64_t N = w.size(0), K = w.size(1);
+  if (use_cpu_path()) {  // host path (host simulation, force-CPU mode): the same three results from fp32 products
+    at::Tensor gf = grad.reshape({-1, N}).to(at::kFloat), xf = x.reshape({-1, K}).to(at::kFloat);
+    at::Tensor dx, dw, db;
+    if (need_dx) dx = at::mm(gf, w.to(at::kFloat)).to(x.scalar_type()).reshape(x.sizes());
+    if (need_dw) {
+      dw = at::mm(gf.t(), xf);
+      if (accum_w.has_value() && accum_w->defined()) {
+        TORCH_CHECK(accum_w->scalar_type() == at::kFloat && accum_w->numel() == N * K && accum_w->is_contiguous(),
+                    "linear_backward_fp32w: accum_w must be a contiguous fp32 tensor of the weight's size");
+        accum_w->view({N, K}).add_(dw);
+        dw = at::Tensor();
+      }
+    }
+    if (need_db) {
+      db = gf.sum(std::vector<int64_t>{0});
+      if (accum_b.has_value() && accum_b->defined()) {
+        accum_b->view({N}).add_(db);
+        db = at::Tensor();
+      }
+    }
+    return {dx, dw, db};
+  }
+  TORCH_CHECK(is_b200(grad), "linear_backward_fp32w: operands must be on the device");
   at::Tensor g2 = grad.reshape({-1, N}), x2 = x.reshape({-1, K});
   if (!g2.is_contiguous()) g2 = g2.contiguous();
   if (!x2.is_contiguous()) x2 = x2.contiguous();

@@ -158,10 +158,30 @@ Tensor k_native_dropout_backward(const Tensor& grad, const Tensor& mask, double 
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> dropout_add_layer_norm(
     const at::Tensor& h, const at::Tensor& residual, const std::optional<at::Tensor>& weight, const std::optional<at::Tensor>& bias,
     double p, bool training, double eps) {
-  TORCH_CHECK(!use_cpu_path() && is_b200(h), "dropout_add_layer_norm runs on the device only");
   TORCH_CHECK(h.sizes() == residual.sizes() && h.scalar_type() == residual.scalar_type() && f_ok(h.scalar_type()) && h.dim() >= 1,
               "dropout_add_layer_norm: h and residual must match");
   const int64_t cols = h.size(-1), rows = cols ? h.numel() / cols : 0;
+  if (use_cpu_path()) {
+    // Host path (host simulation, force-CPU mode): the same five results from ordinary tensor operations; the mask
+    // holds one byte per element here (the device packs it), which only the matching backward below reads.
+    const bool drop = training && p > 0.0;
+    at::Tensor hf = h.to(at::kFloat).reshape({rows, cols});
+    at::Tensor mask = at::empty({0}, h.options().dtype(at::kByte));
+    if (drop) {
+      at::Tensor keep = at::bernoulli(at::full({rows, cols}, 1.0 - p, hf.options()));
+      hf = hf * keep / (1.0 - p);
+      mask = keep.to(at::kByte).reshape({-1});
+    }
+    at::Tensor sf = residual.to(at::kFloat).reshape({rows, cols}) + hf;
+    at::Tensor mean = sf.mean(std::vector<int64_t>{1});
+    at::Tensor var = (sf - mean.unsqueeze(1)).square().mean(std::vector<int64_t>{1});
+    at::Tensor rstd = (var + eps).rsqrt();
+    at::Tensor yf = (sf - mean.unsqueeze(1)) * rstd.unsqueeze(1);
+    if (weight.has_value() && weight->defined()) yf = yf * weight->to(at::kFloat);
+    if (bias.has_value() && bias->defined()) yf = yf + bias->to(at::kFloat);
+    return {yf.to(h.scalar_type()).reshape(h.sizes()), sf.to(h.scalar_type()).reshape(h.sizes()), mask, mean, rstd};
+  }
+  TORCH_CHECK(is_b200(h), "dropout_add_layer_norm: operands must be on the device");
   TORCH_CHECK(cols % 4 == 0 && cols <= b200_dropout_add_layernorm_max_cols(), "dropout_add_layer_norm: unsupported row length ", cols);
   OpScope scope("dropout_add_layer_norm", h);
   at::Tensor hc = h.contiguous(), rc = residual.contiguous();
@@ -193,8 +213,22 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> dropout_a
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> dropout_add_layer_norm_backward(
     const at::Tensor& dy, const at::Tensor& s, const at::Tensor& mask, const std::optional<at::Tensor>& weight,
     const at::Tensor& mean, const at::Tensor& rstd, double p) {
-  TORCH_CHECK(!use_cpu_path() && is_b200(dy), "dropout_add_layer_norm_backward runs on the device only");
   const int64_t cols = s.size(-1), rows = cols ? s.numel() / cols : 0;
+  if (use_cpu_path()) {  // host path: see the forward; `mask` has one byte per element here
+    at::Tensor g = dy.to(at::kFloat).reshape({rows, cols});
+    at::Tensor xhat = (s.to(at::kFloat).reshape({rows, cols}) - mean.unsqueeze(1)) * rstd.unsqueeze(1);
+    at::Tensor gy = (weight.has_value() && weight->defined()) ? g * weight->to(at::kFloat) : g;
+    at::Tensor dgamma = (g * xhat).sum(std::vector<int64_t>{0}), dbeta = g.sum(std::vector<int64_t>{0});
+    at::Tensor c1 = (gy * xhat).mean(std::vector<int64_t>{1}, true), c2 = gy.mean(std::vector<int64_t>{1}, true);
+    at::Tensor ds = (gy - c2 - xhat * c1) * rstd.unsqueeze(1);
+    at::Tensor dh = ds;
+    if (mask.numel() > 0) {
+      TORCH_CHECK(mask.numel() == rows * cols, "dropout_add_layer_norm_backward (host path): expects the host path's mask");
+      dh = ds * mask.to(at::kFloat).reshape({rows, cols}) / (1.0 - p);
+    }
+    return {ds.to(s.scalar_type()).reshape(s.sizes()), dh.to(s.scalar_type()).reshape(s.sizes()), dgamma, dbeta};
+  }
+  TORCH_CHECK(is_b200(dy), "dropout_add_layer_norm_backward: operands must be on the device");
   OpScope scope("dropout_add_layer_norm_backward", dy);
   at::Tensor g = dy.contiguous();
   TORCH_CHECK(g.scalar_type() == s.scalar_type() && g.numel() == s.numel() && s.is_contiguous(), "dropout_add_layer_norm_backward: shape / dtype mismatch");
