@@ -369,6 +369,100 @@ def set_memory_strategy(native_memory_strategy: bool) -> None:
     _C._set_memory_strategy(bool(native_memory_strategy))
 
 
+def set_per_process_memory_fraction(fraction: float, device: _device_t = None) -> None:
+    """Cap the device memory this process's caching allocator may hold at ``fraction`` of the device's capacity
+    (``torch.cuda.set_per_process_memory_fraction``).  A request that would pass the cap fails with an out-of-memory
+    error after cached blocks were given back; 0 lifts the cap."""
+    _C._set_memory_fraction(float(fraction), _get_device_index(device, optional=True))
+
+
+def caching_allocator_alloc(size: int, device: _device_t = None, stream=None) -> int:
+    """A raw block of ``size`` bytes from the caching allocator, bound to ``stream`` (default: the current queue);
+    returns its address (``torch.cuda.caching_allocator_alloc``).  Free it with ``caching_allocator_delete``."""
+    d = _get_device_index(device, optional=True)
+    q = getattr(stream, "_native", stream)
+    return _C._raw_alloc(int(size), d, q)
+
+
+def caching_allocator_delete(mem_ptr: int) -> None:
+    _C._raw_free(int(mem_ptr))
+
+
+def can_device_access_peer(device: _device_t, peer_device: _device_t) -> bool:
+    """Every pair of distinct B200s of one NVSwitch domain maps each other's memory."""
+    a, b = _get_device_index(device, optional=True), _get_device_index(peer_device, optional=True)
+    n = device_count()
+    if not (0 <= a < n and 0 <= b < n):
+        raise ValueError("invalid device ordinal")
+    return a != b
+
+
+def get_arch_list():
+    """The architectures the device library was compiled for."""
+    return ["sm_100a"]
+
+
+def ipc_collect() -> None:
+    """Kept for scripts written for ``torch.cuda``: peer mappings of this backend live as long as their process group."""
+    return None
+
+
+def utilization(device: _device_t = None) -> int:
+    """Percent of the last sampling period during which kernels ran on the device (read through NVML)."""
+    import pynvml
+
+    pynvml.nvmlInit()
+    try:
+        handle = pynvml.nvmlDeviceGetHandleByIndex(_get_device_index(device, optional=True))
+        return int(pynvml.nvmlDeviceGetUtilizationRates(handle).gpu)
+    finally:
+        pynvml.nvmlShutdown()
+
+
+class _Nvtx:
+    """``torch.cuda.nvtx``-shaped annotations; they land in this backend's kernel trace
+    (``catch_b200.profiler.kernel_trace``) and in profiler output."""
+
+    @staticmethod
+    def range_push(msg: str) -> None:
+        _C._trace_range_push(str(msg))
+
+    @staticmethod
+    def range_pop() -> None:
+        _C._trace_range_pop()
+
+    @staticmethod
+    def mark(msg: str) -> None:
+        _C._trace_mark(str(msg))
+
+    @staticmethod
+    @contextlib.contextmanager
+    def range(msg: str, *args, **kwargs):
+        _C._trace_range_push(str(msg).format(*args, **kwargs))
+        try:
+            yield
+        finally:
+            _C._trace_range_pop()
+
+
+nvtx = _Nvtx()
+
+
+class _Amp:
+    """``torch.cuda.amp``-shaped entry points for scripts written for GPUs."""
+
+    @staticmethod
+    def autocast(enabled: bool = True, dtype: torch.dtype = torch.bfloat16, cache_enabled: bool = True):
+        return torch.autocast("blackwell", enabled=enabled, dtype=dtype, cache_enabled=cache_enabled)
+
+    @staticmethod
+    def GradScaler(*args, **kwargs):  # noqa: N802 - the name scripts use
+        return torch.amp.GradScaler("blackwell", *args, **kwargs)
+
+
+amp = _Amp()
+
+
 def set_memory_debug(enable: bool) -> None:
     """Switch the guard-word debug allocator on or off.  Tensors allocated while it is on carry guard regions (and an
     allocation record) until they are freed; tensors allocated while it is off are not checked."""

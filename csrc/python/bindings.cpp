@@ -156,6 +156,13 @@ PYBIND11_MODULE(_C, m) {
   });
   m.def("_set_memory_strategy", [](bool native) { setNativeMemoryStrategy(native); });
   m.def("_get_memory_strategy", [] { return nativeMemoryStrategy(); });
+  m.def("_set_memory_fraction", [](double fraction, int d) { setMemoryFraction(fraction, d); });
+  m.def("_memory_reserve_limit", [](int d) { return memoryReserveLimit(d); });
+  // raw blocks from the caching allocator (torch.cuda.caching_allocator_alloc / _delete)
+  m.def("_raw_alloc", [](size_t bytes, int d, const Queue* q) {
+    return reinterpret_cast<uintptr_t>(raw_alloc(bytes, d, q ? *q : getCurrentQueue(d)));
+  }, py::arg("bytes"), py::arg("device"), py::arg("queue") = nullptr);
+  m.def("_raw_free", [](uintptr_t ptr) { raw_free(reinterpret_cast<void*>(ptr)); });
   // Python frames of the allocating thread for the debug allocator's origin records.
   setAllocationContextHook(+[]() -> std::string {
     if (!Py_IsInitialized() || _Py_IsFinalizing()) return std::string();

@@ -82,6 +82,7 @@ struct DeviceState {
   Pool small_free, large_free;
   MemoryStats stats;
   std::deque<PendingFree> pending;
+  int64_t reserve_limit = 0;  // > 0: the allocator may not hold more than this many bytes of device memory
 };
 
 class CachingAllocator final : public c10::Allocator {
@@ -255,6 +256,14 @@ class CachingAllocator final : public c10::Allocator {
   }
 
   void set_native(bool v) { native_ = v; }
+  void set_reserve_limit(int device, int64_t bytes) {
+    std::lock_guard<std::recursive_mutex> g(mu_);
+    state(device).reserve_limit = bytes;
+  }
+  int64_t reserve_limit(int device) {
+    std::lock_guard<std::recursive_mutex> g(mu_);
+    return state(device).reserve_limit;
+  }
   bool native() const { return native_; }
   // Blocks handed out before the switch keep their layout (each block remembers whether it has guards), so the
   // mode can change while tensors are alive; only blocks allocated in debug mode are checked.
@@ -337,14 +346,16 @@ class CachingAllocator final : public c10::Allocator {
     const size_t seg = segment_size(want, small, device);
     DeviceSwitch sw(device);
     void* p = nullptr;
-    int err = backend().try_malloc(&p, seg);
+    // a per-process limit (set_per_process_memory_fraction) is treated like an allocation failure of the driver
+    auto over_limit = [&] { return st.reserve_limit > 0 && st.stats.reserved + static_cast<int64_t>(seg) > st.reserve_limit; };
+    int err = over_limit() ? -1 : backend().try_malloc(&p, seg);
     if (err != 0) {
       // Give cached memory back to the driver and try again.
       st.stats.num_retries++;
       sync_pending(st);
       release_segments(st, st.small_free, device);
       release_segments(st, st.large_free, device);
-      err = backend().try_malloc(&p, seg);
+      err = over_limit() ? -1 : backend().try_malloc(&p, seg);
     }
     if (err != 0) {
       st.stats.num_ooms++;
@@ -356,7 +367,8 @@ class CachingAllocator final : public c10::Allocator {
       TORCH_CHECK_WITH(OutOfMemoryError, false, "b200 out of memory. Tried to allocate ", seg, " bytes for a request of ",
                        want, " bytes (device ", device, "; ", total_b, " bytes total capacity; ", free_b,
                        " bytes free; ", st.stats.allocated, " bytes already allocated; ", st.stats.reserved,
-                       " bytes reserved by the caching allocator).");
+                       " bytes reserved by the caching allocator",
+                       st.reserve_limit > 0 ? "; per-process limit " + std::to_string(st.reserve_limit) + " bytes" : std::string(), ").");
     }
     Block* b = new Block();
     b->device = device;
@@ -546,6 +558,18 @@ MemoryStats memoryStats(int device) { return alloc().stats(device); }
 void resetPeakStats(int device) { alloc().reset_peak(device); }
 void setNativeMemoryStrategy(bool native) { alloc().set_native(native); }
 bool nativeMemoryStrategy() { return alloc().native(); }
+void setMemoryFraction(double fraction, int device) {
+  TORCH_CHECK(fraction >= 0.0 && fraction <= 1.0, "invalid memory fraction ", fraction, " (expected a value in [0, 1]; 0 lifts the limit)");
+  int64_t limit = 0;
+  if (fraction > 0.0) {
+    DeviceSwitch sw(device);
+    size_t free_b = 0, total_b = 0;
+    backend().mem_info(&free_b, &total_b);
+    limit = static_cast<int64_t>(fraction * static_cast<double>(total_b));
+  }
+  alloc().set_reserve_limit(device, limit);
+}
+int64_t memoryReserveLimit(int device) { return alloc().reserve_limit(device); }
 void setMemoryDebug(bool on) { alloc().set_debug(on); }
 bool memoryDebugEnabled() { return alloc().debug(); }
 DebugReport memoryDebugCheck(const void* ptr) { return alloc().debug_check(ptr); }

@@ -62,6 +62,11 @@ void resetPeakStats(int device);
 // segments); false (default) = cache-friendly segment sizes.
 void setNativeMemoryStrategy(bool native);
 bool nativeMemoryStrategy();
+// Cap on the device memory this process's allocator may hold, as a fraction of the device's capacity (0 = no cap;
+// torch.cuda.set_per_process_memory_fraction semantics: a request that would exceed it fails like an out-of-memory
+// condition, after cached blocks were given back).
+void setMemoryFraction(double fraction, int device);
+int64_t memoryReserveLimit(int device);
 // Debug allocator: enable before the first allocation (or via the environment).
 void setMemoryDebug(bool on);
 bool memoryDebugEnabled();

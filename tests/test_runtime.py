@@ -300,3 +300,50 @@ def test_flags_and_logging(capfd):
         assert "[DEBUG]" in err and "runs on the CPU path" in err
     finally:
         bw.set_log_level(1)
+
+
+def test_cuda_style_conveniences(monkeypatch):
+    """Entry points that scripts converted from torch.cuda call: per-process memory cap, raw allocator blocks, nvtx and
+    amp namespaces, peer access, architecture list."""
+    import pytest
+
+    bw = torch.b200
+    dev = bw.current_device()
+    bw.empty_cache()
+    base = bw.memory_reserved()
+    total = bw.get_device_properties(dev).total_memory
+    # a cap a little above what is reserved now: a small tensor fits, a large one does not
+    frac = (base + (8 << 20)) / total
+    bw.set_per_process_memory_fraction(frac)
+    try:
+        ok = torch.empty(1 << 20, dtype=torch.uint8, device="blackwell")
+        with pytest.raises(torch.OutOfMemoryError, match="per-process limit"):
+            torch.empty(64 << 20, dtype=torch.uint8, device="blackwell")
+        assert bw.memory_stats()["num_ooms"] >= 1
+        del ok
+    finally:
+        bw.set_per_process_memory_fraction(0.0)
+    big = torch.empty(64 << 20, dtype=torch.uint8, device="blackwell")     # the cap is lifted again
+    del big
+    bw.empty_cache()
+    with pytest.raises(RuntimeError, match="fraction"):
+        bw.set_per_process_memory_fraction(1.5)
+    before = bw.memory_allocated()
+    ptr = bw.caching_allocator_alloc(4096)
+    assert ptr != 0 and bw.memory_allocated() >= before + 4096
+    ptr2 = bw.caching_allocator_alloc(4096, stream=bw.current_queue())
+    assert ptr2 not in (0, ptr)
+    bw.caching_allocator_delete(ptr); bw.caching_allocator_delete(ptr2)
+    assert bw.memory_allocated() == before
+    with bw.nvtx.range("step {}", 3):
+        bw.nvtx.mark("inside")
+    bw.nvtx.range_push("a"); bw.nvtx.range_pop()
+    with bw.amp.autocast(dtype=torch.bfloat16):
+        assert torch.is_autocast_enabled("blackwell") and torch.get_autocast_dtype("blackwell") == torch.bfloat16
+    assert type(bw.amp.GradScaler(enabled=False)).__name__ == "GradScaler"
+    assert bw.get_arch_list() == ["sm_100a"]
+    if bw.device_count() > 1:
+        assert bw.can_device_access_peer(0, 1) and not bw.can_device_access_peer(0, 0)
+    with pytest.raises(ValueError):
+        bw.can_device_access_peer(0, 99)
+    assert bw.ipc_collect() is None
