@@ -161,7 +161,10 @@ class Queue:
     (reference: torch_mlu/core/device/queue.py:35-61).
     """
 
-    def __init__(self, device_index: int = -1, _native=None):
+    def __init__(self, device_index: int = -1, _native=None, device=None, priority: int = 0):
+        # `device` / `priority`: the keywords of torch.cuda.Stream (queues of the pool have one priority)
+        if device is not None:
+            device_index = _get_device_index(device, optional=True)
         self._native = _native if _native is not None else _C._getCurrentQueue(device_index)
         self._prev = None
         self._prev_device = None
@@ -463,6 +466,51 @@ class _Amp:
 amp = _Amp()
 
 
+def make_graphed_callables(callables, sample_args, num_warmup_iters: int = 3, **_ignored):
+    """``torch.cuda.make_graphed_callables`` shape: one callable with its sample arguments, or a tuple of callables
+    with a tuple of argument tuples.  Inference only (see :func:`make_graphed_callable`)."""
+    if isinstance(callables, (tuple, list)):
+        return tuple(make_graphed_callable(c, a, num_warmup_iters) for c, a in zip(callables, sample_args))
+    return make_graphed_callable(callables, sample_args, num_warmup_iters)
+
+
+def is_tf32_supported() -> bool:
+    return True
+
+
+def _nvml_query(device, fn):
+    import pynvml
+
+    pynvml.nvmlInit()
+    try:
+        return fn(pynvml, pynvml.nvmlDeviceGetHandleByIndex(_get_device_index(device, optional=True)))
+    finally:
+        pynvml.nvmlShutdown()
+
+
+def temperature(device: _device_t = None) -> int:
+    """Degrees Celsius (read through NVML)."""
+    return int(_nvml_query(device, lambda n, h: n.nvmlDeviceGetTemperature(h, n.NVML_TEMPERATURE_GPU)))
+
+
+def power_draw(device: _device_t = None) -> int:
+    """Milliwatts (read through NVML)."""
+    return int(_nvml_query(device, lambda n, h: n.nvmlDeviceGetPowerUsage(h)))
+
+
+def clock_rate(device: _device_t = None) -> int:
+    """SM clock in MHz (read through NVML)."""
+    return int(_nvml_query(device, lambda n, h: n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)))
+
+
+def device_memory_used(device: _device_t = None) -> int:
+    """Bytes in use on the device by all processes (read through NVML)."""
+    return int(_nvml_query(device, lambda n, h: n.nvmlDeviceGetMemoryInfo(h).used))
+
+
+OutOfMemoryError = torch.OutOfMemoryError
+
+
 def set_memory_debug(enable: bool) -> None:
     """Switch the guard-word debug allocator on or off.  Tensors allocated while it is on carry guard regions (and an
     allocation record) until they are freed; tensors allocated while it is off are not checked."""
@@ -550,9 +598,13 @@ class graph:
         except Exception:
             _C._setCurrentQueue(self._prev)
             raise
+        global _capture_depth
+        _capture_depth += 1
         return self.g
 
     def __exit__(self, exc_type, exc, tb):
+        global _capture_depth
+        _capture_depth -= 1
         try:
             if exc_type is not None:
                 self.g._native.capture_abort()
@@ -567,6 +619,21 @@ class graph:
             raise RuntimeError("b200 graph capture failed: the captured region waited for the device or used a call "
                                "that cannot be recorded")
         return False
+
+
+CUDAGraph = Graph  # the name scripts converted from torch.cuda use
+_capture_depth = 0
+
+
+def is_current_stream_capturing() -> bool:
+    """True inside a ``with torch.b200.graph(g):`` block of this thread's interpreter."""
+    return _capture_depth > 0
+
+
+def graph_pool_handle() -> int:
+    """An id of a private allocator pool (``torch.cuda.graph_pool_handle``); every :class:`Graph` of this backend
+    owns its pool, so the handle is only kept for scripts that pass one around."""
+    return int(_C._new_private_pool())
 
 
 def graphs_supported() -> bool:

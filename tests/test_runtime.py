@@ -347,3 +347,9 @@ def test_cuda_style_conveniences(monkeypatch):
     with pytest.raises(ValueError):
         bw.can_device_access_peer(0, 99)
     assert bw.ipc_collect() is None
+    s = bw.Stream(priority=-1)
+    assert bw.Stream(device=dev).device_index == dev and s.query() in (True, False)
+    assert bw.CUDAGraph is bw.Graph and not bw.is_current_stream_capturing() and bw.graph_pool_handle() > 0
+    assert bw.is_tf32_supported() and bw.OutOfMemoryError is torch.OutOfMemoryError
+    double = bw.make_graphed_callables(lambda t: t * 2, (torch.ones(2, device="blackwell"),))
+    assert torch.equal(double(torch.ones(2, device="blackwell")).cpu(), torch.full((2,), 2.0))

@@ -59,3 +59,68 @@ def test_operator_coverage_table_is_current_and_has_no_fallback_rows():
     assert not [line for line in rows if "| fallback |" in line]
     with open(os.path.join(here, "OP_COVERAGE.md")) as f:
         assert f.read().strip() == r.stdout.strip()
+
+
+GPU_SCRIPT = '''import torch
+import torch.nn as nn
+import torch.backends.cudnn as cudnn
+
+assert torch.cuda.is_available()
+cudnn.benchmark = True
+torch.cuda.set_device(0)
+torch.manual_seed(0); torch.cuda.manual_seed_all(0)
+device = torch.device("cuda:0")
+print(torch.cuda.get_device_name(0), torch.cuda.device_count(), torch.cuda.get_device_capability())
+model = nn.Sequential(nn.Conv2d(3, 8, 3, padding=1), nn.BatchNorm2d(8), nn.ReLU(), nn.AdaptiveAvgPool2d(1), nn.Flatten(),
+                      nn.Linear(8, 4)).cuda()
+opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
+scaler = torch.cuda.amp.GradScaler(enabled=False)
+start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+side = torch.cuda.Stream()
+torch.cuda.reset_peak_memory_stats()
+for step in range(2):
+    x = torch.randn(4, 3, 8, 8).pin_memory().cuda(non_blocking=True)
+    y = torch.randint(0, 4, (4,)).to(device, non_blocking=True)
+    start.record()
+    torch.cuda.nvtx.range_push("step")
+    with torch.cuda.amp.autocast(dtype=torch.bfloat16):
+        loss = nn.functional.cross_entropy(model(x), y)
+    opt.zero_grad(set_to_none=True)
+    scaler.scale(loss).backward()
+    scaler.step(opt); scaler.update()
+    torch.cuda.nvtx.range_pop()
+    end.record()
+    with torch.cuda.stream(side):
+        z = x * 2
+    torch.cuda.current_stream().wait_stream(side)
+    z.record_stream(torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    assert start.elapsed_time(end) >= 0 and float(loss) == float(loss)
+assert torch.cuda.max_memory_allocated() > 0 and torch.cuda.memory_reserved() >= 0
+state = torch.cuda.get_rng_state(); torch.cuda.set_rng_state(state)
+torch.cuda.set_per_process_memory_fraction(0.9)
+torch.save(model.state_dict(), "CKPT")
+sd = torch.load("CKPT", map_location="cuda:0")
+assert next(iter(sd.values())).device.type != "cpu"
+torch.cuda.empty_cache()
+assert torch.cuda.memory_summary()
+print("script finished on", next(model.parameters()).device)
+'''
+
+
+def test_converted_gpu_script_runs(tmp_path):
+    """A training script that uses the usual torch.cuda surface (events, streams, record_stream, nvtx, amp, memory
+    statistics, RNG state, checkpoints with a map_location) runs unchanged after the converter."""
+    import subprocess
+    import sys
+
+    d = tmp_path / "proj"
+    d.mkdir()
+    (d / "train.py").write_text(GPU_SCRIPT.replace("CKPT", str(tmp_path / "model.pt")))
+    out, _ = gpu2blackwell.convert_tree(str(d))
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CATCH_B200_BACKEND="hostsim", PYTHONPATH=repo)
+    r = subprocess.run([sys.executable, os.path.join(out, "train.py")], env=env, capture_output=True, text=True, timeout=300,
+                       cwd=str(tmp_path))
+    assert r.returncode == 0, r.stderr[-3000:]
+    assert "script finished on blackwell:0" in r.stdout
