@@ -610,13 +610,34 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupB200::run_on_comm(c10d::OpType op, st
 // ---- host-simulated transport ----------------------------------------------------------
 std::vector<std::vector<uint8_t>> ProcessGroupB200::store_exchange(const std::vector<uint8_t>& mine, bool everyone_sends,
                                                                    int root) {
+  // The Store refuses values above 8 MiB: a message is one head key (a flag byte, then either the payload itself or
+  // the number of parts) plus, for large messages, part keys of at most kPart bytes each.
+  constexpr size_t kPart = 4u << 20;
   const uint64_t s = ++host_seq_;
   auto key = [&](uint64_t seq, int r) { return uid_ + "/x/" + std::to_string(seq) + "/" + std::to_string(r); };
+  auto part = [&](uint64_t seq, int r, int i) { return key(seq, r) + "/p" + std::to_string(i); };
   auto ack = [&](uint64_t seq, int r) { return uid_ + "/xa/" + std::to_string(seq) + "/" + std::to_string(r); };
   const bool i_send = everyone_sends || rank_ == root;
   if (i_send) {
-    store_->set(key(s, rank_), mine);
-    posted_.push_back(s);
+    int nparts = 0;
+    std::vector<uint8_t> head;
+    if (mine.size() <= kPart) {
+      head.reserve(mine.size() + 1);
+      head.push_back(0);
+      head.insert(head.end(), mine.begin(), mine.end());
+    } else {
+      nparts = static_cast<int>((mine.size() + kPart - 1) / kPart);
+      for (int i = 0; i < nparts; ++i) {  // the parts first: a reader that sees the head finds them all
+        const size_t b = static_cast<size_t>(i) * kPart, e = std::min(mine.size(), b + kPart);
+        store_->set(part(s, rank_, i), std::vector<uint8_t>(mine.begin() + b, mine.begin() + e));
+      }
+      head.resize(1 + sizeof(uint64_t));
+      head[0] = 1;
+      const uint64_t n64 = static_cast<uint64_t>(nparts);
+      std::memcpy(head.data() + 1, &n64, sizeof(n64));
+    }
+    store_->set(key(s, rank_), head);
+    posted_.emplace_back(s, nparts);
   }
   std::vector<std::vector<uint8_t>> all(size_);
   for (int r = 0; r < size_; ++r) {
@@ -626,14 +647,27 @@ std::vector<std::vector<uint8_t>> ProcessGroupB200::store_exchange(const std::ve
       continue;
     }
     store_->wait({key(s, r)}, timeout_);  // throws on timeout: a missing peer is detected here
-    all[r] = store_->get(key(s, r));
-    store_->add(ack(s, r), 1);            // tell the sender that this reader is done with the key
+    std::vector<uint8_t> head = store_->get(key(s, r));
+    TORCH_CHECK(!head.empty(), "bwccl(hostsim): empty message head");
+    if (head[0] == 0) {
+      all[r].assign(head.begin() + 1, head.end());
+    } else {
+      uint64_t n64 = 0;
+      TORCH_CHECK(head.size() == 1 + sizeof(n64), "bwccl(hostsim): malformed message head");
+      std::memcpy(&n64, head.data() + 1, sizeof(n64));
+      for (uint64_t i = 0; i < n64; ++i) {
+        std::vector<uint8_t> piece = store_->get(part(s, r, static_cast<int>(i)));
+        all[r].insert(all[r].end(), piece.begin(), piece.end());
+      }
+    }
+    store_->add(ack(s, r), 1);            // tell the sender that this reader is done with the message
   }
   // A posted message is deleted once every other rank has acknowledged it.  (Counting rounds is not
   // enough: the root of a broadcast waits for nobody, so it can be several rounds ahead of a reader.)
   while (!posted_.empty()) {
-    const uint64_t old = posted_.front();
+    const auto [old, nparts] = posted_.front();
     if (store_->add(ack(old, rank_), 0) < size_ - 1) break;
+    for (int i = 0; i < nparts; ++i) store_->deleteKey(part(old, rank_, i));
     store_->deleteKey(key(old, rank_));
     store_->deleteKey(ack(old, rank_));
     posted_.pop_front();

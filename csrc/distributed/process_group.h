@@ -144,7 +144,7 @@ class ProcessGroupB200 : public c10d::Backend {
   uint64_t seq_ = 0;
   std::vector<uint64_t> send_seq_, recv_seq_;
   uint64_t host_seq_ = 0;
-  std::deque<uint64_t> posted_;   // host-simulated transport: rounds whose message is still in the Store
+  std::deque<std::pair<uint64_t, int>> posted_;  // host-simulated transport: (round, extra parts) of messages still in the Store
   int64_t wait_limit_ms_ = 0;     // explicit device-side wait limit (0 = follow timeout_)
   std::string uid_;
 

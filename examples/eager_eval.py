@@ -1,4 +1,5 @@
 """Eager-mode ResNet-50 inference (counterpart of examples/inference/eager_eval.py)."""
+import argparse
 import os
 import sys
 
@@ -8,9 +9,14 @@ import torchvision
 
 import catch_b200  # noqa: F401
 
+ap = argparse.ArgumentParser()
+ap.add_argument("--model", default="resnet50")
+ap.add_argument("--batch", type=int, default=16)
+ap.add_argument("--image", type=int, default=224)
+args = ap.parse_args()
 dev = torch.device("blackwell", 0)
-model = torchvision.models.resnet50().eval().half().to(dev).to(memory_format=torch.channels_last)
-x = torch.randn(16, 3, 224, 224).half().to(dev)
+model = getattr(torchvision.models, args.model)().eval().half().to(dev).to(memory_format=torch.channels_last)
+x = torch.randn(args.batch, 3, args.image, args.image).half().to(dev)
 with torch.no_grad():
     out = model(x)
 print("top-1:", out.argmax(1).cpu().tolist())

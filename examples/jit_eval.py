@@ -1,4 +1,5 @@
 """Fusion-mode (TorchScript) ResNet-50 inference (counterpart of examples/inference/jit_eval.py)."""
+import argparse
 import os
 import sys
 
@@ -9,10 +10,15 @@ import torchvision
 import catch_b200  # noqa: F401
 from catch_b200 import jit
 
+ap = argparse.ArgumentParser()
+ap.add_argument("--model", default="resnet50")
+ap.add_argument("--batch", type=int, default=16)
+ap.add_argument("--image", type=int, default=224)
+args = ap.parse_args()
 dev = torch.device("blackwell", 0)
 # move first, then trace and freeze: freezing turns the weights into graph constants
-model = torchvision.models.resnet50().eval().half().to(dev).to(memory_format=torch.channels_last)
-x = torch.randn(16, 3, 224, 224).half().to(dev).contiguous(memory_format=torch.channels_last)
+model = getattr(torchvision.models, args.model)().eval().half().to(dev).to(memory_format=torch.channels_last)
+x = torch.randn(args.batch, 3, args.image, args.image).half().to(dev).contiguous(memory_format=torch.channels_last)
 with torch.no_grad():
     traced = torch.jit.trace(model, x)
     fused = jit.optimize(traced)

@@ -25,12 +25,14 @@ def main():
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--fused", action="store_true")
+    ap.add_argument("--model", default="resnet50")
+    ap.add_argument("--image", type=int, default=224)
     args = ap.parse_args()
     rank, local = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
     torch.b200.set_device(local)
     dist.init_process_group("bwccl")
     dev = torch.device("blackwell", local)
-    model = torchvision.models.resnet50().to(dev).to(memory_format=torch.channels_last)
+    model = getattr(torchvision.models, args.model)().to(dev).to(memory_format=torch.channels_last)
     if args.fused:
         ddp = FusedDataParallel(model, "sgd", lr=0.1, momentum=0.9, weight_decay=1e-4)
         opt = None
@@ -39,7 +41,7 @@ def main():
         opt = FusedSGD(ddp.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
     g = torch.Generator().manual_seed(rank)
     for i in range(args.iters):
-        x = torch.randn(args.batch, 3, 224, 224, generator=g).to(dev)
+        x = torch.randn(args.batch, 3, args.image, args.image, generator=g).to(dev)
         y = torch.randint(0, 1000, (args.batch,), generator=g).to(dev)
         with torch.autocast(device_type="blackwell", dtype=torch.bfloat16):
             loss = torch.nn.functional.cross_entropy(ddp(x), y)

@@ -18,11 +18,12 @@ def main():
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--model", default="resnet50")
+    ap.add_argument("--image", type=int, default=224)
     args = ap.parse_args()
     dev = torch.device("blackwell", 0)
     model = getattr(torchvision.models, args.model)().to(dev).to(memory_format=torch.channels_last)
     opt = FusedSGD(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
-    data = torchvision.datasets.FakeData(args.batch * args.iters, (3, 224, 224), 1000, torchvision.transforms.ToTensor())
+    data = torchvision.datasets.FakeData(args.batch * args.iters, (3, args.image, args.image), 1000, torchvision.transforms.ToTensor())
     loader = PrefetchLoader(torch.utils.data.DataLoader(data, batch_size=args.batch), dev)
     model.train()
     for i, (x, y) in enumerate(loader):
