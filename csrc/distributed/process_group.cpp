@@ -1070,6 +1070,114 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupB200::barrier(const c10d::BarrierOpti
   return work;
 }
 
+// ---- gather / scatter / all-to-all, composed ---------------------------------------------------
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::work_on_current_queue(c10d::OpType op, std::vector<at::Tensor> outputs) {
+  if (hostsim()) {
+    auto work = c10::make_intrusive<WorkB200>(rank_, op, std::move(outputs), device_, nullptr, timeout_);
+    work->finish_host();
+    return work;
+  }
+  auto work = make_work(op, outputs);
+  work->keep_alive_ = std::move(outputs);
+  work->notifier_.place(getCurrentQueue(device_));
+  return work;
+}
+
+at::Tensor ProcessGroupB200::gather_all(const at::Tensor& mine) {
+  at::Tensor flat = mine.contiguous().view({-1});
+  at::Tensor all = at::empty({size_, flat.numel()}, flat.options());
+  at::Tensor out_flat = all.view({-1});
+  _allgather_base(out_flat, flat, c10d::AllgatherOptions())->wait();  // the current queue waits for the exchange
+  return all;
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::gather(std::vector<std::vector<at::Tensor>>& outputs,
+                                                        std::vector<at::Tensor>& inputs, const c10d::GatherOptions& opts) {
+  check_single(inputs);
+  const int root = static_cast<int>(opts.rootRank);
+  TORCH_CHECK(root >= 0 && root < size_, "bwccl gather: invalid root rank ", root);
+  if (rank_ == root) {
+    TORCH_CHECK(outputs.size() == 1 && static_cast<int>(outputs[0].size()) == size_,
+                "bwccl gather: the root passes one list of world-size output tensors");
+    for (auto& o : outputs[0])
+      TORCH_CHECK(o.numel() == inputs[0].numel() && o.scalar_type() == inputs[0].scalar_type(),
+                  "bwccl gather: every output must have the input's size and dtype");
+  } else {
+    TORCH_CHECK(outputs.empty() || outputs[0].empty(), "bwccl gather: only the root passes output tensors");
+  }
+  at::Tensor all = gather_all(inputs[0]);
+  std::vector<at::Tensor> outs;
+  if (rank_ == root) {
+    for (int r = 0; r < size_; ++r) {
+      outputs[0][r].copy_(all[r].view(outputs[0][r].sizes()));
+      outs.push_back(outputs[0][r]);
+    }
+  }
+  return work_on_current_queue(c10d::OpType::GATHER, outs);
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::scatter(std::vector<at::Tensor>& outputs,
+                                                         std::vector<std::vector<at::Tensor>>& inputs,
+                                                         const c10d::ScatterOptions& opts) {
+  check_single(outputs);
+  const int root = static_cast<int>(opts.rootRank);
+  TORCH_CHECK(root >= 0 && root < size_, "bwccl scatter: invalid root rank ", root);
+  at::Tensor& out = outputs[0];
+  at::Tensor flat = at::empty({size_, out.numel()}, out.options());
+  if (rank_ == root) {
+    TORCH_CHECK(inputs.size() == 1 && static_cast<int>(inputs[0].size()) == size_,
+                "bwccl scatter: the root passes one list of world-size input tensors");
+    for (int r = 0; r < size_; ++r) {
+      TORCH_CHECK(inputs[0][r].numel() == out.numel() && inputs[0][r].scalar_type() == out.scalar_type(),
+                  "bwccl scatter: every input must have the output's size and dtype");
+      flat[r].copy_(inputs[0][r].reshape({-1}));
+    }
+  } else {
+    TORCH_CHECK(inputs.empty() || inputs[0].empty(), "bwccl scatter: only the root passes input tensors");
+  }
+  std::vector<at::Tensor> one{flat};
+  c10d::BroadcastOptions bo;
+  bo.rootRank = root;
+  broadcast(one, bo)->wait();
+  out.copy_(flat[rank_].view(out.sizes()));
+  return work_on_current_queue(c10d::OpType::SCATTER, {out});
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::alltoall_base(at::Tensor& output, at::Tensor& input,
+                                                               std::vector<int64_t>& output_splits,
+                                                               std::vector<int64_t>& input_splits, const c10d::AllToAllOptions&) {
+  TORCH_CHECK(is_b200(output) && is_b200(input), "bwccl all_to_all: tensors must live on the blackwell device");
+  ensure_arena(input.device().index());
+  TORCH_CHECK(output_splits.empty() && input_splits.empty(), "bwccl all_to_all: only equal splits are implemented");
+  TORCH_CHECK(input.numel() % size_ == 0 && output.numel() == input.numel() && output.scalar_type() == input.scalar_type(),
+              "bwccl all_to_all: input and output must have the same size, divisible by the world size");
+  const int64_t chunk = input.numel() / size_;
+  at::Tensor all = gather_all(input);                                   // [world, world * chunk]
+  at::Tensor mine = all.view({size_, size_, chunk}).select(1, rank_);   // chunk `rank` of every rank's input
+  if (output.is_contiguous()) output.view({size_, chunk}).copy_(mine);
+  else output.copy_(mine.reshape(output.sizes()));
+  return work_on_current_queue(c10d::OpType::ALLTOALL_BASE, {output});
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::alltoall(std::vector<at::Tensor>& outputs, std::vector<at::Tensor>& inputs,
+                                                          const c10d::AllToAllOptions&) {
+  TORCH_CHECK(static_cast<int>(outputs.size()) == size_ && static_cast<int>(inputs.size()) == size_,
+              "bwccl all_to_all: one input and one output tensor per rank expected");
+  const int64_t chunk = inputs[0].numel();
+  for (int r = 0; r < size_; ++r) {
+    TORCH_CHECK(is_b200(inputs[r]) && is_b200(outputs[r]), "bwccl all_to_all: tensors must live on the blackwell device");
+    TORCH_CHECK(inputs[r].numel() == chunk && outputs[r].numel() == chunk && inputs[r].scalar_type() == inputs[0].scalar_type() &&
+                    outputs[r].scalar_type() == inputs[0].scalar_type(),
+                "bwccl all_to_all: only tensors of one size and dtype are implemented");
+  }
+  ensure_arena(inputs[0].device().index());
+  at::Tensor flat = at::empty({size_, chunk}, inputs[0].options());
+  for (int r = 0; r < size_; ++r) flat[r].copy_(inputs[r].reshape({-1}));
+  at::Tensor all = gather_all(flat).view({size_, size_, chunk});
+  for (int r = 0; r < size_; ++r) outputs[r].copy_(all[r][rank_].view(outputs[r].sizes()));
+  return work_on_current_queue(c10d::OpType::ALLTOALL, outputs);
+}
+
 // ---- fused DDP path -------------------------------------------------------------------------
 // The bucket kernel's steps on the host, for ranks that talk through the Store (host simulation): (cast the local
 // fp32 gradients to the exchange dtype and clear them) -> sum over ranks in fp32 -> scale -> optimizer update of this

@@ -83,6 +83,16 @@ class ProcessGroupB200 : public c10d::Backend {
                                                 const c10d::ReduceScatterOptions& opts) override;
   c10::intrusive_ptr<c10d::Work> _reduce_scatter_base(at::Tensor& output, at::Tensor& input,
                                                       const c10d::ReduceScatterOptions& opts) override;
+  // gather / scatter / all-to-all are composed from all-gather and broadcast (every rank receives everything and
+  // keeps its part): correct and built from the collectives above, not bandwidth-optimal.  Equal sizes only.
+  c10::intrusive_ptr<c10d::Work> gather(std::vector<std::vector<at::Tensor>>& outputs, std::vector<at::Tensor>& inputs,
+                                        const c10d::GatherOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> scatter(std::vector<at::Tensor>& outputs, std::vector<std::vector<at::Tensor>>& inputs,
+                                         const c10d::ScatterOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> alltoall_base(at::Tensor& output, at::Tensor& input, std::vector<int64_t>& output_splits,
+                                               std::vector<int64_t>& input_splits, const c10d::AllToAllOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> alltoall(std::vector<at::Tensor>& outputs, std::vector<at::Tensor>& inputs,
+                                          const c10d::AllToAllOptions& opts) override;
   c10::intrusive_ptr<c10d::Work> send(std::vector<at::Tensor>& tensors, int dst, int tag) override;
   c10::intrusive_ptr<c10d::Work> recv(std::vector<at::Tensor>& tensors, int src, int tag) override;
   c10::intrusive_ptr<c10d::Work> barrier(const c10d::BarrierOptions& opts) override;
@@ -121,6 +131,10 @@ class ProcessGroupB200 : public c10d::Backend {
   void apply_wait_limit();
   void check_single(const std::vector<at::Tensor>& tensors) const;
   c10::intrusive_ptr<WorkB200> make_work(c10d::OpType op, std::vector<at::Tensor> outputs);
+  // a Work for results that were produced on the current compute queue (composed collectives)
+  c10::intrusive_ptr<c10d::Work> work_on_current_queue(c10d::OpType op, std::vector<at::Tensor> outputs);
+  // [world, numel] tensor holding every rank's `mine` (flattened), ordered on the current compute queue
+  at::Tensor gather_all(const at::Tensor& mine);
   // runs fn(stream) on the comm queue ordered after the current compute queue
   template <typename F>
   c10::intrusive_ptr<c10d::Work> run_on_comm(c10d::OpType op, std::vector<at::Tensor> tensors, F&& fn, Queue* q = nullptr);

@@ -343,3 +343,36 @@ def _fdp_fused_convnet(rank, world):
 
 def test_fused_data_parallel_with_fused_convolution_modules():
     run_ranks(_fdp_fused_convnet, world=2)
+
+
+def _composed_collectives(rank, world):
+    """gather / scatter / all_to_all: composed from all-gather and broadcast (equal sizes)."""
+    _init(rank, world)
+    for dtype in (torch.float32, torch.bfloat16, torch.int64):
+        inp = (torch.arange(world * 2) + rank * 10).to(dtype).to(DEV)
+        out = torch.empty_like(inp)
+        dist.all_to_all_single(out, inp)
+        exp = torch.cat([torch.arange(rank * 2, rank * 2 + 2) + r * 10 for r in range(world)]).to(dtype)
+        assert torch.equal(out.cpu(), exp), dtype
+    ins = [torch.full((2, 3), float(rank * 10 + r), device=DEV) for r in range(world)]
+    outs = [torch.empty(2, 3, device=DEV) for _ in range(world)]
+    w = dist.all_to_all(outs, ins, async_op=True)
+    w.wait()
+    assert all(torch.equal(outs[r].cpu(), torch.full((2, 3), float(r * 10 + rank))) for r in range(world))
+    t = torch.full((3,), float(rank), device=DEV)
+    got = [torch.empty(3, device=DEV) for _ in range(world)] if rank == 1 else None
+    dist.gather(t, got, dst=1)
+    if rank == 1:
+        assert all(torch.equal(got[r].cpu(), torch.full((3,), float(r))) for r in range(world))
+    piece = torch.empty(2, 2, device=DEV)
+    src = [torch.full((2, 2), float(r + 1), device=DEV) for r in range(world)] if rank == 0 else None
+    dist.scatter(piece, src, src=0)
+    assert torch.equal(piece.cpu(), torch.full((2, 2), float(rank + 1)))
+    with pytest.raises(Exception, match="equal splits"):
+        dist.all_to_all_single(torch.empty(world, device=DEV), torch.ones(world, device=DEV), [1] * world, [1] * world)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_gather_scatter_all_to_all():
+    run_ranks(_composed_collectives, world=3)

@@ -242,3 +242,35 @@ def _multicast(rank, world, expect_on):
 @pytest.mark.parametrize("multicast", [True, False])
 def test_allreduce_with_and_without_multicast(multicast):
     run_ranks(_multicast, world=WORLD, args=(multicast,), env=ENV if multicast else ENV_NO_MULTICAST, timeout=240)
+
+
+def _composed(rank, world):
+    """gather / scatter / all_to_all, which this backend composes from all-gather and broadcast."""
+    _init(rank, world)
+    for dtype in (torch.float32, torch.bfloat16, torch.int64):
+        inp = (torch.arange(world * 1000) % 50 + rank * 3).to(dtype).to(DEV)
+        out = torch.empty_like(inp)
+        dist.all_to_all_single(out, inp)
+        exp = torch.cat([(torch.arange(rank * 1000, (rank + 1) * 1000) % 50 + r * 3) for r in range(world)]).to(dtype)
+        assert torch.equal(out.cpu(), exp), dtype
+    ins = [torch.full((5, 7), float(rank * 10 + r), device=DEV) for r in range(world)]
+    outs = [torch.empty(5, 7, device=DEV) for _ in range(world)]
+    dist.all_to_all(outs, ins)
+    assert all(torch.equal(outs[r].cpu(), torch.full((5, 7), float(r * 10 + rank))) for r in range(world))
+    t = torch.full((333,), float(rank), device=DEV)
+    got = [torch.empty(333, device=DEV) for _ in range(world)] if rank == world - 1 else None
+    dist.gather(t, got, dst=world - 1)
+    if rank == world - 1:
+        assert all(torch.equal(got[r].cpu(), torch.full((333,), float(r))) for r in range(world))
+    piece = torch.empty(9, 9, device=DEV)
+    src = [torch.full((9, 9), float(r + 1), device=DEV) for r in range(world)] if rank == 0 else None
+    dist.scatter(piece, src, src=0)
+    assert torch.equal(piece.cpu(), torch.full((9, 9), float(rank + 1)))
+    dist.barrier()
+    torch.b200.synchronize()
+    dist.destroy_process_group()
+
+
+@needs2
+def test_gather_scatter_all_to_all():
+    run_ranks(_composed, world=WORLD, env=ENV, timeout=240)
