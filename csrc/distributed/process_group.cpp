@@ -1070,6 +1070,19 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupB200::barrier(const c10d::BarrierOpti
   return work;
 }
 
+c10::intrusive_ptr<c10d::Work> ProcessGroupB200::endCoalescing() {
+  if (hostsim() || !arena_) {
+    auto work = c10::make_intrusive<WorkB200>(rank_, c10d::OpType::COALESCED, std::vector<at::Tensor>{}, device_, nullptr, timeout_);
+    work->finish_host();
+    return work;
+  }
+  // every collective of the group ran on the comm queue, in order: a marker behind them covers them all
+  DeviceSwitch sw(device_);
+  auto work = make_work(c10d::OpType::COALESCED, {});
+  work->notifier_.place(comm_q_);
+  return work;
+}
+
 // ---- gather / scatter / all-to-all, composed ---------------------------------------------------
 c10::intrusive_ptr<c10d::Work> ProcessGroupB200::work_on_current_queue(c10d::OpType op, std::vector<at::Tensor> outputs) {
   if (hostsim()) {

@@ -93,6 +93,10 @@ class ProcessGroupB200 : public c10d::Backend {
                                                std::vector<int64_t>& input_splits, const c10d::AllToAllOptions& opts) override;
   c10::intrusive_ptr<c10d::Work> alltoall(std::vector<at::Tensor>& outputs, std::vector<at::Tensor>& inputs,
                                           const c10d::AllToAllOptions& opts) override;
+  // Coalescing (torch.distributed._coalescing_manager): collectives between the two calls are launched as they come
+  // (the comm queue keeps their order); endCoalescing returns one Work that completes after all of them.
+  void startCoalescing() override {}
+  c10::intrusive_ptr<c10d::Work> endCoalescing() override;
   c10::intrusive_ptr<c10d::Work> send(std::vector<at::Tensor>& tensors, int dst, int tag) override;
   c10::intrusive_ptr<c10d::Work> recv(std::vector<at::Tensor>& tensors, int src, int tag) override;
   c10::intrusive_ptr<c10d::Work> barrier(const c10d::BarrierOptions& opts) override;

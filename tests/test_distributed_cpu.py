@@ -368,6 +368,15 @@ def _composed_collectives(rank, world):
     src = [torch.full((2, 2), float(r + 1), device=DEV) for r in range(world)] if rank == 0 else None
     dist.scatter(piece, src, src=0)
     assert torch.equal(piece.cpu(), torch.full((2, 2), float(rank + 1)))
+    # the coalescing manager (used by sharded-training libraries) wraps a group of collectives in one Work
+    a, b = torch.full((3,), float(rank), device=DEV), torch.full((5,), 2.0 * rank, device=DEV)
+    with dist._coalescing_manager(device=torch.device(DEV)):
+        dist.all_reduce(a)
+        dist.all_reduce(b)
+    assert a.cpu()[0] == sum(range(world)) and b.cpu()[0] == 2 * sum(range(world))
+    with dist._coalescing_manager(device=torch.device(DEV), async_ops=True) as cm:
+        dist.all_reduce(a)
+    cm.wait()
     with pytest.raises(Exception, match="equal splits"):
         dist.all_to_all_single(torch.empty(world, device=DEV), torch.ones(world, device=DEV), [1] * world, [1] * world)
     dist.barrier()
