@@ -385,3 +385,37 @@ def _composed_collectives(rank, world):
 
 def test_gather_scatter_all_to_all():
     run_ranks(_composed_collectives, world=3)
+
+
+def _fsdp(rank, world):
+    """Sharded data parallelism (absent from the reference): torch's FullyShardedDataParallel needs
+    all_gather_into_tensor, reduce_scatter_tensor and the stream / event surface of the device module."""
+    import copy
+
+    from torch.distributed.fsdp import FullyShardedDataParallel as FSDP
+
+    _init(rank, world)
+    dev = torch.device(DEV, torch.b200.current_device())
+    torch.manual_seed(0)
+    ref = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4))
+    net = FSDP(copy.deepcopy(ref).to(dev), device_id=dev)
+    opt = torch.optim.SGD(net.parameters(), lr=0.1)
+    opt_ref = torch.optim.SGD(ref.parameters(), lr=0.1)
+    g = torch.Generator().manual_seed(1)
+    for _ in range(3):
+        x, y = torch.randn(8 * world, 16, generator=g), torch.randn(8 * world, 4, generator=g)
+        opt_ref.zero_grad()
+        torch.nn.functional.mse_loss(ref(x), y).backward()
+        opt_ref.step()
+        opt.zero_grad()
+        torch.nn.functional.mse_loss(net(x[rank * 8:(rank + 1) * 8].to(dev)), y[rank * 8:(rank + 1) * 8].to(dev)).backward()
+        opt.step()
+    with FSDP.summon_full_params(net):
+        for a, b in zip(ref.parameters(), net.parameters()):
+            assert (a - b.cpu()).abs().max().item() < 1e-5
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_fully_sharded_data_parallel_runs_on_the_backend():
+    run_ranks(_fsdp, world=2)
