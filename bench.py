@@ -266,7 +266,10 @@ def run_ours(args, rank, local_rank, world, store, sampler):
     from catch_b200.parallel import FusedDataParallel
     from catch_b200.utils import DelayedScalar, PrefetchLoader
 
-    assert torch.b200.backend_name() == "cuda", "bench.py needs a GPU (the host-simulated device is for tests)"
+    # CATCH_B200_BENCH_DRY_RUN=1: walk the whole script on the host-simulated device (tests of the script itself;
+    # the numbers it prints then mean nothing)
+    assert torch.b200.backend_name() == "cuda" or os.environ.get("CATCH_B200_BENCH_DRY_RUN") == "1", \
+        "bench.py needs a GPU (the host-simulated device is for tests)"
     torch.b200.set_device(local_rank)
     dev = torch.device("blackwell", local_rank)
     if world > 1:

@@ -51,6 +51,10 @@ def check(rc: int, what: str = "kernel") -> None:
 
 
 def read_error_flag() -> int:
+    """The code recorded by a kernel whose bounded wait ran out (0 = none), cleared by the read.  Under host
+    simulation no kernel runs: always 0."""
+    if torch.b200.is_hostsim():
+        return 0
     v = C.c_int(0)
     check(lib().b200_read_and_clear_error_flag(C.byref(v)), "read_error_flag")
     return v.value
