@@ -36,3 +36,11 @@ def test_multi_card_training_example(fused):
     out = _run(["-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
                 "--master-port", str(port), "examples/multi_card_train.py", "--iters", "2"] + SMALL + (["--fused"] if fused else []))
     assert "iter 1: loss" in out
+
+
+def test_bert_benchmark_script_walks_through_with_fused_layers():
+    env = dict(os.environ, CATCH_B200_BACKEND="hostsim", CATCH_B200_FUSION_ON_HOSTSIM="1", OMP_NUM_THREADS="2")
+    r = subprocess.run([sys.executable, "benchmarks/bert_train.py", "--steps", "2", "--warmup", "1", "--batch", "2", "--seq", "16",
+                        "--layers", "1"], env=env, capture_output=True, text=True, timeout=600, cwd=REPO)
+    assert r.returncode == 0, r.stderr[-3000:]
+    assert "sequences/sec" in r.stdout and "loss" in r.stdout
