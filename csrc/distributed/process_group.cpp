@@ -534,6 +534,22 @@ void ProcessGroupB200::stop_watchdog() {
 
 ProcessGroupB200::~ProcessGroupB200() {
   stop_watchdog();
+  if (hostsim() && size_ > 1) {
+    // Under host simulation every message travels through the Store, which usually lives in rank 0's process: rank 0
+    // may only go away once the other ranks are done with their last exchange (they can still be reading rank 0's
+    // message of a final barrier when rank 0 has already read theirs).
+    try {
+      const std::string key = uid_ + "/closed";
+      store_->add(key, 1);
+      if (rank_ == 0) {
+        const auto limit = std::min<std::chrono::milliseconds>(timeout_, std::chrono::milliseconds(10000));
+        const auto t0 = std::chrono::steady_clock::now();
+        while (store_->add(key, 0) < size_ && std::chrono::steady_clock::now() - t0 < limit)
+          std::this_thread::sleep_for(std::chrono::milliseconds(2));
+      }
+    } catch (...) {
+    }
+  }
   {
     std::lock_guard<std::mutex> lk(g_groups_mu);
     g_groups.erase(this);
@@ -660,17 +676,23 @@ std::vector<std::vector<uint8_t>> ProcessGroupB200::store_exchange(const std::ve
         all[r].insert(all[r].end(), piece.begin(), piece.end());
       }
     }
-    store_->add(ack(s, r), 1);            // tell the sender that this reader is done with the message
+    try {
+      store_->add(ack(s, r), 1);          // tell the sender that this reader is done with the message
+    } catch (...) {                       // housekeeping only: the data is here (the sender's process may be gone)
+    }
   }
   // A posted message is deleted once every other rank has acknowledged it.  (Counting rounds is not
   // enough: the root of a broadcast waits for nobody, so it can be several rounds ahead of a reader.)
-  while (!posted_.empty()) {
-    const auto [old, nparts] = posted_.front();
-    if (store_->add(ack(old, rank_), 0) < size_ - 1) break;
-    for (int i = 0; i < nparts; ++i) store_->deleteKey(part(old, rank_, i));
-    store_->deleteKey(key(old, rank_));
-    store_->deleteKey(ack(old, rank_));
-    posted_.pop_front();
+  try {
+    while (!posted_.empty()) {
+      const auto [old, nparts] = posted_.front();
+      if (store_->add(ack(old, rank_), 0) < size_ - 1) break;
+      for (int i = 0; i < nparts; ++i) store_->deleteKey(part(old, rank_, i));
+      store_->deleteKey(key(old, rank_));
+      store_->deleteKey(ack(old, rank_));
+      posted_.pop_front();
+    }
+  } catch (...) {  // housekeeping only; a Store that is really gone fails the next exchange
   }
   return all;
 }
