@@ -419,13 +419,24 @@ def _is_add(node: fx.Node) -> bool:
     return False
 
 
+class _FusionTracer(fx.Tracer):
+    """Traces only as deep as the rewrite needs: a sub-module without a convolution or batch norm inside stays one
+    call (torchvision's StochasticDepth, custom activations, attention blocks ...).  Tracing into such a module would
+    freeze its Python-level decisions, ``self.training`` above all, at their value on the day of the trace."""
+
+    def is_leaf_module(self, m: nn.Module, module_qualified_name: str) -> bool:
+        if super().is_leaf_module(m, module_qualified_name):
+            return True
+        return not any(isinstance(c, (nn.Conv2d, nn.BatchNorm2d)) for c in m.modules())
+
+
 def fuse_bn_act(model: nn.Module) -> fx.GraphModule:
     """Return an fx GraphModule of ``model`` with BN(+add)+ReLU chains fused (see module docstring).
 
     A ``Conv2d`` whose only consumer is a batch norm becomes a ``StatsConv2d`` and that batch norm a
     ``BatchNormAct2d`` (with ``act = 0`` when no ReLU follows), so the convolution's epilogue supplies
     the batch statistics."""
-    gm = fx.symbolic_trace(model)
+    gm = fx.GraphModule(model, _FusionTracer().trace(model))
     modules = dict(gm.named_modules())
     fused = 0
     for node in list(gm.graph.nodes):

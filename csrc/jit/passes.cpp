@@ -60,12 +60,44 @@ void eliminate_exception_ifs(Block* block) {
   }
 }
 
+// Does anything downstream of `v` depend on v's strides?  view() and its relatives do, and so does whoever receives
+// a graph output; operators that write a fresh dense result (convolutions, GEMMs, reductions, pooling, cat, reshape ...)
+// cut the dependence; everything else (element-wise operators keep their input's strides, transpose / slice / chunk
+// build their strides from it) passes it on.
+bool strides_matter(Value* v, std::unordered_set<Value*>& seen) {
+  if (!seen.insert(v).second) return false;
+  static const std::unordered_set<std::string> sensitive = {
+      "aten::view", "aten::view_as", "aten::as_strided", "aten::unflatten", "aten::stride", "aten::is_contiguous",
+      "aten::unfold", "aten::_unsafe_view", "aten::resize_", "aten::set_"};
+  static const std::unordered_set<std::string> fresh = {
+      "aten::conv2d", "aten::_convolution", "aten::convolution", "aten::linear", "aten::matmul", "aten::mm", "aten::bmm",
+      "aten::addmm", "aten::cat", "aten::stack", "aten::max_pool2d", "aten::avg_pool2d", "aten::adaptive_avg_pool2d",
+      "aten::adaptive_max_pool2d", "aten::mean", "aten::sum", "aten::softmax", "aten::log_softmax", "aten::layer_norm",
+      "aten::batch_norm", "aten::reshape", "aten::flatten", "aten::contiguous", "aten::upsample_nearest2d", "aten::size",
+      "aten::embedding", "aten::argmax", "aten::max", "aten::min", "aten::topk", "aten::sort",
+      "catch_b200::conv_bn_act", "catch_b200::linear_act", "catch_b200::qconv_act", "catch_b200::conv2d", "catch_b200::linear"};
+  for (const Use& u : v->uses()) {
+    Node* user = u.user;
+    if (user->kind() == prim::Return) return true;
+    const std::string kind = user->kind().toQualString();
+    if (sensitive.count(kind)) return true;
+    if (fresh.count(kind)) continue;
+    for (Value* out : user->outputs())
+      if (strides_matter(out, seen)) return true;
+  }
+  return false;
+}
+
+// x.contiguous() is dropped where nothing downstream can tell the difference (the copy it may make is pure cost
+// there); in front of a view() -- the channel shuffle of ShuffleNet -- or of a graph output it stays.
 void remove_contiguous(Block* block) {
   for (auto it = block->nodes().begin(); it != block->nodes().end();) {
     Node* n = *it;
     ++it;
     for (Block* b : n->blocks()) remove_contiguous(b);
     if (n->kind() == aten::contiguous) {
+      std::unordered_set<Value*> seen;
+      if (strides_matter(n->output(), seen)) continue;
       n->output()->replaceAllUsesWith(n->input(0));
       n->destroy();
     }
@@ -367,12 +399,14 @@ std::optional<Node*> try_fuse(Node* consumer, Value* producer_value, AliasDb& db
   const bool group_producer = producer->kind() == fusion_kind();
   if (!group_producer && !isSupported(producer)) return std::nullopt;
   if (!db.moveBeforeTopologicallyValid(producer, consumer)) return std::nullopt;
+  // every refusal comes before the consumer is wrapped: wrapping destroys the consumer node, and the caller goes on
+  // to its next input with the same pointer when this returns nothing
+  if (!group_producer && !non_tensor_outputs_stay_inside(producer, consumer)) return std::nullopt;
   Node* group = consumer;
   if (consumer->kind() != fusion_kind()) {
     if (!produces_tensor(consumer)) return std::nullopt;
     group = SubgraphUtils::createSingletonSubgraphAndUpdateAliasing(consumer, fusion_kind(), db);
   }
-  if (!group_producer && !non_tensor_outputs_stay_inside(producer, group)) return std::nullopt;
   SubgraphUtils::mergeNodeIntoSubgraphAndUpdateAliasing(producer, group, db);
   return group;
 }

@@ -46,14 +46,31 @@ void test_jit_lowering() {
       %p : float = prim::Constant[value=0.5]()
       %f : bool = prim::Constant[value=0]()
       %one : int = prim::Constant[value=1]()
+      %none : NoneType = prim::Constant()
       %d : Tensor = aten::dropout(%x, %p, %f)
       %c : Tensor = aten::contiguous(%d, %one)
-      %y : Tensor = aten::relu(%c)
+      %r : Tensor = aten::relu(%c)
+      %y : Tensor = aten::mean(%r, %none)
       return (%y))IR");
   jit::LowerGraph(g);
   CHECK_J(count_kind(g, "aten::dropout") == 0);
-  CHECK_J(count_kind(g, "aten::contiguous") == 0);
+  CHECK_J(count_kind(g, "aten::contiguous") == 0);  // nothing after it depends on strides (the reduction writes a fresh result)
   CHECK_J(count_kind(g, "aten::relu") == 1);
+  // ... but in front of a view, or when the result leaves the graph, it stays
+  auto g2 = parse(R"IR(
+    graph(%x : Tensor):
+      %one : int = prim::Constant[value=1]()
+      %zero : int = prim::Constant[value=0]()
+      %m1 : int = prim::Constant[value=-1]()
+      %t : Tensor = aten::transpose(%x, %zero, %one)
+      %c : Tensor = aten::contiguous(%t, %zero)
+      %r : Tensor = aten::relu(%c)
+      %shape : int[] = prim::ListConstruct(%m1)
+      %v : Tensor = aten::view(%r, %shape)
+      %c2 : Tensor = aten::contiguous(%t, %zero)
+      return (%v, %c2))IR");
+  jit::LowerGraph(g2);
+  CHECK_J(count_kind(g2, "aten::contiguous") == 2);
 }
 
 void test_jit_partitioner() {

@@ -167,12 +167,26 @@ def test_lowering_removes_exception_ifs_and_dropout():
         if x.dim() != 2:
             raise RuntimeError("bad rank")
         y = torch.nn.functional.dropout(x, 0.5, False)
-        return y.contiguous() + 1
+        return (y.contiguous() + 1).mean()
 
     g = f.graph
     jit.lower_graph(g)
     s = str(g)
     assert "prim::RaiseException" not in s and "aten::dropout" not in s and "aten::contiguous" not in s
+
+    # contiguous() stays where something downstream depends on strides: in front of a view, or as a graph output
+    @torch.jit.script
+    def shuffle(x):
+        b, c, h, w = x.shape
+        y = x.view(b, 2, c // 2, h, w).transpose(1, 2).contiguous()
+        return y.view(b, c, h, w)
+
+    g = shuffle.graph
+    jit.lower_graph(g)
+    assert str(g).count("aten::contiguous") == 1
+    x = torch.randn(2, 8, 3, 3).to("blackwell")
+    ref = x.cpu().view(2, 2, 4, 3, 3).transpose(1, 2).contiguous().view(2, 8, 3, 3)
+    assert torch.equal(shuffle(x).cpu(), ref)
 
 
 def test_delayed_scalar_returns_each_value_one_push_later():
