@@ -856,6 +856,27 @@ def get_log_level() -> int:
     return _C._get_min_log_level()
 
 
+def show_config() -> str:
+    """A text block for bug reports: versions, backend, devices, run-time switches and every ``CATCH_B200_*``
+    environment variable that is set (the counterpart of ``torch.__config__.show()``)."""
+    import os
+
+    lines = [get_version(), f"torch {torch.__version__}", f"backend: {backend_name()}", f"devices: {device_count()}"]
+    for d in range(device_count()):
+        p = get_device_properties(d)
+        lines.append(f"  blackwell:{d}: {p.name}, sm_{p.major}{p.minor}, {p.total_memory // (1 << 20)} MiB, "
+                     f"{p.multi_processor_count} SMs")
+    lines.append("device code: sm_100a")
+    flags = ("async_disable", "op_trycatch", "test_cpu_dispatch", "fallback_to_cpu", "blocking_wait")
+    lines.append("switches: " + ", ".join(f"{f}={int(get_flag(f))}" for f in flags) +
+                 f", memory_debug={int(_C._memory_debug_enabled()) if hasattr(_C, '_memory_debug_enabled') else '?'}"
+                 f", native_memory_strategy={int(_C._get_memory_strategy())}"
+                 f", fusion={int(_C._jit_can_fuse_on_b200())}")
+    env = sorted((k, v) for k, v in os.environ.items() if k.startswith("CATCH_B200_") or k == "USE_IO_QUEUE")
+    lines.append("environment: " + (", ".join(f"{k}={v}" for k, v in env) if env else "(no CATCH_B200_* variable set)"))
+    return "\n".join(lines)
+
+
 def set_flag(name: str, value: bool) -> None:
     """Flip a runtime switch: async_disable, op_trycatch, test_cpu_dispatch, fallback_to_cpu, blocking_wait."""
     _C._set_flag(name, bool(value))

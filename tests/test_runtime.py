@@ -347,6 +347,8 @@ def test_cuda_style_conveniences(monkeypatch):
     with pytest.raises(ValueError):
         bw.can_device_access_peer(0, 99)
     assert bw.ipc_collect() is None
+    cfg = bw.show_config()
+    assert "backend: hostsim" in cfg and "blackwell:0" in cfg and "op_trycatch=1" in cfg and "sm_100a" in cfg
     s = bw.Stream(priority=-1)
     assert bw.Stream(device=dev).device_index == dev and s.query() in (True, False)
     assert bw.CUDAGraph is bw.Graph and not bw.is_current_stream_capturing() and bw.graph_pool_handle() > 0
