@@ -39,10 +39,13 @@ CXX = os.environ.get("CATCH_B200_CXX", "/usr/bin/g++")
 # Build switches (environment), the counterpart of the reference's setup.py flags (setup.py:24-34,190-204):
 #   DEBUG=1                    host code with -O0 -g and assertions, device code with -G left off (-lineinfo stays)
 #   CATCH_B200_BUILD_ASAN=1    AddressSanitizer for the host libraries (host side only, like RUN_BUILD_ASAN_CHECK)
+#   CATCH_B200_BUILD_UBSAN=1   UndefinedBehaviorSanitizer for the host libraries (reports are printed, execution goes on)
 #   CATCH_B200_BUILD_TEST=0    skip the C++ test program
 #   MAX_JOBS=n                 parallel compile jobs
 DEBUG = os.environ.get("DEBUG", "0") not in ("0", "", "OFF", "off")
 ASAN = os.environ.get("CATCH_B200_BUILD_ASAN", "0") not in ("0", "", "OFF", "off")
+UBSAN = os.environ.get("CATCH_B200_BUILD_UBSAN", "0") not in ("0", "", "OFF", "off")
+SANITIZE = (["-fsanitize=address"] if ASAN else []) + (["-fsanitize=signed-integer-overflow,shift,integer-divide-by-zero,bounds,alignment,float-cast-overflow,float-divide-by-zero,bool,enum,return,unreachable,vla-bound"] if UBSAN else [])
 BUILD_TEST = os.environ.get("CATCH_B200_BUILD_TEST", "1") not in ("0", "OFF", "off")
 
 NVCC_FLAGS = [
@@ -90,7 +93,7 @@ def write_ninja(verbose: bool = False) -> Path:
     py_inc = sysconfig.get_paths()["include"]
     cxx_inc = " ".join(f"-isystem {p}" for p in inc + [py_inc] + ([nccl_inc] if nccl_inc else []))
     cxx_flags = (
-        ("-O0 -g " if DEBUG else "-O2 -DNDEBUG ") + ("-fsanitize=address -fno-omit-frame-pointer " if ASAN else "") +
+        ("-O0 -g " if DEBUG else "-O2 -DNDEBUG ") + (" ".join(SANITIZE) + " -fno-omit-frame-pointer " if SANITIZE else "") +
         "-std=c++17 -fPIC -fvisibility=hidden -Wall -Wno-unused-variable -Wno-unused-function "
         "-Wno-sign-compare -Wno-unknown-pragmas -D_GLIBCXX_USE_CXX11_ABI=1 -DTORCH_EXTENSION_NAME=_C "
         "-DTORCH_API_INCLUDE_EXTENSION_H"
@@ -135,7 +138,7 @@ def write_ninja(verbose: bool = False) -> Path:
         "-lc10", "-ltorch_cpu", "-ltorch", "-ltorch_python",
         f"-L{PKG / 'lib'}", "-lcatch_b200_device",
         "-Wl,-rpath,$$ORIGIN/lib", "-Wl,--no-as-needed",
-    ] + (["-fsanitize=address"] if ASAN else [])
+    ] + SANITIZE
     for p in lib:
         ld.append(f"-Wl,-rpath,{p}")
     lines.append(f"build {HOST_LIB}: link_host {' '.join(map(str, host_objs))} | {DEVICE_LIB}")
@@ -150,7 +153,7 @@ def write_ninja(verbose: bool = False) -> Path:
     if test_objs and BUILD_TEST:
         rt_objs = [o for o in host_objs if o.parent.name in ("runtime", "jit")]
         ld_test = [f"-L{p}" for p in lib] + ["-lc10", "-ltorch_cpu", "-ltorch", f"-L{PKG / 'lib'}", "-lcatch_b200_device",
-                                             "-Wl,-rpath,'$$ORIGIN'", "-Wl,--no-as-needed", "-lpthread"] + (["-fsanitize=address"] if ASAN else [])
+                                             "-Wl,-rpath,'$$ORIGIN'", "-Wl,--no-as-needed", "-lpthread"] + SANITIZE
         for p in lib:
             ld_test.append(f"-Wl,-rpath,{p}")
         lines.insert(lines.index("rule link_host"), "rule link_exe")
