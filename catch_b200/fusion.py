@@ -95,8 +95,10 @@ class _BNActFn(torch.autograd.Function):
         out, mean, invstd, mask = torch.ops.catch_b200.batch_norm_act_mask(x, weight, bias, running_mean, running_var,
                                                                            residual, training, momentum, eps, act, sums,
                                                                            num_batches_tracked)
-        # with a ReLU the backward only needs to know which outputs were positive: one bit each
-        ctx.save_for_backward(mask if mask.numel() else out, x, weight, running_mean, mean, invstd)
+        # with a ReLU the backward only needs to know which outputs were positive: one bit each; without one it does
+        # not need the output at all (and must not hold it: an in-place activation such as ReLU6(inplace=True) or
+        # SiLU(inplace=True) right behind the batch norm would invalidate a saved output)
+        ctx.save_for_backward((mask if mask.numel() else out) if act == 1 else None, x, weight, running_mean, mean, invstd)
         ctx.cfg = (training, act, residual is not None)
         ctx.res_sink = res_sink
         return out
@@ -105,6 +107,8 @@ class _BNActFn(torch.autograd.Function):
     def backward(ctx, grad_out):
         out, x, weight, running_mean, mean, invstd = ctx.saved_tensors
         training, act, has_res = ctx.cfg
+        if out is None:  # no activation: the operator ignores this argument, any tensor of the right shape will do
+            out = grad_out
         dx, dgamma, dbeta, dres = torch.ops.catch_b200.batch_norm_act_backward(
             grad_out, out, x, weight, running_mean, mean, invstd, training, act, has_res)
         sink = ctx.res_sink

@@ -112,3 +112,31 @@ def test_fused_training_path_on_the_host_simulated_device():
     with pytest.raises(Exception):
         torch.ops.catch_b200.batch_norm_act_backward(torch.ones(1, 8, 2, 2), torch.zeros(0, dtype=torch.uint8), torch.ones(1, 8, 2, 2),
                                                      None, None, torch.zeros(8), torch.zeros(0), True, 1, False)
+
+
+def test_inplace_activation_behind_a_fused_batch_norm():
+    """MobileNet / EfficientNet style blocks: BN followed by ReLU6(inplace=True) or SiLU(inplace=True), which the
+    rewrite does not fuse.  The fused batch norm must not keep its output for the backward (the activation overwrites
+    it), on the fused operators' path as well as on the stock one."""
+    from catch_b200 import fusion
+
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Conv2d(8, 64, 3, padding=1, bias=False), torch.nn.BatchNorm2d(64), torch.nn.ReLU6(inplace=True),
+                              torch.nn.Conv2d(64, 64, 1, bias=False), torch.nn.BatchNorm2d(64), torch.nn.SiLU(inplace=True))
+    x = torch.randn(4, 8, 10, 10)
+    ref = copy.deepcopy(net)
+    ref(x).square().mean().backward()
+    fusion.fused_ops_on_host(True)
+    try:
+        fused = fuse_bn_act(copy.deepcopy(net)).to("blackwell").to(memory_format=torch.channels_last)
+        assert sum(isinstance(m, BatchNormAct2d) and m.act == 0 for m in fused.modules()) == 2
+        out = fused(x.to("blackwell"))
+        out.square().mean().backward()          # used to raise: "modified by an inplace operation"
+        for p, q in zip(ref.parameters(), fused.parameters()):
+            assert torch.allclose(q.grad.cpu(), p.grad, atol=1e-4, rtol=1e-3)
+        with torch.autocast("blackwell", dtype=torch.bfloat16):   # and through the fused convolution path
+            fused.zero_grad()
+            fused(x.to("blackwell")).float().square().mean().backward()
+        assert all(torch.isfinite(q.grad).all() for q in fused.parameters())
+    finally:
+        fusion.fused_ops_on_host(False)
