@@ -125,6 +125,27 @@ std::tuple<Tensor, Tensor, Tensor> batch_norm_device(const Tensor& input, const 
   return {in_format_of(out, input), save_mean, save_invstd};
 }
 
+// The host path of batch norm.  The boxed CPU fallback cannot be used for it: the schema of native_batch_norm does not
+// mark the running statistics as written, so the fallback would update copies and drop them (a module would train
+// with frozen statistics under host simulation, and on the device whenever a channel count sends it here).
+std::tuple<Tensor, Tensor, Tensor> batch_norm_on_cpu(const Tensor& input, const std::optional<Tensor>& weight,
+                                                   const std::optional<Tensor>& bias,
+                                                   const std::optional<Tensor>& running_mean,
+                                                   const std::optional<Tensor>& running_var, bool training, double momentum,
+                                                   double eps) {
+  auto host = [](const std::optional<Tensor>& t) {
+    return (t.has_value() && t->defined()) ? std::optional<Tensor>(t->cpu()) : std::optional<Tensor>();
+  };
+  std::optional<Tensor> rm = host(running_mean), rv = host(running_var);
+  auto r = at::native_batch_norm(input.cpu(), host(weight), host(bias), rm, rv, training, momentum, eps);
+  if (training && rm.has_value() && rv.has_value()) {
+    running_mean->copy_(*rm);
+    running_var->copy_(*rv);
+  }
+  const auto dev = input.device();
+  return {std::get<0>(r).to(dev), std::get<1>(r).to(dev), std::get<2>(r).to(dev)};
+}
+
 std::tuple<Tensor, Tensor, Tensor> k_native_batch_norm(const Tensor& input, const std::optional<Tensor>& weight,
                                                      const std::optional<Tensor>& bias,
                                                      const std::optional<Tensor>& running_mean,
@@ -132,7 +153,7 @@ std::tuple<Tensor, Tensor, Tensor> k_native_batch_norm(const Tensor& input, cons
                                                      double momentum, double eps) {
   return B200_DISPATCH("native_batch_norm",
                        batch_norm_device(input, weight, bias, running_mean, running_var, training, momentum, eps),
-                       B200_CPU(native_batch_norm, input, weight, bias, running_mean, running_var, training, momentum, eps));
+                       batch_norm_on_cpu(input, weight, bias, running_mean, running_var, training, momentum, eps));
 }
 
 std::tuple<Tensor, Tensor, Tensor> bn_legit(const Tensor& input, const std::optional<Tensor>& weight,
@@ -559,12 +580,17 @@ std::tuple<Tensor, Tensor, Tensor> k_native_layer_norm_backward(const Tensor& gr
 
 }  // namespace
 
+// The batch-norm forwards are registered under host simulation too: their host path is the one above, not the boxed
+// fallback (see there).
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
-  if (!device_kernels_enabled()) return;
   m.impl("native_batch_norm", TORCH_FN(k_native_batch_norm));
   m.impl("_native_batch_norm_legit", TORCH_FN(bn_legit));
   m.impl("_native_batch_norm_legit.no_stats", TORCH_FN(bn_legit_no_stats));
   m.impl("_native_batch_norm_legit_no_training", TORCH_FN(bn_legit_no_training));
+}
+
+TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+  if (!device_kernels_enabled()) return;
   m.impl("native_batch_norm_backward", TORCH_FN(k_native_batch_norm_backward));
   m.impl("native_layer_norm", TORCH_FN(k_native_layer_norm));
   m.impl("native_layer_norm_backward", TORCH_FN(k_native_layer_norm_backward));

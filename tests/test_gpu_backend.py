@@ -161,3 +161,17 @@ def test_profiler_lists_kernels_with_device_times(tmp_path):
     with profiler.kernel_trace() as kt2:
         pass
     assert kt2.events == []
+
+
+def test_batch_norm_with_a_channel_count_that_takes_the_host_path_updates_its_statistics():
+    """Five channels have no device kernel (vectors of four / eight channels): the operator runs on the host, and the
+    running statistics it updates there have to arrive in the module's buffers on the device."""
+    torch.manual_seed(0)
+    bn, ref = torch.nn.BatchNorm2d(5).to(DEV).train(), torch.nn.BatchNorm2d(5).train()
+    for _ in range(3):
+        x = torch.randn(8, 5, 6, 6) * 2 + 3
+        a, b = bn(x.to(DEV)), ref(x)
+        assert torch.allclose(a.cpu(), b, atol=1e-4)
+    assert torch.allclose(bn.running_mean.cpu(), ref.running_mean, atol=1e-5)
+    assert torch.allclose(bn.running_var.cpu(), ref.running_var, atol=1e-4)
+    assert int(bn.num_batches_tracked) == 3

@@ -52,3 +52,49 @@ def test_training_time_fusion_reproduces_the_module(name):
     fused.eval(); plain.eval()   # fused in training mode, evaluated afterwards: nothing of the mode may be frozen
     with torch.no_grad():
         assert (fused(x) - plain(x)).abs().max().item() <= 1e-5 * (plain(x).abs().max().item() + 1e-6)
+
+
+@pytest.mark.parametrize("name", ["resnet18", "mobilenet_v2", "densenet121", "efficientnet_b0"])
+def test_fused_operators_train_then_evaluate_like_the_stock_layers(name):
+    """The fused convolution / batch-norm functions themselves (host paths of their operators): two training
+    passes, then evaluation: outputs and every buffer (running statistics, batch counters) equal the stock model's."""
+    from catch_b200 import fusion
+
+    m = _model(name)
+    for mod in m.modules():
+        if isinstance(mod, torch.nn.Dropout) or type(mod).__name__ == "StochasticDepth":
+            mod.p = 0.0
+    fusion.fused_ops_on_host(True)
+    try:
+        fused = fuse_bn_act(copy.deepcopy(m)).to("blackwell").to(memory_format=torch.channels_last)
+        plain = copy.deepcopy(m)
+        fused.train(); plain.train()
+        for _ in range(2):
+            xb = torch.randn(4, 3, 64, 64)
+            plain(xb)
+            fused(xb.to("blackwell"))
+        for (k, a), (_, b) in zip(fused.named_buffers(), plain.named_buffers()):
+            assert (a.cpu().float() - b.float()).abs().max().item() <= 1e-4, k
+        fused.eval(); plain.eval()
+        x = torch.randn(2, 3, 64, 64)
+        with torch.no_grad():
+            a, b = fused(x.to("blackwell")).cpu(), plain(x)
+        assert (a - b).abs().max().item() <= 1e-4 * (b.abs().max().item() + 1e-6)
+    finally:
+        fusion.fused_ops_on_host(False)
+
+
+def test_batch_norm_updates_running_statistics_on_the_host_path():
+    """The boxed CPU fallback would update copies of the running statistics and drop them (their arguments are not
+    marked as written in the operator's schema): batch norm has a host path of its own."""
+    bn, ref = torch.nn.BatchNorm2d(5).to("blackwell").train(), torch.nn.BatchNorm2d(5).train()
+    for _ in range(3):
+        x = torch.randn(8, 5, 6, 6) * 2 + 3
+        a, b = bn(x.to("blackwell")), ref(x)
+        assert torch.allclose(a.cpu(), b, atol=1e-5)
+    assert torch.allclose(bn.running_mean.cpu(), ref.running_mean, atol=1e-6) and ref.running_mean.abs().min() > 0.1
+    assert torch.allclose(bn.running_var.cpu(), ref.running_var, atol=1e-5)
+    assert int(bn.num_batches_tracked) == 3
+    bn1 = torch.nn.BatchNorm1d(10).to("blackwell").train()
+    bn1(torch.randn(16, 10).to("blackwell") + 2)
+    assert bn1.running_mean.cpu().abs().min() > 0.05
