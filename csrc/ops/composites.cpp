@@ -1,6 +1,6 @@
 // Operators without a kernel of their own that are built from this backend's device kernels instead of taking the
 // boxed CPU fallback (two copies over PCIe and a host computation per call): var / std (+ _mean forms), dot, addmv,
-// flip, roll, elu_backward, hardswish_backward, logit, xlogy and the group-norm gradient.  The reference runs the same set through its
+// flip, roll, elu_backward, hardswish_backward, logit, xlogy, the group-norm gradient and the LSTM / GRU cells.  The reference runs the same set through its
 // kernel library (torch_mlu/csrc/aten/operators/cnnl/{std.cpp,var.cpp,dot.cpp,addmv.cpp,flip.cpp,roll.cpp}).
 // Every piece below is a device operator of this backend (reductions, element-wise kernels, index_select, GEMM), so
 // the data never leaves the device; accumulation happens in fp32 for 16-bit inputs.
@@ -263,7 +263,81 @@ std::tuple<Tensor, Tensor, Tensor> k_group_norm_backward(const Tensor& grad_out,
                                        c10::SymInt(HxW), group, mask));
 }
 
+// ---- LSTM / GRU cells --------------------------------------------------------------------------------------
+// torch's lstm / gru call these "fused cell" operators for every device that is not the CPU, and only CUDA ships
+// kernels for them (the boxed CPU fallback cannot help: there is no CPU kernel either), so without them nn.LSTM and
+// nn.GRU do not run on this device.  Here they are compositions of element-wise device kernels; the workspace that
+// the forward hands to the backward is this file's own format.
+//   LSTM: gates = input_gates + hidden_gates (+ biases) = [i | f | g | o]; cy = s(f) * cx + s(i) * tanh(g);
+//         hy = s(o) * tanh(cy); workspace = the four activated gates.
+std::tuple<Tensor, Tensor, Tensor> lstm_cell(const Tensor& input_gates, const Tensor& hidden_gates, const Tensor& cx,
+                                             const std::optional<Tensor>& input_bias, const std::optional<Tensor>& hidden_bias) {
+  Tensor gates = at::add(input_gates, hidden_gates);
+  if (input_bias.has_value() && input_bias->defined()) gates = at::add(gates, *input_bias);
+  if (hidden_bias.has_value() && hidden_bias->defined()) gates = at::add(gates, *hidden_bias);
+  auto ch = gates.chunk(4, -1);
+  Tensor i = at::sigmoid(ch[0]), f = at::sigmoid(ch[1]), g = at::tanh(ch[2]), o = at::sigmoid(ch[3]);
+  Tensor cy = at::add(at::mul(f, cx), at::mul(i, g));
+  Tensor hy = at::mul(o, at::tanh(cy));
+  return std::make_tuple(hy, cy, at::cat({i, f, g, o}, -1));
+}
+std::tuple<Tensor, Tensor, Tensor> lstm_cell_backward(const std::optional<Tensor>& grad_hy, const std::optional<Tensor>& grad_cy,
+                                                      const Tensor& cx, const Tensor& cy, const Tensor& workspace, bool has_bias) {
+  auto ch = workspace.chunk(4, -1);
+  const Tensor &i = ch[0], &f = ch[1], &g = ch[2], &o = ch[3];
+  Tensor tc = at::tanh(cy);
+  const bool has_h = grad_hy.has_value() && grad_hy->defined(), has_c = grad_cy.has_value() && grad_cy->defined();
+  Tensor gh = has_h ? *grad_hy : at::zeros_like(cy);
+  Tensor gc = at::mul(at::mul(gh, o), at::rsub(at::mul(tc, tc), Scalar(1.0)));  // through hy = o * tanh(cy)
+  if (has_c) gc = at::add(gc, *grad_cy);
+  auto dsig = [](const Tensor& s) { return at::mul(s, at::rsub(s, Scalar(1.0))); };
+  Tensor di = at::mul(at::mul(gc, g), dsig(i));
+  Tensor df = at::mul(at::mul(gc, cx), dsig(f));
+  Tensor dg = at::mul(at::mul(gc, i), at::rsub(at::mul(g, g), Scalar(1.0)));
+  Tensor d_o = at::mul(at::mul(gh, tc), dsig(o));
+  Tensor grad_gates = at::cat({di, df, dg, d_o}, -1);
+  Tensor grad_cx = at::mul(gc, f);
+  Tensor grad_bias = has_bias ? grad_gates.sum(std::vector<int64_t>{0}) : Tensor();
+  return std::make_tuple(grad_gates, grad_cx, grad_bias);
+}
+//   GRU: r = s(ig_r + hg_r), z = s(ig_z + hg_z), n = tanh(ig_n + r * hg_n), hy = n + z * (hx - n);
+//        workspace = [r | z | n | hx | hg_n].
+std::tuple<Tensor, Tensor> gru_cell(const Tensor& input_gates, const Tensor& hidden_gates, const Tensor& hx,
+                                    const std::optional<Tensor>& input_bias, const std::optional<Tensor>& hidden_bias) {
+  Tensor ig = (input_bias.has_value() && input_bias->defined()) ? at::add(input_gates, *input_bias) : input_gates;
+  Tensor hg = (hidden_bias.has_value() && hidden_bias->defined()) ? at::add(hidden_gates, *hidden_bias) : hidden_gates;
+  auto ic = ig.chunk(3, -1), hc = hg.chunk(3, -1);
+  Tensor r = at::sigmoid(at::add(ic[0], hc[0])), z = at::sigmoid(at::add(ic[1], hc[1]));
+  Tensor n = at::tanh(at::add(ic[2], at::mul(r, hc[2])));
+  Tensor hy = at::add(n, at::mul(z, at::sub(hx, n)));
+  return std::make_tuple(hy, at::cat({r, z, n, hx, hc[2]}, -1));
+}
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> gru_cell_backward(const Tensor& grad_hy, const Tensor& workspace, bool has_bias) {
+  auto ch = workspace.chunk(5, -1);
+  const Tensor &r = ch[0], &z = ch[1], &n = ch[2], &hx = ch[3], &hn = ch[4];
+  Tensor grad_hx = at::mul(grad_hy, z);
+  Tensor dz = at::mul(at::mul(grad_hy, at::sub(hx, n)), at::mul(z, at::rsub(z, Scalar(1.0))));
+  Tensor dn = at::mul(at::mul(grad_hy, at::rsub(z, Scalar(1.0))), at::rsub(at::mul(n, n), Scalar(1.0)));
+  Tensor dr = at::mul(at::mul(dn, hn), at::mul(r, at::rsub(r, Scalar(1.0))));
+  Tensor grad_input_gates = at::cat({dr, dz, dn}, -1);
+  Tensor grad_hidden_gates = at::cat({dr, dz, at::mul(dn, r)}, -1);
+  Tensor gib, ghb;
+  if (has_bias) {
+    gib = grad_input_gates.sum(std::vector<int64_t>{0});
+    ghb = grad_hidden_gates.sum(std::vector<int64_t>{0});
+  }
+  return std::make_tuple(grad_input_gates, grad_hidden_gates, grad_hx, gib, ghb);
+}
+
 }  // namespace
+
+// registered under host simulation as well: the boxed CPU fallback has no kernel to fall back to
+TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+  m.impl("_thnn_fused_lstm_cell", TORCH_FN(lstm_cell));
+  m.impl("_thnn_fused_lstm_cell_backward_impl", TORCH_FN(lstm_cell_backward));
+  m.impl("_thnn_fused_gru_cell", TORCH_FN(gru_cell));
+  m.impl("_thnn_fused_gru_cell_backward", TORCH_FN(gru_cell_backward));
+}
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   if (!device_kernels_enabled()) return;

@@ -175,3 +175,24 @@ def test_batch_norm_with_a_channel_count_that_takes_the_host_path_updates_its_st
     assert torch.allclose(bn.running_mean.cpu(), ref.running_mean, atol=1e-5)
     assert torch.allclose(bn.running_var.cpu(), ref.running_var, atol=1e-4)
     assert int(bn.num_batches_tracked) == 3
+
+
+def test_lstm_and_gru_on_the_device():
+    """nn.LSTM / nn.GRU: the fused-cell operators torch calls on non-CPU devices are composed from this backend's
+    element-wise kernels (fp32 matrix products run as TF32, hence the tolerance)."""
+    import copy
+
+    torch.manual_seed(0)
+    for ctor in (lambda: torch.nn.LSTM(16, 32, num_layers=2, batch_first=True, bidirectional=True), lambda: torch.nn.GRU(16, 32, batch_first=True)):
+        ref = ctor()
+        dev = copy.deepcopy(ref).to(DEV)
+        x = torch.randn(4, 10, 16)
+        xr, xd = x.clone().requires_grad_(), x.to(DEV).requires_grad_()
+        o_ref, _ = ref(xr)
+        o_dev, _ = dev(xd)
+        assert_tensors_equal(o_dev, o_ref, prec=1e-2, use_MSE=True)
+        o_ref.square().sum().backward()
+        o_dev.square().sum().backward()
+        assert_tensors_equal(xd.grad, xr.grad, prec=2e-2, use_MSE=True)
+        for p, q in zip(ref.parameters(), dev.parameters()):
+            assert_tensors_equal(q.grad, p.grad, prec=2e-2, use_MSE=True)

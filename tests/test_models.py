@@ -95,3 +95,38 @@ def test_fused_bert_layers_on_the_host_simulated_device():
         assert torch.allclose(yy.cpu(), torch.nn.functional.layer_norm(s.cpu(), (32,), norm.weight.cpu(), norm.bias.cpu()), atol=1e-4)
     finally:
         fusion.fused_ops_on_host(False)
+
+
+def test_lstm_and_gru_run_on_the_device():
+    """torch's lstm / gru call fused-cell operators on every non-CPU device, and only CUDA has kernels for them:
+    this backend composes them from its element-wise kernels.  Forward, backward and a training step against the CPU."""
+    import copy
+
+    torch.manual_seed(0)
+    for ctor, shape in ((lambda: torch.nn.LSTM(5, 7, num_layers=2, batch_first=True, bidirectional=True), (3, 6, 5)),
+                        (lambda: torch.nn.LSTM(5, 7, bias=False), (6, 3, 5)),
+                        (lambda: torch.nn.GRU(5, 7, num_layers=2, bidirectional=True), (6, 3, 5)),
+                        (lambda: torch.nn.GRU(5, 7, bias=False, batch_first=True), (3, 6, 5))):
+        ref = ctor()
+        dev = copy.deepcopy(ref).to("blackwell")
+        x = torch.randn(*shape)
+        xr, xd = x.clone().requires_grad_(), x.to("blackwell").requires_grad_()
+        o_ref, h_ref = ref(xr)
+        o_dev, h_dev = dev(xd)
+        assert torch.allclose(o_dev.cpu(), o_ref, atol=1e-5)
+        h_ref = h_ref if isinstance(h_ref, tuple) else (h_ref,)
+        h_dev = h_dev if isinstance(h_dev, tuple) else (h_dev,)
+        for a, b in zip(h_dev, h_ref):
+            assert torch.allclose(a.cpu(), b, atol=1e-5)
+        (o_ref.square().sum() + h_ref[-1].sum()).backward()
+        (o_dev.square().sum() + h_dev[-1].sum()).backward()
+        assert torch.allclose(xd.grad.cpu(), xr.grad, atol=1e-4)
+        for p, q in zip(ref.parameters(), dev.parameters()):
+            assert torch.allclose(q.grad.cpu(), p.grad, atol=1e-4)
+    # the single-step cells go the same way
+    cell, cell_d = torch.nn.LSTMCell(5, 7), None
+    cell_d = copy.deepcopy(cell).to("blackwell")
+    x = torch.randn(4, 5)
+    h, c = cell(x)
+    hd, cd = cell_d(x.to("blackwell"))
+    assert torch.allclose(hd.cpu(), h, atol=1e-5) and torch.allclose(cd.cpu(), c, atol=1e-5)
