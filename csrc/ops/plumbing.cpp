@@ -133,9 +133,31 @@ static void copy_d2d(const at::Tensor& src, const at::Tensor& dst, const OpScope
   launch_copy(src.expand_as(dst), dst, scope.stream());
 }
 
+static at::Tensor b200_copy_from(const at::Tensor& self, const at::Tensor& dst, bool non_blocking);
+
+// Lazy conjugate / negative views (x.conj(), the views autograd makes for complex gradients): the bits are metadata, the
+// memory holds the unconjugated values.  The raw values are copied and the mathematical difference between source
+// and destination is then applied to the destination in place.
+static at::Tensor copy_with_lazy_bits(const at::Tensor& self, const at::Tensor& dst, bool non_blocking) {
+  at::Tensor src = self, out = dst;
+  const bool flip_conj = src.is_conj() != out.is_conj(), flip_neg = src.is_neg() != out.is_neg();
+  if (src.is_conj()) src = at::_conj(src);      // the same memory without the bit
+  if (src.is_neg()) src = at::_neg_view(src);
+  if (out.is_conj()) out = at::_conj(out);
+  if (out.is_neg()) out = at::_neg_view(out);
+  b200_copy_from(src, out, non_blocking);
+  if (flip_conj && out.is_complex()) {
+    if (is_b200(out)) at::view_as_real(out).select(-1, 1).neg_();  // conjugate in place: negate the imaginary parts
+    else out.conj_physical_();
+  }
+  if (flip_neg) out.neg_();
+  return dst;
+}
+
 static at::Tensor b200_copy_from(const at::Tensor& self, const at::Tensor& dst, bool non_blocking) {
   TORCH_CHECK(self.defined() && dst.defined(), "copy_: undefined tensor");
   if (dst.numel() == 0) return dst;
+  if (self.is_conj() || self.is_neg() || dst.is_conj() || dst.is_neg()) return copy_with_lazy_bits(self, dst, non_blocking);
   const bool src_dev = is_b200(self), dst_dev = is_b200(dst);
   if (src_dev && dst_dev) {
     OpScope scope("copy_(D2D)", dst);
@@ -286,6 +308,17 @@ static at::Tensor b200_pin_memory(const at::Tensor& self, std::optional<at::Devi
 
 TORCH_LIBRARY_IMPL(_, PrivateUse1, m) { m.fallback(torch::CppFunction::makeFromBoxedFunction<&cpu_fallback>()); }
 
+// The generic kernels of the Conjugate / Negative keys materialise a lazy view by cloning it, and cloning ends in
+// _copy_from again: these two operators handle the bits themselves (copy_with_lazy_bits), so the keys let them through.
+TORCH_LIBRARY_IMPL(aten, Conjugate, m) {
+  m.impl("_copy_from", torch::CppFunction::makeFallthrough());
+  m.impl("_copy_from_and_resize", torch::CppFunction::makeFallthrough());
+}
+TORCH_LIBRARY_IMPL(aten, Negative, m) {
+  m.impl("_copy_from", torch::CppFunction::makeFallthrough());
+  m.impl("_copy_from_and_resize", torch::CppFunction::makeFallthrough());
+}
+
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("empty.memory_format", TORCH_FN(empty_memory_format));
   m.impl("empty_strided", TORCH_FN(b200_empty_strided));
@@ -296,6 +329,10 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("view", TORCH_FN(at::native::view));
   m.impl("_reshape_alias", TORCH_FN(at::native::_reshape_alias));
   m.impl("unfold", TORCH_FN(at::native::unfold));
+  // complex <-> real reinterpretation (rotary embeddings): pure metadata, and a view operator cannot go through the
+  // CPU fallback (the result would be a copy, not a view)
+  m.impl("view_as_real", TORCH_FN(at::native::view_as_real));
+  m.impl("view_as_complex", TORCH_FN(at::native::view_as_complex));
   m.impl("set_.source_Storage_storage_offset", TORCH_FN(set_source_storage_offset));
   m.impl("set_.source_Storage", TORCH_FN(set_source_storage));
   m.impl("set_.source_Tensor", TORCH_FN(set_source_tensor));
