@@ -186,3 +186,27 @@ def test_complex_views_and_lazy_conjugates():
     freqs = torch.polar(torch.ones(6, 4), torch.randn(6, 4))
     rope = lambda t, f: torch.view_as_real(torch.view_as_complex(t.float().reshape(*t.shape[:-1], -1, 2)) * f[None, :, None, :]).flatten(3)
     assert torch.allclose(rope(q.to(D), freqs.to(D)).cpu(), rope(q, freqs), atol=1e-5)
+
+
+def test_autocast_follows_the_stock_policy():
+    """Under torch.autocast("blackwell") matrix products and convolutions run in the autocast dtype; losses,
+    normalisations and the point-wise functions of the fp32 list run in fp32; softmax / sum / prod / cumsum / norm give
+    fp32 results unless the caller names a dtype; mixed inputs promote: the lists torch.autocast("cuda") uses."""
+    a, b = torch.randn(4, 8).to(D), torch.randn(8, 8).to(D)
+    img, w = torch.randn(2, 8, 6, 6).to(D), torch.randn(8, 8, 3, 3).to(D)
+    tgt = torch.zeros(4, dtype=torch.long).to(D)
+    for dt in (torch.bfloat16, torch.float16):
+        h = a.to(dt)
+        with torch.autocast(D, dtype=dt):
+            low = [a @ b, F.linear(a, b), F.conv2d(img, w), torch.bmm(a[None], b[None]), torch.addmm(a, a, b), torch.einsum("ij,jk->ik", a, b),
+                   F.conv_transpose2d(img, w), nn.LSTMCell(8, 4).to(D)(a)[0], F.scaled_dot_product_attention(a[None], a[None], a[None])]
+            f32 = [F.softmax(h, -1), F.log_softmax(h, -1), h.sum(), h.sum(0), h.prod(), h.cumsum(0), h.norm(), torch.linalg.vector_norm(h),
+                   F.layer_norm(h, (8,)), F.cross_entropy(h, tgt), F.mse_loss(h, h), h.pow(2.0), h.exp(), h.abs().log(), F.softplus(h),
+                   F.group_norm(img.to(dt), 2), F.cosine_similarity(h, h), F.binary_cross_entropy_with_logits(h, h.sigmoid()), F.l1_loss(h, h)]
+            promoted = [torch.cat([a, h]), torch.addcmul(a, h, a)]
+            kept = [h.sum(dtype=dt), F.softmax(h, -1, dtype=dt), torch.relu(h), h + h]
+        assert all(t.dtype == dt for t in low), [t.dtype for t in low]
+        assert all(t.dtype == torch.float32 for t in f32), [t.dtype for t in f32]
+        assert all(t.dtype == torch.float32 for t in promoted)
+        assert all(t.dtype == dt for t in kept)
+    assert F.softmax(a.half(), -1).dtype == torch.float16        # outside autocast nothing changes
