@@ -210,3 +210,34 @@ def test_autocast_follows_the_stock_policy():
         assert all(t.dtype == torch.float32 for t in promoted)
         assert all(t.dtype == dt for t in kept)
     assert F.softmax(a.half(), -1).dtype == torch.float16        # outside autocast nothing changes
+
+
+def test_training_utilities_on_the_device():
+    """Activation checkpointing (the dropout mask is replayed from the device generator's saved state), functorch
+    transforms, functional_call, weight averaging and parametrizations."""
+    from torch.optim.swa_utils import AveragedModel
+    from torch.utils.checkpoint import checkpoint
+
+    m = nn.Sequential(nn.Linear(8, 16), nn.Dropout(0.5), nn.ReLU(), nn.Linear(16, 4)).to(D)
+    x = torch.randn(5, 8).to(D).requires_grad_()
+    for reentrant in (False, True):
+        m.zero_grad()
+        torch.manual_seed(0)
+        a = checkpoint(m, x, use_reentrant=reentrant)
+        a.sum().backward()
+        g = m[0].weight.grad.clone()
+        m.zero_grad()
+        torch.manual_seed(0)
+        b = m(x)
+        b.sum().backward()
+        assert torch.allclose(a, b) and torch.allclose(g, m[0].weight.grad)
+    xd = x.detach()
+    assert torch.allclose(torch.vmap(lambda v: (v * v).sum())(xd).cpu(), (xd ** 2).sum(1).cpu())
+    assert torch.allclose(torch.func.grad(lambda v: (v ** 3).sum())(xd).cpu(), (3 * xd ** 2).cpu())
+    assert torch.func.functional_call(m.eval(), dict(m.named_parameters()), (x,)).shape == (5, 4)
+    avg = AveragedModel(m)
+    avg.update_parameters(m)
+    avg.update_parameters(m)
+    assert all(torch.allclose(p, q) for p, q in zip(avg.module.parameters(), m.parameters()))
+    lin = torch.nn.utils.parametrizations.weight_norm(nn.Linear(4, 4).to(D))
+    assert lin(torch.randn(2, 4).to(D)).shape == (2, 4)
