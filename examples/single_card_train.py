@@ -19,6 +19,7 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--model", default="resnet50")
     ap.add_argument("--image", type=int, default=224)
+    ap.add_argument("--checkpoint", default="checkpoint.pt", help="where the final checkpoint goes ('' = do not write one)")
     args = ap.parse_args()
     dev = torch.device("blackwell", 0)
     model = getattr(torchvision.models, args.model)().to(dev).to(memory_format=torch.channels_last)
@@ -33,7 +34,8 @@ def main():
         loss.backward()
         opt.step()
         print(f"iter {i}: loss {loss.item():.4f}")
-    torch.save({"epoch": 0, "model_state_dict": model.state_dict(), "optimizer_state_dict": opt.state_dict()}, "checkpoint.pt")
+    if args.checkpoint:
+        torch.save({"epoch": 0, "model_state_dict": model.state_dict(), "optimizer_state_dict": opt.state_dict()}, args.checkpoint)
 
 
 if __name__ == "__main__":

@@ -17,9 +17,14 @@ def _run(args, timeout=600):
     return r.stdout
 
 
-def test_single_card_training_example():
-    out = _run(["examples/single_card_train.py", "--iters", "2"] + SMALL)
+def test_single_card_training_example(tmp_path):
+    ckpt = str(tmp_path / "checkpoint.pt")
+    out = _run(["examples/single_card_train.py", "--iters", "2", "--checkpoint", ckpt] + SMALL)
     assert "loss" in out
+    import torch
+
+    saved = torch.load(ckpt, map_location="cpu")
+    assert {"epoch", "model_state_dict", "optimizer_state_dict"} <= set(saved)
 
 
 def test_eager_and_fusion_mode_inference_examples():
