@@ -190,9 +190,9 @@ def test_lstm_and_gru_on_the_device():
         xr, xd = x.clone().requires_grad_(), x.to(DEV).requires_grad_()
         o_ref, _ = ref(xr)
         o_dev, _ = dev(xd)
-        assert_tensors_equal(o_dev, o_ref, prec=1e-2, use_MSE=True)
+        assert_tensors_equal(o_dev, o_ref, prec=2e-2, use_MSE=True)
         o_ref.square().sum().backward()
         o_dev.square().sum().backward()
-        assert_tensors_equal(xd.grad, xr.grad, prec=2e-2, use_MSE=True)
+        assert_tensors_equal(xd.grad, xr.grad, prec=5e-2, use_MSE=True)
         for p, q in zip(ref.parameters(), dev.parameters()):
-            assert_tensors_equal(q.grad, p.grad, prec=2e-2, use_MSE=True)
+            assert_tensors_equal(q.grad, p.grad, prec=5e-2, use_MSE=True)
