@@ -102,6 +102,21 @@ class Workspace {
     }                                                                                       \
   }()
 
+// Raises, in the words of the stock backends, when an argument lives on another device than the first one: a kernel
+// handed a host pointer (or another device's) would otherwise read memory it must not.  Undefined / absent tensors pass.
+inline void same_device_one(const char* op, const at::Tensor& first, const at::Tensor& t) {
+  if (!t.defined()) return;
+  TORCH_CHECK(t.device() == first.device(), "Expected all tensors to be on the same device, but found at least two devices, ",
+              first.device(), " and ", t.device(), "! (when checking the arguments of ", op, ")");
+}
+inline void same_device_one(const char* op, const at::Tensor& first, const std::optional<at::Tensor>& t) {
+  if (t.has_value()) same_device_one(op, first, *t);
+}
+template <typename... Ts>
+inline void check_same_device(const char* op, const at::Tensor& first, const Ts&... rest) {
+  (same_device_one(op, first, rest), ...);
+}
+
 // Calls the boxed CPU fallback for one ATen overload with unboxed arguments,
 // e.g. B200_CPU(add_Tensor, self, other, alpha).
 #define B200_CPU(OP, ...) \

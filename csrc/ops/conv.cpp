@@ -55,6 +55,7 @@ Tensor in_format(const Tensor& t, bool channels_last) {
 Tensor convolution_overrideable(const Tensor& input, const Tensor& weight, const std::optional<Tensor>& bias,
                                 at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation,
                                 bool transposed, at::IntArrayRef output_padding, int64_t groups) {
+  check_same_device("convolution", input, weight, bias);
   return B200_DISPATCH("convolution",
                        in_format(conv_forward_device(input, weight, bias, stride, padding, dilation, transposed, output_padding,
                                                      groups),

@@ -643,6 +643,7 @@ std::tuple<at::Tensor, at::Tensor> conv_backward_fp32w_device(const at::Tensor& 
 // ([2 * Cout] fp64), accumulated in the epilogue, for the batch norm that follows it.
 std::tuple<at::Tensor, at::Tensor> conv_stats_device(const at::Tensor& input, const at::Tensor& weight,
                                                      at::IntArrayRef stride, at::IntArrayRef padding) {
+  check_same_device("conv2d_stats", input, weight);
   const int64_t ones[2] = {1, 1};
   if (use_cpu_path()) {
     // Host path: the stock convolution, then the sums of the (rounded) result as the epilogue would have produced them

@@ -66,6 +66,7 @@ static at::Tensor conv_bn_act(const at::Tensor& input, const at::Tensor& weight,
                               const std::optional<at::Tensor>& bias, const std::optional<at::Tensor>& residual,
                               at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation, int64_t groups,
                               int64_t act) {
+  check_same_device("conv_bn_act", input, weight, scale, bias, residual);
   auto compose = [&]() {
     at::Tensor y = at::conv2d(input, weight, {}, stride, padding, dilation, groups);
     if (scale.has_value() && scale->defined()) y = y * scale->to(y.scalar_type()).view({1, -1, 1, 1});

@@ -130,6 +130,7 @@ std::tuple<Tensor, Tensor> nll2d_fwd_device(const Tensor& self, const Tensor& ta
 std::tuple<Tensor, Tensor> k_nll_loss2d_forward(const Tensor& self, const Tensor& target, const std::optional<Tensor>& weight,
                                                 int64_t reduction, c10::SymInt ignore_index) {
   const int64_t ig = ignore_index.expect_int();
+  check_same_device("nll_loss2d", self, target, weight);
   return B200_DISPATCH("nll_loss2d_forward", nll2d_fwd_device(self, target, weight, reduction, ig),
                        B200_CPU_SYMINT(nll_loss2d_forward, self, target, weight, reduction, ignore_index));
 }

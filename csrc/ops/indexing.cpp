@@ -71,6 +71,7 @@ Tensor gather_device(const Tensor& self_in, int64_t dim, const Tensor& index_in)
   return index_in.dim() == 0 ? out.squeeze(0) : out;
 }
 Tensor k_gather(const Tensor& self, int64_t dim, const Tensor& index, bool sparse_grad) {
+  check_same_device("gather", self, index);
   return B200_DISPATCH("gather", gather_device(self, dim, index), B200_CPU(gather, self, dim, index, sparse_grad));
 }
 

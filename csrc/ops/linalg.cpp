@@ -107,6 +107,7 @@ Tensor mm_device(const Tensor& a, const Tensor& b) {
   return out;
 }
 Tensor b200_mm(const Tensor& a, const Tensor& b) {
+  check_same_device("mm", a, b);
   return B200_DISPATCH("mm", mm_device(a, b), B200_CPU(mm, a, b));
 }
 Tensor& mm_out(const Tensor& a, const Tensor& b, Tensor& out) {
@@ -141,6 +142,7 @@ Tensor addmm_device(const Tensor& self, const Tensor& m1, const Tensor& m2, cons
   return out;
 }
 Tensor b200_addmm(const Tensor& self, const Tensor& m1, const Tensor& m2, const Scalar& beta, const Scalar& alpha) {
+  check_same_device("addmm", m1, m2, self);
   return B200_DISPATCH("addmm", addmm_device(self, m1, m2, beta, alpha), B200_CPU(addmm, self, m1, m2, beta, alpha));
 }
 Tensor& addmm_out(const Tensor& self, const Tensor& m1, const Tensor& m2, const Scalar& beta, const Scalar& alpha,
@@ -166,7 +168,10 @@ Tensor bmm_device(const Tensor& a, const Tensor& b) {
   run_gemm(a, b, out, nullptr, nullptr, 1.0, 0.0, 0);
   return out;
 }
-Tensor b200_bmm(const Tensor& a, const Tensor& b) { return B200_DISPATCH("bmm", bmm_device(a, b), B200_CPU(bmm, a, b)); }
+Tensor b200_bmm(const Tensor& a, const Tensor& b) {
+  check_same_device("bmm", a, b);
+  return B200_DISPATCH("bmm", bmm_device(a, b), B200_CPU(bmm, a, b));
+}
 Tensor& bmm_out(const Tensor& a, const Tensor& b, Tensor& out) {
   Tensor r = b200_bmm(a, b);
   out.resize_(r.sizes());
@@ -185,6 +190,7 @@ Tensor baddbmm_device(const Tensor& self, const Tensor& a, const Tensor& b, cons
   return out;
 }
 Tensor b200_baddbmm(const Tensor& self, const Tensor& a, const Tensor& b, const Scalar& beta, const Scalar& alpha) {
+  check_same_device("baddbmm", a, b, self);
   return B200_DISPATCH("baddbmm", baddbmm_device(self, a, b, beta, alpha), B200_CPU(baddbmm, self, a, b, beta, alpha));
 }
 
@@ -193,6 +199,7 @@ Tensor b200_baddbmm(const Tensor& self, const Tensor& a, const Tensor& b, const 
 // Fused linear used by the fusion pass and the quantization-free fast path:
 // act(x @ w^T + bias); x [.., K], w [N, K].
 at::Tensor linear_act(const at::Tensor& x, const at::Tensor& w, const std::optional<at::Tensor>& bias, int64_t act) {
+  check_same_device("linear_act", x, w, bias);
   TORCH_CHECK(x.size(-1) == w.size(1), "linear_act: shape mismatch");
   auto x2 = x.reshape({-1, x.size(-1)});
   std::vector<int64_t> osz(x.sizes().begin(), x.sizes().end());
@@ -219,6 +226,7 @@ at::Tensor linear_act(const at::Tensor& x, const at::Tensor& w, const std::optio
 // head-split views of [batch, seq, heads * dim] activations multiply without being copied into [batch * heads, ...]
 // first, and `out` may itself be such a view (16-bit or, with accumulate, fp32 that is added to).
 at::Tensor gemm_nd(const at::Tensor& a, const at::Tensor& b, const std::optional<at::Tensor>& out_opt, double alpha) {
+  check_same_device("gemm_nd", a, b, out_opt);
   TORCH_CHECK(a.dim() == 4 && b.dim() == 4 && a.size(0) == b.size(0) && a.size(1) == b.size(1) && a.size(3) == b.size(2),
               "gemm_nd: expected [B1, B2, M, K] x [B1, B2, K, N], got ", a.sizes(), " and ", b.sizes());
   TORCH_CHECK(a.scalar_type() == b.scalar_type() && (a.scalar_type() == at::kBFloat16 || a.scalar_type() == at::kHalf),

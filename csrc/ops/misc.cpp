@@ -31,6 +31,7 @@ Tensor embedding_device(const Tensor& weight, const Tensor& indices, int64_t pad
   return out;
 }
 Tensor k_embedding(const Tensor& weight, const Tensor& indices, c10::SymInt padding_idx, bool scale, bool sparse) {
+  check_same_device("embedding", weight, indices);
   return B200_DISPATCH("embedding", embedding_device(weight, indices, padding_idx.expect_int()),
                        B200_CPU_SYMINT(embedding, weight, indices, padding_idx, scale, sparse));
 }
@@ -68,6 +69,7 @@ Tensor index_select_device(const Tensor& self, int64_t dim, const Tensor& index)
   return out.movedim(0, dim).contiguous();  // a contiguous result, as from the stock kernel
 }
 Tensor k_index_select(const Tensor& self, int64_t dim, const Tensor& index) {
+  check_same_device("index_select", self, index);
   return B200_DISPATCH("index_select", index_select_device(self, dim, index), B200_CPU(index_select, self, dim, index));
 }
 

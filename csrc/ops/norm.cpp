@@ -151,6 +151,7 @@ std::tuple<Tensor, Tensor, Tensor> k_native_batch_norm(const Tensor& input, cons
                                                      const std::optional<Tensor>& running_mean,
                                                      const std::optional<Tensor>& running_var, bool training,
                                                      double momentum, double eps) {
+  check_same_device("batch_norm", input, weight, bias, running_mean, running_var);
   return B200_DISPATCH("native_batch_norm",
                        batch_norm_device(input, weight, bias, running_mean, running_var, training, momentum, eps),
                        batch_norm_on_cpu(input, weight, bias, running_mean, running_var, training, momentum, eps));
@@ -405,6 +406,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> batch_norm_act(const at::Tensor& 
                                                               const std::optional<at::Tensor>& residual, bool training,
                                                               double momentum, double eps, int64_t act,
                                                               const std::optional<at::Tensor>& channel_sums) {
+  check_same_device("batch_norm_act", input, weight, bias, running_mean, running_var, residual, channel_sums);
   return batch_norm_act_impl(input, weight, bias, running_mean, running_var, residual, training, momentum, eps, act, channel_sums,
                              nullptr);
 }
@@ -534,6 +536,7 @@ std::tuple<Tensor, Tensor, Tensor> layer_norm_device(const Tensor& input, at::In
 std::tuple<Tensor, Tensor, Tensor> k_native_layer_norm(const Tensor& input, at::IntArrayRef normalized_shape,
                                                      const std::optional<Tensor>& weight,
                                                      const std::optional<Tensor>& bias, double eps) {
+  check_same_device("layer_norm", input, weight, bias);
   return B200_DISPATCH("native_layer_norm", layer_norm_device(input, normalized_shape, weight, bias, eps),
                        B200_CPU(native_layer_norm, input, normalized_shape, weight, bias, eps));
 }

@@ -94,6 +94,7 @@ std::tuple<Tensor, Tensor> nll_fwd_device(const Tensor& self, const Tensor& targ
 std::tuple<Tensor, Tensor> k_nll_loss_forward(const Tensor& self, const Tensor& target, const std::optional<Tensor>& weight,
                                               int64_t reduction, c10::SymInt ignore_index) {
   const int64_t ig = ignore_index.expect_int();
+  check_same_device("nll_loss", self, target, weight);
   return B200_DISPATCH("nll_loss_forward", nll_fwd_device(self, target, weight, reduction, ig),
                        B200_CPU_SYMINT(nll_loss_forward, self, target, weight, reduction, ignore_index));
 }
@@ -131,6 +132,7 @@ Tensor k_nll_loss_backward(const Tensor& grad, const Tensor& self, const Tensor&
 // by the incoming gradient.
 std::tuple<at::Tensor, at::Tensor> softmax_cross_entropy(const at::Tensor& logits, const at::Tensor& target,
                                                          int64_t ignore_index, double label_smoothing) {
+  check_same_device("softmax_cross_entropy", logits, target);
   TORCH_CHECK(logits.dim() == 2 && target.dim() == 1 && target.scalar_type() == at::kLong, "softmax_cross_entropy: logits [N, C], target [N] int64");
   if (use_cpu_path() || !f_ok(logits.scalar_type())) {
     at::Tensor x = logits.detach().to(at::kFloat);

@@ -245,3 +245,57 @@ def test_kernel_case_generator_and_replay(tmp_path, capfd):
     for level in ("L0", "l1", "L4"):
         with pytest.raises(ValueError):
             dumptool.dump_gencase(True, level)
+
+
+_MIXED_DEVICE_SCRIPT = r'''
+import torch, catch_b200
+F = torch.nn.functional
+D = "blackwell"
+w = torch.empty(3, 4, device=D)
+cases = {
+    "mm": lambda: torch.empty(2, 3) @ w,
+    "addmm": lambda: torch.addmm(torch.empty(4), torch.empty(2, 3, device=D), w),
+    "bmm": lambda: torch.bmm(torch.empty(1, 2, 3, device=D), torch.empty(1, 3, 4)),
+    "conv weight": lambda: F.conv2d(torch.empty(1, 3, 8, 8, device=D), torch.empty(4, 3, 3, 3)),
+    "embedding": lambda: F.embedding(torch.tensor([1]), w),
+    "index_select": lambda: w.index_select(0, torch.tensor([1])),
+    "gather": lambda: w.gather(0, torch.zeros(1, 4, dtype=torch.long)),
+    "nll_loss": lambda: F.nll_loss(w, torch.tensor([1, 2, 3])),
+    "layer_norm": lambda: F.layer_norm(w, (4,), torch.ones(4)),
+    "other device": lambda: w.t() @ torch.empty(3, 2, device="blackwell:1"),
+    "linear_act": lambda: torch.ops.catch_b200.linear_act(torch.empty(2, 4), w, None, 0),
+    "softmax_cross_entropy": lambda: torch.ops.catch_b200.softmax_cross_entropy(w, torch.tensor([1, 2, 3]), -100, 0.0),
+}
+bad = []
+for name, fn in cases.items():
+    try:
+        fn()
+        bad.append(name + ": no error")
+    except RuntimeError as e:
+        if "Expected all tensors to be on the same device" not in str(e):
+            bad.append(name + ": " + str(e)[:100])
+print("BAD", bad)
+'''
+
+
+def test_kernels_that_take_raw_pointers_refuse_arguments_on_another_device():
+    """The matrix-product, convolution, normalisation, look-up and loss kernels receive raw pointers: an argument on
+    the host or on another device must raise (in the stock backends' words) before a kernel could read it.  The
+    kernels are registered without a GPU by the registration-check switch; the check runs in front of the launch."""
+    import os
+    import subprocess
+    import sys
+
+    env = dict(os.environ, CATCH_B200_BACKEND="hostsim", CATCH_B200_CHECK_REGISTRATIONS="1")
+    r = subprocess.run([sys.executable, "-c", _MIXED_DEVICE_SCRIPT], env=env, capture_output=True, text=True, timeout=600,
+                       cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "BAD []" in r.stdout, r.stdout[-2000:]
+    # batch normalisation is registered on the host-simulated device as it is: checked in this process
+    import pytest
+    import torch
+
+    import catch_b200  # noqa: F401
+
+    with pytest.raises(RuntimeError, match="same device"):
+        torch.nn.BatchNorm2d(4).to("blackwell")(torch.empty(2, 4, 3, 3))

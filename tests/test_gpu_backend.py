@@ -196,3 +196,13 @@ def test_lstm_and_gru_on_the_device():
         assert_tensors_equal(xd.grad, xr.grad, prec=5e-2, use_MSE=True)
         for p, q in zip(ref.parameters(), dev.parameters()):
             assert_tensors_equal(q.grad, p.grad, prec=5e-2, use_MSE=True)
+
+
+def test_an_argument_on_the_host_raises_instead_of_reaching_a_kernel():
+    w = torch.randn(3, 4, device=DEV)
+    for fn in (lambda: torch.randn(2, 3) @ w, lambda: torch.nn.functional.embedding(torch.tensor([1]), w),
+               lambda: torch.nn.functional.nll_loss(w, torch.tensor([1, 2, 3])),
+               lambda: torch.nn.functional.conv2d(torch.randn(1, 3, 8, 8, device=DEV), torch.randn(4, 3, 3, 3)),
+               lambda: torch.nn.BatchNorm2d(4).to(DEV)(torch.randn(2, 4, 3, 3))):
+        with pytest.raises(RuntimeError, match="same device"):
+            fn()
