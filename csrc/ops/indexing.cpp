@@ -98,6 +98,7 @@ Tensor& scatter_device_(Tensor& self, int64_t dim, const Tensor& index_in, const
   return self;
 }
 Tensor& k_scatter_src_(Tensor& self, int64_t dim, const Tensor& index, const Tensor& src) {
+  check_same_device("scatter", self, index, src);
   B200_DISPATCH("scatter_.src", (void)scatter_device_(self, dim, index, src, false), (void)B200_CPU(scatter__src, self, dim, index, src));
   return self;
 }
@@ -106,6 +107,7 @@ Tensor k_scatter_src(const Tensor& self, int64_t dim, const Tensor& index, const
   return k_scatter_src_(out, dim, index, src);
 }
 Tensor& k_scatter_value_(Tensor& self, int64_t dim, const Tensor& index, const at::Scalar& value) {
+  check_same_device("scatter", self, index);
   B200_DISPATCH("scatter_.value", (void)scatter_device_(self, dim, index, at::full(index.sizes(), value, self.options()), false),
                 (void)B200_CPU(scatter__value, self, dim, index, value));
   return self;
@@ -115,6 +117,7 @@ Tensor k_scatter_value(const Tensor& self, int64_t dim, const Tensor& index, con
   return k_scatter_value_(out, dim, index, value);
 }
 Tensor& k_scatter_add_(Tensor& self, int64_t dim, const Tensor& index, const Tensor& src) {
+  check_same_device("scatter_add", self, index, src);
   B200_DISPATCH("scatter_add_", (void)scatter_device_(self, dim, index, src, true), (void)B200_CPU(scatter_add_, self, dim, index, src));
   return self;
 }
@@ -160,6 +163,7 @@ Tensor masked_select_device(const Tensor& self, const Tensor& mask) {
   return take_flat(s->contiguous().view({-1}), idx, scope);
 }
 Tensor k_masked_select(const Tensor& self, const Tensor& mask) {
+  check_same_device("masked_select", self, mask);
   return B200_DISPATCH("masked_select", masked_select_device(self, mask), B200_CPU(masked_select, self, mask));
 }
 
@@ -181,7 +185,8 @@ LinearIndex linearize(const Tensor& self, const c10::List<std::optional<Tensor>>
       // a mask over k dimensions is k index tensors
       for (int64_t d = 0; d < t.dim(); ++d)
         TORCH_CHECK_INDEX(t.size(d) == self.size((int64_t)per_dim.size() + d), "index: mask shape does not match the indexed tensor");
-      Tensor nz = nonzero_device(t.scalar_type() == at::kBool ? t : t.ne(0));
+      Tensor m = t.device() == self.device() ? t : t.to(self.device());  // a mask on the host is accepted, like an index
+      Tensor nz = nonzero_device(m.scalar_type() == at::kBool ? m : m.ne(0));
       for (int64_t d = 0; d < t.dim(); ++d) per_dim.push_back(nz.select(1, d));
     } else {
       TORCH_CHECK(t.scalar_type() == at::kLong || t.scalar_type() == at::kInt, "index: tensors used as indices must be long, int, byte or bool");
@@ -393,6 +398,7 @@ Tensor k_upsample_bilinear2d_backward(const Tensor& grad, c10::SymIntArrayRef os
 // ---- NMS -----------------------------------------------------------------------------------
 // Returns the indices of the boxes that survive, in order of descending score.
 Tensor nms(const Tensor& boxes, const Tensor& scores, double iou_threshold) {
+  check_same_device("nms", boxes, scores);
   TORCH_CHECK(boxes.dim() == 2 && boxes.size(1) == 4 && scores.dim() == 1 && scores.size(0) == boxes.size(0),
               "nms: boxes must be [N, 4] and scores [N]");
   const int64_t n = boxes.size(0);

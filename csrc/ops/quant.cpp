@@ -277,6 +277,7 @@ Tensor fake_quant_rows(const Tensor& w) {
 Tensor qconv2d(const Tensor& input, const Tensor& weight, const std::optional<Tensor>& bias, at::IntArrayRef padding,
                at::IntArrayRef stride, at::IntArrayRef dilation, int64_t groups, const std::optional<Tensor>& q_scale,
                const std::optional<Tensor>& q_mode) {
+  check_same_device("qconv2d", input, weight, bias);
   if (!quant_active(q_scale, q_mode)) return at::conv2d(input, weight, bias, stride, padding, dilation, groups);
   const int64_t mode = mode_of(q_mode);
   auto reference = [&]() {
@@ -306,6 +307,7 @@ Tensor qconv2d(const Tensor& input, const Tensor& weight, const std::optional<Te
 Tensor qconv_act(const Tensor& input, const Tensor& weight, const std::optional<Tensor>& bias, at::IntArrayRef padding,
                  at::IntArrayRef stride, at::IntArrayRef dilation, int64_t groups, const std::optional<Tensor>& q_scale,
                  const std::optional<Tensor>& q_mode, const std::optional<Tensor>& residual, int64_t act, double out_scale) {
+  check_same_device("qconv_act", input, weight, bias, residual);
   const bool pre_quantized = input.scalar_type() == at::kChar;
   const bool quant = quant_active(q_scale, q_mode);
   TORCH_CHECK(quant || !pre_quantized, "catch_b200::qconv_act: an int8 input needs the layer's quantization scale");
@@ -342,6 +344,7 @@ Tensor qconv_act(const Tensor& input, const Tensor& weight, const std::optional<
 
 Tensor qlinear(const Tensor& input, const Tensor& weight, const std::optional<Tensor>& bias,
                const std::optional<Tensor>& q_scale, const std::optional<Tensor>& q_mode) {
+  check_same_device("qlinear", input, weight, bias);
   if (!quant_active(q_scale, q_mode)) return at::linear(input, weight, bias);
   const int64_t mode = mode_of(q_mode);
   auto reference = [&]() {

@@ -260,6 +260,9 @@ cases = {
     "embedding": lambda: F.embedding(torch.tensor([1]), w),
     "index_select": lambda: w.index_select(0, torch.tensor([1])),
     "gather": lambda: w.gather(0, torch.zeros(1, 4, dtype=torch.long)),
+    "scatter": lambda: w.scatter(0, torch.zeros(1, 4, dtype=torch.long), 1.0),
+    "scatter_add": lambda: w.scatter_add(0, torch.zeros(1, 4, dtype=torch.long, device=D), torch.ones(1, 4)),
+    "masked_select": lambda: w.masked_select(torch.ones(3, 4, dtype=torch.bool)),
     "nll_loss": lambda: F.nll_loss(w, torch.tensor([1, 2, 3])),
     "layer_norm": lambda: F.layer_norm(w, (4,), torch.ones(4)),
     "other device": lambda: w.t() @ torch.empty(3, 2, device="blackwell:1"),
