@@ -18,8 +18,10 @@ using at::Tensor;
 
 bool f_ok(at::ScalarType t) { return t == at::kFloat || t == at::kBFloat16 || t == at::kHalf; }
 
-Tensor embedding_device(const Tensor& weight, const Tensor& indices, int64_t padding_idx) {
-  TORCH_CHECK(weight.dim() == 2 && indices.scalar_type() == at::kLong, "b200 embedding: weight must be 2-D and indices int64");
+Tensor embedding_device(const Tensor& weight, const Tensor& indices_in, int64_t padding_idx) {
+  TORCH_CHECK(weight.dim() == 2 && (indices_in.scalar_type() == at::kLong || indices_in.scalar_type() == at::kInt),
+              "b200 embedding: weight must be 2-D and indices int64 or int32");
+  const Tensor indices = indices_in.scalar_type() == at::kInt ? indices_in.to(at::kLong) : indices_in;  // the kernel reads int64
   OpScope scope("embedding", weight);
   Tensor w = weight.contiguous(), idx = indices.contiguous();
   std::vector<int64_t> shape(indices.sizes().begin(), indices.sizes().end());
@@ -35,7 +37,8 @@ Tensor k_embedding(const Tensor& weight, const Tensor& indices, c10::SymInt padd
   return B200_DISPATCH("embedding", embedding_device(weight, indices, padding_idx.expect_int()),
                        B200_CPU_SYMINT(embedding, weight, indices, padding_idx, scale, sparse));
 }
-Tensor embedding_bwd_device(const Tensor& grad, const Tensor& indices, int64_t num_weights, int64_t padding_idx, bool scale) {
+Tensor embedding_bwd_device(const Tensor& grad, const Tensor& indices_in, int64_t num_weights, int64_t padding_idx, bool scale) {
+  const Tensor indices = indices_in.scalar_type() == at::kInt ? indices_in.to(at::kLong) : indices_in;
   TORCH_CHECK(!scale && f_ok(grad.scalar_type()) && indices.scalar_type() == at::kLong, "b200 embedding_backward: unsupported arguments");
   OpScope scope("embedding_dense_backward", grad);
   Tensor g = grad.contiguous().view({-1, grad.size(-1)}), idx = indices.contiguous();
@@ -52,8 +55,10 @@ Tensor k_embedding_dense_backward(const Tensor& grad, const Tensor& indices, c10
                        B200_CPU_SYMINT(embedding_dense_backward, grad, indices, num_weights, padding_idx, scale));
 }
 
-Tensor index_select_device(const Tensor& self, int64_t dim, const Tensor& index) {
-  TORCH_CHECK(index.dim() <= 1 && index.scalar_type() == at::kLong, "b200 index_select: index must be a 1-D int64 tensor");
+Tensor index_select_device(const Tensor& self, int64_t dim, const Tensor& index_in) {
+  TORCH_CHECK(index_in.dim() <= 1 && (index_in.scalar_type() == at::kLong || index_in.scalar_type() == at::kInt),
+              "b200 index_select: index must be a 1-D int64 or int32 tensor");
+  const Tensor index = index_in.scalar_type() == at::kInt ? index_in.to(at::kLong) : index_in;  // the kernel reads int64
   dim = at::maybe_wrap_dim(dim, self.dim());
   OpScope scope("index_select", self);
   if (self.dim() == 0) return self.clone();

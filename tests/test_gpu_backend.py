@@ -206,3 +206,15 @@ def test_an_argument_on_the_host_raises_instead_of_reaching_a_kernel():
                lambda: torch.nn.BatchNorm2d(4).to(DEV)(torch.randn(2, 4, 3, 3))):
         with pytest.raises(RuntimeError, match="same device"):
             fn()
+
+
+def test_embedding_and_index_select_take_int32_indices():
+    w = torch.randn(10, 6)
+    idx = torch.tensor([[1, 9], [0, 3]], dtype=torch.int32)
+    dw = w.to(DEV).requires_grad_()
+    out = torch.nn.functional.embedding(idx.to(DEV), dw)
+    assert torch.equal(out.detach().cpu(), torch.nn.functional.embedding(idx, w))
+    out.sum().backward()
+    ref = torch.zeros(10, 6).index_add_(0, idx.flatten().long(), torch.ones(4, 6))
+    assert torch.equal(dw.grad.cpu(), ref)
+    assert torch.equal(w.to(DEV).index_select(1, torch.tensor([5, 0], dtype=torch.int32, device=DEV)).cpu(), w[:, [5, 0]])
