@@ -21,6 +21,10 @@ from dataclasses import dataclass, field
 from typing import List, Tuple
 
 RULES = [(re.compile("cuda"), "blackwell"), (re.compile("nccl"), "bwccl")]
+# Call sites the rewrite cannot make work: they are left as they are and listed in the report.
+NEEDS_ATTENTION = [(re.compile(r"\bnn\.DataParallel\("),
+                    "nn.DataParallel drives several devices from one process through torch.cuda only: use one process per "
+                    "device with DistributedDataParallel (or catch_b200.parallel.FusedDataParallel) on the bwccl backend")]
 STRICT_RULES = [(re.compile("CUDA"), "BLACKWELL"), (re.compile("gpu"), "blackwell"), (re.compile("GPU"), "BLACKWELL")]
 
 
@@ -51,6 +55,9 @@ def convert_source(text: str, rel_path: str, strict: bool, report: Report) -> st
             out.append(line.replace("import torch", "import catch_b200"))
             report.add(rel_path, n, 'add "import catch_b200"')
             continue
+        for pat, why in NEEDS_ATTENTION:
+            if pat.search(line):
+                report.add(rel_path, n, "needs attention: " + why)
         new = line
         for pat, repl in rules:
             new = pat.sub(repl, new)

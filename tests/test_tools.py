@@ -196,3 +196,14 @@ def test_converted_ddp_script_runs_on_two_ranks(tmp_path):
     import torch
 
     assert set(torch.load(ckpt, map_location="cpu")) == {"0.weight", "0.bias", "2.weight", "2.bias"}
+
+
+def test_converter_lists_data_parallel_call_sites_as_needing_attention():
+    """nn.DataParallel works for CUDA tensors only: the converter leaves the call as it is and says so in the report;
+    DistributedDataParallel lines get no such note."""
+    report = gpu2blackwell.Report()
+    src = "import torch\nm = torch.nn.DataParallel(net.cuda())\nd = torch.nn.parallel.DistributedDataParallel(net)\n"
+    out = gpu2blackwell.convert_source(src, "train.py", False, report)
+    assert "torch.nn.DataParallel(net.blackwell())" in out
+    notes = [e for e in report.entries if e[2].startswith("needs attention")]
+    assert [(p, n) for p, n, _ in notes] == [("train.py", 2)] and "DistributedDataParallel" in notes[0][2]
